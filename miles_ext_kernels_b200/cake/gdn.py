@@ -1,0 +1,46 @@
+"""Chunked gated delta rule (GDN), forward and backward, K = V = 128, packed sequences and context parallelism, on
+hand-written sm_100a kernels.
+
+:func:`chunk_gated_delta_rule` has the signature and autograd contract of FLA's ``chunk_gated_delta_rule`` (v0.5.2),
+as the reference's entry point does (reference: miles_ext_kernels/cake/gdn.py:33-65,
+miles_ext_kernels/cake/_impl/gdn/ops.py:2420-2501).  A call runs, by its ``cp_context``:
+
+- no ``cp_context``: the single-GPU kernels (forward: prep, WY transform, state scan, output; backward: adjoint scan
+  and the fused gradient tail);
+- a :class:`KcpContext` (:func:`build_kcp_context`): this rank's contiguous slice of every sequence, with the chunk
+  state passed rank to rank (:func:`kcp_chunk_gated_delta_rule` calls it directly).
+
+Under any ``cp_context`` the contract is FLA's: no initial state, no final state, and the context's boundaries.
+
+Both variants (``det``, ``fast``) run the same kernels here: every reduction has a fixed order and no kernel uses a
+value atomic, so identical inputs give identical bits on the same GPU model and build.  ``--cake-gdn-recompute-state``
+recomputes the WY and state tapes in the backward instead of keeping them.
+
+Importing this module imports neither torch nor the kernels.
+"""
+
+from ._runtime.spec import Flag, OpSpec, lazy_exports
+
+OP = OpSpec(
+    name="gdn",
+    summary="chunked gated delta rule, forward + backward, K = V = 128, packed sequences, context parallelism",
+    variants=("det", "fast"),
+    selected_by=(("linear_attention_backend", "cake"),),
+    packages=("libmek_b200",),
+    exports=("KcpContext", "build_kcp_context", "chunk_gated_delta_rule", "kcp_chunk_gated_delta_rule"),
+    flags=(
+        Flag(
+            "--cake-gdn-recompute-state",
+            dict(
+                action="store_true",
+                default=False,
+                help=(
+                    "Recompute w/u/h/v_new in the backward instead of keeping them on the autograd tape: less "
+                    "activation memory, more backward time. The gradients are the bits of the saved backward."
+                ),
+            ),
+        ),
+    ),
+)
+
+__all__, __getattr__, __dir__ = lazy_exports(__name__, OP)

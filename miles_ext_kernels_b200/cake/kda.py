@@ -1,0 +1,41 @@
+"""Packed KDA (Kimi Delta Attention: the gated delta rule with a per-key-channel decay), chunk 64, K = V = 128,
+1 to 64 heads per call, per-document zero initial state, forward and backward, on hand-written sm_100a kernels.
+
+The entry points and their argument meaning follow the reference's op (reference: miles_ext_kernels/cake/kda.py:53-78,
+miles_ext_kernels/cake/_impl/kda/ops.py:142-234).  miles selects the op with ``--kda-backend cake``, builds the library
+when a layer is built (``cake.prebuild("kda", num_heads=...)``) and calls :func:`chunk_kda` in its forward.
+
+Importing this module imports neither torch nor the implementation.
+"""
+
+from argparse import Namespace
+
+from ._runtime.spec import OpSpec, lazy_exports
+
+
+def _validate(args: Namespace) -> None:
+    """Under ``--kda-backend cake``: no context parallelism (miles shards every document over the ranks, the kernels
+    run whole documents of one packed row) and the packed ``thd`` layout only."""
+    ranks = getattr(args, "context_parallel_size", None) or 1
+    if ranks > 1:
+        raise ValueError(
+            f"--kda-backend cake does not support context parallelism yet (--context-parallel-size {ranks}); use "
+            "--kda-backend fla"
+        )
+    layout = getattr(args, "qkv_format", "thd")
+    if layout != "thd":
+        raise ValueError(f"--kda-backend cake needs --qkv-format thd (one packed sequence), got {layout!r}")
+
+
+OP = OpSpec(
+    name="kda",
+    summary="packed KDA chunked training, forward + backward, K = V = 128, 1 to 64 heads",
+    variants=("det", "fast"),
+    cli_variants=("det",),
+    selected_by=(("kda_backend", "cake"),),
+    packages=("libmek_b200",),
+    exports=("DEFAULT_SCALE", "MAX_HEADS", "chunk_kda", "chunk_kda_bwd", "chunk_kda_fwd"),
+    validate=_validate,
+)
+
+__all__, __getattr__, __dir__ = lazy_exports(__name__, OP)

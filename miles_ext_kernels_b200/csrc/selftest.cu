@@ -1,0 +1,102 @@
+// Self-test of the tcgen05 building block and the library-wide C-ABI helpers (version stamp, error text, device gate).
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace mek {
+
+char* error_buffer() {
+  static thread_local char text[512] = {0};
+  return text;
+}
+
+// Operand images are copied verbatim into shared memory; the caller's descriptors decide how the tensor core reads
+// them.  128 threads: thread t dumps tensor-memory lane t.
+__global__ void __launch_bounds__(128) selftest_umma_kernel(const uint4* a_img, int a_bytes, const uint4* b_img,
+                                                            int b_bytes, uint64_t a_desc, uint64_t b_desc,
+                                                            const int32_t* a_off, const int32_t* b_off, int nk,
+                                                            uint32_t idesc, int ncols, float* out, int32_t* status) {
+  extern __shared__ uint8_t raw[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  uint4* a_s = reinterpret_cast<uint4*>(base);
+  uint4* b_s = reinterpret_cast<uint4*>(base + 65536);
+  const uint32_t tid = threadIdx.x, warp = tid >> 5;
+
+  for (int i = tid; i < a_bytes / 16; i += 128) a_s[i] = a_img[i];
+  for (int i = tid; i < b_bytes / 16; i += 128) b_s[i] = b_img[i];
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 256);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (tid == 0) {
+    const uint32_t a0 = smem_u32(a_s), b0 = smem_u32(b_s);
+    for (int k = 0; k < nk; ++k) {
+      const uint64_t da = a_desc | uint64_t(((a0 + uint32_t(a_off[k])) >> 4) & 0x3FFFu);
+      const uint64_t db = b_desc | uint64_t(((b0 + uint32_t(b_off[k])) >> 4) & 0x3FFFu);
+      umma_f16(tmem, da, db, idesc, k > 0 ? 1u : 0u);
+    }
+    umma_commit(&bar);
+  }
+  const bool done = mbar_wait(&bar, 0);
+  tc_fence_after();
+  if (done) {
+    for (int c0 = 0; c0 < ncols; c0 += 16) {
+      float v[16];
+      tmem_ld16(tmem_addr(tmem, warp, c0), v);
+      tmem_ld_wait();
+      for (int j = 0; j < 16; ++j) out[tid * ncols + c0 + j] = v[j];
+    }
+  } else if (tid == 0) {
+    *status = kDevWaitTimeout;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+}  // namespace mek
+
+extern "C" {
+
+int mek_build_cuda_version(void) { return CUDART_VERSION; }
+
+const char* mek_last_error(void) { return mek::error_buffer(); }
+
+int mek_check_device(int device) {
+  int major = 0, minor = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device) != cudaSuccess) {
+    cudaGetLastError();
+    return mek::fail(MEK_ERR_CUDA, "cannot query the compute capability of device %d", device);
+  }
+  if (major != 10 || minor != 0)
+    return mek::fail(MEK_ERR_UNSUPPORTED, "the kernels are built for sm_100a (B200), not compute capability %d.%d",
+                     major, minor);
+  return MEK_OK;
+}
+
+int mek_selftest_umma(const void* a_img, int a_bytes, const void* b_img, int b_bytes, uint64_t a_desc, uint64_t b_desc,
+                      const int32_t* a_off, const int32_t* b_off, int nk, uint32_t idesc, int ncols, float* out,
+                      int32_t* status, void* stream) {
+  using namespace mek;
+  if (a_bytes <= 0 || b_bytes <= 0 || a_bytes > 65536 || b_bytes > 65536 || a_bytes % 16 || b_bytes % 16)
+    return fail(MEK_ERR_INVALID, "selftest: operand images must be 16..65536 bytes, multiples of 16");
+  if (ncols < 16 || ncols > 256 || ncols % 16 || nk < 1 || nk > 64)
+    return fail(MEK_ERR_INVALID, "selftest: ncols in 16..256 (multiple of 16), nk in 1..64");
+  const size_t smem = 2 * 65536 + 1024;
+  if (int rc = want_smem(selftest_umma_kernel, smem, "selftest")) return rc;
+  selftest_umma_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(a_img), a_bytes, static_cast<const uint4*>(b_img), b_bytes, a_desc, b_desc, a_off,
+      b_off, nk, idesc, ncols, out, status);
+  return launched("selftest");
+}
+
+}  // extern "C"

@@ -1,0 +1,231 @@
+// Blackwell (sm_100a) primitives shared by the gated-delta-rule kernels: tensor-memory allocation, shared-memory
+// matrix descriptors, tcgen05.mma issue/commit, bounded mbarrier waits, tensor-memory loads, and the 128-byte
+// swizzled tile layout every operand tile uses.
+//
+// Tile layout. An operand tile of R rows x 64 bf16 columns ("block") occupies R x 128 bytes; the 16-byte chunk c of
+// row r sits at byte  r*128 + ((c ^ (r & 7)) << 4)  (the SWIZZLE_128B pattern of TMA and of the UMMA descriptors).
+// A 128-column tile is two such blocks, `block_stride` bytes apart.  One block serves two roles without a copy:
+//   * K-major operand  (contraction along the 64 contiguous columns): descriptor SBO = 1024 B (8 rows), k-step of
+//     16 columns = +32 B on the start address;
+//   * MN-major operand (contraction along the rows): descriptor SBO = 1024 B (8 rows of the contraction),
+//     LBO = block_stride (next 64 columns of the M/N extent), k-step of 16 rows = +2048 B.
+// Blocks start on 1024-byte boundaries.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mek {
+
+// ---------------------------------------------------------------------------------------------------------------
+// small PTX wrappers
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// Generic-proxy writes to shared memory become visible to the async proxy (tcgen05.mma operand reads, TMA).
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// Spin limit of every wait in these kernels: ~2^22 polls with a short back-off is of the order of a second, far
+// beyond any legitimate MMA latency.  A wait that runs out returns false; the kernel then records an error status
+// and leaves through its normal exit (tensor memory freed), so the context stays usable.
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (spin > 64) __nanosleep(64);
+  }
+  return false;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// tensor memory
+// ---------------------------------------------------------------------------------------------------------------
+// One warp allocates `ncols` (power of two, 32..512) columns; the base address lands in *slot (shared memory).
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// Thread `lane` of warp w reads 32 consecutive fp32 columns of tensor-memory lane 32*(w%4)+lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// The tensor-memory address of (lane quadrant of this warp, column): bits 31..16 lane, 15..0 column.
+__device__ __forceinline__ uint32_t tmem_addr(uint32_t base, uint32_t warp, uint32_t col) {
+  return base + (((warp & 3u) * 32u) << 16) + col;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// descriptors
+// ---------------------------------------------------------------------------------------------------------------
+// Instruction descriptor of tcgen05.mma.kind::f16 with bf16 operands and an fp32 accumulator.
+//   bits 4..5 accumulator format (1 = f32); 7..9 A format (1 = bf16); 10..12 B format (1 = bf16); 13 negate A;
+//   14 negate B; 15 A major (1 = MN); 16 B major (1 = MN); 17..22 N >> 3; 24..28 M >> 4.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool a_mn_major, bool b_mn_major, bool neg_a = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(neg_a) << 13) | (uint32_t(a_mn_major) << 15) |
+         (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+// Shared-memory matrix descriptor, SWIZZLE_128B: bits 0..13 start address >> 4; 16..29 leading byte offset >> 4;
+// 32..45 stride byte offset >> 4; 46..47 descriptor version (1 on sm_100); 61..63 layout type (2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= uint64_t((saddr >> 4) & 0x3FFFu);
+  d |= uint64_t((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= uint64_t((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(2) << 61;
+  return d;
+}
+
+// D[tmem] (+)= A * B, one instruction (K = 16 bf16).  Issued by ONE thread.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrive on `bar` once every tcgen05.mma issued so far by this thread has completed (implies
+// tcgen05.fence::before_thread_sync).
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// swizzled tiles
+// ---------------------------------------------------------------------------------------------------------------
+constexpr uint32_t kBlockCols = 64;     // bf16 columns of one swizzled block (128 bytes)
+constexpr uint32_t kSbo = 1024;         // 8 rows x 128 bytes
+
+// Byte offset of the 16-byte chunk `chunk` (0..7) of row `row` inside a block.
+__device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk) {
+  return row * 128u + ((chunk ^ (row & 7u)) << 4);
+}
+
+// An operand view of a tile made of SWIZZLE_128B blocks.
+struct Operand {
+  uint32_t saddr;         // shared address of block 0 (1024-byte aligned)
+  uint32_t block_stride;  // bytes between consecutive 64-column blocks
+};
+
+// K-major use: contraction index = tile column.  `k0` = first contraction column (multiple of 16).
+__device__ __forceinline__ uint64_t desc_kmajor(const Operand& t, uint32_t k0) {
+  const uint32_t addr = t.saddr + (k0 / kBlockCols) * t.block_stride + (k0 % kBlockCols) * 2u;
+  return umma_desc_sw128(addr, 16u, kSbo);
+}
+
+// MN-major use: contraction index = tile row.  `k0` = first contraction row (multiple of 16).  The M/N extent
+// starts at column 0 of block 0 and continues in the next blocks.
+__device__ __forceinline__ uint64_t desc_mnmajor(const Operand& t, uint32_t k0) {
+  const uint32_t addr = t.saddr + k0 * 128u;
+  return umma_desc_sw128(addr, t.block_stride, kSbo);
+}
+
+// The operand that starts `rows` rows (multiple of 8) below / `blocks` 64-column blocks to the right of `t`.
+__device__ __forceinline__ Operand operand_at(const Operand& t, uint32_t rows, uint32_t blocks = 0) {
+  return Operand{t.saddr + rows * 128u + blocks * t.block_stride, t.block_stride};
+}
+
+// D[M x N] (+)= A * B over a contraction of `kdim` (multiple of 16).  a_mn/b_mn pick the operand role of each tile.
+// Issued by ONE thread; `accumulate` says whether the first instruction adds to what tensor memory holds.
+template <int M, int N>
+__device__ __forceinline__ void umma_gemm(uint32_t tmem_d, const Operand& a, bool a_mn, const Operand& b, bool b_mn,
+                                          uint32_t kdim, bool accumulate, bool neg_a = false) {
+  const uint32_t idesc = umma_idesc(M, N, a_mn, b_mn, neg_a);
+  for (uint32_t k0 = 0; k0 < kdim; k0 += 16) {
+    const uint64_t da = a_mn ? desc_mnmajor(a, k0) : desc_kmajor(a, k0);
+    const uint64_t db = b_mn ? desc_mnmajor(b, k0) : desc_kmajor(b, k0);
+    umma_f16(tmem_d, da, db, idesc, (accumulate || k0 > 0) ? 1u : 0u);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// bf16 packing
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float2 unpack_bf16(uint32_t w) {
+  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&w);
+  return __bfloat1622float2(v);
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+}  // namespace mek

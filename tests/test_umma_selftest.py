@@ -1,0 +1,77 @@
+"""The tensor-core building block against a CPU matmul: every operand role the kernels use (K-major and MN-major
+tiles in the 128-byte swizzled block layout, M = 64 and M = 128, negated A), through the C ABI."""
+
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import pytest
+
+from umma_images import (
+    bf16_round,
+    desc_template,
+    idesc,
+    kmajor_offsets,
+    lane_of_row,
+    mnmajor_offsets,
+    tile_image,
+)
+
+torch = pytest.importorskip("torch")
+
+CASES = {
+    # name: (M, N, K, a_mn, b_mn, neg_a)
+    "k_k_m128_n64_k64": (128, 64, 64, False, False, False),
+    "k_k_m128_n128_k128": (128, 128, 128, False, False, False),
+    "k_k_m64_n64_k128": (64, 64, 128, False, False, False),
+    "k_mn_m64_n128_k64": (64, 128, 64, False, True, False),
+    "k_mn_m64_n128_k128": (64, 128, 128, False, True, False),
+    "mn_mn_m128_n128_k64": (128, 128, 64, True, True, False),
+    "mn_mn_m128_n64_k64_neg": (128, 64, 64, True, True, True),
+    "mn_k_m64_n128_k64": (64, 128, 64, True, False, False),
+    "k_k_m64_n256_k64": (64, 256, 64, False, False, False),
+}
+
+
+def run_case(lib, m, n, k, a_mn, b_mn, neg_a, seed=0):
+    rng = np.random.default_rng(seed)
+    a = bf16_round(rng.standard_normal((m, k)).astype(np.float32))
+    b = bf16_round(rng.standard_normal((n, k)).astype(np.float32))
+    # K-major: the tile is [rows = M or N, cols = K].  MN-major: the tile is [rows = K, cols = M or N].
+    a_img, a_stride = tile_image(a.T.copy() if a_mn else a)
+    b_img, b_stride = tile_image(b.T.copy() if b_mn else b)
+    a_off = mnmajor_offsets(k) if a_mn else kmajor_offsets(k, a_stride)
+    b_off = mnmajor_offsets(k) if b_mn else kmajor_offsets(k, b_stride)
+    a_desc = desc_template(a_stride if a_mn else 16)
+    b_desc = desc_template(b_stride if b_mn else 16)
+    dev = torch.device("cuda")
+    t = lambda x, dt: torch.from_numpy(np.ascontiguousarray(x)).to(dev, dt)  # noqa: E731
+    a_d, b_d = t(a_img, torch.uint8), t(b_img, torch.uint8)
+    ao, bo = t(np.array(a_off, np.int32), torch.int32), t(np.array(b_off, np.int32), torch.int32)
+    out = torch.zeros(128, n, dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    p = lambda x: ctypes.c_void_p(x.data_ptr())  # noqa: E731
+    rc = lib.mek_selftest_umma(
+        p(a_d), a_img.size, p(b_d), b_img.size, ctypes.c_uint64(a_desc), ctypes.c_uint64(b_desc), p(ao), p(bo),
+        len(a_off), ctypes.c_uint32(idesc(m, n, a_mn, b_mn, neg_a)), n, p(out), p(status),
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
+    )
+    lib.check(rc)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "the MMA wait ran out"
+    want = (a.astype(np.float64) @ b.astype(np.float64).T) * (-1.0 if neg_a else 1.0)
+    lanes = [lane_of_row(m, r) for r in range(m)]
+    got = out.cpu().numpy()[lanes]
+    return got, want
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", list(CASES))
+def test_umma_operand_layouts(name):
+    from miles_ext_kernels_b200.cake._runtime import loader
+
+    lib = loader.load_library()
+    got, want = run_case(lib, *CASES[name])
+    err = np.abs(got - want).max()
+    assert err <= 1e-3 * max(1.0, np.abs(want).max()), f"{name}: max error {err}"
