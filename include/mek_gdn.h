@@ -56,6 +56,68 @@ int mek_selftest_umma(const void* a_img, int a_bytes, const void* b_img, int b_b
                       const int32_t* a_off, const int32_t* b_off, int nk, uint32_t idesc, int ncols, float* out,
                       int32_t* status, void* stream);
 
+/* Extents and chunk tables of one call.  Tokens are packed: [total_tokens, heads, 128]; a batch of B equal-length
+ * sequences is B sequences of one packed row.  Chunks hold at most 64 tokens and never straddle a sequence.
+ * Replaces the reference's ChunkMeta int32 tables (reference: miles_ext_kernels/cake/_impl/gdn/ops.py:157-174). */
+typedef struct MekGdnDims {
+  int64_t total_tokens;
+  int32_t num_qk_heads;           /* H */
+  int32_t num_v_heads;            /* HV, a multiple of H; value head hv reads q / k head hv / (HV / H) */
+  int32_t head_dim;               /* 128 */
+  int32_t num_seqs;               /* N */
+  int32_t num_chunks;             /* NC */
+  float scale;                    /* multiplies q k^T and q h */
+  const int32_t* chunk_start;     /* device [NC]: first token of the chunk */
+  const int32_t* chunk_len;       /* device [NC]: 1..64 */
+  const int32_t* chunk_seq;       /* device [NC]: the chunk's sequence */
+  const int32_t* seq_chunk_start; /* device [N + 1]: first chunk of each sequence */
+} MekGdnDims;
+
+/* y = bf16(x r), r = 1 / sqrt(sum x^2 + 1e-6) per row of 128 bf16; rstd[row] = r.
+ * Replaces the `prep` stage's q / k normalisation (reference: miles_ext_kernels/cake/_impl/gdn/ops.py:1361-1380). */
+int mek_gdn_l2norm(const void* x, void* y, float* rstd, int64_t rows, void* stream);
+
+/* g_cs[t, hv] = log2(e) * chunk-local inclusive cumulative sum of g (fp32 [T, HV]).
+ * Replaces the `prep` stage's gate cumsum (reference: ops.py:1361-1380). */
+int mek_gdn_gate_cumsum(const MekGdnDims* dims, const float* g, float* g_cs, void* stream);
+
+/* WY / UT transform per (chunk, value head): a_out, aqk_out bf16 [NC, HV, 64, 64]; w_out, u_out bf16 [T, HV, 128].
+ * q, k bf16 [T, H, 128] (already normalised), v bf16 [T, HV, 128], beta fp32 [T, HV].
+ * Replaces `_launch_wy` (reference: ops.py:1154-1188); Aqk follows the KCP prep program
+ * (reference: _vendor/cake_gdn_det_train_kcp/cake_fake_backend.py:173-222). */
+int mek_gdn_wy_fwd(const MekGdnDims* dims, const void* q, const void* k, const void* v, const float* beta,
+                   const float* g_cs, void* a_out, void* aqk_out, void* w_out, void* u_out, int32_t* status,
+                   void* stream);
+
+/* State recurrence per (sequence, value head): h_tape bf16 [NC, HV, 128, 128] (state at the start of each chunk),
+ * v_new bf16 [T, HV, 128], final_state fp32 [N, HV, 128, 128] or NULL; h0 fp32 [N, HV, 128, 128] or NULL.
+ * Replaces `_launch_fwd_h` (reference: ops.py:1191-1317). */
+int mek_gdn_fwd_h(const MekGdnDims* dims, const void* k, const void* w, const void* u, const float* g_cs,
+                  const float* h0, void* h_tape, void* v_new, float* final_state, int32_t* status, void* stream);
+
+/* Output per (chunk, value head): o bf16 [T, HV, 128] = bf16(scale 2^G (q h_tape) + Aqk v_new).
+ * Replaces the `fwd_o` launch (reference: ops.py:1425-1440). */
+int mek_gdn_fwd_o(const MekGdnDims* dims, const void* q, const void* aqk, const void* v_new, const void* h_tape,
+                  const float* g_cs, void* o, int32_t* status, void* stream);
+
+/* Adjoint state scan per (sequence, value head), reverse over chunks, with dv_local fused:
+ * dh_tape bf16 [NC, HV, 128, 128] (adjoint state at the end of each chunk), dv_new bf16 [T, HV, 128],
+ * dh0 fp32 [N, HV, 128, 128] or NULL; dht fp32 [N, HV, 128, 128] or NULL; d_o bf16 [T, HV, 128].
+ * Replaces the `dv_local` and `dhu` launches (reference: miles_ext_kernels/cake/_impl/gdn/ops.py:1519-1640). */
+int mek_gdn_bwd_dh(const MekGdnDims* dims, const void* q, const void* k, const void* w, const void* d_o,
+                   const void* aqk, const float* g_cs, const float* dht, void* dh_tape, void* dv_new, float* dh0,
+                   int32_t* status, void* stream);
+
+/* Gradient tail per (chunk, key head): dq, dk bf16 [T, H, 128] (fp32 sum over the key head's value heads, the L2
+ * norm's pull-back when q_raw / k_raw / rstd_q / rstd_k are given, one rounding), dv bf16 [T, HV, 128], dbeta and
+ * dg fp32 [T, HV] (dg includes the in-chunk suffix sum).  q, k are the normalised rows the forward used.
+ * Replaces the `dqkwg`, `wy_bwd` and `finalize` launches (reference: ops.py:1642-1727). */
+int mek_gdn_bwd_tail(const MekGdnDims* dims, const void* q, const void* k, const void* v, const float* beta,
+                     const float* g_cs, const void* a, const void* aqk, const void* h_tape, const void* dh_tape,
+                     const void* v_new, const void* dv_new, const void* d_o, const void* q_raw, const void* k_raw,
+                     const float* rstd_q, const float* rstd_k, void* dq, void* dk, void* dv, float* dbeta, float* dg,
+                     int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,162 @@
+"""The stages of the GDN forward and backward as launches of the native library, on packed ``[T, heads, 128]``
+operands.  No stage synchronises; all run on torch's current stream.
+
+Forward (reference launch order: miles_ext_kernels/cake/_impl/gdn/ops.py:1320-1450): prep -> wy -> fwd_h -> fwd_o.
+Backward (reference: ops.py:1474-1735): bwd_dh (adjoint scan with dv_local fused) -> bwd_tail (dq, dk, dv, dbeta, dg
+with the group sum, the norm's pull-back and the in-chunk gate suffix sum fused).
+
+Scratch that does not outlive a call comes from the runtime's workspace pool; tensors that the autograd tape or the
+caller keeps are fresh allocations.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..._runtime import workspace
+from . import native
+from .meta import ChunkMeta
+
+OP = "gdn"
+HEAD_DIM = 128
+BF16, F32 = torch.bfloat16, torch.float32
+
+__all__ = ["ForwardTape", "dims_of", "forward", "backward", "check_status"]
+
+
+def dims_of(meta: ChunkMeta, num_qk_heads: int, num_v_heads: int, scale: float) -> native.Dims:
+    return native.Dims(
+        meta.total_tokens, num_qk_heads, num_v_heads, HEAD_DIM, meta.num_seqs, meta.num_chunks, float(scale),
+        meta.chunk_start.data_ptr(), meta.chunk_len.data_ptr(), meta.chunk_seq.data_ptr(),
+        meta.seq_chunk_start.data_ptr(),
+    )
+
+
+@dataclass
+class ForwardTape:
+    """What the forward leaves for the backward (packed layouts)."""
+
+    qn: torch.Tensor  # [T, H, 128] bf16, normalised when the op normalises
+    kn: torch.Tensor
+    v: torch.Tensor  # [T, HV, 128]
+    beta32: torch.Tensor  # [T, HV] fp32
+    g_cs: torch.Tensor  # [T, HV] fp32, log2 domain
+    a: torch.Tensor  # [NC, HV, 64, 64] bf16
+    aqk: torch.Tensor
+    w: torch.Tensor | None  # [T, HV, 128] bf16
+    u: torch.Tensor | None
+    h: torch.Tensor | None  # [NC, HV, 128, 128] bf16
+    v_new: torch.Tensor | None
+    q_raw: torch.Tensor | None  # raw rows and their rstd when the op normalised
+    k_raw: torch.Tensor | None
+    rstd_q: torch.Tensor | None
+    rstd_k: torch.Tensor | None
+    status: torch.Tensor  # int32 [1]: nonzero when a bounded wait in a kernel ran out
+
+
+def check_status(status: torch.Tensor) -> None:
+    """Raise when a kernel recorded an error.  Synchronises: for tests and debugging, never on the hot path."""
+    word = int(status.item())
+    if word:
+        raise RuntimeError(f"a GDN kernel gave up a bounded wait (code {word & 0xFF}, stage {word >> 8})")
+
+
+def _l2norm(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    y = torch.empty_like(x)
+    rstd = torch.empty(x.shape[:-1], dtype=F32, device=x.device)
+    native.launch("gdn_l2norm", x, y, rstd, x.numel() // HEAD_DIM, device=x.device)
+    return y, rstd
+
+
+def forward(q, k, v, g, beta32, meta: ChunkMeta, scale: float, h0, output_final_state: bool, use_qk_l2norm: bool,
+            keep_state: bool = True):
+    """q, k ``[T, H, 128]`` bf16; v ``[T, HV, 128]`` bf16; g, beta32 ``[T, HV]`` fp32; h0 ``[N, HV, 128, 128]`` fp32
+    or None.  Returns ``(o [T, HV, 128] bf16, final_state or None, tape)``."""
+    device = q.device
+    T, H = q.shape[0], q.shape[1]
+    HV = v.shape[1]
+    NC = meta.num_chunks
+    dims = dims_of(meta, H, HV, scale)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    q_raw = k_raw = rstd_q = rstd_k = None
+    if use_qk_l2norm:
+        q_raw, k_raw = q, k
+        q, rstd_q = _l2norm(q)
+        k, rstd_k = _l2norm(k)
+    g_cs = torch.empty_like(g)
+    native.launch("gdn_gate_cumsum", dims, g, g_cs, device=device)
+
+    # pad chunks of the device route are never written: their A / Aqk / h rows must not hold NaN bit patterns
+    alloc = torch.empty if meta.exact else torch.zeros
+    a = alloc((NC, HV, 64, 64), dtype=BF16, device=device)
+    aqk = alloc((NC, HV, 64, 64), dtype=BF16, device=device)
+    w = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    u = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    native.launch("gdn_wy_fwd", dims, q, k, v, beta32, g_cs, a, aqk, w, u, status, device=device)
+
+    h = alloc((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
+    v_new = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    final_state = (
+        torch.empty((meta.num_seqs, HV, HEAD_DIM, HEAD_DIM), dtype=F32, device=device) if output_final_state else None
+    )
+    native.launch("gdn_fwd_h", dims, k, w, u, g_cs, h0, h, v_new, final_state, status, device=device)
+
+    o = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    native.launch("gdn_fwd_o", dims, q, aqk, v_new, h, g_cs, o, status, device=device)
+
+    if not keep_state:
+        w = u = h = v_new = None
+    tape = ForwardTape(q, k, v, beta32, g_cs, a, aqk, w, u, h, v_new, q_raw, k_raw, rstd_q, rstd_k, status)
+    return o, final_state, tape
+
+
+def recompute_state(tape: ForwardTape, meta: ChunkMeta, scale: float, h0) -> None:
+    """Rebuild ``w, u, h, v_new`` of a tape that dropped them (the same kernels on the same inputs: the same bits)."""
+    device = tape.qn.device
+    T, H = tape.qn.shape[0], tape.qn.shape[1]
+    HV = tape.v.shape[1]
+    NC = meta.num_chunks
+    dims = dims_of(meta, H, HV, scale)
+    alloc = torch.empty if meta.exact else torch.zeros
+    a = workspace.take(OP, "recompute_a", (NC, HV, 64, 64), BF16, device)
+    aqk = workspace.take(OP, "recompute_aqk", (NC, HV, 64, 64), BF16, device)
+    tape.w = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    tape.u = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    native.launch("gdn_wy_fwd", dims, tape.qn, tape.kn, tape.v, tape.beta32, tape.g_cs, a, aqk, tape.w, tape.u,
+                  tape.status, device=device)
+    tape.h = alloc((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
+    tape.v_new = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    native.launch("gdn_fwd_h", dims, tape.kn, tape.w, tape.u, tape.g_cs, h0, tape.h, tape.v_new, None, tape.status,
+                  device=device)
+
+
+def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want_dh0: bool):
+    """``do [T, HV, 128]`` bf16, ``dht [N, HV, 128, 128]`` fp32 or None.  Returns ``(dq, dk [T, H, 128] bf16, dv
+    [T, HV, 128] bf16, dg, dbeta [T, HV] fp32, dh0 [N, HV, 128, 128] fp32 or None)``."""
+    device = do.device
+    T, H = tape.qn.shape[0], tape.qn.shape[1]
+    HV = tape.v.shape[1]
+    NC = meta.num_chunks
+    dims = dims_of(meta, H, HV, scale)
+    if tape.w is None:
+        recompute_state(tape, meta, scale, h0)
+    if meta.exact:
+        dh_tape = workspace.take(OP, "dh_tape", (NC, HV, HEAD_DIM, HEAD_DIM), BF16, device)
+    else:  # pad chunks are never written
+        dh_tape = torch.zeros((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
+    dv_new = workspace.take(OP, "dv_new", (T, HV, HEAD_DIM), BF16, device)
+    dh0 = torch.empty((meta.num_seqs, HV, HEAD_DIM, HEAD_DIM), dtype=F32, device=device) if want_dh0 else None
+    native.launch("gdn_bwd_dh", dims, tape.qn, tape.kn, tape.w, do, tape.aqk, tape.g_cs, dht, dh_tape, dv_new, dh0,
+                  tape.status, device=device)
+    dq = torch.empty((T, H, HEAD_DIM), dtype=BF16, device=device)
+    dk = torch.empty((T, H, HEAD_DIM), dtype=BF16, device=device)
+    dv = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    dbeta = torch.empty((T, HV), dtype=F32, device=device)
+    dg = torch.empty((T, HV), dtype=F32, device=device)
+    native.launch("gdn_bwd_tail", dims, tape.qn, tape.kn, tape.v, tape.beta32, tape.g_cs, tape.a, tape.aqk, tape.h,
+                  dh_tape, tape.v_new, dv_new, do, tape.q_raw, tape.k_raw, tape.rstd_q, tape.rstd_k, dq, dk, dv,
+                  dbeta, dg, tape.status, device=device)
+    return dq, dk, dv, dg, dbeta, dh0, dh_tape, dv_new

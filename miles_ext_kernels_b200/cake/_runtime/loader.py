@@ -303,6 +303,7 @@ class LibrarySpec:
             for stale in _IN_TREE.glob(f"{self.name}_{self.arch}_*.so"):
                 if stale != path:
                     stale.unlink(missing_ok=True)
+                    stale.with_suffix(".lock").unlink(missing_ok=True)
         return path
 
 

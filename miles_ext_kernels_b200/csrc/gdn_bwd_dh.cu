@@ -1,0 +1,204 @@
+// Adjoint state scan of the chunked gated delta rule (reverse over chunks), sm_100a, with dv_local fused.
+//
+// Per (sequence, value head), from dh = dht (or 0), for each chunk from the last to the first:
+//   dh_tape = bf16(dh)
+//   dv_new  = bf16( bf16(Aqk^T do) + rowscale (k dh_tape) )            -> tape, and the W-side operand
+//   dh      = gamma dh + q^T bf16(qscale do) - w^T dv_new
+// after the first chunk dh is the gradient of the initial state.
+//
+// Reference semantics: miles_ext_kernels/cake/_vendor/cake_gdn_det_train_kcp/cake_fake_backend.py:313-349 (adjoint
+// walk) and :433-448 (do_g, dv_intra); reference launches: miles_ext_kernels/cake/_impl/gdn/ops.py:1519-1640.
+#include "common.cuh"
+#include "tiles.cuh"
+
+namespace mek {
+
+struct BwdDhSmem {
+  static constexpr uint32_t kK = 0;                 // [64][128] k        K-major A of k dh
+  static constexpr uint32_t kQ = 16384;             // [64][128] q        MN-major A of q^T do_g
+  static constexpr uint32_t kW = 2 * 16384;         // [64][128] w        MN-major A of w^T dv_new (negated)
+  static constexpr uint32_t kDO = 3 * 16384;        // [64][128] do       MN-major B of Aqk^T do
+  static constexpr uint32_t kDOG = 4 * 16384;       // [64][128] bf16(qscale do)
+  static constexpr uint32_t kDV = 5 * 16384;        // [64][128] dv_new
+  static constexpr uint32_t kDH = 6 * 16384;        // [128][128] bf16(dh), 2 blocks of 16 KiB
+  static constexpr uint32_t kAqk = kDH + 32768;     // [64][64]
+  static constexpr uint32_t kG = kAqk + 8192;       // g2[64]
+  static constexpr uint32_t kBytes = kG + 256;
+};
+
+__global__ void __launch_bounds__(128) gdn_bwd_dh_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ w,
+    const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ aqk, const float* __restrict__ g_cs,
+    const float* __restrict__ dht, __nv_bfloat16* __restrict__ dh_tape, __nv_bfloat16* __restrict__ dv_new,
+    float* __restrict__ dh0, const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len,
+    const int32_t* __restrict__ seq_chunk_start, int num_qk_heads, int num_v_heads, float scale,
+    int32_t* __restrict__ status) {
+  extern __shared__ uint8_t raw[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n = blockIdx.x, hv = blockIdx.y, hq = hv / (num_v_heads / num_qk_heads);
+  float* s_g2 = reinterpret_cast<float*>(sm + BwdDhSmem::kG);
+  Abort abort{&abort_flag};
+
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+    abort_flag = 0;
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t sbase = smem_u32(sm);
+  const Operand op_k{sbase + BwdDhSmem::kK, 8192}, op_q{sbase + BwdDhSmem::kQ, 8192};
+  const Operand op_w{sbase + BwdDhSmem::kW, 8192}, op_do{sbase + BwdDhSmem::kDO, 8192};
+  const Operand op_dog{sbase + BwdDhSmem::kDOG, 8192}, op_dv{sbase + BwdDhSmem::kDV, 8192};
+  const Operand op_dh{sbase + BwdDhSmem::kDH, 16384}, op_aqk{sbase + BwdDhSmem::kAqk, 8192};
+  const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
+  constexpr uint32_t kD1 = 0, kD1b = 128, kD2 = 256;  // tensor-memory columns
+
+  // fp32 adjoint state: thread `tid` holds row k = tid of dh [K, V]
+  float dh[128];
+  if (dht != nullptr) {
+    const float4* src = reinterpret_cast<const float4*>(dht + ((int64_t(n) * num_v_heads + hv) * kDim + tid) * kDim);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float4 t = __ldg(src + j);
+      dh[4 * j] = t.x, dh[4 * j + 1] = t.y, dh[4 * j + 2] = t.z, dh[4 * j + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 128; ++j) dh[j] = 0.f;
+  }
+
+  uint32_t phase = 0;
+  const int c_begin = seq_chunk_start[n];
+  for (int c = seq_chunk_start[n + 1] - 1; c >= c_begin; --c) {
+    const int start = chunk_start[c], len = chunk_len[c];
+    const int64_t tile = int64_t(c) * num_v_heads + hv;
+    load_tile<64, 128, 128>(sm + BwdDhSmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+    load_tile<64, 128, 128>(sm + BwdDhSmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+    load_tile<64, 128, 128>(sm + BwdDhSmem::kW, 8192, w + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+    load_tile<64, 128, 128>(sm + BwdDhSmem::kDO, 8192, d_o + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+    load_tile<64, 64, 128>(sm + BwdDhSmem::kAqk, 8192, aqk + tile * 4096, 64, 64, tid);
+    if (tid < 64) s_g2[tid] = g_cs[int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv];
+    {
+      __nv_bfloat16* tape = dh_tape + (tile * kDim + tid) * kDim;
+#pragma unroll
+      for (int cc = 0; cc < 16; ++cc) {
+        const uint4 packed = pack8(dh + 8 * cc);
+        set_tile_chunk(sm + BwdDhSmem::kDH, 16384, tid, cc, packed);
+        reinterpret_cast<uint4*>(tape)[cc] = packed;
+      }
+    }
+    __syncthreads();
+    if (abort.raised()) break;
+    // do_g = bf16(qscale do)
+    for (int i = tid; i < 64 * 16; i += 128) {
+      const int r = i >> 4, cc = i & 15;
+      const float qs = scale * fast_exp2(s_g2[r]);
+      float x[8];
+      unpack8(tile_chunk(sm + BwdDhSmem::kDO, 8192, r, cc), x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] *= qs;
+      set_tile_chunk(sm + BwdDhSmem::kDOG, 8192, r, cc, pack8(x));
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    if (tid == 0) {
+      umma_gemm<64, 128>(tmem + kD1, op_k, false, op_dh, true, 128, false);      // k dh_tape
+      umma_gemm<64, 128>(tmem + kD1b, op_aqk, true, op_do, true, 64, false);     // Aqk^T do
+      umma_gemm<128, 128>(tmem + kD2, op_q, true, op_dog, true, 64, false);      // q^T do_g
+      umma_commit(&bar);
+    }
+    if (!mbar_wait(&bar, phase)) abort.raise();
+    phase ^= 1;
+    tc_fence_after();
+
+    const float g_last = s_g2[len - 1];
+    {
+      // every lane runs the warp-wide tensor-memory loads; lanes 0..15 own the rows of an M = 64 accumulator
+      const int i = warp * 16 + (lane & 15);
+      const bool owner = lane < 16;
+      const bool live = owner && i < len;
+      const float rs = live ? fast_exp2(g_last - s_g2[i]) : 0.f;
+      __nv_bfloat16* drow = dv_new + int64_t(start + i) * v_stride + hv * kDim;
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        float a[32], b[32];
+        tmem_ld32(tmem_addr(tmem, warp, kD1 + p * 32), a);
+        tmem_ld32(tmem_addr(tmem, warp, kD1b + p * 32), b);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) a[j] = live ? fmaf(rs, a[j], round_bf16(b[j])) : 0.f;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const uint4 packed = pack8(a + 8 * jj);
+          if (live) reinterpret_cast<uint4*>(drow + p * 32)[jj] = packed;
+          if (owner) set_tile_chunk(sm + BwdDhSmem::kDV, 8192, i, p * 4 + jj, packed);
+        }
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    if (tid == 0) {
+      umma_gemm<128, 128>(tmem + kD2, op_w, true, op_dv, true, 64, true, /*neg_a=*/true);  // - w^T dv_new
+      umma_commit(&bar);
+    }
+    if (!mbar_wait(&bar, phase)) abort.raise();
+    phase ^= 1;
+    tc_fence_after();
+
+    const float gamma = fast_exp2(g_last);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      float d[32];
+      tmem_ld32(tmem_addr(tmem, warp, kD2 + p * 32), d);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) dh[p * 32 + j] = fmaf(gamma, dh[p * 32 + j], d[j]);
+    }
+    tc_fence_before();
+    __syncthreads();
+  }
+
+  if (dh0 != nullptr && !abort.raised()) {
+    float4* dst = reinterpret_cast<float4*>(dh0 + ((int64_t(n) * num_v_heads + hv) * kDim + tid) * kDim);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dst[j] = make_float4(dh[4 * j], dh[4 * j + 1], dh[4 * j + 2], dh[4 * j + 3]);
+  }
+  if (abort.raised() && tid == 0) atomicExch(status, kDevWaitTimeout | (4 << 8));
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace mek
+
+extern "C" int mek_gdn_bwd_dh(const MekGdnDims* d, const void* q, const void* k, const void* w, const void* d_o,
+                              const void* aqk, const float* g_cs, const float* dht, void* dh_tape, void* dv_new,
+                              float* dh0, int32_t* status, void* stream) {
+  using namespace mek;
+  if (d == nullptr || d->num_seqs <= 0 || d->num_v_heads <= 0 || d->num_qk_heads <= 0 ||
+      d->num_v_heads % d->num_qk_heads != 0)
+    return fail(MEK_ERR_INVALID, "bwd_dh: bad extents");
+  if (d->head_dim != 128) return fail(MEK_ERR_UNSUPPORTED, "bwd_dh: head dims must be 128, not %d", d->head_dim);
+  const size_t smem = BwdDhSmem::kBytes + 1024;
+  if (int rc = want_smem(gdn_bwd_dh_kernel, smem, "bwd_dh")) return rc;
+  gdn_bwd_dh_kernel<<<dim3(d->num_seqs, d->num_v_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(w),
+      static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(aqk), g_cs, dht,
+      static_cast<__nv_bfloat16*>(dh_tape), static_cast<__nv_bfloat16*>(dv_new), dh0, d->chunk_start, d->chunk_len,
+      d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, d->scale, status);
+  return launched("bwd_dh");
+}

@@ -1,0 +1,557 @@
+// Forward kernels of the chunked gated delta rule (chunk 64, K = V = 128), sm_100a.
+//
+//   prep      per-row L2 norm of q / k (optional) and the chunk-local cumulative gate in the log2 domain
+//   wy        per (chunk, value head): Aqk = tril(scale q k^T 2^{G_i-G_j}),  A = (I + tril(beta_i 2^{G_i-G_j} k_i.k_j, -1))^-1,
+//             w = A bf16(beta 2^G k),  u = A bf16(beta v)                      [tcgen05, TMEM accumulators]
+//   fwd_h     per (sequence, value head), serial over chunks: h_tape = bf16(h); v_new = u - w h_tape;
+//             h = gamma h + k^T bf16(rowscale v_new)                           [tcgen05, fp32 state in registers]
+//   fwd_o     per (chunk, value head): o = bf16(qscale (q h_tape) + Aqk v_new)  [tcgen05]
+//
+// The stages and their rounding points follow the reference's dataflow (reference:
+// miles_ext_kernels/cake/_impl/gdn/ops.py:1320-1450 launch order; semantics
+// miles_ext_kernels/cake/_vendor/cake_gdn_det_train_kcp/cake_fake_backend.py:173-279, 418-430).
+//
+// Shared-memory operand tiles use the swizzled block layout of umma.cuh; one tile serves as a K-major operand
+// (contraction over the feature axis) and as an MN-major operand (contraction over the token axis).
+#include "common.cuh"
+#include "tiles.cuh"
+
+namespace mek {
+
+// ---------------------------------------------------------------------------------------------------------------
+// prep
+// ---------------------------------------------------------------------------------------------------------------
+// One warp per row of 128 bf16: y = bf16(x r), r = 1 / sqrt(sum x^2 + 1e-6), r saved.
+__global__ void __launch_bounds__(256) l2norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                                     float* __restrict__ rstd, int64_t rows) {
+  const int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + row * kDim) + lane);
+  const float2 a = unpack_bf16(raw.x), b = unpack_bf16(raw.y);
+  float ss = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+  const float r = 1.0f / sqrtf(ss + 1e-6f);
+  uint2 out;
+  out.x = pack_bf16(a.x * r, a.y * r);
+  out.y = pack_bf16(b.x * r, b.y * r);
+  reinterpret_cast<uint2*>(y + row * kDim)[lane] = out;
+  if (lane == 0) rstd[row] = r;
+}
+
+// One block per chunk, one thread per value head: g_cs[t, hv] = log2(e) * sum_{s <= t, same chunk} g[s, hv].
+__global__ void gate_cumsum_kernel(const float* __restrict__ g, float* __restrict__ g_cs,
+                                   const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len,
+                                   int num_v_heads) {
+  const int c = blockIdx.x;
+  const int start = chunk_start[c], len = chunk_len[c];
+  for (int hv = threadIdx.x; hv < num_v_heads; hv += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < len; ++i) {
+      const int64_t at = int64_t(start + i) * num_v_heads + hv;
+      acc += g[at];
+      g_cs[at] = acc * kLog2e;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// wy
+// ---------------------------------------------------------------------------------------------------------------
+struct WySmem {
+  static constexpr uint32_t kQK = 0;               // [128 rows: q then k][128 cols], 2 blocks of 16 KiB
+  static constexpr uint32_t kQKStride = 16384;
+  static constexpr uint32_t kV = 32768;            // [64][128] v -> beta v, 2 blocks of 8 KiB
+  static constexpr uint32_t kKB = kV + 16384;      // [64][128] beta 2^G k
+  static constexpr uint32_t kA = kKB + 16384;      // [64][64] A (bf16)
+  static constexpr uint32_t kL = kA + 8192;        // fp32 [64 cols j][64 rows i]: L transposed
+  static constexpr uint32_t kScal = kL + 16384;    // beta[64], g2[64]
+  static constexpr uint32_t kBytes = kScal + 512;
+};
+
+__global__ void __launch_bounds__(128) gdn_wy_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+    const float* __restrict__ beta, const float* __restrict__ g_cs, __nv_bfloat16* __restrict__ a_out,
+    __nv_bfloat16* __restrict__ aqk_out, __nv_bfloat16* __restrict__ w_out, __nv_bfloat16* __restrict__ u_out,
+    const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len, int num_qk_heads, int num_v_heads,
+    float scale, int32_t* __restrict__ status) {
+  extern __shared__ uint8_t raw[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, hv = blockIdx.y, hq = hv / (num_v_heads / num_qk_heads);
+  const int start = chunk_start[c], len = chunk_len[c];
+  if (len <= 0) return;  // a pad chunk of a device-built table
+  float* s_beta = reinterpret_cast<float*>(sm + WySmem::kScal);
+  float* s_g2 = s_beta + 64;
+  float* s_lt = reinterpret_cast<float*>(sm + WySmem::kL);
+
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 256);
+
+  const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
+  load_tile<64, 128, 128>(sm + WySmem::kQK, WySmem::kQKStride, q + int64_t(start) * qk_stride + hq * kDim, qk_stride,
+                          len, tid, 0);
+  load_tile<64, 128, 128>(sm + WySmem::kQK, WySmem::kQKStride, k + int64_t(start) * qk_stride + hq * kDim, qk_stride,
+                          len, tid, 64);
+  load_tile<64, 128, 128>(sm + WySmem::kV, 8192, v + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+  if (tid < 64) {
+    const int i = tid < len ? tid : len - 1;
+    s_beta[tid] = tid < len ? beta[int64_t(start + i) * num_v_heads + hv] : 0.f;
+    s_g2[tid] = g_cs[int64_t(start + i) * num_v_heads + hv];
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t sbase = smem_u32(sm);
+
+  // S = [q; k] k^T : rows 0..63 = q k^T, rows 64..127 = k k^T
+  if (tid == 0) {
+    const Operand qk{sbase + WySmem::kQK, WySmem::kQKStride};
+    const Operand kk{sbase + WySmem::kQK + 64 * 128, WySmem::kQKStride};
+    umma_gemm<128, 64>(tmem, qk, false, kk, false, 128, false);
+    umma_commit(&bar);
+  }
+  // meanwhile: kb = bf16(beta 2^G k), vb = bf16(beta v) (in place)
+  for (int i = tid; i < 64 * 16; i += 128) {
+    const int r = i >> 4, cc = i & 15;
+    const float b = s_beta[r], s = b * fast_exp2(s_g2[r]);
+    float x[8];
+    unpack8(tile_chunk(sm + WySmem::kQK, WySmem::kQKStride, 64 + r, cc), x);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] *= s;
+    set_tile_chunk(sm + WySmem::kKB, 8192, r, cc, pack8(x));
+    unpack8(tile_chunk(sm + WySmem::kV, 8192, r, cc), x);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] *= b;
+    set_tile_chunk(sm + WySmem::kV, 8192, r, cc, pack8(x));
+  }
+  bool ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0));
+  tc_fence_after();
+
+  if (ok) {
+    const int i = tid & 63;
+    const float gi = s_g2[i], bi = s_beta[i];
+    if (tid < 64) {
+      // Aqk row i -> global
+      __nv_bfloat16* dst = aqk_out + (int64_t(c) * num_v_heads + hv) * 4096 + i * 64;
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        float s[32];
+        tmem_ld32(tmem_addr(tmem, warp, p * 32), s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = p * 32 + j;
+          s[j] = col <= i ? scale * s[j] * fast_exp2(gi - s_g2[col]) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst + p * 32)[j] = pack8(s + 8 * j);
+      }
+    } else {
+      // L row i -> shared, transposed ([j][i]) so that the store is conflict-free and the solve reads broadcasts
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        float s[32];
+        tmem_ld32(tmem_addr(tmem, warp, p * 32), s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = p * 32 + j;
+          s_lt[col * 64 + i] = col < i ? bi * s[j] * fast_exp2(gi - s_g2[col]) : 0.f;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+
+  // A = (I + L)^-1 : thread c solves (I + L) x = e_c by forward substitution (columns are independent)
+  if (tid < 64) {
+    float x[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      float acc = (i == tid) ? 1.f : 0.f;
+#pragma unroll
+      for (int j = 0; j < i; ++j) acc = fmaf(-s_lt[j * 64 + i], x[j], acc);
+      x[i] = acc;
+    }
+    uint8_t* at = sm + WySmem::kA;
+#pragma unroll
+    for (int i = 0; i < 64; ++i)
+      *reinterpret_cast<__nv_bfloat16*>(at + sw128_offset(i, tid >> 3) + (tid & 7) * 2) = __float2bfloat16_rn(x[i]);
+  }
+  fence_async_smem();
+  __syncthreads();
+  tc_fence_after();
+
+  if (tid == 0) {
+    const Operand a{sbase + WySmem::kA, 8192};
+    const Operand kb{sbase + WySmem::kKB, 8192};
+    const Operand vb{sbase + WySmem::kV, 8192};
+    umma_gemm<64, 128>(tmem, a, false, kb, true, 64, false);
+    umma_gemm<64, 128>(tmem + 128, a, false, vb, true, 64, false);
+    umma_commit(&bar);
+  }
+  // A -> global while the MMAs run
+  store_tile<64, 64, 128>(sm + WySmem::kA, 8192, a_out + (int64_t(c) * num_v_heads + hv) * 4096, 64, 64, tid);
+  ok = mbar_wait(&bar, 1) && ok;
+  tc_fence_after();
+
+  ok = __all_sync(0xffffffffu, ok);
+  if (ok) {
+    // M = 64 accumulators live in lanes 0..15 of each warp's quadrant; tcgen05.ld is warp-wide, so every lane loads
+    // and only the lanes that own a row use what they read
+    const int i = warp * 16 + (lane & 15);
+    const bool live = lane < 16 && i < len;
+    __nv_bfloat16* wd = w_out + int64_t(start + i) * v_stride + hv * kDim;
+    __nv_bfloat16* ud = u_out + int64_t(start + i) * v_stride + hv * kDim;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      float s[32];
+      tmem_ld32(tmem_addr(tmem, warp, p * 32), s);
+      tmem_ld_wait();
+      __nv_bfloat16* dst = (p < 4 ? wd : ud) + (p & 3) * 32;
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = pack8(s + 8 * j);
+      }
+    }
+  }
+  if (!ok && tid == 0) atomicExch(status, kDevWaitTimeout | (1 << 8));
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// fwd_h : the state recurrence
+// ---------------------------------------------------------------------------------------------------------------
+struct FwdHSmem {
+  static constexpr uint32_t kW = 0;               // [64][128] w
+  static constexpr uint32_t kK = 16384;           // [64][128] k
+  static constexpr uint32_t kH = 32768;           // [128 k][128 v] bf16(h), 2 blocks of 16 KiB
+  static constexpr uint32_t kVS = kH + 32768;     // [64][128] bf16(rowscale v_new)
+  static constexpr uint32_t kG = kVS + 16384;     // g2[64]
+  static constexpr uint32_t kBytes = kG + 256;
+};
+
+__global__ void __launch_bounds__(128) gdn_fwd_h_kernel(
+    const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ u,
+    const float* __restrict__ g_cs, const float* __restrict__ h0, __nv_bfloat16* __restrict__ h_tape,
+    __nv_bfloat16* __restrict__ v_new, float* __restrict__ final_state, const int32_t* __restrict__ chunk_start,
+    const int32_t* __restrict__ chunk_len, const int32_t* __restrict__ seq_chunk_start, int num_qk_heads,
+    int num_v_heads, int32_t* __restrict__ status) {
+  extern __shared__ uint8_t raw[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n = blockIdx.x, hv = blockIdx.y, hq = hv / (num_v_heads / num_qk_heads);
+  float* s_g2 = reinterpret_cast<float*>(sm + FwdHSmem::kG);
+  Abort abort{&abort_flag};
+
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+    abort_flag = 0;
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t sbase = smem_u32(sm);
+  const Operand op_w{sbase + FwdHSmem::kW, 8192}, op_k{sbase + FwdHSmem::kK, 8192};
+  const Operand op_h{sbase + FwdHSmem::kH, 16384}, op_vs{sbase + FwdHSmem::kVS, 8192};
+  const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
+
+  // fp32 state: thread `tid` holds row k = tid of h [K, V]
+  float h[128];
+  if (h0 != nullptr) {
+    const float4* src = reinterpret_cast<const float4*>(h0 + ((int64_t(n) * num_v_heads + hv) * kDim + tid) * kDim);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float4 t = __ldg(src + j);
+      h[4 * j] = t.x, h[4 * j + 1] = t.y, h[4 * j + 2] = t.z, h[4 * j + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 128; ++j) h[j] = 0.f;
+  }
+
+  uint32_t phase = 0;
+  const int c_end = seq_chunk_start[n + 1];
+  for (int c = seq_chunk_start[n]; c < c_end; ++c) {
+    const int start = chunk_start[c], len = chunk_len[c];
+    load_tile<64, 128, 128>(sm + FwdHSmem::kW, 8192, w + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+    load_tile<64, 128, 128>(sm + FwdHSmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+    if (tid < 64) s_g2[tid] = g_cs[int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv];
+    // h_tape = bf16(h): to shared (MN-major B operand of w h) and to the tape
+    {
+      __nv_bfloat16* tape = h_tape + ((int64_t(c) * num_v_heads + hv) * kDim + tid) * kDim;
+#pragma unroll
+      for (int cc = 0; cc < 16; ++cc) {
+        const uint4 packed = pack8(h + 8 * cc);
+        set_tile_chunk(sm + FwdHSmem::kH, 16384, tid, cc, packed);
+        reinterpret_cast<uint4*>(tape)[cc] = packed;
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (abort.raised()) break;
+
+    if (tid == 0) {
+      umma_gemm<64, 128>(tmem, op_w, false, op_h, true, 128, false);
+      umma_commit(&bar);
+    }
+    if (!mbar_wait(&bar, phase)) abort.raise();
+    phase ^= 1;
+    tc_fence_after();
+
+    const float g_last = s_g2[len - 1];
+    {
+      // every lane runs the warp-wide tensor-memory loads; lanes 0..15 own the rows of an M = 64 accumulator
+      const int i = warp * 16 + (lane & 15);
+      const bool owner = lane < 16;
+      const bool live = owner && i < len;
+      const float rs = live ? fast_exp2(g_last - s_g2[i]) : 0.f;
+      const __nv_bfloat16* urow = u + int64_t(start + i) * v_stride + hv * kDim;
+      __nv_bfloat16* vrow = v_new + int64_t(start + i) * v_stride + hv * kDim;
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        float d[32];
+        tmem_ld32(tmem_addr(tmem, warp, p * 32), d);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          float uv[8], vs[8];
+          if (live) {
+            unpack8(ldg16(urow + p * 32 + jj * 8), uv);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) uv[e] = 0.f;
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            uv[e] -= d[jj * 8 + e];
+            vs[e] = rs * uv[e];
+          }
+          if (live) reinterpret_cast<uint4*>(vrow + p * 32)[jj] = pack8(uv);
+          if (owner) set_tile_chunk(sm + FwdHSmem::kVS, 8192, i, p * 4 + jj, pack8(vs));
+        }
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    if (tid == 0) {
+      umma_gemm<128, 128>(tmem + 128, op_k, true, op_vs, true, 64, false);
+      umma_commit(&bar);
+    }
+    if (!mbar_wait(&bar, phase)) abort.raise();
+    phase ^= 1;
+    tc_fence_after();
+
+    const float gamma = fast_exp2(g_last);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      float d[32];
+      tmem_ld32(tmem_addr(tmem, warp, 128 + p * 32), d);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) h[p * 32 + j] = fmaf(gamma, h[p * 32 + j], d[j]);
+    }
+    tc_fence_before();
+    __syncthreads();
+  }
+
+  if (final_state != nullptr && !abort.raised()) {
+    float4* dst = reinterpret_cast<float4*>(final_state + ((int64_t(n) * num_v_heads + hv) * kDim + tid) * kDim);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dst[j] = make_float4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+  }
+  if (abort.raised() && tid == 0) atomicExch(status, kDevWaitTimeout | (2 << 8));
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// fwd_o
+// ---------------------------------------------------------------------------------------------------------------
+struct FwdOSmem {
+  static constexpr uint32_t kQ = 0;               // [64][128] q
+  static constexpr uint32_t kVN = 16384;          // [64][128] v_new
+  static constexpr uint32_t kH = 32768;           // [128][128] h_tape
+  static constexpr uint32_t kAqk = kH + 32768;    // [64][64]
+  static constexpr uint32_t kG = kAqk + 8192;
+  static constexpr uint32_t kBytes = kG + 256;
+};
+
+__global__ void __launch_bounds__(128) gdn_fwd_o_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ aqk, const __nv_bfloat16* __restrict__ v_new,
+    const __nv_bfloat16* __restrict__ h_tape, const float* __restrict__ g_cs, __nv_bfloat16* __restrict__ o,
+    const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len, int num_qk_heads, int num_v_heads,
+    float scale, int32_t* __restrict__ status) {
+  extern __shared__ uint8_t raw[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, hv = blockIdx.y, hq = hv / (num_v_heads / num_qk_heads);
+  const int start = chunk_start[c], len = chunk_len[c];
+  if (len <= 0) return;  // a pad chunk of a device-built table
+  float* s_g2 = reinterpret_cast<float*>(sm + FwdOSmem::kG);
+
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 256);
+  const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
+  const int64_t tile = int64_t(c) * num_v_heads + hv;
+  load_tile<64, 128, 128>(sm + FwdOSmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+  load_tile<64, 128, 128>(sm + FwdOSmem::kVN, 8192, v_new + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+  load_tile<128, 128, 128>(sm + FwdOSmem::kH, 16384, h_tape + tile * 16384, 128, 128, tid);
+  load_tile<64, 64, 128>(sm + FwdOSmem::kAqk, 8192, aqk + tile * 4096, 64, 64, tid);
+  if (tid < 64) s_g2[tid] = g_cs[int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv];
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t sbase = smem_u32(sm);
+  if (tid == 0) {
+    const Operand op_q{sbase + FwdOSmem::kQ, 8192}, op_vn{sbase + FwdOSmem::kVN, 8192};
+    const Operand op_h{sbase + FwdOSmem::kH, 16384}, op_a{sbase + FwdOSmem::kAqk, 8192};
+    umma_gemm<64, 128>(tmem, op_q, false, op_h, true, 128, false);
+    umma_gemm<64, 128>(tmem + 128, op_a, false, op_vn, true, 64, false);
+    umma_commit(&bar);
+  }
+  const bool ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0));
+  tc_fence_after();
+  if (ok) {
+    const int i = warp * 16 + (lane & 15);
+    const bool live = lane < 16 && i < len;
+    const float qs = scale * fast_exp2(s_g2[i]);
+    __nv_bfloat16* dst = o + int64_t(start + i) * v_stride + hv * kDim;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      float a[32], b[32];
+      tmem_ld32(tmem_addr(tmem, warp, p * 32), a);
+      tmem_ld32(tmem_addr(tmem, warp, 128 + p * 32), b);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) a[j] = fmaf(qs, a[j], b[j]);
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst + p * 32)[j] = pack8(a + 8 * j);
+      }
+    }
+  }
+  if (!ok && tid == 0) atomicExch(status, kDevWaitTimeout | (3 << 8));
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+}  // namespace mek
+
+// ---------------------------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+
+int check_dims(const MekGdnDims* d, const char* what) {
+  using namespace mek;
+  if (d == nullptr) return fail(MEK_ERR_INVALID, "%s: dims is null", what);
+  if (d->total_tokens <= 0 || d->num_chunks <= 0 || d->num_seqs <= 0)
+    return fail(MEK_ERR_INVALID, "%s: no tokens (total_tokens=%lld, num_chunks=%d, num_seqs=%d)", what,
+                (long long)d->total_tokens, d->num_chunks, d->num_seqs);
+  if (d->num_qk_heads <= 0 || d->num_v_heads <= 0 || d->num_v_heads % d->num_qk_heads != 0)
+    return fail(MEK_ERR_INVALID, "%s: the value heads (HV=%d) must be a positive multiple of the q / k heads (H=%d)",
+                what, d->num_v_heads, d->num_qk_heads);
+  if (d->head_dim != 128) return fail(MEK_ERR_UNSUPPORTED, "%s: head dims must be 128, not %d", what, d->head_dim);
+  if (d->num_v_heads > 65535 || d->num_seqs > 65535)
+    return fail(MEK_ERR_INVALID, "%s: more than 65535 value heads or sequences", what);
+  if (!d->chunk_start || !d->chunk_len || !d->seq_chunk_start)
+    return fail(MEK_ERR_INVALID, "%s: a chunk table pointer is null", what);
+  return MEK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int mek_gdn_l2norm(const void* x, void* y, float* rstd, int64_t rows, void* stream) {
+  using namespace mek;
+  if (rows <= 0 || !x || !y || !rstd) return fail(MEK_ERR_INVALID, "l2norm: rows=%lld or a null pointer", (long long)rows);
+  l2norm_kernel<<<unsigned((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), rstd, rows);
+  return launched("l2norm");
+}
+
+int mek_gdn_gate_cumsum(const MekGdnDims* d, const float* g, float* g_cs, void* stream) {
+  using namespace mek;
+  if (int rc = check_dims(d, "gate_cumsum")) return rc;
+  const int threads = d->num_v_heads <= 32 ? 32 : (d->num_v_heads <= 64 ? 64 : 128);
+  gate_cumsum_kernel<<<d->num_chunks, threads, 0, static_cast<cudaStream_t>(stream)>>>(g, g_cs, d->chunk_start,
+                                                                                    d->chunk_len, d->num_v_heads);
+  return launched("gate_cumsum");
+}
+
+int mek_gdn_wy_fwd(const MekGdnDims* d, const void* q, const void* k, const void* v, const float* beta,
+                   const float* g_cs, void* a_out, void* aqk_out, void* w_out, void* u_out, int32_t* status,
+                   void* stream) {
+  using namespace mek;
+  if (int rc = check_dims(d, "wy_fwd")) return rc;
+  const size_t smem = WySmem::kBytes + 1024;
+  if (int rc = want_smem(gdn_wy_kernel, smem, "wy_fwd")) return rc;
+  gdn_wy_kernel<<<dim3(d->num_chunks, d->num_v_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
+      beta, g_cs, static_cast<__nv_bfloat16*>(a_out), static_cast<__nv_bfloat16*>(aqk_out),
+      static_cast<__nv_bfloat16*>(w_out), static_cast<__nv_bfloat16*>(u_out), d->chunk_start, d->chunk_len,
+      d->num_qk_heads, d->num_v_heads, d->scale, status);
+  return launched("wy_fwd");
+}
+
+int mek_gdn_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* u, const float* g_cs, const float* h0,
+                  void* h_tape, void* v_new, float* final_state, int32_t* status, void* stream) {
+  using namespace mek;
+  if (int rc = check_dims(d, "fwd_h")) return rc;
+  const size_t smem = FwdHSmem::kBytes + 1024;
+  if (int rc = want_smem(gdn_fwd_h_kernel, smem, "fwd_h")) return rc;
+  gdn_fwd_h_kernel<<<dim3(d->num_seqs, d->num_v_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(u),
+      g_cs, h0, static_cast<__nv_bfloat16*>(h_tape), static_cast<__nv_bfloat16*>(v_new), final_state, d->chunk_start,
+      d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, status);
+  return launched("fwd_h");
+}
+
+int mek_gdn_fwd_o(const MekGdnDims* d, const void* q, const void* aqk, const void* v_new, const void* h_tape,
+                  const float* g_cs, void* o, int32_t* status, void* stream) {
+  using namespace mek;
+  if (int rc = check_dims(d, "fwd_o")) return rc;
+  const size_t smem = FwdOSmem::kBytes + 1024;
+  if (int rc = want_smem(gdn_fwd_o_kernel, smem, "fwd_o")) return rc;
+  gdn_fwd_o_kernel<<<dim3(d->num_chunks, d->num_v_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(aqk),
+      static_cast<const __nv_bfloat16*>(v_new), static_cast<const __nv_bfloat16*>(h_tape), g_cs,
+      static_cast<__nv_bfloat16*>(o), d->chunk_start, d->chunk_len, d->num_qk_heads, d->num_v_heads, d->scale, status);
+  return launched("fwd_o");
+}
+
+}  // extern "C"

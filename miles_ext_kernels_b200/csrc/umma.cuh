@@ -45,10 +45,16 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-// Spin limit of every wait in these kernels: ~2^22 polls with a short back-off is of the order of a second, far
-// beyond any legitimate MMA latency.  A wait that runs out returns false; the kernel then records an error status
-// and leaves through its normal exit (tensor memory freed), so the context stays usable.
-constexpr uint32_t kSpinLimit = 1u << 22;
+// Time limit of every wait in these kernels: one second of wall clock (%globaltimer), far beyond any legitimate MMA
+// latency.  A wait that runs out returns false; the kernel then records an error status and leaves through its
+// normal exit (tensor memory freed), so the context stays usable.
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -63,11 +69,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (spin > 64) __nanosleep(64);
+    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
   }
-  return false;
 }
 
 // ---------------------------------------------------------------------------------------------------------------

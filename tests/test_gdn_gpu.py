@@ -1,0 +1,205 @@
+"""The public entry ``cake.gdn.chunk_gated_delta_rule`` on a B200 against the CPU oracle.
+
+Accuracy budgets are the reference's (reference: tests/cake/gdn/test_gdn_det_gpu.py:58-59, 213-223): per output
+tensor, relative RMS error <= 1e-2 and largest absolute error <= 2e-2 x the largest reference magnitude, against the
+FP64 token recurrence; the FP32 final state and dh0 are held to 1e-3 x their largest magnitude against the chunked
+FP32-state oracle.  Determinism is bitwise.
+"""
+
+from __future__ import annotations
+
+import itertools
+from pathlib import Path
+
+import pytest
+import torch
+
+from gdn_cases import draw
+from oracle import gdn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+NAMES = ("o", "dq", "dk", "dv", "dg", "dbeta")
+REF_LAYOUT = (63, 130, 257, 450)
+
+
+def _cu(seq_lens):
+    return tuple(itertools.accumulate(seq_lens, initial=0))
+
+
+def run(x, seq_lens, *, state=False, l2=True, route="host", views=False, batch=None, **kwargs):
+    """One forward + backward through the public entry; outputs and gradients on the host."""
+    from miles_ext_kernels_b200.cake import gdn
+
+    dev = torch.device("cuda")
+    T = sum(seq_lens)
+    H, HV = x["q"].shape[1], x["v"].shape[1]
+    lead = (1, T) if batch is None else (batch, T // batch)
+    if views:  # miles' packed row: per key head its q, its k, then its value heads
+        G = HV // H
+        mixed = torch.cat([x["q"], x["k"], x["v"].reshape(T, H, G * 128)], dim=-1).reshape(*lead, -1).to(dev)
+        mixed.requires_grad_(True)
+        q, k, v = mixed.view(*lead, H, -1).split([128, 128, G * 128], dim=-1)
+        v = v.reshape(*lead, HV, 128)
+        assert not q.is_contiguous()
+    else:
+        q, k, v = (x[n].to(dev).reshape(*lead, *x[n].shape[1:]).requires_grad_(True) for n in ("q", "k", "v"))
+    g = x["g"].to(dev).reshape(*lead, HV).requires_grad_(True)
+    beta = x["beta"].to(dev).bfloat16().reshape(*lead, HV).requires_grad_(True)
+    h0 = x["h0"].to(dev).requires_grad_(True) if state else None
+    if batch is None:
+        kwargs["cu_seqlens"] = torch.tensor(_cu(seq_lens), dtype=torch.int32, device=dev)
+        if route == "host":
+            kwargs["cu_seqlens_cpu"] = _cu(seq_lens)
+    o, final = gdn.chunk_gated_delta_rule(q, k, v, g=g, beta=beta, initial_state=h0, output_final_state=state,
+                                          use_qk_l2norm_in_kernel=l2, **kwargs)
+    do = x["do"].to(dev).reshape(o.shape)
+    if state:
+        torch.autograd.backward([o, final], [do, x["dht"].to(dev)])
+    else:
+        o.backward(do)
+    torch.cuda.synchronize()
+    if views:
+        dq, dk, dv = mixed.grad.view(*lead, H, -1).split([128, 128, (HV // H) * 128], dim=-1)
+        dv = dv.reshape(*lead, HV, 128)
+    else:
+        dq, dk, dv = q.grad, k.grad, v.grad
+    flat = lambda t: t.detach().reshape(T, *t.shape[2:]).cpu()  # noqa: E731
+    out = {"o": flat(o), "dq": flat(dq), "dk": flat(dk), "dv": flat(dv), "dg": flat(g.grad), "dbeta": flat(beta.grad)}
+    if state:
+        out.update(final_state=final.detach().cpu(), dh0=h0.grad.cpu())
+    return out
+
+
+def assert_within(got, ref, what, names=NAMES):
+    report = {n: O.within_budget(got[n].float(), ref[n]) for n in names}
+    failed = [n for n, (ok, _) in report.items() if not ok]
+    assert not failed, f"{what}: outside the accuracy budgets: {failed}; {report}"
+
+
+def assert_same_bits(got, want, what):
+    differing = [n for n in want if not torch.equal(got[n], want[n])]
+    assert not differing, f"{what}: not the same bits: {differing}"
+
+
+@pytest.mark.parametrize("heads", [(2, 6), (2, 4), (2, 2)], ids=["2x6", "2x4", "2x2"])
+@pytest.mark.parametrize("state", [False, True], ids=["nostate", "state"])
+def test_within_the_reference_budgets_of_the_fp64_recurrence(heads, state):
+    x = draw(REF_LAYOUT, heads, seed=1, gate="weak", state=state)
+    got = run(x, REF_LAYOUT, state=state)
+    ref = O.recurrence_fp64(x["q"], x["k"], x["v"], x["g"], x["beta"], REF_LAYOUT, h0=x.get("h0"), do=x["do"],
+                            dht=x.get("dht"), use_qk_l2norm=True, output_final_state=state)
+    assert_within(got, ref, f"{heads} state={state}")
+    if state:
+        # fp32 state outputs: 1e-3 of the largest magnitude, against the oracle that rounds where the kernels round
+        chunked = O.chunked_forward_backward(x["q"], x["k"], x["v"], x["g"], x["beta"], REF_LAYOUT, x["do"].float(),
+                                             h0=x["h0"], dht=x["dht"], use_qk_l2norm=True, output_final_state=True)
+        for name in ("final_state", "dh0"):
+            m = O.metrics(got[name], chunked[name])
+            assert m["finite"] and m["max_abs"] <= 1e-3 * m["max_ref"], (name, m)
+            ok, m64 = O.within_budget(got[name], ref[name])
+            assert ok, (name, m64)
+
+
+def test_strong_gates_of_the_benchmark_generator():
+    seq_lens = (257, 320)
+    x = draw(seq_lens, (2, 4), seed=2, gate="strong", normalised=True)
+    got = run(x, seq_lens, l2=False)
+    ref = O.recurrence_fp64(x["q"], x["k"], x["v"], x["g"], x["beta"], seq_lens, do=x["do"])
+    assert_within(got, ref, "strong gates")
+
+
+@pytest.mark.parametrize("path", sorted((Path(__file__).parent / "golden").glob("gdn_fake_backend_*.pt")),
+                         ids=lambda p: p.stem)
+def test_against_the_reference_emulation_fixtures(path):
+    record = torch.load(path)
+    i = record["inputs"]
+    x = {n: i[n][0] for n in ("q", "k", "v", "do")}
+    x["g"], x["beta"] = i["g"][0], i["beta"][0].float()
+    got = run(x, record["seq_lens"], l2=record["use_qk_l2norm"])
+    want = {n: record["outputs"][n][0].float() for n in NAMES}
+    assert_within(got, want, path.stem)
+
+
+def test_repeats_bit_for_bit_and_views_give_contiguous_bits():
+    x = draw(REF_LAYOUT, (2, 4), seed=4, state=True)
+    first = run(x, REF_LAYOUT, state=True)
+    again = run(x, REF_LAYOUT, state=True)
+    assert_same_bits(again, first, "second run")
+    views = run(x, REF_LAYOUT, state=True, views=True)
+    assert_same_bits(views, first, "strided views of one packed row")
+
+
+def test_device_boundaries_give_the_host_route_bits():
+    x = draw(REF_LAYOUT, (2, 4), seed=5, state=True)
+    host = run(x, REF_LAYOUT, state=True, route="host")
+    device = run(x, REF_LAYOUT, state=True, route="device")
+    assert_same_bits(device, host, "device-built chunk table")
+
+
+def test_recomputed_state_gives_the_saved_backward_bits():
+    import miles_ext_kernels_b200 as package
+
+    x = draw(REF_LAYOUT, (2, 4), seed=6)
+    saved = run(x, REF_LAYOUT)
+    package.configure(cake_gdn_recompute_state=True)
+    recomputed = run(x, REF_LAYOUT)
+    assert_same_bits(recomputed, saved, "--cake-gdn-recompute-state")
+
+
+def test_equal_length_batch():
+    seq_lens = (256, 256, 256)
+    x = draw(seq_lens, (2, 4), seed=7, state=True)
+    got = run(x, seq_lens, state=True, batch=3)
+    packed = run(x, seq_lens, state=True)
+    assert_same_bits(got, packed, "[B, T] batch vs the same tokens packed")
+
+
+def test_side_stream_and_pool_give_the_same_bits():
+    import miles_ext_kernels_b200 as package
+
+    x = draw(REF_LAYOUT, (2, 4), seed=8)
+    want = run(x, REF_LAYOUT)
+    package.configure(cake_workspace_pool_bytes=1 << 30)
+    side = torch.cuda.Stream()
+    for _ in range(2):
+        with torch.cuda.stream(side):
+            got = run(x, REF_LAYOUT)
+        assert_same_bits(got, want, "side stream with the pool")
+        assert_same_bits(run(x, REF_LAYOUT), want, "default stream with the pool")
+    assert package.release() > 0
+
+
+def test_a_call_without_tokens():
+    from miles_ext_kernels_b200.cake import gdn
+
+    dev = torch.device("cuda")
+    q = torch.empty(1, 0, 2, 128, dtype=torch.bfloat16, device=dev, requires_grad=True)
+    v = torch.empty(1, 0, 4, 128, dtype=torch.bfloat16, device=dev)
+    g = torch.empty(1, 0, 4, device=dev)
+    h0 = torch.randn(1, 4, 128, 128, device=dev)
+    cu = torch.zeros(2, dtype=torch.int32, device=dev)
+    o, final = gdn.chunk_gated_delta_rule(q, q, v, g, g, initial_state=h0, output_final_state=True, cu_seqlens=cu)
+    assert o.shape == v.shape and torch.equal(final, h0)
+
+
+def test_rejections_match_the_reference_messages():
+    from miles_ext_kernels_b200.cake import gdn
+
+    dev = torch.device("cuda")
+    q = torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16, device=dev)
+    v = torch.zeros(1, 128, 4, 128, dtype=torch.bfloat16, device=dev)
+    g = torch.zeros(1, 128, 4, device=dev)
+    cu = torch.tensor([0, 128], dtype=torch.int32, device=dev)
+    with pytest.raises(ValueError, match="must end at the 128 tokens of q; it ends at 127"):
+        gdn.chunk_gated_delta_rule(q, q, v, g, g, cu_seqlens=cu, cu_seqlens_cpu=(0, 127))
+    with pytest.raises(ValueError, match="one state per sequence"):
+        gdn.chunk_gated_delta_rule(q, q, v, g, g, cu_seqlens=cu, initial_state=torch.zeros(2, 4, 128, 128, device=dev))
+    with pytest.raises(ValueError, match="k must have q's shape"):
+        gdn.chunk_gated_delta_rule(q, q[:, :64], v, g, g)
+    with pytest.raises(NotImplementedError, match="chunk_size must be 64"):
+        gdn.chunk_gated_delta_rule(q, q, v, g, g, chunk_size=32)
+    with pytest.raises(NotImplementedError, match="use_gate_in_kernel"):
+        gdn.chunk_gated_delta_rule(q, q, v, g, g, use_gate_in_kernel=True)
+    with pytest.raises(NotImplementedError, match="bfloat16"):
+        gdn.chunk_gated_delta_rule(q.float(), q.float(), v.float(), g, g)
