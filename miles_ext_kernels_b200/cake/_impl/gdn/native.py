@@ -16,7 +16,7 @@ import torch
 
 from ..._runtime import loader
 
-__all__ = ["Dims", "library", "launch", "release"]
+__all__ = ["Dims", "LaunchLog", "library", "launch", "release", "set_launch_log"]
 
 
 class Dims(ctypes.Structure):
@@ -62,11 +62,45 @@ def _argument(value: Any) -> Any:
     return value
 
 
+class LaunchLog:
+    """Counts the kernels launched and, when ``timed``, brackets each launch with CUDA events on the launching
+    stream (``bench.py`` reads per-kernel device times from it; ordinary calls never time)."""
+
+    def __init__(self, timed: bool = False) -> None:
+        self.timed = timed
+        self.count = 0
+        self.events: list[tuple[str, Any, Any]] = []
+
+    def milliseconds(self) -> dict[str, list[float]]:
+        """Per kernel name, the device time of each launch (call after synchronising)."""
+        times: dict[str, list[float]] = {}
+        for name, start, end in self.events:
+            times.setdefault(name, []).append(start.elapsed_time(end))
+        return times
+
+
+_log: LaunchLog | None = None
+
+
+def set_launch_log(log: LaunchLog | None) -> None:
+    global _log
+    _log = log
+
+
 def launch(name: str, *arguments: Any, device: torch.device | None = None) -> None:
     """Call ``mek_<name>(*arguments, stream)`` with torch's current stream of ``device`` appended."""
     lib = library()
-    stream = torch.cuda.current_stream(device).cuda_stream
-    code = getattr(lib, f"mek_{name}")(*(_argument(a) for a in arguments), ctypes.c_void_p(stream))
+    current = torch.cuda.current_stream(device)
+    log = _log
+    if log is not None:
+        log.count += 1
+        if log.timed:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(current)
+    code = getattr(lib, f"mek_{name}")(*(_argument(a) for a in arguments), ctypes.c_void_p(current.cuda_stream))
+    if log is not None and log.timed:
+        end.record(current)
+        log.events.append((name, start, end))
     lib.check(code)
 
 
