@@ -118,6 +118,18 @@ int mek_gdn_bwd_tail(const MekGdnDims* dims, const void* q, const void* k, const
                      const float* rstd_q, const float* rstd_k, void* dq, void* dk, void* dv, float* dbeta, float* dg,
                      int32_t* status, void* stream);
 
+/* Forward of the gated delta rule without any device allocation: o bf16 [T, HV, 128] and, when final_state is not
+ * NULL, the fp32 final state [N, HV, 128, 128], from q, k (normalised), v, beta, the raw gate g and an optional h0.
+ * The intermediates of the forward stages live in a fixed device array inside the library instead of
+ * caller-allocated tensors, for hosts that may not allocate once their memory plan is set.  Limits:
+ * total_tokens * num_v_heads <= 8192 and num_chunks * num_v_heads <= 256 (MEK_ERR_INVALID beyond).  The first call on
+ * a device looks up the array's address and should come before any stream capture; calls that overlap on one GPU
+ * share the array and race.  Same results as mek_gdn_gate_cumsum + mek_gdn_wy_fwd + mek_gdn_fwd_h + mek_gdn_fwd_o.
+ * This entry point has no counterpart in the reference. */
+int mek_gdn_forward_static(const MekGdnDims* dims, const void* q, const void* k, const void* v, const float* beta,
+                           const float* g, const float* h0, void* o, float* final_state, int32_t* status,
+                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif
