@@ -71,7 +71,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+                 "-lms", "50"], stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
         return self
@@ -248,13 +248,20 @@ def run_ours(args) -> None:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    for _ in range(max(args.warmup, 3)):
-        step(resident)
-    log = native.LaunchLog(timed=False)
-    native.set_launch_log(log)
+    # clocks are sampled from the warm-up on (a 10-step timed region is shorter than nvidia-smi's sampling period);
+    # only samples taken under load enter the median
     with ClockSampler(local) as sampler:
+        for _ in range(max(args.warmup, 3)):
+            step(resident)
+        log = native.LaunchLog(timed=False)
+        native.set_launch_log(log)
         ms = timed(lambda: step(resident), args.steps)
-    native.set_launch_log(None)
+        native.set_launch_log(None)
+        if ms < 400.0:  # keep the GPU busy with the same step until the sampler has seen it under load
+            busy_until = time.perf_counter() + 0.5
+            while time.perf_counter() < busy_until:
+                step(resident)
+            torch.cuda.synchronize()
     clocks = sampler.summary()
     launches = log.count
 

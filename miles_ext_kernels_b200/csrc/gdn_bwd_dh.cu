@@ -13,20 +13,22 @@
 
 namespace mek {
 
+// One CTA of two warpgroups per (sequence, value head); thread (k, half) holds row k of one half of the V columns of
+// the fp32 adjoint state.  The previous chunk's (c - 1, walked next) tiles arrive by cp.async while chunk c computes.
 struct BwdDhSmem {
+  static constexpr uint32_t kStage = 4 * 16384 + 8192;  // k, q, w, do tiles and Aqk of one chunk
   static constexpr uint32_t kK = 0;                 // [64][128] k        K-major A of k dh
   static constexpr uint32_t kQ = 16384;             // [64][128] q        MN-major A of q^T do_g
   static constexpr uint32_t kW = 2 * 16384;         // [64][128] w        MN-major A of w^T dv_new (negated)
-  static constexpr uint32_t kDO = 3 * 16384;        // [64][128] do       MN-major B of Aqk^T do
-  static constexpr uint32_t kDOG = 4 * 16384;       // [64][128] bf16(qscale do)
-  static constexpr uint32_t kDV = 5 * 16384;        // [64][128] dv_new
-  static constexpr uint32_t kDH = 6 * 16384;        // [128][128] bf16(dh), 2 blocks of 16 KiB
-  static constexpr uint32_t kAqk = kDH + 32768;     // [64][64]
-  static constexpr uint32_t kG = kAqk + 8192;       // g2[64]
-  static constexpr uint32_t kBytes = kG + 256;
+  static constexpr uint32_t kDO = 3 * 16384;        // [64][128] do -> bf16(qscale do) in place
+  static constexpr uint32_t kAqk = 4 * 16384;       // [64][64]
+  static constexpr uint32_t kDV = 2 * kStage;       // [64][128] dv_new
+  static constexpr uint32_t kDH = kDV + 16384;      // [128][128] bf16(dh), 2 blocks of 16 KiB (one per V half)
+  static constexpr uint32_t kG = kDH + 32768;       // g2[2][64]
+  static constexpr uint32_t kBytes = kG + 512;
 };
 
-__global__ void __launch_bounds__(128) gdn_bwd_dh_kernel(
+__global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ w,
     const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ aqk, const float* __restrict__ g_cs,
     const float* __restrict__ dht, __nv_bfloat16* __restrict__ dh_tape, __nv_bfloat16* __restrict__ dv_new,
@@ -39,6 +41,8 @@ __global__ void __launch_bounds__(128) gdn_bwd_dh_kernel(
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quad = warp & 3, half = warp >> 2;
+  const int krow = quad * 32 + lane;
   const int n = blockIdx.x, hv = blockIdx.y, hq = hv / (num_v_heads / num_qk_heads);
   float* s_g2 = reinterpret_cast<float*>(sm + BwdDhSmem::kG);
   Abort abort{&abort_flag};
@@ -49,92 +53,94 @@ __global__ void __launch_bounds__(128) gdn_bwd_dh_kernel(
     abort_flag = 0;
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 512);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_slot;
   const uint32_t sbase = smem_u32(sm);
-  const Operand op_k{sbase + BwdDhSmem::kK, 8192}, op_q{sbase + BwdDhSmem::kQ, 8192};
-  const Operand op_w{sbase + BwdDhSmem::kW, 8192}, op_do{sbase + BwdDhSmem::kDO, 8192};
-  const Operand op_dog{sbase + BwdDhSmem::kDOG, 8192}, op_dv{sbase + BwdDhSmem::kDV, 8192};
-  const Operand op_dh{sbase + BwdDhSmem::kDH, 16384}, op_aqk{sbase + BwdDhSmem::kAqk, 8192};
   const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
   constexpr uint32_t kD1 = 0, kD1b = 128, kD2 = 256;  // tensor-memory columns
+  const int c_begin = seq_chunk_start[n], c_end = seq_chunk_start[n + 1];
 
-  // fp32 adjoint state: thread `tid` holds row k = tid of dh [K, V]
-  float dh[128];
+  auto prefetch = [&](int c, int stage) {
+    const int start = chunk_start[c], len = chunk_len[c];
+    const uint32_t base = sbase + stage * BwdDhSmem::kStage;
+    prefetch_tile<64, 128, 256>(base + BwdDhSmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+    prefetch_tile<64, 128, 256>(base + BwdDhSmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+    prefetch_tile<64, 128, 256>(base + BwdDhSmem::kW, 8192, w + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+    prefetch_tile<64, 128, 256>(base + BwdDhSmem::kDO, 8192, d_o + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+    prefetch_tile<64, 64, 256>(base + BwdDhSmem::kAqk, 8192, aqk + (int64_t(c) * num_v_heads + hv) * 4096, 64, 64, tid);
+    if (tid < 64)
+      cp_async4(smem_u32(s_g2 + stage * 64 + tid), g_cs + int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv);
+    cp_async_commit();
+  };
+  if (c_begin < c_end) prefetch(c_end - 1, 0);
+
+  // fp32 adjoint state: 64 columns of row krow
+  float dh[64];
   if (dht != nullptr) {
-    const float4* src = reinterpret_cast<const float4*>(dht + ((int64_t(n) * num_v_heads + hv) * kDim + tid) * kDim);
+    const float4* src =
+        reinterpret_cast<const float4*>(dht + ((int64_t(n) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < 16; ++j) {
       const float4 t = __ldg(src + j);
       dh[4 * j] = t.x, dh[4 * j + 1] = t.y, dh[4 * j + 2] = t.z, dh[4 * j + 3] = t.w;
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 128; ++j) dh[j] = 0.f;
+    for (int j = 0; j < 64; ++j) dh[j] = 0.f;
   }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const Operand op_dv{sbase + BwdDhSmem::kDV, 8192}, op_dh{sbase + BwdDhSmem::kDH, 16384};
 
   uint32_t phase = 0;
-  const int c_begin = seq_chunk_start[n];
-  for (int c = seq_chunk_start[n + 1] - 1; c >= c_begin; --c) {
+  for (int c = c_end - 1; c >= c_begin; --c) {
+    const int stage = (c_end - 1 - c) & 1;
     const int start = chunk_start[c], len = chunk_len[c];
     const int64_t tile = int64_t(c) * num_v_heads + hv;
-    load_tile<64, 128, 128>(sm + BwdDhSmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-    load_tile<64, 128, 128>(sm + BwdDhSmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-    load_tile<64, 128, 128>(sm + BwdDhSmem::kW, 8192, w + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-    load_tile<64, 128, 128>(sm + BwdDhSmem::kDO, 8192, d_o + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-    load_tile<64, 64, 128>(sm + BwdDhSmem::kAqk, 8192, aqk + tile * 4096, 64, 64, tid);
-    if (tid < 64) s_g2[tid] = g_cs[int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv];
+    uint8_t* st = sm + stage * BwdDhSmem::kStage;
+    const uint32_t sst = sbase + stage * BwdDhSmem::kStage;
+    const Operand op_k{sst + BwdDhSmem::kK, 8192}, op_q{sst + BwdDhSmem::kQ, 8192};
+    const Operand op_w{sst + BwdDhSmem::kW, 8192}, op_do{sst + BwdDhSmem::kDO, 8192};
+    const Operand op_aqk{sst + BwdDhSmem::kAqk, 8192};
     {
-      __nv_bfloat16* tape = dh_tape + (tile * kDim + tid) * kDim;
+      __nv_bfloat16* tape = dh_tape + (tile * kDim + krow) * kDim + half * 64;
 #pragma unroll
-      for (int cc = 0; cc < 16; ++cc) {
+      for (int cc = 0; cc < 8; ++cc) {
         const uint4 packed = pack8(dh + 8 * cc);
-        set_tile_chunk(sm + BwdDhSmem::kDH, 16384, tid, cc, packed);
+        set_tile_chunk(sm + BwdDhSmem::kDH, 16384, krow, half * 8 + cc, packed);
         reinterpret_cast<uint4*>(tape)[cc] = packed;
       }
     }
-    __syncthreads();
-    if (abort.raised()) break;
-    // do_g = bf16(qscale do)
-    for (int i = tid; i < 64 * 16; i += 128) {
-      const int r = i >> 4, cc = i & 15;
-      const float qs = scale * fast_exp2(s_g2[r]);
-      float x[8];
-      unpack8(tile_chunk(sm + BwdDhSmem::kDO, 8192, r, cc), x);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] *= qs;
-      set_tile_chunk(sm + BwdDhSmem::kDOG, 8192, r, cc, pack8(x));
-    }
+    cp_async_wait_all();
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (abort.raised()) break;
 
     if (tid == 0) {
       umma_gemm<64, 128>(tmem + kD1, op_k, false, op_dh, true, 128, false);      // k dh_tape
       umma_gemm<64, 128>(tmem + kD1b, op_aqk, true, op_do, true, 64, false);     // Aqk^T do
-      umma_gemm<128, 128>(tmem + kD2, op_q, true, op_dog, true, 64, false);      // q^T do_g
       umma_commit(&bar);
     }
+    if (c > c_begin) prefetch(c - 1, stage ^ 1);
     if (!mbar_wait(&bar, phase)) abort.raise();
     phase ^= 1;
     tc_fence_after();
 
-    const float g_last = s_g2[len - 1];
+    const float* g2 = s_g2 + stage * 64;
+    const float g_last = g2[len - 1];
     {
-      // every lane runs the warp-wide tensor-memory loads; lanes 0..15 own the rows of an M = 64 accumulator
-      const int i = warp * 16 + (lane & 15);
+      const int i = quad * 16 + (lane & 15);
       const bool owner = lane < 16;
       const bool live = owner && i < len;
-      const float rs = live ? fast_exp2(g_last - s_g2[i]) : 0.f;
-      __nv_bfloat16* drow = dv_new + int64_t(start + i) * v_stride + hv * kDim;
+      const float rs = live ? fast_exp2(g_last - g2[i]) : 0.f;
+      __nv_bfloat16* drow = dv_new + int64_t(start + i) * v_stride + hv * kDim + half * 64;
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
+      for (int p = 0; p < 2; ++p) {
         float a[32], b[32];
-        tmem_ld32(tmem_addr(tmem, warp, kD1 + p * 32), a);
-        tmem_ld32(tmem_addr(tmem, warp, kD1b + p * 32), b);
+        tmem_ld32(tmem_addr(tmem, warp, kD1 + half * 64 + p * 32), a);
+        tmem_ld32(tmem_addr(tmem, warp, kD1b + half * 64 + p * 32), b);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) a[j] = live ? fmaf(rs, a[j], round_bf16(b[j])) : 0.f;
@@ -142,9 +148,19 @@ __global__ void __launch_bounds__(128) gdn_bwd_dh_kernel(
         for (int jj = 0; jj < 4; ++jj) {
           const uint4 packed = pack8(a + 8 * jj);
           if (live) reinterpret_cast<uint4*>(drow + p * 32)[jj] = packed;
-          if (owner) set_tile_chunk(sm + BwdDhSmem::kDV, 8192, i, p * 4 + jj, packed);
+          if (owner) set_tile_chunk(sm + BwdDhSmem::kDV, 8192, i, half * 8 + p * 4 + jj, packed);
         }
       }
+    }
+    // do -> do_g = bf16(qscale do), in place (Aqk^T do has read do)
+    for (int i = tid; i < 64 * 16; i += 256) {
+      const int r = i >> 4, cc = i & 15;
+      const float qs = scale * fast_exp2(g2[r]);
+      float x[8];
+      unpack8(tile_chunk(st + BwdDhSmem::kDO, 8192, r, cc), x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] *= qs;
+      set_tile_chunk(st + BwdDhSmem::kDO, 8192, r, cc, pack8(x));
     }
     fence_async_smem();
     tc_fence_before();
@@ -152,7 +168,8 @@ __global__ void __launch_bounds__(128) gdn_bwd_dh_kernel(
     tc_fence_after();
 
     if (tid == 0) {
-      umma_gemm<128, 128>(tmem + kD2, op_w, true, op_dv, true, 64, true, /*neg_a=*/true);  // - w^T dv_new
+      umma_gemm<128, 128>(tmem + kD2, op_q, true, op_do, true, 64, false);                  // q^T do_g
+      umma_gemm<128, 128>(tmem + kD2, op_w, true, op_dv, true, 64, true, /*neg_a=*/true);   // - w^T dv_new
       umma_commit(&bar);
     }
     if (!mbar_wait(&bar, phase)) abort.raise();
@@ -161,25 +178,24 @@ __global__ void __launch_bounds__(128) gdn_bwd_dh_kernel(
 
     const float gamma = fast_exp2(g_last);
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
+    for (int p = 0; p < 2; ++p) {
       float d[32];
-      tmem_ld32(tmem_addr(tmem, warp, kD2 + p * 32), d);
+      tmem_ld32(tmem_addr(tmem, warp, kD2 + half * 64 + p * 32), d);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) dh[p * 32 + j] = fmaf(gamma, dh[p * 32 + j], d[j]);
     }
-    tc_fence_before();
-    __syncthreads();
   }
-
-  if (dh0 != nullptr && !abort.raised()) {
-    float4* dst = reinterpret_cast<float4*>(dh0 + ((int64_t(n) * num_v_heads + hv) * kDim + tid) * kDim);
-#pragma unroll
-    for (int j = 0; j < 32; ++j) dst[j] = make_float4(dh[4 * j], dh[4 * j + 1], dh[4 * j + 2], dh[4 * j + 3]);
-  }
-  if (abort.raised() && tid == 0) atomicExch(status, kDevWaitTimeout | (4 << 8));
+  cp_async_wait_all();
   tc_fence_before();
   __syncthreads();
+
+  if (dh0 != nullptr && !abort.raised()) {
+    float4* dst = reinterpret_cast<float4*>(dh0 + ((int64_t(n) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) dst[j] = make_float4(dh[4 * j], dh[4 * j + 1], dh[4 * j + 2], dh[4 * j + 3]);
+  }
+  if (abort.raised() && tid == 0) atomicExch(status, kDevWaitTimeout | (4 << 8));
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
@@ -195,7 +211,7 @@ extern "C" int mek_gdn_bwd_dh(const MekGdnDims* d, const void* q, const void* k,
   if (d->head_dim != 128) return fail(MEK_ERR_UNSUPPORTED, "bwd_dh: head dims must be 128, not %d", d->head_dim);
   const size_t smem = BwdDhSmem::kBytes + 1024;
   if (int rc = want_smem(gdn_bwd_dh_kernel, smem, "bwd_dh")) return rc;
-  gdn_bwd_dh_kernel<<<dim3(d->num_seqs, d->num_v_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
+  gdn_bwd_dh_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(w),
       static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(aqk), g_cs, dht,
       static_cast<__nv_bfloat16*>(dh_tape), static_cast<__nv_bfloat16*>(dv_new), dh0, d->chunk_start, d->chunk_len,

@@ -234,16 +234,22 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
 // ---------------------------------------------------------------------------------------------------------------
 // fwd_h : the state recurrence
 // ---------------------------------------------------------------------------------------------------------------
+// One CTA of two warpgroups per (sequence, value head).  The fp32 state h [K, V] lives in registers: thread (k, half)
+// holds row k of one half of the V columns (warpgroup 0: columns 0..63, warpgroup 1: 64..127).  Per chunk:
+//   1. h_tape = bf16(h) -> shared (MN-major B operand) and the tape;            2. D1 = w h_tape        (M=64,N=128,K=128)
+//   3. v_new = u - D1 -> tape; vs = bf16(rowscale v_new) -> shared;              4. D2 = k^T vs         (M=128,N=128,K=64)
+//   5. h = gamma h + D2.
+// The next chunk's w / k / u tiles and gates arrive by cp.async while the current chunk computes (two stages).
 struct FwdHSmem {
-  static constexpr uint32_t kW = 0;               // [64][128] w
-  static constexpr uint32_t kK = 16384;           // [64][128] k
-  static constexpr uint32_t kH = 32768;           // [128 k][128 v] bf16(h), 2 blocks of 16 KiB
+  static constexpr uint32_t kStage = 3 * 16384;   // w, k, u tiles of one chunk
+  static constexpr uint32_t kW = 0, kK = 16384, kU = 32768;
+  static constexpr uint32_t kH = 2 * kStage;      // [128 k][128 v] bf16(h), 2 blocks of 16 KiB (one per V half)
   static constexpr uint32_t kVS = kH + 32768;     // [64][128] bf16(rowscale v_new)
-  static constexpr uint32_t kG = kVS + 16384;     // g2[64]
-  static constexpr uint32_t kBytes = kG + 256;
+  static constexpr uint32_t kG = kVS + 16384;     // g2[2][64]
+  static constexpr uint32_t kBytes = kG + 512;
 };
 
-__global__ void __launch_bounds__(128) gdn_fwd_h_kernel(
+__global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ u,
     const float* __restrict__ g_cs, const float* __restrict__ h0, __nv_bfloat16* __restrict__ h_tape,
     __nv_bfloat16* __restrict__ v_new, float* __restrict__ final_state, const int32_t* __restrict__ chunk_start,
@@ -255,6 +261,8 @@ __global__ void __launch_bounds__(128) gdn_fwd_h_kernel(
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quad = warp & 3, half = warp >> 2;   // tensor-memory lane quadrant; V half of this warpgroup
+  const int krow = quad * 32 + lane;             // row of h this thread holds
   const int n = blockIdx.x, hv = blockIdx.y, hq = hv / (num_v_heads / num_qk_heads);
   float* s_g2 = reinterpret_cast<float*>(sm + FwdHSmem::kG);
   Abort abort{&abort_flag};
@@ -265,46 +273,60 @@ __global__ void __launch_bounds__(128) gdn_fwd_h_kernel(
     abort_flag = 0;
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 256);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_slot;
   const uint32_t sbase = smem_u32(sm);
-  const Operand op_w{sbase + FwdHSmem::kW, 8192}, op_k{sbase + FwdHSmem::kK, 8192};
-  const Operand op_h{sbase + FwdHSmem::kH, 16384}, op_vs{sbase + FwdHSmem::kVS, 8192};
   const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
+  const int c_begin = seq_chunk_start[n], c_end = seq_chunk_start[n + 1];
 
-  // fp32 state: thread `tid` holds row k = tid of h [K, V]
-  float h[128];
+  auto prefetch = [&](int c, int stage) {
+    const int start = chunk_start[c], len = chunk_len[c];
+    const uint32_t base = sbase + stage * FwdHSmem::kStage;
+    prefetch_tile<64, 128, 256>(base + FwdHSmem::kW, 8192, w + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+    prefetch_tile<64, 128, 256>(base + FwdHSmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+    prefetch_tile<64, 128, 256>(base + FwdHSmem::kU, 8192, u + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+    if (tid < 64)
+      cp_async4(smem_u32(s_g2 + stage * 64 + tid), g_cs + int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv);
+    cp_async_commit();
+  };
+  if (c_begin < c_end) prefetch(c_begin, 0);
+
+  // fp32 state: 64 columns of row krow
+  float h[64];
   if (h0 != nullptr) {
-    const float4* src = reinterpret_cast<const float4*>(h0 + ((int64_t(n) * num_v_heads + hv) * kDim + tid) * kDim);
+    const float4* src =
+        reinterpret_cast<const float4*>(h0 + ((int64_t(n) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < 16; ++j) {
       const float4 t = __ldg(src + j);
       h[4 * j] = t.x, h[4 * j + 1] = t.y, h[4 * j + 2] = t.z, h[4 * j + 3] = t.w;
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 128; ++j) h[j] = 0.f;
+    for (int j = 0; j < 64; ++j) h[j] = 0.f;
   }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const Operand op_h{sbase + FwdHSmem::kH, 16384}, op_vs{sbase + FwdHSmem::kVS, 8192};
 
   uint32_t phase = 0;
-  const int c_end = seq_chunk_start[n + 1];
-  for (int c = seq_chunk_start[n]; c < c_end; ++c) {
+  for (int c = c_begin; c < c_end; ++c) {
+    const int stage = (c - c_begin) & 1;
     const int start = chunk_start[c], len = chunk_len[c];
-    load_tile<64, 128, 128>(sm + FwdHSmem::kW, 8192, w + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-    load_tile<64, 128, 128>(sm + FwdHSmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-    if (tid < 64) s_g2[tid] = g_cs[int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv];
-    // h_tape = bf16(h): to shared (MN-major B operand of w h) and to the tape
+    uint8_t* st = sm + stage * FwdHSmem::kStage;
+    const Operand op_w{sbase + stage * FwdHSmem::kStage + FwdHSmem::kW, 8192};
+    const Operand op_k{sbase + stage * FwdHSmem::kStage + FwdHSmem::kK, 8192};
+    // 1. h_tape = bf16(h): this thread's half row -> shared (block `half`) and the tape
     {
-      __nv_bfloat16* tape = h_tape + ((int64_t(c) * num_v_heads + hv) * kDim + tid) * kDim;
+      __nv_bfloat16* tape = h_tape + ((int64_t(c) * num_v_heads + hv) * kDim + krow) * kDim + half * 64;
 #pragma unroll
-      for (int cc = 0; cc < 16; ++cc) {
+      for (int cc = 0; cc < 8; ++cc) {
         const uint4 packed = pack8(h + 8 * cc);
-        set_tile_chunk(sm + FwdHSmem::kH, 16384, tid, cc, packed);
+        set_tile_chunk(sm + FwdHSmem::kH, 16384, krow, half * 8 + cc, packed);
         reinterpret_cast<uint4*>(tape)[cc] = packed;
       }
     }
+    cp_async_wait_all();  // this chunk's tiles have landed (issued one step ago)
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -315,40 +337,36 @@ __global__ void __launch_bounds__(128) gdn_fwd_h_kernel(
       umma_gemm<64, 128>(tmem, op_w, false, op_h, true, 128, false);
       umma_commit(&bar);
     }
+    if (c + 1 < c_end) prefetch(c + 1, stage ^ 1);  // the other stage's last readers finished a step ago
     if (!mbar_wait(&bar, phase)) abort.raise();
     phase ^= 1;
     tc_fence_after();
 
-    const float g_last = s_g2[len - 1];
+    const float* g2 = s_g2 + stage * 64;
+    const float g_last = g2[len - 1];
     {
-      // every lane runs the warp-wide tensor-memory loads; lanes 0..15 own the rows of an M = 64 accumulator
-      const int i = warp * 16 + (lane & 15);
+      // rows of the M = 64 accumulator: lanes 0..15 of each quadrant; the warpgroups split the columns
+      const int i = quad * 16 + (lane & 15);
       const bool owner = lane < 16;
       const bool live = owner && i < len;
-      const float rs = live ? fast_exp2(g_last - s_g2[i]) : 0.f;
-      const __nv_bfloat16* urow = u + int64_t(start + i) * v_stride + hv * kDim;
-      __nv_bfloat16* vrow = v_new + int64_t(start + i) * v_stride + hv * kDim;
+      const float rs = live ? fast_exp2(g_last - g2[i]) : 0.f;
+      __nv_bfloat16* vrow = v_new + int64_t(start + i) * v_stride + hv * kDim + half * 64;
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
+      for (int p = 0; p < 2; ++p) {
         float d[32];
-        tmem_ld32(tmem_addr(tmem, warp, p * 32), d);
+        tmem_ld32(tmem_addr(tmem, warp, half * 64 + p * 32), d);
         tmem_ld_wait();
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
           float uv[8], vs[8];
-          if (live) {
-            unpack8(ldg16(urow + p * 32 + jj * 8), uv);
-          } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) uv[e] = 0.f;
-          }
+          unpack8(tile_chunk(st + FwdHSmem::kU, 8192, i, half * 8 + p * 4 + jj), uv);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            uv[e] -= d[jj * 8 + e];
+            uv[e] = live ? uv[e] - d[jj * 8 + e] : 0.f;
             vs[e] = rs * uv[e];
           }
           if (live) reinterpret_cast<uint4*>(vrow + p * 32)[jj] = pack8(uv);
-          if (owner) set_tile_chunk(sm + FwdHSmem::kVS, 8192, i, p * 4 + jj, pack8(vs));
+          if (owner) set_tile_chunk(sm + FwdHSmem::kVS, 8192, i, half * 8 + p * 4 + jj, pack8(vs));
         }
       }
     }
@@ -367,25 +385,25 @@ __global__ void __launch_bounds__(128) gdn_fwd_h_kernel(
 
     const float gamma = fast_exp2(g_last);
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
+    for (int p = 0; p < 2; ++p) {
       float d[32];
-      tmem_ld32(tmem_addr(tmem, warp, 128 + p * 32), d);
+      tmem_ld32(tmem_addr(tmem, warp, 128 + half * 64 + p * 32), d);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) h[p * 32 + j] = fmaf(gamma, h[p * 32 + j], d[j]);
     }
-    tc_fence_before();
-    __syncthreads();
   }
-
-  if (final_state != nullptr && !abort.raised()) {
-    float4* dst = reinterpret_cast<float4*>(final_state + ((int64_t(n) * num_v_heads + hv) * kDim + tid) * kDim);
-#pragma unroll
-    for (int j = 0; j < 32; ++j) dst[j] = make_float4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
-  }
-  if (abort.raised() && tid == 0) atomicExch(status, kDevWaitTimeout | (2 << 8));
+  cp_async_wait_all();
   tc_fence_before();
   __syncthreads();
+
+  if (final_state != nullptr && !abort.raised()) {
+    float4* dst =
+        reinterpret_cast<float4*>(final_state + ((int64_t(n) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) dst[j] = make_float4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+  }
+  if (abort.raised() && tid == 0) atomicExch(status, kDevWaitTimeout | (2 << 8));
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
@@ -534,7 +552,7 @@ int mek_gdn_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void*
   if (int rc = check_dims(d, "fwd_h")) return rc;
   const size_t smem = FwdHSmem::kBytes + 1024;
   if (int rc = want_smem(gdn_fwd_h_kernel, smem, "fwd_h")) return rc;
-  gdn_fwd_h_kernel<<<dim3(d->num_seqs, d->num_v_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
+  gdn_fwd_h_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(u),
       g_cs, h0, static_cast<__nv_bfloat16*>(h_tape), static_cast<__nv_bfloat16*>(v_new), final_state, d->chunk_start,
       d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, status);

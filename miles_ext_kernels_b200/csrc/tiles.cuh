@@ -42,6 +42,32 @@ __device__ __forceinline__ void store_tile(const uint8_t* tile, uint32_t block_s
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// asynchronous copies (cp.async): the next chunk's tiles land in shared memory while the current chunk computes
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Asynchronous version of load_tile: rows >= valid_rows are zero-filled (copy size 0).  `tile` is a shared address.
+template <int ROWS, int COLS, int NT>
+__device__ __forceinline__ void prefetch_tile(uint32_t tile, uint32_t block_stride, const __nv_bfloat16* g,
+                                              int64_t row_stride, int valid_rows, int tid) {
+  constexpr int CPR = COLS / 8;
+#pragma unroll 4
+  for (int i = tid; i < ROWS * CPR; i += NT) {
+    const int r = i / CPR, cc = i % CPR;
+    const bool valid = r < valid_rows;
+    cp_async16(tile + (cc >> 3) * block_stride + sw128_offset(r, cc & 7),
+               g + (valid ? int64_t(r) * row_stride : 0) + cc * 8, valid);
+  }
+}
+
 // 8 consecutive bf16 (one 16-byte chunk) of row `row`, logical column chunk `cc` (0..COLS/8-1).
 __device__ __forceinline__ uint4 tile_chunk(const uint8_t* tile, uint32_t block_stride, int row, int cc) {
   return *reinterpret_cast<const uint4*>(tile + (cc >> 3) * block_stride + sw128_offset(row, cc & 7));
