@@ -20,25 +20,32 @@
 namespace mek {
 
 struct TailSmem {
-  static constexpr uint32_t kQ = 0;                    // [64][128] q (per key head)
-  static constexpr uint32_t kK = 16384;                // [64][128] k
-  static constexpr uint32_t kH = 32768;                // [128][128] h_tape; later DW at +0, KB at +16384
+  static constexpr uint32_t kQK = 0;                   // 2 x {[64][128] q, [64][128] k}: one buffer per (chunk, key head)
+  static constexpr uint32_t kQKStride = 32768;
+  static constexpr uint32_t kH = 2 * kQKStride;        // [128][128] h_tape; later DW at +0, KB at +16384
   static constexpr uint32_t kDH = kH + 32768;          // [128][128] dh_tape; later VB at +0
   static constexpr uint32_t kDO = kDH + 32768;         // [64][128] do -> do_g in place
-  static constexpr uint32_t kVN = kDO + 16384;         // [64][128] v_new
+  static constexpr uint32_t kVN = kDO + 16384;         // [64][128] v_new, then this value head's raw v
   static constexpr uint32_t kDVN = kVN + 16384;        // [64][128] dv_new
   static constexpr uint32_t kA = kDVN + 16384;         // [64][64] A
   static constexpr uint32_t kAqk = kA + 8192;          // [64][64] Aqk
   static constexpr uint32_t kB8a = kAqk + 8192;        // [64][64] dS -> dA -> bf16(beta dL D)
   static constexpr uint32_t kB8b = kB8a + 8192;        // [64][64] X = A^T dA
-  static constexpr uint32_t kKKt = kB8b + 8192;        // fp32 [64 j][65] : KK[i][j] at j * 65 + i
-  static constexpr uint32_t kP = kKKt + 64 * 65 * 4;   // fp32 [64 j][65] : scratch for column sums
-  static constexpr uint32_t kScal = kP + 64 * 65 * 4;  // beta[64], g2[64], red[2][64], red2[2][64], warp[8]
-  static constexpr uint32_t kBytes = kScal + (64 * 6 + 16) * 4;
+  static constexpr uint32_t kScal = kB8b + 8192;       // floats: beta[2][64], g2[2][64], cs[2][4][64], red[2][64],
+                                                       //         red2[2][64], warp[8]
+  static constexpr uint32_t kBytes = kScal + (2 * 64 * 2 + 2 * 4 * 64 + 4 * 64 + 16) * 4;
 };
 
-constexpr uint32_t kColDQ = 0, kColDK = 128, kColT0 = 256, kColT1 = 320, kColT2 = 384;
+constexpr uint32_t kColDQ = 0, kColDK = 128, kColT0 = 256, kColTa = 384, kColTb = 448;
 
+template <int N>
+__device__ __forceinline__ void cp_async_wait_pending() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// One persistent CTA per SM walks (chunk, key head) pairs; inside a pair it walks the value heads of the group.
+// While one value head computes, the next one's tiles arrive by cp.async in the buffers the current one has
+// finished with (q / k of the next pair are double-buffered).
 __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
     const float* __restrict__ beta, const float* __restrict__ g_cs, const __nv_bfloat16* __restrict__ a_in,
@@ -48,31 +55,28 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     const __nv_bfloat16* __restrict__ q_raw, const __nv_bfloat16* __restrict__ k_raw,
     const float* __restrict__ rstd_q, const float* __restrict__ rstd_k, __nv_bfloat16* __restrict__ dq,
     __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, float* __restrict__ dbeta, float* __restrict__ dg,
-    const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len, int num_qk_heads, int num_v_heads,
-    float scale, int32_t* __restrict__ status) {
+    const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len, int num_chunks, int num_qk_heads,
+    int num_v_heads, float scale, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = blockIdx.x, hq = blockIdx.y, group = num_v_heads / num_qk_heads;
-  const int start = chunk_start[c], len = chunk_len[c];
-  if (len <= 0) return;  // a pad chunk of a device-built table
+  const int group = num_v_heads / num_qk_heads;
+  const int num_pairs = num_chunks * num_qk_heads;
   // accumulator rows: M = 64 results live in lanes 0..15 of each warp's tensor-memory quadrant; warps w and w + 4
   // share the rows 16 (w % 4) .. + 15 and split the columns in halves
   const int quad = warp & 3, ch = warp >> 2;
   const int row = quad * 16 + (lane & 15);
   const bool owner = lane < 16;
-  const bool live = owner && row < len;
 
-  float* s_kkt = reinterpret_cast<float*>(sm + TailSmem::kKKt);
-  float* s_p = reinterpret_cast<float*>(sm + TailSmem::kP);
-  float* s_beta = reinterpret_cast<float*>(sm + TailSmem::kScal);
-  float* s_g2 = s_beta + 64;
-  float* s_red = s_g2 + 64;    // [2][64]
-  float* s_red2 = s_red + 128; // [2][64]
-  float* s_warp = s_red2 + 128;  // [8] (+ broadcast slot at [8])
+  float* s_beta = reinterpret_cast<float*>(sm + TailSmem::kScal);  // [2][64]
+  float* s_g2 = s_beta + 128;                                      // [2][64]
+  float* s_cs = s_g2 + 128;                                        // [2][4][64] partial column sums per quadrant
+  float* s_red = s_cs + 512;                                       // [2][64]
+  float* s_red2 = s_red + 128;                                     // [2][64]
+  float* s_warp = s_red2 + 128;                                    // [8]
   Abort abort{&abort_flag};
 
   if (tid == 0) {
@@ -81,17 +85,68 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     abort_flag = 0;
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 512);
-
+  const uint32_t sbase = smem_u32(sm);
   const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
-  load_tile<64, 128, 256>(sm + TailSmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-  load_tile<64, 128, 256>(sm + TailSmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-  fence_async_smem();
+
+  // a pair is live when it exists and its chunk is not a pad chunk of a device-built table (pads come last)
+  auto pair_live = [&](int p) { return p < num_pairs && chunk_len[p / num_qk_heads] > 0; };
+  // ---- asynchronous loads of one work item (pair p, group index gi) ------------------------------------------------
+  auto load_qk = [&](int p, int buf) {
+    const int c = p / num_qk_heads, hq = p % num_qk_heads;
+    const int start = chunk_start[c], len = chunk_len[c];
+    const uint32_t base = sbase + TailSmem::kQK + buf * TailSmem::kQKStride;
+    prefetch_tile<64, 128, 256>(base, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+    prefetch_tile<64, 128, 256>(base + 16384, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+  };
+  struct Item {
+    int c, hv, start, len;
+    int64_t tile;
+  };
+  auto item_of = [&](int p, int gi) {
+    Item it;
+    it.c = p / num_qk_heads;
+    it.hv = (p % num_qk_heads) * group + gi;
+    it.start = chunk_start[it.c];
+    it.len = chunk_len[it.c];
+    it.tile = int64_t(it.c) * num_v_heads + it.hv;
+    return it;
+  };
+  auto load_scalars_aqk = [&](const Item& it, int buf) {
+    if (tid < 64) {
+      const int64_t at = int64_t(it.start + (tid < it.len ? tid : it.len - 1)) * num_v_heads + it.hv;
+      cp_async4(smem_u32(s_beta + buf * 64 + tid), beta + at);
+      cp_async4(smem_u32(s_g2 + buf * 64 + tid), g_cs + at);
+    }
+    prefetch_tile<64, 64, 256>(sbase + TailSmem::kAqk, 8192, aqk_in + it.tile * 4096, 64, 64, tid);
+  };
+  auto load_rows = [&](uint32_t where, const __nv_bfloat16* base, const Item& it) {
+    prefetch_tile<64, 128, 256>(sbase + where, 8192, base + int64_t(it.start) * v_stride + it.hv * kDim, v_stride,
+                                it.len, tid);
+  };
+  auto load_states = [&](const Item& it) {
+    prefetch_tile<128, 128, 256>(sbase + TailSmem::kH, 16384, h_tape + it.tile * 16384, 128, 128, tid);
+    prefetch_tile<128, 128, 256>(sbase + TailSmem::kDH, 16384, dh_tape + it.tile * 16384, 128, 128, tid);
+  };
+  auto load_a = [&](const Item& it) {
+    prefetch_tile<64, 64, 256>(sbase + TailSmem::kA, 8192, a_in + it.tile * 4096, 64, 64, tid);
+  };
+
+  int pair = blockIdx.x;
+  if (pair_live(pair)) {  // prologue: everything of the first item
+    const Item it = item_of(pair, 0);
+    load_qk(pair, 0);
+    load_scalars_aqk(it, 0);
+    load_rows(TailSmem::kDO, d_o, it);
+    load_rows(TailSmem::kVN, v_new, it);
+    load_rows(TailSmem::kDVN, dv_new, it);
+    load_states(it);
+    load_a(it);
+    cp_async_commit();
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t sbase = smem_u32(sm);
-  const Operand op_q{sbase + TailSmem::kQ, 8192}, op_k{sbase + TailSmem::kK, 8192};
   const Operand op_h{sbase + TailSmem::kH, 16384}, op_dh{sbase + TailSmem::kDH, 16384};
   const Operand op_dw{sbase + TailSmem::kH, 8192}, op_kb{sbase + TailSmem::kH + 16384, 8192};
   const Operand op_vb{sbase + TailSmem::kDH, 8192};
@@ -112,392 +167,409 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     __syncthreads();
     tc_fence_after();
   };
-
-  // KK = k k^T, kept in shared memory (fp32, transposed) for the whole group
-  if (tid == 0) {
-    umma_gemm<64, 64>(tmem + kColT0, op_k, false, op_k, false, 128, false);
-    umma_commit(&bar);
-  }
-  mma_wait();
-  {
-    float s[32];
-    tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), s);
-    tmem_ld_wait();
-    if (owner) {
+  // column sums of a [64 x 64] matrix held one 32-column row piece per owner thread: reduce over the 16 rows of the
+  // warp by shuffles, then publish one partial per quadrant (summed after the next block barrier)
+  auto publish_column_sums = [&](float* piece, float* where) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) s_kkt[(ch * 32 + j) * 65 + row] = s[j];
+    for (int j = 0; j < 32; ++j) {
+      float x = owner ? piece[j] : 0.f;
+#pragma unroll
+      for (int m = 8; m >= 1; m >>= 1) x += __shfl_xor_sync(0xffffffffu, x, m);
+      if (lane == 0) where[quad * 64 + ch * 32 + j] = x;
     }
-  }
+  };
 
   float dk_reg[64];  // scaled dk terms of this thread's (row, column half), summed over the group
+  int item_parity = 0, qk_buf = 0;
+  bool aborted = false;
+  for (; pair_live(pair) && !aborted; pair += gridDim.x, qk_buf ^= 1) {
+    const int hq = pair % num_qk_heads;
+    const uint32_t qk_base = sbase + TailSmem::kQK + qk_buf * TailSmem::kQKStride;
+    uint8_t* k_tile = sm + TailSmem::kQK + qk_buf * TailSmem::kQKStride + 16384;
+    const Operand op_q{qk_base, 8192}, op_k{qk_base + 16384, 8192};
+    const int next_pair = pair + gridDim.x;
+    const bool has_next_pair = pair_live(next_pair);
 #pragma unroll
-  for (int j = 0; j < 64; ++j) dk_reg[j] = 0.f;
+    for (int j = 0; j < 64; ++j) dk_reg[j] = 0.f;
 
-  for (int gi = 0; gi < group; ++gi) {
-    const int hv = hq * group + gi;
-    const int64_t tile = int64_t(c) * num_v_heads + hv;
-    tc_fence_before();
-    __syncthreads();  // the previous value head's tiles and tensor-memory temporaries are free
-    tc_fence_after();
-    if (abort.raised()) break;
+    for (int gi = 0; gi < group; ++gi, item_parity ^= 1) {
+      const Item it = item_of(pair, gi);
+      const int start = it.start, len = it.len, hv = it.hv;
+      const bool live = owner && row < len;
+      const bool last_of_pair = gi + 1 == group;
+      const bool has_next = !last_of_pair || has_next_pair;
+      const Item nx = has_next ? (last_of_pair ? item_of(next_pair, 0) : item_of(pair, gi + 1)) : it;
+      const float* beta_s = s_beta + item_parity * 64;
+      const float* g2 = s_g2 + item_parity * 64;
 
-    load_tile<128, 128, 256>(sm + TailSmem::kH, 16384, h_tape + tile * 16384, 128, 128, tid);
-    load_tile<128, 128, 256>(sm + TailSmem::kDH, 16384, dh_tape + tile * 16384, 128, 128, tid);
-    load_tile<64, 128, 256>(sm + TailSmem::kDO, 8192, d_o + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-    load_tile<64, 128, 256>(sm + TailSmem::kVN, 8192, v_new + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-    load_tile<64, 128, 256>(sm + TailSmem::kDVN, 8192, dv_new + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-    load_tile<64, 64, 256>(sm + TailSmem::kA, 8192, a_in + tile * 4096, 64, 64, tid);
-    load_tile<64, 64, 256>(sm + TailSmem::kAqk, 8192, aqk_in + tile * 4096, 64, 64, tid);
-    if (tid < 64) {
-      const int i = tid < len ? tid : len - 1;
-      s_beta[tid] = tid < len ? beta[int64_t(start + i) * num_v_heads + hv] : 0.f;
-      s_g2[tid] = g_cs[int64_t(start + i) * num_v_heads + hv];
-    }
-    stage_sync();
-
-    // ---- phase 1: dAqk = do v_new^T ; dkh = v_new dh^T ----------------------------------------------------------
-    if (tid == 0) {
-      umma_gemm<64, 64>(tmem + kColT0, op_do, false, op_vn, false, 128, false);
-      umma_gemm<64, 128>(tmem + kColT2, op_vn, false, op_dh, false, 128, false);
-      umma_commit(&bar);
-    }
-    // meanwhile: sum(dh . h) over the whole state tile
-    float hdh = 0.f;
-    for (int i = tid; i < 128 * 16; i += 256) {
-      float a[8], b[8];
-      unpack8(tile_chunk(sm + TailSmem::kH, 16384, i >> 4, i & 15), a);
-      unpack8(tile_chunk(sm + TailSmem::kDH, 16384, i >> 4, i & 15), b);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) hdh = fmaf(a[j], b[j], hdh);
-    }
-    const float gi_row = s_g2[row], beta_row = s_beta[row];
-    const float g_last = s_g2[len - 1];
-    const float rs_row = fast_exp2(g_last - gi_row);
-    float dG = 0.f, dB = 0.f, gdot = 0.f;
-    mma_wait();
-    {
-      // dAqk piece: 32 columns
-      float s[32];
-      tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), s);
-      tmem_ld_wait();
-      float rowsum = 0.f;
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        float aq[8], ds[8];
-        unpack8(tile_chunk(sm + TailSmem::kAqk, 8192, row, ch * 4 + jj), aq);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int col = ch * 32 + jj * 8 + e;
-          const float d = col <= row ? s[jj * 8 + e] : 0.f;
-          const float p = d * aq[e];
-          rowsum += p;
-          if (owner) s_p[col * 65 + row] = p;
-          ds[e] = col <= row ? scale * d * fast_exp2(gi_row - s_g2[col]) : 0.f;
-        }
-        if (owner) set_tile_chunk(sm + TailSmem::kB8a, 8192, row, ch * 4 + jj, pack8(ds));
+      cp_async_wait_pending<0>();  // this item's tiles (issued while the previous item computed) have landed
+      stage_sync();
+      if (abort.raised()) {
+        aborted = true;
+        break;
       }
-      dG += rowsum;
-      // dkh piece: 64 columns
-      float dot = 0.f;
+      if (last_of_pair && has_next_pair) {  // the other q / k buffer is free: the previous pair is done
+        load_qk(next_pair, qk_buf ^ 1);
+        cp_async_commit();
+      }
+
+      // ---- phase 1: dAqk = do v_new^T ; dkh = v_new dh^T --------------------------------------------------------
+      if (tid == 0) {
+        umma_gemm<64, 64>(tmem + kColTa, op_do, false, op_vn, false, 128, false);
+        umma_gemm<64, 128>(tmem + kColT0, op_vn, false, op_dh, false, 128, false);
+        umma_commit(&bar);
+      }
+      // meanwhile: sum(dh . h) over the whole state tile
+      float hdh = 0.f;
+      for (int i = tid; i < 128 * 16; i += 256) {
+        float a[8], b[8];
+        unpack8(tile_chunk(sm + TailSmem::kH, 16384, i >> 4, i & 15), a);
+        unpack8(tile_chunk(sm + TailSmem::kDH, 16384, i >> 4, i & 15), b);
 #pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        float d[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColT2 + ch * 64 + p * 32), d);
+        for (int j = 0; j < 8; ++j) hdh = fmaf(a[j], b[j], hdh);
+      }
+      const float gi_row = g2[row], beta_row = beta_s[row];
+      const float g_last = g2[len - 1];
+      const float rs_row = fast_exp2(g_last - gi_row);
+      float dG = 0.f, dB = 0.f, gdot = 0.f;
+      mma_wait();
+      {
+        // dAqk piece: 32 columns
+        float s[32];
+        tmem_ld32(tmem_addr(tmem, warp, kColTa + ch * 32), s);
         tmem_ld_wait();
+        float rowsum = 0.f;
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
-          float kk[8];
-          unpack8(tile_chunk(sm + TailSmem::kK, 8192, row, ch * 8 + p * 4 + jj), kk);
+          float aq[8], ds[8];
+          unpack8(tile_chunk(sm + TailSmem::kAqk, 8192, row, ch * 4 + jj), aq);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const float x = rs_row * d[jj * 8 + e];
-            dot = fmaf(x, kk[e], dot);
-            dk_reg[p * 32 + jj * 8 + e] += x;
+            const int col = ch * 32 + jj * 8 + e;
+            const float d = col <= row ? s[jj * 8 + e] : 0.f;
+            ds[e] = col <= row ? scale * d * fast_exp2(gi_row - g2[col]) : 0.f;
+            s[jj * 8 + e] = d * aq[e];  // P = dAqk . Aqk
+            rowsum += s[jj * 8 + e];
+          }
+          if (owner) set_tile_chunk(sm + TailSmem::kB8a, 8192, row, ch * 4 + jj, pack8(ds));
+        }
+        dG += rowsum;
+        publish_column_sums(s, s_cs);
+        // dkh piece: 64 columns
+        float dot = 0.f;
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          float d[32];
+          tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 64 + p * 32), d);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            float kk[8];
+            unpack8(tile_chunk(k_tile, 8192, row, ch * 8 + p * 4 + jj), kk);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float x = rs_row * d[jj * 8 + e];
+              dot = fmaf(x, kk[e], dot);
+              dk_reg[p * 32 + jj * 8 + e] += x;
+            }
           }
         }
-      }
-      if (owner) {
         dG -= dot;
         gdot += dot;
       }
-    }
-    // do -> do_g = bf16(qscale do), in place (phase 1 has read do)
-    for (int i = tid; i < 64 * 16; i += 256) {
-      const int r = i >> 4, cc = i & 15;
-      const float qs = scale * fast_exp2(s_g2[r]);
-      float x[8];
-      unpack8(tile_chunk(sm + TailSmem::kDO, 8192, r, cc), x);
+      // do -> do_g = bf16(qscale do), in place (phase 1 has read do)
+      for (int i = tid; i < 64 * 16; i += 256) {
+        const int r = i >> 4, cc = i & 15;
+        const float qs = scale * fast_exp2(g2[r]);
+        float x[8];
+        unpack8(tile_chunk(sm + TailSmem::kDO, 8192, r, cc), x);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] *= qs;
-      set_tile_chunk(sm + TailSmem::kDO, 8192, r, cc, pack8(x));
-    }
-    stage_sync();
+        for (int j = 0; j < 8; ++j) x[j] *= qs;
+        set_tile_chunk(sm + TailSmem::kDO, 8192, r, cc, pack8(x));
+      }
+      stage_sync();
+      // v_new and Aqk are done with: this value head's raw v comes into the v_new buffer, the next item's Aqk and
+      // scalars into theirs
+      {
+        Item cur = it;
+        load_rows(TailSmem::kVN, v, cur);
+        cp_async_commit();
+        if (has_next) load_scalars_aqk(nx, item_parity ^ 1);
+        cp_async_commit();
+      }
 
-    // ---- phase 2: dq += dS k + do_g h^T ; dk += dS^T q ; qh = q h ; dw = -dv_new h^T ----------------------------
-    if (tid == 0) {
-      umma_gemm<64, 128>(tmem + kColDQ, op_b8a, false, op_k, true, 64, gi > 0);
-      umma_gemm<64, 128>(tmem + kColDQ, op_do, false, op_h, false, 128, true);
-      umma_gemm<64, 128>(tmem + kColDK, op_b8a, true, op_q, true, 64, gi > 0);
-      umma_gemm<64, 128>(tmem + kColT2, op_q, false, op_h, true, 128, false);
-      umma_gemm<64, 128>(tmem + kColT0, op_dvn, false, op_h, false, 128, false, /*neg_a=*/true);
-      umma_commit(&bar);
-    }
-    if (owner) {  // column sums of P = dAqk . Aqk
-      float cs = 0.f;
-#pragma unroll 8
-      for (int i = 0; i < 32; ++i) cs += s_p[row * 65 + ch * 32 + i];
-      dG -= cs;
-    }
-    mma_wait();
-    {
-      float dot = 0.f;
-#pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        float qh[32], dw[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColT2 + ch * 64 + p * 32), qh);
-        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 64 + p * 32), dw);
-        tmem_ld_wait();
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          float dog[8];
-          unpack8(tile_chunk(sm + TailSmem::kDO, 8192, row, ch * 8 + p * 4 + jj), dog);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(dog[e], qh[jj * 8 + e], dot);
-          // h has been read by phase 2: its first half becomes the dw tile
-          if (owner) set_tile_chunk(sm + TailSmem::kH, 8192, row, ch * 8 + p * 4 + jj, pack8(dw + jj * 8));
-        }
+      // ---- phase 2: dq += dS k + do_g h^T ; dk += dS^T q ; qh = q h ; dw = -dv_new h^T --------------------------
+      if (tid == 0) {
+        umma_gemm<64, 128>(tmem + kColDQ, op_b8a, false, op_k, true, 64, gi > 0);
+        umma_gemm<64, 128>(tmem + kColDQ, op_do, false, op_h, false, 128, true);
+        umma_gemm<64, 128>(tmem + kColDK, op_b8a, true, op_q, true, 64, gi > 0);
+        umma_gemm<64, 128>(tmem + kColT0, op_q, false, op_h, true, 128, false);
+        umma_gemm<64, 128>(tmem + kColTa, op_dvn, false, op_h, false, 128, false, /*neg_a=*/true);
+        umma_commit(&bar);
       }
-      if (owner) dG += dot;
-    }
-    // kb = bf16(beta 2^G k) -> second half of the h region; vb = bf16(beta v) -> the dh region
-    for (int i = tid; i < 64 * 16; i += 256) {
-      const int r = i >> 4, cc = i & 15;
-      const float b = s_beta[r], s = b * fast_exp2(s_g2[r]);
-      float x[8];
-      unpack8(tile_chunk(sm + TailSmem::kK, 8192, r, cc), x);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] *= s;
-      set_tile_chunk(sm + TailSmem::kH + 16384, 8192, r, cc, pack8(x));
-      uint4 rawv = make_uint4(0u, 0u, 0u, 0u);
-      if (r < len) rawv = ldg16(v + int64_t(start + r) * v_stride + hv * kDim + cc * 8);
-      unpack8(rawv, x);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] *= b;
-      set_tile_chunk(sm + TailSmem::kDH, 8192, r, cc, pack8(x));
-    }
-    stage_sync();
-
-    // ---- phase 3a: dkb = A^T dw ; dvb = A^T dv_new --------------------------------------------------------------
-    if (tid == 0) {
-      umma_gemm<64, 128>(tmem + kColT0, op_a, true, op_dw, true, 64, false);
-      umma_gemm<64, 128>(tmem + kColT2, op_a, true, op_dvn, true, 64, false);
-      umma_commit(&bar);
-    }
-    mma_wait();
-    {
-      const float eg = fast_exp2(gi_row), sk = beta_row * eg;
-      float dot_k = 0.f, dot_kb = 0.f, dot_v = 0.f;
-      __nv_bfloat16* dv_row = dv + int64_t(start + row) * v_stride + hv * kDim + ch * 64;
-      const __nv_bfloat16* v_row = v + int64_t(start + row) * v_stride + hv * kDim + ch * 64;
-#pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        float dkb[32], dvb[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 64 + p * 32), dkb);
-        tmem_ld32(tmem_addr(tmem, warp, kColT2 + ch * 64 + p * 32), dvb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          float kk[8], kb[8], vv[8], out[8];
-          unpack8(tile_chunk(sm + TailSmem::kK, 8192, row, ch * 8 + p * 4 + jj), kk);
-          unpack8(tile_chunk(sm + TailSmem::kH + 16384, 8192, row, ch * 8 + p * 4 + jj), kb);
-          uint4 rawv = make_uint4(0u, 0u, 0u, 0u);
-          if (live) rawv = ldg16(v_row + p * 32 + jj * 8);
-          unpack8(rawv, vv);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float x = dkb[jj * 8 + e], y = dvb[jj * 8 + e];
-            dot_k = fmaf(x, kk[e], dot_k);
-            dot_kb = fmaf(x, kb[e], dot_kb);
-            dot_v = fmaf(y, vv[e], dot_v);
-            dk_reg[p * 32 + jj * 8 + e] = fmaf(sk, x, dk_reg[p * 32 + jj * 8 + e]);
-            out[e] = y * beta_row;
-          }
-          if (live) reinterpret_cast<uint4*>(dv_row + p * 32)[jj] = pack8(out);
-        }
-      }
-      if (owner) {
-        dB += eg * dot_k + dot_v;
-        dG += dot_kb;
-      }
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    // ---- phase 3b: dA = dw kb^T + dv_new vb^T -------------------------------------------------------------------
-    if (tid == 0) {
-      umma_gemm<64, 64>(tmem + kColT0, op_dw, false, op_kb, false, 128, false);
-      umma_gemm<64, 64>(tmem + kColT0, op_dvn, false, op_vb, false, 128, true);
-      umma_commit(&bar);
-    }
-    mma_wait();
-    {
-      float s[32];
-      tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), s);
-      tmem_ld_wait();
-      if (owner) {
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) set_tile_chunk(sm + TailSmem::kB8a, 8192, row, ch * 4 + jj, pack8(s + jj * 8));
-      }
-    }
-    stage_sync();
-
-    // ---- phase 4: X = A^T dA ------------------------------------------------------------------------------------
-    if (tid == 0) {
-      umma_gemm<64, 64>(tmem + kColT1, op_a, true, op_b8a, true, 64, false);
-      umma_commit(&bar);
-    }
-    mma_wait();
-    {
-      float s[32];
-      tmem_ld32(tmem_addr(tmem, warp, kColT1 + ch * 32), s);
-      tmem_ld_wait();
-      if (owner) {
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) set_tile_chunk(sm + TailSmem::kB8b, 8192, row, ch * 4 + jj, pack8(s + jj * 8));
-      }
-    }
-    stage_sync();
-
-    // ---- phase 5: Y = X A^T ; dL = bf16(-tril(Y, -1)) -----------------------------------------------------------
-    if (tid == 0) {
-      umma_gemm<64, 64>(tmem + kColT0, op_b8b, false, op_a, false, 64, false);
-      umma_commit(&bar);
-    }
-    mma_wait();
-    {
-      float s[32];
-      tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), s);
-      tmem_ld_wait();
-      float rowsum = 0.f, dot = 0.f;
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        float out[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int col = ch * 32 + jj * 8 + e;
-          const float dl = col < row ? round_bf16(-s[jj * 8 + e]) : 0.f;
-          const float dld = col < row ? dl * fast_exp2(gi_row - s_g2[col]) : 0.f;
-          const float kk = owner ? s_kkt[col * 65 + row] : 0.f;
-          dot = fmaf(dld, kk, dot);
-          const float pl = beta_row * dld * kk;
-          rowsum += pl;
-          if (owner) s_p[col * 65 + row] = pl;
-          out[e] = beta_row * dld;
-        }
-        if (owner) set_tile_chunk(sm + TailSmem::kB8a, 8192, row, ch * 4 + jj, pack8(out));
-      }
-      if (owner) {
-        dB += dot;
-        dG += rowsum;
-      }
-    }
-    stage_sync();
-
-    // ---- phase 6: dk += bf16(beta dL D) k + bf16(beta dL D)^T k -------------------------------------------------
-    if (tid == 0) {
-      umma_gemm<64, 128>(tmem + kColDK, op_b8a, false, op_k, true, 64, true);
-      umma_gemm<64, 128>(tmem + kColDK, op_b8a, true, op_k, true, 64, true);
-      umma_commit(&bar);
-    }
-    if (owner) {  // column sums of dL . L
-      float cs = 0.f;
-#pragma unroll 8
-      for (int i = 0; i < 32; ++i) cs += s_p[row * 65 + ch * 32 + i];
-      dG -= cs;
-    }
-    // gate and beta gradients of this value head: combine the column halves, add the chunk-end term, suffix sum
-    float part = fmaf(fast_exp2(g_last), hdh, gdot);
-#pragma unroll
-    for (int m = 16; m >= 1; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
-    if (lane == 0) s_warp[warp] = part;
-    if (owner) {
-      s_red[ch * 64 + row] = dG;
-      s_red2[ch * 64 + row] = dB;
-    }
-    __syncthreads();
-    if (tid < 64) {
-      float gamma_dot = 0.f;
-#pragma unroll
-      for (int wv = 0; wv < 8; ++wv) gamma_dot += s_warp[wv];
-      float acc = 0.f;
-      for (int j = len - 1; j >= tid; --j) {
-        acc += s_red[j] + s_red[64 + j];
-        if (j == len - 1) acc += gamma_dot;
-      }
-      if (tid < len) {
-        dg[int64_t(start + tid) * num_v_heads + hv] = acc;
-        dbeta[int64_t(start + tid) * num_v_heads + hv] = s_red2[tid] + s_red2[64 + tid];
-      }
-    }
-    mma_wait();
-  }
-
-  // ---- the group's dq, dk: fp32 sums, the norm's pull-back, one rounding ----------------------------------------
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  if (!abort.raised()) {
-    const int64_t tok = int64_t(start + row) * qk_stride + hq * kDim + ch * 64;
-    // acc: this thread's 64 columns of the fp32 group sum.  With the op's L2 norm: dx = r (D - y (D . y)), y = x r
-    // from the raw row and the saved r; the dot product spans both column halves (exchanged through shared memory).
-    auto finish = [&](float* acc, const __nv_bfloat16* raw_rows, const float* rstd, __nv_bfloat16* out) {
-      if (rstd != nullptr) {
-        const float r = live ? rstd[int64_t(start + row) * num_qk_heads + hq] : 0.f;
-        float y[64];
+      if (owner && ch == 0) dG -= s_cs[row] + s_cs[64 + row] + s_cs[128 + row] + s_cs[192 + row];
+      mma_wait();
+      {
         float dot = 0.f;
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          uint4 x = make_uint4(0u, 0u, 0u, 0u);
-          if (live) x = ldg16(raw_rows + tok + jj * 8);
-          unpack8(x, y + jj * 8);
+        for (int p = 0; p < 2; ++p) {
+          float qh[32], dw[32];
+          tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 64 + p * 32), qh);
+          tmem_ld32(tmem_addr(tmem, warp, kColTa + ch * 64 + p * 32), dw);
+          tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            y[jj * 8 + e] *= r;
-            dot = fmaf(acc[jj * 8 + e], y[jj * 8 + e], dot);
+          for (int jj = 0; jj < 4; ++jj) {
+            float dog[8];
+            unpack8(tile_chunk(sm + TailSmem::kDO, 8192, row, ch * 8 + p * 4 + jj), dog);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dot = fmaf(dog[e], qh[jj * 8 + e], dot);
+            // h has been read by phase 2: its first half becomes the dw tile
+            if (owner) set_tile_chunk(sm + TailSmem::kH, 8192, row, ch * 8 + p * 4 + jj, pack8(dw + jj * 8));
           }
         }
-        if (owner) s_red[ch * 64 + row] = dot;
-        __syncthreads();
-        dot = s_red[row] + s_red[64 + row];
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < 64; ++j) acc[j] = r * (acc[j] - y[j] * dot);
+        dG += dot;
       }
-      if (live) {
+      cp_async_wait_pending<1>();  // this value head's raw v has landed (the next item's Aqk group may be in flight)
+      __syncthreads();
+      // kb = bf16(beta 2^G k) -> second half of the h region; vb = bf16(beta v) -> the dh region
+      for (int i = tid; i < 64 * 16; i += 256) {
+        const int r = i >> 4, cc = i & 15;
+        const float b = beta_s[r], sc = b * fast_exp2(g2[r]);
+        float x[8];
+        unpack8(tile_chunk(k_tile, 8192, r, cc), x);
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) reinterpret_cast<uint4*>(out + tok)[jj] = pack8(acc + jj * 8);
+        for (int j = 0; j < 8; ++j) x[j] *= sc;
+        set_tile_chunk(sm + TailSmem::kH + 16384, 8192, r, cc, pack8(x));
+        unpack8(tile_chunk(sm + TailSmem::kVN, 8192, r, cc), x);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] *= b;
+        set_tile_chunk(sm + TailSmem::kDH, 8192, r, cc, pack8(x));
       }
-    };
-    {
-      float dqv[64];
+      stage_sync();
+      if (has_next) {  // do_g is done with
+        load_rows(TailSmem::kDO, d_o, nx);
+        cp_async_commit();
+      }
+
+      // ---- phase 3: dkb = A^T dw ; dA = dw kb^T + dv_new vb^T ----------------------------------------------------
+      if (tid == 0) {
+        umma_gemm<64, 128>(tmem + kColT0, op_a, true, op_dw, true, 64, false);
+        umma_gemm<64, 64>(tmem + kColTa, op_dw, false, op_kb, false, 128, false);
+        umma_gemm<64, 64>(tmem + kColTa, op_dvn, false, op_vb, false, 128, true);
+        umma_commit(&bar);
+      }
+      mma_wait();
+      const float eg = fast_exp2(gi_row), sk = beta_row * eg;
+      {
+        float dot_k = 0.f, dot_kb = 0.f;
 #pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        tmem_ld32(tmem_addr(tmem, warp, kColDQ + ch * 64 + p * 32), dqv + p * 32);
+        for (int p = 0; p < 2; ++p) {
+          float dkb[32];
+          tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 64 + p * 32), dkb);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            float kk[8], kb[8];
+            unpack8(tile_chunk(k_tile, 8192, row, ch * 8 + p * 4 + jj), kk);
+            unpack8(tile_chunk(sm + TailSmem::kH + 16384, 8192, row, ch * 8 + p * 4 + jj), kb);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float x = dkb[jj * 8 + e];
+              dot_k = fmaf(x, kk[e], dot_k);
+              dot_kb = fmaf(x, kb[e], dot_kb);
+              dk_reg[p * 32 + jj * 8 + e] = fmaf(sk, x, dk_reg[p * 32 + jj * 8 + e]);
+            }
+          }
+        }
+        dB += eg * dot_k;
+        dG += dot_kb;
+        float s[32];
+        tmem_ld32(tmem_addr(tmem, warp, kColTa + ch * 32), s);
         tmem_ld_wait();
+        if (owner) {
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            set_tile_chunk(sm + TailSmem::kB8a, 8192, row, ch * 4 + jj, pack8(s + jj * 8));
+        }
       }
-      finish(dqv, q_raw, rstd_q, dq);
-    }
+      stage_sync();
+      if (has_next) {  // dw, kb (h region) and vb (dh region) are done with
+        load_states(nx);
+        cp_async_commit();
+      }
+
+      // ---- phase 4: X = A^T dA ; dvb = A^T dv_new ----------------------------------------------------------------
+      if (tid == 0) {
+        umma_gemm<64, 64>(tmem + kColTb, op_a, true, op_b8a, true, 64, false);
+        umma_gemm<64, 128>(tmem + kColT0, op_a, true, op_dvn, true, 64, false);
+        umma_commit(&bar);
+      }
+      mma_wait();
+      {
+        float s[32];
+        tmem_ld32(tmem_addr(tmem, warp, kColTb + ch * 32), s);
+        tmem_ld_wait();
+        if (owner) {
 #pragma unroll
-    for (int p = 0; p < 2; ++p) {
-      float b[32];
-      tmem_ld32(tmem_addr(tmem, warp, kColDK + ch * 64 + p * 32), b);
-      tmem_ld_wait();
+          for (int jj = 0; jj < 4; ++jj)
+            set_tile_chunk(sm + TailSmem::kB8b, 8192, row, ch * 4 + jj, pack8(s + jj * 8));
+        }
+        float dot_v = 0.f;
+        __nv_bfloat16* dv_row = dv + int64_t(start + row) * v_stride + hv * kDim + ch * 64;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) dk_reg[p * 32 + j] += b[j];
+        for (int p = 0; p < 2; ++p) {
+          float dvb[32];
+          tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 64 + p * 32), dvb);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            float vv[8], out[8];
+            unpack8(tile_chunk(sm + TailSmem::kVN, 8192, row, ch * 8 + p * 4 + jj), vv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float y = dvb[jj * 8 + e];
+              dot_v = fmaf(y, vv[e], dot_v);
+              out[e] = y * beta_row;
+            }
+            if (live) reinterpret_cast<uint4*>(dv_row + p * 32)[jj] = pack8(out);
+          }
+        }
+        dB += dot_v;
+      }
+      stage_sync();
+      if (has_next) {  // raw v and dv_new are done with
+        load_rows(TailSmem::kVN, v_new, nx);
+        load_rows(TailSmem::kDVN, dv_new, nx);
+        cp_async_commit();
+      }
+
+      // ---- phase 5: Y = X A^T ; KK = k k^T ; dL = bf16(-tril(Y, -1)) ---------------------------------------------
+      if (tid == 0) {
+        umma_gemm<64, 64>(tmem + kColTa, op_b8b, false, op_a, false, 64, false);
+        umma_gemm<64, 64>(tmem + kColTb, op_k, false, op_k, false, 128, false);
+        umma_commit(&bar);
+      }
+      mma_wait();
+      {
+        float s[32], kk[32];
+        tmem_ld32(tmem_addr(tmem, warp, kColTa + ch * 32), s);
+        tmem_ld32(tmem_addr(tmem, warp, kColTb + ch * 32), kk);
+        tmem_ld_wait();
+        float rowsum = 0.f, dot = 0.f;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          float out[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int col = ch * 32 + jj * 8 + e;
+            const float dl = col < row ? round_bf16(-s[jj * 8 + e]) : 0.f;
+            const float dld = col < row ? dl * fast_exp2(gi_row - g2[col]) : 0.f;
+            const float kij = col < row ? kk[jj * 8 + e] : 0.f;
+            dot = fmaf(dld, kij, dot);
+            out[e] = beta_row * dld;
+            s[jj * 8 + e] = out[e] * kij;  // dL . L
+            rowsum += s[jj * 8 + e];
+          }
+          if (owner) set_tile_chunk(sm + TailSmem::kB8a, 8192, row, ch * 4 + jj, pack8(out));
+        }
+        dB += dot;
+        dG += rowsum;
+        publish_column_sums(s, s_cs + 256);
+      }
+      stage_sync();
+      if (has_next) {  // A is done with
+        load_a(nx);
+        cp_async_commit();
+      }
+
+      // ---- phase 6: dk += bf16(beta dL D) k + bf16(beta dL D)^T k ------------------------------------------------
+      if (tid == 0) {
+        umma_gemm<64, 128>(tmem + kColDK, op_b8a, false, op_k, true, 64, true);
+        umma_gemm<64, 128>(tmem + kColDK, op_b8a, true, op_k, true, 64, true);
+        if (last_of_pair) umma_commit(&bar);  // otherwise the next item's first commit covers these too
+      }
+      if (owner && ch == 0) dG -= s_cs[256 + row] + s_cs[320 + row] + s_cs[384 + row] + s_cs[448 + row];
+      // gate and beta gradients of this value head: combine the column halves, add the chunk-end term, suffix sum
+      float part = fmaf(fast_exp2(g_last), hdh, owner ? gdot : 0.f);
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
+      if (lane == 0) s_warp[warp] = part;
+      if (owner) {
+        s_red[ch * 64 + row] = dG;
+        s_red2[ch * 64 + row] = dB;
+      }
+      __syncthreads();
+      if (tid < 64) {
+        float gamma_dot = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < 8; ++wv) gamma_dot += s_warp[wv];
+        float acc = 0.f;
+        for (int j = len - 1; j >= tid; --j) {
+          acc += s_red[j] + s_red[64 + j];
+          if (j == len - 1) acc += gamma_dot;
+        }
+        if (tid < len) {
+          dg[int64_t(start + tid) * num_v_heads + hv] = acc;
+          dbeta[int64_t(start + tid) * num_v_heads + hv] = s_red2[tid] + s_red2[64 + tid];
+        }
+      }
+
+      if (last_of_pair) {
+        // ---- the group's dq, dk: fp32 sums, the norm's pull-back, one rounding ----------------------------------
+        mma_wait();
+        const int64_t tok = int64_t(start + row) * qk_stride + hq * kDim + ch * 64;
+        // acc: this thread's 64 columns of the fp32 group sum.  With the op's L2 norm: dx = r (D - y (D . y)),
+        // y = x r from the raw row and the saved r; the dot product spans both column halves.
+        auto finish = [&](float* acc, const __nv_bfloat16* raw_rows, const float* rstd, __nv_bfloat16* out) {
+          if (rstd != nullptr) {
+            const float r = live ? rstd[int64_t(start + row) * num_qk_heads + hq] : 0.f;
+            float y[64];
+            float dot = 0.f;
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+              uint4 x = make_uint4(0u, 0u, 0u, 0u);
+              if (live) x = ldg16(raw_rows + tok + jj * 8);
+              unpack8(x, y + jj * 8);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                y[jj * 8 + e] *= r;
+                dot = fmaf(acc[jj * 8 + e], y[jj * 8 + e], dot);
+              }
+            }
+            __syncthreads();  // the gate reduction above has read s_red
+            if (owner) s_red[ch * 64 + row] = dot;
+            __syncthreads();
+            dot = s_red[row] + s_red[64 + row];
+#pragma unroll
+            for (int j = 0; j < 64; ++j) acc[j] = r * (acc[j] - y[j] * dot);
+          }
+          if (live) {
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) reinterpret_cast<uint4*>(out + tok)[jj] = pack8(acc + jj * 8);
+          }
+        };
+        {
+          float dqv[64];
+#pragma unroll
+          for (int p = 0; p < 2; ++p) {
+            tmem_ld32(tmem_addr(tmem, warp, kColDQ + ch * 64 + p * 32), dqv + p * 32);
+            tmem_ld_wait();
+          }
+          finish(dqv, q_raw, rstd_q, dq);
+        }
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          float b[32];
+          tmem_ld32(tmem_addr(tmem, warp, kColDK + ch * 64 + p * 32), b);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) dk_reg[p * 32 + j] += b[j];
+        }
+        finish(dk_reg, k_raw, rstd_k, dk);
+      }
     }
-    finish(dk_reg, k_raw, rstd_k, dk);
   }
+  cp_async_wait_pending<0>();
   if (abort.raised() && tid == 0) atomicExch(status, kDevWaitTimeout | (5 << 8));
   tc_fence_before();
   __syncthreads();
@@ -522,9 +594,16 @@ extern "C" int mek_gdn_bwd_tail(const MekGdnDims* d, const void* q, const void* 
   typedef __nv_bfloat16* Out;
   const size_t smem = TailSmem::kBytes + 1024;
   if (int rc = want_smem(gdn_bwd_tail_kernel, smem, "bwd_tail")) return rc;
-  gdn_bwd_tail_kernel<<<dim3(d->num_chunks, d->num_qk_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
+    cudaGetLastError();
+    return fail(MEK_ERR_CUDA, "bwd_tail: cannot query the SM count");
+  }
+  const int pairs = d->num_chunks * d->num_qk_heads;
+  gdn_bwd_tail_kernel<<<pairs < sms ? pairs : sms, 256, smem, static_cast<cudaStream_t>(stream)>>>(
       In(q), In(k), In(v), beta, g_cs, In(a), In(aqk), In(h_tape), In(dh_tape), In(v_new), In(dv_new), In(d_o),
       In(q_raw), In(k_raw), rstd_q, rstd_k, Out(dq), Out(dk), Out(dv), dbeta, dg, d->chunk_start, d->chunk_len,
-      d->num_qk_heads, d->num_v_heads, d->scale, status);
+      d->num_chunks, d->num_qk_heads, d->num_v_heads, d->scale, status);
   return launched("bwd_tail");
 }
