@@ -49,12 +49,14 @@ int mek_check_device(int device);
  *   a_desc/b_desc descriptor templates with a zero start address; a_off/b_off [nk] (device int32) byte offsets added
  *                 to the buffer's start per instruction
  *   idesc         instruction descriptor
+ *   d_lane        first tensor-memory lane of the accumulator: 0, or 16 (an M = 64 accumulator may sit in the upper
+ *                 half of each 32-lane quadrant, sharing its columns with another M = 64 accumulator)
  *   out           device float [128 * ncols], row = tensor-memory lane
  *   status        device int32, 0 = fine
  * No counterpart in the reference (its kernels are generated and tested end to end). */
 int mek_selftest_umma(const void* a_img, int a_bytes, const void* b_img, int b_bytes, uint64_t a_desc, uint64_t b_desc,
-                      const int32_t* a_off, const int32_t* b_off, int nk, uint32_t idesc, int ncols, float* out,
-                      int32_t* status, void* stream);
+                      const int32_t* a_off, const int32_t* b_off, int nk, uint32_t idesc, int ncols, int d_lane,
+                      float* out, int32_t* status, void* stream);
 
 /* Extents and chunk tables of one call.  Tokens are packed: [total_tokens, heads, 128]; a batch of B equal-length
  * sequences is B sequences of one packed row.  Chunks hold at most 64 tokens and never straddle a sequence.

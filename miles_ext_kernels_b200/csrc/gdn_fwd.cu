@@ -65,8 +65,9 @@ struct WySmem {
   static constexpr uint32_t kV = 32768;            // [64][128] v -> beta v, 2 blocks of 8 KiB
   static constexpr uint32_t kKB = kV + 16384;      // [64][128] beta 2^G k
   static constexpr uint32_t kA = kKB + 16384;      // [64][64] A (bf16)
-  static constexpr uint32_t kL = kA + 8192;        // fp32 [64 cols j][64 rows i]: L transposed
-  static constexpr uint32_t kScal = kL + 16384;    // beta[64], g2[64]
+  static constexpr uint32_t kL = kA + 8192;        // fp32 L[64 rows i][68]: rows padded to spread the banks
+  static constexpr uint32_t kLStride = 68;
+  static constexpr uint32_t kScal = kL + 64 * 68 * 4;  // beta[64], g2[64]
   static constexpr uint32_t kBytes = kScal + 512;
 };
 
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
         for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst + p * 32)[j] = pack8(s + 8 * j);
       }
     } else {
-      // L row i -> shared, transposed ([j][i]) so that the store is conflict-free and the solve reads broadcasts
+      // L row i -> shared (row-major, padded rows): the solve reads it as float4 broadcasts
 #pragma unroll
       for (int p = 0; p < 2; ++p) {
         float s[32];
@@ -165,7 +166,7 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int col = p * 32 + j;
-          s_lt[col * 64 + i] = col < i ? bi * s[j] * fast_exp2(gi - s_g2[col]) : 0.f;
+          s_lt[i * WySmem::kLStride + col] = col < i ? bi * s[j] * fast_exp2(gi - s_g2[col]) : 0.f;
         }
       }
     }
@@ -175,13 +176,21 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
 
   // A = (I + L)^-1 : thread c solves (I + L) x = e_c by forward substitution (columns are independent)
   if (tid < 64) {
+    // x_i = delta_ic - sum_{j < i} L_ij x_j; four partial sums per row shorten the dependent FMA chain, and the
+    // row of L comes in 16-byte broadcasts (entries at and above the diagonal are zero)
     float x[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) {
-      float acc = (i == tid) ? 1.f : 0.f;
+      float acc0 = (i == tid) ? 1.f : 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
-      for (int j = 0; j < i; ++j) acc = fmaf(-s_lt[j * 64 + i], x[j], acc);
-      x[i] = acc;
+      for (int j = 0; j < i; j += 4) {
+        const float4 l = *reinterpret_cast<const float4*>(s_lt + i * WySmem::kLStride + j);
+        acc0 = fmaf(-l.x, x[j], acc0);
+        if (j + 1 < i) acc1 = fmaf(-l.y, x[j + 1], acc1);
+        if (j + 2 < i) acc2 = fmaf(-l.z, x[j + 2], acc2);
+        if (j + 3 < i) acc3 = fmaf(-l.w, x[j + 3], acc3);
+      }
+      x[i] = (acc0 + acc1) + (acc2 + acc3);
     }
     uint8_t* at = sm + WySmem::kA;
 #pragma unroll

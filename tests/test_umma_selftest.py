@@ -34,7 +34,7 @@ CASES = {
 }
 
 
-def run_case(lib, m, n, k, a_mn, b_mn, neg_a, seed=0):
+def run_case(lib, m, n, k, a_mn, b_mn, neg_a, seed=0, d_lane=0):
     rng = np.random.default_rng(seed)
     a = bf16_round(rng.standard_normal((m, k)).astype(np.float32))
     b = bf16_round(rng.standard_normal((n, k)).astype(np.float32))
@@ -54,14 +54,14 @@ def run_case(lib, m, n, k, a_mn, b_mn, neg_a, seed=0):
     p = lambda x: ctypes.c_void_p(x.data_ptr())  # noqa: E731
     rc = lib.mek_selftest_umma(
         p(a_d), a_img.size, p(b_d), b_img.size, ctypes.c_uint64(a_desc), ctypes.c_uint64(b_desc), p(ao), p(bo),
-        len(a_off), ctypes.c_uint32(idesc(m, n, a_mn, b_mn, neg_a)), n, p(out), p(status),
+        len(a_off), ctypes.c_uint32(idesc(m, n, a_mn, b_mn, neg_a)), n, d_lane, p(out), p(status),
         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
     )
     lib.check(rc)
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "the MMA wait ran out"
     want = (a.astype(np.float64) @ b.astype(np.float64).T) * (-1.0 if neg_a else 1.0)
-    lanes = [lane_of_row(m, r) for r in range(m)]
+    lanes = [lane_of_row(m, r) + d_lane for r in range(m)]
     got = out.cpu().numpy()[lanes]
     return got, want
 
@@ -73,5 +73,17 @@ def test_umma_operand_layouts(name):
 
     lib = loader.load_library()
     got, want = run_case(lib, *CASES[name])
+    err = np.abs(got - want).max()
+    assert err <= 1e-3 * max(1.0, np.abs(want).max()), f"{name}: max error {err}"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["k_k_m64_n64_k128", "k_mn_m64_n128_k64", "mn_k_m64_n128_k64"])
+def test_m64_accumulator_in_the_upper_half_lanes(name):
+    """An M = 64 accumulator placed at lane 16 of each quadrant: rows 16 q + r land in lanes 32 q + 16 + r."""
+    from miles_ext_kernels_b200.cake._runtime import loader
+
+    lib = loader.load_library()
+    got, want = run_case(lib, *CASES[name], d_lane=16)
     err = np.abs(got - want).max()
     assert err <= 1e-3 * max(1.0, np.abs(want).max()), f"{name}: max error {err}"
