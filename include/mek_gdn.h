@@ -132,6 +132,40 @@ int mek_gdn_forward_static(const MekGdnDims* dims, const void* q, const void* k,
                            const float* g, const float* h0, void* o, float* final_state, int32_t* status,
                            void* stream);
 
+/* ---- KDA: the per-key-channel-decay variant (packed documents, zero initial state, HV = H <= 64) -----------------
+ * Replaces the reference's KDA programs (reference: miles_ext_kernels/cake/_impl/kda/ops.py:142-234 entry points;
+ * the generated kernels of cake/_vendor/cake_kda_det_train are not used). */
+
+/* g2 fp32 [T, H, 128] = log2(e) * chunk-local cumulative gate; qg = bf16(q 2^g2), kg = bf16(k 2^g2),
+ * kr = bf16(k 2^{G_L - g2}) bf16 [T, H, 128]; gl2 fp32 [NC, H, 128] = g2 at each chunk's last token. */
+int mek_kda_prep(const MekGdnDims* dims, const void* q, const void* k, const float* g, float* g2, void* qg, void* kg,
+                 void* kr, float* gl2, void* stream);
+
+/* a_out, aqk_out bf16 [NC, H, 64, 64]; w_out, u_out bf16 [T, H, 128] (the WY transform with per-channel decays). */
+int mek_kda_intra(const MekGdnDims* dims, const void* q, const void* k, const void* v, const void* kg, const float* g2,
+                  const float* beta, void* a_out, void* aqk_out, void* w_out, void* u_out, int32_t* status,
+                  void* stream);
+
+/* The GDN scan / output / adjoint-scan kernels on the decayed operands (kr, qg) with a per-channel chunk decay. */
+int mek_kda_fwd_h(const MekGdnDims* dims, const void* kr, const void* w, const void* u, const float* gl2, void* h_tape,
+                  void* v_new, int32_t* status, void* stream);
+int mek_kda_fwd_o(const MekGdnDims* dims, const void* qg, const void* aqk, const void* v_new, const void* h_tape,
+                  void* o, int32_t* status, void* stream);
+int mek_kda_bwd_dh(const MekGdnDims* dims, const void* qg, const void* kr, const void* w, const void* d_o,
+                   const void* aqk, const float* gl2, void* dh_tape, void* dv_new, int32_t* status, void* stream);
+
+/* Gradient tail: dq32, dk32 fp32 [T, H, 128] (before the norm's pull-back and the rounding), dv bf16 [T, H, 128],
+ * dg fp32 [T, H, 128] (in-chunk suffix sum included), dbeta fp32 [T, H].  Scratch the caller provides: m1, m2 fp32
+ * [NC, H, 64, 64]; dqg, dkr, dkg fp32 [T, H, 128]; hdh fp32 [NC, H, 128]; dbeta_part fp32 [T, H]. */
+int mek_kda_bwd_tail(const MekGdnDims* dims, const void* q, const void* k, const void* v, const void* kg,
+                     const float* g2, const float* beta, const void* a, const void* h_tape, const void* dh_tape,
+                     const void* v_new, const void* dv_new, const void* d_o, float* m1, float* m2, float* dqg,
+                     float* dkr, float* dkg, float* hdh, float* dbeta_part, float* dq32, float* dk32, void* dv,
+                     float* dg, float* dbeta, int32_t* status, void* stream);
+
+/* out bf16 = x fp32 per row of 128, through the L2 norm's pull-back r (x - y (x . y)), y = raw r, when rstd is given. */
+int mek_qk_grad_finish(const float* x, const void* raw_rows, const float* rstd, void* out, int64_t rows, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

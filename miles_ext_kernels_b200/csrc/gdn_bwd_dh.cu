@@ -24,8 +24,8 @@ struct BwdDhSmem {
   static constexpr uint32_t kAqk = 4 * 16384;       // [64][64]
   static constexpr uint32_t kDV = 2 * kStage;       // [64][128] dv_new
   static constexpr uint32_t kDH = kDV + 16384;      // [128][128] bf16(dh), 2 blocks of 16 KiB (one per V half)
-  static constexpr uint32_t kG = kDH + 32768;       // g2[2][64]
-  static constexpr uint32_t kBytes = kG + 512;
+  static constexpr uint32_t kG = kDH + 32768;       // gates[2][128]
+  static constexpr uint32_t kBytes = kG + 1024;
 };
 
 __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
@@ -34,13 +34,16 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
     const float* __restrict__ dht, __nv_bfloat16* __restrict__ dh_tape, __nv_bfloat16* __restrict__ dv_new,
     float* __restrict__ dh0, const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len,
     const int32_t* __restrict__ seq_chunk_start, int num_qk_heads, int num_v_heads, float scale,
-    int32_t* __restrict__ status) {
+    const float* __restrict__ gl2, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // gl2 != nullptr: the per-channel-decay variant (KDA): k holds k 2^{G_L - G}, q holds q 2^G, rowscale = 1,
+  // qscale = scale, and the adjoint state decays per key channel
+  const bool kda = gl2 != nullptr;
   const int quad = warp & 3, half = warp >> 2;
   const int krow = quad * 32 + lane;
   const int n = blockIdx.x, hv = blockIdx.y, hq = hv / (num_v_heads / num_qk_heads);
@@ -66,8 +69,12 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
     prefetch_tile<64, 128, 256>(base + BwdDhSmem::kW, 8192, w + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
     prefetch_tile<64, 128, 256>(base + BwdDhSmem::kDO, 8192, d_o + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
     prefetch_tile<64, 64, 256>(base + BwdDhSmem::kAqk, 8192, aqk + (int64_t(c) * num_v_heads + hv) * 4096, 64, 64, tid);
-    if (tid < 64)
-      cp_async4(smem_u32(s_g2 + stage * 64 + tid), g_cs + int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv);
+    if (kda) {
+      if (tid < 128) cp_async4(smem_u32(s_g2 + stage * 128 + tid), gl2 + (int64_t(c) * num_v_heads + hv) * kDim + tid);
+    } else if (tid < 64) {
+      cp_async4(smem_u32(s_g2 + stage * 128 + tid),
+                g_cs + int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv);
+    }
     cp_async_commit();
   };
   if (c_begin < c_end) prefetch(c_end - 1, 0);
@@ -128,13 +135,13 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
     phase ^= 1;
     tc_fence_after();
 
-    const float* g2 = s_g2 + stage * 64;
-    const float g_last = g2[len - 1];
+    const float* g2 = s_g2 + stage * 128;
+    const float g_last = kda ? g2[krow] : g2[len - 1];
     {
       const int i = quad * 16 + (lane & 15);
       const bool owner = lane < 16;
       const bool live = owner && i < len;
-      const float rs = live ? fast_exp2(g_last - g2[i]) : 0.f;
+      const float rs = live ? (kda ? 1.f : fast_exp2(g_last - g2[i])) : 0.f;
       __nv_bfloat16* drow = dv_new + int64_t(start + i) * v_stride + hv * kDim + half * 64;
 #pragma unroll
       for (int p = 0; p < 2; ++p) {
@@ -155,7 +162,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
     // do -> do_g = bf16(qscale do), in place (Aqk^T do has read do)
     for (int i = tid; i < 64 * 16; i += 256) {
       const int r = i >> 4, cc = i & 15;
-      const float qs = scale * fast_exp2(g2[r]);
+      const float qs = kda ? scale : scale * fast_exp2(g2[r]);
       float x[8];
       unpack8(tile_chunk(st + BwdDhSmem::kDO, 8192, r, cc), x);
 #pragma unroll
@@ -215,6 +222,24 @@ extern "C" int mek_gdn_bwd_dh(const MekGdnDims* d, const void* q, const void* k,
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(w),
       static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(aqk), g_cs, dht,
       static_cast<__nv_bfloat16*>(dh_tape), static_cast<__nv_bfloat16*>(dv_new), dh0, d->chunk_start, d->chunk_len,
-      d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, d->scale, status);
+      d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, d->scale, nullptr, status);
   return launched("bwd_dh");
+}
+
+extern "C" int mek_kda_bwd_dh(const MekGdnDims* d, const void* qg, const void* kr, const void* w, const void* d_o,
+                              const void* aqk, const float* gl2, void* dh_tape, void* dv_new, int32_t* status,
+                              void* stream) {
+  using namespace mek;
+  if (d == nullptr || d->num_seqs <= 0 || d->num_v_heads <= 0 || d->num_qk_heads != d->num_v_heads)
+    return fail(MEK_ERR_INVALID, "kda_bwd_dh: bad extents (KDA has one value head per key head)");
+  if (d->head_dim != 128) return fail(MEK_ERR_UNSUPPORTED, "kda_bwd_dh: head dims must be 128, not %d", d->head_dim);
+  if (gl2 == nullptr) return fail(MEK_ERR_INVALID, "kda_bwd_dh: gl2 is null");
+  const size_t smem = BwdDhSmem::kBytes + 1024;
+  if (int rc = want_smem(gdn_bwd_dh_kernel, smem, "kda_bwd_dh")) return rc;
+  gdn_bwd_dh_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(qg), static_cast<const __nv_bfloat16*>(kr), static_cast<const __nv_bfloat16*>(w),
+      static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(aqk), nullptr, nullptr,
+      static_cast<__nv_bfloat16*>(dh_tape), static_cast<__nv_bfloat16*>(dv_new), nullptr, d->chunk_start, d->chunk_len,
+      d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, d->scale, gl2, status);
+  return launched("kda_bwd_dh");
 }

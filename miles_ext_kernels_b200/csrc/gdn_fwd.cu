@@ -254,22 +254,25 @@ struct FwdHSmem {
   static constexpr uint32_t kW = 0, kK = 16384, kU = 32768;
   static constexpr uint32_t kH = 2 * kStage;      // [128 k][128 v] bf16(h), 2 blocks of 16 KiB (one per V half)
   static constexpr uint32_t kVS = kH + 32768;     // [64][128] bf16(rowscale v_new)
-  static constexpr uint32_t kG = kVS + 16384;     // g2[2][64]
-  static constexpr uint32_t kBytes = kG + 512;
+  static constexpr uint32_t kG = kVS + 16384;     // gates[2][128]: GDN g2 per token [64]; KDA chunk-end gate per channel
+  static constexpr uint32_t kBytes = kG + 1024;
 };
 
+// `gl2` != nullptr selects the per-channel-decay variant (KDA): `k` then holds k 2^{G_L - G} (the decay to the chunk
+// end is folded into the operand, so rowscale = 1) and the state decays per key channel: row k by 2^{gl2[c, hv, k]}.
 __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ u,
     const float* __restrict__ g_cs, const float* __restrict__ h0, __nv_bfloat16* __restrict__ h_tape,
     __nv_bfloat16* __restrict__ v_new, float* __restrict__ final_state, const int32_t* __restrict__ chunk_start,
     const int32_t* __restrict__ chunk_len, const int32_t* __restrict__ seq_chunk_start, int num_qk_heads,
-    int num_v_heads, int32_t* __restrict__ status) {
+    int num_v_heads, const float* __restrict__ gl2, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool kda = gl2 != nullptr;
   const int quad = warp & 3, half = warp >> 2;   // tensor-memory lane quadrant; V half of this warpgroup
   const int krow = quad * 32 + lane;             // row of h this thread holds
   const int n = blockIdx.x, hv = blockIdx.y, hq = hv / (num_v_heads / num_qk_heads);
@@ -292,8 +295,12 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     prefetch_tile<64, 128, 256>(base + FwdHSmem::kW, 8192, w + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
     prefetch_tile<64, 128, 256>(base + FwdHSmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
     prefetch_tile<64, 128, 256>(base + FwdHSmem::kU, 8192, u + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-    if (tid < 64)
-      cp_async4(smem_u32(s_g2 + stage * 64 + tid), g_cs + int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv);
+    if (kda) {
+      if (tid < 128) cp_async4(smem_u32(s_g2 + stage * 128 + tid), gl2 + (int64_t(c) * num_v_heads + hv) * kDim + tid);
+    } else if (tid < 64) {
+      cp_async4(smem_u32(s_g2 + stage * 128 + tid),
+                g_cs + int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv);
+    }
     cp_async_commit();
   };
   if (c_begin < c_end) prefetch(c_begin, 0);
@@ -351,14 +358,14 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     phase ^= 1;
     tc_fence_after();
 
-    const float* g2 = s_g2 + stage * 64;
-    const float g_last = g2[len - 1];
+    const float* g2 = s_g2 + stage * 128;
+    const float g_last = kda ? g2[krow] : g2[len - 1];  // KDA: this thread's key channel
     {
       // rows of the M = 64 accumulator: lanes 0..15 of each quadrant; the warpgroups split the columns
       const int i = quad * 16 + (lane & 15);
       const bool owner = lane < 16;
       const bool live = owner && i < len;
-      const float rs = live ? fast_exp2(g_last - g2[i]) : 0.f;
+      const float rs = live ? (kda ? 1.f : fast_exp2(g_last - g2[i])) : 0.f;
       __nv_bfloat16* vrow = v_new + int64_t(start + i) * v_stride + hv * kDim + half * 64;
 #pragma unroll
       for (int p = 0; p < 2; ++p) {
@@ -454,7 +461,8 @@ __global__ void __launch_bounds__(128) gdn_fwd_o_kernel(
   load_tile<64, 128, 128>(sm + FwdOSmem::kVN, 8192, v_new + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
   load_tile<128, 128, 128>(sm + FwdOSmem::kH, 16384, h_tape + tile * 16384, 128, 128, tid);
   load_tile<64, 64, 128>(sm + FwdOSmem::kAqk, 8192, aqk + tile * 4096, 64, 64, tid);
-  if (tid < 64) s_g2[tid] = g_cs[int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv];
+  // g_cs == nullptr: the per-channel-decay variant, whose q operand already holds q 2^G (qscale = scale)
+  if (tid < 64) s_g2[tid] = g_cs ? g_cs[int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv] : 0.f;
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -564,8 +572,23 @@ int mek_gdn_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void*
   gdn_fwd_h_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(u),
       g_cs, h0, static_cast<__nv_bfloat16*>(h_tape), static_cast<__nv_bfloat16*>(v_new), final_state, d->chunk_start,
-      d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, status);
+      d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, nullptr, status);
   return launched("fwd_h");
+}
+
+int mek_kda_fwd_h(const MekGdnDims* d, const void* kr, const void* w, const void* u, const float* gl2, void* h_tape,
+                  void* v_new, int32_t* status, void* stream) {
+  using namespace mek;
+  if (int rc = check_dims(d, "kda_fwd_h")) return rc;
+  if (d->num_qk_heads != d->num_v_heads) return fail(MEK_ERR_INVALID, "kda_fwd_h: KDA has one value head per key head");
+  if (gl2 == nullptr) return fail(MEK_ERR_INVALID, "kda_fwd_h: gl2 is null");
+  const size_t smem = FwdHSmem::kBytes + 1024;
+  if (int rc = want_smem(gdn_fwd_h_kernel, smem, "kda_fwd_h")) return rc;
+  gdn_fwd_h_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(kr), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(u),
+      nullptr, nullptr, static_cast<__nv_bfloat16*>(h_tape), static_cast<__nv_bfloat16*>(v_new), nullptr,
+      d->chunk_start, d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, gl2, status);
+  return launched("kda_fwd_h");
 }
 
 int mek_gdn_fwd_o(const MekGdnDims* d, const void* q, const void* aqk, const void* v_new, const void* h_tape,
@@ -579,6 +602,11 @@ int mek_gdn_fwd_o(const MekGdnDims* d, const void* q, const void* aqk, const voi
       static_cast<const __nv_bfloat16*>(v_new), static_cast<const __nv_bfloat16*>(h_tape), g_cs,
       static_cast<__nv_bfloat16*>(o), d->chunk_start, d->chunk_len, d->num_qk_heads, d->num_v_heads, d->scale, status);
   return launched("fwd_o");
+}
+
+int mek_kda_fwd_o(const MekGdnDims* d, const void* qg, const void* aqk, const void* v_new, const void* h_tape, void* o,
+                  int32_t* status, void* stream) {
+  return mek_gdn_fwd_o(d, qg, aqk, v_new, h_tape, nullptr, o, status, stream);
 }
 
 }  // extern "C"

@@ -1,0 +1,170 @@
+"""KDA on a B200 against the CPU oracle: every stage against the oracle's tape, the public entry against the exact
+FP64 recurrence and the reference-oracle fixtures (``tests/golden/kda_reference_*.pt``), the benchmark's unbounded
+gates, the raw gate with its parameter gradients, and bitwise repeatability.
+
+Budgets: relative RMS error <= 1e-2 and largest absolute error <= 2e-2 x the largest reference magnitude per tensor
+(the reference's measured KDA errors are 4e-3 .. 1e-2, reference: tests/cake/kda/_budgets.py:45-52)."""
+
+from __future__ import annotations
+
+import math
+from pathlib import Path
+
+import pytest
+import torch
+
+from gdn_cases import to_token_major
+from oracle import gdn_oracle as O
+from oracle import kda_oracle as K
+
+pytestmark = pytest.mark.gpu
+NAMES = ("o", "dq", "dk", "dv", "dg", "dbeta")
+LOG2E = 1.4426950408889634
+
+
+def draw(seq_lens, H, seed, gate="weak", normalised=True):
+    T = sum(seq_lens)
+    gen = torch.Generator().manual_seed(seed)
+    q, k = torch.randn(T, H, 128, generator=gen), torch.randn(T, H, 128, generator=gen)
+    if normalised:
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6)
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    v = torch.randn(T, H, 128, generator=gen)
+    beta = torch.sigmoid(torch.randn(T, H, generator=gen))
+    a = torch.randn(T, H, 128, generator=gen)
+    if gate == "weak":
+        g = -0.3 * torch.rand(T, H, 128, generator=gen)
+    else:  # the benchmark generator: unbounded
+        a_log = torch.rand(H, generator=gen) * math.log(16.0)
+        g = -torch.nn.functional.softplus(a) * torch.exp(a_log)[None, :, None]
+    do = torch.randn(T, H, 128, generator=gen)
+    return {"q": q.bfloat16(), "k": k.bfloat16(), "v": v.bfloat16(), "g": g, "beta": beta.bfloat16(),
+            "do": do.bfloat16()}
+
+
+def close(got, want, name, rel_rms=5e-3, max_rel=2e-2):
+    m = O.metrics(got.float().cpu(), want.float())
+    assert m["finite"] and m["rel_rms"] <= rel_rms and m["max_abs"] <= max_rel * max(m["max_ref"], 1e-6), (name, m)
+
+
+def run(x, seq_lens, **modes):
+    from miles_ext_kernels_b200.cake import kda
+
+    dev = torch.device("cuda")
+    cu = [0]
+    for n in seq_lens:
+        cu.append(cu[-1] + n)
+    leaves = {n: x[n].to(dev).requires_grad_(True) for n in ("q", "k", "v", "g", "beta")}
+    extra = {n: modes[n].to(dev).requires_grad_(True) for n in ("A_log", "dt_bias") if n in modes}
+    flags = {n: v for n, v in modes.items() if n not in extra}
+    out = kda.chunk_kda(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"],
+                        torch.tensor(cu, dtype=torch.int32, device=dev), **flags, **extra)
+    out.backward(x["do"].to(dev))
+    torch.cuda.synchronize()
+    got = {"o": out.detach().cpu(), **{f"d{n}": t.grad.cpu() for n, t in leaves.items()}}
+    got.update({f"d{n}": t.grad.cpu() for n, t in extra.items()})
+    return got
+
+
+@pytest.mark.parametrize("case", ["ragged", "strong"])
+def test_stages_against_the_oracle_tape(case):
+    from miles_ext_kernels_b200.cake._impl.kda import ops
+    from miles_ext_kernels_b200.cake._impl.gdn.stages import check_status
+
+    seq_lens, H, gate = {"ragged": ((1, 63, 64, 65, 130), 2, "weak"), "strong": ((200,), 2, "strong")}[case]
+    x = draw(seq_lens, H, seed=41, gate=gate)
+    dev = torch.device("cuda")
+    cu = [0]
+    for n in seq_lens:
+        cu.append(cu[-1] + n)
+    d = {n: t.to(dev) for n, t in x.items()}
+    beta32 = d["beta"].float()
+    o, s = ops._forward(d["q"], d["k"], d["v"], d["g"], beta32, torch.tensor(cu, dtype=torch.int32, device=dev),
+                        128**-0.5, False)
+    dq, dk, dv, dg, dbeta = ops._backward(s, d["v"], beta32, d["do"])
+    torch.cuda.synchronize()
+    check_status(s.status)
+    f = {n: t.float() for n, t in x.items()}
+    o_ref, t = K.chunked_forward(f["q"], f["k"], f["v"], f["g"], f["beta"], seq_lens)
+    ref = K.chunked_backward(t, f["do"])
+    nc = t.table.num_chunks
+    close(s.g2, to_token_major(t.G, t.table) * LOG2E, "g2", rel_rms=1e-5, max_rel=1e-4)
+    close(s.qg, to_token_major(t.qg, t.table), "qg")
+    close(s.kr, to_token_major(t.kr, t.table), "kr")
+    close(s.aqk[:nc], t.Aqk, "Aqk")
+    close(s.a[:nc], t.A, "A")
+    close(s.w, to_token_major(t.w, t.table), "w")
+    close(s.h[:nc], t.h, "h")
+    close(s.v_new, to_token_major(t.v_new, t.table), "v_new")
+    close(o, o_ref, "o")
+    for name, got in (("dv", dv), ("dq", dq), ("dk", dk), ("dg", dg), ("dbeta", dbeta)):
+        close(got, ref[name], name)
+
+
+@pytest.mark.parametrize("l2", [False, True], ids=["normalised", "l2norm_in_op"])
+def test_within_budgets_of_the_fp64_recurrence(l2):
+    seq_lens = (63, 130, 257)
+    x = draw(seq_lens, 2, seed=42, normalised=not l2)
+    got = run(x, seq_lens, use_qk_l2norm_in_kernel=l2)
+    ref = K.recurrence_fp64(x["q"], x["k"], x["v"], x["g"], x["beta"], seq_lens, do=x["do"], use_qk_l2norm=l2)
+    for name in NAMES:
+        ok, m = O.within_budget(got[name].float(), ref[name])
+        assert ok, (name, m)
+
+
+def test_unbounded_gates_of_the_benchmark_generator_stay_finite_and_accurate():
+    seq_lens = (300,)
+    x = draw(seq_lens, 2, seed=43, gate="strong")
+    got = run(x, seq_lens)
+    ref = K.recurrence_fp64(x["q"], x["k"], x["v"], x["g"], x["beta"], seq_lens, do=x["do"])
+    for name in NAMES:
+        ok, m = O.within_budget(got[name].float(), ref[name])
+        assert ok, (name, m)
+
+
+@pytest.mark.parametrize("path", sorted((Path(__file__).parent / "golden").glob("kda_reference_*.pt")),
+                         ids=lambda p: p.stem)
+def test_against_the_reference_oracle_fixtures_with_the_raw_gate(path):
+    r = torch.load(path)
+    x = {n: r["inputs"][n] for n in ("q", "k", "v", "g", "beta")}
+    x["do"] = r["inputs"]["dout"]
+    got = run(x, r["lengths"], use_gate_in_kernel=True, A_log=r["inputs"]["A_log"], dt_bias=r["inputs"]["dt_bias"],
+              scale=r["scale"])
+    for name in (*NAMES, "dA_log", "ddt_bias"):
+        ok, m = O.within_budget(got[name].float(), r["raw"][name], rel_rms_max=1.2e-2, max_abs_rel=3e-2)
+        assert ok, (name, m)
+    assert got["dbeta"].dtype == torch.bfloat16
+
+
+def test_repeats_bit_for_bit_and_the_split_entry_points_agree():
+    from miles_ext_kernels_b200.cake import kda
+
+    seq_lens = (100, 60)
+    x = draw(seq_lens, 2, seed=44)
+    first, again = run(x, seq_lens), run(x, seq_lens)
+    for name in NAMES:
+        assert torch.equal(first[name], again[name]), name
+    dev = torch.device("cuda")
+    d = {n: t.to(dev) for n, t in x.items()}
+    cu = torch.tensor((0, 100, 160), dtype=torch.int32, device=dev)
+    out, saved = kda.chunk_kda_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], cu)
+    for s in (saved, None):
+        dq, dk, dv, dbeta, dg = kda.chunk_kda_bwd(d["q"], d["k"], d["v"], d["g"], d["beta"], cu, d["do"], saved=s)
+        torch.cuda.synchronize()
+        for name, t in (("o", out), ("dq", dq), ("dk", dk), ("dv", dv), ("dbeta", dbeta), ("dg", dg)):
+            assert torch.equal(t.cpu(), first[name]), name
+
+
+def test_head_count_and_shape_rejections():
+    from miles_ext_kernels_b200.cake import kda
+
+    dev = torch.device("cuda")
+    q = torch.zeros(8, 65, 128, dtype=torch.bfloat16, device=dev)
+    cu = torch.tensor((0, 8), dtype=torch.int32, device=dev)
+    with pytest.raises(ValueError, match="serve 1 to 64 heads"):
+        kda.chunk_kda(q, q, q, q.float(), q[..., 0], cu)
+    q = torch.zeros(8, 2, 128, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(ValueError, match="beta must be"):
+        kda.chunk_kda(q, q, q, q.float(), q[..., :3], cu)
+    with pytest.raises(ValueError, match="needs A_log and dt_bias"):
+        kda.chunk_kda(q, q, q, q, q[..., 0], cu, use_gate_in_kernel=True)
