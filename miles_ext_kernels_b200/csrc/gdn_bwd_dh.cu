@@ -126,8 +126,11 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
     if (abort.raised()) break;
 
     if (tid == 0) {
-      umma_gemm<64, 128>(tmem + kD1, op_k, false, op_dh, true, 128, false);      // k dh_tape
-      umma_gemm<64, 128>(tmem + kD1b, op_aqk, true, op_do, true, 64, false);     // Aqk^T do
+      // both [64 x 128] products as two N = 64 halves: V columns 0..63 -> lanes 0..15, 64..127 -> lanes 16..31
+      umma_gemm<64, 64>(tmem + kD1, op_k, false, op_dh, true, 128, false);                        // k dh_tape
+      umma_gemm<64, 64>(tmem + kD1 + (16u << 16), op_k, false, operand_at(op_dh, 0, 1), true, 128, false);
+      umma_gemm<64, 64>(tmem + kD1b, op_aqk, true, op_do, true, 64, false);                       // Aqk^T do
+      umma_gemm<64, 64>(tmem + kD1b + (16u << 16), op_aqk, true, operand_at(op_do, 0, 1), true, 64, false);
       umma_commit(&bar);
     }
     if (c > c_begin) prefetch(c - 1, stage ^ 1);
@@ -139,24 +142,21 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
     const float g_last = kda ? g2[krow] : g2[len - 1];
     {
       const int i = quad * 16 + (lane & 15);
-      const bool owner = lane < 16;
-      const bool live = owner && i < len;
+      const int lcol = (lane >> 4) * 64 + half * 32;
+      const bool live = i < len;
       const float rs = live ? (kda ? 1.f : fast_exp2(g_last - g2[i])) : 0.f;
-      __nv_bfloat16* drow = dv_new + int64_t(start + i) * v_stride + hv * kDim + half * 64;
+      __nv_bfloat16* drow = dv_new + int64_t(start + i) * v_stride + hv * kDim + lcol;
+      float a[32], b[32];
+      tmem_ld32(tmem_addr(tmem, warp, kD1 + half * 32), a);
+      tmem_ld32(tmem_addr(tmem, warp, kD1b + half * 32), b);
+      tmem_ld_wait();
 #pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        float a[32], b[32];
-        tmem_ld32(tmem_addr(tmem, warp, kD1 + half * 64 + p * 32), a);
-        tmem_ld32(tmem_addr(tmem, warp, kD1b + half * 64 + p * 32), b);
-        tmem_ld_wait();
+      for (int j = 0; j < 32; ++j) a[j] = live ? fmaf(rs, a[j], round_bf16(b[j])) : 0.f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) a[j] = live ? fmaf(rs, a[j], round_bf16(b[j])) : 0.f;
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          const uint4 packed = pack8(a + 8 * jj);
-          if (live) reinterpret_cast<uint4*>(drow + p * 32)[jj] = packed;
-          if (owner) set_tile_chunk(sm + BwdDhSmem::kDV, 8192, i, half * 8 + p * 4 + jj, packed);
-        }
+      for (int jj = 0; jj < 4; ++jj) {
+        const uint4 packed = pack8(a + 8 * jj);
+        if (live) reinterpret_cast<uint4*>(drow)[jj] = packed;
+        set_tile_chunk(sm + BwdDhSmem::kDV, 8192, i, (lcol >> 3) + jj, packed);
       }
     }
     // do -> do_g = bf16(qscale do), in place (Aqk^T do has read do)

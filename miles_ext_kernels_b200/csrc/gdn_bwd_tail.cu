@@ -32,11 +32,15 @@ struct TailSmem {
   static constexpr uint32_t kB8a = kAqk + 8192;        // [64][64] dS -> dA -> bf16(beta dL D)
   static constexpr uint32_t kB8b = kB8a + 8192;        // [64][64] X = A^T dA
   static constexpr uint32_t kScal = kB8b + 8192;       // floats: beta[2][64], g2[2][64], cs[2][4][64], red[2][64],
-                                                       //         red2[2][64], warp[8]
-  static constexpr uint32_t kBytes = kScal + (2 * 64 * 2 + 2 * 4 * 64 + 4 * 64 + 16) * 4;
+                                                       //         red2[4][64], warp[8]   (red is [4][64] too)
+  static constexpr uint32_t kBytes = kScal + (2 * 64 * 2 + 2 * 4 * 64 + 8 * 64 + 16) * 4;
 };
 
-constexpr uint32_t kColDQ = 0, kColDK = 128, kColT0 = 256, kColTa = 384, kColTb = 448;
+// Tensor-memory columns.  A [64 x 128] accumulator takes 64 columns: its logical columns 0..63 sit in lanes 0..15 of
+// each quadrant and 64..127 in lanes 16..31 (two N = 64 instructions), so every lane of a warp owns a row piece.
+// [64 x 64] accumulators (Ta, Tb) are not split: lanes 0..15 only.
+constexpr uint32_t kColDQ = 0, kColDK = 64, kColT0 = 128, kColT1 = 192, kColTa = 256, kColTb = 320;
+constexpr uint32_t kUpperLanes = 16u << 16;
 
 template <int N>
 __device__ __forceinline__ void cp_async_wait_pending() {
@@ -65,18 +69,21 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int group = num_v_heads / num_qk_heads;
   const int num_pairs = num_chunks * num_qk_heads;
-  // accumulator rows: M = 64 results live in lanes 0..15 of each warp's tensor-memory quadrant; warps w and w + 4
-  // share the rows 16 (w % 4) .. + 15 and split the columns in halves
-  const int quad = warp & 3, ch = warp >> 2;
+  // accumulator rows: warps w and w + 4 share the rows 16 (w % 4) .. + 15.  A 128-wide accumulator is split four
+  // ways: the lane half picks logical columns 0..63 / 64..127, the warpgroup the 32-column piece inside that half.
+  // A 64-wide accumulator lives in lanes 0..15 only and is split in two by the warpgroup.
+  const int quad = warp & 3, ch = warp >> 2, lh = lane >> 4;
   const int row = quad * 16 + (lane & 15);
-  const bool owner = lane < 16;
+  const bool owner = lane < 16;       // holds a piece of the 64-wide accumulators
+  const int cq = lh * 2 + ch;         // which 32-column quarter of a 128-wide accumulator
+  const int lcol = lh * 64 + ch * 32; // its first logical column
 
   float* s_beta = reinterpret_cast<float*>(sm + TailSmem::kScal);  // [2][64]
   float* s_g2 = s_beta + 128;                                      // [2][64]
   float* s_cs = s_g2 + 128;                                        // [2][4][64] partial column sums per quadrant
-  float* s_red = s_cs + 512;                                       // [2][64]
-  float* s_red2 = s_red + 128;                                     // [2][64]
-  float* s_warp = s_red2 + 128;                                    // [8]
+  float* s_red = s_cs + 512;                                       // [4][64]
+  float* s_red2 = s_red + 256;                                     // [4][64]
+  float* s_warp = s_red2 + 256;                                    // [8]
   Abort abort{&abort_flag};
 
   if (tid == 0) {
@@ -167,6 +174,13 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     __syncthreads();
     tc_fence_after();
   };
+  // D[64 x 128] (+)= A B as two N = 64 instructions: logical columns 0..63 -> lanes 0..15, 64..127 -> lanes 16..31
+  auto gemm128 = [&](uint32_t col, const Operand& a, bool a_mn, const Operand& b, bool b_mn, uint32_t kdim,
+                     bool accumulate, bool neg_a = false) {
+    const Operand b_hi = b_mn ? operand_at(b, 0, 1) : operand_at(b, 64, 0);
+    umma_gemm<64, 64>(tmem + col, a, a_mn, b, b_mn, kdim, accumulate, neg_a);
+    umma_gemm<64, 64>(tmem + col + kUpperLanes, a, a_mn, b_hi, b_mn, kdim, accumulate, neg_a);
+  };
   // column sums of a [64 x 64] matrix held one 32-column row piece per owner thread: reduce over the 16 rows of the
   // warp by shuffles, then publish one partial per quadrant (summed after the next block barrier)
   auto publish_column_sums = [&](float* piece, float* where) {
@@ -179,7 +193,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     }
   };
 
-  float dk_reg[64];  // scaled dk terms of this thread's (row, column half), summed over the group
+  float dk_reg[32];  // scaled dk terms of this thread's (row, 32-column quarter), summed over the group
   int item_parity = 0, qk_buf = 0;
   bool aborted = false;
   for (; pair_live(pair) && !aborted; pair += gridDim.x, qk_buf ^= 1) {
@@ -190,12 +204,12 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     const int next_pair = pair + gridDim.x;
     const bool has_next_pair = pair_live(next_pair);
 #pragma unroll
-    for (int j = 0; j < 64; ++j) dk_reg[j] = 0.f;
+    for (int j = 0; j < 32; ++j) dk_reg[j] = 0.f;
 
     for (int gi = 0; gi < group; ++gi, item_parity ^= 1) {
       const Item it = item_of(pair, gi);
       const int start = it.start, len = it.len, hv = it.hv;
-      const bool live = owner && row < len;
+      const bool live = row < len;
       const bool last_of_pair = gi + 1 == group;
       const bool has_next = !last_of_pair || has_next_pair;
       const Item nx = has_next ? (last_of_pair ? item_of(next_pair, 0) : item_of(pair, gi + 1)) : it;
@@ -216,7 +230,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       // ---- phase 1: dAqk = do v_new^T ; dkh = v_new dh^T --------------------------------------------------------
       if (tid == 0) {
         umma_gemm<64, 64>(tmem + kColTa, op_do, false, op_vn, false, 128, false);
-        umma_gemm<64, 128>(tmem + kColT0, op_vn, false, op_dh, false, 128, false);
+        gemm128(kColT0, op_vn, false, op_dh, false, 128, false);
         umma_commit(&bar);
       }
       // meanwhile: sum(dh . h) over the whole state tile
@@ -253,25 +267,22 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
           }
           if (owner) set_tile_chunk(sm + TailSmem::kB8a, 8192, row, ch * 4 + jj, pack8(ds));
         }
-        dG += rowsum;
+        if (owner) dG += rowsum;
         publish_column_sums(s, s_cs);
-        // dkh piece: 64 columns
+        // dkh piece: 32 columns
         float dot = 0.f;
+        float d[32];
+        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), d);
+        tmem_ld_wait();
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-          float d[32];
-          tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 64 + p * 32), d);
-          tmem_ld_wait();
+        for (int jj = 0; jj < 4; ++jj) {
+          float kk[8];
+          unpack8(tile_chunk(k_tile, 8192, row, (lcol >> 3) + jj), kk);
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            float kk[8];
-            unpack8(tile_chunk(k_tile, 8192, row, ch * 8 + p * 4 + jj), kk);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float x = rs_row * d[jj * 8 + e];
-              dot = fmaf(x, kk[e], dot);
-              dk_reg[p * 32 + jj * 8 + e] += x;
-            }
+          for (int e = 0; e < 8; ++e) {
+            const float x = rs_row * d[jj * 8 + e];
+            dot = fmaf(x, kk[e], dot);
+            dk_reg[jj * 8 + e] += x;
           }
         }
         dG -= dot;
@@ -300,32 +311,29 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
 
       // ---- phase 2: dq += dS k + do_g h^T ; dk += dS^T q ; qh = q h ; dw = -dv_new h^T --------------------------
       if (tid == 0) {
-        umma_gemm<64, 128>(tmem + kColDQ, op_b8a, false, op_k, true, 64, gi > 0);
-        umma_gemm<64, 128>(tmem + kColDQ, op_do, false, op_h, false, 128, true);
-        umma_gemm<64, 128>(tmem + kColDK, op_b8a, true, op_q, true, 64, gi > 0);
-        umma_gemm<64, 128>(tmem + kColT0, op_q, false, op_h, true, 128, false);
-        umma_gemm<64, 128>(tmem + kColTa, op_dvn, false, op_h, false, 128, false, /*neg_a=*/true);
+        gemm128(kColDQ, op_b8a, false, op_k, true, 64, gi > 0);
+        gemm128(kColDQ, op_do, false, op_h, false, 128, true);
+        gemm128(kColDK, op_b8a, true, op_q, true, 64, gi > 0);
+        gemm128(kColT0, op_q, false, op_h, true, 128, false);
+        gemm128(kColT1, op_dvn, false, op_h, false, 128, false, /*neg_a=*/true);
         umma_commit(&bar);
       }
       if (owner && ch == 0) dG -= s_cs[row] + s_cs[64 + row] + s_cs[128 + row] + s_cs[192 + row];
       mma_wait();
       {
         float dot = 0.f;
+        float qh[32], dw[32];
+        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), qh);
+        tmem_ld32(tmem_addr(tmem, warp, kColT1 + ch * 32), dw);
+        tmem_ld_wait();
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-          float qh[32], dw[32];
-          tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 64 + p * 32), qh);
-          tmem_ld32(tmem_addr(tmem, warp, kColTa + ch * 64 + p * 32), dw);
-          tmem_ld_wait();
+        for (int jj = 0; jj < 4; ++jj) {
+          float dog[8];
+          unpack8(tile_chunk(sm + TailSmem::kDO, 8192, row, (lcol >> 3) + jj), dog);
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            float dog[8];
-            unpack8(tile_chunk(sm + TailSmem::kDO, 8192, row, ch * 8 + p * 4 + jj), dog);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) dot = fmaf(dog[e], qh[jj * 8 + e], dot);
-            // h has been read by phase 2: its first half becomes the dw tile
-            if (owner) set_tile_chunk(sm + TailSmem::kH, 8192, row, ch * 8 + p * 4 + jj, pack8(dw + jj * 8));
-          }
+          for (int e = 0; e < 8; ++e) dot = fmaf(dog[e], qh[jj * 8 + e], dot);
+          // h has been read by phase 2: its first half becomes the dw tile
+          set_tile_chunk(sm + TailSmem::kH, 8192, row, (lcol >> 3) + jj, pack8(dw + jj * 8));
         }
         dG += dot;
       }
@@ -353,7 +361,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
 
       // ---- phase 3: dkb = A^T dw ; dA = dw kb^T + dv_new vb^T ----------------------------------------------------
       if (tid == 0) {
-        umma_gemm<64, 128>(tmem + kColT0, op_a, true, op_dw, true, 64, false);
+        gemm128(kColT0, op_a, true, op_dw, true, 64, false);
         umma_gemm<64, 64>(tmem + kColTa, op_dw, false, op_kb, false, 128, false);
         umma_gemm<64, 64>(tmem + kColTa, op_dvn, false, op_vb, false, 128, true);
         umma_commit(&bar);
@@ -362,23 +370,20 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       const float eg = fast_exp2(gi_row), sk = beta_row * eg;
       {
         float dot_k = 0.f, dot_kb = 0.f;
+        float dkb[32];
+        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), dkb);
+        tmem_ld_wait();
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-          float dkb[32];
-          tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 64 + p * 32), dkb);
-          tmem_ld_wait();
+        for (int jj = 0; jj < 4; ++jj) {
+          float kk[8], kb[8];
+          unpack8(tile_chunk(k_tile, 8192, row, (lcol >> 3) + jj), kk);
+          unpack8(tile_chunk(sm + TailSmem::kH + 16384, 8192, row, (lcol >> 3) + jj), kb);
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            float kk[8], kb[8];
-            unpack8(tile_chunk(k_tile, 8192, row, ch * 8 + p * 4 + jj), kk);
-            unpack8(tile_chunk(sm + TailSmem::kH + 16384, 8192, row, ch * 8 + p * 4 + jj), kb);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float x = dkb[jj * 8 + e];
-              dot_k = fmaf(x, kk[e], dot_k);
-              dot_kb = fmaf(x, kb[e], dot_kb);
-              dk_reg[p * 32 + jj * 8 + e] = fmaf(sk, x, dk_reg[p * 32 + jj * 8 + e]);
-            }
+          for (int e = 0; e < 8; ++e) {
+            const float x = dkb[jj * 8 + e];
+            dot_k = fmaf(x, kk[e], dot_k);
+            dot_kb = fmaf(x, kb[e], dot_kb);
+            dk_reg[jj * 8 + e] = fmaf(sk, x, dk_reg[jj * 8 + e]);
           }
         }
         dB += eg * dot_k;
@@ -401,7 +406,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       // ---- phase 4: X = A^T dA ; dvb = A^T dv_new ----------------------------------------------------------------
       if (tid == 0) {
         umma_gemm<64, 64>(tmem + kColTb, op_a, true, op_b8a, true, 64, false);
-        umma_gemm<64, 128>(tmem + kColT0, op_a, true, op_dvn, true, 64, false);
+        gemm128(kColT0, op_a, true, op_dvn, true, 64, false);
         umma_commit(&bar);
       }
       mma_wait();
@@ -415,24 +420,21 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
             set_tile_chunk(sm + TailSmem::kB8b, 8192, row, ch * 4 + jj, pack8(s + jj * 8));
         }
         float dot_v = 0.f;
-        __nv_bfloat16* dv_row = dv + int64_t(start + row) * v_stride + hv * kDim + ch * 64;
+        __nv_bfloat16* dv_row = dv + int64_t(start + row) * v_stride + hv * kDim + lcol;
+        float dvb[32];
+        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), dvb);
+        tmem_ld_wait();
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-          float dvb[32];
-          tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 64 + p * 32), dvb);
-          tmem_ld_wait();
+        for (int jj = 0; jj < 4; ++jj) {
+          float vv[8], out[8];
+          unpack8(tile_chunk(sm + TailSmem::kVN, 8192, row, (lcol >> 3) + jj), vv);
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            float vv[8], out[8];
-            unpack8(tile_chunk(sm + TailSmem::kVN, 8192, row, ch * 8 + p * 4 + jj), vv);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float y = dvb[jj * 8 + e];
-              dot_v = fmaf(y, vv[e], dot_v);
-              out[e] = y * beta_row;
-            }
-            if (live) reinterpret_cast<uint4*>(dv_row + p * 32)[jj] = pack8(out);
+          for (int e = 0; e < 8; ++e) {
+            const float y = dvb[jj * 8 + e];
+            dot_v = fmaf(y, vv[e], dot_v);
+            out[e] = y * beta_row;
           }
+          if (live) reinterpret_cast<uint4*>(dv_row)[jj] = pack8(out);
         }
         dB += dot_v;
       }
@@ -472,8 +474,10 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
           }
           if (owner) set_tile_chunk(sm + TailSmem::kB8a, 8192, row, ch * 4 + jj, pack8(out));
         }
-        dB += dot;
-        dG += rowsum;
+        if (owner) {
+          dB += dot;
+          dG += rowsum;
+        }
         publish_column_sums(s, s_cs + 256);
       }
       stage_sync();
@@ -484,20 +488,18 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
 
       // ---- phase 6: dk += bf16(beta dL D) k + bf16(beta dL D)^T k ------------------------------------------------
       if (tid == 0) {
-        umma_gemm<64, 128>(tmem + kColDK, op_b8a, false, op_k, true, 64, true);
-        umma_gemm<64, 128>(tmem + kColDK, op_b8a, true, op_k, true, 64, true);
+        gemm128(kColDK, op_b8a, false, op_k, true, 64, true);
+        gemm128(kColDK, op_b8a, true, op_k, true, 64, true);
         if (last_of_pair) umma_commit(&bar);  // otherwise the next item's first commit covers these too
       }
       if (owner && ch == 0) dG -= s_cs[256 + row] + s_cs[320 + row] + s_cs[384 + row] + s_cs[448 + row];
       // gate and beta gradients of this value head: combine the column halves, add the chunk-end term, suffix sum
-      float part = fmaf(fast_exp2(g_last), hdh, owner ? gdot : 0.f);
+      float part = fmaf(fast_exp2(g_last), hdh, gdot);
 #pragma unroll
       for (int m = 16; m >= 1; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
       if (lane == 0) s_warp[warp] = part;
-      if (owner) {
-        s_red[ch * 64 + row] = dG;
-        s_red2[ch * 64 + row] = dB;
-      }
+      s_red[cq * 64 + row] = dG;
+      s_red2[cq * 64 + row] = dB;
       __syncthreads();
       if (tid < 64) {
         float gamma_dot = 0.f;
@@ -505,28 +507,29 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
         for (int wv = 0; wv < 8; ++wv) gamma_dot += s_warp[wv];
         float acc = 0.f;
         for (int j = len - 1; j >= tid; --j) {
-          acc += s_red[j] + s_red[64 + j];
+          acc += (s_red[j] + s_red[64 + j]) + (s_red[128 + j] + s_red[192 + j]);
           if (j == len - 1) acc += gamma_dot;
         }
         if (tid < len) {
           dg[int64_t(start + tid) * num_v_heads + hv] = acc;
-          dbeta[int64_t(start + tid) * num_v_heads + hv] = s_red2[tid] + s_red2[64 + tid];
+          dbeta[int64_t(start + tid) * num_v_heads + hv] =
+              (s_red2[tid] + s_red2[64 + tid]) + (s_red2[128 + tid] + s_red2[192 + tid]);
         }
       }
 
       if (last_of_pair) {
         // ---- the group's dq, dk: fp32 sums, the norm's pull-back, one rounding ----------------------------------
         mma_wait();
-        const int64_t tok = int64_t(start + row) * qk_stride + hq * kDim + ch * 64;
-        // acc: this thread's 64 columns of the fp32 group sum.  With the op's L2 norm: dx = r (D - y (D . y)),
+        const int64_t tok = int64_t(start + row) * qk_stride + hq * kDim + lcol;
+        // acc: this thread's 32 columns of the fp32 group sum.  With the op's L2 norm: dx = r (D - y (D . y)),
         // y = x r from the raw row and the saved r; the dot product spans both column halves.
         auto finish = [&](float* acc, const __nv_bfloat16* raw_rows, const float* rstd, __nv_bfloat16* out) {
           if (rstd != nullptr) {
             const float r = live ? rstd[int64_t(start + row) * num_qk_heads + hq] : 0.f;
-            float y[64];
+            float y[32];
             float dot = 0.f;
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
+            for (int jj = 0; jj < 4; ++jj) {
               uint4 x = make_uint4(0u, 0u, 0u, 0u);
               if (live) x = ldg16(raw_rows + tok + jj * 8);
               unpack8(x, y + jj * 8);
@@ -537,33 +540,29 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
               }
             }
             __syncthreads();  // the gate reduction above has read s_red
-            if (owner) s_red[ch * 64 + row] = dot;
+            s_red[cq * 64 + row] = dot;
             __syncthreads();
-            dot = s_red[row] + s_red[64 + row];
+            dot = (s_red[row] + s_red[64 + row]) + (s_red[128 + row] + s_red[192 + row]);
 #pragma unroll
-            for (int j = 0; j < 64; ++j) acc[j] = r * (acc[j] - y[j] * dot);
+            for (int j = 0; j < 32; ++j) acc[j] = r * (acc[j] - y[j] * dot);
           }
           if (live) {
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj) reinterpret_cast<uint4*>(out + tok)[jj] = pack8(acc + jj * 8);
+            for (int jj = 0; jj < 4; ++jj) reinterpret_cast<uint4*>(out + tok)[jj] = pack8(acc + jj * 8);
           }
         };
         {
-          float dqv[64];
-#pragma unroll
-          for (int p = 0; p < 2; ++p) {
-            tmem_ld32(tmem_addr(tmem, warp, kColDQ + ch * 64 + p * 32), dqv + p * 32);
-            tmem_ld_wait();
-          }
+          float dqv[32];
+          tmem_ld32(tmem_addr(tmem, warp, kColDQ + ch * 32), dqv);
+          tmem_ld_wait();
           finish(dqv, q_raw, rstd_q, dq);
         }
-#pragma unroll
-        for (int p = 0; p < 2; ++p) {
+        {
           float b[32];
-          tmem_ld32(tmem_addr(tmem, warp, kColDK + ch * 64 + p * 32), b);
+          tmem_ld32(tmem_addr(tmem, warp, kColDK + ch * 32), b);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) dk_reg[p * 32 + j] += b[j];
+          for (int j = 0; j < 32; ++j) dk_reg[j] += b[j];
         }
         finish(dk_reg, k_raw, rstd_k, dk);
       }

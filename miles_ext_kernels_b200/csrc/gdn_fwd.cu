@@ -60,17 +60,20 @@ __global__ void gate_cumsum_kernel(const float* __restrict__ g, float* __restric
 // wy
 // ---------------------------------------------------------------------------------------------------------------
 struct WySmem {
-  static constexpr uint32_t kQK = 0;               // [128 rows: q then k][128 cols], 2 blocks of 16 KiB
-  static constexpr uint32_t kQKStride = 16384;
-  static constexpr uint32_t kV = 32768;            // [64][128] v -> beta v, 2 blocks of 8 KiB
+  static constexpr uint32_t kQ = 0;                // [64][128] q; after the first products: fp32 L [64][64], swizzled
+  static constexpr uint32_t kK = 16384;            // [64][128] k
+  static constexpr uint32_t kV = 32768;            // [64][128] v -> beta v
   static constexpr uint32_t kKB = kV + 16384;      // [64][128] beta 2^G k
   static constexpr uint32_t kA = kKB + 16384;      // [64][64] A (bf16)
-  static constexpr uint32_t kL = kA + 8192;        // fp32 L[64 rows i][68]: rows padded to spread the banks
-  static constexpr uint32_t kLStride = 68;
-  static constexpr uint32_t kScal = kL + 64 * 68 * 4;  // beta[64], g2[64]
+  static constexpr uint32_t kScal = kA + 8192;     // beta[64], g2[64]
   static constexpr uint32_t kBytes = kScal + 512;
 };
 
+// fp32 L[i][j] in a [64][64] array whose 16-byte groups are XOR-swizzled by the row, so that rows written by
+// different threads spread over the banks and a row is still read in 16-byte pieces
+__device__ __forceinline__ int wy_l_index(int i, int j) { return i * 64 + (j ^ ((i & 7) << 2)); }
+
+// Three CTAs per SM (shared memory) hide each other's global-load and solve latencies; tensor memory: 128 columns.
 __global__ void __launch_bounds__(128) gdn_wy_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
     const float* __restrict__ beta, const float* __restrict__ g_cs, __nv_bfloat16* __restrict__ a_out,
@@ -87,19 +90,18 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   if (len <= 0) return;  // a pad chunk of a device-built table
   float* s_beta = reinterpret_cast<float*>(sm + WySmem::kScal);
   float* s_g2 = s_beta + 64;
-  float* s_lt = reinterpret_cast<float*>(sm + WySmem::kL);
+  float* s_l = reinterpret_cast<float*>(sm + WySmem::kQ);
+  constexpr uint32_t kUpper = 16u << 16;  // an M = 64 accumulator in lanes 16..31 of each quadrant
 
   if (tid == 0) {
     mbar_init(&bar, 1);
     fence_mbar_init();
   }
-  if (warp == 0) tmem_alloc(&tmem_slot, 256);
+  if (warp == 0) tmem_alloc(&tmem_slot, 128);
 
   const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
-  load_tile<64, 128, 128>(sm + WySmem::kQK, WySmem::kQKStride, q + int64_t(start) * qk_stride + hq * kDim, qk_stride,
-                          len, tid, 0);
-  load_tile<64, 128, 128>(sm + WySmem::kQK, WySmem::kQKStride, k + int64_t(start) * qk_stride + hq * kDim, qk_stride,
-                          len, tid, 64);
+  load_tile<64, 128, 128>(sm + WySmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+  load_tile<64, 128, 128>(sm + WySmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
   load_tile<64, 128, 128>(sm + WySmem::kV, 8192, v + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
   if (tid < 64) {
     const int i = tid < len ? tid : len - 1;
@@ -113,11 +115,11 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   const uint32_t tmem = tmem_slot;
   const uint32_t sbase = smem_u32(sm);
 
-  // S = [q; k] k^T : rows 0..63 = q k^T, rows 64..127 = k k^T
+  // q k^T -> lanes 0..15, k k^T -> lanes 16..31 of the same 64 columns
   if (tid == 0) {
-    const Operand qk{sbase + WySmem::kQK, WySmem::kQKStride};
-    const Operand kk{sbase + WySmem::kQK + 64 * 128, WySmem::kQKStride};
-    umma_gemm<128, 64>(tmem, qk, false, kk, false, 128, false);
+    const Operand op_q{sbase + WySmem::kQ, 8192}, op_k{sbase + WySmem::kK, 8192};
+    umma_gemm<64, 64>(tmem, op_q, false, op_k, false, 128, false);
+    umma_gemm<64, 64>(tmem + kUpper, op_k, false, op_k, false, 128, false);
     umma_commit(&bar);
   }
   // meanwhile: kb = bf16(beta 2^G k), vb = bf16(beta v) (in place)
@@ -125,7 +127,7 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
     const int r = i >> 4, cc = i & 15;
     const float b = s_beta[r], s = b * fast_exp2(s_g2[r]);
     float x[8];
-    unpack8(tile_chunk(sm + WySmem::kQK, WySmem::kQKStride, 64 + r, cc), x);
+    unpack8(tile_chunk(sm + WySmem::kK, 8192, r, cc), x);
 #pragma unroll
     for (int j = 0; j < 8; ++j) x[j] *= s;
     set_tile_chunk(sm + WySmem::kKB, 8192, r, cc, pack8(x));
@@ -136,18 +138,20 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   }
   bool ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0));
   tc_fence_after();
+  __syncthreads();  // every thread sees the products done: the q tile's space now takes L
 
   if (ok) {
-    const int i = tid & 63;
+    // lanes 0..15: Aqk row i -> global; lanes 16..31: L row i -> shared
+    const int i = warp * 16 + (lane & 15);
+    const bool upper = lane >= 16;
     const float gi = s_g2[i], bi = s_beta[i];
-    if (tid < 64) {
-      // Aqk row i -> global
-      __nv_bfloat16* dst = aqk_out + (int64_t(c) * num_v_heads + hv) * 4096 + i * 64;
+    __nv_bfloat16* dst = aqk_out + (int64_t(c) * num_v_heads + hv) * 4096 + i * 64;
 #pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        float s[32];
-        tmem_ld32(tmem_addr(tmem, warp, p * 32), s);
-        tmem_ld_wait();
+    for (int p = 0; p < 2; ++p) {
+      float s[32];
+      tmem_ld32(tmem_addr(tmem, warp, p * 32), s);
+      tmem_ld_wait();
+      if (!upper) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int col = p * 32 + j;
@@ -155,18 +159,11 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst + p * 32)[j] = pack8(s + 8 * j);
-      }
-    } else {
-      // L row i -> shared (row-major, padded rows): the solve reads it as float4 broadcasts
-#pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        float s[32];
-        tmem_ld32(tmem_addr(tmem, warp, p * 32), s);
-        tmem_ld_wait();
+      } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int col = p * 32 + j;
-          s_lt[i * WySmem::kLStride + col] = col < i ? bi * s[j] * fast_exp2(gi - s_g2[col]) : 0.f;
+          s_l[wy_l_index(i, col)] = col < i ? bi * s[j] * fast_exp2(gi - s_g2[col]) : 0.f;
         }
       }
     }
@@ -184,7 +181,7 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
       float acc0 = (i == tid) ? 1.f : 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
       for (int j = 0; j < i; j += 4) {
-        const float4 l = *reinterpret_cast<const float4*>(s_lt + i * WySmem::kLStride + j);
+        const float4 l = *reinterpret_cast<const float4*>(s_l + wy_l_index(i, j));
         acc0 = fmaf(-l.x, x[j], acc0);
         if (j + 1 < i) acc1 = fmaf(-l.y, x[j + 1], acc1);
         if (j + 2 < i) acc2 = fmaf(-l.z, x[j + 2], acc2);
@@ -201,12 +198,13 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   __syncthreads();
   tc_fence_after();
 
+  // w = A kb -> lanes 0..15, u = A vb -> lanes 16..31 of columns 0..127
   if (tid == 0) {
     const Operand a{sbase + WySmem::kA, 8192};
     const Operand kb{sbase + WySmem::kKB, 8192};
     const Operand vb{sbase + WySmem::kV, 8192};
     umma_gemm<64, 128>(tmem, a, false, kb, true, 64, false);
-    umma_gemm<64, 128>(tmem + 128, a, false, vb, true, 64, false);
+    umma_gemm<64, 128>(tmem + kUpper, a, false, vb, true, 64, false);
     umma_commit(&bar);
   }
   // A -> global while the MMAs run
@@ -216,28 +214,24 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
 
   ok = __all_sync(0xffffffffu, ok);
   if (ok) {
-    // M = 64 accumulators live in lanes 0..15 of each warp's quadrant; tcgen05.ld is warp-wide, so every lane loads
-    // and only the lanes that own a row use what they read
     const int i = warp * 16 + (lane & 15);
-    const bool live = lane < 16 && i < len;
-    __nv_bfloat16* wd = w_out + int64_t(start + i) * v_stride + hv * kDim;
-    __nv_bfloat16* ud = u_out + int64_t(start + i) * v_stride + hv * kDim;
+    const bool live = i < len;
+    __nv_bfloat16* dst = (lane < 16 ? w_out : u_out) + int64_t(start + i) * v_stride + hv * kDim;
 #pragma unroll
-    for (int p = 0; p < 8; ++p) {
+    for (int p = 0; p < 4; ++p) {
       float s[32];
       tmem_ld32(tmem_addr(tmem, warp, p * 32), s);
       tmem_ld_wait();
-      __nv_bfloat16* dst = (p < 4 ? wd : ud) + (p & 3) * 32;
       if (live) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = pack8(s + 8 * j);
+        for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst + p * 32)[j] = pack8(s + 8 * j);
       }
     }
   }
   if (!ok && tid == 0) atomicExch(status, kDevWaitTimeout | (1 << 8));
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 256);
+  if (warp == 0) tmem_dealloc(tmem, 128);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -350,7 +344,10 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     if (abort.raised()) break;
 
     if (tid == 0) {
-      umma_gemm<64, 128>(tmem, op_w, false, op_h, true, 128, false);
+      // D1 = w h_tape as two N = 64 products: V columns 0..63 -> lanes 0..15, 64..127 -> lanes 16..31 (columns 0..63
+      // of tensor memory), so every lane of a warp owns a row piece in the epilogue
+      umma_gemm<64, 64>(tmem, op_w, false, op_h, true, 128, false);
+      umma_gemm<64, 64>(tmem + (16u << 16), op_w, false, operand_at(op_h, 0, 1), true, 128, false);
       umma_commit(&bar);
     }
     if (c + 1 < c_end) prefetch(c + 1, stage ^ 1);  // the other stage's last readers finished a step ago
@@ -361,29 +358,26 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     const float* g2 = s_g2 + stage * 128;
     const float g_last = kda ? g2[krow] : g2[len - 1];  // KDA: this thread's key channel
     {
-      // rows of the M = 64 accumulator: lanes 0..15 of each quadrant; the warpgroups split the columns
+      // row i = 16 quad + lane % 16; logical V columns (lane / 16) * 64 + half * 32 .. + 32
       const int i = quad * 16 + (lane & 15);
-      const bool owner = lane < 16;
-      const bool live = owner && i < len;
+      const int lcol = (lane >> 4) * 64 + half * 32;
+      const bool live = i < len;
       const float rs = live ? (kda ? 1.f : fast_exp2(g_last - g2[i])) : 0.f;
-      __nv_bfloat16* vrow = v_new + int64_t(start + i) * v_stride + hv * kDim + half * 64;
+      __nv_bfloat16* vrow = v_new + int64_t(start + i) * v_stride + hv * kDim + lcol;
+      float d[32];
+      tmem_ld32(tmem_addr(tmem, warp, half * 32), d);
+      tmem_ld_wait();
 #pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        float d[32];
-        tmem_ld32(tmem_addr(tmem, warp, half * 64 + p * 32), d);
-        tmem_ld_wait();
+      for (int jj = 0; jj < 4; ++jj) {
+        float uv[8], vs[8];
+        unpack8(tile_chunk(st + FwdHSmem::kU, 8192, i, (lcol >> 3) + jj), uv);
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          float uv[8], vs[8];
-          unpack8(tile_chunk(st + FwdHSmem::kU, 8192, i, half * 8 + p * 4 + jj), uv);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            uv[e] = live ? uv[e] - d[jj * 8 + e] : 0.f;
-            vs[e] = rs * uv[e];
-          }
-          if (live) reinterpret_cast<uint4*>(vrow + p * 32)[jj] = pack8(uv);
-          if (owner) set_tile_chunk(sm + FwdHSmem::kVS, 8192, i, half * 8 + p * 4 + jj, pack8(vs));
+        for (int e = 0; e < 8; ++e) {
+          uv[e] = live ? uv[e] - d[jj * 8 + e] : 0.f;
+          vs[e] = rs * uv[e];
         }
+        if (live) reinterpret_cast<uint4*>(vrow)[jj] = pack8(uv);
+        set_tile_chunk(sm + FwdHSmem::kVS, 8192, i, (lcol >> 3) + jj, pack8(vs));
       }
     }
     fence_async_smem();
