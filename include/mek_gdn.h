@@ -115,10 +115,10 @@ int mek_gdn_bwd_dh(const MekGdnDims* dims, const void* q, const void* k, const v
  * dg fp32 [T, HV] (dg includes the in-chunk suffix sum).  q, k are the normalised rows the forward used.
  * Replaces the `dqkwg`, `wy_bwd` and `finalize` launches (reference: ops.py:1642-1727). */
 int mek_gdn_bwd_tail(const MekGdnDims* dims, const void* q, const void* k, const void* v, const float* beta,
-                     const float* g_cs, const void* a, const void* aqk, const void* h_tape, const void* dh_tape,
-                     const void* v_new, const void* dv_new, const void* d_o, const void* q_raw, const void* k_raw,
-                     const float* rstd_q, const float* rstd_k, void* dq, void* dk, void* dv, float* dbeta, float* dg,
-                     int32_t* status, void* stream);
+                     const float* g_cs, const void* a, const void* aqk, const void* w, const void* u,
+                     const void* h_tape, const void* dh_tape, const void* v_new, const void* dv_new, const void* d_o,
+                     const void* q_raw, const void* k_raw, const float* rstd_q, const float* rstd_k, void* dq,
+                     void* dk, void* dv, float* dbeta, float* dg, int32_t* status, void* stream);
 
 /* Forward of the gated delta rule without any device allocation: o bf16 [T, HV, 128] and, when final_state is not
  * NULL, the fp32 final state [N, HV, 128, 128], from q, k (normalised), v, beta, the raw gate g and an optional h0.

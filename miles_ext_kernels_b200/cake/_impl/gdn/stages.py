@@ -156,7 +156,7 @@ def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want
     dv = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
     dbeta = torch.empty((T, HV), dtype=F32, device=device)
     dg = torch.empty((T, HV), dtype=F32, device=device)
-    native.launch("gdn_bwd_tail", dims, tape.qn, tape.kn, tape.v, tape.beta32, tape.g_cs, tape.a, tape.aqk, tape.h,
-                  dh_tape, tape.v_new, dv_new, do, tape.q_raw, tape.k_raw, tape.rstd_q, tape.rstd_k, dq, dk, dv,
+    native.launch("gdn_bwd_tail", dims, tape.qn, tape.kn, tape.v, tape.beta32, tape.g_cs, tape.a, tape.aqk, tape.w, tape.u,
+                  tape.h, dh_tape, tape.v_new, dv_new, do, tape.q_raw, tape.k_raw, tape.rstd_q, tape.rstd_k, dq, dk, dv,
                   dbeta, dg, tape.status, device=device)
     return dq, dk, dv, dg, dbeta, dh0, dh_tape, dv_new

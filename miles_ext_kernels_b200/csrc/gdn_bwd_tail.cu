@@ -9,7 +9,8 @@
 //   dAqk = tril(do v_new^T); dS = bf16(scale dAqk D);           D_ij = 2^{G_i - G_j}, j <= i
 //   dq  += dS k + do_g h^T;  dk += dS^T q + rowscale (v_new dh^T)
 //   dw   = bf16(-dv_new h^T); dkb = A^T dw; dvb = A^T dv_new;  dv = bf16(beta dvb)
-//   dk  += beta 2^G dkb;  dA = bf16(dw kb^T + dv_new vb^T);  dL = bf16(-tril(A^T dA A^T, -1))
+//   dk  += beta 2^G dkb;  dL = bf16(-tril(A^T dA A^T, -1)) with dA = dw kb^T + dv_new vb^T, evaluated as
+//          A^T dA A^T = dkb (A kb)^T + dvb (A vb)^T = bf16(dkb) w^T + bf16(dvb) u^T   (w, u: the forward's tapes)
 //   dk  += bf16(beta dL D) k + bf16(beta dL D)^T k
 //   dbeta, dg: row sums of the products above; the chunk-end term gamma sum(dh h) + sum(dkh k) lands on the chunk's
 //   last token before the suffix sum.
@@ -22,24 +23,25 @@ namespace mek {
 struct TailSmem {
   static constexpr uint32_t kQK = 0;                   // 2 x {[64][128] q, [64][128] k}: one buffer per (chunk, key head)
   static constexpr uint32_t kQKStride = 32768;
-  static constexpr uint32_t kH = 2 * kQKStride;        // [128][128] h_tape; later DW at +0, KB at +16384
-  static constexpr uint32_t kDH = kH + 32768;          // [128][128] dh_tape; later VB at +0
-  static constexpr uint32_t kDO = kDH + 32768;         // [64][128] do -> do_g in place
-  static constexpr uint32_t kVN = kDO + 16384;         // [64][128] v_new, then this value head's raw v
-  static constexpr uint32_t kDVN = kVN + 16384;        // [64][128] dv_new
-  static constexpr uint32_t kA = kDVN + 16384;         // [64][64] A
+  static constexpr uint32_t kH = 2 * kQKStride;        // [128][128] h_tape; after phase A: dw at +0
+  static constexpr uint32_t kDH = kH + 32768;          // [128][128] dh_tape
+  static constexpr uint32_t kDO = kDH + 32768;         // [64][128] do; after phase A: u
+  static constexpr uint32_t kVN = kDO + 16384;         // [64][128] v_new; after phase A: w
+  static constexpr uint32_t kDVN = kVN + 16384;        // [64][128] dv_new; after phase A: bf16(dkb)
+  static constexpr uint32_t kV = kDVN + 16384;         // [64][128] v; after phase A: bf16(dvb)
+  static constexpr uint32_t kA = kV + 16384;           // [64][64] A
   static constexpr uint32_t kAqk = kA + 8192;          // [64][64] Aqk
-  static constexpr uint32_t kB8a = kAqk + 8192;        // [64][64] dS -> dA -> bf16(beta dL D)
-  static constexpr uint32_t kB8b = kB8a + 8192;        // [64][64] X = A^T dA
-  static constexpr uint32_t kScal = kB8b + 8192;       // floats: beta[2][64], g2[2][64], cs[2][4][64], red[2][64],
-                                                       //         red2[4][64], warp[8]   (red is [4][64] too)
+  static constexpr uint32_t kB8 = kAqk + 8192;         // [64][64] dS, then bf16(beta dL D)
+  static constexpr uint32_t kScal = kB8 + 8192;        // floats: beta[2][64], g2[2][64], cs[2][4][64], red[4][64],
+                                                       //         red2[4][64], warp[8]
   static constexpr uint32_t kBytes = kScal + (2 * 64 * 2 + 2 * 4 * 64 + 8 * 64 + 16) * 4;
 };
 
 // Tensor-memory columns.  A [64 x 128] accumulator takes 64 columns: its logical columns 0..63 sit in lanes 0..15 of
 // each quadrant and 64..127 in lanes 16..31 (two N = 64 instructions), so every lane of a warp owns a row piece.
 // [64 x 64] accumulators (Ta, Tb) are not split: lanes 0..15 only.
-constexpr uint32_t kColDQ = 0, kColDK = 64, kColT0 = 128, kColT1 = 192, kColTa = 256, kColTb = 320;
+constexpr uint32_t kColDQ = 0, kColDK = 64, kColT0 = 128, kColT1 = 192, kColT2 = 256, kColT3 = 320, kColTa = 384,
+                   kColTb = 448;
 constexpr uint32_t kUpperLanes = 16u << 16;
 
 template <int N>
@@ -48,12 +50,18 @@ __device__ __forceinline__ void cp_async_wait_pending() {
 }
 
 // One persistent CTA per SM walks (chunk, key head) pairs; inside a pair it walks the value heads of the group.
-// While one value head computes, the next one's tiles arrive by cp.async in the buffers the current one has
-// finished with (q / k of the next pair are double-buffered).
+// Per value head, three waited tensor-core phases:
+//   A  (needs only loaded tiles)  dAqk = do v_new^T, dkh = v_new dh^T, dq2 = do h^T, dw = -dv_new h^T, dvb = A^T dv_new
+//   B  (needs dS, dw)             dq += dS k, dk += dS^T q, dkb = A^T dw
+//   C  (needs dkb, dvb)           Y = bf16(dkb) w^T + bf16(dvb) u^T, KK = k k^T
+// and a fourth that nobody waits for until the pair ends: dk += bf16(beta dL D) k + bf16(beta dL D)^T k.
+// While one value head computes, the next one's tiles arrive by cp.async in the buffers the current one has finished
+// with (q / k of the next pair are double-buffered).
 __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
     const float* __restrict__ beta, const float* __restrict__ g_cs, const __nv_bfloat16* __restrict__ a_in,
-    const __nv_bfloat16* __restrict__ aqk_in, const __nv_bfloat16* __restrict__ h_tape,
+    const __nv_bfloat16* __restrict__ aqk_in, const __nv_bfloat16* __restrict__ w_in,
+    const __nv_bfloat16* __restrict__ u_in, const __nv_bfloat16* __restrict__ h_tape,
     const __nv_bfloat16* __restrict__ dh_tape, const __nv_bfloat16* __restrict__ v_new,
     const __nv_bfloat16* __restrict__ dv_new, const __nv_bfloat16* __restrict__ d_o,
     const __nv_bfloat16* __restrict__ q_raw, const __nv_bfloat16* __restrict__ k_raw,
@@ -74,9 +82,10 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
   // A 64-wide accumulator lives in lanes 0..15 only and is split in two by the warpgroup.
   const int quad = warp & 3, ch = warp >> 2, lh = lane >> 4;
   const int row = quad * 16 + (lane & 15);
-  const bool owner = lane < 16;       // holds a piece of the 64-wide accumulators
-  const int cq = lh * 2 + ch;         // which 32-column quarter of a 128-wide accumulator
-  const int lcol = lh * 64 + ch * 32; // its first logical column
+  const bool owner = lane < 16;        // holds a piece of the 64-wide accumulators
+  const int cq = lh * 2 + ch;          // which 32-column quarter of a 128-wide accumulator
+  const int lcol = lh * 64 + ch * 32;  // its first logical column
+  const int lchunk = lcol >> 3;        // ... as a 16-byte chunk index of a tile row
 
   float* s_beta = reinterpret_cast<float*>(sm + TailSmem::kScal);  // [2][64]
   float* s_g2 = s_beta + 128;                                      // [2][64]
@@ -97,7 +106,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
 
   // a pair is live when it exists and its chunk is not a pad chunk of a device-built table (pads come last)
   auto pair_live = [&](int p) { return p < num_pairs && chunk_len[p / num_qk_heads] > 0; };
-  // ---- asynchronous loads of one work item (pair p, group index gi) ------------------------------------------------
+  // ---- asynchronous loads --------------------------------------------------------------------------------------
   auto load_qk = [&](int p, int buf) {
     const int c = p / num_qk_heads, hq = p % num_qk_heads;
     const int start = chunk_start[c], len = chunk_len[c];
@@ -146,6 +155,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     load_rows(TailSmem::kDO, d_o, it);
     load_rows(TailSmem::kVN, v_new, it);
     load_rows(TailSmem::kDVN, dv_new, it);
+    load_rows(TailSmem::kV, v, it);
     load_states(it);
     load_a(it);
     cp_async_commit();
@@ -155,12 +165,12 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
   const Operand op_h{sbase + TailSmem::kH, 16384}, op_dh{sbase + TailSmem::kDH, 16384};
-  const Operand op_dw{sbase + TailSmem::kH, 8192}, op_kb{sbase + TailSmem::kH + 16384, 8192};
-  const Operand op_vb{sbase + TailSmem::kDH, 8192};
+  const Operand op_dw{sbase + TailSmem::kH, 8192};
   const Operand op_do{sbase + TailSmem::kDO, 8192}, op_vn{sbase + TailSmem::kVN, 8192};
-  const Operand op_dvn{sbase + TailSmem::kDVN, 8192};
-  const Operand op_a{sbase + TailSmem::kA, 8192}, op_b8a{sbase + TailSmem::kB8a, 8192};
-  const Operand op_b8b{sbase + TailSmem::kB8b, 8192};
+  const Operand op_u{sbase + TailSmem::kDO, 8192}, op_w{sbase + TailSmem::kVN, 8192};
+  const Operand op_dvn{sbase + TailSmem::kDVN, 8192}, op_dkb{sbase + TailSmem::kDVN, 8192};
+  const Operand op_dvb{sbase + TailSmem::kV, 8192};
+  const Operand op_a{sbase + TailSmem::kA, 8192}, op_b8{sbase + TailSmem::kB8, 8192};
 
   uint32_t phase = 0;
   auto mma_wait = [&]() {
@@ -193,18 +203,21 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     }
   };
 
-  float dk_reg[32];  // scaled dk terms of this thread's (row, 32-column quarter), summed over the group
+  // scaled terms of this thread's (row, 32-column quarter) that cannot accumulate in tensor memory, summed over the
+  // group: dq gets qscale (do h^T); dk gets rowscale (v_new dh^T) and beta 2^G dkb
+  float dq_reg[32], dk_reg[32];
   int item_parity = 0, qk_buf = 0;
   bool aborted = false;
   for (; pair_live(pair) && !aborted; pair += gridDim.x, qk_buf ^= 1) {
     const int hq = pair % num_qk_heads;
     const uint32_t qk_base = sbase + TailSmem::kQK + qk_buf * TailSmem::kQKStride;
-    uint8_t* k_tile = sm + TailSmem::kQK + qk_buf * TailSmem::kQKStride + 16384;
+    uint8_t* q_tile = sm + TailSmem::kQK + qk_buf * TailSmem::kQKStride;
+    uint8_t* k_tile = q_tile + 16384;
     const Operand op_q{qk_base, 8192}, op_k{qk_base + 16384, 8192};
     const int next_pair = pair + gridDim.x;
     const bool has_next_pair = pair_live(next_pair);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) dk_reg[j] = 0.f;
+    for (int j = 0; j < 32; ++j) dq_reg[j] = dk_reg[j] = 0.f;
 
     for (int gi = 0; gi < group; ++gi, item_parity ^= 1) {
       const Item it = item_of(pair, gi);
@@ -227,10 +240,13 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
         cp_async_commit();
       }
 
-      // ---- phase 1: dAqk = do v_new^T ; dkh = v_new dh^T --------------------------------------------------------
+      // ---- phase A: everything that needs only loaded tiles -------------------------------------------------------
       if (tid == 0) {
-        umma_gemm<64, 64>(tmem + kColTa, op_do, false, op_vn, false, 128, false);
-        gemm128(kColT0, op_vn, false, op_dh, false, 128, false);
+        umma_gemm<64, 64>(tmem + kColTa, op_do, false, op_vn, false, 128, false);   // dAqk = do v_new^T
+        gemm128(kColT0, op_vn, false, op_dh, false, 128, false);                    // dkh  = v_new dh^T
+        gemm128(kColT2, op_do, false, op_h, false, 128, false);                     // dq2  = do h^T
+        gemm128(kColT1, op_dvn, false, op_h, false, 128, false, /*neg_a=*/true);    // dw   = -dv_new h^T
+        gemm128(kColT3, op_a, true, op_dvn, true, 64, false);                       // dvb  = A^T dv_new
         umma_commit(&bar);
       }
       // meanwhile: sum(dh . h) over the whole state tile
@@ -245,10 +261,12 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       const float gi_row = g2[row], beta_row = beta_s[row];
       const float g_last = g2[len - 1];
       const float rs_row = fast_exp2(g_last - gi_row);
+      const float eg = fast_exp2(gi_row), qs_row = scale * eg, sk = beta_row * eg;
       float dG = 0.f, dB = 0.f, gdot = 0.f;
       mma_wait();
+      __syncthreads();  // every thread is past its reads of h / dh: epilogue A overwrites operand buffers
       {
-        // dAqk piece: 32 columns
+        // dAqk piece (lanes 0..15): dS, P = dAqk . Aqk
         float s[32];
         tmem_ld32(tmem_addr(tmem, warp, kColTa + ch * 32), s);
         tmem_ld_wait();
@@ -262,192 +280,118 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
             const int col = ch * 32 + jj * 8 + e;
             const float d = col <= row ? s[jj * 8 + e] : 0.f;
             ds[e] = col <= row ? scale * d * fast_exp2(gi_row - g2[col]) : 0.f;
-            s[jj * 8 + e] = d * aq[e];  // P = dAqk . Aqk
+            s[jj * 8 + e] = d * aq[e];
             rowsum += s[jj * 8 + e];
           }
-          if (owner) set_tile_chunk(sm + TailSmem::kB8a, 8192, row, ch * 4 + jj, pack8(ds));
+          if (owner) set_tile_chunk(sm + TailSmem::kB8, 8192, row, ch * 4 + jj, pack8(ds));
         }
         if (owner) dG += rowsum;
         publish_column_sums(s, s_cs);
-        // dkh piece: 32 columns
-        float dot = 0.f;
-        float d[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), d);
+      }
+      {
+        // dkh and dq2 pieces: the scaled terms go to the register accumulators, their row dots to the gate gradient
+        float a[32], b[32];
+        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), a);
+        tmem_ld32(tmem_addr(tmem, warp, kColT2 + ch * 32), b);
         tmem_ld_wait();
+        float dot_k = 0.f, dot_q = 0.f;
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
-          float kk[8];
-          unpack8(tile_chunk(k_tile, 8192, row, (lcol >> 3) + jj), kk);
+          float kk[8], qq[8];
+          unpack8(tile_chunk(k_tile, 8192, row, lchunk + jj), kk);
+          unpack8(tile_chunk(q_tile, 8192, row, lchunk + jj), qq);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const float x = rs_row * d[jj * 8 + e];
-            dot = fmaf(x, kk[e], dot);
+            const float x = rs_row * a[jj * 8 + e], y = qs_row * b[jj * 8 + e];
+            dot_k = fmaf(x, kk[e], dot_k);
+            dot_q = fmaf(y, qq[e], dot_q);
             dk_reg[jj * 8 + e] += x;
+            dq_reg[jj * 8 + e] += y;
           }
         }
-        dG -= dot;
-        gdot += dot;
+        dG += dot_q - dot_k;
+        gdot += dot_k;
       }
-      // do -> do_g = bf16(qscale do), in place (phase 1 has read do)
-      for (int i = tid; i < 64 * 16; i += 256) {
-        const int r = i >> 4, cc = i & 15;
-        const float qs = scale * fast_exp2(g2[r]);
-        float x[8];
-        unpack8(tile_chunk(sm + TailSmem::kDO, 8192, r, cc), x);
+      {
+        // dw -> its tile (the h region); dvb -> dv, dbeta, and its tile (the v buffer, read first)
+        float wv[32], y[32];
+        tmem_ld32(tmem_addr(tmem, warp, kColT1 + ch * 32), wv);
+        tmem_ld32(tmem_addr(tmem, warp, kColT3 + ch * 32), y);
+        tmem_ld_wait();
+        float dot_v = 0.f;
+        __nv_bfloat16* dv_row = dv + int64_t(start + row) * v_stride + hv * kDim + lcol;
+        uint4 vraw[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] *= qs;
-        set_tile_chunk(sm + TailSmem::kDO, 8192, r, cc, pack8(x));
+        for (int jj = 0; jj < 4; ++jj) vraw[jj] = tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj);
+        __syncwarp();
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          float vv[8], out[8];
+          unpack8(vraw[jj], vv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            dot_v = fmaf(y[jj * 8 + e], vv[e], dot_v);
+            out[e] = y[jj * 8 + e] * beta_row;
+          }
+          if (live) reinterpret_cast<uint4*>(dv_row)[jj] = pack8(out);
+          set_tile_chunk(sm + TailSmem::kH, 8192, row, lchunk + jj, pack8(wv + jj * 8));
+        }
+        dB += dot_v;
+        // every thread reads only its own (row, chunk) cells of the v tile and rewrites exactly those with dvb
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) set_tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj, pack8(y + jj * 8));
       }
       stage_sync();
-      // v_new and Aqk are done with: this value head's raw v comes into the v_new buffer, the next item's Aqk and
-      // scalars into theirs
-      {
-        Item cur = it;
-        load_rows(TailSmem::kVN, v, cur);
+      {  // do and v_new are done with: this value head's u and w take their buffers; then the next item's Aqk
+        load_rows(TailSmem::kDO, u_in, it);
+        load_rows(TailSmem::kVN, w_in, it);
         cp_async_commit();
         if (has_next) load_scalars_aqk(nx, item_parity ^ 1);
         cp_async_commit();
       }
 
-      // ---- phase 2: dq += dS k + do_g h^T ; dk += dS^T q ; qh = q h ; dw = -dv_new h^T --------------------------
+      // ---- phase B: dq += dS k ; dk += dS^T q ; dkb = A^T dw ---------------------------------------------------------
       if (tid == 0) {
-        gemm128(kColDQ, op_b8a, false, op_k, true, 64, gi > 0);
-        gemm128(kColDQ, op_do, false, op_h, false, 128, true);
-        gemm128(kColDK, op_b8a, true, op_q, true, 64, gi > 0);
-        gemm128(kColT0, op_q, false, op_h, true, 128, false);
-        gemm128(kColT1, op_dvn, false, op_h, false, 128, false, /*neg_a=*/true);
+        gemm128(kColDQ, op_b8, false, op_k, true, 64, gi > 0);
+        gemm128(kColDK, op_b8, true, op_q, true, 64, gi > 0);
+        gemm128(kColT0, op_a, true, op_dw, true, 64, false);
         umma_commit(&bar);
       }
       if (owner && ch == 0) dG -= s_cs[row] + s_cs[64 + row] + s_cs[128 + row] + s_cs[192 + row];
       mma_wait();
       {
-        float dot = 0.f;
-        float qh[32], dw[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), qh);
-        tmem_ld32(tmem_addr(tmem, warp, kColT1 + ch * 32), dw);
-        tmem_ld_wait();
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          float dog[8];
-          unpack8(tile_chunk(sm + TailSmem::kDO, 8192, row, (lcol >> 3) + jj), dog);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(dog[e], qh[jj * 8 + e], dot);
-          // h has been read by phase 2: its first half becomes the dw tile
-          set_tile_chunk(sm + TailSmem::kH, 8192, row, (lcol >> 3) + jj, pack8(dw + jj * 8));
-        }
-        dG += dot;
-      }
-      cp_async_wait_pending<1>();  // this value head's raw v has landed (the next item's Aqk group may be in flight)
-      __syncthreads();
-      // kb = bf16(beta 2^G k) -> second half of the h region; vb = bf16(beta v) -> the dh region
-      for (int i = tid; i < 64 * 16; i += 256) {
-        const int r = i >> 4, cc = i & 15;
-        const float b = beta_s[r], sc = b * fast_exp2(g2[r]);
-        float x[8];
-        unpack8(tile_chunk(k_tile, 8192, r, cc), x);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] *= sc;
-        set_tile_chunk(sm + TailSmem::kH + 16384, 8192, r, cc, pack8(x));
-        unpack8(tile_chunk(sm + TailSmem::kVN, 8192, r, cc), x);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] *= b;
-        set_tile_chunk(sm + TailSmem::kDH, 8192, r, cc, pack8(x));
-      }
-      stage_sync();
-      if (has_next) {  // do_g is done with
-        load_rows(TailSmem::kDO, d_o, nx);
-        cp_async_commit();
-      }
-
-      // ---- phase 3: dkb = A^T dw ; dA = dw kb^T + dv_new vb^T ----------------------------------------------------
-      if (tid == 0) {
-        gemm128(kColT0, op_a, true, op_dw, true, 64, false);
-        umma_gemm<64, 64>(tmem + kColTa, op_dw, false, op_kb, false, 128, false);
-        umma_gemm<64, 64>(tmem + kColTa, op_dvn, false, op_vb, false, 128, true);
-        umma_commit(&bar);
-      }
-      mma_wait();
-      const float eg = fast_exp2(gi_row), sk = beta_row * eg;
-      {
-        float dot_k = 0.f, dot_kb = 0.f;
         float dkb[32];
         tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), dkb);
         tmem_ld_wait();
+        float dot_k = 0.f, dot_kb = 0.f;
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
-          float kk[8], kb[8];
-          unpack8(tile_chunk(k_tile, 8192, row, (lcol >> 3) + jj), kk);
-          unpack8(tile_chunk(sm + TailSmem::kH + 16384, 8192, row, (lcol >> 3) + jj), kb);
+          float kk[8];
+          unpack8(tile_chunk(k_tile, 8192, row, lchunk + jj), kk);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const float x = dkb[jj * 8 + e];
             dot_k = fmaf(x, kk[e], dot_k);
-            dot_kb = fmaf(x, kb[e], dot_kb);
+            dot_kb = fmaf(x, round_bf16(kk[e] * sk), dot_kb);  // kb = bf16(beta 2^G k), the forward's operand
             dk_reg[jj * 8 + e] = fmaf(sk, x, dk_reg[jj * 8 + e]);
           }
+          set_tile_chunk(sm + TailSmem::kDVN, 8192, row, lchunk + jj, pack8(dkb + jj * 8));  // dv_new is done with
         }
         dB += eg * dot_k;
         dG += dot_kb;
-        float s[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColTa + ch * 32), s);
-        tmem_ld_wait();
-        if (owner) {
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj)
-            set_tile_chunk(sm + TailSmem::kB8a, 8192, row, ch * 4 + jj, pack8(s + jj * 8));
-        }
       }
+      cp_async_wait_pending<1>();  // u and w have landed (the next item's Aqk group may be in flight)
       stage_sync();
-      if (has_next) {  // dw, kb (h region) and vb (dh region) are done with
+      if (has_next) {  // h / dh (and the dw tile) and A are done with
         load_states(nx);
+        load_a(nx);
         cp_async_commit();
       }
 
-      // ---- phase 4: X = A^T dA ; dvb = A^T dv_new ----------------------------------------------------------------
+      // ---- phase C: Y = bf16(dkb) w^T + bf16(dvb) u^T ; KK = k k^T ---------------------------------------------------
       if (tid == 0) {
-        umma_gemm<64, 64>(tmem + kColTb, op_a, true, op_b8a, true, 64, false);
-        gemm128(kColT0, op_a, true, op_dvn, true, 64, false);
-        umma_commit(&bar);
-      }
-      mma_wait();
-      {
-        float s[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColTb + ch * 32), s);
-        tmem_ld_wait();
-        if (owner) {
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj)
-            set_tile_chunk(sm + TailSmem::kB8b, 8192, row, ch * 4 + jj, pack8(s + jj * 8));
-        }
-        float dot_v = 0.f;
-        __nv_bfloat16* dv_row = dv + int64_t(start + row) * v_stride + hv * kDim + lcol;
-        float dvb[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), dvb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          float vv[8], out[8];
-          unpack8(tile_chunk(sm + TailSmem::kVN, 8192, row, (lcol >> 3) + jj), vv);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float y = dvb[jj * 8 + e];
-            dot_v = fmaf(y, vv[e], dot_v);
-            out[e] = y * beta_row;
-          }
-          if (live) reinterpret_cast<uint4*>(dv_row)[jj] = pack8(out);
-        }
-        dB += dot_v;
-      }
-      stage_sync();
-      if (has_next) {  // raw v and dv_new are done with
-        load_rows(TailSmem::kVN, v_new, nx);
-        load_rows(TailSmem::kDVN, dv_new, nx);
-        cp_async_commit();
-      }
-
-      // ---- phase 5: Y = X A^T ; KK = k k^T ; dL = bf16(-tril(Y, -1)) ---------------------------------------------
-      if (tid == 0) {
-        umma_gemm<64, 64>(tmem + kColTa, op_b8b, false, op_a, false, 64, false);
+        umma_gemm<64, 64>(tmem + kColTa, op_dkb, false, op_w, false, 128, false);
+        umma_gemm<64, 64>(tmem + kColTa, op_dvb, false, op_u, false, 128, true);
         umma_gemm<64, 64>(tmem + kColTb, op_k, false, op_k, false, 128, false);
         umma_commit(&bar);
       }
@@ -472,7 +416,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
             s[jj * 8 + e] = out[e] * kij;  // dL . L
             rowsum += s[jj * 8 + e];
           }
-          if (owner) set_tile_chunk(sm + TailSmem::kB8a, 8192, row, ch * 4 + jj, pack8(out));
+          if (owner) set_tile_chunk(sm + TailSmem::kB8, 8192, row, ch * 4 + jj, pack8(out));
         }
         if (owner) {
           dB += dot;
@@ -481,19 +425,22 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
         publish_column_sums(s, s_cs + 256);
       }
       stage_sync();
-      if (has_next) {  // A is done with
-        load_a(nx);
+      if (has_next) {  // w, u, bf16(dkb), bf16(dvb) are done with
+        load_rows(TailSmem::kDO, d_o, nx);
+        load_rows(TailSmem::kVN, v_new, nx);
+        load_rows(TailSmem::kDVN, dv_new, nx);
+        load_rows(TailSmem::kV, v, nx);
         cp_async_commit();
       }
 
-      // ---- phase 6: dk += bf16(beta dL D) k + bf16(beta dL D)^T k ------------------------------------------------
+      // ---- phase D: dk += bf16(beta dL D) k + bf16(beta dL D)^T k ------------------------------------------------
       if (tid == 0) {
-        gemm128(kColDK, op_b8a, false, op_k, true, 64, true);
-        gemm128(kColDK, op_b8a, true, op_k, true, 64, true);
+        gemm128(kColDK, op_b8, false, op_k, true, 64, true);
+        gemm128(kColDK, op_b8, true, op_k, true, 64, true);
         if (last_of_pair) umma_commit(&bar);  // otherwise the next item's first commit covers these too
       }
       if (owner && ch == 0) dG -= s_cs[256 + row] + s_cs[320 + row] + s_cs[384 + row] + s_cs[448 + row];
-      // gate and beta gradients of this value head: combine the column halves, add the chunk-end term, suffix sum
+      // gate and beta gradients of this value head: combine the column quarters, add the chunk-end term, suffix sum
       float part = fmaf(fast_exp2(g_last), hdh, gdot);
 #pragma unroll
       for (int m = 16; m >= 1; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
@@ -522,7 +469,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
         mma_wait();
         const int64_t tok = int64_t(start + row) * qk_stride + hq * kDim + lcol;
         // acc: this thread's 32 columns of the fp32 group sum.  With the op's L2 norm: dx = r (D - y (D . y)),
-        // y = x r from the raw row and the saved r; the dot product spans both column halves.
+        // y = x r from the raw row and the saved r; the dot product spans the four column quarters.
         auto finish = [&](float* acc, const __nv_bfloat16* raw_rows, const float* rstd, __nv_bfloat16* out) {
           if (rstd != nullptr) {
             const float r = live ? rstd[int64_t(start + row) * num_qk_heads + hq] : 0.f;
@@ -539,7 +486,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
                 dot = fmaf(acc[jj * 8 + e], y[jj * 8 + e], dot);
               }
             }
-            __syncthreads();  // the gate reduction above has read s_red
+            __syncthreads();  // the previous reduction has read s_red
             s_red[cq * 64 + row] = dot;
             __syncthreads();
             dot = (s_red[row] + s_red[64 + row]) + (s_red[128 + row] + s_red[192 + row]);
@@ -552,11 +499,13 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
           }
         };
         {
-          float dqv[32];
-          tmem_ld32(tmem_addr(tmem, warp, kColDQ + ch * 32), dqv);
+          float b[32];
+          tmem_ld32(tmem_addr(tmem, warp, kColDQ + ch * 32), b);
           tmem_ld_wait();
-          finish(dqv, q_raw, rstd_q, dq);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) dq_reg[j] += b[j];
         }
+        finish(dq_reg, q_raw, rstd_q, dq);
         {
           float b[32];
           tmem_ld32(tmem_addr(tmem, warp, kColDK + ch * 32), b);
@@ -578,10 +527,11 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
 }  // namespace mek
 
 extern "C" int mek_gdn_bwd_tail(const MekGdnDims* d, const void* q, const void* k, const void* v, const float* beta,
-                                const float* g_cs, const void* a, const void* aqk, const void* h_tape,
-                                const void* dh_tape, const void* v_new, const void* dv_new, const void* d_o,
-                                const void* q_raw, const void* k_raw, const float* rstd_q, const float* rstd_k,
-                                void* dq, void* dk, void* dv, float* dbeta, float* dg, int32_t* status, void* stream) {
+                                const float* g_cs, const void* a, const void* aqk, const void* w, const void* u,
+                                const void* h_tape, const void* dh_tape, const void* v_new, const void* dv_new,
+                                const void* d_o, const void* q_raw, const void* k_raw, const float* rstd_q,
+                                const float* rstd_k, void* dq, void* dk, void* dv, float* dbeta, float* dg,
+                                int32_t* status, void* stream) {
   using namespace mek;
   if (d == nullptr || d->num_chunks <= 0 || d->num_v_heads <= 0 || d->num_qk_heads <= 0 ||
       d->num_v_heads % d->num_qk_heads != 0)
@@ -601,8 +551,8 @@ extern "C" int mek_gdn_bwd_tail(const MekGdnDims* d, const void* q, const void* 
   }
   const int pairs = d->num_chunks * d->num_qk_heads;
   gdn_bwd_tail_kernel<<<pairs < sms ? pairs : sms, 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      In(q), In(k), In(v), beta, g_cs, In(a), In(aqk), In(h_tape), In(dh_tape), In(v_new), In(dv_new), In(d_o),
-      In(q_raw), In(k_raw), rstd_q, rstd_k, Out(dq), Out(dk), Out(dv), dbeta, dg, d->chunk_start, d->chunk_len,
-      d->num_chunks, d->num_qk_heads, d->num_v_heads, d->scale, status);
+      In(q), In(k), In(v), beta, g_cs, In(a), In(aqk), In(w), In(u), In(h_tape), In(dh_tape), In(v_new), In(dv_new),
+      In(d_o), In(q_raw), In(k_raw), rstd_q, rstd_k, Out(dq), Out(dk), Out(dv), dbeta, dg, d->chunk_start,
+      d->chunk_len, d->num_chunks, d->num_qk_heads, d->num_v_heads, d->scale, status);
   return launched("bwd_tail");
 }
