@@ -38,7 +38,7 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-METRIC = "gdn_fwd_bwd_tokens_per_sec"
+METRIC = "gdn_fwd_bwd_tokens_per_sec"  # on a KDA workload the same metric of the per-channel-decay variant
 UNIT = "tokens/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -116,8 +116,13 @@ def cpu_tokens_per_sec(workload_name: str, sample_tokens: int, steps: int, warmu
     args = [flat(t) for t in (work.q, work.k, work.v, work.g, work.beta)]
 
     def step():
-        oracle.chunked_forward_backward(*args, seq_lens, flat(work.do), h0=work.h0, dht=work.dht,
-                                        output_final_state=work.config.final_state)
+        if work.config.op == "kda":
+            from oracle import kda_oracle
+
+            kda_oracle.chunked_forward_backward(*args, seq_lens, flat(work.do))
+        else:
+            oracle.chunked_forward_backward(*args, seq_lens, flat(work.do), h0=work.h0, dht=work.dht,
+                                            output_final_state=work.config.final_state)
 
     for _ in range(warmup):
         step()
@@ -167,6 +172,17 @@ KERNEL_BYTES = {
     "gdn_bwd_tail": lambda H, HV: 2 * 256 * H + (256 + 8 + 2 * 128 + 2 * 512 + 3 * 256) * HV + 2 * 256 * H
     + (256 + 8) * HV,
 }
+KERNEL_BYTES.update({
+    # KDA (H = HV): g, G and dg are [., 128] fp32 per head
+    "kda_prep": lambda H, HV: (2 * 256 + 512 + 512 + 3 * 256 + 8) * HV,
+    "kda_intra": lambda H, HV: (4 * 256 + 512 + 4 + 2 * 128 + 2 * 256) * HV,
+    "kda_fwd_h": lambda H, HV: (3 * 256 + 8 + 512 + 256) * HV,
+    "kda_fwd_o": lambda H, HV: (256 + 128 + 256 + 512 + 256) * HV,
+    "kda_bwd_dh": lambda H, HV: (4 * 256 + 128 + 8 + 512 + 256) * HV,
+    "kda_bwd_tail": lambda H, HV: (4 * 256 + 512 + 4 + 128 + 2 * 512 + 3 * 256 + 2 * 2 * 256 + 3 * 2 * 512 + 16
+                                   + 2 * 512 + 256 + 512 + 4) * HV,
+    "qk_grad_finish": lambda H, HV: (512 + 256) * HV,
+})
 KERNEL_FLOPS = {  # per (chunk, value head): dense contractions as 2 m n k
     "gdn_wy_fwd": 2 * 128 * 64 * 128 + 2 * 64**3 / 3 + 2 * 2 * 64 * 128 * 64,
     "gdn_fwd_h": 2 * 64 * 128 * 128 + 2 * 128 * 128 * 64,
@@ -181,7 +197,7 @@ def run_ours(args) -> None:
     import torch.distributed as dist
 
     import miles_ext_kernels_b200 as package
-    from miles_ext_kernels_b200.cake import gdn
+    from miles_ext_kernels_b200.cake import gdn, kda
     from miles_ext_kernels_b200.cake._impl.gdn import native
     from miles_ext_kernels_b200.workloads import bytes_per_token, flops_per_token, make_workload
 
@@ -196,7 +212,7 @@ def run_ours(args) -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
     package.configure(cake_gdn_variant="det")
-    gdn.chunk_gated_delta_rule  # noqa: B018  import the implementation (and the native library) before timing
+    gdn.chunk_gated_delta_rule, kda.chunk_kda  # noqa: B018  import the implementations before timing
 
     work = make_workload(args.workload, tokens=args.tokens)
     cfg = work.config
@@ -212,9 +228,12 @@ def run_ours(args) -> None:
         q, k, v = (t[n].detach().requires_grad_(True) for n in ("q", "k", "v"))
         g, beta = t["g"].detach().requires_grad_(True), t["beta"].detach().requires_grad_(True)
         h0 = t["h0"].detach().requires_grad_(True) if "h0" in t else None
-        o, final = gdn.chunk_gated_delta_rule(q, k, v, g=g, beta=beta, initial_state=h0,
-                                              output_final_state=cfg.final_state, cu_seqlens=cu_dev,
-                                              cu_seqlens_cpu=work.cu_seqlens, use_qk_l2norm_in_kernel=False)
+        if cfg.op == "kda":
+            o, final = kda.chunk_kda(q, k, v, g, beta, cu_dev), None
+        else:
+            o, final = gdn.chunk_gated_delta_rule(q, k, v, g=g, beta=beta, initial_state=h0,
+                                                  output_final_state=cfg.final_state, cu_seqlens=cu_dev,
+                                                  cu_seqlens_cpu=work.cu_seqlens, use_qk_l2norm_in_kernel=False)
         if final is not None and "dht" in t:
             torch.autograd.backward([o, final], [t["do"], t["dht"]])
         else:
@@ -287,7 +306,7 @@ def run_ours(args) -> None:
     top = max(per_kernel, key=lambda n: per_kernel[n][2])
     peak, peak_kind = peaks()
     mean_ms = per_kernel[top][0]
-    gbs = KERNEL_BYTES[top](H, HV) * tokens / (mean_ms * 1e-3) / 1e9
+    gbs = KERNEL_BYTES.get(top, lambda H, HV: 0.0)(H, HV) * tokens / (mean_ms * 1e-3) / 1e9
     tiles = (tokens / 64) * HV
     tfs = KERNEL_FLOPS.get(top, 0.0) * tiles / (mean_ms * 1e-3) / 1e12
     frac_hbm, frac_tc = gbs / peak["hbm_gbs"], tfs / peak["bf16_tflops"]
@@ -300,7 +319,7 @@ def run_ours(args) -> None:
 
     step_s = ms * 1e-3 / args.steps
     t_roof = max(flops_per_token(HV) * tokens / (peak["bf16_tflops_sustained"] * 1e12),
-                 bytes_per_token(H, HV) * tokens / (peak["hbm_gbs"] * 1e9))
+                 bytes_per_token(H, HV, op=cfg.op) * tokens / (peak["hbm_gbs"] * 1e9))
     value = world * tokens / step_s
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -315,7 +334,7 @@ def run_ours(args) -> None:
         "gpu_launches": launches,
         "roofline": roofline,
         "path_roofline": {"t_roof_ms": 1e3 * t_roof, "frac": t_roof / step_s, "flops_per_token": flops_per_token(HV),
-                          "bytes_per_token": bytes_per_token(H, HV), "peak_source": f"of {peak_kind}"},
+                          "bytes_per_token": bytes_per_token(H, HV, op=cfg.op), "peak_source": f"of {peak_kind}"},
         "kernels_ms": {n: {"mean": v[0], "launches": v[1], "total": v[2]} for n, v in per_kernel.items()},
         "clocks": clocks,
     }

@@ -100,20 +100,23 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   if (warp == 0) tmem_alloc(&tmem_slot, 128);
 
   const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
-  load_tile<64, 128, 128>(sm + WySmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-  load_tile<64, 128, 128>(sm + WySmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-  load_tile<64, 128, 128>(sm + WySmem::kV, 8192, v + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+  // all three tiles in flight at once (cp.async), the scalars by plain loads meanwhile
+  const uint32_t sbase = smem_u32(sm);
+  prefetch_tile<64, 128, 128>(sbase + WySmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+  prefetch_tile<64, 128, 128>(sbase + WySmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+  prefetch_tile<64, 128, 128>(sbase + WySmem::kV, 8192, v + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+  cp_async_commit();
   if (tid < 64) {
     const int i = tid < len ? tid : len - 1;
     s_beta[tid] = tid < len ? beta[int64_t(start + i) * num_v_heads + hv] : 0.f;
     s_g2[tid] = g_cs[int64_t(start + i) * num_v_heads + hv];
   }
+  cp_async_wait_all();
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t sbase = smem_u32(sm);
 
   // q k^T -> lanes 0..15, k k^T -> lanes 16..31 of the same 64 columns
   if (tid == 0) {
@@ -448,40 +451,46 @@ __global__ void __launch_bounds__(128) gdn_fwd_o_kernel(
     mbar_init(&bar, 1);
     fence_mbar_init();
   }
-  if (warp == 0) tmem_alloc(&tmem_slot, 256);
+  if (warp == 0) tmem_alloc(&tmem_slot, 128);
   const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
   const int64_t tile = int64_t(c) * num_v_heads + hv;
-  load_tile<64, 128, 128>(sm + FwdOSmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-  load_tile<64, 128, 128>(sm + FwdOSmem::kVN, 8192, v_new + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-  load_tile<128, 128, 128>(sm + FwdOSmem::kH, 16384, h_tape + tile * 16384, 128, 128, tid);
-  load_tile<64, 64, 128>(sm + FwdOSmem::kAqk, 8192, aqk + tile * 4096, 64, 64, tid);
+  const uint32_t sbase = smem_u32(sm);
+  prefetch_tile<64, 128, 128>(sbase + FwdOSmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+  prefetch_tile<64, 128, 128>(sbase + FwdOSmem::kVN, 8192, v_new + int64_t(start) * v_stride + hv * kDim, v_stride, len,
+                              tid);
+  prefetch_tile<128, 128, 128>(sbase + FwdOSmem::kH, 16384, h_tape + tile * 16384, 128, 128, tid);
+  prefetch_tile<64, 64, 128>(sbase + FwdOSmem::kAqk, 8192, aqk + tile * 4096, 64, 64, tid);
+  cp_async_commit();
   // g_cs == nullptr: the per-channel-decay variant, whose q operand already holds q 2^G (qscale = scale)
   if (tid < 64) s_g2[tid] = g_cs ? g_cs[int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv] : 0.f;
+  cp_async_wait_all();
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t sbase = smem_u32(sm);
   if (tid == 0) {
     const Operand op_q{sbase + FwdOSmem::kQ, 8192}, op_vn{sbase + FwdOSmem::kVN, 8192};
     const Operand op_h{sbase + FwdOSmem::kH, 16384}, op_a{sbase + FwdOSmem::kAqk, 8192};
-    umma_gemm<64, 128>(tmem, op_q, false, op_h, true, 128, false);
-    umma_gemm<64, 128>(tmem + 128, op_a, false, op_vn, true, 64, false);
+    // both [64 x 128] products as two N = 64 halves: V columns 0..63 -> lanes 0..15, 64..127 -> lanes 16..31
+    umma_gemm<64, 64>(tmem, op_q, false, op_h, true, 128, false);
+    umma_gemm<64, 64>(tmem + (16u << 16), op_q, false, operand_at(op_h, 0, 1), true, 128, false);
+    umma_gemm<64, 64>(tmem + 64, op_a, false, op_vn, true, 64, false);
+    umma_gemm<64, 64>(tmem + 64 + (16u << 16), op_a, false, operand_at(op_vn, 0, 1), true, 64, false);
     umma_commit(&bar);
   }
   const bool ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0));
   tc_fence_after();
   if (ok) {
     const int i = warp * 16 + (lane & 15);
-    const bool live = lane < 16 && i < len;
+    const bool live = i < len;
     const float qs = scale * fast_exp2(s_g2[i]);
-    __nv_bfloat16* dst = o + int64_t(start + i) * v_stride + hv * kDim;
+    __nv_bfloat16* dst = o + int64_t(start + i) * v_stride + hv * kDim + (lane >> 4) * 64;
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
+    for (int p = 0; p < 2; ++p) {
       float a[32], b[32];
       tmem_ld32(tmem_addr(tmem, warp, p * 32), a);
-      tmem_ld32(tmem_addr(tmem, warp, 128 + p * 32), b);
+      tmem_ld32(tmem_addr(tmem, warp, 64 + p * 32), b);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) a[j] = fmaf(qs, a[j], b[j]);
@@ -494,7 +503,7 @@ __global__ void __launch_bounds__(128) gdn_fwd_o_kernel(
   if (!ok && tid == 0) atomicExch(status, kDevWaitTimeout | (3 << 8));
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 256);
+  if (warp == 0) tmem_dealloc(tmem, 128);
 }
 
 }  // namespace mek

@@ -116,6 +116,9 @@ def make_workload(name: str, *, tokens: int | None = None, heads: tuple[int, int
     num_seqs = len(seq_lens) if cfg.packed else B
     h0 = 0.02 * torch.randn(num_seqs, HV, d, d, generator=gen) if cfg.initial_state else None
     dht = torch.randn(num_seqs, HV, d, d, generator=gen) if cfg.initial_state else None
+    if cfg.op == "kda":  # per-key-channel gate: g [B, T, H, d] = -softplus(N(0, 1)) exp(A_log), A_log ~ U(0, ln 16)
+        a_log = torch.rand(H, generator=gen) * math.log(16.0)
+        g = -torch.nn.functional.softplus(torch.randn(B, T, H, d, generator=gen)) * torch.exp(a_log)[None, None, :, None]
     low = torch.bfloat16 if cfg.dtype == "bf16" else torch.float32
     cu = None
     if cfg.packed:

@@ -103,12 +103,11 @@ def test_cfg4_one_rank_slice_of_the_long_sequence():
 def test_cfg3_kda_full_size():
     from miles_ext_kernels_b200.cake import kda
 
-    w = make_workload("cfg3")  # one 4,096-token sequence per GPU, H = 32, per-channel gate
+    w = make_workload("cfg3")  # one 4,096-token sequence per GPU, H = 32, per-channel gate [1, T, H, 128]
     dev = torch.device("cuda")
-    gen = torch.Generator().manual_seed(3)
     T, H = w.q.shape[1], w.q.shape[2]
-    a_log = torch.rand(H, generator=gen) * 2.772588722239781  # U(0, ln 16)
-    g = -torch.nn.functional.softplus(torch.randn(T, H, 128, generator=gen)) * torch.exp(a_log)[None, :, None]
+    g = w.g[0]
+    assert g.shape == (T, H, 128)
     cu = torch.tensor((0, T), dtype=torch.int32, device=dev)
 
     def once():
