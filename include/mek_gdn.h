@@ -53,6 +53,8 @@ int mek_check_device(int device);
  *                 half of each 32-lane quadrant, sharing its columns with another M = 64 accumulator)
  *   out           device float [128 * ncols], row = tensor-memory lane
  *   status        device int32, 0 = fine
+ * With nk = 0 nothing is issued: the kernel's wait runs into its one-second limit, status becomes 1 and the kernel
+ * returns normally (tensor memory freed) -- how the tests exercise the bounded waits without faulting the GPU.
  * No counterpart in the reference (its kernels are generated and tested end to end). */
 int mek_selftest_umma(const void* a_img, int a_bytes, const void* b_img, int b_bytes, uint64_t a_desc, uint64_t b_desc,
                       const int32_t* a_off, const int32_t* b_off, int nk, uint32_t idesc, int ncols, int d_lane,

@@ -76,6 +76,15 @@ def _packed3(x: torch.Tensor, name: str) -> torch.Tensor:
     return x
 
 
+def _packed_beta(beta: torch.Tensor) -> torch.Tensor:
+    """``[1, S, H]`` -> ``[S, H]`` (``[S, H]`` passes through)."""
+    if beta.dim() == 3:
+        if beta.shape[0] != 1:
+            raise ValueError(f"chunk_kda: beta must be one packed batch [1, S, H]; got {tuple(beta.shape)}")
+        return beta[0]
+    return beta
+
+
 def _check(q, k, v, g, beta, cu_seqlens) -> None:
     for name, t in (("q", q), ("k", k), ("v", v), ("g", g), ("beta", beta), ("cu_seqlens", cu_seqlens)):
         if not isinstance(t, torch.Tensor) or not t.is_cuda:
@@ -184,7 +193,7 @@ class _ChunkKda(torch.autograd.Function):
     def forward(ctx, q, k, v, g, beta, cu_seqlens, scale, use_qk_l2norm):
         shape = q.shape
         q3, k3, v3, g3 = (_packed3(t, n).contiguous() for t, n in ((q, "q"), (k, "k"), (v, "v"), (g, "g")))
-        beta3 = _packed3(beta, "beta") if beta.dim() == 3 else beta
+        beta3 = _packed_beta(beta)
         g3 = g3 if g3.dtype == F32 else g3.float()
         _check(q3, k3, v3, g3, beta3, cu_seqlens)
         beta32 = beta3.float().contiguous()
@@ -233,7 +242,7 @@ def chunk_kda_fwd(q, k, v, g, beta, cu_seqlens, *, scale=None, save_for_backward
     with torch.no_grad():
         gate = _gate(g, use_gate_in_kernel, A_log, dt_bias, lower_bound)
         q3, k3, v3, g3 = (_packed3(t, n).contiguous() for t, n in ((q, "q"), (k, "k"), (v, "v"), (gate, "g")))
-        beta3 = _packed3(beta, "beta") if beta.dim() == 3 else beta
+        beta3 = _packed_beta(beta)
         _check(q3, k3, v3, g3, beta3, cu_seqlens)
         with torch.cuda.device(q.device):
             o, saved = _forward(q3, k3, v3, g3.float(), beta3.float().contiguous(), cu_seqlens,
@@ -254,7 +263,7 @@ def chunk_kda_bwd(q, k, v, g, beta, cu_seqlens, dout, *, saved=None, scale=None,
                                  A_log=A_log, dt_bias=dt_bias, lower_bound=lower_bound,
                                  use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel)
     v3 = _packed3(v, "v").contiguous()
-    beta3 = _packed3(beta, "beta") if beta.dim() == 3 else beta
+    beta3 = _packed_beta(beta)
     do3 = _packed3(dout, "dout").contiguous().to(BF16)
     with torch.no_grad(), torch.cuda.device(v.device):
         dq, dk, dv, dg, dbeta = _backward(saved, v3, beta3.float().contiguous(), do3)

@@ -36,7 +36,9 @@ __global__ void __launch_bounds__(128) selftest_umma_kernel(const uint4* a_img, 
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
 
-  if (tid == 0) {
+  // nk == 0: nothing is issued and nothing ever arrives on the barrier -- the wait below must run out by itself and
+  // report it (the bounded-wait path every kernel of this library relies on)
+  if (tid == 0 && nk > 0) {
     const uint32_t a0 = smem_u32(a_s), b0 = smem_u32(b_s);
     for (int k = 0; k < nk; ++k) {
       const uint64_t da = a_desc | uint64_t(((a0 + uint32_t(a_off[k])) >> 4) & 0x3FFFu);
@@ -89,8 +91,8 @@ int mek_selftest_umma(const void* a_img, int a_bytes, const void* b_img, int b_b
   using namespace mek;
   if (a_bytes <= 0 || b_bytes <= 0 || a_bytes > 65536 || b_bytes > 65536 || a_bytes % 16 || b_bytes % 16)
     return fail(MEK_ERR_INVALID, "selftest: operand images must be 16..65536 bytes, multiples of 16");
-  if (ncols < 16 || ncols > 256 || ncols % 16 || nk < 1 || nk > 64)
-    return fail(MEK_ERR_INVALID, "selftest: ncols in 16..256 (multiple of 16), nk in 1..64");
+  if (ncols < 16 || ncols > 256 || ncols % 16 || nk < 0 || nk > 64)
+    return fail(MEK_ERR_INVALID, "selftest: ncols in 16..256 (multiple of 16), nk in 0..64");
   if (d_lane != 0 && d_lane != 16) return fail(MEK_ERR_INVALID, "selftest: d_lane must be 0 or 16");
   const size_t smem = 2 * 65536 + 1024;
   if (int rc = want_smem(selftest_umma_kernel, smem, "selftest")) return rc;

@@ -144,6 +144,10 @@ def test_repeats_bit_for_bit_and_the_split_entry_points_agree():
     first, again = run(x, seq_lens), run(x, seq_lens)
     for name in NAMES:
         assert torch.equal(first[name], again[name]), name
+    batched = {n: t.unsqueeze(0) for n, t in x.items()}  # the [1, S, H, ...] form of the same call
+    lead = run(batched, seq_lens)
+    for name in NAMES:
+        assert torch.equal(lead[name][0], first[name]), name
     dev = torch.device("cuda")
     d = {n: t.to(dev) for n, t in x.items()}
     cu = torch.tensor((0, 100, 160), dtype=torch.int32, device=dev)

@@ -87,3 +87,32 @@ def test_m64_accumulator_in_the_upper_half_lanes(name):
     got, want = run_case(lib, *CASES[name], d_lane=16)
     err = np.abs(got - want).max()
     assert err <= 1e-3 * max(1.0, np.abs(want).max()), f"{name}: max error {err}"
+
+
+@pytest.mark.gpu
+def test_a_wait_that_nothing_satisfies_runs_out_and_reports_it():
+    """Failure detection without a fault: no MMA is issued, so no arrival ever reaches the barrier; the kernel's wait
+    gives up after its one-second limit, writes the status word and exits cleanly; the context stays usable."""
+    import time
+
+    from miles_ext_kernels_b200.cake._runtime import loader
+
+    lib = loader.load_library()
+    dev = torch.device("cuda")
+    img = torch.zeros(1024, dtype=torch.uint8, device=dev)
+    off = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.zeros(128, 16, dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    p = lambda x: ctypes.c_void_p(x.data_ptr())  # noqa: E731
+    torch.cuda.synchronize()
+    begin = time.perf_counter()
+    rc = lib.mek_selftest_umma(p(img), 1024, p(img), 1024, ctypes.c_uint64(desc_template(16)),
+                               ctypes.c_uint64(desc_template(16)), p(off), p(off), 0,
+                               ctypes.c_uint32(idesc(64, 16, False, False)), 16, 0, p(out), p(status),
+                               ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    lib.check(rc)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - begin
+    assert int(status.item()) == 1 and 0.5 < elapsed < 10.0
+    got, want = run_case(lib, *CASES["k_k_m128_n64_k64"])  # the context still works
+    assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max()
