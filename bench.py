@@ -222,30 +222,23 @@ def run_ours(args) -> None:
     resident = {n: t.to(device) for n, t in host.items()}
     cu_dev = None if work.cu_seqlens is None else torch.tensor(work.cu_seqlens, dtype=torch.int32, device=device)
 
-    landing: list[torch.Tensor] = []
-
-    def step(t: dict, copy_back: bool = False):
+    def step(t: dict, cu=None):
+        cu_cpu, cu_gpu = (work.cu_seqlens, cu_dev) if cu is None else cu
         q, k, v = (t[n].detach().requires_grad_(True) for n in ("q", "k", "v"))
         g, beta = t["g"].detach().requires_grad_(True), t["beta"].detach().requires_grad_(True)
         h0 = t["h0"].detach().requires_grad_(True) if "h0" in t else None
         if cfg.op == "kda":
-            o, final = kda.chunk_kda(q, k, v, g, beta, cu_dev), None
+            o, final = kda.chunk_kda(q, k, v, g, beta, cu_gpu), None
         else:
             o, final = gdn.chunk_gated_delta_rule(q, k, v, g=g, beta=beta, initial_state=h0,
-                                                  output_final_state=cfg.final_state, cu_seqlens=cu_dev,
-                                                  cu_seqlens_cpu=work.cu_seqlens, use_qk_l2norm_in_kernel=False)
+                                                  output_final_state=cfg.final_state, cu_seqlens=cu_gpu,
+                                                  cu_seqlens_cpu=cu_cpu, use_qk_l2norm_in_kernel=False)
         if final is not None and "dht" in t:
             torch.autograd.backward([o, final], [t["do"], t["dht"]])
         else:
             o.backward(t["do"])
         outs = [o, q.grad, k.grad, v.grad, g.grad, beta.grad] + ([h0.grad] if h0 is not None else []) + (
             [final] if final is not None else [])
-        if copy_back:  # into pinned host buffers, allocated on the first call
-            if not landing:
-                landing.extend(torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs)
-            for dst, src in zip(landing, outs):
-                dst.copy_(src.detach(), non_blocking=True)
-            return landing
         return outs
 
     def barrier():
@@ -284,10 +277,21 @@ def run_ours(args) -> None:
     clocks = sampler.summary()
     launches = log.count
 
-    # end to end: pinned host buffers in, outputs and gradients out, every step
+    # end to end: pinned host buffers in, outputs and gradients out to pinned host buffers, every step, through the
+    # package's host-memory pipeline (parts of the call on three streams: copy in, compute, copy out)
+    from miles_ext_kernels_b200 import host_io
+
+    if work.cu_seqlens is None:
+        parts = host_io.batch_parts(work.q.shape[0])
+    else:
+        parts = host_io.packed_parts(work.cu_seqlens, 8)
+    part_cu = {id(p): (p.cu_seqlens, torch.tensor(p.cu_seqlens, dtype=torch.int32, device=device))
+               for p in parts if p.cu_seqlens is not None}
+    pipeline = host_io.HostPipeline(device, parts, per_token=("q", "k", "v", "g", "beta", "do"))
+    total = (work.q.shape[0], work.q.shape[1], len(work.cu_seqlens) - 1 if work.cu_seqlens else work.q.shape[0])
+
     def e2e_step():
-        on_device = {n: t.to(device, non_blocking=True) for n, t in host.items()}
-        return step(on_device, copy_back=True)
+        return pipeline.run(host, lambda part, t: step(t, part_cu.get(id(part))), range(6), total)
 
     e2e_step()
     ms_e2e = timed(e2e_step, args.steps)
@@ -330,7 +334,7 @@ def run_ours(args) -> None:
                    "l2_hygiene": "inputs (q+k+v+dO = 768 MiB at cfg1) are larger than the 126 MB L2",
                    "sharding": "each rank runs the whole workload; no collective on the data path"},
         "e2e": {"value": world * tokens / (ms_e2e * 1e-3 / args.steps), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
+                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps, "parts": len(parts)},
         "gpu_launches": launches,
         "roofline": roofline,
         "path_roofline": {"t_roof_ms": 1e3 * t_roof, "frac": t_roof / step_s, "flops_per_token": flops_per_token(HV),
