@@ -60,6 +60,15 @@ int mek_selftest_umma(const void* a_img, int a_bytes, const void* b_img, int b_b
                       const int32_t* a_off, const int32_t* b_off, int nk, uint32_t idesc, int ncols, int d_lane,
                       float* out, int32_t* status, void* stream);
 
+/* Self-test of the tile loads: one box (64 bf16 columns x box_rows rows, 128-byte swizzle) of the row-major bf16
+ * matrix src [rows, cols] whose first element is (x, y) is copied by the copy engine (TMA) into shared memory and
+ * from there, byte for byte, to out [box_rows * 128 bytes].  The tests compare it with the operand layout the
+ * tensor-core self-test pins, including boxes that hang over the matrix's last row (zero-filled).
+ *   box_rows 8..128, a multiple of 8; x a multiple of 8 elements; cols a multiple of 64
+ * No counterpart in the reference. */
+int mek_selftest_tma(const void* src, int64_t rows, int64_t cols, int box_rows, int x, int y, void* out,
+                     int32_t* status, void* stream);
+
 /* Extents and chunk tables of one call.  Tokens are packed: [total_tokens, heads, 128]; a batch of B equal-length
  * sequences is B sequences of one packed row.  Chunks hold at most 64 tokens and never straddle a sequence.
  * Replaces the reference's ChunkMeta int32 tables (reference: miles_ext_kernels/cake/_impl/gdn/ops.py:157-174). */

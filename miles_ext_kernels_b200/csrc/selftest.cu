@@ -1,5 +1,6 @@
 // Self-test of the tcgen05 building block and the library-wide C-ABI helpers (version stamp, error text, device gate).
 #include "common.cuh"
+#include "tma.cuh"
 #include "umma.cuh"
 
 namespace mek {
@@ -64,6 +65,30 @@ __global__ void __launch_bounds__(128) selftest_umma_kernel(const uint4* a_img, 
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
+// One box of a tensor map -> shared memory -> `out`, byte for byte: what the copy engine wrote where.
+__global__ void __launch_bounds__(128) selftest_tma_kernel(const __grid_constant__ CUtensorMap map, int x, int y,
+                                                           int box_bytes, uint4* out, int32_t* status) {
+  extern __shared__ uint8_t raw[];
+  __shared__ uint64_t bar;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (tid == 0) {
+    mbar_arrive_expect(&bar, uint32_t(box_bytes));
+    tma_load_box(smem_u32(base), &map, x, y, &bar);
+  }
+  const bool done = mbar_wait(&bar, 0);
+  if (done) {
+    for (int i = tid; i < box_bytes / 16; i += 128) out[i] = reinterpret_cast<const uint4*>(base)[i];
+  } else if (tid == 0) {
+    *status = kDevWaitTimeout;
+  }
+}
+
 }  // namespace mek
 
 extern "C" {
@@ -100,6 +125,20 @@ int mek_selftest_umma(const void* a_img, int a_bytes, const void* b_img, int b_b
       static_cast<const uint4*>(a_img), a_bytes, static_cast<const uint4*>(b_img), b_bytes, a_desc, b_desc, a_off,
       b_off, nk, idesc, ncols, d_lane, out, status);
   return launched("selftest");
+}
+
+int mek_selftest_tma(const void* src, int64_t rows, int64_t cols, int box_rows, int x, int y, void* out,
+                     int32_t* status, void* stream) {
+  using namespace mek;
+  if (rows <= 0 || cols <= 0 || box_rows < 8 || box_rows > 128 || box_rows % 8 || x % 8 || out == nullptr ||
+      status == nullptr)
+    return fail(MEK_ERR_INVALID, "selftest_tma: box_rows in 8..128 (multiple of 8), x a multiple of 8 elements");
+  CUtensorMap map;
+  if (int rc = make_tile_map(&map, src, uint64_t(rows), uint64_t(cols), uint32_t(box_rows), "selftest_tma")) return rc;
+  const size_t smem = size_t(box_rows) * 128 + 1024;
+  selftest_tma_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(map, x, y, box_rows * 128,
+                                                                          static_cast<uint4*>(out), status);
+  return launched("selftest_tma");
 }
 
 }  // extern "C"

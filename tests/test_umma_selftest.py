@@ -116,3 +116,30 @@ def test_a_wait_that_nothing_satisfies_runs_out_and_reports_it():
     assert int(status.item()) == 1 and 0.5 < elapsed < 10.0
     got, want = run_case(lib, *CASES["k_k_m128_n64_k64"])  # the context still works
     assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("box_rows,x,y", [(64, 0, 0), (64, 64, 37), (128, 128, 256), (64, 192, 480), (64, 0, 500)])
+def test_tma_box_lands_in_the_operand_layout(box_rows, x, y):
+    """A TMA box is, byte for byte, the swizzled 64-column block the tensor-core operands use; rows past the
+    matrix's end arrive as zeros."""
+    from miles_ext_kernels_b200.cake._runtime import loader
+
+    lib = loader.load_library()
+    rows, cols = 512, 256
+    rng = np.random.default_rng(box_rows + x + y)
+    src = bf16_round(rng.standard_normal((rows, cols)).astype(np.float32))
+    dev = torch.device("cuda")
+    src_dev = torch.from_numpy(src).to(dev).to(torch.bfloat16).contiguous()
+    out = torch.zeros(box_rows * 128, dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    lib.check(lib.mek_selftest_tma(p(src_dev), ctypes.c_int64(rows), ctypes.c_int64(cols), box_rows, x, y, p(out),
+                                   p(status), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    box = np.zeros((box_rows, 64), dtype=np.float32)
+    live = max(0, min(box_rows, rows - y))
+    box[:live] = src[y:y + live, x:x + 64]
+    want, _ = tile_image(box)
+    assert np.array_equal(out.cpu().numpy(), want)
