@@ -17,6 +17,7 @@
 // Every reduction has a fixed order; no atomics.
 #include "common.cuh"
 #include "tiles.cuh"
+#include "tma.cuh"
 
 namespace mek {
 
@@ -55,26 +56,33 @@ __device__ __forceinline__ void cp_async_wait_pending() {
 //   B  (needs dS, dw)             dq += dS k, dk += dS^T q, dkb = A^T dw
 //   C  (needs dkb, dvb)           Y = bf16(dkb) w^T + bf16(dvb) u^T, KK = k k^T
 // and a fourth that nobody waits for until the pair ends: dk += bf16(beta dL D) k + bf16(beta dL D)^T k.
-// While one value head computes, the next one's tiles arrive by cp.async in the buffers the current one has finished
-// with (q / k of the next pair are double-buffered).
+// While one value head computes, the next one's tiles arrive by TMA in the buffers the current one has finished
+// with (q / k of the next pair are double-buffered); one elected thread issues every copy, and the copies of an item
+// complete on one mbarrier in three instalments (Aqk; the states and A; the row tiles).
+struct TailMaps {
+  CUtensorMap q, k;                      // rows [tokens, H * 128], box 64 x 64
+  CUtensorMap v, d_o, v_new, dv_new, w, u;  // rows [tokens, HV * 128], box 64 x 64
+  CUtensorMap h, dh;                     // tiles [num_tiles * 128, 128], box 64 x 128
+  CUtensorMap a, aqk;                    // tiles [num_tiles * 64, 64], box 64 x 64
+};
+
 __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-    const float* __restrict__ beta, const float* __restrict__ g_cs, const __nv_bfloat16* __restrict__ a_in,
-    const __nv_bfloat16* __restrict__ aqk_in, const __nv_bfloat16* __restrict__ w_in,
-    const __nv_bfloat16* __restrict__ u_in, const __nv_bfloat16* __restrict__ h_tape,
-    const __nv_bfloat16* __restrict__ dh_tape, const __nv_bfloat16* __restrict__ v_new,
-    const __nv_bfloat16* __restrict__ dv_new, const __nv_bfloat16* __restrict__ d_o,
+    const __grid_constant__ TailMaps maps, const float* __restrict__ beta, const float* __restrict__ g_cs,
     const __nv_bfloat16* __restrict__ q_raw, const __nv_bfloat16* __restrict__ k_raw,
     const float* __restrict__ rstd_q, const float* __restrict__ rstd_k, __nv_bfloat16* __restrict__ dq,
     __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, float* __restrict__ dbeta, float* __restrict__ dg,
     const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len, int num_chunks, int num_qk_heads,
     int num_v_heads, float scale, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar;         // tensor-core commits
+  __shared__ uint64_t bar_item;    // the item's tiles: three instalments, one arrival each
+  __shared__ uint64_t bar_uw;      // the item's u and w
+  __shared__ uint64_t bar_qk[2];   // q and k of a pair, one barrier per buffer
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool loader = tid == 64;   // the thread that issues every copy
   const int group = num_v_heads / num_qk_heads;
   const int num_pairs = num_chunks * num_qk_heads;
   // accumulator rows: warps w and w + 4 share the rows 16 (w % 4) .. + 15.  A 128-wide accumulator is split four
@@ -97,22 +105,29 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
 
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar_item, 3);
+    mbar_init(&bar_uw, 1);
+    mbar_init(&bar_qk[0], 1);
+    mbar_init(&bar_qk[1], 1);
     fence_mbar_init();
     abort_flag = 0;
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 512);
   const uint32_t sbase = smem_u32(sm);
   const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
 
   // a pair is live when it exists and its chunk is not a pad chunk of a device-built table (pads come last)
   auto pair_live = [&](int p) { return p < num_pairs && chunk_len[p / num_qk_heads] > 0; };
-  // ---- asynchronous loads --------------------------------------------------------------------------------------
+  // ---- asynchronous loads (issued by the loader thread only; scalars by cp.async from the first 64 threads) -----
   auto load_qk = [&](int p, int buf) {
     const int c = p / num_qk_heads, hq = p % num_qk_heads;
-    const int start = chunk_start[c], len = chunk_len[c];
     const uint32_t base = sbase + TailSmem::kQK + buf * TailSmem::kQKStride;
-    prefetch_tile<64, 128, 256>(base, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-    prefetch_tile<64, 128, 256>(base + 16384, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
+    mbar_arrive_expect(&bar_qk[buf], 2 * 16384);
+    tma_load_tile128(base, 8192, &maps.q, hq * kDim, chunk_start[c], &bar_qk[buf]);
+    tma_load_tile128(base + 16384, 8192, &maps.k, hq * kDim, chunk_start[c], &bar_qk[buf]);
   };
   struct Item {
     int c, hv, start, len;
@@ -127,42 +142,52 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     it.tile = int64_t(it.c) * num_v_heads + it.hv;
     return it;
   };
-  auto load_scalars_aqk = [&](const Item& it, int buf) {
+  auto load_scalars = [&](const Item& it, int buf) {  // every thread calls; the first 64 copy
     if (tid < 64) {
       const int64_t at = int64_t(it.start + (tid < it.len ? tid : it.len - 1)) * num_v_heads + it.hv;
       cp_async4(smem_u32(s_beta + buf * 64 + tid), beta + at);
       cp_async4(smem_u32(s_g2 + buf * 64 + tid), g_cs + at);
     }
-    prefetch_tile<64, 64, 256>(sbase + TailSmem::kAqk, 8192, aqk_in + it.tile * 4096, 64, 64, tid);
+    cp_async_commit();
   };
-  auto load_rows = [&](uint32_t where, const __nv_bfloat16* base, const Item& it) {
-    prefetch_tile<64, 128, 256>(sbase + where, 8192, base + int64_t(it.start) * v_stride + it.hv * kDim, v_stride,
-                                it.len, tid);
+  auto load_rows = [&](uint32_t where, const CUtensorMap* map, const Item& it, uint64_t* on) {
+    tma_load_tile128(sbase + where, 8192, map, it.hv * kDim, it.start, on);
+  };
+  // the three instalments of an item
+  auto load_aqk = [&](const Item& it) {
+    mbar_arrive_expect(&bar_item, 8192);
+    tma_load_box(sbase + TailSmem::kAqk, &maps.aqk, 0, int(it.tile * 64), &bar_item);
   };
   auto load_states = [&](const Item& it) {
-    prefetch_tile<128, 128, 256>(sbase + TailSmem::kH, 16384, h_tape + it.tile * 16384, 128, 128, tid);
-    prefetch_tile<128, 128, 256>(sbase + TailSmem::kDH, 16384, dh_tape + it.tile * 16384, 128, 128, tid);
+    mbar_arrive_expect(&bar_item, 2 * 32768 + 8192);
+    tma_load_tile128(sbase + TailSmem::kH, 16384, &maps.h, 0, int(it.tile * 128), &bar_item);
+    tma_load_tile128(sbase + TailSmem::kDH, 16384, &maps.dh, 0, int(it.tile * 128), &bar_item);
+    tma_load_box(sbase + TailSmem::kA, &maps.a, 0, int(it.tile * 64), &bar_item);
   };
-  auto load_a = [&](const Item& it) {
-    prefetch_tile<64, 64, 256>(sbase + TailSmem::kA, 8192, a_in + it.tile * 4096, 64, 64, tid);
+  auto load_row_tiles = [&](const Item& it) {
+    mbar_arrive_expect(&bar_item, 4 * 16384);
+    load_rows(TailSmem::kDO, &maps.d_o, it, &bar_item);
+    load_rows(TailSmem::kVN, &maps.v_new, it, &bar_item);
+    load_rows(TailSmem::kDVN, &maps.dv_new, it, &bar_item);
+    load_rows(TailSmem::kV, &maps.v, it, &bar_item);
+  };
+  auto load_uw = [&](const Item& it) {
+    mbar_arrive_expect(&bar_uw, 2 * 16384);
+    load_rows(TailSmem::kDO, &maps.u, it, &bar_uw);
+    load_rows(TailSmem::kVN, &maps.w, it, &bar_uw);
   };
 
   int pair = blockIdx.x;
   if (pair_live(pair)) {  // prologue: everything of the first item
     const Item it = item_of(pair, 0);
-    load_qk(pair, 0);
-    load_scalars_aqk(it, 0);
-    load_rows(TailSmem::kDO, d_o, it);
-    load_rows(TailSmem::kVN, v_new, it);
-    load_rows(TailSmem::kDVN, dv_new, it);
-    load_rows(TailSmem::kV, v, it);
-    load_states(it);
-    load_a(it);
-    cp_async_commit();
+    if (loader) {
+      load_qk(pair, 0);
+      load_aqk(it);
+      load_states(it);
+      load_row_tiles(it);
+    }
+    load_scalars(it, 0);
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
   const uint32_t tmem = tmem_slot;
   const Operand op_h{sbase + TailSmem::kH, 16384}, op_dh{sbase + TailSmem::kDH, 16384};
   const Operand op_dw{sbase + TailSmem::kH, 8192};
@@ -206,9 +231,9 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
   // scaled terms of this thread's (row, 32-column quarter) that cannot accumulate in tensor memory, summed over the
   // group: dq gets qscale (do h^T); dk gets rowscale (v_new dh^T) and beta 2^G dkb
   float dq_reg[32], dk_reg[32];
-  int item_parity = 0, qk_buf = 0;
+  int item_parity = 0, qk_buf = 0, pairs_done = 0;
   bool aborted = false;
-  for (; pair_live(pair) && !aborted; pair += gridDim.x, qk_buf ^= 1) {
+  for (; pair_live(pair) && !aborted; pair += gridDim.x, qk_buf ^= 1, ++pairs_done) {
     const int hq = pair % num_qk_heads;
     const uint32_t qk_base = sbase + TailSmem::kQK + qk_buf * TailSmem::kQKStride;
     uint8_t* q_tile = sm + TailSmem::kQK + qk_buf * TailSmem::kQKStride;
@@ -229,16 +254,27 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       const float* beta_s = s_beta + item_parity * 64;
       const float* g2 = s_g2 + item_parity * 64;
 
-      cp_async_wait_pending<0>();  // this item's tiles (issued while the previous item computed) have landed
+      // this item's tiles (issued while the previous item computed) have landed
+      cp_async_wait_pending<0>();
+      if (!mbar_wait(&bar_item, item_parity)) abort.raise();
+      if (gi == 0 && !mbar_wait(&bar_qk[qk_buf], (pairs_done >> 1) & 1)) abort.raise();
+      if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows
+        clear_tile_rows<256>(sm + TailSmem::kDO, len, tid);
+        clear_tile_rows<256>(sm + TailSmem::kVN, len, tid);
+        clear_tile_rows<256>(sm + TailSmem::kDVN, len, tid);
+        clear_tile_rows<256>(sm + TailSmem::kV, len, tid);
+        if (gi == 0) {
+          clear_tile_rows<256>(q_tile, len, tid);
+          clear_tile_rows<256>(k_tile, len, tid);
+        }
+      }
       stage_sync();
       if (abort.raised()) {
         aborted = true;
         break;
       }
-      if (last_of_pair && has_next_pair) {  // the other q / k buffer is free: the previous pair is done
-        load_qk(next_pair, qk_buf ^ 1);
-        cp_async_commit();
-      }
+      // the other q / k buffer is free: the previous pair is done
+      if (last_of_pair && has_next_pair && loader) load_qk(next_pair, qk_buf ^ 1);
 
       // ---- phase A: everything that needs only loaded tiles -------------------------------------------------------
       if (tid == 0) {
@@ -342,13 +378,12 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
         for (int jj = 0; jj < 4; ++jj) set_tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj, pack8(y + jj * 8));
       }
       stage_sync();
-      {  // do and v_new are done with: this value head's u and w take their buffers; then the next item's Aqk
-        load_rows(TailSmem::kDO, u_in, it);
-        load_rows(TailSmem::kVN, w_in, it);
-        cp_async_commit();
-        if (has_next) load_scalars_aqk(nx, item_parity ^ 1);
-        cp_async_commit();
+      // do and v_new are done with: this value head's u and w take their buffers; then the next item's Aqk
+      if (loader) {
+        load_uw(it);
+        if (has_next) load_aqk(nx);
       }
+      if (has_next) load_scalars(nx, item_parity ^ 1);
 
       // ---- phase B: dq += dS k ; dk += dS^T q ; dkb = A^T dw ---------------------------------------------------------
       if (tid == 0) {
@@ -380,13 +415,13 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
         dB += eg * dot_k;
         dG += dot_kb;
       }
-      cp_async_wait_pending<1>();  // u and w have landed (the next item's Aqk group may be in flight)
-      stage_sync();
-      if (has_next) {  // h / dh (and the dw tile) and A are done with
-        load_states(nx);
-        load_a(nx);
-        cp_async_commit();
+      if (!mbar_wait(&bar_uw, item_parity)) abort.raise();  // u and w have landed
+      if (len < kChunk) {
+        clear_tile_rows<256>(sm + TailSmem::kDO, len, tid);
+        clear_tile_rows<256>(sm + TailSmem::kVN, len, tid);
       }
+      stage_sync();
+      if (has_next && loader) load_states(nx);  // h / dh (and the dw tile) and A are done with
 
       // ---- phase C: Y = bf16(dkb) w^T + bf16(dvb) u^T ; KK = k k^T ---------------------------------------------------
       if (tid == 0) {
@@ -425,13 +460,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
         publish_column_sums(s, s_cs + 256);
       }
       stage_sync();
-      if (has_next) {  // w, u, bf16(dkb), bf16(dvb) are done with
-        load_rows(TailSmem::kDO, d_o, nx);
-        load_rows(TailSmem::kVN, v_new, nx);
-        load_rows(TailSmem::kDVN, dv_new, nx);
-        load_rows(TailSmem::kV, v, nx);
-        cp_async_commit();
-      }
+      if (has_next && loader) load_row_tiles(nx);  // w, u, bf16(dkb), bf16(dvb) are done with
 
       // ---- phase D: dk += bf16(beta dL D) k + bf16(beta dL D)^T k ------------------------------------------------
       if (tid == 0) {
@@ -518,6 +547,11 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     }
   }
   cp_async_wait_pending<0>();
+  if (abort.raised()) {  // copies of the next item may still be in flight: give them time to land before the CTA ends
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 100000ull) {
+    }
+  }
   if (abort.raised() && tid == 0) atomicExch(status, kDevWaitTimeout | (5 << 8));
   tc_fence_before();
   __syncthreads();
@@ -549,10 +583,27 @@ extern "C" int mek_gdn_bwd_tail(const MekGdnDims* d, const void* q, const void* 
     cudaGetLastError();
     return fail(MEK_ERR_CUDA, "bwd_tail: cannot query the SM count");
   }
+  const uint64_t tokens = uint64_t(d->total_tokens), tiles = uint64_t(d->num_chunks) * d->num_v_heads;
+  const uint64_t qk_cols = uint64_t(d->num_qk_heads) * kDim, v_cols = uint64_t(d->num_v_heads) * kDim;
+  TailMaps maps;
+  struct {
+    CUtensorMap* map;
+    const void* base;
+    uint64_t rows, cols;
+    uint32_t box_rows;
+  } const wanted[] = {
+      {&maps.q, q, tokens, qk_cols, 64},      {&maps.k, k, tokens, qk_cols, 64},
+      {&maps.v, v, tokens, v_cols, 64},       {&maps.d_o, d_o, tokens, v_cols, 64},
+      {&maps.v_new, v_new, tokens, v_cols, 64}, {&maps.dv_new, dv_new, tokens, v_cols, 64},
+      {&maps.w, w, tokens, v_cols, 64},       {&maps.u, u, tokens, v_cols, 64},
+      {&maps.h, h_tape, tiles * 128, 128, 128}, {&maps.dh, dh_tape, tiles * 128, 128, 128},
+      {&maps.a, a, tiles * 64, 64, 64},       {&maps.aqk, aqk, tiles * 64, 64, 64},
+  };
+  for (const auto& m : wanted)
+    if (int rc = make_tile_map(m.map, m.base, m.rows, m.cols, m.box_rows, "bwd_tail")) return rc;
   const int pairs = d->num_chunks * d->num_qk_heads;
   gdn_bwd_tail_kernel<<<pairs < sms ? pairs : sms, 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      In(q), In(k), In(v), beta, g_cs, In(a), In(aqk), In(w), In(u), In(h_tape), In(dh_tape), In(v_new), In(dv_new),
-      In(d_o), In(q_raw), In(k_raw), rstd_q, rstd_k, Out(dq), Out(dk), Out(dv), dbeta, dg, d->chunk_start,
+      maps, beta, g_cs, In(q_raw), In(k_raw), rstd_q, rstd_k, Out(dq), Out(dk), Out(dv), dbeta, dg, d->chunk_start,
       d->chunk_len, d->num_chunks, d->num_qk_heads, d->num_v_heads, d->scale, status);
   return launched("bwd_tail");
 }
