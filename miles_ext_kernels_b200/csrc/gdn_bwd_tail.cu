@@ -216,15 +216,29 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     umma_gemm<64, 64>(tmem + col, a, a_mn, b, b_mn, kdim, accumulate, neg_a);
     umma_gemm<64, 64>(tmem + col + kUpperLanes, a, a_mn, b_hi, b_mn, kdim, accumulate, neg_a);
   };
-  // column sums of a [64 x 64] matrix held one 32-column row piece per owner thread: reduce over the 16 rows of the
-  // warp by shuffles, then publish one partial per quadrant (summed after the next block barrier)
+  // column sums of a [64 x 64] matrix held one 32-column row piece per owner thread: a butterfly over the 16 rows of
+  // the warp that halves the columns a lane carries at every step (30 shuffles instead of 128), then one partial per
+  // quadrant (summed after the next block barrier).  The order of the additions is fixed.
   auto publish_column_sums = [&](float* piece, float* where) {
+    float x[32];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      float x = owner ? piece[j] : 0.f;
+    for (int j = 0; j < 32; ++j) x[j] = owner ? piece[j] : 0.f;
+    const int l16 = lane & 15;
 #pragma unroll
-      for (int m = 8; m >= 1; m >>= 1) x += __shfl_xor_sync(0xffffffffu, x, m);
-      if (lane == 0) where[quad * 64 + ch * 32 + j] = x;
+    for (int width = 16, m = 8; width >= 2; width >>= 1, m >>= 1) {
+      const bool up = (l16 & m) != 0;  // this lane keeps the upper half of the columns it still carries
+#pragma unroll
+      for (int j = 0; j < width; ++j) {
+        const float mine = up ? x[j + width] : x[j], send = up ? x[j] : x[j + width];
+        x[j] = mine + __shfl_xor_sync(0xffffffffu, send, m);
+      }
+    }
+    // lane l16 now holds, over the warp's 16 rows, the sums of the two columns whose index bits 4..1 spell its
+    // butterfly path: bit 4 <- (l16 & 8), bit 3 <- (l16 & 4), bit 2 <- (l16 & 2), bit 1 <- (l16 & 1)
+    if (lane < 16) {
+      const int col = ((l16 & 8) << 1) | ((l16 & 4) << 1) | ((l16 & 2) << 1) | ((l16 & 1) << 1);
+      where[quad * 64 + ch * 32 + col] = x[0];
+      where[quad * 64 + ch * 32 + col + 1] = x[1];
     }
   };
 
@@ -477,20 +491,31 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       s_red[cq * 64 + row] = dG;
       s_red2[cq * 64 + row] = dB;
       __syncthreads();
+      // warps 0 and 1: the in-chunk suffix sum of the gate gradient as two warp scans joined by the upper total
+      float suffix = 0.f;
       if (tid < 64) {
-        float gamma_dot = 0.f;
-#pragma unroll
-        for (int wv = 0; wv < 8; ++wv) gamma_dot += s_warp[wv];
-        float acc = 0.f;
-        for (int j = len - 1; j >= tid; --j) {
-          acc += (s_red[j] + s_red[64 + j]) + (s_red[128 + j] + s_red[192 + j]);
-          if (j == len - 1) acc += gamma_dot;
-        }
         if (tid < len) {
-          dg[int64_t(start + tid) * num_v_heads + hv] = acc;
-          dbeta[int64_t(start + tid) * num_v_heads + hv] =
-              (s_red2[tid] + s_red2[64 + tid]) + (s_red2[128 + tid] + s_red2[192 + tid]);
+          suffix = (s_red[tid] + s_red[64 + tid]) + (s_red[128 + tid] + s_red[192 + tid]);
+          if (tid == len - 1) {
+            float gamma_dot = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < 8; ++wv) gamma_dot += s_warp[wv];
+            suffix += gamma_dot;
+          }
         }
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) {
+          const float other = __shfl_down_sync(0xffffffffu, suffix, m);
+          if (lane + m < 32) suffix += other;
+        }
+        if (tid == 32) s_warp[8] = suffix;  // the total of rows 32..63
+      }
+      __syncthreads();
+      if (tid < len) {
+        if (tid < 32) suffix += s_warp[8];
+        dg[int64_t(start + tid) * num_v_heads + hv] = suffix;
+        dbeta[int64_t(start + tid) * num_v_heads + hv] =
+            (s_red2[tid] + s_red2[64 + tid]) + (s_red2[128 + tid] + s_red2[192 + tid]);
       }
 
       if (last_of_pair) {
