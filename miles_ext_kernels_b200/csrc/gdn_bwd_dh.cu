@@ -10,6 +10,7 @@
 // walk) and :433-448 (do_g, dv_intra); reference launches: miles_ext_kernels/cake/_impl/gdn/ops.py:1519-1640.
 #include "common.cuh"
 #include "tiles.cuh"
+#include "tma.cuh"
 
 namespace mek {
 
@@ -28,15 +29,19 @@ struct BwdDhSmem {
   static constexpr uint32_t kBytes = kG + 1024;
 };
 
+struct BwdDhMaps {
+  CUtensorMap q, k, w, d_o;  // rows, box 64 x 64
+  CUtensorMap aqk;           // tiles [num_tiles * 64, 64], box 64 x 64
+};
+
 __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ w,
-    const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ aqk, const float* __restrict__ g_cs,
+    const __grid_constant__ BwdDhMaps maps, const float* __restrict__ g_cs,
     const float* __restrict__ dht, __nv_bfloat16* __restrict__ dh_tape, __nv_bfloat16* __restrict__ dv_new,
     float* __restrict__ dh0, const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len,
     const int32_t* __restrict__ seq_chunk_start, int num_qk_heads, int num_v_heads, float scale,
     const float* __restrict__ gl2, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, bar_load[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -52,23 +57,30 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
 
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar_load[0], 1);
+    mbar_init(&bar_load[1], 1);
     fence_mbar_init();
     abort_flag = 0;
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 512);
   const uint32_t sbase = smem_u32(sm);
-  const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
+  const int64_t v_stride = int64_t(num_v_heads) * kDim;
+  __syncthreads();  // the barriers' initialisation is visible before the first copy is issued
   constexpr uint32_t kD1 = 0, kD1b = 128, kD2 = 256;  // tensor-memory columns
   const int c_begin = seq_chunk_start[n], c_end = seq_chunk_start[n + 1];
 
+  // the tiles of chunk c by TMA (one issuing thread), its gates by cp.async
   auto prefetch = [&](int c, int stage) {
     const int start = chunk_start[c], len = chunk_len[c];
     const uint32_t base = sbase + stage * BwdDhSmem::kStage;
-    prefetch_tile<64, 128, 256>(base + BwdDhSmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-    prefetch_tile<64, 128, 256>(base + BwdDhSmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-    prefetch_tile<64, 128, 256>(base + BwdDhSmem::kW, 8192, w + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-    prefetch_tile<64, 128, 256>(base + BwdDhSmem::kDO, 8192, d_o + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-    prefetch_tile<64, 64, 256>(base + BwdDhSmem::kAqk, 8192, aqk + (int64_t(c) * num_v_heads + hv) * 4096, 64, 64, tid);
+    if (tid == 32) {
+      mbar_arrive_expect(&bar_load[stage], 4 * 16384 + 8192);
+      tma_load_tile128(base + BwdDhSmem::kK, 8192, &maps.k, hq * kDim, start, &bar_load[stage]);
+      tma_load_tile128(base + BwdDhSmem::kQ, 8192, &maps.q, hq * kDim, start, &bar_load[stage]);
+      tma_load_tile128(base + BwdDhSmem::kW, 8192, &maps.w, hv * kDim, start, &bar_load[stage]);
+      tma_load_tile128(base + BwdDhSmem::kDO, 8192, &maps.d_o, hv * kDim, start, &bar_load[stage]);
+      tma_load_box(base + BwdDhSmem::kAqk, &maps.aqk, 0, int((int64_t(c) * num_v_heads + hv) * 64), &bar_load[stage]);
+    }
     if (kda) {
       if (tid < 128) cp_async4(smem_u32(s_g2 + stage * 128 + tid), gl2 + (int64_t(c) * num_v_heads + hv) * kDim + tid);
     } else if (tid < 64) {
@@ -118,7 +130,14 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
         reinterpret_cast<uint4*>(tape)[cc] = packed;
       }
     }
-    cp_async_wait_all();
+    cp_async_wait_all();  // this chunk's gates and tiles have landed (issued one step ago)
+    if (!mbar_wait(&bar_load[stage], ((c_end - 1 - c) >> 1) & 1)) abort.raise();
+    if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows
+      clear_tile_rows<256>(st + BwdDhSmem::kK, len, tid);
+      clear_tile_rows<256>(st + BwdDhSmem::kQ, len, tid);
+      clear_tile_rows<256>(st + BwdDhSmem::kW, len, tid);
+      clear_tile_rows<256>(st + BwdDhSmem::kDO, len, tid);
+    }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -208,38 +227,46 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
 
 }  // namespace mek
 
+namespace {
+int launch_bwd_dh(const MekGdnDims* d, const void* q, const void* k, const void* w, const void* d_o, const void* aqk,
+                  const float* g_cs, const float* dht, void* dh_tape, void* dv_new, float* dh0, const float* gl2,
+                  int32_t* status, void* stream, const char* what) {
+  using namespace mek;
+  const size_t smem = BwdDhSmem::kBytes + 1024;
+  if (int rc = want_smem(gdn_bwd_dh_kernel, smem, what)) return rc;
+  BwdDhMaps maps;
+  if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_qk_heads, what)) return rc;
+  if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, what)) return rc;
+  if (int rc = make_rows_map(&maps.w, w, d->total_tokens, d->num_v_heads, what)) return rc;
+  if (int rc = make_rows_map(&maps.d_o, d_o, d->total_tokens, d->num_v_heads, what)) return rc;
+  if (int rc = make_tiles_map(&maps.aqk, aqk, int64_t(d->num_chunks) * d->num_v_heads, 64, 64, what)) return rc;
+  gdn_bwd_dh_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      maps, g_cs, dht, static_cast<__nv_bfloat16*>(dh_tape), static_cast<__nv_bfloat16*>(dv_new), dh0, d->chunk_start,
+      d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, d->scale, gl2, status);
+  return launched(what);
+}
+}  // namespace
+
 extern "C" int mek_gdn_bwd_dh(const MekGdnDims* d, const void* q, const void* k, const void* w, const void* d_o,
                               const void* aqk, const float* g_cs, const float* dht, void* dh_tape, void* dv_new,
                               float* dh0, int32_t* status, void* stream) {
   using namespace mek;
-  if (d == nullptr || d->num_seqs <= 0 || d->num_v_heads <= 0 || d->num_qk_heads <= 0 ||
-      d->num_v_heads % d->num_qk_heads != 0)
+  if (d == nullptr || d->num_seqs <= 0 || d->num_v_heads <= 0 || d->num_qk_heads <= 0 || d->num_chunks <= 0 ||
+      d->total_tokens <= 0 || d->num_v_heads % d->num_qk_heads != 0)
     return fail(MEK_ERR_INVALID, "bwd_dh: bad extents");
   if (d->head_dim != 128) return fail(MEK_ERR_UNSUPPORTED, "bwd_dh: head dims must be 128, not %d", d->head_dim);
-  const size_t smem = BwdDhSmem::kBytes + 1024;
-  if (int rc = want_smem(gdn_bwd_dh_kernel, smem, "bwd_dh")) return rc;
-  gdn_bwd_dh_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(w),
-      static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(aqk), g_cs, dht,
-      static_cast<__nv_bfloat16*>(dh_tape), static_cast<__nv_bfloat16*>(dv_new), dh0, d->chunk_start, d->chunk_len,
-      d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, d->scale, nullptr, status);
-  return launched("bwd_dh");
+  return launch_bwd_dh(d, q, k, w, d_o, aqk, g_cs, dht, dh_tape, dv_new, dh0, nullptr, status, stream, "bwd_dh");
 }
 
 extern "C" int mek_kda_bwd_dh(const MekGdnDims* d, const void* qg, const void* kr, const void* w, const void* d_o,
                               const void* aqk, const float* gl2, void* dh_tape, void* dv_new, int32_t* status,
                               void* stream) {
   using namespace mek;
-  if (d == nullptr || d->num_seqs <= 0 || d->num_v_heads <= 0 || d->num_qk_heads != d->num_v_heads)
+  if (d == nullptr || d->num_seqs <= 0 || d->num_v_heads <= 0 || d->num_qk_heads != d->num_v_heads ||
+      d->num_chunks <= 0 || d->total_tokens <= 0)
     return fail(MEK_ERR_INVALID, "kda_bwd_dh: bad extents (KDA has one value head per key head)");
   if (d->head_dim != 128) return fail(MEK_ERR_UNSUPPORTED, "kda_bwd_dh: head dims must be 128, not %d", d->head_dim);
   if (gl2 == nullptr) return fail(MEK_ERR_INVALID, "kda_bwd_dh: gl2 is null");
-  const size_t smem = BwdDhSmem::kBytes + 1024;
-  if (int rc = want_smem(gdn_bwd_dh_kernel, smem, "kda_bwd_dh")) return rc;
-  gdn_bwd_dh_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(qg), static_cast<const __nv_bfloat16*>(kr), static_cast<const __nv_bfloat16*>(w),
-      static_cast<const __nv_bfloat16*>(d_o), static_cast<const __nv_bfloat16*>(aqk), nullptr, nullptr,
-      static_cast<__nv_bfloat16*>(dh_tape), static_cast<__nv_bfloat16*>(dv_new), nullptr, d->chunk_start, d->chunk_len,
-      d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, d->scale, gl2, status);
-  return launched("kda_bwd_dh");
+  return launch_bwd_dh(d, qg, kr, w, d_o, aqk, nullptr, nullptr, dh_tape, dv_new, nullptr, gl2, status, stream,
+                       "kda_bwd_dh");
 }

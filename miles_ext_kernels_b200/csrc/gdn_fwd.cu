@@ -15,6 +15,7 @@
 // (contraction over the feature axis) and as an MN-major operand (contraction over the token axis).
 #include "common.cuh"
 #include "tiles.cuh"
+#include "tma.cuh"
 
 namespace mek {
 
@@ -74,14 +75,17 @@ struct WySmem {
 __device__ __forceinline__ int wy_l_index(int i, int j) { return i * 64 + (j ^ ((i & 7) << 2)); }
 
 // Three CTAs per SM (shared memory) hide each other's global-load and solve latencies; tensor memory: 128 columns.
+struct WyMaps {
+  CUtensorMap q, k, v;  // rows, box 64 x 64
+};
+
 __global__ void __launch_bounds__(128) gdn_wy_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-    const float* __restrict__ beta, const float* __restrict__ g_cs, __nv_bfloat16* __restrict__ a_out,
+    const __grid_constant__ WyMaps maps, const float* __restrict__ beta, const float* __restrict__ g_cs, __nv_bfloat16* __restrict__ a_out,
     __nv_bfloat16* __restrict__ aqk_out, __nv_bfloat16* __restrict__ w_out, __nv_bfloat16* __restrict__ u_out,
     const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len, int num_qk_heads, int num_v_heads,
     float scale, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, bar_load;
   __shared__ uint32_t tmem_slot;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -93,25 +97,30 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   float* s_l = reinterpret_cast<float*>(sm + WySmem::kQ);
   constexpr uint32_t kUpper = 16u << 16;  // an M = 64 accumulator in lanes 16..31 of each quadrant
 
-  if (tid == 0) {
+  const int64_t v_stride = int64_t(num_v_heads) * kDim;
+  const uint32_t sbase = smem_u32(sm);
+  if (tid == 0) {  // all three tiles in flight at once (TMA), the scalars by plain loads meanwhile
     mbar_init(&bar, 1);
+    mbar_init(&bar_load, 1);
     fence_mbar_init();
+    mbar_arrive_expect(&bar_load, 3 * 16384);
+    tma_load_tile128(sbase + WySmem::kQ, 8192, &maps.q, hq * kDim, start, &bar_load);
+    tma_load_tile128(sbase + WySmem::kK, 8192, &maps.k, hq * kDim, start, &bar_load);
+    tma_load_tile128(sbase + WySmem::kV, 8192, &maps.v, hv * kDim, start, &bar_load);
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 128);
-
-  const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
-  // all three tiles in flight at once (cp.async), the scalars by plain loads meanwhile
-  const uint32_t sbase = smem_u32(sm);
-  prefetch_tile<64, 128, 128>(sbase + WySmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-  prefetch_tile<64, 128, 128>(sbase + WySmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-  prefetch_tile<64, 128, 128>(sbase + WySmem::kV, 8192, v + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-  cp_async_commit();
   if (tid < 64) {
     const int i = tid < len ? tid : len - 1;
     s_beta[tid] = tid < len ? beta[int64_t(start + i) * num_v_heads + hv] : 0.f;
     s_g2[tid] = g_cs[int64_t(start + i) * num_v_heads + hv];
   }
-  cp_async_wait_all();
+  __syncthreads();  // the barrier's initialisation is visible to every waiter
+  bool ok = __all_sync(0xffffffffu, mbar_wait(&bar_load, 0));
+  if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows
+    clear_tile_rows<128>(sm + WySmem::kQ, len, tid);
+    clear_tile_rows<128>(sm + WySmem::kK, len, tid);
+    clear_tile_rows<128>(sm + WySmem::kV, len, tid);
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -139,7 +148,7 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
     for (int j = 0; j < 8; ++j) x[j] *= b;
     set_tile_chunk(sm + WySmem::kV, 8192, r, cc, pack8(x));
   }
-  bool ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0));
+  ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0)) && ok;
   tc_fence_after();
   __syncthreads();  // every thread sees the products done: the q tile's space now takes L
 
@@ -257,14 +266,17 @@ struct FwdHSmem {
 
 // `gl2` != nullptr selects the per-channel-decay variant (KDA): `k` then holds k 2^{G_L - G} (the decay to the chunk
 // end is folded into the operand, so rowscale = 1) and the state decays per key channel: row k by 2^{gl2[c, hv, k]}.
+struct FwdHMaps {
+  CUtensorMap k, w, u;  // rows, box 64 x 64
+};
+
 __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
-    const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ u,
-    const float* __restrict__ g_cs, const float* __restrict__ h0, __nv_bfloat16* __restrict__ h_tape,
+    const __grid_constant__ FwdHMaps maps, const float* __restrict__ g_cs, const float* __restrict__ h0, __nv_bfloat16* __restrict__ h_tape,
     __nv_bfloat16* __restrict__ v_new, float* __restrict__ final_state, const int32_t* __restrict__ chunk_start,
     const int32_t* __restrict__ chunk_len, const int32_t* __restrict__ seq_chunk_start, int num_qk_heads,
     int num_v_heads, const float* __restrict__ gl2, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, bar_load[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -278,20 +290,27 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
 
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar_load[0], 1);
+    mbar_init(&bar_load[1], 1);
     fence_mbar_init();
     abort_flag = 0;
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 256);
   const uint32_t sbase = smem_u32(sm);
-  const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
+  const int64_t v_stride = int64_t(num_v_heads) * kDim;
   const int c_begin = seq_chunk_start[n], c_end = seq_chunk_start[n + 1];
+  __syncthreads();  // the barriers' initialisation is visible before the first copy is issued
 
+  // the tiles of chunk c by TMA (one issuing thread), its gates by cp.async
   auto prefetch = [&](int c, int stage) {
     const int start = chunk_start[c], len = chunk_len[c];
     const uint32_t base = sbase + stage * FwdHSmem::kStage;
-    prefetch_tile<64, 128, 256>(base + FwdHSmem::kW, 8192, w + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
-    prefetch_tile<64, 128, 256>(base + FwdHSmem::kK, 8192, k + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-    prefetch_tile<64, 128, 256>(base + FwdHSmem::kU, 8192, u + int64_t(start) * v_stride + hv * kDim, v_stride, len, tid);
+    if (tid == 32) {
+      mbar_arrive_expect(&bar_load[stage], 3 * 16384);
+      tma_load_tile128(base + FwdHSmem::kW, 8192, &maps.w, hv * kDim, start, &bar_load[stage]);
+      tma_load_tile128(base + FwdHSmem::kK, 8192, &maps.k, hq * kDim, start, &bar_load[stage]);
+      tma_load_tile128(base + FwdHSmem::kU, 8192, &maps.u, hv * kDim, start, &bar_load[stage]);
+    }
     if (kda) {
       if (tid < 128) cp_async4(smem_u32(s_g2 + stage * 128 + tid), gl2 + (int64_t(c) * num_v_heads + hv) * kDim + tid);
     } else if (tid < 64) {
@@ -339,7 +358,13 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
         reinterpret_cast<uint4*>(tape)[cc] = packed;
       }
     }
-    cp_async_wait_all();  // this chunk's tiles have landed (issued one step ago)
+    cp_async_wait_all();  // this chunk's gates and tiles have landed (issued one step ago)
+    if (!mbar_wait(&bar_load[stage], ((c - c_begin) >> 1) & 1)) abort.raise();
+    if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows
+      clear_tile_rows<256>(st + FwdHSmem::kW, len, tid);
+      clear_tile_rows<256>(st + FwdHSmem::kK, len, tid);
+      clear_tile_rows<256>(st + FwdHSmem::kU, len, tid);
+    }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -432,13 +457,18 @@ struct FwdOSmem {
   static constexpr uint32_t kBytes = kG + 256;
 };
 
+struct FwdOMaps {
+  CUtensorMap q, v_new;  // rows, box 64 x 64
+  CUtensorMap h;         // tiles [num_tiles * 128, 128], box 64 x 128
+  CUtensorMap aqk;       // tiles [num_tiles * 64, 64], box 64 x 64
+};
+
 __global__ void __launch_bounds__(128) gdn_fwd_o_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ aqk, const __nv_bfloat16* __restrict__ v_new,
-    const __nv_bfloat16* __restrict__ h_tape, const float* __restrict__ g_cs, __nv_bfloat16* __restrict__ o,
+    const __grid_constant__ FwdOMaps maps, const float* __restrict__ g_cs, __nv_bfloat16* __restrict__ o,
     const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len, int num_qk_heads, int num_v_heads,
     float scale, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, bar_load;
   __shared__ uint32_t tmem_slot;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -447,23 +477,28 @@ __global__ void __launch_bounds__(128) gdn_fwd_o_kernel(
   if (len <= 0) return;  // a pad chunk of a device-built table
   float* s_g2 = reinterpret_cast<float*>(sm + FwdOSmem::kG);
 
-  if (tid == 0) {
-    mbar_init(&bar, 1);
-    fence_mbar_init();
-  }
-  if (warp == 0) tmem_alloc(&tmem_slot, 128);
-  const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
+  const int64_t v_stride = int64_t(num_v_heads) * kDim;
   const int64_t tile = int64_t(c) * num_v_heads + hv;
   const uint32_t sbase = smem_u32(sm);
-  prefetch_tile<64, 128, 128>(sbase + FwdOSmem::kQ, 8192, q + int64_t(start) * qk_stride + hq * kDim, qk_stride, len, tid);
-  prefetch_tile<64, 128, 128>(sbase + FwdOSmem::kVN, 8192, v_new + int64_t(start) * v_stride + hv * kDim, v_stride, len,
-                              tid);
-  prefetch_tile<128, 128, 128>(sbase + FwdOSmem::kH, 16384, h_tape + tile * 16384, 128, 128, tid);
-  prefetch_tile<64, 64, 128>(sbase + FwdOSmem::kAqk, 8192, aqk + tile * 4096, 64, 64, tid);
-  cp_async_commit();
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_init(&bar_load, 1);
+    fence_mbar_init();
+    mbar_arrive_expect(&bar_load, 2 * 16384 + 32768 + 8192);
+    tma_load_tile128(sbase + FwdOSmem::kQ, 8192, &maps.q, hq * kDim, start, &bar_load);
+    tma_load_tile128(sbase + FwdOSmem::kVN, 8192, &maps.v_new, hv * kDim, start, &bar_load);
+    tma_load_tile128(sbase + FwdOSmem::kH, 16384, &maps.h, 0, int(tile * 128), &bar_load);
+    tma_load_box(sbase + FwdOSmem::kAqk, &maps.aqk, 0, int(tile * 64), &bar_load);
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 128);
   // g_cs == nullptr: the per-channel-decay variant, whose q operand already holds q 2^G (qscale = scale)
   if (tid < 64) s_g2[tid] = g_cs ? g_cs[int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv] : 0.f;
-  cp_async_wait_all();
+  __syncthreads();  // the barrier's initialisation is visible to every waiter
+  const bool landed = __all_sync(0xffffffffu, mbar_wait(&bar_load, 0));
+  if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows
+    clear_tile_rows<128>(sm + FwdOSmem::kQ, len, tid);
+    clear_tile_rows<128>(sm + FwdOSmem::kVN, len, tid);
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -479,7 +514,7 @@ __global__ void __launch_bounds__(128) gdn_fwd_o_kernel(
     umma_gemm<64, 64>(tmem + 64 + (16u << 16), op_a, false, operand_at(op_vn, 0, 1), true, 64, false);
     umma_commit(&bar);
   }
-  const bool ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0));
+  const bool ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0)) && landed;
   tc_fence_after();
   if (ok) {
     const int i = warp * 16 + (lane & 15);
@@ -558,25 +593,39 @@ int mek_gdn_wy_fwd(const MekGdnDims* d, const void* q, const void* k, const void
   if (int rc = check_dims(d, "wy_fwd")) return rc;
   const size_t smem = WySmem::kBytes + 1024;
   if (int rc = want_smem(gdn_wy_kernel, smem, "wy_fwd")) return rc;
+  WyMaps maps;
+  if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_qk_heads, "wy_fwd")) return rc;
+  if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, "wy_fwd")) return rc;
+  if (int rc = make_rows_map(&maps.v, v, d->total_tokens, d->num_v_heads, "wy_fwd")) return rc;
   gdn_wy_kernel<<<dim3(d->num_chunks, d->num_v_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
-      beta, g_cs, static_cast<__nv_bfloat16*>(a_out), static_cast<__nv_bfloat16*>(aqk_out),
+      maps, beta, g_cs, static_cast<__nv_bfloat16*>(a_out), static_cast<__nv_bfloat16*>(aqk_out),
       static_cast<__nv_bfloat16*>(w_out), static_cast<__nv_bfloat16*>(u_out), d->chunk_start, d->chunk_len,
       d->num_qk_heads, d->num_v_heads, d->scale, status);
   return launched("wy_fwd");
 }
 
+namespace {
+int launch_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* u, const float* g_cs, const float* h0,
+                 void* h_tape, void* v_new, float* final_state, const float* gl2, int32_t* status, void* stream,
+                 const char* what) {
+  using namespace mek;
+  const size_t smem = FwdHSmem::kBytes + 1024;
+  if (int rc = want_smem(gdn_fwd_h_kernel, smem, what)) return rc;
+  FwdHMaps maps;
+  if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, what)) return rc;
+  if (int rc = make_rows_map(&maps.w, w, d->total_tokens, d->num_v_heads, what)) return rc;
+  if (int rc = make_rows_map(&maps.u, u, d->total_tokens, d->num_v_heads, what)) return rc;
+  gdn_fwd_h_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      maps, g_cs, h0, static_cast<__nv_bfloat16*>(h_tape), static_cast<__nv_bfloat16*>(v_new), final_state,
+      d->chunk_start, d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, gl2, status);
+  return launched(what);
+}
+}  // namespace
+
 int mek_gdn_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* u, const float* g_cs, const float* h0,
                   void* h_tape, void* v_new, float* final_state, int32_t* status, void* stream) {
-  using namespace mek;
   if (int rc = check_dims(d, "fwd_h")) return rc;
-  const size_t smem = FwdHSmem::kBytes + 1024;
-  if (int rc = want_smem(gdn_fwd_h_kernel, smem, "fwd_h")) return rc;
-  gdn_fwd_h_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(u),
-      g_cs, h0, static_cast<__nv_bfloat16*>(h_tape), static_cast<__nv_bfloat16*>(v_new), final_state, d->chunk_start,
-      d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, nullptr, status);
-  return launched("fwd_h");
+  return launch_fwd_h(d, k, w, u, g_cs, h0, h_tape, v_new, final_state, nullptr, status, stream, "fwd_h");
 }
 
 int mek_kda_fwd_h(const MekGdnDims* d, const void* kr, const void* w, const void* u, const float* gl2, void* h_tape,
@@ -585,13 +634,7 @@ int mek_kda_fwd_h(const MekGdnDims* d, const void* kr, const void* w, const void
   if (int rc = check_dims(d, "kda_fwd_h")) return rc;
   if (d->num_qk_heads != d->num_v_heads) return fail(MEK_ERR_INVALID, "kda_fwd_h: KDA has one value head per key head");
   if (gl2 == nullptr) return fail(MEK_ERR_INVALID, "kda_fwd_h: gl2 is null");
-  const size_t smem = FwdHSmem::kBytes + 1024;
-  if (int rc = want_smem(gdn_fwd_h_kernel, smem, "kda_fwd_h")) return rc;
-  gdn_fwd_h_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(kr), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(u),
-      nullptr, nullptr, static_cast<__nv_bfloat16*>(h_tape), static_cast<__nv_bfloat16*>(v_new), nullptr,
-      d->chunk_start, d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, gl2, status);
-  return launched("kda_fwd_h");
+  return launch_fwd_h(d, kr, w, u, nullptr, nullptr, h_tape, v_new, nullptr, gl2, status, stream, "kda_fwd_h");
 }
 
 int mek_gdn_fwd_o(const MekGdnDims* d, const void* q, const void* aqk, const void* v_new, const void* h_tape,
@@ -600,10 +643,15 @@ int mek_gdn_fwd_o(const MekGdnDims* d, const void* q, const void* aqk, const voi
   if (int rc = check_dims(d, "fwd_o")) return rc;
   const size_t smem = FwdOSmem::kBytes + 1024;
   if (int rc = want_smem(gdn_fwd_o_kernel, smem, "fwd_o")) return rc;
+  const int64_t tiles = int64_t(d->num_chunks) * d->num_v_heads;
+  FwdOMaps maps;
+  if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_qk_heads, "fwd_o")) return rc;
+  if (int rc = make_rows_map(&maps.v_new, v_new, d->total_tokens, d->num_v_heads, "fwd_o")) return rc;
+  if (int rc = make_tiles_map(&maps.h, h_tape, tiles, 128, 128, "fwd_o")) return rc;
+  if (int rc = make_tiles_map(&maps.aqk, aqk, tiles, 64, 64, "fwd_o")) return rc;
   gdn_fwd_o_kernel<<<dim3(d->num_chunks, d->num_v_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(aqk),
-      static_cast<const __nv_bfloat16*>(v_new), static_cast<const __nv_bfloat16*>(h_tape), g_cs,
-      static_cast<__nv_bfloat16*>(o), d->chunk_start, d->chunk_len, d->num_qk_heads, d->num_v_heads, d->scale, status);
+      maps, g_cs, static_cast<__nv_bfloat16*>(o), d->chunk_start, d->chunk_len, d->num_qk_heads, d->num_v_heads,
+      d->scale, status);
   return launched("fwd_o");
 }
 

@@ -63,6 +63,15 @@ inline int make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint
   return MEK_OK;
 }
 
+// rows [tokens, heads * 128], read in boxes of 64 columns x 64 tokens
+inline int make_rows_map(CUtensorMap* map, const void* base, int64_t tokens, int heads, const char* what) {
+  return make_tile_map(map, base, uint64_t(tokens), uint64_t(heads) * 128, 64, what);
+}
+// tiles [num_tiles * rows, cols], read in boxes of 64 columns x `rows` rows
+inline int make_tiles_map(CUtensorMap* map, const void* base, int64_t num_tiles, int rows, int cols, const char* what) {
+  return make_tile_map(map, base, uint64_t(num_tiles) * rows, uint64_t(cols), uint32_t(rows), what);
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // device
 // ---------------------------------------------------------------------------------------------------------------
