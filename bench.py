@@ -183,6 +183,16 @@ KERNEL_BYTES.update({
                                    + 2 * 512 + 256 + 512 + 4) * HV,
     "qk_grad_finish": lambda H, HV: (512 + 256) * HV,
 })
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch in the committed ncu capture of an 8,192-token cut of cfg1
+# (H=16, HV=32; profiles/gdn_kernels_8192_tokens_full_set.md).  Every tensor is per token or per chunk, so traffic
+# grows in proportion to the tokens: `roofline.traffic` scales these to the launch that was timed.
+NCU_TRAFFIC_BYTES_AT_8192_TOKENS = {
+    "gdn_wy_fwd": 136.8e6 + 149.0e6,
+    "gdn_fwd_h": 170.7e6 + 159.7e6,
+    "gdn_fwd_o": 269.8e6 + 49.8e6,
+    "gdn_bwd_dh": 236.8e6 + 157.5e6,
+    "gdn_bwd_tail": 807.5e6 + 122.1e6,
+}
 KERNEL_FLOPS = {  # per (chunk, value head): dense contractions as 2 m n k
     "gdn_wy_fwd": 2 * 128 * 64 * 128 + 2 * 64**3 / 3 + 2 * 2 * 64 * 128 * 64,
     "gdn_fwd_h": 2 * 64 * 128 * 128 + 2 * 128 * 128 * 64,
@@ -318,7 +328,11 @@ def run_ours(args) -> None:
         roofline = {"bound": "tensor", "achieved": tfs, "peak": peak["bf16_tflops"], "unit": "TFLOP/s", "frac": frac_tc}
     else:
         roofline = {"bound": "hbm", "achieved": gbs, "peak": peak["hbm_gbs"], "unit": "GB/s", "frac": frac_hbm}
-    roofline.update(kernel=top, ms_per_launch=mean_ms, traffic=None, peak_source=f"of {peak_kind}",
+    traffic = None
+    if (H, HV) == (16, 32) and top in NCU_TRAFFIC_BYTES_AT_8192_TOKENS:
+        traffic = NCU_TRAFFIC_BYTES_AT_8192_TOKENS[top] * tokens / 8192
+    roofline.update(kernel=top, ms_per_launch=mean_ms, traffic=traffic, traffic_unit="bytes per launch",
+                    traffic_source="ncu capture at 8,192 tokens, scaled by tokens", peak_source=f"of {peak_kind}",
                     share_of_step=per_kernel[top][2] / sum(v[2] for v in per_kernel.values()))
 
     step_s = ms * 1e-3 / args.steps
