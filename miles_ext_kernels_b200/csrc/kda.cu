@@ -516,21 +516,29 @@ __global__ void __launch_bounds__(256) kda_tail_mma_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// tail, pairwise part: one block per (chunk, head), one thread per key channel
+// tail, pairwise part: one block per (chunk, head); thread (d, role) owns key channel d in one of two passes
 // ---------------------------------------------------------------------------------------------------------------
+// With E_ij = 2^{G_i - G_j} per channel (j <= i), M1 = scale tril(do v_new^T) and M2 = bf16(-tril(A^T dA A^T, -1)):
+//   row pass     RQ_i = sum_{j<=i} M1_ij k_j E_ij,  RK_i = sum_{j<i} M2_ij k_j E_ij     -> dq, the row part of dk, dg
+//   column pass  CC_j = sum_{i>=j} (M1_ij q_i + beta_i M2_ij k_i) E_ij                  -> the column part of dk, dg
+// No pair costs an exponential: E runs along a row or a column as a product of the per-token factors
+// R_i = 2^{G_i - G_{i-1}} <= 1 (E_{i,j-1} = E_ij R_j, E_{i+1,j} = E_ij R_{i+1}); all sums live in registers.  512
+// threads: thread (d, role, half) owns channel d in the row pass (role 0) or the column pass (role 1) for the even
+// (half 0) or odd (half 1) blocks of four rows / columns, so sixteen warps hide each other's latencies.
 struct KdaPairSmem {
-  static constexpr uint32_t kQ = 0;                  // fp32 [64][128] q, then the gate-gradient partials
+  static constexpr uint32_t kQ = 0;                  // fp32 [64][128] q
   static constexpr uint32_t kK = 32768;              // fp32 [64][128] k
-  static constexpr uint32_t kG = 2 * 32768;          // fp32 [64][128] G (log2)
-  static constexpr uint32_t kCC = 3 * 32768;         // fp32 [64][128] column-role sums
-  static constexpr uint32_t kDK = 4 * 32768;         // fp32 [64][128] row-role dk partials
-  static constexpr uint32_t kM1 = 5 * 32768;         // fp32 [64][64]
-  static constexpr uint32_t kM2 = kM1 + 16384;       // fp32 [64][64]
-  static constexpr uint32_t kBeta = kM2 + 16384;     // beta[64], db[64][4]
+  static constexpr uint32_t kR = 2 * 32768;          // fp32 [64][128] R
+  static constexpr uint32_t kCC = 3 * 32768;         // fp32 [64][128] column-pass sums
+  static constexpr uint32_t kM1 = 4 * 32768;         // fp32 [64][64] M1
+  static constexpr uint32_t kM2 = kM1 + 16384;       // fp32 [64][64] M2
+  static constexpr uint32_t kM1T = kM2 + 16384;      // fp32 [64][68] M1^T
+  static constexpr uint32_t kM2T = kM1T + 17408;     // fp32 [64][68] (beta_i M2_ij)^T
+  static constexpr uint32_t kBeta = kM2T + 17408;    // beta[64], db[64][4]
   static constexpr uint32_t kBytes = kBeta + 256 + 1024;
 };
 
-__global__ void __launch_bounds__(128) kda_tail_pair_kernel(
+__global__ void __launch_bounds__(512) kda_tail_pair_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const float* __restrict__ g2,
     const float* __restrict__ beta, const float* __restrict__ m1, const float* __restrict__ m2,
     const float* __restrict__ dqg, const float* __restrict__ dkr, const float* __restrict__ dkg,
@@ -539,76 +547,202 @@ __global__ void __launch_bounds__(128) kda_tail_pair_kernel(
     const int32_t* __restrict__ chunk_len, int num_heads) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 127) & ~uintptr_t(127));
-  const int d = threadIdx.x, warp = d >> 5, lane = d & 31;
+  const int tid = threadIdx.x, d = tid & 127, role = (tid >> 7) & 1, half = tid >> 8, warp = (tid >> 5) & 3;
+  const int lane = tid & 31;
   const int c = blockIdx.x, h = blockIdx.y;
   const int start = chunk_start[c], len = chunk_len[c];
   if (len <= 0) return;
   float* sQ = reinterpret_cast<float*>(sm + KdaPairSmem::kQ);
   float* sK = reinterpret_cast<float*>(sm + KdaPairSmem::kK);
-  float* sG = reinterpret_cast<float*>(sm + KdaPairSmem::kG);
+  float* sR = reinterpret_cast<float*>(sm + KdaPairSmem::kR);
   float* sCC = reinterpret_cast<float*>(sm + KdaPairSmem::kCC);
-  float* sDK = reinterpret_cast<float*>(sm + KdaPairSmem::kDK);
   float* sM1 = reinterpret_cast<float*>(sm + KdaPairSmem::kM1);
   float* sM2 = reinterpret_cast<float*>(sm + KdaPairSmem::kM2);
+  float* sM1T = reinterpret_cast<float*>(sm + KdaPairSmem::kM1T);
+  float* sM2T = reinterpret_cast<float*>(sm + KdaPairSmem::kM2T);
   float* s_beta = reinterpret_cast<float*>(sm + KdaPairSmem::kBeta);
   float* s_db = s_beta + 64;
   const int64_t stride = int64_t(num_heads) * kDim;
   const int64_t tile = int64_t(c) * num_heads + h;
   const int64_t col = int64_t(start) * stride + h * kDim + d;
 
-  for (int i = 0; i < len; ++i) {
-    const int64_t at = col + i * stride;
-    sQ[i * 128 + d] = __bfloat162float(q[at]);
-    sK[i * 128 + d] = __bfloat162float(k[at]);
-    sG[i * 128 + d] = g2[at];
-    sCC[i * 128 + d] = 0.f;
+  if (tid < 64) s_beta[tid] = tid < len ? beta[int64_t(start + tid) * num_heads + h] : 0.f;
+#pragma unroll 8
+  for (int i = tid >> 7; i < 64; i += 4) {  // rows past the chunk's length: q = k = 0, R = 1
+    const bool live = i < len;
+    const int64_t at = col + int64_t(live ? i : 0) * stride;
+    sQ[i * 128 + d] = live ? __bfloat162float(q[at]) : 0.f;
+    sK[i * 128 + d] = live ? __bfloat162float(k[at]) : 0.f;
+    sR[i * 128 + d] = (live && i > 0) ? fast_exp2(g2[at] - g2[at - stride]) : 1.f;
   }
-  for (int i = d; i < 4096; i += 128) {
-    sM1[i] = m1[tile * 4096 + i];
-    sM2[i] = m2[tile * 4096 + i];
+  __syncthreads();  // beta is in place for the transposed copy of M2
+#pragma unroll 8
+  for (int i = tid; i < 4096; i += 512) {  // M and its transpose (rows of 68 floats: 16-byte aligned, few conflicts)
+    const float a = m1[tile * 4096 + i], b = m2[tile * 4096 + i];
+    const int ii = i >> 6, jj = i & 63;
+    sM1[i] = a;
+    sM2[i] = b;
+    sM1T[jj * 68 + ii] = a;
+    sM2T[jj * 68 + ii] = s_beta[ii] * b;
   }
-  if (d < 64) s_beta[d] = d < len ? beta[int64_t(start + d) * num_heads + h] : 0.f;
   __syncthreads();
 
-  const float gl = sG[(len - 1) * 128 + d];
   float chunk_end = 0.f;
-  for (int i = 0; i < len; ++i) {
-    const float qi = sQ[i * 128 + d], ki = sK[i * 128 + d], gi = sG[i * 128 + d], bi = s_beta[i];
-    float rq = 0.f, rk = 0.f;
-    for (int j = 0; j <= i; ++j) {
-      const float e = fast_exp2(gi - sG[j * 128 + d]);  // j <= i: the exponent is <= 0
-      const float kj = sK[j * 128 + d] * e;
-      const float a = sM1[i * 64 + j], b = sM2[i * 64 + j];  // M2 is zero on the diagonal
-      rq = fmaf(a, kj, rq);
-      rk = fmaf(b, kj, rk);
-      sCC[j * 128 + d] = fmaf(fmaf(a, qi, bi * b * ki), e, sCC[j * 128 + d]);
-    }
-    const int64_t at = col + i * stride;
-    const float eg = fast_exp2(gi), er = fast_exp2(gl - gi);
-    const float qgr = round_bf16(qi * eg), kgr = round_bf16(ki * eg), krr = round_bf16(ki * er);
-    const float xq = dqg[at], xr = dkr[at], xg = dkg[at];
-    dq[at] = fmaf(xq, eg, rq);
-    sDK[i * 128 + d] = fmaf(bi, rk, fmaf(xr, er, xg * eg));
-    sQ[i * 128 + d] = qi * rq + ki * bi * rk + xq * qgr + xg * kgr - xr * krr;  // q_i is not read again
-    chunk_end = fmaf(xr, krr, chunk_end);
-    float db = ki * rk;  // dbeta_i += sum_d k_id RK'_id
+  if (role == 0) {
+    // ---- row pass: four rows at a time.  For j below the block, E_{i0+r, j} = E_{i0, j} E_{i0+r, i0}: the four rows
+    // share k_j E_{i0, j} and take their own factor (<= 1) once at the end; the 4 x 4 diagonal block is done apart.
+    const float gl = g2[col + int64_t(len - 1) * stride];
+    for (int i0 = 4 * half; i0 < len; i0 += 8) {
+      float rq[4] = {0.f, 0.f, 0.f, 0.f}, rk[4] = {0.f, 0.f, 0.f, 0.f};
+      float gi4[4], xq4[4], xr4[4], xg4[4];  // the rows' global operands, in flight while the sums run
 #pragma unroll
-    for (int m = 16; m >= 1; m >>= 1) db += __shfl_xor_sync(0xffffffffu, db, m);
-    if (lane == 0) s_db[i * 4 + warp] = db;
+      for (int r = 0; r < 4; ++r) {
+        const int64_t at = col + int64_t(i0 + r < len ? i0 + r : len - 1) * stride;
+        gi4[r] = g2[at], xq4[r] = dqg[at], xr4[r] = dkr[at], xg4[r] = dkg[at];
+      }
+      float e = sR[i0 * 128 + d];  // E_{i0, i0 - 1}
+      for (int j0 = i0 - 4; j0 >= 0; j0 -= 4) {
+        float av[4][4], bv[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float4 a = *reinterpret_cast<const float4*>(sM1 + (i0 + r) * 64 + j0);
+          const float4 b = *reinterpret_cast<const float4*>(sM2 + (i0 + r) * 64 + j0);
+          av[r][0] = a.x, av[r][1] = a.y, av[r][2] = a.z, av[r][3] = a.w;
+          bv[r][0] = b.x, bv[r][1] = b.y, bv[r][2] = b.z, bv[r][3] = b.w;
+        }
+#pragma unroll
+        for (int t = 3; t >= 0; --t) {
+          const float kj = sK[(j0 + t) * 128 + d] * e;
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            rq[r] = fmaf(av[r][t], kj, rq[r]);
+            rk[r] = fmaf(bv[r][t], kj, rk[r]);
+          }
+          e *= sR[(j0 + t) * 128 + d];
+        }
+      }
+      float r4[4], k4[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) r4[r] = sR[(i0 + r) * 128 + d], k4[r] = sK[(i0 + r) * 128 + d];
+      {
+        float f = 1.f;
+#pragma unroll
+        for (int r = 1; r < 4; ++r) {
+          f *= r4[r];  // E_{i0 + r, i0}
+          rq[r] *= f;
+          rk[r] *= f;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {  // the diagonal block: pairs (i0 + r, i0 + t), t <= r
+        const float4 a = *reinterpret_cast<const float4*>(sM1 + (i0 + r) * 64 + i0);
+        const float4 b = *reinterpret_cast<const float4*>(sM2 + (i0 + r) * 64 + i0);  // zero on the diagonal
+        const float at4[4] = {a.x, a.y, a.z, a.w}, bt4[4] = {b.x, b.y, b.z, b.w};
+        float ee = 1.f;
+#pragma unroll
+        for (int t = r; t >= 0; --t) {
+          const float kj = k4[t] * ee;
+          rq[r] = fmaf(at4[t], kj, rq[r]);
+          rk[r] = fmaf(bt4[t], kj, rk[r]);
+          ee *= r4[t];
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int i = i0 + r;
+        float db = 0.f;
+        if (i < len) {
+          const float qi = sQ[i * 128 + d], ki = k4[r], bi = s_beta[i];
+          const int64_t at = col + i * stride;
+          const float gi = gi4[r];
+          const float eg = fast_exp2(gi), er = fast_exp2(gl - gi);
+          const float qgr = round_bf16(qi * eg), kgr = round_bf16(ki * eg), krr = round_bf16(ki * er);
+          const float xq = xq4[r], xr = xr4[r], xg = xg4[r];
+          dq[at] = fmaf(xq, eg, rq[r]);
+          dk[at] = fmaf(bi, rk[r], fmaf(xr, er, xg * eg));                             // + the column part below
+          dg[at] = qi * rq[r] + ki * bi * rk[r] + xq * qgr + xg * kgr - xr * krr;      // likewise
+          chunk_end = fmaf(xr, krr, chunk_end);
+          db = ki * rk[r];  // dbeta_i += sum_d k_id RK_id
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) db += __shfl_xor_sync(0xffffffffu, db, m);
+        if (lane == 0 && i < len) s_db[i * 4 + warp] = db;
+      }
+    }
+    if (half == 0) chunk_end = fmaf(fast_exp2(gl), hdh[tile * kDim + d], chunk_end);
+  } else {
+    // ---- column pass: four columns at a time.  For i below the block, E_{i, j0+c} = E_{i, j0+3} E_{j0+3, j0+c}.
+    for (int j0 = 4 * half; j0 < len; j0 += 8) {
+      float cc[4] = {0.f, 0.f, 0.f, 0.f};
+      float e = 1.f;
+      for (int i0 = j0 + 4; i0 < len; i0 += 4) {  // rows at or past the chunk's length hold q = k = 0 and R = 1
+        float av[4][4], bv[4][4];
+#pragma unroll
+        for (int cidx = 0; cidx < 4; ++cidx) {
+          const float4 a = *reinterpret_cast<const float4*>(sM1T + (j0 + cidx) * 68 + i0);
+          const float4 b = *reinterpret_cast<const float4*>(sM2T + (j0 + cidx) * 68 + i0);
+          av[cidx][0] = a.x, av[cidx][1] = a.y, av[cidx][2] = a.z, av[cidx][3] = a.w;
+          bv[cidx][0] = b.x, bv[cidx][1] = b.y, bv[cidx][2] = b.z, bv[cidx][3] = b.w;
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          e *= sR[(i0 + t) * 128 + d];  // E_{i0 + t, j0 + 3}
+          const float tq = sQ[(i0 + t) * 128 + d] * e, tk = sK[(i0 + t) * 128 + d] * e;
+#pragma unroll
+          for (int cidx = 0; cidx < 4; ++cidx) cc[cidx] = fmaf(av[cidx][t], tq, fmaf(bv[cidx][t], tk, cc[cidx]));
+        }
+      }
+      float r4[4], k4[4], q4[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        r4[r] = sR[(j0 + r) * 128 + d], k4[r] = sK[(j0 + r) * 128 + d], q4[r] = sQ[(j0 + r) * 128 + d];
+      {
+        float f = 1.f;
+#pragma unroll
+        for (int cidx = 2; cidx >= 0; --cidx) {
+          f *= r4[cidx + 1];  // E_{j0 + 3, j0 + cidx}
+          cc[cidx] *= f;
+        }
+      }
+#pragma unroll
+      for (int cidx = 0; cidx < 4; ++cidx) {  // the diagonal block: pairs (j0 + r, j0 + cidx), r >= cidx
+        const float4 a = *reinterpret_cast<const float4*>(sM1T + (j0 + cidx) * 68 + j0);
+        const float4 b = *reinterpret_cast<const float4*>(sM2T + (j0 + cidx) * 68 + j0);
+        const float at4[4] = {a.x, a.y, a.z, a.w}, bt4[4] = {b.x, b.y, b.z, b.w};
+        float ee = 1.f;
+#pragma unroll
+        for (int r = cidx; r < 4; ++r) {
+          if (r > cidx) ee *= r4[r];
+          cc[cidx] = fmaf(fmaf(at4[r], q4[r], bt4[r] * k4[r]), ee, cc[cidx]);
+        }
+        sCC[(j0 + cidx) * 128 + d] = cc[cidx];
+      }
+    }
   }
-  chunk_end = fmaf(fast_exp2(gl), hdh[tile * kDim + d], chunk_end);
-  float running = 0.f;
-  for (int i = len - 1; i >= 0; --i) {
+  float* s_end = sR;  // after the passes: the chunk-end term per channel (two halves) in R's space ...
+  float* s_dg = sQ;   // ... and the per-row gate gradients in q's space
+  __syncthreads();
+  if (role == 0) s_end[half * 128 + d] = chunk_end;
+  __syncthreads();
+  // every thread: the column parts join the row parts (which the row pass left in dk and dg) -- elementwise, so the
+  // global reads overlap; the block barriers above order the row pass's global writes before these reads
+#pragma unroll 8
+  for (int i = tid >> 7; i < len; i += 4) {
     const int64_t at = col + i * stride;
     const float cc = sCC[i * 128 + d];
-    dk[at] = sDK[i * 128 + d] + cc;
-    float dgi = sQ[i * 128 + d] - sK[i * 128 + d] * cc;
-    if (i == len - 1) dgi += chunk_end;
-    running += dgi;
-    dg[at] = running;
+    dk[at] += cc;
+    float dgi = dg[at] - sK[i * 128 + d] * cc;
+    if (i == len - 1) dgi += s_end[d] + s_end[128 + d];
+    s_dg[i * 128 + d] = dgi;
   }
   __syncthreads();
-  if (d < len) {
+  if (tid < 128) {  // the in-chunk suffix sum, one channel per thread
+    float running = 0.f;
+    for (int i = len - 1; i >= 0; --i) {
+      running += s_dg[i * 128 + d];
+      dg[col + i * stride] = running;
+    }
+  } else if (tid < 256 && d < len) {
     const int64_t at = int64_t(start + d) * num_heads + h;
     dbeta[at] = dbeta_part[at] + ((s_db[d * 4] + s_db[d * 4 + 1]) + (s_db[d * 4 + 2] + s_db[d * 4 + 3]));
   }
@@ -700,7 +834,7 @@ int mek_kda_bwd_tail(const MekGdnDims* d, const void* q, const void* k, const vo
                                                 In(dv_new), In(d_o), m1, m2, dqg, dkr, dkg, hdh, Out(dv), dbeta_part,
                                                 d->chunk_start, d->chunk_len, d->num_v_heads, d->scale, status);
   if (int rc = launched("kda_bwd_tail (tensor-core part)")) return rc;
-  kda_tail_pair_kernel<<<grid, 128, smem_b, s>>>(In(q), In(k), g2, beta, m1, m2, dqg, dkr, dkg, hdh, dbeta_part, dq32,
+  kda_tail_pair_kernel<<<grid, 512, smem_b, s>>>(In(q), In(k), g2, beta, m1, m2, dqg, dkr, dkg, hdh, dbeta_part, dq32,
                                                  dk32, dg, dbeta, d->chunk_start, d->chunk_len, d->num_v_heads);
   return launched("kda_bwd_tail (pairwise part)");
 }
