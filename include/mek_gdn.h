@@ -157,13 +157,17 @@ int mek_kda_intra(const MekGdnDims* dims, const void* q, const void* k, const vo
                   const float* beta, void* a_out, void* aqk_out, void* w_out, void* u_out, int32_t* status,
                   void* stream);
 
-/* The GDN scan / output / adjoint-scan kernels on the decayed operands (kr, qg) with a per-channel chunk decay. */
-int mek_kda_fwd_h(const MekGdnDims* dims, const void* kr, const void* w, const void* u, const float* gl2, void* h_tape,
-                  void* v_new, int32_t* status, void* stream);
+/* The GDN scan / output / adjoint-scan kernels on the decayed operands (kr, qg) with a per-channel chunk decay.
+ * h0 / final_state and dht / dh0: fp32 [N, H, 128, 128] per document, or null (zero initial state, nothing kept):
+ * the states that cross rank boundaries under context parallelism (reference:
+ * miles_ext_kernels/cake/_impl/kda/kcp.py:126-214). */
+int mek_kda_fwd_h(const MekGdnDims* dims, const void* kr, const void* w, const void* u, const float* gl2,
+                  const float* h0, void* h_tape, void* v_new, float* final_state, int32_t* status, void* stream);
 int mek_kda_fwd_o(const MekGdnDims* dims, const void* qg, const void* aqk, const void* v_new, const void* h_tape,
                   void* o, int32_t* status, void* stream);
 int mek_kda_bwd_dh(const MekGdnDims* dims, const void* qg, const void* kr, const void* w, const void* d_o,
-                   const void* aqk, const float* gl2, void* dh_tape, void* dv_new, int32_t* status, void* stream);
+                   const void* aqk, const float* gl2, const float* dht, void* dh_tape, void* dv_new, float* dh0,
+                   int32_t* status, void* stream);
 
 /* Gradient tail: dq32, dk32 fp32 [T, H, 128] (before the norm's pull-back and the rounding), dv bf16 [T, H, 128],
  * dg fp32 [T, H, 128] (in-chunk suffix sum included), dbeta fp32 [T, H].  Scratch the caller provides: m1, m2 fp32

@@ -1,0 +1,239 @@
+"""Context-parallel packed KDA: one packed batch split into contiguous token slices over the ranks of a process group,
+with the per-document state crossing the rank boundaries exactly.
+
+Entry points and argument meaning follow the reference (reference: miles_ext_kernels/cake/_impl/kda/kcp.py:86-230)::
+
+    part = partition_kcp(cu_seqlens_global_cpu, world_size)   # the same object on every rank
+    ctx = build_context_kcp(part, group, rank, device)         # this rank's tables and boundary flags
+    out_local = chunk_kda_kcp(q_local, k_local, v_local, g_local, beta_local, ctx)   # autograd
+
+A rank's operands are its shard (the tokens of its slice), with the shapes, dtypes and modes of the single-rank
+:func:`chunk_kda`.  Forward: the ``[H, 128, 128]`` fp32 state at the end of this rank's last fragment goes to the next
+rank when the document continues there; backward: the adjoint state at the start of this rank's first fragment goes
+to the previous rank.  The hand-over is sequential along the rank chain (point to point on the group's backend) and
+reproduces the single-rank recurrence: bit for bit when the rank boundaries fall on multiples of 64 tokens inside
+their documents, within the accuracy budgets otherwise (the chunking restarts at a boundary).
+
+Only the ``"contiguous"`` layout is served (``"zigzag"``, ``"zigzag_per_document"`` and explicit fragments raise
+``NotImplementedError``), and no package options (``save_mode``, ``graph``, ...).
+
+In the raw gate mode the gradients of ``A_log`` / ``dt_bias`` are this rank's partial sums;
+:func:`reduce_gate_param_grads_kcp` sums them over the group in rank order, the same bits on every rank.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+from ..._runtime import config
+from ..gdn.kcp import KcpContext
+from . import ops
+
+__all__ = [
+    "KcpPartition",
+    "build_context_kcp",
+    "chunk_kda_bwd_kcp",
+    "chunk_kda_fwd_kcp",
+    "chunk_kda_kcp",
+    "partition_kcp",
+    "reduce_gate_param_grads_kcp",
+]
+
+
+@dataclass(frozen=True)
+class KcpPartition:
+    """The partition of one packed batch: the global document offsets, the number of ranks and the layout."""
+
+    cu_seqlens_global: tuple[int, ...]
+    world_size: int
+    layout: str = "contiguous"
+
+
+def partition_kcp(cu_seqlens_global_cpu: Any, world_size: int, layout: str = "contiguous", fragments: Any = None, *,
+                  cut_points: Any = None) -> KcpPartition:
+    """The context-parallel partition of one packed batch over ``world_size`` ranks (equal token shares in order).
+    ``cu_seqlens_global_cpu``: the whole batch's ``[num_docs + 1]`` document offsets on the host."""
+    if layout != "contiguous" or fragments is not None or cut_points is not None:
+        raise NotImplementedError(
+            f"partition_kcp: only the 'contiguous' layout without explicit fragments or cut points is served, not "
+            f"{layout!r}"
+        )
+    if isinstance(cu_seqlens_global_cpu, torch.Tensor):
+        if cu_seqlens_global_cpu.is_cuda:
+            raise ValueError("partition_kcp: cu_seqlens_global_cpu must be on the host")
+        cu_seqlens_global_cpu = cu_seqlens_global_cpu.tolist()
+    cu = tuple(int(b) for b in cu_seqlens_global_cpu)
+    if len(cu) < 2 or cu[0] != 0 or any(b < a for a, b in zip(cu, cu[1:])):
+        raise ValueError("partition_kcp: the document offsets must start at 0 and not decrease")
+    world_size = int(world_size)
+    if world_size < 1:
+        raise ValueError(f"partition_kcp: world_size must be positive, got {world_size}")
+    if cu[-1] % world_size:
+        raise ValueError(f"partition_kcp: a contiguous partition needs the token count ({cu[-1]}) to divide by the "
+                         f"world size ({world_size})")
+    return KcpPartition(cu, world_size, layout)
+
+
+def build_context_kcp(part: KcpPartition, group: Any, rank: int, device: Any, conv_kernel_size: int = 4, *,
+                      sm_count: int | None = None, heads: Any = None, stream: Any = None) -> KcpContext:
+    """This rank's context of ``part``: the argument of every KCP entry point, reusable across the calls and layers
+    of the same batch layout.  ``group`` is the context-parallel process group (``None`` for a one-rank partition).
+    ``sm_count``, ``heads`` and ``stream`` are accepted for the reference's signature; there is one launch plan and
+    the context's table copy is a few hundred bytes.  No collective runs here."""
+    if not isinstance(part, KcpPartition):
+        raise TypeError(f"build_context_kcp: part must come from partition_kcp, got {type(part).__name__}")
+    if group is None and part.world_size != 1:
+        raise ValueError("build_context_kcp: a partition over several ranks needs its process group")
+    if heads is not None:
+        for count in (heads if isinstance(heads, (list, tuple)) else (heads,)):
+            ops.check_heads(count)
+    return KcpContext(part.cu_seqlens_global, group, int(rank), part.world_size, device, conv_kernel_size, part.layout)
+
+
+def _no_options(options: dict[str, Any]) -> None:
+    if options:
+        raise NotImplementedError(f"the KCP entry points take no package options here, got {sorted(options)}")
+
+
+def _context(ctx: Any) -> KcpContext:
+    if not isinstance(ctx, KcpContext):
+        raise TypeError(f"ctx must be a context built by build_context_kcp, got {type(ctx).__name__}")
+    return ctx
+
+
+def _shard(q, k, v, g, beta, ctx: KcpContext):
+    q3, k3, v3, g3 = (ops._packed3(t, n).contiguous() for t, n in ((q, "q"), (k, "k"), (v, "v"), (g, "g")))
+    beta3 = ops._packed_beta(beta)
+    g3 = g3 if g3.dtype == torch.float32 else g3.float()
+    ops._check(q3, k3, v3, g3, beta3, ctx.cu_seqlens)
+    if q3.shape[0] != ctx.num_tokens:
+        raise ValueError(f"this rank's shard must hold the {ctx.num_tokens} tokens of its slice; q has {q3.shape[0]}")
+    return q3, k3, v3, g3, beta3.float().contiguous()
+
+
+def _forward_kcp(q3, k3, v3, g3, beta32, ctx: KcpContext, scale: float, l2norm: bool):
+    exchange = ctx.exchange()
+    num_seqs, heads = len(ctx.cu_seqlens_cpu) - 1, q3.shape[1]
+    with torch.cuda.device(q3.device):
+        h0 = exchange.incoming_state(num_seqs, heads, q3.device)
+        want_final = ctx.continues_out and ctx.world_size > 1
+        o, saved, final = ops._forward(q3, k3, v3, g3, beta32, ctx.cu_seqlens, scale, l2norm,
+                                       cu_seqlens_cpu=ctx.cu_seqlens_cpu, h0=h0, want_final=want_final)
+        if want_final:
+            exchange.outgoing_state(final)
+    return o, saved
+
+
+def _backward_kcp(saved, v3, beta32, do3, ctx: KcpContext):
+    exchange = ctx.exchange()
+    num_seqs, heads = len(ctx.cu_seqlens_cpu) - 1, v3.shape[1]
+    with torch.cuda.device(v3.device):
+        dht = exchange.incoming_adjoint(num_seqs, heads, v3.device)
+        want_dh0 = ctx.continues_in and ctx.world_size > 1
+        dq, dk, dv, dg, dbeta, dh0 = ops._backward(saved, v3, beta32, do3, dht=dht, want_dh0=want_dh0)
+        if want_dh0:
+            exchange.outgoing_adjoint(dh0)
+    return dq, dk, dv, dg, dbeta
+
+
+class _ChunkKdaKcp(torch.autograd.Function):
+    @staticmethod
+    def forward(fn, q, k, v, g, beta, ctx, scale, l2norm):
+        q3, k3, v3, g3, beta32 = _shard(q, k, v, g, beta, ctx)
+        o, saved = _forward_kcp(q3, k3, v3, g3, beta32, ctx, scale, l2norm)
+        fn.saved, fn.v, fn.beta32, fn.kcp = saved, v3, beta32, ctx
+        fn.shapes = (q.shape, g.shape, beta.shape)
+        fn.dtypes = (g.dtype, beta.dtype)
+        return o.view(q.shape)
+
+    @staticmethod
+    def backward(fn, do):
+        shape, g_shape, beta_shape = fn.shapes
+        do3 = ops._packed3(do, "dout").contiguous().to(torch.bfloat16)
+        dq, dk, dv, dg, dbeta = _backward_kcp(fn.saved, fn.v, fn.beta32, do3, fn.kcp)
+        g_dtype, beta_dtype = fn.dtypes
+        return (dq.view(shape), dk.view(shape), dv.view(shape), dg.view(g_shape).to(g_dtype),
+                dbeta.view(beta_shape).to(beta_dtype), None, None, None)
+
+
+def chunk_kda_kcp(q, k, v, g, beta, ctx, *, scale=None, use_gate_in_kernel=False, A_log=None, dt_bias=None,
+                  lower_bound=None, use_qk_l2norm_in_kernel=False, **options):
+    """The context-parallel autograd node of this rank's slice: ``out`` BF16 like ``v`` (this rank's tokens), with
+    gradients to ``q, k, v, g, beta`` and, in the raw gate mode, to ``A_log`` / ``dt_bias`` (this rank's partial sums).
+    Every rank of the group calls it in the same order (reference: kcp.py:126-155)."""
+    _no_options(options)
+    ctx = _context(ctx)
+    ops.check_heads(int(v.shape[-2]))
+    config.variant(ops.OP)
+    v, beta = ops.seam(v, beta)
+    gate = ops._gate(g, use_gate_in_kernel, A_log, dt_bias, lower_bound)
+    return _ChunkKdaKcp.apply(q, k, v, gate, beta, ctx, ops.DEFAULT_SCALE if scale is None else float(scale),
+                              bool(use_qk_l2norm_in_kernel))
+
+
+def chunk_kda_fwd_kcp(q, k, v, g, beta, ctx, *, scale=None, save_for_backward=True, use_gate_in_kernel=False,
+                      A_log=None, dt_bias=None, lower_bound=None, use_qk_l2norm_in_kernel=False, **options):
+    """The context-parallel forward alone: ``(out, saved)`` (reference: kcp.py:158-184)."""
+    _no_options(options)
+    ctx = _context(ctx)
+    ops.check_heads(int(v.shape[-2]))
+    v, beta = ops.seam(v, beta)
+    with torch.no_grad():
+        gate = ops._gate(g, use_gate_in_kernel, A_log, dt_bias, lower_bound)
+        q3, k3, v3, g3, beta32 = _shard(q, k, v, gate, beta, ctx)
+        o, saved = _forward_kcp(q3, k3, v3, g3, beta32, ctx, ops.DEFAULT_SCALE if scale is None else float(scale),
+                                bool(use_qk_l2norm_in_kernel))
+    return o.view(q.shape), (saved if save_for_backward else None)
+
+
+def chunk_kda_bwd_kcp(q, k, v, g, beta, ctx, dout, *, saved=None, scale=None, use_gate_in_kernel=False, A_log=None,
+                      dt_bias=None, lower_bound=None, use_qk_l2norm_in_kernel=False, **options):
+    """The context-parallel backward alone: ``(dq, dk, dv, dbeta, dg)`` and, in the raw gate mode,
+    ``(..., dA_log, ddt_bias)`` (this rank's partial sums); ``saved=None`` replays the forward, its exchange
+    included (reference: kcp.py:187-220)."""
+    _no_options(options)
+    ctx = _context(ctx)
+    ops.check_heads(int(v.shape[-2]))
+    beta_dtype = beta.dtype
+    v, beta = ops.seam(v, beta)
+    if saved is None:
+        _, saved = chunk_kda_fwd_kcp(q, k, v, g, beta, ctx, scale=scale, use_gate_in_kernel=use_gate_in_kernel,
+                                     A_log=A_log, dt_bias=dt_bias, lower_bound=lower_bound,
+                                     use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel)
+    v3 = ops._packed3(v, "v").contiguous()
+    beta32 = ops._packed_beta(beta).float().contiguous()
+    do3 = ops._packed3(dout, "dout").contiguous().to(torch.bfloat16)
+    with torch.no_grad():
+        dq, dk, dv, dg, dbeta = _backward_kcp(saved, v3, beta32, do3, ctx)
+    grads = [dq.view(q.shape), dk.view(q.shape), dv.view(v.shape), dbeta.view(beta.shape).to(beta_dtype),
+             dg.view(g.shape)]
+    if use_gate_in_kernel:
+        raw = g.detach().requires_grad_(True)
+        a_leaf, b_leaf = A_log.detach().requires_grad_(True), dt_bias.detach().requires_grad_(True)
+        gate = ops._activate(raw, a_leaf, b_leaf, lower_bound)
+        draw, da, db = torch.autograd.grad(gate, [raw, a_leaf, b_leaf], dg.view(gate.shape))
+        grads[4] = draw
+        grads += [da, db]
+    return tuple(grads)
+
+
+def reduce_gate_param_grads_kcp(ctx, dA_log: torch.Tensor, ddt_bias: torch.Tensor):
+    """The raw gate mode's full ``(dA_log, ddt_bias)`` from every rank's partial sums: one all-gather on the
+    context's group, then an FP32 sum in rank order, so every rank gets the same bits whatever the collective's
+    algorithm (reference: kcp.py:223-230).  Every rank of the group calls it with the same shapes."""
+    ctx = _context(ctx)
+    if ctx.world_size == 1 or ctx.group is None and not torch.distributed.is_initialized():
+        return dA_log.clone(), ddt_bias.clone()
+    import torch.distributed as dist
+
+    packed = torch.cat([dA_log.reshape(-1).float(), ddt_bias.reshape(-1).float()])
+    gathered = [torch.empty_like(packed) for _ in range(ctx.world_size)]
+    dist.all_gather(gathered, packed, group=ctx.group)
+    total = gathered[0].clone()
+    for part in gathered[1:]:
+        total += part
+    n = dA_log.numel()
+    return total[:n].view(dA_log.shape).to(dA_log.dtype), total[n:].view(ddt_bias.shape).to(ddt_bias.dtype)

@@ -129,11 +129,14 @@ class Saved:
     status: torch.Tensor
 
 
-def _forward(q, k, v, g, beta32, cu_seqlens, scale, use_qk_l2norm):
-    """q, k, v ``[S, H, 128]`` bf16 contiguous; g fp32 ``[S, H, 128]``; beta32 fp32 ``[S, H]``."""
+def _forward(q, k, v, g, beta32, cu_seqlens, scale, use_qk_l2norm, *, cu_seqlens_cpu=None, h0=None,
+             want_final=False):
+    """q, k, v ``[S, H, 128]`` bf16 contiguous; g fp32 ``[S, H, 128]``; beta32 fp32 ``[S, H]``.  ``h0`` (fp32
+    ``[N, H, 128, 128]`` or None) and ``want_final`` are the boundary states of a context-parallel call; returns
+    ``(o, saved, final_state | None)``."""
     device = q.device
     S, H = q.shape[0], q.shape[1]
-    meta = meta_module.chunk_meta(cu_seqlens, None, 1, S, device)
+    meta = meta_module.chunk_meta(cu_seqlens, cu_seqlens_cpu, 1, S, device)
     NC = meta.num_chunks
     dims = dims_of(meta, H, H, scale)
     status = torch.zeros(1, dtype=torch.int32, device=device)
@@ -154,14 +157,19 @@ def _forward(q, k, v, g, beta32, cu_seqlens, scale, use_qk_l2norm):
     native.launch("kda_intra", dims, q, k, v, kg, g2, beta32, a, aqk, w, u, status, device=device)
     h = torch.zeros((NC, H, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
     v_new = torch.empty_like(v)
-    native.launch("kda_fwd_h", dims, kr, w, u, gl2, h, v_new, status, device=device)
+    final = None
+    if want_final:
+        final = torch.empty((meta.num_seqs, H, HEAD_DIM, HEAD_DIM), dtype=F32, device=device)
+    native.launch("kda_fwd_h", dims, kr, w, u, gl2, h0, h, v_new, final, status, device=device)
     o = torch.empty_like(v)
     native.launch("kda_fwd_o", dims, qg, aqk, v_new, h, o, status, device=device)
     saved = Saved(meta, scale, q, k, q_raw, k_raw, rstd_q, rstd_k, g2, gl2, qg, kg, kr, a, aqk, w, h, v_new, status)
-    return o, saved
+    return o, saved, final
 
 
-def _backward(s: Saved, v, beta32, do):
+def _backward(s: Saved, v, beta32, do, *, dht=None, want_dh0=False):
+    """Returns ``(dq, dk, dv, dg, dbeta, dh0 | None)``; ``dht`` / ``want_dh0``: the boundary adjoint states of a
+    context-parallel call (fp32 ``[N, H, 128, 128]``)."""
     device = do.device
     S, H = v.shape[0], v.shape[1]
     meta = s.meta
@@ -170,7 +178,9 @@ def _backward(s: Saved, v, beta32, do):
     take = lambda role, shape, dtype: workspace.take(OP, role, shape, dtype, device)  # noqa: E731
     dh = torch.zeros((NC, H, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)  # pad chunks are never written
     dv_new = take("dv_new", (S, H, HEAD_DIM), BF16)
-    native.launch("kda_bwd_dh", dims, s.qg, s.kr, s.w, do, s.aqk, s.gl2, dh, dv_new, s.status, device=device)
+    dh0 = torch.empty((meta.num_seqs, H, HEAD_DIM, HEAD_DIM), dtype=F32, device=device) if want_dh0 else None
+    native.launch("kda_bwd_dh", dims, s.qg, s.kr, s.w, do, s.aqk, s.gl2, dht, dh, dv_new, dh0, s.status,
+                  device=device)
     m1 = take("m1", (NC, H, 64, 64), F32)
     m2 = take("m2", (NC, H, 64, 64), F32)
     dqg, dkr, dkg = (take(role, (S, H, HEAD_DIM), F32) for role in ("dqg", "dkr", "dkg"))
@@ -185,7 +195,7 @@ def _backward(s: Saved, v, beta32, do):
     dq, dk = torch.empty_like(v), torch.empty_like(v)
     native.launch("qk_grad_finish", dq32, s.q_raw, s.rstd_q, dq, S * H, device=device)
     native.launch("qk_grad_finish", dk32, s.k_raw, s.rstd_k, dk, S * H, device=device)
-    return dq, dk, dv, dg, dbeta
+    return dq, dk, dv, dg, dbeta, dh0
 
 
 class _ChunkKda(torch.autograd.Function):
@@ -198,7 +208,7 @@ class _ChunkKda(torch.autograd.Function):
         _check(q3, k3, v3, g3, beta3, cu_seqlens)
         beta32 = beta3.float().contiguous()
         with torch.cuda.device(q.device):
-            o, saved = _forward(q3, k3, v3, g3, beta32, cu_seqlens, scale, use_qk_l2norm)
+            o, saved, _ = _forward(q3, k3, v3, g3, beta32, cu_seqlens, scale, use_qk_l2norm)
         ctx.saved, ctx.v, ctx.beta32 = saved, v3, beta32
         ctx.shapes = (shape, g.shape, beta.shape)
         ctx.dtypes = (g.dtype, beta.dtype)
@@ -211,7 +221,7 @@ class _ChunkKda(torch.autograd.Function):
         if do3.dtype != BF16:
             do3 = do3.to(BF16)
         with torch.cuda.device(do.device):
-            dq, dk, dv, dg, dbeta = _backward(ctx.saved, ctx.v, ctx.beta32, do3)
+            dq, dk, dv, dg, dbeta, _ = _backward(ctx.saved, ctx.v, ctx.beta32, do3)
         g_dtype, beta_dtype = ctx.dtypes
         return (dq.view(shape), dk.view(shape), dv.view(shape), dg.view(g_shape).to(g_dtype),
                 dbeta.view(beta_shape).to(beta_dtype), None, None, None)
@@ -245,8 +255,8 @@ def chunk_kda_fwd(q, k, v, g, beta, cu_seqlens, *, scale=None, save_for_backward
         beta3 = _packed_beta(beta)
         _check(q3, k3, v3, g3, beta3, cu_seqlens)
         with torch.cuda.device(q.device):
-            o, saved = _forward(q3, k3, v3, g3.float(), beta3.float().contiguous(), cu_seqlens,
-                                DEFAULT_SCALE if scale is None else float(scale), bool(use_qk_l2norm_in_kernel))
+            o, saved, _ = _forward(q3, k3, v3, g3.float(), beta3.float().contiguous(), cu_seqlens,
+                                   DEFAULT_SCALE if scale is None else float(scale), bool(use_qk_l2norm_in_kernel))
     return o.view(q.shape), (saved if save_for_backward else None)
 
 
@@ -266,7 +276,7 @@ def chunk_kda_bwd(q, k, v, g, beta, cu_seqlens, dout, *, saved=None, scale=None,
     beta3 = _packed_beta(beta)
     do3 = _packed3(dout, "dout").contiguous().to(BF16)
     with torch.no_grad(), torch.cuda.device(v.device):
-        dq, dk, dv, dg, dbeta = _backward(saved, v3, beta3.float().contiguous(), do3)
+        dq, dk, dv, dg, dbeta, _ = _backward(saved, v3, beta3.float().contiguous(), do3)
     grads = [dq.view(q.shape), dk.view(q.shape), dv.view(v.shape), dbeta.view(beta.shape).to(beta_dtype),
              dg.view(g.shape)]
     if use_gate_in_kernel:

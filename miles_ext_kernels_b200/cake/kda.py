@@ -2,7 +2,8 @@
 1 to 64 heads per call, per-document zero initial state, forward and backward, on hand-written sm_100a kernels.
 
 The entry points and their argument meaning follow the reference's op (reference: miles_ext_kernels/cake/kda.py:53-78,
-miles_ext_kernels/cake/_impl/kda/ops.py:142-234).  miles selects the op with ``--kda-backend cake``, builds the library
+miles_ext_kernels/cake/_impl/kda/ops.py:142-234; the context-parallel entry points ``*_kcp``:
+miles_ext_kernels/cake/_impl/kda/kcp.py:86-230).  miles selects the op with ``--kda-backend cake``, builds the library
 when a layer is built (``cake.prebuild("kda", num_heads=...)``) and calls :func:`chunk_kda` in its forward.
 
 Importing this module imports neither torch nor the implementation.
@@ -29,12 +30,24 @@ def _validate(args: Namespace) -> None:
 
 OP = OpSpec(
     name="kda",
-    summary="packed KDA chunked training, forward + backward, K = V = 128, 1 to 64 heads",
+    summary="packed KDA chunked training, forward + backward, K = V = 128, 1 to 64 heads, context parallelism",
     variants=("det", "fast"),
     cli_variants=("det",),
     selected_by=(("kda_backend", "cake"),),
     packages=("libmek_b200",),
-    exports=("DEFAULT_SCALE", "MAX_HEADS", "chunk_kda", "chunk_kda_bwd", "chunk_kda_fwd"),
+    exports=(
+        "DEFAULT_SCALE",
+        "MAX_HEADS",
+        "build_context_kcp",
+        "chunk_kda",
+        "chunk_kda_bwd",
+        "chunk_kda_bwd_kcp",
+        "chunk_kda_fwd",
+        "chunk_kda_fwd_kcp",
+        "chunk_kda_kcp",
+        "partition_kcp",
+        "reduce_gate_param_grads_kcp",
+    ),
     validate=_validate,
 )
 

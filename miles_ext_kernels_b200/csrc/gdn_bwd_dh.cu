@@ -259,14 +259,13 @@ extern "C" int mek_gdn_bwd_dh(const MekGdnDims* d, const void* q, const void* k,
 }
 
 extern "C" int mek_kda_bwd_dh(const MekGdnDims* d, const void* qg, const void* kr, const void* w, const void* d_o,
-                              const void* aqk, const float* gl2, void* dh_tape, void* dv_new, int32_t* status,
-                              void* stream) {
+                              const void* aqk, const float* gl2, const float* dht, void* dh_tape, void* dv_new,
+                              float* dh0, int32_t* status, void* stream) {
   using namespace mek;
   if (d == nullptr || d->num_seqs <= 0 || d->num_v_heads <= 0 || d->num_qk_heads != d->num_v_heads ||
       d->num_chunks <= 0 || d->total_tokens <= 0)
     return fail(MEK_ERR_INVALID, "kda_bwd_dh: bad extents (KDA has one value head per key head)");
   if (d->head_dim != 128) return fail(MEK_ERR_UNSUPPORTED, "kda_bwd_dh: head dims must be 128, not %d", d->head_dim);
   if (gl2 == nullptr) return fail(MEK_ERR_INVALID, "kda_bwd_dh: gl2 is null");
-  return launch_bwd_dh(d, qg, kr, w, d_o, aqk, nullptr, nullptr, dh_tape, dv_new, nullptr, gl2, status, stream,
-                       "kda_bwd_dh");
+  return launch_bwd_dh(d, qg, kr, w, d_o, aqk, nullptr, dht, dh_tape, dv_new, dh0, gl2, status, stream, "kda_bwd_dh");
 }

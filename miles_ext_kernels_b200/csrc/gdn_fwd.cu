@@ -628,13 +628,13 @@ int mek_gdn_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void*
   return launch_fwd_h(d, k, w, u, g_cs, h0, h_tape, v_new, final_state, nullptr, status, stream, "fwd_h");
 }
 
-int mek_kda_fwd_h(const MekGdnDims* d, const void* kr, const void* w, const void* u, const float* gl2, void* h_tape,
-                  void* v_new, int32_t* status, void* stream) {
+int mek_kda_fwd_h(const MekGdnDims* d, const void* kr, const void* w, const void* u, const float* gl2, const float* h0,
+                  void* h_tape, void* v_new, float* final_state, int32_t* status, void* stream) {
   using namespace mek;
   if (int rc = check_dims(d, "kda_fwd_h")) return rc;
   if (d->num_qk_heads != d->num_v_heads) return fail(MEK_ERR_INVALID, "kda_fwd_h: KDA has one value head per key head");
   if (gl2 == nullptr) return fail(MEK_ERR_INVALID, "kda_fwd_h: gl2 is null");
-  return launch_fwd_h(d, kr, w, u, nullptr, nullptr, h_tape, v_new, nullptr, gl2, status, stream, "kda_fwd_h");
+  return launch_fwd_h(d, kr, w, u, nullptr, h0, h_tape, v_new, final_state, gl2, status, stream, "kda_fwd_h");
 }
 
 int mek_gdn_fwd_o(const MekGdnDims* d, const void* q, const void* aqk, const void* v_new, const void* h_tape,

@@ -79,9 +79,9 @@ def test_stages_against_the_oracle_tape(case):
         cu.append(cu[-1] + n)
     d = {n: t.to(dev) for n, t in x.items()}
     beta32 = d["beta"].float()
-    o, s = ops._forward(d["q"], d["k"], d["v"], d["g"], beta32, torch.tensor(cu, dtype=torch.int32, device=dev),
+    o, s, _ = ops._forward(d["q"], d["k"], d["v"], d["g"], beta32, torch.tensor(cu, dtype=torch.int32, device=dev),
                         128**-0.5, False)
-    dq, dk, dv, dg, dbeta = ops._backward(s, d["v"], beta32, d["do"])
+    dq, dk, dv, dg, dbeta, _ = ops._backward(s, d["v"], beta32, d["do"])
     torch.cuda.synchronize()
     check_status(s.status)
     f = {n: t.float() for n, t in x.items()}
