@@ -121,6 +121,34 @@ int mek_gdn_bwd_dh(const MekGdnDims* dims, const void* q, const void* k, const v
                    const void* aqk, const float* g_cs, const float* dht, void* dh_tape, void* dv_new, float* dh0,
                    int32_t* status, void* stream);
 
+/* Segment-parallel scans (long sequences, fewer chains than SMs).  The sequences are cut into segments of whole
+ * chunks; `seg_dims` is the call's MekGdnDims with num_seqs = the number of segments and seq_chunk_start = the
+ * segments' chunk ranges [segments + 1].  One chunk step is affine in the state, so a segment has a summary (B, M)
+ * with S_out = M S_in + B:
+ *   *_prescan   per segment and value head the offset walk (from zero, or from row state_row[s] of `boundary` when
+ *               the segment is the first its sequence's walk meets) -> B, and the transfer walk (from the identity,
+ *               inhomogeneous operand zeroed) -> M; summary fp32 [segments, HV, 2, 128, 128]; no tape is written.
+ *               seg_flags[s]: bit 0 = the walk starts from zero (a transfer walk exists), bit 1 = no summary needed.
+ *   scan_stitch per (sequence, value head) chains the summaries in walk order from the sequence's boundary state
+ *               (`boundary` fp32 [N, HV, 128, 128] or NULL) and writes the state every segment's real walk starts
+ *               from: seg_state fp32 [segments, HV, 128, 128]; seq_seg_start int32 [N + 1]; reverse = 1 for the
+ *               adjoint scan.
+ * The real walk is mek_gdn_fwd_h / mek_gdn_bwd_dh on seg_dims with h0 / dht = seg_state.
+ * Warm-up rule: when the summed gate of the warm_chunks chunks through which a state leaves a segment is below
+ * warm_log2 (log2 domain), the offset walk covers those chunks only and M is taken as zero (warm_chunks = 0: never).
+ * Replaces the reference's pre-scan / split-scan launches and stitch (reference:
+ * miles_ext_kernels/cake/_impl/gdn/ops.py:405-531, 1191-1317, 1551-1640). */
+int mek_gdn_fwd_h_prescan(const MekGdnDims* seg_dims, const void* k, const void* w, const void* u, const float* g_cs,
+                          const float* boundary, const int32_t* seg_flags, const int32_t* state_row, int warm_chunks,
+                          float warm_log2, float* summary, int32_t* status, void* stream);
+int mek_gdn_bwd_dh_prescan(const MekGdnDims* seg_dims, const void* q, const void* k, const void* w, const void* d_o,
+                           const void* aqk, const float* g_cs, const float* boundary, const int32_t* seg_flags,
+                           const int32_t* state_row, int warm_chunks, float warm_log2, float* summary,
+                           int32_t* status, void* stream);
+int mek_gdn_scan_stitch(const MekGdnDims* seg_dims, int num_seqs, const int32_t* seq_seg_start, const float* summary,
+                        const float* boundary, const float* g_cs, float* seg_state, int reverse, int warm_chunks,
+                        float warm_log2, void* stream);
+
 /* Gradient tail per (chunk, key head): dq, dk bf16 [T, H, 128] (fp32 sum over the key head's value heads, the L2
  * norm's pull-back when q_raw / k_raw / rstd_q / rstd_k are given, one rounding), dv bf16 [T, HV, 128], dbeta and
  * dg fp32 [T, HV] (dg includes the in-chunk suffix sum).  q, k are the normalised rows the forward used.

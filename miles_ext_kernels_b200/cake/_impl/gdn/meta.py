@@ -40,6 +40,7 @@ class ChunkMeta:
     total_tokens: int
     exact: bool  # False: built on the device, padded
     max_seq_chunks: int  # most chunks of one sequence (an upper bound on the device route)
+    host_seq_chunk_start: tuple[int, ...] | None = None  # the host route's copy of seq_chunk_start (scan planner)
 
 
 def host_tables(seq_lens: Sequence[int]) -> tuple[list[int], list[int], list[int], list[int]]:
@@ -88,7 +89,7 @@ def _from_host(seq_lens: tuple[int, ...], device: torch.device) -> ChunkMeta:
         flat = flat.pin_memory().to(device, non_blocking=True)
     meta = ChunkMeta(
         flat[:nc], flat[nc : 2 * nc], flat[2 * nc : 3 * nc], flat[3 * nc :], nc, len(seq_lens), sum(seq_lens), True,
-        max((first[n + 1] - first[n] for n in range(len(seq_lens))), default=0),
+        max((first[n + 1] - first[n] for n in range(len(seq_lens))), default=0), tuple(first),
     )
     _HOST_BUILDS += 1
     _HOST_CACHE[key] = meta

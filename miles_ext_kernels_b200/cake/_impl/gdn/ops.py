@@ -126,6 +126,11 @@ def _save_state() -> bool:
     return not config.option(OP, "cake_gdn_recompute_state")
 
 
+def _scan_segments() -> int:
+    """``--cake-gdn-scan-segments``: 0 = the scan planner decides, 1 = serial scans, more = that many segments."""
+    return int(config.option(OP, "cake_gdn_scan_segments") or 0)
+
+
 # --------------------------------------------------------------------------------------------------------------------
 # the empty call
 # --------------------------------------------------------------------------------------------------------------------
@@ -190,8 +195,10 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             if exchange is not None:  # the state at this rank's start comes from the previous rank
                 h0 = exchange.incoming_state(meta.num_seqs, HV, device)
                 want_final = True
+            ctx.scan_segments = _scan_segments()
             o, final_state, tape = stages.forward(qp, kp, vp, gp, beta32, meta, scale, h0, want_final,
-                                                  bool(use_qk_l2norm), keep_state=bool(save_state))
+                                                  bool(use_qk_l2norm), keep_state=bool(save_state),
+                                                  scan_segments=ctx.scan_segments)
             if exchange is not None:  # ... and the state at its end goes to the next one
                 exchange.outgoing_state(final_state)
                 final_state = None
@@ -218,7 +225,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             if ctx.exchange is not None:  # the adjoint state at this rank's end comes from the next rank
                 dhtp = ctx.exchange.incoming_adjoint(meta.num_seqs, tape.v.shape[1], device)
                 want_dh0 = True
-            dq, dk, dv, dg, dbeta, dh0, _, _ = stages.backward(tape, meta, ctx.scale, dop, dhtp, ctx.h0, want_dh0)
+            dq, dk, dv, dg, dbeta, dh0, _, _ = stages.backward(tape, meta, ctx.scale, dop, dhtp, ctx.h0, want_dh0,
+                                                               scan_segments=ctx.scan_segments)
             if ctx.exchange is not None:  # ... and the one at its start goes to the previous one
                 ctx.exchange.outgoing_adjoint(dh0)
                 dh0 = None
@@ -323,6 +331,8 @@ def release() -> None:
     contexts and the library handle."""
     meta_module.host_cache_clear()
     native.release()
-    from . import kcp
+    from . import kcp, scan
+
+    scan.release()
 
     kcp.release()

@@ -1,0 +1,172 @@
+"""The launch plan of the two state scans (reference: ``choose_scan_plan`` / ``scan_plans`` / ``finalize_stage``,
+miles_ext_kernels/cake/_impl/gdn/ops.py:405-531, 733-860).
+
+A scan is one chain of dependent chunk steps per (sequence, value head).  With fewer chains than SMs and long
+sequences the serial walk leaves most of the GPU idle, so the planner may cut every long sequence into segments of
+whole chunks and run three launches instead of one: a pre-scan (each segment's affine summary ``S_out = M S_in + B``,
+all segments in parallel), a stitch (the summaries chained per sequence) and the real walk (all segments in parallel
+from their true start states).  When a segment's closing gates are strong enough (below ``WARM_NATS`` nats over its
+last ``WARM_CHUNKS`` chunks) the kernels shorten the pre-scan to those chunks and take ``M`` as zero.
+
+The plan is a pure function of the layout, the head count and the SM count: the same call always takes the same plan
+and gives the same bits.  A segmented scan is not bit-identical to the serial one (the state crosses a segment
+boundary as ``M S + B`` in fp32 instead of through the chunk steps); both are inside the accuracy budgets.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from functools import lru_cache
+
+import torch
+
+from . import native
+
+MIN_SEGMENT_CHUNKS = 16  # a segment shorter than this does not pay for its summary
+MAX_PARTS = 16
+WARM_CHUNKS = 2
+WARM_NATS = -10.0
+MIN_GAIN = 0.95  # take a segmented plan only when its modelled time is below this fraction of the serial walk's
+STITCH_STEPS = 3  # modelled cost of one stitch step, in chunk steps
+
+
+@dataclass(frozen=True)
+class Segmentation:
+    """The segments of a layout for ``parts`` segments per long sequence (host lists)."""
+
+    parts: int
+    seg_chunk_start: tuple[int, ...]  # [segments + 1]
+    seq_seg_start: tuple[int, ...]  # [N + 1]
+
+    @property
+    def segments(self) -> int:
+        return len(self.seg_chunk_start) - 1
+
+
+def segment(seq_chunk_start: tuple[int, ...], parts: int) -> Segmentation:
+    """Cut every sequence into at most ``parts`` segments of at least :data:`MIN_SEGMENT_CHUNKS` chunks, as equal
+    as whole chunks allow."""
+    starts, first = [], [0]
+    for begin, end in zip(seq_chunk_start, seq_chunk_start[1:]):
+        chunks = end - begin
+        pieces = max(1, min(parts, chunks // MIN_SEGMENT_CHUNKS))
+        for p in range(pieces):
+            starts.append(begin + (chunks * p) // pieces)
+        first.append(len(starts))
+    starts.append(seq_chunk_start[-1])
+    return Segmentation(parts, tuple(starts), tuple(first))
+
+
+def _waves(ctas: int, sms: int) -> int:
+    return -(-ctas // sms)
+
+
+def modelled_steps(seg: Segmentation, num_v_heads: int, sms: int) -> float:
+    """Chunk steps on the critical path of the three launches, every summary exact (no warm-up)."""
+    longest = max((b - a for a, b in zip(seg.seg_chunk_start, seg.seg_chunk_start[1:])), default=0)
+    per_seq = [b - a for a, b in zip(seg.seq_seg_start, seg.seq_seg_start[1:])]
+    offset = sum(max(p - 1, 0) for p in per_seq)
+    transfer = sum(max(p - 2, 0) for p in per_seq)
+    pre = longest * _waves((offset + transfer) * num_v_heads, sms) if offset else 0
+    real = longest * _waves(seg.segments * num_v_heads, sms)
+    return pre + real + STITCH_STEPS * max(per_seq, default=0)
+
+
+@lru_cache(maxsize=256)
+def choose_parts(seq_chunk_start: tuple[int, ...], num_v_heads: int, sms: int, forced: int = 0) -> int:
+    """How many segments per long sequence: 1 = the serial walk.  ``forced`` > 0 overrides the model."""
+    if forced > 0:
+        return min(forced, MAX_PARTS)
+    num_seqs = len(seq_chunk_start) - 1
+    if num_seqs <= 0 or num_seqs * num_v_heads * 2 > sms:
+        return 1
+    serial = modelled_steps(segment(seq_chunk_start, 1), num_v_heads, sms)
+    best, best_steps = 1, serial
+    for parts in range(2, MAX_PARTS + 1):
+        seg = segment(seq_chunk_start, parts)
+        if seg.segments == num_seqs:
+            break  # no sequence is long enough to cut
+        steps = modelled_steps(seg, num_v_heads, sms)
+        if steps < best_steps:
+            best, best_steps = parts, steps
+    return best if best_steps < MIN_GAIN * serial else 1
+
+
+@dataclass
+class ScanPlan:
+    """Device tables of a segmented scan."""
+
+    segments: int
+    num_seqs: int
+    seg_chunk_start: torch.Tensor  # int32 [segments + 1]
+    seq_seg_start: torch.Tensor  # int32 [N + 1]
+    flags_fwd: torch.Tensor  # int32 [segments]: bit 0 not the sequence's first, bit 1 its last
+    flags_bwd: torch.Tensor  # int32 [segments]: bit 0 not the sequence's last, bit 1 its first
+    state_row: torch.Tensor  # int32 [segments]: the sequence of each segment
+    first_index: torch.Tensor  # int64 [N]: each sequence's first segment
+    last_index: torch.Tensor  # int64 [N]: each sequence's last segment
+    warm_chunks: int = WARM_CHUNKS
+    warm_log2: float = WARM_NATS * math.log2(math.e)
+
+
+_PLANS: dict[tuple, ScanPlan] = {}
+
+
+def device_plan(seg: Segmentation, device: torch.device) -> ScanPlan:
+    key = (seg, device.type, device.index)
+    found = _PLANS.get(key)
+    if found is not None:
+        return found
+    first, last, rows, fwd, bwd = [], [], [], [], []
+    for n, (a, b) in enumerate(zip(seg.seq_seg_start, seg.seq_seg_start[1:])):
+        first.append(a)
+        last.append(b - 1)
+        for s in range(a, b):
+            rows.append(n)
+            fwd.append((1 if s > a else 0) | (2 if s == b - 1 else 0))
+            bwd.append((1 if s < b - 1 else 0) | (2 if s == a else 0))
+    flat = torch.tensor([*seg.seg_chunk_start, *seg.seq_seg_start, *fwd, *bwd, *rows], dtype=torch.int32)
+    index = torch.tensor([*first, *last], dtype=torch.int64)
+    if device.type == "cuda":
+        flat = flat.pin_memory().to(device, non_blocking=True)
+        index = index.pin_memory().to(device, non_blocking=True)
+    ns, n = seg.segments, len(seg.seq_seg_start) - 1
+    at = [0, ns + 1, ns + n + 2, 2 * ns + n + 2, 3 * ns + n + 2, 4 * ns + n + 2]
+    plan = ScanPlan(ns, n, flat[at[0]:at[1]], flat[at[1]:at[2]], flat[at[2]:at[3]], flat[at[3]:at[4]],
+                    flat[at[4]:at[5]], index[:n], index[n:])
+    if len(_PLANS) >= 64:
+        _PLANS.clear()
+    _PLANS[key] = plan
+    return plan
+
+
+@lru_cache(maxsize=8)
+def sm_count(index: int) -> int:
+    return int(torch.cuda.get_device_properties(index).multi_processor_count)
+
+
+def plan_for(meta, num_v_heads: int, device: torch.device, forced: int = 0) -> ScanPlan | None:
+    """The segmented plan of a layout, or ``None`` for the serial walk (also for layouts whose tables were built on
+    the device: the planner needs the chunk counts on the host)."""
+    if meta.host_seq_chunk_start is None or device.type != "cuda":
+        return None
+    parts = choose_parts(meta.host_seq_chunk_start, num_v_heads, sm_count(device.index or 0), forced)
+    if parts <= 1:
+        return None
+    seg = segment(meta.host_seq_chunk_start, parts)
+    if seg.segments == meta.num_seqs:
+        return None
+    return device_plan(seg, device)
+
+
+def segment_dims(dims: native.Dims, plan: ScanPlan) -> native.Dims:
+    """The call's extents with the segments in place of the sequences."""
+    return native.Dims(dims.total_tokens, dims.num_qk_heads, dims.num_v_heads, dims.head_dim, plan.segments,
+                       dims.num_chunks, dims.scale, dims.chunk_start, dims.chunk_len, dims.chunk_seq,
+                       plan.seg_chunk_start.data_ptr())
+
+
+def release() -> None:
+    _PLANS.clear()
+    choose_parts.cache_clear()

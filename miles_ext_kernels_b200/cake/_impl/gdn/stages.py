@@ -16,7 +16,7 @@ from dataclasses import dataclass
 import torch
 
 from ..._runtime import workspace
-from . import native
+from . import native, scan
 from .meta import ChunkMeta
 
 OP = "gdn"
@@ -70,10 +70,61 @@ def _l2norm(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return y, rstd
 
 
+def _scan_forward(dims, meta: ChunkMeta, k, w, u, g_cs, h0, h, v_new, want_final: bool, status, scan_segments: int):
+    """The state scan: one serial walk per (sequence, value head), or the planner's segmented form (pre-scan,
+    stitch, real walk over the segments).  Returns the final state or None."""
+    device = k.device
+    HV = w.shape[1]
+    plan = scan.plan_for(meta, HV, device, scan_segments)
+    if plan is None:
+        final = torch.empty((meta.num_seqs, HV, HEAD_DIM, HEAD_DIM), dtype=F32, device=device) if want_final else None
+        native.launch("gdn_fwd_h", dims, k, w, u, g_cs, h0, h, v_new, final, status, device=device)
+        return final
+    seg_dims = scan.segment_dims(dims, plan)
+    summary = workspace.take(OP, "scan_summary", (plan.segments, HV, 2, HEAD_DIM, HEAD_DIM), F32, device)
+    seg_state = workspace.take(OP, "scan_state", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
+    native.launch("gdn_fwd_h_prescan", seg_dims, k, w, u, g_cs, h0, plan.flags_fwd, plan.state_row, plan.warm_chunks,
+                  plan.warm_log2, summary, status, device=device)
+    native.launch("gdn_scan_stitch", seg_dims, plan.num_seqs, plan.seq_seg_start, summary, h0, g_cs, seg_state, 0,
+                  plan.warm_chunks, plan.warm_log2, device=device)
+    seg_final = None
+    if want_final:
+        seg_final = workspace.take(OP, "scan_final", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
+    native.launch("gdn_fwd_h", seg_dims, k, w, u, g_cs, seg_state, h, v_new, seg_final, status, device=device)
+    return seg_final.index_select(0, plan.last_index) if want_final else None
+
+
+def _scan_backward(dims, meta: ChunkMeta, tape, do, dht, dh_tape, dv_new, want_dh0: bool, scan_segments: int):
+    """The adjoint scan, serial or segmented like the forward's.  Returns dh0 or None."""
+    device = do.device
+    HV = tape.v.shape[1]
+    plan = scan.plan_for(meta, HV, device, scan_segments)
+    if plan is None:
+        dh0 = torch.empty((meta.num_seqs, HV, HEAD_DIM, HEAD_DIM), dtype=F32, device=device) if want_dh0 else None
+        native.launch("gdn_bwd_dh", dims, tape.qn, tape.kn, tape.w, do, tape.aqk, tape.g_cs, dht, dh_tape, dv_new, dh0,
+                      tape.status, device=device)
+        return dh0
+    seg_dims = scan.segment_dims(dims, plan)
+    summary = workspace.take(OP, "scan_summary", (plan.segments, HV, 2, HEAD_DIM, HEAD_DIM), F32, device)
+    seg_state = workspace.take(OP, "scan_state", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
+    native.launch("gdn_bwd_dh_prescan", seg_dims, tape.qn, tape.kn, tape.w, do, tape.aqk, tape.g_cs, dht,
+                  plan.flags_bwd, plan.state_row, plan.warm_chunks, plan.warm_log2, summary, tape.status,
+                  device=device)
+    native.launch("gdn_scan_stitch", seg_dims, plan.num_seqs, plan.seq_seg_start, summary, dht, tape.g_cs, seg_state,
+                  1, plan.warm_chunks, plan.warm_log2, device=device)
+    seg_dh0 = None
+    if want_dh0:
+        seg_dh0 = workspace.take(OP, "scan_final", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
+    native.launch("gdn_bwd_dh", seg_dims, tape.qn, tape.kn, tape.w, do, tape.aqk, tape.g_cs, seg_state, dh_tape, dv_new,
+                  seg_dh0, tape.status, device=device)
+    return seg_dh0.index_select(0, plan.first_index) if want_dh0 else None
+
+
 def forward(q, k, v, g, beta32, meta: ChunkMeta, scale: float, h0, output_final_state: bool, use_qk_l2norm: bool,
-            keep_state: bool = True):
+            keep_state: bool = True, scan_segments: int = 0):
     """q, k ``[T, H, 128]`` bf16; v ``[T, HV, 128]`` bf16; g, beta32 ``[T, HV]`` fp32; h0 ``[N, HV, 128, 128]`` fp32
-    or None.  Returns ``(o [T, HV, 128] bf16, final_state or None, tape)``."""
+    or None.  ``scan_segments``: 0 lets the scan planner decide, 1 forces the serial walk, more forces that many
+    segments per long sequence.  Returns ``(o [T, HV, 128] bf16, final_state or None, tape)``."""
     device = q.device
     T, H = q.shape[0], q.shape[1]
     HV = v.shape[1]
@@ -99,10 +150,7 @@ def forward(q, k, v, g, beta32, meta: ChunkMeta, scale: float, h0, output_final_
 
     h = alloc((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
     v_new = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
-    final_state = (
-        torch.empty((meta.num_seqs, HV, HEAD_DIM, HEAD_DIM), dtype=F32, device=device) if output_final_state else None
-    )
-    native.launch("gdn_fwd_h", dims, k, w, u, g_cs, h0, h, v_new, final_state, status, device=device)
+    final_state = _scan_forward(dims, meta, k, w, u, g_cs, h0, h, v_new, output_final_state, status, scan_segments)
 
     o = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
     native.launch("gdn_fwd_o", dims, q, aqk, v_new, h, g_cs, o, status, device=device)
@@ -113,7 +161,7 @@ def forward(q, k, v, g, beta32, meta: ChunkMeta, scale: float, h0, output_final_
     return o, final_state, tape
 
 
-def recompute_state(tape: ForwardTape, meta: ChunkMeta, scale: float, h0) -> None:
+def recompute_state(tape: ForwardTape, meta: ChunkMeta, scale: float, h0, scan_segments: int = 0) -> None:
     """Rebuild ``w, u, h, v_new`` of a tape that dropped them (the same kernels on the same inputs: the same bits)."""
     device = tape.qn.device
     T, H = tape.qn.shape[0], tape.qn.shape[1]
@@ -129,11 +177,11 @@ def recompute_state(tape: ForwardTape, meta: ChunkMeta, scale: float, h0) -> Non
                   tape.status, device=device)
     tape.h = alloc((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
     tape.v_new = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
-    native.launch("gdn_fwd_h", dims, tape.kn, tape.w, tape.u, tape.g_cs, h0, tape.h, tape.v_new, None, tape.status,
-                  device=device)
+    _scan_forward(dims, meta, tape.kn, tape.w, tape.u, tape.g_cs, h0, tape.h, tape.v_new, False, tape.status,
+                  scan_segments)
 
 
-def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want_dh0: bool):
+def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want_dh0: bool, scan_segments: int = 0):
     """``do [T, HV, 128]`` bf16, ``dht [N, HV, 128, 128]`` fp32 or None.  Returns ``(dq, dk [T, H, 128] bf16, dv
     [T, HV, 128] bf16, dg, dbeta [T, HV] fp32, dh0 [N, HV, 128, 128] fp32 or None)``."""
     device = do.device
@@ -142,15 +190,13 @@ def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want
     NC = meta.num_chunks
     dims = dims_of(meta, H, HV, scale)
     if tape.w is None:
-        recompute_state(tape, meta, scale, h0)
+        recompute_state(tape, meta, scale, h0, scan_segments)
     if meta.exact:
         dh_tape = workspace.take(OP, "dh_tape", (NC, HV, HEAD_DIM, HEAD_DIM), BF16, device)
     else:  # pad chunks are never written
         dh_tape = torch.zeros((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
     dv_new = workspace.take(OP, "dv_new", (T, HV, HEAD_DIM), BF16, device)
-    dh0 = torch.empty((meta.num_seqs, HV, HEAD_DIM, HEAD_DIM), dtype=F32, device=device) if want_dh0 else None
-    native.launch("gdn_bwd_dh", dims, tape.qn, tape.kn, tape.w, do, tape.aqk, tape.g_cs, dht, dh_tape, dv_new, dh0,
-                  tape.status, device=device)
+    dh0 = _scan_backward(dims, meta, tape, do, dht, dh_tape, dv_new, want_dh0, scan_segments)
     dq = torch.empty((T, H, HEAD_DIM), dtype=BF16, device=device)
     dk = torch.empty((T, H, HEAD_DIM), dtype=BF16, device=device)
     dv = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)

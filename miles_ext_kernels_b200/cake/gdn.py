@@ -14,7 +14,9 @@ Under any ``cp_context`` the contract is FLA's: no initial state, no final state
 
 Both variants (``det``, ``fast``) run the same kernels here: every reduction has a fixed order and no kernel uses a
 value atomic, so identical inputs give identical bits on the same GPU model and build.  ``--cake-gdn-recompute-state``
-recomputes the WY and state tapes in the backward instead of keeping them.
+recomputes the WY and state tapes in the backward instead of keeping them.  ``--cake-gdn-scan-segments`` overrides the
+scan planner, which cuts long sequences into segments scanned in parallel when a call has fewer (sequence, value
+head) chains than the GPU has SMs.
 
 Importing this module imports neither torch nor the kernels.
 """
@@ -37,6 +39,18 @@ OP = OpSpec(
                 help=(
                     "Recompute w/u/h/v_new in the backward instead of keeping them on the autograd tape: less "
                     "activation memory, more backward time. The gradients are the bits of the saved backward."
+                ),
+            ),
+        ),
+        Flag(
+            "--cake-gdn-scan-segments",
+            dict(
+                type=int,
+                default=0,
+                help=(
+                    "Segments per long sequence in the two state scans: 0 lets the scan planner decide from the "
+                    "layout, the head count and the SM count (it cuts sequences when there are fewer chains than "
+                    "SMs), 1 forces the serial scans, N > 1 forces N segments."
                 ),
             ),
         ),

@@ -9,6 +9,7 @@
 // Reference semantics: miles_ext_kernels/cake/_vendor/cake_gdn_det_train_kcp/cake_fake_backend.py:313-349 (adjoint
 // walk) and :433-448 (do_g, dv_intra); reference launches: miles_ext_kernels/cake/_impl/gdn/ops.py:1519-1640.
 #include "common.cuh"
+#include "scan_plan.cuh"
 #include "tiles.cuh"
 #include "tma.cuh"
 
@@ -39,7 +40,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
     const float* __restrict__ dht, __nv_bfloat16* __restrict__ dh_tape, __nv_bfloat16* __restrict__ dv_new,
     float* __restrict__ dh0, const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len,
     const int32_t* __restrict__ seq_chunk_start, int num_qk_heads, int num_v_heads, float scale,
-    const float* __restrict__ gl2, int32_t* __restrict__ status) {
+    const float* __restrict__ gl2, const ScanPlan plan, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
   __shared__ uint64_t bar, bar_load[2];
   __shared__ uint32_t tmem_slot;
@@ -55,6 +56,24 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
   float* s_g2 = reinterpret_cast<float*>(sm + BwdDhSmem::kG);
   Abort abort{&abort_flag};
 
+  // pre-scan of a segment-parallel plan: blockIdx.z = 0 is the offset walk, 1 the transfer walk (from the identity,
+  // with do = 0); neither writes the tapes.  The adjoint leaves a segment through its first chunks.
+  const bool prescan = plan.seg_flags != nullptr;
+  const bool transfer = prescan && blockIdx.z == 1;
+  const int c_first = seq_chunk_start[n];
+  int c_last = seq_chunk_start[n + 1];
+  int state_row = n;
+  if (prescan) {
+    const int flags = plan.seg_flags[n];
+    const bool inner = (flags & 1) != 0;
+    if ((flags & 2) != 0 || (transfer && !inner) || c_first >= c_last) return;
+    state_row = inner ? -1 : plan.state_row[n];
+    if (inner && warm_up_suffices(plan, g_cs, chunk_start, chunk_len, c_first, c_last, num_v_heads, hv, true)) {
+      if (transfer) return;  // M is taken as zero
+      c_last = c_first + plan.warm_chunks;
+    }
+  }
+
   if (tid == 0) {
     mbar_init(&bar, 1);
     mbar_init(&bar_load[0], 1);
@@ -67,7 +86,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
   const int64_t v_stride = int64_t(num_v_heads) * kDim;
   __syncthreads();  // the barriers' initialisation is visible before the first copy is issued
   constexpr uint32_t kD1 = 0, kD1b = 128, kD2 = 256;  // tensor-memory columns
-  const int c_begin = seq_chunk_start[n], c_end = seq_chunk_start[n + 1];
+  const int c_begin = c_first, c_end = c_last;
 
   // the tiles of chunk c by TMA (one issuing thread), its gates by cp.async
   auto prefetch = [&](int c, int stage) {
@@ -93,9 +112,12 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
 
   // fp32 adjoint state: 64 columns of row krow
   float dh[64];
-  if (dht != nullptr) {
-    const float4* src =
-        reinterpret_cast<const float4*>(dht + ((int64_t(n) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
+  if (transfer) {
+#pragma unroll
+    for (int j = 0; j < 64; ++j) dh[j] = (krow == half * 64 + j) ? 1.f : 0.f;
+  } else if (dht != nullptr && state_row >= 0) {
+    const float4* src = reinterpret_cast<const float4*>(
+        dht + ((int64_t(state_row) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const float4 t = __ldg(src + j);
@@ -127,7 +149,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
       for (int cc = 0; cc < 8; ++cc) {
         const uint4 packed = pack8(dh + 8 * cc);
         set_tile_chunk(sm + BwdDhSmem::kDH, 16384, krow, half * 8 + cc, packed);
-        reinterpret_cast<uint4*>(tape)[cc] = packed;
+        if (!prescan) reinterpret_cast<uint4*>(tape)[cc] = packed;
       }
     }
     cp_async_wait_all();  // this chunk's gates and tiles have landed (issued one step ago)
@@ -138,6 +160,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
       clear_tile_rows<256>(st + BwdDhSmem::kW, len, tid);
       clear_tile_rows<256>(st + BwdDhSmem::kDO, len, tid);
     }
+    if (transfer) clear_tile_rows<256>(st + BwdDhSmem::kDO, 0, tid);  // the homogeneous recurrence: do = 0
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -174,7 +197,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
         const uint4 packed = pack8(a + 8 * jj);
-        if (live) reinterpret_cast<uint4*>(drow)[jj] = packed;
+        if (live && !prescan) reinterpret_cast<uint4*>(drow)[jj] = packed;
         set_tile_chunk(sm + BwdDhSmem::kDV, 8192, i, (lcol >> 3) + jj, packed);
       }
     }
@@ -216,8 +239,10 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
   tc_fence_before();
   __syncthreads();
 
-  if (dh0 != nullptr && !abort.raised()) {
-    float4* dst = reinterpret_cast<float4*>(dh0 + ((int64_t(n) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
+  float* out_state = prescan ? plan.summary + ((int64_t(n) * num_v_heads + hv) * 2 + (transfer ? 1 : 0)) * kDim * kDim
+                             : (dh0 ? dh0 + (int64_t(n) * num_v_heads + hv) * kDim * kDim : nullptr);
+  if (out_state != nullptr && !abort.raised()) {
+    float4* dst = reinterpret_cast<float4*>(out_state + krow * kDim + half * 64);
 #pragma unroll
     for (int j = 0; j < 16; ++j) dst[j] = make_float4(dh[4 * j], dh[4 * j + 1], dh[4 * j + 2], dh[4 * j + 3]);
   }
@@ -230,7 +255,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
 namespace {
 int launch_bwd_dh(const MekGdnDims* d, const void* q, const void* k, const void* w, const void* d_o, const void* aqk,
                   const float* g_cs, const float* dht, void* dh_tape, void* dv_new, float* dh0, const float* gl2,
-                  int32_t* status, void* stream, const char* what) {
+                  const mek::ScanPlan& plan, int32_t* status, void* stream, const char* what) {
   using namespace mek;
   const size_t smem = BwdDhSmem::kBytes + 1024;
   if (int rc = want_smem(gdn_bwd_dh_kernel, smem, what)) return rc;
@@ -240,32 +265,53 @@ int launch_bwd_dh(const MekGdnDims* d, const void* q, const void* k, const void*
   if (int rc = make_rows_map(&maps.w, w, d->total_tokens, d->num_v_heads, what)) return rc;
   if (int rc = make_rows_map(&maps.d_o, d_o, d->total_tokens, d->num_v_heads, what)) return rc;
   if (int rc = make_tiles_map(&maps.aqk, aqk, int64_t(d->num_chunks) * d->num_v_heads, 64, 64, what)) return rc;
-  gdn_bwd_dh_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+  const dim3 grid(d->num_seqs, d->num_v_heads, plan.seg_flags != nullptr ? 2 : 1);
+  gdn_bwd_dh_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(
       maps, g_cs, dht, static_cast<__nv_bfloat16*>(dh_tape), static_cast<__nv_bfloat16*>(dv_new), dh0, d->chunk_start,
-      d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, d->scale, gl2, status);
+      d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, d->scale, gl2, plan, status);
   return launched(what);
+}
+const mek::ScanPlan kNoPlan = {nullptr, nullptr, nullptr, 0, 0.f};
+
+int check_bwd_dh(const MekGdnDims* d, const char* what) {
+  using namespace mek;
+  if (d == nullptr || d->num_seqs <= 0 || d->num_v_heads <= 0 || d->num_qk_heads <= 0 || d->num_chunks <= 0 ||
+      d->total_tokens <= 0 || d->num_v_heads % d->num_qk_heads != 0)
+    return fail(MEK_ERR_INVALID, "%s: bad extents", what);
+  if (d->head_dim != 128) return fail(MEK_ERR_UNSUPPORTED, "%s: head dims must be 128, not %d", what, d->head_dim);
+  return MEK_OK;
 }
 }  // namespace
 
 extern "C" int mek_gdn_bwd_dh(const MekGdnDims* d, const void* q, const void* k, const void* w, const void* d_o,
                               const void* aqk, const float* g_cs, const float* dht, void* dh_tape, void* dv_new,
                               float* dh0, int32_t* status, void* stream) {
+  if (int rc = check_bwd_dh(d, "bwd_dh")) return rc;
+  return launch_bwd_dh(d, q, k, w, d_o, aqk, g_cs, dht, dh_tape, dv_new, dh0, nullptr, kNoPlan, status, stream,
+                       "bwd_dh");
+}
+
+extern "C" int mek_gdn_bwd_dh_prescan(const MekGdnDims* d, const void* q, const void* k, const void* w,
+                                      const void* d_o, const void* aqk, const float* g_cs, const float* boundary,
+                                      const int32_t* seg_flags, const int32_t* state_row, int warm_chunks,
+                                      float warm_log2, float* summary, int32_t* status, void* stream) {
   using namespace mek;
-  if (d == nullptr || d->num_seqs <= 0 || d->num_v_heads <= 0 || d->num_qk_heads <= 0 || d->num_chunks <= 0 ||
-      d->total_tokens <= 0 || d->num_v_heads % d->num_qk_heads != 0)
-    return fail(MEK_ERR_INVALID, "bwd_dh: bad extents");
-  if (d->head_dim != 128) return fail(MEK_ERR_UNSUPPORTED, "bwd_dh: head dims must be 128, not %d", d->head_dim);
-  return launch_bwd_dh(d, q, k, w, d_o, aqk, g_cs, dht, dh_tape, dv_new, dh0, nullptr, status, stream, "bwd_dh");
+  if (int rc = check_bwd_dh(d, "bwd_dh_prescan")) return rc;
+  if (!seg_flags || !state_row || !summary || warm_chunks < 0)
+    return fail(MEK_ERR_INVALID, "bwd_dh_prescan: a null table or summary, or negative warm_chunks");
+  const ScanPlan plan = {seg_flags, state_row, summary, warm_chunks, warm_log2};
+  return launch_bwd_dh(d, q, k, w, d_o, aqk, g_cs, boundary, nullptr, nullptr, nullptr, nullptr, plan, status, stream,
+                       "bwd_dh_prescan");
 }
 
 extern "C" int mek_kda_bwd_dh(const MekGdnDims* d, const void* qg, const void* kr, const void* w, const void* d_o,
                               const void* aqk, const float* gl2, const float* dht, void* dh_tape, void* dv_new,
                               float* dh0, int32_t* status, void* stream) {
   using namespace mek;
-  if (d == nullptr || d->num_seqs <= 0 || d->num_v_heads <= 0 || d->num_qk_heads != d->num_v_heads ||
-      d->num_chunks <= 0 || d->total_tokens <= 0)
-    return fail(MEK_ERR_INVALID, "kda_bwd_dh: bad extents (KDA has one value head per key head)");
-  if (d->head_dim != 128) return fail(MEK_ERR_UNSUPPORTED, "kda_bwd_dh: head dims must be 128, not %d", d->head_dim);
+  if (int rc = check_bwd_dh(d, "kda_bwd_dh")) return rc;
+  if (d->num_qk_heads != d->num_v_heads)
+    return fail(MEK_ERR_INVALID, "kda_bwd_dh: KDA has one value head per key head");
   if (gl2 == nullptr) return fail(MEK_ERR_INVALID, "kda_bwd_dh: gl2 is null");
-  return launch_bwd_dh(d, qg, kr, w, d_o, aqk, nullptr, dht, dh_tape, dv_new, dh0, gl2, status, stream, "kda_bwd_dh");
+  return launch_bwd_dh(d, qg, kr, w, d_o, aqk, nullptr, dht, dh_tape, dv_new, dh0, gl2, kNoPlan, status, stream,
+                       "kda_bwd_dh");
 }

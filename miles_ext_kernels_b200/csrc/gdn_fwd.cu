@@ -14,6 +14,7 @@
 // Shared-memory operand tiles use the swizzled block layout of umma.cuh; one tile serves as a K-major operand
 // (contraction over the feature axis) and as an MN-major operand (contraction over the token axis).
 #include "common.cuh"
+#include "scan_plan.cuh"
 #include "tiles.cuh"
 #include "tma.cuh"
 
@@ -274,7 +275,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     const __grid_constant__ FwdHMaps maps, const float* __restrict__ g_cs, const float* __restrict__ h0, __nv_bfloat16* __restrict__ h_tape,
     __nv_bfloat16* __restrict__ v_new, float* __restrict__ final_state, const int32_t* __restrict__ chunk_start,
     const int32_t* __restrict__ chunk_len, const int32_t* __restrict__ seq_chunk_start, int num_qk_heads,
-    int num_v_heads, const float* __restrict__ gl2, int32_t* __restrict__ status) {
+    int num_v_heads, const float* __restrict__ gl2, const ScanPlan plan, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
   __shared__ uint64_t bar, bar_load[2];
   __shared__ uint32_t tmem_slot;
@@ -288,6 +289,24 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
   float* s_g2 = reinterpret_cast<float*>(sm + FwdHSmem::kG);
   Abort abort{&abort_flag};
 
+  // pre-scan of a segment-parallel plan: blockIdx.z = 0 is the offset walk (B), 1 the transfer walk (M: from the
+  // identity, with u = 0); neither writes the tapes.  Decided before anything is allocated: the whole CTA leaves.
+  const bool prescan = plan.seg_flags != nullptr;
+  const bool transfer = prescan && blockIdx.z == 1;
+  int c_first = seq_chunk_start[n];
+  const int c_last = seq_chunk_start[n + 1];
+  int state_row = n;
+  if (prescan) {
+    const int flags = plan.seg_flags[n];
+    const bool inner = (flags & 1) != 0;
+    if ((flags & 2) != 0 || (transfer && !inner) || c_first >= c_last) return;
+    state_row = inner ? -1 : plan.state_row[n];
+    if (inner && warm_up_suffices(plan, g_cs, chunk_start, chunk_len, c_first, c_last, num_v_heads, hv, false)) {
+      if (transfer) return;  // M is taken as zero
+      c_first = c_last - plan.warm_chunks;
+    }
+  }
+
   if (tid == 0) {
     mbar_init(&bar, 1);
     mbar_init(&bar_load[0], 1);
@@ -298,7 +317,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
   if (warp == 0) tmem_alloc(&tmem_slot, 256);
   const uint32_t sbase = smem_u32(sm);
   const int64_t v_stride = int64_t(num_v_heads) * kDim;
-  const int c_begin = seq_chunk_start[n], c_end = seq_chunk_start[n + 1];
+  const int c_begin = c_first, c_end = c_last;
   __syncthreads();  // the barriers' initialisation is visible before the first copy is issued
 
   // the tiles of chunk c by TMA (one issuing thread), its gates by cp.async
@@ -323,9 +342,12 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
 
   // fp32 state: 64 columns of row krow
   float h[64];
-  if (h0 != nullptr) {
-    const float4* src =
-        reinterpret_cast<const float4*>(h0 + ((int64_t(n) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
+  if (transfer) {
+#pragma unroll
+    for (int j = 0; j < 64; ++j) h[j] = (krow == half * 64 + j) ? 1.f : 0.f;
+  } else if (h0 != nullptr && state_row >= 0) {
+    const float4* src = reinterpret_cast<const float4*>(
+        h0 + ((int64_t(state_row) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const float4 t = __ldg(src + j);
@@ -355,7 +377,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
       for (int cc = 0; cc < 8; ++cc) {
         const uint4 packed = pack8(h + 8 * cc);
         set_tile_chunk(sm + FwdHSmem::kH, 16384, krow, half * 8 + cc, packed);
-        reinterpret_cast<uint4*>(tape)[cc] = packed;
+        if (!prescan) reinterpret_cast<uint4*>(tape)[cc] = packed;
       }
     }
     cp_async_wait_all();  // this chunk's gates and tiles have landed (issued one step ago)
@@ -365,6 +387,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
       clear_tile_rows<256>(st + FwdHSmem::kK, len, tid);
       clear_tile_rows<256>(st + FwdHSmem::kU, len, tid);
     }
+    if (transfer) clear_tile_rows<256>(st + FwdHSmem::kU, 0, tid);  // the homogeneous recurrence: u = 0
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -404,7 +427,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
           uv[e] = live ? uv[e] - d[jj * 8 + e] : 0.f;
           vs[e] = rs * uv[e];
         }
-        if (live) reinterpret_cast<uint4*>(vrow)[jj] = pack8(uv);
+        if (live && !prescan) reinterpret_cast<uint4*>(vrow)[jj] = pack8(uv);
         set_tile_chunk(sm + FwdHSmem::kVS, 8192, i, (lcol >> 3) + jj, pack8(vs));
       }
     }
@@ -435,9 +458,10 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
   tc_fence_before();
   __syncthreads();
 
-  if (final_state != nullptr && !abort.raised()) {
-    float4* dst =
-        reinterpret_cast<float4*>(final_state + ((int64_t(n) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
+  float* out_state = prescan ? plan.summary + ((int64_t(n) * num_v_heads + hv) * 2 + (transfer ? 1 : 0)) * kDim * kDim
+                             : (final_state ? final_state + (int64_t(n) * num_v_heads + hv) * kDim * kDim : nullptr);
+  if (out_state != nullptr && !abort.raised()) {
+    float4* dst = reinterpret_cast<float4*>(out_state + krow * kDim + half * 64);
 #pragma unroll
     for (int j = 0; j < 16; ++j) dst[j] = make_float4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
   }
@@ -606,8 +630,8 @@ int mek_gdn_wy_fwd(const MekGdnDims* d, const void* q, const void* k, const void
 
 namespace {
 int launch_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* u, const float* g_cs, const float* h0,
-                 void* h_tape, void* v_new, float* final_state, const float* gl2, int32_t* status, void* stream,
-                 const char* what) {
+                 void* h_tape, void* v_new, float* final_state, const float* gl2, const mek::ScanPlan& plan,
+                 int32_t* status, void* stream, const char* what) {
   using namespace mek;
   const size_t smem = FwdHSmem::kBytes + 1024;
   if (int rc = want_smem(gdn_fwd_h_kernel, smem, what)) return rc;
@@ -615,17 +639,31 @@ int launch_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* 
   if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, what)) return rc;
   if (int rc = make_rows_map(&maps.w, w, d->total_tokens, d->num_v_heads, what)) return rc;
   if (int rc = make_rows_map(&maps.u, u, d->total_tokens, d->num_v_heads, what)) return rc;
-  gdn_fwd_h_kernel<<<dim3(d->num_seqs, d->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+  const dim3 grid(d->num_seqs, d->num_v_heads, plan.seg_flags != nullptr ? 2 : 1);
+  gdn_fwd_h_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(
       maps, g_cs, h0, static_cast<__nv_bfloat16*>(h_tape), static_cast<__nv_bfloat16*>(v_new), final_state,
-      d->chunk_start, d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, gl2, status);
+      d->chunk_start, d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, gl2, plan, status);
   return launched(what);
 }
+const mek::ScanPlan kNoPlan = {nullptr, nullptr, nullptr, 0, 0.f};
 }  // namespace
 
 int mek_gdn_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* u, const float* g_cs, const float* h0,
                   void* h_tape, void* v_new, float* final_state, int32_t* status, void* stream) {
   if (int rc = check_dims(d, "fwd_h")) return rc;
-  return launch_fwd_h(d, k, w, u, g_cs, h0, h_tape, v_new, final_state, nullptr, status, stream, "fwd_h");
+  return launch_fwd_h(d, k, w, u, g_cs, h0, h_tape, v_new, final_state, nullptr, kNoPlan, status, stream, "fwd_h");
+}
+
+int mek_gdn_fwd_h_prescan(const MekGdnDims* d, const void* k, const void* w, const void* u, const float* g_cs,
+                          const float* boundary, const int32_t* seg_flags, const int32_t* state_row, int warm_chunks,
+                          float warm_log2, float* summary, int32_t* status, void* stream) {
+  using namespace mek;
+  if (int rc = check_dims(d, "fwd_h_prescan")) return rc;
+  if (!seg_flags || !state_row || !summary || warm_chunks < 0)
+    return fail(MEK_ERR_INVALID, "fwd_h_prescan: a null table or summary, or negative warm_chunks");
+  const ScanPlan plan = {seg_flags, state_row, summary, warm_chunks, warm_log2};
+  return launch_fwd_h(d, k, w, u, g_cs, boundary, nullptr, nullptr, nullptr, nullptr, plan, status, stream,
+                      "fwd_h_prescan");
 }
 
 int mek_kda_fwd_h(const MekGdnDims* d, const void* kr, const void* w, const void* u, const float* gl2, const float* h0,
@@ -634,7 +672,7 @@ int mek_kda_fwd_h(const MekGdnDims* d, const void* kr, const void* w, const void
   if (int rc = check_dims(d, "kda_fwd_h")) return rc;
   if (d->num_qk_heads != d->num_v_heads) return fail(MEK_ERR_INVALID, "kda_fwd_h: KDA has one value head per key head");
   if (gl2 == nullptr) return fail(MEK_ERR_INVALID, "kda_fwd_h: gl2 is null");
-  return launch_fwd_h(d, kr, w, u, nullptr, h0, h_tape, v_new, final_state, gl2, status, stream, "kda_fwd_h");
+  return launch_fwd_h(d, kr, w, u, nullptr, h0, h_tape, v_new, final_state, gl2, kNoPlan, status, stream, "kda_fwd_h");
 }
 
 int mek_gdn_fwd_o(const MekGdnDims* d, const void* q, const void* aqk, const void* v_new, const void* h_tape,
