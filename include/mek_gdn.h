@@ -131,8 +131,11 @@ int mek_gdn_bwd_dh(const MekGdnDims* dims, const void* q, const void* k, const v
  *               seg_flags[s]: bit 0 = the walk starts from zero (a transfer walk exists), bit 1 = no summary needed.
  *   scan_stitch per (sequence, value head) chains the summaries in walk order from the sequence's boundary state
  *               (`boundary` fp32 [N, HV, 128, 128] or NULL) and writes the state every segment's real walk starts
- *               from: seg_state fp32 [segments, HV, 128, 128]; seq_seg_start int32 [N + 1]; reverse = 1 for the
- *               adjoint scan.
+ *               from: seg_state fp32 [segments, HV, 128, 128] (or NULL); seq_seg_start int32 [N + 1]; reverse = 1
+ *               for the adjoint scan; final_out fp32 [N, HV, 128, 128] (or NULL): the state after the last segment.
+ *               mode bits: 1 start from the identity, 2 leave the offsets out, 4 every segment started from zero
+ *               (modes 4 and 7 compose the (B, M) of a run of segments: a rank's summary under context parallelism;
+ *               mode 0 with warm_chunks = 0 over the ranks' summaries folds the chain of ranks before a rank).
  * The real walk is mek_gdn_fwd_h / mek_gdn_bwd_dh on seg_dims with h0 / dht = seg_state.
  * Warm-up rule: when the summed gate of the warm_chunks chunks through which a state leaves a segment is below
  * warm_log2 (log2 domain), the offset walk covers those chunks only and M is taken as zero (warm_chunks = 0: never).
@@ -146,8 +149,8 @@ int mek_gdn_bwd_dh_prescan(const MekGdnDims* seg_dims, const void* q, const void
                            const int32_t* state_row, int warm_chunks, float warm_log2, float* summary,
                            int32_t* status, void* stream);
 int mek_gdn_scan_stitch(const MekGdnDims* seg_dims, int num_seqs, const int32_t* seq_seg_start, const float* summary,
-                        const float* boundary, const float* g_cs, float* seg_state, int reverse, int warm_chunks,
-                        float warm_log2, void* stream);
+                        const float* boundary, const float* g_cs, float* seg_state, float* final_out, int reverse,
+                        int warm_chunks, float warm_log2, int mode, void* stream);
 
 /* Gradient tail per (chunk, key head): dq, dk bf16 [T, H, 128] (fp32 sum over the key head's value heads, the L2
  * norm's pull-back when q_raw / k_raw / rstd_q / rstd_k are given, one rounding), dv bf16 [T, HV, 128], dbeta and

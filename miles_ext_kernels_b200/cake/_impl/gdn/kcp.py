@@ -9,8 +9,10 @@ caches it (reference: kcp.py:185-226).
 Contract under a context (FLA's): no ``initial_state``, no final state; tokens never move, only ``[HV, 128, 128]``
 fp32 states.  Forward: the state at the end of this rank's last fragment goes to the next rank when the document
 continues there; backward: the adjoint state at the start of this rank's first fragment goes to the previous rank.
-States travel point to point on the group's backend (NCCL over NVLink between GPUs; gloo in the CPU tests) and land
-in this GPU's own memory before any kernel reads them.
+Two exchanges serve that: the sequential hand-over (point to point along the rank chain: rank r waits for rank
+r - 1) and the parallel one (every rank summarises its boundary fragment as an affine map, one all-gather, a local
+fold: ranks do not wait for one another; ``--cake-gdn-kcp-exchange``).  Either way the states land in this GPU's own
+memory before any kernel reads them (NCCL over NVLink between GPUs; gloo in the CPU tests).
 
 Only the ``"contiguous"`` layout is served; the load-balanced layouts of the reference (zigzag, per-document
 zigzag, explicit fragments) raise ``NotImplementedError``.
@@ -28,7 +30,7 @@ LAYOUTS = ("contiguous",)
 _CACHE_LIMIT = 32
 _CONTEXTS: OrderedDict[tuple[Any, ...], KcpContext] = OrderedDict()
 
-__all__ = ["KcpContext", "build_kcp_context", "local_partition", "release"]
+__all__ = ["KcpContext", "build_kcp_context", "document_run", "local_partition", "release"]
 
 
 def local_partition(cu_global: Sequence[int], rank: int, world_size: int):
@@ -54,6 +56,24 @@ def local_partition(cu_global: Sequence[int], rank: int, world_size: int):
     return local, continues_in, continues_out
 
 
+def document_run(cu_global: Sequence[int], rank: int, world_size: int) -> tuple[int, int]:
+    """``(first, last)``: the first rank that holds tokens of the document this rank's first fragment continues, and
+    the last rank that holds tokens of the document its last fragment continues into (``rank`` itself when nothing
+    continues on that side)."""
+    total = int(cu_global[-1])
+    part = total // world_size
+    lo, hi = rank * part, (rank + 1) * part
+    bounds = sorted(int(b) for b in cu_global)
+    first, last = rank, rank
+    if part > 0 and lo not in bounds:
+        begin = max(b for b in bounds if b < lo)  # where the document that crosses `lo` starts
+        first = begin // part
+    if part > 0 and hi not in bounds:
+        end = min(b for b in bounds if b > hi)  # where the document that crosses `hi` ends
+        last = (end - 1) // part
+    return first, last
+
+
 class _Exchange:
     """The state hand-over of one call: receive before the scan, send after it (forward: to the next rank; backward:
     to the previous one).  The hand-over is sequential along the rank chain, which reproduces the single-rank
@@ -61,6 +81,27 @@ class _Exchange:
 
     def __init__(self, context: KcpContext) -> None:
         self.context = context
+
+    # the hooks the stages call: around the state scan ...
+    def forward_begin(self, dims, meta, k, w, u, g_cs, status):
+        """-> ``(h0 or None, keep the final state?)``"""
+        ctx = self.context
+        return self.incoming_state(meta.num_seqs, w.shape[1], w.device), ctx.continues_out and ctx.world_size > 1
+
+    def forward_end(self, final_state) -> None:
+        if final_state is not None:
+            self.outgoing_state(final_state)
+
+    # ... and around the adjoint scan
+    def backward_begin(self, dims, meta, tape, do):
+        """-> ``(dht or None, keep dh0?)``"""
+        ctx = self.context
+        dht = self.incoming_adjoint(meta.num_seqs, tape.v.shape[1], do.device)
+        return dht, ctx.continues_in and ctx.world_size > 1
+
+    def backward_end(self, dh0) -> None:
+        if dh0 is not None:
+            self.outgoing_adjoint(dh0)
 
     def _peer(self, offset: int) -> int:
         import torch.distributed as dist
@@ -108,6 +149,77 @@ class _Exchange:
         dist.send(dh0[0].contiguous(), dst=self._peer(-1), group=ctx.group)
 
 
+class _ParallelExchange:
+    """Every rank works at once: a rank summarises the fragment through which a state leaves it as ``(B, M)`` with
+    ``S_out = M S_in + B`` (pre-scan of the fragment's segments, composed by the stitch kernel), one all-gather
+    shares the summaries, and each rank folds the chain of ranks its boundary document has crossed into the state
+    that enters it (reference: the affine rank summaries of miles_ext_kernels/cake/_impl/gdn/kcp.py and
+    _vendor/cake_gdn_det_train_kcp).  The cost per rank is one pre-scan, one gather and its own scan, whatever the
+    number of ranks; the result agrees with the sequential hand-over within the accuracy budgets, not bit for bit
+    (a state crosses a rank as ``M S + B`` in fp32 instead of through the chunk steps)."""
+
+    def __init__(self, context: KcpContext) -> None:
+        self.context = context
+        self.first_rank, self.last_rank = document_run(context.cu_seqlens_global, context.rank, context.world_size)
+
+    def _gather(self, local: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+
+        ctx = self.context
+        gathered = torch.empty((ctx.world_size, *local.shape), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(gathered, local, group=ctx.group)
+        return gathered
+
+    def forward_begin(self, dims, meta, k, w, u, g_cs, status):
+        from . import native, scan
+
+        ctx = self.context
+        device, HV = w.device, w.shape[1]
+        local = torch.zeros((HV, 2, 128, 128), dtype=torch.float32, device=device)
+        if ctx.continues_out:  # the state leaves through the last fragment
+            table = meta.host_seq_chunk_start
+            plan = scan.fragment_plan(table[-2], table[-1], HV, device)
+            seg_dims = scan.segment_dims(dims, plan)
+            summary = torch.empty((plan.segments, HV, 2, 128, 128), dtype=torch.float32, device=device)
+            native.launch("gdn_fwd_h_prescan", seg_dims, k, w, u, g_cs, None, plan.flags_fwd, plan.state_row,
+                          plan.warm_chunks, plan.warm_log2, summary, status, device=device)
+            local = scan.compose_summary(seg_dims, plan, summary, g_cs, reverse=False)
+        gathered = self._gather(local)
+        if not ctx.continues_in:
+            return None, False
+        h0 = torch.zeros((meta.num_seqs, HV, 128, 128), dtype=torch.float32, device=device)
+        h0[0] = scan.fold_ranks(dims, gathered, self.first_rank, ctx.rank - 1, reverse=False)[0]
+        return h0, False
+
+    def forward_end(self, final_state) -> None:
+        pass
+
+    def backward_begin(self, dims, meta, tape, do):
+        from . import native, scan
+
+        ctx = self.context
+        device, HV = do.device, tape.v.shape[1]
+        local = torch.zeros((HV, 2, 128, 128), dtype=torch.float32, device=device)
+        if ctx.continues_in:  # the adjoint state leaves through the first fragment
+            table = meta.host_seq_chunk_start
+            plan = scan.fragment_plan(table[0], table[1], HV, device)
+            seg_dims = scan.segment_dims(dims, plan)
+            summary = torch.empty((plan.segments, HV, 2, 128, 128), dtype=torch.float32, device=device)
+            native.launch("gdn_bwd_dh_prescan", seg_dims, tape.qn, tape.kn, tape.w, do, tape.aqk, tape.g_cs, None,
+                          plan.flags_bwd, plan.state_row, plan.warm_chunks, plan.warm_log2, summary, tape.status,
+                          device=device)
+            local = scan.compose_summary(seg_dims, plan, summary, tape.g_cs, reverse=True)
+        gathered = self._gather(local)
+        if not ctx.continues_out:
+            return None, False
+        dht = torch.zeros((meta.num_seqs, HV, 128, 128), dtype=torch.float32, device=device)
+        dht[-1] = scan.fold_ranks(dims, gathered, ctx.rank + 1, self.last_rank, reverse=True)[0]
+        return dht, False
+
+    def backward_end(self, dh0) -> None:
+        pass
+
+
 class KcpContext:
     """One rank's view of a contiguous partition of a packed batch."""
 
@@ -132,7 +244,16 @@ class KcpContext:
         self.cu_seqlens = torch.tensor(local, dtype=torch.int32, device=self.device)
         self.fla_compatible = True  # a contiguous partition is FLA's
 
-    def exchange(self) -> _Exchange:
+    def exchange(self, mode: str = "auto"):
+        """The boundary-state exchange of one call: ``"sequential"`` (rank to rank; the single-rank bits on aligned
+        boundaries), ``"parallel"`` (affine rank summaries, one all-gather; every rank works at once) or ``"auto"``
+        (parallel from three ranks on)."""
+        if mode not in ("auto", "sequential", "parallel"):
+            raise ValueError(f"unknown exchange mode {mode!r}")
+        if mode == "auto":
+            mode = "parallel" if self.world_size > 2 else "sequential"
+        if mode == "parallel" and self.world_size > 1:
+            return _ParallelExchange(self)
         return _Exchange(self)
 
     def __repr__(self) -> str:

@@ -192,16 +192,12 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             qp, kp, vp, gp = _packed(q), _packed(k), _packed(v), _packed(g)
             h0 = None if initial_state is None else initial_state.detach().float().contiguous()
             want_final = bool(output_final_state)
-            if exchange is not None:  # the state at this rank's start comes from the previous rank
-                h0 = exchange.incoming_state(meta.num_seqs, HV, device)
-                want_final = True
             ctx.scan_segments = _scan_segments()
-            o, final_state, tape = stages.forward(qp, kp, vp, gp, beta32, meta, scale, h0, want_final,
-                                                  bool(use_qk_l2norm), keep_state=bool(save_state),
-                                                  scan_segments=ctx.scan_segments)
-            if exchange is not None:  # ... and the state at its end goes to the next one
-                exchange.outgoing_state(final_state)
-                final_state = None
+            # under context parallelism the exchange supplies the state at this rank's start and takes the one at
+            # its end (inside the stages: the parallel exchange needs the WY outputs first)
+            o, final_state, tape, h0 = stages.forward(qp, kp, vp, gp, beta32, meta, scale, h0, want_final,
+                                                      bool(use_qk_l2norm), keep_state=bool(save_state),
+                                                      scan_segments=ctx.scan_segments, exchange=exchange)
         ctx.tape, ctx.meta, ctx.scale, ctx.h0 = tape, meta, scale, h0
         ctx.exchange = exchange
         ctx.shapes = (q.shape, v.shape, g.shape)
@@ -222,14 +218,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             dop = _packed(do if do.dtype == torch.bfloat16 else do.bfloat16())
             dhtp = None if dht is None else dht.float().contiguous()
             want_dh0 = ctx.has_initial_state
-            if ctx.exchange is not None:  # the adjoint state at this rank's end comes from the next rank
-                dhtp = ctx.exchange.incoming_adjoint(meta.num_seqs, tape.v.shape[1], device)
-                want_dh0 = True
             dq, dk, dv, dg, dbeta, dh0, _, _ = stages.backward(tape, meta, ctx.scale, dop, dhtp, ctx.h0, want_dh0,
-                                                               scan_segments=ctx.scan_segments)
-            if ctx.exchange is not None:  # ... and the one at its start goes to the previous one
-                ctx.exchange.outgoing_adjoint(dh0)
-                dh0 = None
+                                                               scan_segments=ctx.scan_segments, exchange=ctx.exchange)
         dq, dk, dv = dq.view(q_shape), dk.view(q_shape), dv.view(v_shape)
         dg = dg.view(g_shape)
         dbeta = dbeta.view(g_shape)
@@ -299,7 +289,7 @@ def chunk_gated_delta_rule(
         cu_seqlens, cu_seqlens_cpu = _cp_contract(cp_context, initial_state, output_final_state, cu_seqlens,
                                                   cu_seqlens_cpu)
         return _apply(q, k, v, g, beta, scale, None, False, cu_seqlens, cu_seqlens_cpu, use_qk_l2norm_in_kernel,
-                      exchange=cp_context.exchange())
+                      exchange=cp_context.exchange(str(config.option(OP, "cake_gdn_kcp_exchange") or "auto")))
     return _apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
                   use_qk_l2norm_in_kernel)
 

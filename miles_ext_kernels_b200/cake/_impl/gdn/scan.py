@@ -167,6 +167,57 @@ def segment_dims(dims: native.Dims, plan: ScanPlan) -> native.Dims:
                        plan.seg_chunk_start.data_ptr())
 
 
+# --------------------------------------------------------------------------------------------------------------------
+# summaries of one fragment and folds over ranks (context parallelism with ranks working in parallel)
+# --------------------------------------------------------------------------------------------------------------------
+def fragment_plan(chunk_begin: int, chunk_end: int, num_v_heads: int, device: torch.device) -> ScanPlan:
+    """Segments of the chunk range of one document fragment, every segment walked from zero / the identity and none
+    skipped: what a rank's summary ``(B, M)`` of the fragment is composed from."""
+    chunks = chunk_end - chunk_begin
+    sms = sm_count(device.index or 0)
+    parts = max(1, min(MAX_PARTS, chunks // MIN_SEGMENT_CHUNKS, sms // max(1, num_v_heads)))
+    seg = Segmentation(-parts, tuple(chunk_begin + (chunks * p) // parts for p in range(parts)) + (chunk_end,),
+                       (0, parts))
+    key = (seg, device.type, device.index)
+    found = _PLANS.get(key)
+    if found is not None:
+        return found
+    ns = parts
+    flat = torch.tensor([*seg.seg_chunk_start, 0, ns, *([1] * ns), *([0] * ns)], dtype=torch.int32)
+    if device.type == "cuda":
+        flat = flat.pin_memory().to(device, non_blocking=True)
+    plan = ScanPlan(ns, 1, flat[: ns + 1], flat[ns + 1 : ns + 3], flat[ns + 3 : 2 * ns + 3], flat[ns + 3 : 2 * ns + 3],
+                    flat[2 * ns + 3 :], None, None)
+    if len(_PLANS) >= 64:
+        _PLANS.clear()
+    _PLANS[key] = plan
+    return plan
+
+
+def compose_summary(seg_dims: native.Dims, plan: ScanPlan, summary: torch.Tensor, g_cs: torch.Tensor, reverse: bool):
+    """``[HV, 2, 128, 128]``: the (B, M) of the whole run of segments, from the segments' summaries."""
+    device = summary.device
+    HV = summary.shape[1]
+    out = torch.empty((2, HV, 128, 128), dtype=torch.float32, device=device)
+    for which, mode in ((0, 4), (1, 7)):  # B: from zero with the offsets; M: from the identity without them
+        native.launch("gdn_scan_stitch", seg_dims, 1, plan.seq_seg_start, summary, None, g_cs, None, out[which],
+                      int(reverse), plan.warm_chunks, plan.warm_log2, mode, device=device)
+    return out.transpose(0, 1).contiguous()
+
+
+def fold_ranks(dims: native.Dims, gathered: torch.Tensor, first: int, last: int, reverse: bool) -> torch.Tensor:
+    """The state that the ranks ``first .. last`` (inclusive) hand on, from their gathered summaries
+    ``[W, HV, 2, 128, 128]``: ``S = B_first``, then ``S = M_r S + B_r`` along the chain (``reverse``: from ``last``
+    down to ``first``).  ``[1, HV, 128, 128]``."""
+    device = gathered.device
+    HV = gathered.shape[1]
+    span = torch.tensor([first, last + 1], dtype=torch.int32).pin_memory().to(device, non_blocking=True)
+    out = torch.empty((1, HV, 128, 128), dtype=torch.float32, device=device)
+    native.launch("gdn_scan_stitch", dims, 1, span, gathered, None, None, None, out, int(reverse), 0, 0.0, 0,
+                  device=device)
+    return out
+
+
 def release() -> None:
     _PLANS.clear()
     choose_parts.cache_clear()

@@ -85,8 +85,8 @@ def _scan_forward(dims, meta: ChunkMeta, k, w, u, g_cs, h0, h, v_new, want_final
     seg_state = workspace.take(OP, "scan_state", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
     native.launch("gdn_fwd_h_prescan", seg_dims, k, w, u, g_cs, h0, plan.flags_fwd, plan.state_row, plan.warm_chunks,
                   plan.warm_log2, summary, status, device=device)
-    native.launch("gdn_scan_stitch", seg_dims, plan.num_seqs, plan.seq_seg_start, summary, h0, g_cs, seg_state, 0,
-                  plan.warm_chunks, plan.warm_log2, device=device)
+    native.launch("gdn_scan_stitch", seg_dims, plan.num_seqs, plan.seq_seg_start, summary, h0, g_cs, seg_state, None, 0,
+                  plan.warm_chunks, plan.warm_log2, 0, device=device)
     seg_final = None
     if want_final:
         seg_final = workspace.take(OP, "scan_final", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
@@ -111,7 +111,7 @@ def _scan_backward(dims, meta: ChunkMeta, tape, do, dht, dh_tape, dv_new, want_d
                   plan.flags_bwd, plan.state_row, plan.warm_chunks, plan.warm_log2, summary, tape.status,
                   device=device)
     native.launch("gdn_scan_stitch", seg_dims, plan.num_seqs, plan.seq_seg_start, summary, dht, tape.g_cs, seg_state,
-                  1, plan.warm_chunks, plan.warm_log2, device=device)
+                  None, 1, plan.warm_chunks, plan.warm_log2, 0, device=device)
     seg_dh0 = None
     if want_dh0:
         seg_dh0 = workspace.take(OP, "scan_final", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
@@ -121,10 +121,12 @@ def _scan_backward(dims, meta: ChunkMeta, tape, do, dht, dh_tape, dv_new, want_d
 
 
 def forward(q, k, v, g, beta32, meta: ChunkMeta, scale: float, h0, output_final_state: bool, use_qk_l2norm: bool,
-            keep_state: bool = True, scan_segments: int = 0):
+            keep_state: bool = True, scan_segments: int = 0, exchange=None):
     """q, k ``[T, H, 128]`` bf16; v ``[T, HV, 128]`` bf16; g, beta32 ``[T, HV]`` fp32; h0 ``[N, HV, 128, 128]`` fp32
     or None.  ``scan_segments``: 0 lets the scan planner decide, 1 forces the serial walk, more forces that many
-    segments per long sequence.  Returns ``(o [T, HV, 128] bf16, final_state or None, tape)``."""
+    segments per long sequence.  ``exchange`` (context parallelism) supplies the state that enters this rank's first
+    fragment and takes the one that leaves its last.  Returns ``(o [T, HV, 128] bf16, final_state or None, tape,
+    h0 used)``."""
     device = q.device
     T, H = q.shape[0], q.shape[1]
     HV = v.shape[1]
@@ -150,7 +152,12 @@ def forward(q, k, v, g, beta32, meta: ChunkMeta, scale: float, h0, output_final_
 
     h = alloc((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
     v_new = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    if exchange is not None:
+        h0, output_final_state = exchange.forward_begin(dims, meta, k, w, u, g_cs, status)
     final_state = _scan_forward(dims, meta, k, w, u, g_cs, h0, h, v_new, output_final_state, status, scan_segments)
+    if exchange is not None:
+        exchange.forward_end(final_state)
+        final_state = None
 
     o = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
     native.launch("gdn_fwd_o", dims, q, aqk, v_new, h, g_cs, o, status, device=device)
@@ -158,7 +165,7 @@ def forward(q, k, v, g, beta32, meta: ChunkMeta, scale: float, h0, output_final_
     if not keep_state:
         w = u = h = v_new = None
     tape = ForwardTape(q, k, v, beta32, g_cs, a, aqk, w, u, h, v_new, q_raw, k_raw, rstd_q, rstd_k, status)
-    return o, final_state, tape
+    return o, final_state, tape, h0
 
 
 def recompute_state(tape: ForwardTape, meta: ChunkMeta, scale: float, h0, scan_segments: int = 0) -> None:
@@ -181,7 +188,8 @@ def recompute_state(tape: ForwardTape, meta: ChunkMeta, scale: float, h0, scan_s
                   scan_segments)
 
 
-def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want_dh0: bool, scan_segments: int = 0):
+def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want_dh0: bool, scan_segments: int = 0,
+             exchange=None):
     """``do [T, HV, 128]`` bf16, ``dht [N, HV, 128, 128]`` fp32 or None.  Returns ``(dq, dk [T, H, 128] bf16, dv
     [T, HV, 128] bf16, dg, dbeta [T, HV] fp32, dh0 [N, HV, 128, 128] fp32 or None)``."""
     device = do.device
@@ -196,7 +204,12 @@ def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want
     else:  # pad chunks are never written
         dh_tape = torch.zeros((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
     dv_new = workspace.take(OP, "dv_new", (T, HV, HEAD_DIM), BF16, device)
+    if exchange is not None:
+        dht, want_dh0 = exchange.backward_begin(dims, meta, tape, do)
     dh0 = _scan_backward(dims, meta, tape, do, dht, dh_tape, dv_new, want_dh0, scan_segments)
+    if exchange is not None:
+        exchange.backward_end(dh0)
+        dh0 = None
     dq = torch.empty((T, H, HEAD_DIM), dtype=BF16, device=device)
     dk = torch.empty((T, H, HEAD_DIM), dtype=BF16, device=device)
     dv = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)

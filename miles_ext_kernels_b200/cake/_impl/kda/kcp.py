@@ -115,7 +115,7 @@ def _shard(q, k, v, g, beta, ctx: KcpContext):
 
 
 def _forward_kcp(q3, k3, v3, g3, beta32, ctx: KcpContext, scale: float, l2norm: bool):
-    exchange = ctx.exchange()
+    exchange = ctx.exchange("sequential")
     num_seqs, heads = len(ctx.cu_seqlens_cpu) - 1, q3.shape[1]
     with torch.cuda.device(q3.device):
         h0 = exchange.incoming_state(num_seqs, heads, q3.device)
@@ -128,7 +128,7 @@ def _forward_kcp(q3, k3, v3, g3, beta32, ctx: KcpContext, scale: float, l2norm: 
 
 
 def _backward_kcp(saved, v3, beta32, do3, ctx: KcpContext):
-    exchange = ctx.exchange()
+    exchange = ctx.exchange("sequential")
     num_seqs, heads = len(ctx.cu_seqlens_cpu) - 1, v3.shape[1]
     with torch.cuda.device(v3.device):
         dht = exchange.incoming_adjoint(num_seqs, heads, v3.device)

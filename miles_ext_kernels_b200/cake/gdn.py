@@ -43,6 +43,20 @@ OP = OpSpec(
             ),
         ),
         Flag(
+            "--cake-gdn-kcp-exchange",
+            dict(
+                choices=("auto", "sequential", "parallel"),
+                default="auto",
+                help=(
+                    "How the chunk state crosses rank boundaries under context parallelism: 'sequential' hands it "
+                    "from rank to rank (the single-rank bits on chunk-aligned boundaries; rank r waits for rank "
+                    "r - 1), 'parallel' has every rank summarise its boundary fragment as an affine map, shares the "
+                    "summaries with one all-gather and folds them locally (ranks work at once), 'auto' takes "
+                    "'parallel' from three ranks on."
+                ),
+            ),
+        ),
+        Flag(
             "--cake-gdn-scan-segments",
             dict(
                 type=int,

@@ -5,29 +5,38 @@
 //     S_next = M S + B           otherwise (fp32 FMA, fixed order),
 // forward from the sequence's initial state, or in reverse from its final adjoint state (reference:
 // miles_ext_kernels/cake/_impl/gdn/ops.py:1601-1613).  One CTA per (sequence, value head); the running state lives
-// in shared memory.
+// in shared memory.  The same chain composes the summary of a whole run of segments (context parallelism: a rank's
+// (B, M)) and folds the ranks' summaries into the state that enters a rank.
 #include "common.cuh"
 #include "scan_plan.cuh"
 
 namespace mek {
 
+// mode bits: 1 = start from the identity instead of the boundary state; 2 = leave the offsets out (B := 0);
+// 4 = every segment started from zero, the first too.  Modes 4 and 5 | 2 compose the summary of a whole run of
+// segments (its B, then its M); mode 0 with rank summaries as the "segments" folds a chain of ranks.
 __global__ void __launch_bounds__(256) scan_stitch_kernel(
     const float* __restrict__ summary, const float* __restrict__ boundary, const float* __restrict__ g_cs,
-    float* __restrict__ seg_state, const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len,
-    const int32_t* __restrict__ seg_chunk_start, const int32_t* __restrict__ seq_seg_start, int num_v_heads,
-    int reverse, int warm_chunks, float warm_log2) {
+    float* __restrict__ seg_state, float* __restrict__ final_out, const int32_t* __restrict__ chunk_start,
+    const int32_t* __restrict__ chunk_len, const int32_t* __restrict__ seg_chunk_start,
+    const int32_t* __restrict__ seq_seg_start, int num_v_heads, int reverse, int warm_chunks, float warm_log2,
+    int mode) {
   extern __shared__ float s_state[];  // [128][128]
   const int n = blockIdx.x, hv = blockIdx.y, tid = threadIdx.x;
   const int seg_begin = seq_seg_start[n], seg_end = seq_seg_start[n + 1];
-  if (seg_begin >= seg_end) return;
   const ScanPlan plan = {nullptr, nullptr, nullptr, warm_chunks, warm_log2};
   const int r = tid >> 1, c0 = (tid & 1) * 64;  // this thread's row and column half of the state
 
-  // the sequence's boundary state
+  // the state the walk starts from
   for (int i = tid; i < 128 * 32; i += 256) {
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (boundary != nullptr)
+    if (mode & 1) {
+      const int row = i >> 5, col = (i & 31) * 4;
+      v = make_float4(row == col ? 1.f : 0.f, row == col + 1 ? 1.f : 0.f, row == col + 2 ? 1.f : 0.f,
+                      row == col + 3 ? 1.f : 0.f);
+    } else if (boundary != nullptr) {
       v = reinterpret_cast<const float4*>(boundary + (int64_t(n) * num_v_heads + hv) * 16384)[i];
+    }
     reinterpret_cast<float4*>(s_state)[i] = v;
   }
   __syncthreads();
@@ -35,18 +44,22 @@ __global__ void __launch_bounds__(256) scan_stitch_kernel(
   const int count = seg_end - seg_begin;
   for (int step = 0; step < count; ++step) {
     const int s = reverse ? seg_end - 1 - step : seg_begin + step;
-    float* out = seg_state + (int64_t(s) * num_v_heads + hv) * 16384;
-    for (int i = tid; i < 128 * 32; i += 256) reinterpret_cast<float4*>(out)[i] = reinterpret_cast<float4*>(s_state)[i];
-    if (step + 1 == count) break;
+    if (seg_state != nullptr) {
+      float* out = seg_state + (int64_t(s) * num_v_heads + hv) * 16384;
+      for (int i = tid; i < 128 * 32; i += 256)
+        reinterpret_cast<float4*>(out)[i] = reinterpret_cast<float4*>(s_state)[i];
+    }
+    if (step + 1 == count && final_out == nullptr) break;
     const float* b_mat = summary + (int64_t(s) * num_v_heads + hv) * 2 * 16384;
     const float* m_mat = b_mat + 16384;
-    const bool inner = step > 0;
+    const bool inner = (mode & 4) != 0 || step > 0;
     const bool replace = !inner || warm_up_suffices(plan, g_cs, chunk_start, chunk_len, seg_chunk_start[s],
                                                     seg_chunk_start[s + 1], num_v_heads, hv, reverse != 0);
     float acc[64];
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
-      const float4 b = reinterpret_cast<const float4*>(b_mat + r * 128 + c0)[j];
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (!(mode & 2)) b = reinterpret_cast<const float4*>(b_mat + r * 128 + c0)[j];
       acc[4 * j] = b.x, acc[4 * j + 1] = b.y, acc[4 * j + 2] = b.z, acc[4 * j + 3] = b.w;
     }
     if (!replace) {
@@ -74,21 +87,28 @@ __global__ void __launch_bounds__(256) scan_stitch_kernel(
           make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
     __syncthreads();
   }
+  if (final_out != nullptr) {
+    float* out = final_out + (int64_t(n) * num_v_heads + hv) * 16384;
+    for (int i = tid; i < 128 * 32; i += 256) reinterpret_cast<float4*>(out)[i] = reinterpret_cast<float4*>(s_state)[i];
+  }
 }
 
 }  // namespace mek
 
 extern "C" int mek_gdn_scan_stitch(const MekGdnDims* seg_dims, int num_seqs, const int32_t* seq_seg_start,
                                    const float* summary, const float* boundary, const float* g_cs, float* seg_state,
-                                   int reverse, int warm_chunks, float warm_log2, void* stream) {
+                                   float* final_out, int reverse, int warm_chunks, float warm_log2, int mode,
+                                   void* stream) {
   using namespace mek;
-  if (seg_dims == nullptr || num_seqs <= 0 || seg_dims->num_v_heads <= 0 || !seq_seg_start || !summary || !g_cs ||
-      !seg_state || !seg_dims->seq_chunk_start || !seg_dims->chunk_start || !seg_dims->chunk_len || warm_chunks < 0)
-    return fail(MEK_ERR_INVALID, "scan_stitch: a null pointer or bad extents");
+  if (seg_dims == nullptr || num_seqs <= 0 || seg_dims->num_v_heads <= 0 || !seq_seg_start || !summary ||
+      (!seg_state && !final_out) || warm_chunks < 0 || mode < 0 || mode > 7)
+    return fail(MEK_ERR_INVALID, "scan_stitch: a null pointer, bad extents or an unknown mode");
+  if (warm_chunks > 0 && (!g_cs || !seg_dims->seq_chunk_start || !seg_dims->chunk_start || !seg_dims->chunk_len))
+    return fail(MEK_ERR_INVALID, "scan_stitch: the warm-up rule needs the gates and the chunk tables");
   const size_t smem = 128 * 128 * sizeof(float);
   if (int rc = want_smem(scan_stitch_kernel, smem, "scan_stitch")) return rc;
   scan_stitch_kernel<<<dim3(num_seqs, seg_dims->num_v_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      summary, boundary, g_cs, seg_state, seg_dims->chunk_start, seg_dims->chunk_len, seg_dims->seq_chunk_start,
-      seq_seg_start, seg_dims->num_v_heads, reverse, warm_chunks, warm_log2);
+      summary, boundary, g_cs, seg_state, final_out, seg_dims->chunk_start, seg_dims->chunk_len,
+      seg_dims->seq_chunk_start, seq_seg_start, seg_dims->num_v_heads, reverse, warm_chunks, warm_log2, mode);
   return launched("scan_stitch");
 }

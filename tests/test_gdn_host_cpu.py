@@ -101,6 +101,19 @@ def test_contiguous_partition_is_flas():
         kcp.KcpContext(cu, None, 0, 2, "cpu", layout="zigzag")
 
 
+def test_document_runs_across_ranks():
+    from miles_ext_kernels_b200.cake._impl.gdn.kcp import document_run
+
+    cu = (0, 6000, 8192)  # four ranks of 2,048 tokens: the first document crosses ranks 0..2, the second 2..3
+    assert document_run(cu, 0, 4) == (0, 2)
+    assert document_run(cu, 1, 4) == (0, 2)
+    assert document_run(cu, 2, 4) == (0, 3)
+    assert document_run(cu, 3, 4) == (2, 3)
+    cu = (0, 2048, 4096, 8192)  # documents end on rank boundaries: nothing continues there
+    assert document_run(cu, 0, 4) == (0, 0) and document_run(cu, 1, 4) == (1, 1)
+    assert document_run(cu, 2, 4) == (2, 3) and document_run(cu, 3, 4) == (2, 3)
+
+
 # ---- two ranks on gloo: the hand-over reproduces the single-rank recurrence -----------------------------------------
 def _free_port() -> int:
     with socket.socket() as s:

@@ -43,7 +43,7 @@ def test_forward_stages(name):
     meta = M.chunk_meta(torch.tensor(cu, dtype=torch.int32, device=dev), tuple(cu), 1, cu[-1], dev)
     scale = 1.0 / math.sqrt(128)
     d = {n: t.to(dev) for n, t in x.items()}
-    o, final, tape = stages.forward(d["q"], d["k"], d["v"], d["g"], d["beta"], meta, scale, d.get("h0"), state, l2)
+    o, final, tape, _ = stages.forward(d["q"], d["k"], d["v"], d["g"], d["beta"], meta, scale, d.get("h0"), state, l2)
     torch.cuda.synchronize()
     stages.check_status(tape.status)
 
@@ -80,7 +80,7 @@ def test_backward_stages(name):
     meta = M.chunk_meta(torch.tensor(cu, dtype=torch.int32, device=dev), tuple(cu), 1, cu[-1], dev)
     scale = 1.0 / math.sqrt(128)
     d = {n: t.to(dev) for n, t in x.items()}
-    o, final, tape = stages.forward(d["q"], d["k"], d["v"], d["g"], d["beta"], meta, scale, d.get("h0"), state, l2)
+    o, final, tape, _ = stages.forward(d["q"], d["k"], d["v"], d["g"], d["beta"], meta, scale, d.get("h0"), state, l2)
     dq, dk, dv, dg, dbeta, dh0, dh_tape, dv_new = stages.backward(tape, meta, scale, d["do"], d.get("dht"),
                                                                   d.get("h0"), state)
     torch.cuda.synchronize()

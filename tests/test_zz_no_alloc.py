@@ -30,7 +30,7 @@ def _forward_both(seq_lens, heads, seed, state):
         cu.append(cu[-1] + n)
     meta = M.chunk_meta(torch.tensor(cu, dtype=torch.int32, device=dev), tuple(cu), 1, cu[-1], dev)
     scale = 1.0 / math.sqrt(128)
-    o_ref, final_ref, tape = stages.forward(x["q"], x["k"], x["v"], x["g"], x["beta"], meta, scale, x.get("h0"), state,
+    o_ref, final_ref, tape, _ = stages.forward(x["q"], x["k"], x["v"], x["g"], x["beta"], meta, scale, x.get("h0"), state,
                                             False)
     o = torch.full_like(o_ref, float("nan"))
     final = torch.full_like(final_ref, float("nan")) if state else None
