@@ -86,6 +86,14 @@ typedef struct MekGdnDims {
   const int32_t* seq_chunk_start; /* device [N + 1]: first chunk of each sequence */
 } MekGdnDims;
 
+/* Chunk tables from a device cu_seqlens (int32, or int64 when offsets_are_int64) [num_seqs + 1], in one launch and
+ * without a host round trip: chunk_start, chunk_len, chunk_seq int32 [bound] and seq_chunk_start int32 [num_seqs + 1],
+ * bound >= ceil(total_tokens / 64) + num_seqs.  Entries past the real chunk count are pad chunks (length 0), which
+ * every kernel skips.  Replaces the reference's device-side `meta` launch (reference:
+ * miles_ext_kernels/cake/_impl/gdn/ops.py:311-376, 1808-1858). */
+int mek_gdn_chunk_meta(const void* cu_seqlens, int offsets_are_int64, int num_seqs, int bound, int32_t* chunk_start,
+                       int32_t* chunk_len, int32_t* chunk_seq, int32_t* seq_chunk_start, void* stream);
+
 /* y = bf16(x r), r = 1 / sqrt(sum x^2 + 1e-6) per row of 128 bf16; rstd[row] = r.
  * Replaces the `prep` stage's q / k normalisation (reference: miles_ext_kernels/cake/_impl/gdn/ops.py:1361-1380). */
 int mek_gdn_l2norm(const void* x, void* y, float* rstd, int64_t rows, void* stream);

@@ -99,7 +99,21 @@ def _from_host(seq_lens: tuple[int, ...], device: torch.device) -> ChunkMeta:
 
 
 def _from_device(cu_seqlens: torch.Tensor, total_tokens: int) -> ChunkMeta:
-    """Tables from a device ``cu_seqlens`` with torch integer ops only: no synchronisation, padded extents."""
+    """Tables from a device ``cu_seqlens``: no synchronisation, padded extents (``ceil(T / 64) + N`` chunks, the
+    surplus being pad chunks of length 0).  On a GPU one launch of the library's ``chunk_meta`` kernel; for a host
+    tensor (the CPU tests of the layout logic) the same tables by torch integer ops."""
+    if cu_seqlens.is_cuda:
+        from . import native
+
+        num_seqs = cu_seqlens.numel() - 1
+        bound = (total_tokens + CHUNK - 1) // CHUNK + num_seqs
+        cu = cu_seqlens.contiguous()
+        flat = torch.empty(3 * bound + num_seqs + 1, dtype=torch.int32, device=cu.device)
+        with torch.cuda.device(cu.device):
+            native.launch("gdn_chunk_meta", cu, int(cu.dtype == torch.int64), num_seqs, bound, flat[:bound],
+                          flat[bound : 2 * bound], flat[2 * bound : 3 * bound], flat[3 * bound :], device=cu.device)
+        return ChunkMeta(flat[:bound], flat[bound : 2 * bound], flat[2 * bound : 3 * bound], flat[3 * bound :], bound,
+                         num_seqs, total_tokens, False, (total_tokens + CHUNK - 1) // CHUNK + 1)
     cu = cu_seqlens.to(torch.int64)
     num_seqs = cu.numel() - 1
     bound = (total_tokens + CHUNK - 1) // CHUNK + num_seqs

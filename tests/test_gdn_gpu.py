@@ -203,3 +203,21 @@ def test_rejections_match_the_reference_messages():
         gdn.chunk_gated_delta_rule(q, q, v, g, g, use_gate_in_kernel=True)
     with pytest.raises(NotImplementedError, match="bfloat16"):
         gdn.chunk_gated_delta_rule(q.float(), q.float(), v.float(), g, g)
+
+
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int64], ids=["int32", "int64"])
+def test_the_chunk_table_kernel_gives_the_torch_route_tables(dtype):
+    """The device route's one-launch table kernel against the same tables built by torch integer ops on the host
+    copy, pad chunks included: ragged, empty and single-token sequences, and more sequences than threads."""
+    from miles_ext_kernels_b200.cake._impl.gdn import meta as meta_module
+
+    gen = torch.Generator().manual_seed(3)
+    layouts = [(64,), (1,), (63, 65, 0, 128, 1), (300, 0, 0, 724), tuple(int(n) for n in torch.randint(0, 200, (1500,), generator=gen))]
+    for seq_lens in layouts:
+        cu = torch.tensor([0, *torch.tensor(seq_lens).cumsum(0).tolist()], dtype=dtype)
+        total = int(cu[-1])
+        want = meta_module._from_device(cu, total)
+        got = meta_module._from_device(cu.cuda(), total)
+        assert (got.num_chunks, got.num_seqs, got.total_tokens, got.exact) == (want.num_chunks, want.num_seqs, total, False)
+        for name in ("chunk_start", "chunk_len", "chunk_seq", "seq_chunk_start"):
+            assert torch.equal(getattr(got, name).cpu(), getattr(want, name)), (seq_lens[:8], name)
