@@ -168,6 +168,8 @@ KERNEL_BYTES = {
     "gdn_wy_fwd": lambda H, HV: 2 * 256 * H + 256 * HV + 8 * HV + (2 * 128 + 2 * 256) * HV,
     "gdn_fwd_h": lambda H, HV: 256 * H + (2 * 256 + 4) * HV + (512 + 256) * HV,
     "gdn_fwd_o": lambda H, HV: 256 * H + (128 + 256 + 512 + 4) * HV + 256 * HV,
+    # the scan with the output fused in: fwd_h's traffic + q, Aqk in and o out (h is not read back)
+    "gdn_fwd_ho": lambda H, HV: 2 * 256 * H + (2 * 256 + 4 + 128) * HV + (512 + 2 * 256) * HV,
     "gdn_bwd_dh": lambda H, HV: 2 * 256 * H + (256 + 256 + 128 + 4) * HV + (512 + 256) * HV,
     "gdn_bwd_tail": lambda H, HV: 2 * 256 * H + (256 + 8 + 2 * 128 + 2 * 512 + 3 * 256) * HV + 2 * 256 * H
     + (256 + 8) * HV,
@@ -197,6 +199,7 @@ KERNEL_FLOPS = {  # per (chunk, value head): dense contractions as 2 m n k
     "gdn_wy_fwd": 2 * 128 * 64 * 128 + 2 * 64**3 / 3 + 2 * 2 * 64 * 128 * 64,
     "gdn_fwd_h": 2 * 64 * 128 * 128 + 2 * 128 * 128 * 64,
     "gdn_fwd_o": 2 * 64 * 128 * 128 + 2 * 64 * 128 * 64,
+    "gdn_fwd_ho": 2 * 2 * 64 * 128 * 128 + 2 * 128 * 128 * 64 + 2 * 64 * 128 * 64,
     "gdn_bwd_dh": 2 * 64 * 128 * 128 + 2 * 64 * 128 * 64 + 2 * 2 * 128 * 128 * 64,
     # 4 products [64 x 128, K = 128], 3 of [64 x 64, K = 128], 6 of [64 x 128, K = 64], 2 of [64 x 64, K = 64]
     "gdn_bwd_tail": 4 * 2 * 64 * 128 * 128 + 3 * 2 * 64 * 64 * 128 + 6 * 2 * 64 * 128 * 64 + 2 * 2 * 64**3,

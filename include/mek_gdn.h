@@ -116,6 +116,15 @@ int mek_gdn_wy_fwd(const MekGdnDims* dims, const void* q, const void* k, const v
 int mek_gdn_fwd_h(const MekGdnDims* dims, const void* k, const void* w, const void* u, const float* g_cs,
                   const float* h0, void* h_tape, void* v_new, float* final_state, int32_t* status, void* stream);
 
+/* The state scan with the output fused in (the reference's `fwd_ho`): mek_gdn_fwd_h that also writes
+ * o bf16 [T, HV, 128] = bf16(scale 2^G (q h_tape) + Aqk v_new) chunk by chunk from the h_tape and v_new the step
+ * holds in shared memory; h_tape and v_new are still written for the backward.  On segment dims it is the real walk
+ * of a segmented plan.  Replaces the `fwd_h` + `fwd_o` launches (reference:
+ * miles_ext_kernels/cake/_impl/gdn/ops.py:1191-1317, 1425-1440; cake_chain.py:1868-1973 of the det package). */
+int mek_gdn_fwd_ho(const MekGdnDims* dims, const void* q, const void* k, const void* w, const void* u, const void* aqk,
+                   const float* g_cs, const float* h0, void* h_tape, void* v_new, void* o, float* final_state,
+                   int32_t* status, void* stream);
+
 /* Output per (chunk, value head): o bf16 [T, HV, 128] = bf16(scale 2^G (q h_tape) + Aqk v_new).
  * Replaces the `fwd_o` launch (reference: ops.py:1425-1440). */
 int mek_gdn_fwd_o(const MekGdnDims* dims, const void* q, const void* aqk, const void* v_new, const void* h_tape,

@@ -1,7 +1,8 @@
 """The stages of the GDN forward and backward as launches of the native library, on packed ``[T, heads, 128]``
 operands.  No stage synchronises; all run on torch's current stream.
 
-Forward (reference launch order: miles_ext_kernels/cake/_impl/gdn/ops.py:1320-1450): prep -> wy -> fwd_h -> fwd_o.
+Forward (reference launch order: miles_ext_kernels/cake/_impl/gdn/ops.py:1320-1450): prep -> wy -> fwd_ho (the state
+scan with the output fused in; the separate fwd_o launch remains in the library).
 Backward (reference: ops.py:1474-1735): bwd_dh (adjoint scan with dv_local fused) -> bwd_tail (dq, dk, dv, dbeta, dg
 with the group sum, the norm's pull-back and the in-chunk gate suffix sum fused).
 
@@ -70,7 +71,18 @@ def _l2norm(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return y, rstd
 
 
-def _scan_forward(dims, meta: ChunkMeta, k, w, u, g_cs, h0, h, v_new, want_final: bool, status, scan_segments: int):
+def _walk_forward(dims, k, w, u, g_cs, h0, h, v_new, final, status, output) -> None:
+    """One launch of the state scan over ``dims``' sequences; with ``output = (q, aqk, o)`` the walk writes the op's
+    output too."""
+    if output is None:
+        native.launch("gdn_fwd_h", dims, k, w, u, g_cs, h0, h, v_new, final, status, device=k.device)
+    else:
+        q, aqk, o = output
+        native.launch("gdn_fwd_ho", dims, q, k, w, u, aqk, g_cs, h0, h, v_new, o, final, status, device=k.device)
+
+
+def _scan_forward(dims, meta: ChunkMeta, k, w, u, g_cs, h0, h, v_new, want_final: bool, status, scan_segments: int,
+                  output=None):
     """The state scan: one serial walk per (sequence, value head), or the planner's segmented form (pre-scan,
     stitch, real walk over the segments).  Returns the final state or None."""
     device = k.device
@@ -78,7 +90,7 @@ def _scan_forward(dims, meta: ChunkMeta, k, w, u, g_cs, h0, h, v_new, want_final
     plan = scan.plan_for(meta, HV, device, scan_segments)
     if plan is None:
         final = torch.empty((meta.num_seqs, HV, HEAD_DIM, HEAD_DIM), dtype=F32, device=device) if want_final else None
-        native.launch("gdn_fwd_h", dims, k, w, u, g_cs, h0, h, v_new, final, status, device=device)
+        _walk_forward(dims, k, w, u, g_cs, h0, h, v_new, final, status, output)
         return final
     seg_dims = scan.segment_dims(dims, plan)
     summary = workspace.take(OP, "scan_summary", (plan.segments, HV, 2, HEAD_DIM, HEAD_DIM), F32, device)
@@ -90,7 +102,7 @@ def _scan_forward(dims, meta: ChunkMeta, k, w, u, g_cs, h0, h, v_new, want_final
     seg_final = None
     if want_final:
         seg_final = workspace.take(OP, "scan_final", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
-    native.launch("gdn_fwd_h", seg_dims, k, w, u, g_cs, seg_state, h, v_new, seg_final, status, device=device)
+    _walk_forward(seg_dims, k, w, u, g_cs, seg_state, h, v_new, seg_final, status, output)
     return seg_final.index_select(0, plan.last_index) if want_final else None
 
 
@@ -154,13 +166,13 @@ def forward(q, k, v, g, beta32, meta: ChunkMeta, scale: float, h0, output_final_
     v_new = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
     if exchange is not None:
         h0, output_final_state = exchange.forward_begin(dims, meta, k, w, u, g_cs, status)
-    final_state = _scan_forward(dims, meta, k, w, u, g_cs, h0, h, v_new, output_final_state, status, scan_segments)
+    # the output is written by the walk itself (h_tape and v_new are consumed from shared memory, not read back)
+    o = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    final_state = _scan_forward(dims, meta, k, w, u, g_cs, h0, h, v_new, output_final_state, status, scan_segments,
+                                output=(q, aqk, o))
     if exchange is not None:
         exchange.forward_end(final_state)
         final_state = None
-
-    o = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
-    native.launch("gdn_fwd_o", dims, q, aqk, v_new, h, g_cs, o, status, device=device)
 
     if not keep_state:
         w = u = h = v_new = None

@@ -257,27 +257,35 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
 //   5. h = gamma h + D2.
 // The next chunk's w / k / u tiles and gates arrive by cp.async while the current chunk computes (two stages).
 struct FwdHSmem {
-  static constexpr uint32_t kStage = 3 * 16384;   // w, k, u tiles of one chunk
-  static constexpr uint32_t kW = 0, kK = 16384, kU = 32768;
+  static constexpr uint32_t kStage = 4 * 16384 + 8192;   // w, k, u, q tiles and Aqk of one chunk
+  static constexpr uint32_t kW = 0, kK = 16384, kU = 32768, kQ = 49152, kAqk = 65536;
   static constexpr uint32_t kH = 2 * kStage;      // [128 k][128 v] bf16(h), 2 blocks of 16 KiB (one per V half)
   static constexpr uint32_t kVS = kH + 32768;     // [64][128] bf16(rowscale v_new)
-  static constexpr uint32_t kG = kVS + 16384;     // gates[2][128]: GDN g2 per token [64]; KDA chunk-end gate per channel
+  static constexpr uint32_t kVN = kVS + 16384;    // [64][128] v_new (the fused output's operand)
+  static constexpr uint32_t kG = kVN + 16384;     // gates[2][128]: GDN g2 per token [64]; KDA chunk-end gate per channel
   static constexpr uint32_t kBytes = kG + 1024;
 };
 
+// With `o` != nullptr the walk also writes the op's output, chunk by chunk (the reference's fused `fwd_ho`):
+//   o = bf16(qscale (q h_tape) + Aqk v_new)
+// Both products read what the step already holds in shared memory (h_tape, v_new) and run on the tensor core behind
+// the step's own products; their epilogue runs one step later, in the shadow of the next step's first wait, on a
+// second set of tensor-memory columns -- the chain of dependent steps does not get longer and h is not read back.
 // `gl2` != nullptr selects the per-channel-decay variant (KDA): `k` then holds k 2^{G_L - G} (the decay to the chunk
 // end is folded into the operand, so rowscale = 1) and the state decays per key channel: row k by 2^{gl2[c, hv, k]}.
 struct FwdHMaps {
-  CUtensorMap k, w, u;  // rows, box 64 x 64
+  CUtensorMap k, w, u, q;  // rows, box 64 x 64 (q: the fused output only)
+  CUtensorMap aqk;         // tiles [num_tiles * 64, 64], box 64 x 64 (the fused output only)
 };
 
 __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     const __grid_constant__ FwdHMaps maps, const float* __restrict__ g_cs, const float* __restrict__ h0, __nv_bfloat16* __restrict__ h_tape,
     __nv_bfloat16* __restrict__ v_new, float* __restrict__ final_state, const int32_t* __restrict__ chunk_start,
     const int32_t* __restrict__ chunk_len, const int32_t* __restrict__ seq_chunk_start, int num_qk_heads,
-    int num_v_heads, const float* __restrict__ gl2, const ScanPlan plan, int32_t* __restrict__ status) {
+    int num_v_heads, const float* __restrict__ gl2, const ScanPlan plan, __nv_bfloat16* __restrict__ o, float scale,
+    int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  __shared__ uint64_t bar, bar_load[2];
+  __shared__ uint64_t bar, bar_o, bar_load[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -307,14 +315,16 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     }
   }
 
+  const bool fused = o != nullptr && !prescan;
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar_o, 1);
     mbar_init(&bar_load[0], 1);
     mbar_init(&bar_load[1], 1);
     fence_mbar_init();
     abort_flag = 0;
   }
-  if (warp == 0) tmem_alloc(&tmem_slot, 256);
+  if (warp == 0) tmem_alloc(&tmem_slot, 512);
   const uint32_t sbase = smem_u32(sm);
   const int64_t v_stride = int64_t(num_v_heads) * kDim;
   const int c_begin = c_first, c_end = c_last;
@@ -325,10 +335,15 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     const int start = chunk_start[c], len = chunk_len[c];
     const uint32_t base = sbase + stage * FwdHSmem::kStage;
     if (tid == 32) {
-      mbar_arrive_expect(&bar_load[stage], 3 * 16384);
+      mbar_arrive_expect(&bar_load[stage], fused ? 4 * 16384 + 8192 : 3 * 16384);
       tma_load_tile128(base + FwdHSmem::kW, 8192, &maps.w, hv * kDim, start, &bar_load[stage]);
       tma_load_tile128(base + FwdHSmem::kK, 8192, &maps.k, hq * kDim, start, &bar_load[stage]);
       tma_load_tile128(base + FwdHSmem::kU, 8192, &maps.u, hv * kDim, start, &bar_load[stage]);
+      if (fused) {
+        tma_load_tile128(base + FwdHSmem::kQ, 8192, &maps.q, hq * kDim, start, &bar_load[stage]);
+        tma_load_box(base + FwdHSmem::kAqk, &maps.aqk, 0, int((int64_t(c) * num_v_heads + hv) * 64),
+                     &bar_load[stage]);
+      }
     }
     if (kda) {
       if (tid < 128) cp_async4(smem_u32(s_g2 + stage * 128 + tid), gl2 + (int64_t(c) * num_v_heads + hv) * kDim + tid);
@@ -362,6 +377,34 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
   const Operand op_h{sbase + FwdHSmem::kH, 16384}, op_vs{sbase + FwdHSmem::kVS, 8192};
+  const Operand op_vn{sbase + FwdHSmem::kVN, 8192};
+  // tensor-memory columns: D1 0..63 (lane split), D2 128..255, the fused output's two accumulators (q h_tape at +0,
+  // Aqk v_new at +64, both lane split) in one of two sets at 256 and 384
+  constexpr uint32_t kColO = 256;
+  // this thread's piece of a [64 x 128] lane-split accumulator: row out_row, logical columns out_col .. + 32
+  const int out_row = quad * 16 + (lane & 15), out_col = (lane >> 4) * 64 + half * 32;
+
+  // the fused output of the previous chunk: its products were committed on bar_o a step ago
+  uint32_t phase_o = 0;
+  int prev_start = 0, prev_len = 0;
+  float prev_qs = 0.f;
+  auto write_output = [&](int c_prev) {
+    if (!mbar_wait(&bar_o, phase_o)) abort.raise();
+    phase_o ^= 1;
+    tc_fence_after();
+    const uint32_t set = kColO + uint32_t((c_prev - c_begin) & 1) * 128;
+    float a[32], b[32];
+    tmem_ld32(tmem_addr(tmem, warp, set + half * 32), a);
+    tmem_ld32(tmem_addr(tmem, warp, set + 64 + half * 32), b);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) a[j] = fmaf(prev_qs, a[j], b[j]);
+    if (out_row < prev_len) {
+      __nv_bfloat16* dst = o + int64_t(prev_start + out_row) * v_stride + hv * kDim + out_col;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = pack8(a + 8 * j);
+    }
+  };
 
   uint32_t phase = 0;
   for (int c = c_begin; c < c_end; ++c) {
@@ -386,6 +429,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
       clear_tile_rows<256>(st + FwdHSmem::kW, len, tid);
       clear_tile_rows<256>(st + FwdHSmem::kK, len, tid);
       clear_tile_rows<256>(st + FwdHSmem::kU, len, tid);
+      if (fused) clear_tile_rows<256>(st + FwdHSmem::kQ, len, tid);
     }
     if (transfer) clear_tile_rows<256>(st + FwdHSmem::kU, 0, tid);  // the homogeneous recurrence: u = 0
     fence_async_smem();
@@ -400,8 +444,17 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
       umma_gemm<64, 64>(tmem, op_w, false, op_h, true, 128, false);
       umma_gemm<64, 64>(tmem + (16u << 16), op_w, false, operand_at(op_h, 0, 1), true, 128, false);
       umma_commit(&bar);
+      if (fused) {  // q h_tape, behind the step's own product
+        const Operand op_q{sbase + stage * FwdHSmem::kStage + FwdHSmem::kQ, 8192};
+        const uint32_t set = tmem + kColO + uint32_t((c - c_begin) & 1) * 128;
+        umma_gemm<64, 64>(set, op_q, false, op_h, true, 128, false);
+        umma_gemm<64, 64>(set + (16u << 16), op_q, false, operand_at(op_h, 0, 1), true, 128, false);
+      }
     }
-    if (c + 1 < c_end) prefetch(c + 1, stage ^ 1);  // the other stage's last readers finished a step ago
+    // the previous chunk's output, in the shadow of this step's first wait; its products were the other stage's
+    // last readers, so the next chunk's tiles may only be requested after them
+    if (fused && c > c_begin) write_output(c - 1);
+    if (c + 1 < c_end) prefetch(c + 1, stage ^ 1);
     if (!mbar_wait(&bar, phase)) abort.raise();
     phase ^= 1;
     tc_fence_after();
@@ -427,8 +480,14 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
           uv[e] = live ? uv[e] - d[jj * 8 + e] : 0.f;
           vs[e] = rs * uv[e];
         }
-        if (live && !prescan) reinterpret_cast<uint4*>(vrow)[jj] = pack8(uv);
+        const uint4 packed = pack8(uv);
+        if (live && !prescan) reinterpret_cast<uint4*>(vrow)[jj] = packed;
         set_tile_chunk(sm + FwdHSmem::kVS, 8192, i, (lcol >> 3) + jj, pack8(vs));
+        if (fused) set_tile_chunk(sm + FwdHSmem::kVN, 8192, i, (lcol >> 3) + jj, packed);
+      }
+      if (fused) {  // what the output's epilogue needs one step from now
+        prev_start = start, prev_len = len;
+        prev_qs = kda ? scale : scale * fast_exp2(g2[i]);
       }
     }
     fence_async_smem();
@@ -439,6 +498,13 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     if (tid == 0) {
       umma_gemm<128, 128>(tmem + 128, op_k, true, op_vs, true, 64, false);
       umma_commit(&bar);
+      if (fused) {  // Aqk v_new, behind the state update's product
+        const Operand op_a{sbase + stage * FwdHSmem::kStage + FwdHSmem::kAqk, 8192};
+        const uint32_t set = tmem + kColO + uint32_t((c - c_begin) & 1) * 128 + 64;
+        umma_gemm<64, 64>(set, op_a, false, op_vn, true, 64, false);
+        umma_gemm<64, 64>(set + (16u << 16), op_a, false, operand_at(op_vn, 0, 1), true, 64, false);
+        umma_commit(&bar_o);
+      }
     }
     if (!mbar_wait(&bar, phase)) abort.raise();
     phase ^= 1;
@@ -454,6 +520,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
       for (int j = 0; j < 32; ++j) h[p * 32 + j] = fmaf(gamma, h[p * 32 + j], d[j]);
     }
   }
+  if (fused && c_end > c_begin && !abort.raised()) write_output(c_end - 1);
   cp_async_wait_all();
   tc_fence_before();
   __syncthreads();
@@ -466,7 +533,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     for (int j = 0; j < 16; ++j) dst[j] = make_float4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
   }
   if (abort.raised() && tid == 0) atomicExch(status, kDevWaitTimeout | (2 << 8));
-  if (warp == 0) tmem_dealloc(tmem, 256);
+  if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -629,9 +696,15 @@ int mek_gdn_wy_fwd(const MekGdnDims* d, const void* q, const void* k, const void
 }
 
 namespace {
+struct FusedOutput {
+  const void* q;
+  const void* aqk;
+  void* o;
+};
+
 int launch_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* u, const float* g_cs, const float* h0,
                  void* h_tape, void* v_new, float* final_state, const float* gl2, const mek::ScanPlan& plan,
-                 int32_t* status, void* stream, const char* what) {
+                 const FusedOutput& fused, int32_t* status, void* stream, const char* what) {
   using namespace mek;
   const size_t smem = FwdHSmem::kBytes + 1024;
   if (int rc = want_smem(gdn_fwd_h_kernel, smem, what)) return rc;
@@ -639,19 +712,41 @@ int launch_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* 
   if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, what)) return rc;
   if (int rc = make_rows_map(&maps.w, w, d->total_tokens, d->num_v_heads, what)) return rc;
   if (int rc = make_rows_map(&maps.u, u, d->total_tokens, d->num_v_heads, what)) return rc;
+  if (fused.o != nullptr) {
+    if (int rc = make_rows_map(&maps.q, fused.q, d->total_tokens, d->num_qk_heads, what)) return rc;
+    if (int rc = make_tiles_map(&maps.aqk, fused.aqk, int64_t(d->num_chunks) * d->num_v_heads, 64, 64, what))
+      return rc;
+  } else {
+    maps.q = maps.k;  // never read
+    maps.aqk = maps.k;
+  }
   const dim3 grid(d->num_seqs, d->num_v_heads, plan.seg_flags != nullptr ? 2 : 1);
   gdn_fwd_h_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(
       maps, g_cs, h0, static_cast<__nv_bfloat16*>(h_tape), static_cast<__nv_bfloat16*>(v_new), final_state,
-      d->chunk_start, d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, gl2, plan, status);
+      d->chunk_start, d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, gl2, plan,
+      static_cast<__nv_bfloat16*>(fused.o), d->scale, status);
   return launched(what);
 }
 const mek::ScanPlan kNoPlan = {nullptr, nullptr, nullptr, 0, 0.f};
+const FusedOutput kNoOutput = {nullptr, nullptr, nullptr};
 }  // namespace
 
 int mek_gdn_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* u, const float* g_cs, const float* h0,
                   void* h_tape, void* v_new, float* final_state, int32_t* status, void* stream) {
   if (int rc = check_dims(d, "fwd_h")) return rc;
-  return launch_fwd_h(d, k, w, u, g_cs, h0, h_tape, v_new, final_state, nullptr, kNoPlan, status, stream, "fwd_h");
+  return launch_fwd_h(d, k, w, u, g_cs, h0, h_tape, v_new, final_state, nullptr, kNoPlan, kNoOutput, status, stream,
+                      "fwd_h");
+}
+
+int mek_gdn_fwd_ho(const MekGdnDims* d, const void* q, const void* k, const void* w, const void* u, const void* aqk,
+                   const float* g_cs, const float* h0, void* h_tape, void* v_new, void* o, float* final_state,
+                   int32_t* status, void* stream) {
+  using namespace mek;
+  if (int rc = check_dims(d, "fwd_ho")) return rc;
+  if (!q || !aqk || !o) return fail(MEK_ERR_INVALID, "fwd_ho: q, aqk or o is null");
+  const FusedOutput fused = {q, aqk, o};
+  return launch_fwd_h(d, k, w, u, g_cs, h0, h_tape, v_new, final_state, nullptr, kNoPlan, fused, status, stream,
+                      "fwd_ho");
 }
 
 int mek_gdn_fwd_h_prescan(const MekGdnDims* d, const void* k, const void* w, const void* u, const float* g_cs,
@@ -662,7 +757,7 @@ int mek_gdn_fwd_h_prescan(const MekGdnDims* d, const void* k, const void* w, con
   if (!seg_flags || !state_row || !summary || warm_chunks < 0)
     return fail(MEK_ERR_INVALID, "fwd_h_prescan: a null table or summary, or negative warm_chunks");
   const ScanPlan plan = {seg_flags, state_row, summary, warm_chunks, warm_log2};
-  return launch_fwd_h(d, k, w, u, g_cs, boundary, nullptr, nullptr, nullptr, nullptr, plan, status, stream,
+  return launch_fwd_h(d, k, w, u, g_cs, boundary, nullptr, nullptr, nullptr, nullptr, plan, kNoOutput, status, stream,
                       "fwd_h_prescan");
 }
 
@@ -672,7 +767,8 @@ int mek_kda_fwd_h(const MekGdnDims* d, const void* kr, const void* w, const void
   if (int rc = check_dims(d, "kda_fwd_h")) return rc;
   if (d->num_qk_heads != d->num_v_heads) return fail(MEK_ERR_INVALID, "kda_fwd_h: KDA has one value head per key head");
   if (gl2 == nullptr) return fail(MEK_ERR_INVALID, "kda_fwd_h: gl2 is null");
-  return launch_fwd_h(d, kr, w, u, nullptr, h0, h_tape, v_new, final_state, gl2, kNoPlan, status, stream, "kda_fwd_h");
+  return launch_fwd_h(d, kr, w, u, nullptr, h0, h_tape, v_new, final_state, gl2, kNoPlan, kNoOutput, status, stream,
+                      "kda_fwd_h");
 }
 
 int mek_gdn_fwd_o(const MekGdnDims* d, const void* q, const void* aqk, const void* v_new, const void* h_tape,
