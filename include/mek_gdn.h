@@ -51,6 +51,7 @@ int mek_check_device(int device);
  *   idesc         instruction descriptor
  *   d_lane        first tensor-memory lane of the accumulator: 0, or 16 (an M = 64 accumulator may sit in the upper
  *                 half of each 32-lane quadrant, sharing its columns with another M = 64 accumulator)
+ *   tf32          0: kind::f16 (bf16 operands, K = 16 per instruction); 1: kind::tf32 (fp32 words, K = 8)
  *   out           device float [128 * ncols], row = tensor-memory lane
  *   status        device int32, 0 = fine
  * With nk = 0 nothing is issued: the kernel's wait runs into its one-second limit, status becomes 1 and the kernel
@@ -58,7 +59,7 @@ int mek_check_device(int device);
  * No counterpart in the reference (its kernels are generated and tested end to end). */
 int mek_selftest_umma(const void* a_img, int a_bytes, const void* b_img, int b_bytes, uint64_t a_desc, uint64_t b_desc,
                       const int32_t* a_off, const int32_t* b_off, int nk, uint32_t idesc, int ncols, int d_lane,
-                      float* out, int32_t* status, void* stream);
+                      int tf32, float* out, int32_t* status, void* stream);
 
 /* Self-test of the tile loads: one box (64 bf16 columns x box_rows rows, 128-byte swizzle) of the row-major bf16
  * matrix src [rows, cols] whose first element is (x, y) is copied by the copy engine (TMA) into shared memory and

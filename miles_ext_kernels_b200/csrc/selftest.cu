@@ -15,7 +15,8 @@ char* error_buffer() {
 __global__ void __launch_bounds__(128) selftest_umma_kernel(const uint4* a_img, int a_bytes, const uint4* b_img,
                                                             int b_bytes, uint64_t a_desc, uint64_t b_desc,
                                                             const int32_t* a_off, const int32_t* b_off, int nk,
-                                                            uint32_t idesc, int ncols, int d_lane, float* out, int32_t* status) {
+                                                            uint32_t idesc, int ncols, int d_lane, int tf32,
+                                                            float* out, int32_t* status) {
   extern __shared__ uint8_t raw[];
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_slot;
@@ -44,7 +45,10 @@ __global__ void __launch_bounds__(128) selftest_umma_kernel(const uint4* a_img, 
     for (int k = 0; k < nk; ++k) {
       const uint64_t da = a_desc | uint64_t(((a0 + uint32_t(a_off[k])) >> 4) & 0x3FFFu);
       const uint64_t db = b_desc | uint64_t(((b0 + uint32_t(b_off[k])) >> 4) & 0x3FFFu);
-      umma_f16(tmem + (uint32_t(d_lane) << 16), da, db, idesc, k > 0 ? 1u : 0u);
+      if (tf32)
+        umma_tf32(tmem + (uint32_t(d_lane) << 16), da, db, idesc, k > 0 ? 1u : 0u);
+      else
+        umma_f16(tmem + (uint32_t(d_lane) << 16), da, db, idesc, k > 0 ? 1u : 0u);
     }
     umma_commit(&bar);
   }
@@ -112,7 +116,7 @@ int mek_check_device(int device) {
 
 int mek_selftest_umma(const void* a_img, int a_bytes, const void* b_img, int b_bytes, uint64_t a_desc, uint64_t b_desc,
                       const int32_t* a_off, const int32_t* b_off, int nk, uint32_t idesc, int ncols, int d_lane,
-                      float* out, int32_t* status, void* stream) {
+                      int tf32, float* out, int32_t* status, void* stream) {
   using namespace mek;
   if (a_bytes <= 0 || b_bytes <= 0 || a_bytes > 65536 || b_bytes > 65536 || a_bytes % 16 || b_bytes % 16)
     return fail(MEK_ERR_INVALID, "selftest: operand images must be 16..65536 bytes, multiples of 16");
@@ -123,7 +127,7 @@ int mek_selftest_umma(const void* a_img, int a_bytes, const void* b_img, int b_b
   if (int rc = want_smem(selftest_umma_kernel, smem, "selftest")) return rc;
   selftest_umma_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(a_img), a_bytes, static_cast<const uint4*>(b_img), b_bytes, a_desc, b_desc, a_off,
-      b_off, nk, idesc, ncols, d_lane, out, status);
+      b_off, nk, idesc, ncols, d_lane, tf32, out, status);
   return launched("selftest");
 }
 

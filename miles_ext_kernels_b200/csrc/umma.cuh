@@ -161,6 +161,25 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
       : "memory");
 }
 
+// The same with TF32 operands (fp32 words in shared memory, 10 mantissa bits used), K = 8 per instruction.
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Instruction descriptor of tcgen05.mma.kind::tf32 (operand format code 2), fp32 accumulator, both operands K-major
+// unless said otherwise.
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n, bool neg_a = false) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(neg_a) << 13) | (uint32_t(n >> 3) << 17) |
+         (uint32_t(m >> 4) << 24);
+}
+
 // Arrive on `bar` once every tcgen05.mma issued so far by this thread has completed (implies
 // tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {

@@ -54,7 +54,7 @@ def run_case(lib, m, n, k, a_mn, b_mn, neg_a, seed=0, d_lane=0):
     p = lambda x: ctypes.c_void_p(x.data_ptr())  # noqa: E731
     rc = lib.mek_selftest_umma(
         p(a_d), a_img.size, p(b_d), b_img.size, ctypes.c_uint64(a_desc), ctypes.c_uint64(b_desc), p(ao), p(bo),
-        len(a_off), ctypes.c_uint32(idesc(m, n, a_mn, b_mn, neg_a)), n, d_lane, p(out), p(status),
+        len(a_off), ctypes.c_uint32(idesc(m, n, a_mn, b_mn, neg_a)), n, d_lane, 0, p(out), p(status),
         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
     )
     lib.check(rc)
@@ -108,7 +108,7 @@ def test_a_wait_that_nothing_satisfies_runs_out_and_reports_it():
     begin = time.perf_counter()
     rc = lib.mek_selftest_umma(p(img), 1024, p(img), 1024, ctypes.c_uint64(desc_template(16)),
                                ctypes.c_uint64(desc_template(16)), p(off), p(off), 0,
-                               ctypes.c_uint32(idesc(64, 16, False, False)), 16, 0, p(out), p(status),
+                               ctypes.c_uint32(idesc(64, 16, False, False)), 16, 0, 0, p(out), p(status),
                                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     lib.check(rc)
     torch.cuda.synchronize()
@@ -143,3 +143,40 @@ def test_tma_box_lands_in_the_operand_layout(box_rows, x, y):
     box[:live] = src[y:y + live, x:x + 64]
     want, _ = tile_image(box)
     assert np.array_equal(out.cpu().numpy(), want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k,neg_a,d_lane", [(64, 32, 32, False, 0), (64, 32, 32, True, 16), (64, 64, 64, False, 0),
+                                                (128, 64, 32, False, 0)])
+def test_tf32_operands_in_the_swizzled_layout(m, n, k, neg_a, d_lane):
+    """kind::tf32 with K-major fp32 operands (blocks of 32 columns = 128 bytes, the same 16-byte-chunk swizzle, K = 8
+    per instruction): what the WY kernel's blocked triangular inverse relies on."""
+    from miles_ext_kernels_b200.cake._runtime import loader
+    from umma_images import idesc_tf32, kmajor_offsets_f32, tile_image_f32
+
+    lib = loader.load_library()
+    rng = np.random.default_rng(m + n + k)
+    a = bf16_round(rng.standard_normal((m, k)).astype(np.float32))  # exact in tf32
+    b = bf16_round(rng.standard_normal((n, k)).astype(np.float32))
+    a_img, a_stride = tile_image_f32(a)
+    b_img, b_stride = tile_image_f32(b)
+    a_off, b_off = kmajor_offsets_f32(k, a_stride), kmajor_offsets_f32(k, b_stride)
+    dev = torch.device("cuda")
+    a_d, b_d = torch.from_numpy(a_img.copy()).to(dev), torch.from_numpy(b_img.copy()).to(dev)
+    ao = torch.tensor(a_off, dtype=torch.int32, device=dev)
+    bo = torch.tensor(b_off, dtype=torch.int32, device=dev)
+    ncols = max(16, n)
+    out = torch.zeros(128, ncols, dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    p = lambda x: ctypes.c_void_p(x.data_ptr())  # noqa: E731
+    rc = lib.mek_selftest_umma(p(a_d), a_img.size, p(b_d), b_img.size, ctypes.c_uint64(desc_template(16)),
+                               ctypes.c_uint64(desc_template(16)), p(ao), p(bo), len(a_off),
+                               ctypes.c_uint32(idesc_tf32(m, n, neg_a)), ncols, d_lane, 1, p(out), p(status),
+                               ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    lib.check(rc)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want = (a.astype(np.float64) @ b.astype(np.float64).T) * (-1.0 if neg_a else 1.0)
+    lanes = np.array([lane_of_row(m, r) + d_lane for r in range(m)])
+    got = out.cpu().numpy()[lanes][:, :n]
+    assert np.abs(got - want).max() <= 1e-4 * np.abs(want).max()

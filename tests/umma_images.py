@@ -63,3 +63,28 @@ def mnmajor_offsets(kdim: int) -> list[int]:
 def lane_of_row(m_rows: int, row: int) -> int:
     """Tensor-memory lane that holds accumulator row ``row`` for an M = 128 or M = 64 instruction."""
     return row if m_rows == 128 else (row % 16) + 32 * (row // 16)
+
+
+def tile_image_f32(tile: np.ndarray) -> tuple[np.ndarray, int]:
+    """The bytes of a [rows, cols] fp32 tile (cols a multiple of 32) in the same swizzled layout: one block per 32
+    columns (128 bytes per row), row r's 16-byte chunk c (4 floats) at ``r * 128 + ((c ^ (r & 7)) << 4)``."""
+    rows, cols = tile.shape
+    assert cols % 32 == 0 and rows % 8 == 0
+    blocks, stride = cols // 32, rows * 128
+    words = np.ascontiguousarray(tile, dtype=np.float32).view(np.uint32)
+    image = np.zeros(blocks * stride // 4, dtype=np.uint32)
+    for b in range(blocks):
+        for r in range(rows):
+            for c in range(8):
+                dst = (b * stride + r * 128 + ((c ^ (r & 7)) << 4)) // 4
+                image[dst : dst + 4] = words[r, b * 32 + c * 4 : b * 32 + c * 4 + 4]
+    return image.view(np.uint8), stride
+
+
+def idesc_tf32(m: int, n: int, neg_a: bool = False) -> int:
+    return (1 << 4) | (2 << 7) | (2 << 10) | (int(neg_a) << 13) | ((n >> 3) << 17) | ((m >> 4) << 24)
+
+
+def kmajor_offsets_f32(kdim: int, block_stride: int) -> list[int]:
+    """Start-address offsets of each K = 8 tf32 instruction when the contraction runs along the tile's columns."""
+    return [(k0 // 32) * block_stride + (k0 % 32) * 4 for k0 in range(0, kdim, 8)]
