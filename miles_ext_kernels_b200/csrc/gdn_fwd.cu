@@ -71,9 +71,13 @@ struct WySmem {
   static constexpr uint32_t kBytes = kScal + 512;
 };
 
-// fp32 L[i][j] in a [64][64] array whose 16-byte groups are XOR-swizzled by the row, so that rows written by
-// different threads spread over the banks and a row is still read in 16-byte pieces
-__device__ __forceinline__ int wy_l_index(int i, int j) { return i * 64 + (j ^ ((i & 7) << 2)); }
+// fp32 L[i][j] as a K-major tf32 operand: two blocks of 32 columns (8 KiB each), 128 bytes per row, the 16-byte
+// chunks of a row XOR-swizzled by the row (the layout of every operand tile, with 4-byte elements)
+__device__ __forceinline__ int wy_l_index(int i, int j) {
+  return (j >> 5) * 2048 + i * 32 + ((((j & 31) >> 2) ^ (i & 7)) << 2) + (j & 3);
+}
+// float index of element (row, k) of a one-block fp32 operand of 32 contraction columns
+__device__ __forceinline__ int f32_block_index(int row, int k) { return row * 32 + (((k >> 2) ^ (row & 7)) << 2) + (k & 3); }
 
 // Three CTAs per SM (shared memory) hide each other's global-load and solve latencies; tensor memory: 128 columns.
 struct WyMaps {
@@ -184,17 +188,23 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   tc_fence_before();
   __syncthreads();
 
-  // A = (I + L)^-1 : thread c solves (I + L) x = e_c by forward substitution (columns are independent)
+  // A = (I + L)^-1 by blocks of 32: with I + L = [[M11, 0], [L21, M22]],
+  //     A = [[X11, 0], [X21, X22]],  X11 = M11^-1, X22 = M22^-1 (fp32 forward substitution, 64 threads, 496 FMAs each)
+  //     X21 = -X22 (L21 X11)  (two tensor-core products with TF32 operands; A is rounded to bf16 afterwards)
+  // The dead k tile holds the products' operands: B1 = X11^T [32 x 32], A2 = [0; X22] [64 x 32], B2 = T^T [32 x 32].
+  float* s_b1 = reinterpret_cast<float*>(sm + WySmem::kK);
+  float* s_a2 = s_b1 + 1024;
+  float* s_b2 = s_a2 + 2048;
+  uint8_t* a_tile = sm + WySmem::kA;
   if (tid < 64) {
-    // x_i = delta_ic - sum_{j < i} L_ij x_j; four partial sums per row shorten the dependent FMA chain, and the
-    // row of L comes in 16-byte broadcasts (entries at and above the diagonal are zero)
-    float x[64];
+    const int b = tid >> 5, c = tid & 31, base = 32 * b;
+    float x[32];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      float acc0 = (i == tid) ? 1.f : 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    for (int i = 0; i < 32; ++i) {
+      float acc0 = (i == c) ? 1.f : 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
       for (int j = 0; j < i; j += 4) {
-        const float4 l = *reinterpret_cast<const float4*>(s_l + wy_l_index(i, j));
+        const float4 l = *reinterpret_cast<const float4*>(s_l + wy_l_index(base + i, base + j));
         acc0 = fmaf(-l.x, x[j], acc0);
         if (j + 1 < i) acc1 = fmaf(-l.y, x[j + 1], acc1);
         if (j + 2 < i) acc2 = fmaf(-l.z, x[j + 2], acc2);
@@ -202,12 +212,76 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
       }
       x[i] = (acc0 + acc1) + (acc2 + acc3);
     }
-    uint8_t* at = sm + WySmem::kA;
+    const int col = base + c;
 #pragma unroll
-    for (int i = 0; i < 64; ++i)
-      *reinterpret_cast<__nv_bfloat16*>(at + sw128_offset(i, tid >> 3) + (tid & 7) * 2) = __float2bfloat16_rn(x[i]);
+    for (int i = 0; i < 32; ++i)
+      *reinterpret_cast<__nv_bfloat16*>(a_tile + sw128_offset(base + i, col >> 3) + (col & 7) * 2) =
+          __float2bfloat16_rn(x[i]);
+    if (b == 0) {  // row c of B1 = column c of X11
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        *reinterpret_cast<float4*>(s_b1 + f32_block_index(c, i)) = make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]);
+    } else {  // column c of X22 in the rows 32..63 of A2
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s_a2[f32_block_index(32 + i, c)] = x[i];
+    }
+  } else {  // rows 0..31 of A2 and the upper right block of A are zero
+    const int t = tid - 64;
+    for (int i = t; i < 256; i += 64) reinterpret_cast<float4*>(s_a2)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = t; i < 32 * 4; i += 64)
+      set_tile_chunk(a_tile, 8192, i >> 2, 4 + (i & 3), make_uint4(0u, 0u, 0u, 0u));
   }
   fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const uint32_t l_addr = sbase + WySmem::kQ, k_addr = sbase + WySmem::kK;
+  constexpr uint32_t kColT = 64, kColX = 96;  // free until the w / u products
+  if (tid == 0) {  // T' = L[:, 0:32] X11 (rows 32..63 are T = L21 X11)
+    const uint32_t idesc = umma_idesc_tf32(64, 32);
+    for (uint32_t k0 = 0; k0 < 32; k0 += 8)
+      umma_tf32(tmem + kColT, umma_desc_sw128(l_addr + k0 * 4, 16u, kSbo), umma_desc_sw128(k_addr + k0 * 4, 16u, kSbo),
+                idesc, k0 > 0 ? 1u : 0u);
+    umma_commit(&bar);
+  }
+  ok = mbar_wait(&bar, 1) && ok;
+  tc_fence_after();
+  {
+    float t[32];
+    tmem_ld32(tmem_addr(tmem, warp, kColT), t);
+    tmem_ld_wait();
+    if (warp >= 2 && lane < 16) {  // row i = 16 warp + lane of T' -> column i - 32 of B2 = T^T
+      const int kk = 16 * warp + lane - 32;
+#pragma unroll
+      for (int n = 0; n < 32; ++n) s_b2[f32_block_index(n, kk)] = t[n];
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (tid == 0) {  // X' = -A2 T (rows 32..63 are X21)
+    const uint32_t idesc = umma_idesc_tf32(64, 32, /*neg_a=*/true);
+    for (uint32_t k0 = 0; k0 < 32; k0 += 8)
+      umma_tf32(tmem + kColX, umma_desc_sw128(k_addr + 4096 + k0 * 4, 16u, kSbo),
+                umma_desc_sw128(k_addr + 12288 + k0 * 4, 16u, kSbo), idesc, k0 > 0 ? 1u : 0u);
+    umma_commit(&bar);
+  }
+  ok = mbar_wait(&bar, 0) && ok;
+  tc_fence_after();
+  {
+    float xv[32];
+    tmem_ld32(tmem_addr(tmem, warp, kColX), xv);
+    tmem_ld_wait();
+    if (warp >= 2 && lane < 16) {
+      const int i = 16 * warp + lane;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) set_tile_chunk(a_tile, 8192, i, j, pack8(xv + 8 * j));
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
   __syncthreads();
   tc_fence_after();
 
@@ -222,7 +296,7 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   }
   // A -> global while the MMAs run
   store_tile<64, 64, 128>(sm + WySmem::kA, 8192, a_out + (int64_t(c) * num_v_heads + hv) * 4096, 64, 64, tid);
-  ok = mbar_wait(&bar, 1) && ok;
+  ok = mbar_wait(&bar, 1) && ok;  // the fourth commit on this barrier
   tc_fence_after();
 
   ok = __all_sync(0xffffffffu, ok);
