@@ -460,23 +460,29 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
 
   // the fused output of the previous chunk: its products were committed on bar_o a step ago
   uint32_t phase_o = 0;
-  int prev_start = 0, prev_len = 0;
-  float prev_qs = 0.f;
-  auto write_output = [&](int c_prev) {
-    if (!mbar_wait(&bar_o, phase_o)) abort.raise();
-    phase_o ^= 1;
-    tc_fence_after();
+  struct Rows {
+    int start, len;
+    float qs;
+  } cur = {0, 0, 0.f}, prev = {0, 0, 0.f};  // of the chunk the walk is at / of the one before it
+  // in two parts (16 of this thread's 32 columns each), one per wait shadow of the step: a part is about as long
+  // as the wait it hides in
+  auto write_output = [&](int c_prev, int part, const Rows& rows) {
+    if (part == 0) {
+      if (!mbar_wait(&bar_o, phase_o)) abort.raise();
+      phase_o ^= 1;
+      tc_fence_after();
+    }
     const uint32_t set = kColO + uint32_t((c_prev - c_begin) & 1) * 128;
-    float a[32], b[32];
-    tmem_ld32(tmem_addr(tmem, warp, set + half * 32), a);
-    tmem_ld32(tmem_addr(tmem, warp, set + 64 + half * 32), b);
+    float a[16], b[16];
+    tmem_ld16(tmem_addr(tmem, warp, set + half * 32 + part * 16), a);
+    tmem_ld16(tmem_addr(tmem, warp, set + 64 + half * 32 + part * 16), b);
     tmem_ld_wait();
 #pragma unroll
-    for (int j = 0; j < 32; ++j) a[j] = fmaf(prev_qs, a[j], b[j]);
-    if (out_row < prev_len) {
-      __nv_bfloat16* dst = o + int64_t(prev_start + out_row) * v_stride + hv * kDim + out_col;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = pack8(a + 8 * j);
+    for (int j = 0; j < 16; ++j) a[j] = fmaf(rows.qs, a[j], b[j]);
+    if (out_row < rows.len) {
+      __nv_bfloat16* dst = o + int64_t(rows.start + out_row) * v_stride + hv * kDim + out_col + part * 16;
+      reinterpret_cast<uint4*>(dst)[0] = pack8(a);
+      reinterpret_cast<uint4*>(dst)[1] = pack8(a + 8);
     }
   };
 
@@ -527,7 +533,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     }
     // the previous chunk's output, in the shadow of this step's first wait; its products were the other stage's
     // last readers, so the next chunk's tiles may only be requested after them
-    if (fused && c > c_begin) write_output(c - 1);
+    if (fused && c > c_begin) write_output(c - 1, 0, cur);  // `cur` still describes chunk c - 1 here
     if (c + 1 < c_end) prefetch(c + 1, stage ^ 1);
     if (!mbar_wait(&bar, phase)) abort.raise();
     phase ^= 1;
@@ -560,8 +566,8 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
         if (fused) set_tile_chunk(sm + FwdHSmem::kVN, 8192, i, (lcol >> 3) + jj, packed);
       }
       if (fused) {  // what the output's epilogue needs one step from now
-        prev_start = start, prev_len = len;
-        prev_qs = kda ? scale : scale * fast_exp2(g2[i]);
+        prev = cur;
+        cur = {start, len, kda ? scale : scale * fast_exp2(g2[i])};
       }
     }
     fence_async_smem();
@@ -580,6 +586,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
         umma_commit(&bar_o);
       }
     }
+    if (fused && c > c_begin) write_output(c - 1, 1, prev);
     if (!mbar_wait(&bar, phase)) abort.raise();
     phase ^= 1;
     tc_fence_after();
@@ -594,7 +601,10 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
       for (int j = 0; j < 32; ++j) h[p * 32 + j] = fmaf(gamma, h[p * 32 + j], d[j]);
     }
   }
-  if (fused && c_end > c_begin && !abort.raised()) write_output(c_end - 1);
+  if (fused && c_end > c_begin && !abort.raised()) {
+    write_output(c_end - 1, 0, cur);
+    write_output(c_end - 1, 1, cur);
+  }
   cp_async_wait_all();
   tc_fence_before();
   __syncthreads();
