@@ -221,3 +221,48 @@ def test_the_chunk_table_kernel_gives_the_torch_route_tables(dtype):
         assert (got.num_chunks, got.num_seqs, got.total_tokens, got.exact) == (want.num_chunks, want.num_seqs, total, False)
         for name in ("chunk_start", "chunk_len", "chunk_seq", "seq_chunk_start"):
             assert torch.equal(getattr(got, name).cpu(), getattr(want, name)), (seq_lens[:8], name)
+
+
+def test_forward_and_backward_replay_from_a_cuda_graph():
+    """The op is capturable: no host synchronisation, no allocation outside torch's capture-aware allocator, tensor
+    maps travel as kernel parameters.  A replay on new inputs written into the captured buffers gives the bits of an
+    eager call on those inputs."""
+    import miles_ext_kernels_b200 as package
+    from miles_ext_kernels_b200.cake import gdn
+
+    dev = torch.device("cuda")
+    seq_lens = (200, 312)
+    cu = _cu(seq_lens)
+    first, second = (draw(seq_lens, (2, 4), seed=s) for s in (41, 42))
+    want = run(second, seq_lens)
+    static = {n: first[n].to(dev).unsqueeze(0).clone() for n in ("q", "k", "v", "g", "do")}
+    static["beta"] = first["beta"].to(dev).bfloat16().unsqueeze(0).clone()
+    cu_dev = torch.tensor(cu, dtype=torch.int32, device=dev)
+
+    def step():
+        leaves = {n: static[n].detach().requires_grad_(True) for n in ("q", "k", "v", "g", "beta")}
+        o, _ = gdn.chunk_gated_delta_rule(leaves["q"], leaves["k"], leaves["v"], g=leaves["g"], beta=leaves["beta"],
+                                          cu_seqlens=cu_dev, cu_seqlens_cpu=cu, use_qk_l2norm_in_kernel=True)
+        o.backward(static["do"])
+        return [o.detach()] + [leaves[n].grad for n in ("q", "k", "v", "g", "beta")]
+
+    package.configure(cake_workspace_pool_bytes=1 << 28)  # the pool is bypassed while capturing
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            outs = step()
+        for n in ("q", "k", "v", "g", "do"):
+            static[n].copy_(second[n].to(dev).unsqueeze(0))
+        static["beta"].copy_(second["beta"].to(dev).bfloat16().unsqueeze(0))
+        graph.replay()
+        torch.cuda.synchronize()
+    finally:
+        package.configure()
+    got = dict(zip(NAMES, (t[0].cpu() for t in outs)))
+    assert_same_bits(got, {n: want[n] for n in NAMES}, "graph replay")
