@@ -89,8 +89,8 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
   const int c_begin = c_first, c_end = c_last;
 
   // the tiles of chunk c by TMA (one issuing thread), its gates by cp.async
-  auto prefetch = [&](int c, int stage) {
-    const int start = chunk_start[c], len = chunk_len[c];
+  // (warps 2.. issue the gate copies: warp 0 also issues the MMAs and must not wait on anything here)
+  auto prefetch = [&](int c, int stage, int start, int len) {
     const uint32_t base = sbase + stage * BwdDhSmem::kStage;
     if (tid == 32) {
       mbar_arrive_expect(&bar_load[stage], 4 * 16384 + 8192);
@@ -100,15 +100,19 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
       tma_load_tile128(base + BwdDhSmem::kDO, 8192, &maps.d_o, hv * kDim, start, &bar_load[stage]);
       tma_load_box(base + BwdDhSmem::kAqk, &maps.aqk, 0, int((int64_t(c) * num_v_heads + hv) * 64), &bar_load[stage]);
     }
+    const int t = tid - 64;
     if (kda) {
-      if (tid < 128) cp_async4(smem_u32(s_g2 + stage * 128 + tid), gl2 + (int64_t(c) * num_v_heads + hv) * kDim + tid);
-    } else if (tid < 64) {
-      cp_async4(smem_u32(s_g2 + stage * 128 + tid),
-                g_cs + int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv);
+      if (t >= 0 && t < 128) cp_async4(smem_u32(s_g2 + stage * 128 + t), gl2 + (int64_t(c) * num_v_heads + hv) * kDim + t);
+    } else if (t >= 0 && t < 64) {
+      cp_async4(smem_u32(s_g2 + stage * 128 + t), g_cs + int64_t(start + (t < len ? t : len - 1)) * num_v_heads + hv);
     }
     cp_async_commit();
   };
-  if (c_begin < c_end) prefetch(c_end - 1, 0);
+  int start = 0, len = 0;
+  if (c_begin < c_end) {
+    start = chunk_start[c_end - 1], len = chunk_len[c_end - 1];
+    prefetch(c_end - 1, 0, start, len);
+  }
 
   // fp32 adjoint state: 64 columns of row krow
   float dh[64];
@@ -136,7 +140,9 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
   uint32_t phase = 0;
   for (int c = c_end - 1; c >= c_begin; --c) {
     const int stage = (c_end - 1 - c) & 1;
-    const int start = chunk_start[c], len = chunk_len[c];
+    // the next chunk's extent: requested now, needed when its tiles are (nothing on the step's path waits for it)
+    int next_start = 0, next_len = 0;
+    if (c > c_begin) next_start = chunk_start[c - 1], next_len = chunk_len[c - 1];
     const int64_t tile = int64_t(c) * num_v_heads + hv;
     uint8_t* st = sm + stage * BwdDhSmem::kStage;
     const uint32_t sst = sbase + stage * BwdDhSmem::kStage;
@@ -175,7 +181,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
       umma_gemm<64, 64>(tmem + kD1b + (16u << 16), op_aqk, true, operand_at(op_do, 0, 1), true, 64, false);
       umma_commit(&bar);
     }
-    if (c > c_begin) prefetch(c - 1, stage ^ 1);
+    if (c > c_begin) prefetch(c - 1, stage ^ 1, next_start, next_len);
     if (!mbar_wait(&bar, phase)) abort.raise();
     phase ^= 1;
     tc_fence_after();
@@ -234,6 +240,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
 #pragma unroll
       for (int j = 0; j < 32; ++j) dh[p * 32 + j] = fmaf(gamma, dh[p * 32 + j], d[j]);
     }
+    start = next_start, len = next_len;
   }
   cp_async_wait_all();
   tc_fence_before();

@@ -405,8 +405,8 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
   __syncthreads();  // the barriers' initialisation is visible before the first copy is issued
 
   // the tiles of chunk c by TMA (one issuing thread), its gates by cp.async
-  auto prefetch = [&](int c, int stage) {
-    const int start = chunk_start[c], len = chunk_len[c];
+  // (warps 2.. issue the gate copies: warp 0 also issues the MMAs and must not wait on anything here)
+  auto prefetch = [&](int c, int stage, int start, int len) {
     const uint32_t base = sbase + stage * FwdHSmem::kStage;
     if (tid == 32) {
       mbar_arrive_expect(&bar_load[stage], fused ? 4 * 16384 + 8192 : 3 * 16384);
@@ -419,15 +419,19 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
                      &bar_load[stage]);
       }
     }
+    const int t = tid - 64;
     if (kda) {
-      if (tid < 128) cp_async4(smem_u32(s_g2 + stage * 128 + tid), gl2 + (int64_t(c) * num_v_heads + hv) * kDim + tid);
-    } else if (tid < 64) {
-      cp_async4(smem_u32(s_g2 + stage * 128 + tid),
-                g_cs + int64_t(start + (tid < len ? tid : len - 1)) * num_v_heads + hv);
+      if (t >= 0 && t < 128) cp_async4(smem_u32(s_g2 + stage * 128 + t), gl2 + (int64_t(c) * num_v_heads + hv) * kDim + t);
+    } else if (t >= 0 && t < 64) {
+      cp_async4(smem_u32(s_g2 + stage * 128 + t), g_cs + int64_t(start + (t < len ? t : len - 1)) * num_v_heads + hv);
     }
     cp_async_commit();
   };
-  if (c_begin < c_end) prefetch(c_begin, 0);
+  int start = 0, len = 0;
+  if (c_begin < c_end) {
+    start = chunk_start[c_begin], len = chunk_len[c_begin];
+    prefetch(c_begin, 0, start, len);
+  }
 
   // fp32 state: 64 columns of row krow
   float h[64];
@@ -489,7 +493,9 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
   uint32_t phase = 0;
   for (int c = c_begin; c < c_end; ++c) {
     const int stage = (c - c_begin) & 1;
-    const int start = chunk_start[c], len = chunk_len[c];
+    // the next chunk's extent: requested now, needed when its tiles are (nothing on the step's path waits for it)
+    int next_start = 0, next_len = 0;
+    if (c + 1 < c_end) next_start = chunk_start[c + 1], next_len = chunk_len[c + 1];
     uint8_t* st = sm + stage * FwdHSmem::kStage;
     const Operand op_w{sbase + stage * FwdHSmem::kStage + FwdHSmem::kW, 8192};
     const Operand op_k{sbase + stage * FwdHSmem::kStage + FwdHSmem::kK, 8192};
@@ -534,7 +540,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     // the previous chunk's output, in the shadow of this step's first wait; its products were the other stage's
     // last readers, so the next chunk's tiles may only be requested after them
     if (fused && c > c_begin) write_output(c - 1, 0, cur);  // `cur` still describes chunk c - 1 here
-    if (c + 1 < c_end) prefetch(c + 1, stage ^ 1);
+    if (c + 1 < c_end) prefetch(c + 1, stage ^ 1, next_start, next_len);
     if (!mbar_wait(&bar, phase)) abort.raise();
     phase ^= 1;
     tc_fence_after();
@@ -600,6 +606,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
 #pragma unroll
       for (int j = 0; j < 32; ++j) h[p * 32 + j] = fmaf(gamma, h[p * 32 + j], d[j]);
     }
+    start = next_start, len = next_len;
   }
   if (fused && c_end > c_begin && !abort.raised()) {
     write_output(c_end - 1, 0, cur);

@@ -224,14 +224,28 @@ __device__ __forceinline__ Operand operand_at(const Operand& t, uint32_t rows, u
 
 // D[M x N] (+)= A * B over a contraction of `kdim` (multiple of 16).  a_mn/b_mn pick the operand role of each tile.
 // Issued by ONE thread; `accumulate` says whether the first instruction adds to what tensor memory holds.
+//
+// The issuing thread is on the critical path of its whole CTA (its warp joins the epilogue late), so the loop does
+// no descriptor arithmetic: the first step's descriptors are built once and the later ones differ only in the 14-bit
+// start-address field, by a constant (K-major: +32 bytes per step, and at every fourth step on to the next
+// 64-column block; MN-major: +2048 bytes per step).  Shared addresses stay below 256 KiB, so the field never carries.
 template <int M, int N>
 __device__ __forceinline__ void umma_gemm(uint32_t tmem_d, const Operand& a, bool a_mn, const Operand& b, bool b_mn,
                                           uint32_t kdim, bool accumulate, bool neg_a = false) {
   const uint32_t idesc = umma_idesc(M, N, a_mn, b_mn, neg_a);
-  for (uint32_t k0 = 0; k0 < kdim; k0 += 16) {
-    const uint64_t da = a_mn ? desc_mnmajor(a, k0) : desc_kmajor(a, k0);
-    const uint64_t db = b_mn ? desc_mnmajor(b, k0) : desc_kmajor(b, k0);
-    umma_f16(tmem_d, da, db, idesc, (accumulate || k0 > 0) ? 1u : 0u);
+  uint64_t da = a_mn ? desc_mnmajor(a, 0) : desc_kmajor(a, 0);
+  uint64_t db = b_mn ? desc_mnmajor(b, 0) : desc_kmajor(b, 0);
+  const uint32_t a_step = a_mn ? 128u : 2u, b_step = b_mn ? 128u : 2u;  // in 16-byte units
+  const uint32_t a_jump = a_mn ? 128u : (a.block_stride >> 4) - 6u;     // K-major: from column 48 to the next block
+  const uint32_t b_jump = b_mn ? 128u : (b.block_stride >> 4) - 6u;
+  const uint32_t steps = kdim >> 4;
+#pragma unroll
+  for (uint32_t k = 0; k < 8; ++k) {
+    if (k < steps) {
+      umma_f16(tmem_d, da, db, idesc, (accumulate || k > 0) ? 1u : 0u);
+      da += (k & 3u) == 3u ? a_jump : a_step;
+      db += (k & 3u) == 3u ? b_jump : b_step;
+    }
   }
 }
 
