@@ -311,6 +311,34 @@ def run_ours(args) -> None:
     d2h = sum(x.numel() * x.element_size() for x in e2e_step())
     torch.cuda.synchronize()
 
+    # the form the training framework calls (GDN only): q, k, v as strided views of one packed row per key head
+    # [q | k | its value heads], raw q / k with the L2 norm inside the op; gradients land in the packed row
+    miles_form = None
+    if cfg.op == "gdn":
+        group = HV // H
+        mixed = torch.cat([resident["q"], resident["k"],
+                           resident["v"].reshape(*resident["v"].shape[:2], H, group * 128)], dim=-1)
+        mixed = mixed.reshape(*resident["q"].shape[:2], -1).contiguous()
+
+        def miles_step():
+            row = mixed.detach().requires_grad_(True)
+            q, k, v = row.view(*row.shape[:2], H, -1).split([128, 128, group * 128], dim=-1)
+            v = v.reshape(*row.shape[:2], HV, 128)
+            g, beta = resident["g"].detach().requires_grad_(True), resident["beta"].detach().requires_grad_(True)
+            h0 = resident["h0"] if "h0" in resident else None
+            o, _ = gdn.chunk_gated_delta_rule(q, k, v, g=g, beta=beta, initial_state=h0, cu_seqlens=cu_dev,
+                                              cu_seqlens_cpu=work.cu_seqlens, use_qk_l2norm_in_kernel=True)
+            o.backward(resident["do"])
+            return row.grad
+
+        for _ in range(3):
+            miles_step()
+        ms_miles = timed(miles_step, args.steps)
+        miles_form = {"ms_per_step": ms_miles / args.steps, "value": world * tokens / (ms_miles * 1e-3 / args.steps),
+                      "unit": UNIT, "what": "q, k, v as strided views of one packed row; L2 norm of q / k in the op; "
+                      "gradient of the packed row"}
+        del mixed
+
     # per-kernel device times: a separate pass of the same steps with events around every launch
     prof = native.LaunchLog(timed=True)
     native.set_launch_log(prof)
@@ -355,6 +383,7 @@ def run_ours(args) -> None:
         "roofline": roofline,
         "path_roofline": {"t_roof_ms": 1e3 * t_roof, "frac": t_roof / step_s, "flops_per_token": flops_per_token(HV),
                           "bytes_per_token": bytes_per_token(H, HV, op=cfg.op), "peak_source": f"of {peak_kind}"},
+        "miles_form": miles_form,
         "kernels_ms": {n: {"mean": v[0], "launches": v[1], "total": v[2]} for n, v in per_kernel.items()},
         "clocks": clocks,
     }
