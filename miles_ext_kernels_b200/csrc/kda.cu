@@ -61,14 +61,14 @@ struct KdaIntraSmem {
   static constexpr uint32_t kA = 0;                                 // [64][64] bf16 (after the pair phase)
   static constexpr uint32_t kKB = 8192;                             // [64][128] beta kg
   static constexpr uint32_t kVB = kKB + 16384;                      // [64][128] beta v
-  static constexpr uint32_t kSqk = ((kG + 64 * kRow * 4 + 1023) / 1024) * 1024;  // fp32 [64][65]
-  static constexpr uint32_t kSkk = kSqk + 64 * 65 * 4;
-  static constexpr uint32_t kL = kSkk + 64 * 65 * 4;                // fp32 [64][68]
+  static constexpr uint32_t kSqk = ((kG + 64 * kRow * 4 + 1023) / 1024) * 1024;  // fp32 [2][64][65]: one per channel half
+  static constexpr uint32_t kSkk = kSqk + 2 * 64 * 65 * 4;
+  static constexpr uint32_t kL = kSkk + 2 * 64 * 65 * 4;            // fp32 [64][68]
   static constexpr uint32_t kBeta = kL + 64 * 68 * 4;               // beta[64]
   static constexpr uint32_t kBytes = kBeta + 256;
 };
 
-__global__ void __launch_bounds__(160) kda_intra_kernel(
+__global__ void __launch_bounds__(288) kda_intra_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
     const __nv_bfloat16* __restrict__ kg, const float* __restrict__ g2, const float* __restrict__ beta,
     __nv_bfloat16* __restrict__ a_out, __nv_bfloat16* __restrict__ aqk_out, __nv_bfloat16* __restrict__ w_out,
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(160) kda_intra_kernel(
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 256);
-  for (int i = tid; i < 64 * 128; i += 160) {
+  for (int i = tid; i < 64 * 128; i += 288) {
     const int r = i >> 7, d = i & 127;
     const bool live = r < len;
     const int64_t at = int64_t(start + (live ? r : len - 1)) * stride + h * kDim + d;
@@ -112,34 +112,73 @@ __global__ void __launch_bounds__(160) kda_intra_kernel(
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
 
-  // pair phase: thread b owns the 4 x 4 block (bi, bj), bj <= bi, of the lower triangle (136 blocks)
-  if (tid < 136) {
-    int bi = int((sqrtf(8.f * tid + 1.f) - 1.f) * 0.5f);
-    while ((bi + 1) * (bi + 2) / 2 <= tid) ++bi;
-    while (bi * (bi + 1) / 2 > tid) --bi;
-    const int bj = tid - bi * (bi + 1) / 2;
+  // pair phase: a thread owns a 4 x 4 block (bi, bj), bj <= bi, of the lower triangle and one half of the channels:
+  // threads 0..239 the 120 blocks below the diagonal, threads 256..287 (one warp) the 16 diagonal blocks.
+  // Below the diagonal every pair of a block is valid and 2^{G_i - G_j} factors as 2^{G_i - G_{j0+3}} 2^{G_{j0+3} - G_j}
+  // with both exponents <= 0: 7 exponentials per channel instead of 16.
+  if (tid < 240) {
+    const int t = tid >> 1, half = tid & 1;
+    int bi = int((sqrtf(8.f * t + 1.f) + 1.f) * 0.5f);
+    while (bi * (bi + 1) / 2 <= t) ++bi;
+    while (bi * (bi - 1) / 2 > t) --bi;
+    const int bj = t - bi * (bi - 1) / 2;
     const int i0 = 4 * bi, j0 = 4 * bj;
     float aqk[4][4], akk[4][4];
 #pragma unroll
     for (int a = 0; a < 4; ++a)
 #pragma unroll
       for (int b = 0; b < 4; ++b) aqk[a][b] = akk[a][b] = 0.f;
-    for (int d = 0; d < 128; ++d) {
-      float qi[4], ki[4], gi[4], kj[4], gj[4];
+    for (int d = half * 64; d < half * 64 + 64; ++d) {
+      float qe[4], ke[4], kj[4], gj[4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        kj[a] = sk[(j0 + a) * kRow + d];
+        gj[a] = sg[(j0 + a) * kRow + d];
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const float ea = fast_exp2(sg[(i0 + a) * kRow + d] - gj[3]);
+        qe[a] = sq[(i0 + a) * kRow + d] * ea;
+        ke[a] = sk[(i0 + a) * kRow + d] * ea;
+      }
+#pragma unroll
+      for (int b = 0; b < 3; ++b) kj[b] *= fast_exp2(gj[3] - gj[b]);
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          aqk[a][b] = fmaf(qe[a], kj[b], aqk[a][b]);
+          akk[a][b] = fmaf(ke[a], kj[b], akk[a][b]);
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        s_qk[half * 4160 + (i0 + a) * 65 + j0 + b] = aqk[a][b];
+        s_kk[half * 4160 + (i0 + a) * 65 + j0 + b] = akk[a][b];
+      }
+  } else if (tid >= 256) {
+    const int bi = (tid - 256) >> 1, half = tid & 1;
+    const int i0 = 4 * bi;
+    float aqk[4][4], akk[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) aqk[a][b] = akk[a][b] = 0.f;
+    for (int d = half * 64; d < half * 64 + 64; ++d) {
+      float qi[4], ki[4], gi[4];
 #pragma unroll
       for (int a = 0; a < 4; ++a) {
         qi[a] = sq[(i0 + a) * kRow + d];
         ki[a] = sk[(i0 + a) * kRow + d];
         gi[a] = sg[(i0 + a) * kRow + d];
-        kj[a] = sk[(j0 + a) * kRow + d];
-        gj[a] = sg[(j0 + a) * kRow + d];
       }
 #pragma unroll
       for (int a = 0; a < 4; ++a)
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const bool valid = j0 + b <= i0 + a;  // the exponent of a valid pair is <= 0
-          const float e = valid ? fast_exp2(gi[a] - gj[b]) * kj[b] : 0.f;
+        for (int b = 0; b <= a; ++b) {  // the exponent of a valid pair is <= 0
+          const float e = fast_exp2(gi[a] - gi[b]) * ki[b];
           aqk[a][b] = fmaf(qi[a], e, aqk[a][b]);
           akk[a][b] = fmaf(ki[a], e, akk[a][b]);
         }
@@ -148,8 +187,8 @@ __global__ void __launch_bounds__(160) kda_intra_kernel(
     for (int a = 0; a < 4; ++a)
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        s_qk[(i0 + a) * 65 + j0 + b] = aqk[a][b];
-        s_kk[(i0 + a) * 65 + j0 + b] = akk[a][b];
+        s_qk[half * 4160 + (i0 + a) * 65 + i0 + b] = aqk[a][b];
+        s_kk[half * 4160 + (i0 + a) * 65 + i0 + b] = akk[a][b];
       }
   }
   __syncthreads();
@@ -165,8 +204,8 @@ __global__ void __launch_bounds__(160) kda_intra_kernel(
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const int j = jj * 8 + e;
-        x[e] = j <= i ? scale * s_qk[i * 65 + j] : 0.f;
-        s_l[i * 68 + j] = j < i ? bi * s_kk[i * 65 + j] : 0.f;
+        x[e] = j <= i ? scale * (s_qk[i * 65 + j] + s_qk[4160 + i * 65 + j]) : 0.f;
+        s_l[i * 68 + j] = j < i ? bi * (s_kk[i * 65 + j] + s_kk[4160 + i * 65 + j]) : 0.f;
       }
       reinterpret_cast<uint4*>(dst)[jj] = pack8(x);
     }
@@ -174,7 +213,7 @@ __global__ void __launch_bounds__(160) kda_intra_kernel(
   __syncthreads();  // the fp32 copies of q / k / G are dead: their space holds the operand tiles from here on
 
   // kb = bf16(beta kg), vb = bf16(beta v)
-  for (int i = tid; i < 64 * 16; i += 160) {
+  for (int i = tid; i < 64 * 16; i += 288) {
     const int r = i >> 4, cc = i & 15;
     const float b = s_beta[r];
     float x[8];
@@ -812,7 +851,7 @@ int mek_kda_intra(const MekGdnDims* d, const void* q, const void* k, const void*
   if (int rc = check_kda(d, "kda_intra")) return rc;
   const size_t smem = KdaIntraSmem::kBytes + 1024;
   if (int rc = want_smem(kda_intra_kernel, smem, "kda_intra")) return rc;
-  kda_intra_kernel<<<dim3(d->num_chunks, d->num_v_heads), 160, smem, static_cast<cudaStream_t>(stream)>>>(
+  kda_intra_kernel<<<dim3(d->num_chunks, d->num_v_heads), 288, smem, static_cast<cudaStream_t>(stream)>>>(
       In(q), In(k), In(v), In(kg), g2, beta, Out(a_out), Out(aqk_out), Out(w_out), Out(u_out), d->chunk_start,
       d->chunk_len, d->num_v_heads, d->scale, status);
   return launched("kda_intra");
