@@ -311,19 +311,18 @@ def run_ours(args) -> None:
     d2h = sum(x.numel() * x.element_size() for x in e2e_step())
     torch.cuda.synchronize()
 
-    # the form the training framework calls (GDN only): q, k, v as strided views of one packed row per key head
-    # [q | k | its value heads], raw q / k with the L2 norm inside the op; gradients land in the packed row
+    # the form the training framework calls (GDN only): q, k, v as views of one packed row [q heads | k heads |
+    # v heads] (what a fused projection writes), raw q / k with the L2 norm inside the op; the op reads the views in
+    # place and the gradient comes back as one packed row
     miles_form = None
     if cfg.op == "gdn":
-        group = HV // H
-        mixed = torch.cat([resident["q"], resident["k"],
-                           resident["v"].reshape(*resident["v"].shape[:2], H, group * 128)], dim=-1)
-        mixed = mixed.reshape(*resident["q"].shape[:2], -1).contiguous()
+        lead = resident["q"].shape[:2]
+        mixed = torch.cat([resident["q"].reshape(*lead, -1), resident["k"].reshape(*lead, -1),
+                           resident["v"].reshape(*lead, -1)], dim=-1).contiguous()
 
         def miles_step():
             row = mixed.detach().requires_grad_(True)
-            q, k, v = row.view(*row.shape[:2], H, -1).split([128, 128, group * 128], dim=-1)
-            v = v.reshape(*row.shape[:2], HV, 128)
+            q, k, v = gdn.packed_qkv_views(row, H, HV)
             g, beta = resident["g"].detach().requires_grad_(True), resident["beta"].detach().requires_grad_(True)
             h0 = resident["h0"] if "h0" in resident else None
             o, _ = gdn.chunk_gated_delta_rule(q, k, v, g=g, beta=beta, initial_state=h0, cu_seqlens=cu_dev,
@@ -335,8 +334,8 @@ def run_ours(args) -> None:
             miles_step()
         ms_miles = timed(miles_step, args.steps)
         miles_form = {"ms_per_step": ms_miles / args.steps, "value": world * tokens / (ms_miles * 1e-3 / args.steps),
-                      "unit": UNIT, "what": "q, k, v as strided views of one packed row; L2 norm of q / k in the op; "
-                      "gradient of the packed row"}
+                      "unit": UNIT, "what": "q, k, v as packed_qkv_views of one [q | k | v] row, read in place; L2 norm "
+                      "of q / k in the op; the gradient is one packed row"}
         del mixed
 
     # per-kernel device times: a separate pass of the same steps with events around every launch

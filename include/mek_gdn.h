@@ -85,6 +85,14 @@ typedef struct MekGdnDims {
   const int32_t* chunk_len;       /* device [NC]: 1..64 */
   const int32_t* chunk_seq;       /* device [NC]: the chunk's sequence */
   const int32_t* seq_chunk_start; /* device [N + 1]: first chunk of each sequence */
+  /* Token strides, in elements, of operands that may be column slices of a wider packed row (q, k, v as views of
+   * one [T, (2 H + HV) * 128] row, gradients written into the packed gradient row); 0 = dense (heads * 128).  Inside
+   * a token the heads stay contiguous.  Multiples of 8 elements (the copy engine's 16-byte rule). */
+  int64_t qk_pitch;               /* of the q and k operands of an entry point */
+  int64_t v_pitch;                /* of v */
+  int64_t raw_pitch;              /* of q_raw and k_raw (gradient tail) */
+  int64_t dqk_pitch;              /* of the dq and dk outputs */
+  int64_t dv_pitch;               /* of the dv output */
 } MekGdnDims;
 
 /* Chunk tables from a device cu_seqlens (int32, or int64 when offsets_are_int64) [num_seqs + 1], in one launch and
@@ -95,9 +103,10 @@ typedef struct MekGdnDims {
 int mek_gdn_chunk_meta(const void* cu_seqlens, int offsets_are_int64, int num_seqs, int bound, int32_t* chunk_start,
                        int32_t* chunk_len, int32_t* chunk_seq, int32_t* seq_chunk_start, void* stream);
 
-/* y = bf16(x r), r = 1 / sqrt(sum x^2 + 1e-6) per row of 128 bf16; rstd[row] = r.
+/* y = bf16(x r), r = 1 / sqrt(sum x^2 + 1e-6) per row of 128 bf16; rstd[row] = r.  Row (token, head) of x sits at
+ * token * x_pitch + head * 128 (x_pitch = 0: dense, heads * 128); y and rstd are dense.
  * Replaces the `prep` stage's q / k normalisation (reference: miles_ext_kernels/cake/_impl/gdn/ops.py:1361-1380). */
-int mek_gdn_l2norm(const void* x, void* y, float* rstd, int64_t rows, void* stream);
+int mek_gdn_l2norm(const void* x, void* y, float* rstd, int64_t rows, int heads, int64_t x_pitch, void* stream);
 
 /* g_cs[t, hv] = log2(e) * chunk-local inclusive cumulative sum of g (fp32 [T, HV]).
  * Replaces the `prep` stage's gate cumsum (reference: ops.py:1361-1380). */

@@ -34,6 +34,12 @@ class Dims(ctypes.Structure):
         ("chunk_len", ctypes.c_void_p),
         ("chunk_seq", ctypes.c_void_p),
         ("seq_chunk_start", ctypes.c_void_p),
+        # token strides (elements) of operands that are column slices of a packed row; 0 = dense
+        ("qk_pitch", ctypes.c_int64),
+        ("v_pitch", ctypes.c_int64),
+        ("raw_pitch", ctypes.c_int64),
+        ("dqk_pitch", ctypes.c_int64),
+        ("dv_pitch", ctypes.c_int64),
     ]
 
 

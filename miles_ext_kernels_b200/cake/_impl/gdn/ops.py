@@ -175,6 +175,36 @@ def _packed(x: torch.Tensor) -> torch.Tensor:
     return x.contiguous().view(x.shape[0] * x.shape[1], *x.shape[2:])
 
 
+def _rows(x: torch.Tensor) -> torch.Tensor:
+    """``[B, T, heads, 128]`` -> ``[B * T, heads, 128]`` without a copy when x is dense or a column slice of a wider
+    packed row (heads contiguous inside a token, tokens a fixed stride apart, 16-byte aligned): the kernels take the
+    token stride.  Anything else is made contiguous first."""
+    B, T = x.shape[0], x.shape[1]
+    if x.is_contiguous():
+        return x.view(B * T, *x.shape[2:])
+    pitch = x.stride(1)
+    sliced = (
+        x.stride(3) == 1 and x.stride(2) == HEAD_DIM and pitch >= x.shape[2] * HEAD_DIM and pitch % 8 == 0
+        and (B == 1 or x.stride(0) == T * pitch) and x.data_ptr() % 16 == 0
+    )
+    if not sliced:
+        return x.contiguous().view(B * T, *x.shape[2:])
+    return x.as_strided((B * T, x.shape[2], HEAD_DIM), (pitch, HEAD_DIM, 1))
+
+
+def _tile_one_row(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    """Whether q, k, v ``[T, heads, 128]`` are the column slices ``[q heads | k heads | v heads]`` of one packed row
+    ``[T, (2 H + HV) * 128]``: their gradients are then written as the same slices of one packed gradient row."""
+    H, HV = q.shape[1], v.shape[1]
+    width = (2 * H + HV) * HEAD_DIM
+    if q.is_contiguous() or not (q.stride(0) == k.stride(0) == v.stride(0) == width):
+        return False
+    if not (q.untyped_storage().data_ptr() == k.untyped_storage().data_ptr() == v.untyped_storage().data_ptr()):
+        return False
+    base = q.storage_offset()
+    return k.storage_offset() == base + H * HEAD_DIM and v.storage_offset() == base + 2 * H * HEAD_DIM
+
+
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     """The kernels with FLA's autograd contract.  ``save_state`` keeps w / u / h / v_new for the backward; without it
     the backward recomputes them with the forward's kernels (the same bits).  ``exchange`` (context parallelism)
@@ -189,7 +219,10 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         with torch.cuda.device(device):
             meta = meta_module.chunk_meta(cu_seqlens, cu_seqlens_cpu, B, T, device)
             beta32 = _packed(beta if beta.dtype == torch.float32 else beta.float())
-            qp, kp, vp, gp = _packed(q), _packed(k), _packed(v), _packed(g)
+            qp, kp, vp, gp = _rows(q), _rows(k), _rows(v), _packed(g)
+            if qp.stride(0) != kp.stride(0):  # the kernels take one token stride for q and k
+                qp, kp = qp.contiguous(), kp.contiguous()
+            ctx.packed_grads = _tile_one_row(qp, kp, vp)
             h0 = None if initial_state is None else initial_state.detach().float().contiguous()
             want_final = bool(output_final_state)
             ctx.scan_segments = _scan_segments()
@@ -219,7 +252,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             dhtp = None if dht is None else dht.float().contiguous()
             want_dh0 = ctx.has_initial_state
             dq, dk, dv, dg, dbeta, dh0, _, _ = stages.backward(tape, meta, ctx.scale, dop, dhtp, ctx.h0, want_dh0,
-                                                               scan_segments=ctx.scan_segments, exchange=ctx.exchange)
+                                                               scan_segments=ctx.scan_segments, exchange=ctx.exchange,
+                                                               packed_grads=ctx.packed_grads)
         dq, dk, dv = dq.view(q_shape), dk.view(q_shape), dv.view(v_shape)
         dg = dg.view(g_shape)
         dbeta = dbeta.view(g_shape)
@@ -241,6 +275,75 @@ def _apply(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlen
         q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu, use_qk_l2norm,
         _save_state(), exchange,
     )
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# packed q / k / v
+# --------------------------------------------------------------------------------------------------------------------
+def _common_row(dq, dk, dv, H: int, HV: int):
+    """The packed gradient row whose column slices ``[q heads | k heads | v heads]`` dq, dk, dv are, or None."""
+    if dq is None or dk is None or dv is None:
+        return None
+    row = dq._base
+    if row is None or dk._base is not row or dv._base is not row or not row.is_contiguous():
+        return None
+    width = (2 * H + HV) * HEAD_DIM
+    size = dq.element_size()
+    tokens = dq.numel() // (H * HEAD_DIM)
+    if row.numel() != tokens * width or row.dtype != dq.dtype:
+        return None
+    if not (dq.stride(-1) == dk.stride(-1) == dv.stride(-1) == 1 and dq.stride(-2) == dk.stride(-2) == dv.stride(-2)
+            == HEAD_DIM and dq.stride(-3) == dk.stride(-3) == dv.stride(-3) == width):
+        return None
+    base = row.data_ptr()
+    if dq.data_ptr() != base or dk.data_ptr() != base + H * HEAD_DIM * size or \
+            dv.data_ptr() != base + 2 * H * HEAD_DIM * size:
+        return None
+    return row
+
+
+class _PackedQkvViews(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, num_qk_heads: int, num_v_heads: int):
+        H, HV = int(num_qk_heads), int(num_v_heads)
+        ctx.heads, ctx.shape = (H, HV), qkv.shape
+        lead = qkv.shape[:-1]
+        q = qkv[..., : H * HEAD_DIM].unflatten(-1, (H, HEAD_DIM))
+        k = qkv[..., H * HEAD_DIM : 2 * H * HEAD_DIM].unflatten(-1, (H, HEAD_DIM))
+        v = qkv[..., 2 * H * HEAD_DIM :].unflatten(-1, (HV, HEAD_DIM))
+        assert q.shape[:-2] == lead
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        H, HV = ctx.heads
+        row = _common_row(dq, dk, dv, H, HV)
+        if row is not None:  # the op wrote the three gradients as the slices of one row: that row is the gradient
+            return row.view(ctx.shape), None, None
+        lead = ctx.shape[:-1]
+        like = next(t for t in (dq, dk, dv) if t is not None)
+        pieces = []
+        for grad, heads in ((dq, H), (dk, H), (dv, HV)):
+            if grad is None:
+                grad = torch.zeros((*lead, heads, HEAD_DIM), dtype=like.dtype, device=like.device)
+            pieces.append(grad.reshape(*lead, heads * HEAD_DIM))
+        return torch.cat(pieces, dim=-1), None, None
+
+
+def packed_qkv_views(qkv: torch.Tensor, num_qk_heads: int, num_v_heads: int):
+    """``q [.., H, 128]``, ``k [.., H, 128]``, ``v [.., HV, 128]`` as views of one packed row ``qkv [.., (2 H + HV) *
+    128]`` laid out ``[q heads | k heads | v heads]`` (the row a fused projection writes).
+
+    :func:`chunk_gated_delta_rule` reads such views in place (no copies) and writes their gradients as the same
+    slices of one packed gradient row; the backward of this split hands that row on as ``qkv``'s gradient instead of
+    concatenating three tensors.  Plain ``split`` / ``view`` views of the row give the same bits, with the
+    concatenation (reference: ``packed_qkv_views`` of the context-parallel packages,
+    miles_ext_kernels/cake/_vendor/cake_gdn_det_train_kcp/README.md:314-356)."""
+    width = (2 * int(num_qk_heads) + int(num_v_heads)) * HEAD_DIM
+    if qkv.shape[-1] != width:
+        raise ValueError(f"packed_qkv_views: the row must hold (2 * {num_qk_heads} + {num_v_heads}) * {HEAD_DIM} = "
+                         f"{width} columns; it has {qkv.shape[-1]}")
+    return _PackedQkvViews.apply(qkv, num_qk_heads, num_v_heads)
 
 
 # --------------------------------------------------------------------------------------------------------------------

@@ -27,11 +27,22 @@ BF16, F32 = torch.bfloat16, torch.float32
 __all__ = ["ForwardTape", "dims_of", "forward", "backward", "check_status"]
 
 
-def dims_of(meta: ChunkMeta, num_qk_heads: int, num_v_heads: int, scale: float) -> native.Dims:
+def pitch_of(x: torch.Tensor | None) -> int:
+    """The token stride (elements) a kernel is told for ``x [T, heads, 128]``: 0 when dense, else ``x.stride(0)`` (x
+    is then a column slice of a wider packed row; its heads are contiguous inside a token)."""
+    if x is None or x.is_contiguous():
+        return 0
+    if x.stride(2) != 1 or x.stride(1) != HEAD_DIM or x.stride(0) % 8 or x.data_ptr() % 16:
+        raise ValueError(f"a strided operand must keep its heads contiguous inside a token; strides {x.stride()}")
+    return int(x.stride(0))
+
+
+def dims_of(meta: ChunkMeta, num_qk_heads: int, num_v_heads: int, scale: float, *, qk_pitch: int = 0,
+            v_pitch: int = 0, raw_pitch: int = 0, dqk_pitch: int = 0, dv_pitch: int = 0) -> native.Dims:
     return native.Dims(
         meta.total_tokens, num_qk_heads, num_v_heads, HEAD_DIM, meta.num_seqs, meta.num_chunks, float(scale),
         meta.chunk_start.data_ptr(), meta.chunk_len.data_ptr(), meta.chunk_seq.data_ptr(),
-        meta.seq_chunk_start.data_ptr(),
+        meta.seq_chunk_start.data_ptr(), qk_pitch, v_pitch, raw_pitch, dqk_pitch, dv_pitch,
     )
 
 
@@ -65,9 +76,10 @@ def check_status(status: torch.Tensor) -> None:
 
 
 def _l2norm(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    y = torch.empty_like(x)
+    """x ``[T, heads, 128]``, dense or a column slice of a packed row -> dense normalised rows and their rstd."""
+    y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
     rstd = torch.empty(x.shape[:-1], dtype=F32, device=x.device)
-    native.launch("gdn_l2norm", x, y, rstd, x.numel() // HEAD_DIM, device=x.device)
+    native.launch("gdn_l2norm", x, y, rstd, x.numel() // HEAD_DIM, x.shape[1], pitch_of(x), device=x.device)
     return y, rstd
 
 
@@ -143,7 +155,6 @@ def forward(q, k, v, g, beta32, meta: ChunkMeta, scale: float, h0, output_final_
     T, H = q.shape[0], q.shape[1]
     HV = v.shape[1]
     NC = meta.num_chunks
-    dims = dims_of(meta, H, HV, scale)
     status = torch.zeros(1, dtype=torch.int32, device=device)
 
     q_raw = k_raw = rstd_q = rstd_k = None
@@ -151,6 +162,8 @@ def forward(q, k, v, g, beta32, meta: ChunkMeta, scale: float, h0, output_final_
         q_raw, k_raw = q, k
         q, rstd_q = _l2norm(q)
         k, rstd_k = _l2norm(k)
+    # q, k, v may be column slices of one packed row (dense heads inside a token): the kernels read them in place
+    dims = dims_of(meta, H, HV, scale, qk_pitch=pitch_of(q), v_pitch=pitch_of(v))
     g_cs = torch.empty_like(g)
     native.launch("gdn_gate_cumsum", dims, g, g_cs, device=device)
 
@@ -186,7 +199,7 @@ def recompute_state(tape: ForwardTape, meta: ChunkMeta, scale: float, h0, scan_s
     T, H = tape.qn.shape[0], tape.qn.shape[1]
     HV = tape.v.shape[1]
     NC = meta.num_chunks
-    dims = dims_of(meta, H, HV, scale)
+    dims = dims_of(meta, H, HV, scale, qk_pitch=pitch_of(tape.qn), v_pitch=pitch_of(tape.v))
     alloc = torch.empty if meta.exact else torch.zeros
     a = workspace.take(OP, "recompute_a", (NC, HV, 64, 64), BF16, device)
     aqk = workspace.take(OP, "recompute_aqk", (NC, HV, 64, 64), BF16, device)
@@ -201,14 +214,28 @@ def recompute_state(tape: ForwardTape, meta: ChunkMeta, scale: float, h0, scan_s
 
 
 def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want_dh0: bool, scan_segments: int = 0,
-             exchange=None):
+             exchange=None, packed_grads: bool = False):
     """``do [T, HV, 128]`` bf16, ``dht [N, HV, 128, 128]`` fp32 or None.  Returns ``(dq, dk [T, H, 128] bf16, dv
-    [T, HV, 128] bf16, dg, dbeta [T, HV] fp32, dh0 [N, HV, 128, 128] fp32 or None)``."""
+    [T, HV, 128] bf16, dg, dbeta [T, HV] fp32, dh0 [N, HV, 128, 128] fp32 or None)``.  With ``packed_grads`` dq, dk
+    and dv are the column slices ``[q heads | k heads | v heads]`` of one ``[T, (2 H + HV) * 128]`` row."""
     device = do.device
     T, H = tape.qn.shape[0], tape.qn.shape[1]
     HV = tape.v.shape[1]
     NC = meta.num_chunks
-    dims = dims_of(meta, H, HV, scale)
+    if packed_grads:
+        row = torch.empty((T, (2 * H + HV) * HEAD_DIM), dtype=BF16, device=device)
+        dq = row[:, : H * HEAD_DIM].view(T, H, HEAD_DIM)
+        dk = row[:, H * HEAD_DIM : 2 * H * HEAD_DIM].view(T, H, HEAD_DIM)
+        dv = row[:, 2 * H * HEAD_DIM :].view(T, HV, HEAD_DIM)
+    else:
+        dq = torch.empty((T, H, HEAD_DIM), dtype=BF16, device=device)
+        dk = torch.empty((T, H, HEAD_DIM), dtype=BF16, device=device)
+        dv = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    raw_pitch = pitch_of(tape.q_raw)
+    if tape.k_raw is not None and pitch_of(tape.k_raw) != raw_pitch:
+        raise ValueError("q and k must share their token stride")
+    dims = dims_of(meta, H, HV, scale, qk_pitch=pitch_of(tape.qn), v_pitch=pitch_of(tape.v), raw_pitch=raw_pitch,
+                   dqk_pitch=pitch_of(dq), dv_pitch=pitch_of(dv))
     if tape.w is None:
         recompute_state(tape, meta, scale, h0, scan_segments)
     if meta.exact:
@@ -222,9 +249,6 @@ def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want
     if exchange is not None:
         exchange.backward_end(dh0)
         dh0 = None
-    dq = torch.empty((T, H, HEAD_DIM), dtype=BF16, device=device)
-    dk = torch.empty((T, H, HEAD_DIM), dtype=BF16, device=device)
-    dv = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
     dbeta = torch.empty((T, HV), dtype=F32, device=device)
     dg = torch.empty((T, HV), dtype=F32, device=device)
     native.launch("gdn_bwd_tail", dims, tape.qn, tape.kn, tape.v, tape.beta32, tape.g_cs, tape.a, tape.aqk, tape.w, tape.u,

@@ -145,8 +145,8 @@ def _forward(q, k, v, g, beta32, cu_seqlens, scale, use_qk_l2norm, *, cu_seqlens
         q_raw, k_raw = q, k
         rstd_q, rstd_k = (torch.empty((S, H), dtype=F32, device=device) for _ in range(2))
         q, k = torch.empty_like(q), torch.empty_like(k)
-        native.launch("gdn_l2norm", q_raw, q, rstd_q, S * H, device=device)
-        native.launch("gdn_l2norm", k_raw, k, rstd_k, S * H, device=device)
+        native.launch("gdn_l2norm", q_raw, q, rstd_q, S * H, H, 0, device=device)
+        native.launch("gdn_l2norm", k_raw, k, rstd_k, S * H, H, 0, device=device)
     g2 = torch.empty((S, H, HEAD_DIM), dtype=F32, device=device)
     qg, kg, kr = (torch.empty_like(q) for _ in range(3))
     gl2 = torch.zeros((NC, H, HEAD_DIM), dtype=F32, device=device)

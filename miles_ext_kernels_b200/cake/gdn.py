@@ -10,6 +10,10 @@ miles_ext_kernels/cake/_impl/gdn/ops.py:2420-2501).  A call runs, by its ``cp_co
 - a :class:`KcpContext` (:func:`build_kcp_context`): this rank's contiguous slice of every sequence, with the chunk
   state passed rank to rank (:func:`kcp_chunk_gated_delta_rule` calls it directly).
 
+:func:`packed_qkv_views` splits one packed row ``[.., (2 H + HV) * 128]`` into q, k, v views that the op reads in place
+and whose gradients come back as one packed row (no copies on either side; not among the reference's exports of
+this module: its context-parallel packages offer it).
+
 Under any ``cp_context`` the contract is FLA's: no initial state, no final state, and the context's boundaries.
 
 Both variants (``det``, ``fast``) run the same kernels here: every reduction has a fixed order and no kernel uses a
@@ -29,7 +33,8 @@ OP = OpSpec(
     variants=("det", "fast"),
     selected_by=(("linear_attention_backend", "cake"),),
     packages=("libmek_b200",),
-    exports=("KcpContext", "build_kcp_context", "chunk_gated_delta_rule", "kcp_chunk_gated_delta_rule"),
+    exports=("KcpContext", "build_kcp_context", "chunk_gated_delta_rule", "kcp_chunk_gated_delta_rule",
+             "packed_qkv_views"),
     flags=(
         Flag(
             "--cake-gdn-recompute-state",

@@ -267,8 +267,8 @@ int launch_bwd_dh(const MekGdnDims* d, const void* q, const void* k, const void*
   const size_t smem = BwdDhSmem::kBytes + 1024;
   if (int rc = want_smem(gdn_bwd_dh_kernel, smem, what)) return rc;
   BwdDhMaps maps;
-  if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_qk_heads, what)) return rc;
-  if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, what)) return rc;
+  if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_qk_heads, what, d->qk_pitch)) return rc;
+  if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, what, d->qk_pitch)) return rc;
   if (int rc = make_rows_map(&maps.w, w, d->total_tokens, d->num_v_heads, what)) return rc;
   if (int rc = make_rows_map(&maps.d_o, d_o, d->total_tokens, d->num_v_heads, what)) return rc;
   if (int rc = make_tiles_map(&maps.aqk, aqk, int64_t(d->num_chunks) * d->num_v_heads, 64, 64, what)) return rc;

@@ -72,7 +72,8 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     const float* __restrict__ rstd_q, const float* __restrict__ rstd_k, __nv_bfloat16* __restrict__ dq,
     __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, float* __restrict__ dbeta, float* __restrict__ dg,
     const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len, int num_chunks, int num_qk_heads,
-    int num_v_heads, float scale, int32_t* __restrict__ status) {
+    int num_v_heads, float scale, int64_t raw_pitch, int64_t dqk_pitch, int64_t dv_pitch,
+    int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
   __shared__ uint64_t bar;         // tensor-core commits
   __shared__ uint64_t bar_item;    // the item's tiles: three instalments, one arrival each
@@ -369,7 +370,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
         tmem_ld32(tmem_addr(tmem, warp, kColT3 + ch * 32), y);
         tmem_ld_wait();
         float dot_v = 0.f;
-        __nv_bfloat16* dv_row = dv + int64_t(start + row) * v_stride + hv * kDim + lcol;
+        __nv_bfloat16* dv_row = dv + int64_t(start + row) * dv_pitch + hv * kDim + lcol;
         uint4 vraw[4];
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) vraw[jj] = tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj);
@@ -521,7 +522,10 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       if (last_of_pair) {
         // ---- the group's dq, dk: fp32 sums, the norm's pull-back, one rounding ----------------------------------
         mma_wait();
-        const int64_t tok = int64_t(start + row) * qk_stride + hq * kDim + lcol;
+        // this thread's 32 columns of its row: in the raw operands and in the outputs (token pitches may differ:
+        // either may be a column slice of a packed row)
+        const int64_t raw_at = int64_t(start + row) * raw_pitch + hq * kDim + lcol;
+        const int64_t out_at = int64_t(start + row) * dqk_pitch + hq * kDim + lcol;
         // acc: this thread's 32 columns of the fp32 group sum.  With the op's L2 norm: dx = r (D - y (D . y)),
         // y = x r from the raw row and the saved r; the dot product spans the four column quarters.
         auto finish = [&](float* acc, const __nv_bfloat16* raw_rows, const float* rstd, __nv_bfloat16* out) {
@@ -532,7 +536,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
               uint4 x = make_uint4(0u, 0u, 0u, 0u);
-              if (live) x = ldg16(raw_rows + tok + jj * 8);
+              if (live) x = ldg16(raw_rows + raw_at + jj * 8);
               unpack8(x, y + jj * 8);
 #pragma unroll
               for (int e = 0; e < 8; ++e) {
@@ -549,7 +553,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
           }
           if (live) {
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) reinterpret_cast<uint4*>(out + tok)[jj] = pack8(acc + jj * 8);
+            for (int jj = 0; jj < 4; ++jj) reinterpret_cast<uint4*>(out + out_at)[jj] = pack8(acc + jj * 8);
           }
         };
         {
@@ -616,19 +620,26 @@ extern "C" int mek_gdn_bwd_tail(const MekGdnDims* d, const void* q, const void* 
     const void* base;
     uint64_t rows, cols;
     uint32_t box_rows;
+    uint64_t pitch;
   } const wanted[] = {
-      {&maps.q, q, tokens, qk_cols, 64},      {&maps.k, k, tokens, qk_cols, 64},
-      {&maps.v, v, tokens, v_cols, 64},       {&maps.d_o, d_o, tokens, v_cols, 64},
-      {&maps.v_new, v_new, tokens, v_cols, 64}, {&maps.dv_new, dv_new, tokens, v_cols, 64},
-      {&maps.w, w, tokens, v_cols, 64},       {&maps.u, u, tokens, v_cols, 64},
-      {&maps.h, h_tape, tiles * 128, 128, 128}, {&maps.dh, dh_tape, tiles * 128, 128, 128},
-      {&maps.a, a, tiles * 64, 64, 64},       {&maps.aqk, aqk, tiles * 64, 64, 64},
+      {&maps.q, q, tokens, qk_cols, 64, uint64_t(d->qk_pitch)}, {&maps.k, k, tokens, qk_cols, 64, uint64_t(d->qk_pitch)},
+      {&maps.v, v, tokens, v_cols, 64, uint64_t(d->v_pitch)},   {&maps.d_o, d_o, tokens, v_cols, 64, 0},
+      {&maps.v_new, v_new, tokens, v_cols, 64, 0},              {&maps.dv_new, dv_new, tokens, v_cols, 64, 0},
+      {&maps.w, w, tokens, v_cols, 64, 0},                      {&maps.u, u, tokens, v_cols, 64, 0},
+      {&maps.h, h_tape, tiles * 128, 128, 128, 0},              {&maps.dh, dh_tape, tiles * 128, 128, 128, 0},
+      {&maps.a, a, tiles * 64, 64, 64, 0},                      {&maps.aqk, aqk, tiles * 64, 64, 64, 0},
   };
   for (const auto& m : wanted)
-    if (int rc = make_tile_map(m.map, m.base, m.rows, m.cols, m.box_rows, "bwd_tail")) return rc;
+    if (int rc = make_tile_map(m.map, m.base, m.rows, m.cols, m.box_rows, "bwd_tail", m.pitch)) return rc;
+  const int64_t raw_pitch = d->raw_pitch != 0 ? d->raw_pitch : int64_t(qk_cols);
+  const int64_t dqk_pitch = d->dqk_pitch != 0 ? d->dqk_pitch : int64_t(qk_cols);
+  const int64_t dv_pitch = d->dv_pitch != 0 ? d->dv_pitch : int64_t(v_cols);
+  if (raw_pitch < int64_t(qk_cols) || dqk_pitch < int64_t(qk_cols) || dv_pitch < int64_t(v_cols) ||
+      (raw_pitch | dqk_pitch | dv_pitch) % 8 != 0)
+    return fail(MEK_ERR_INVALID, "bwd_tail: a token pitch is smaller than its row or not a multiple of 8 elements");
   const int pairs = d->num_chunks * d->num_qk_heads;
   gdn_bwd_tail_kernel<<<pairs < sms ? pairs : sms, 256, smem, static_cast<cudaStream_t>(stream)>>>(
       maps, beta, g_cs, In(q_raw), In(k_raw), rstd_q, rstd_k, Out(dq), Out(dk), Out(dv), dbeta, dg, d->chunk_start,
-      d->chunk_len, d->num_chunks, d->num_qk_heads, d->num_v_heads, d->scale, status);
+      d->chunk_len, d->num_chunks, d->num_qk_heads, d->num_v_heads, d->scale, raw_pitch, dqk_pitch, dv_pitch, status);
   return launched("bwd_tail");
 }

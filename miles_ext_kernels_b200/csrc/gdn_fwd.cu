@@ -23,13 +23,15 @@ namespace mek {
 // ---------------------------------------------------------------------------------------------------------------
 // prep
 // ---------------------------------------------------------------------------------------------------------------
-// One warp per row of 128 bf16: y = bf16(x r), r = 1 / sqrt(sum x^2 + 1e-6), r saved.
+// One warp per row of 128 bf16: y = bf16(x r), r = 1 / sqrt(sum x^2 + 1e-6), r saved.  Row (token, head) of x sits
+// at token * pitch + head * 128 (x may be a column slice of a packed row); y and rstd are dense.
 __global__ void __launch_bounds__(256) l2norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
-                                                     float* __restrict__ rstd, int64_t rows) {
+                                                     float* __restrict__ rstd, int64_t rows, int heads, int64_t pitch) {
   const int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
-  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + row * kDim) + lane);
+  const int64_t at = (row / heads) * pitch + (row % heads) * kDim;
+  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + at) + lane);
   const float2 a = unpack_bf16(raw.x), b = unpack_bf16(raw.y);
   float ss = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
 #pragma unroll
@@ -751,11 +753,15 @@ int check_dims(const MekGdnDims* d, const char* what) {
 
 extern "C" {
 
-int mek_gdn_l2norm(const void* x, void* y, float* rstd, int64_t rows, void* stream) {
+int mek_gdn_l2norm(const void* x, void* y, float* rstd, int64_t rows, int heads, int64_t x_pitch, void* stream) {
   using namespace mek;
-  if (rows <= 0 || !x || !y || !rstd) return fail(MEK_ERR_INVALID, "l2norm: rows=%lld or a null pointer", (long long)rows);
+  if (rows <= 0 || heads <= 0 || !x || !y || !rstd)
+    return fail(MEK_ERR_INVALID, "l2norm: rows=%lld, heads=%d or a null pointer", (long long)rows, heads);
+  const int64_t pitch = x_pitch != 0 ? x_pitch : int64_t(heads) * kDim;
+  if (pitch < int64_t(heads) * kDim || pitch % 4 != 0)
+    return fail(MEK_ERR_INVALID, "l2norm: x_pitch %lld does not hold %d heads of 128", (long long)x_pitch, heads);
   l2norm_kernel<<<unsigned((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), rstd, rows);
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), rstd, rows, heads, pitch);
   return launched("l2norm");
 }
 
@@ -776,9 +782,9 @@ int mek_gdn_wy_fwd(const MekGdnDims* d, const void* q, const void* k, const void
   const size_t smem = WySmem::kBytes + 1024;
   if (int rc = want_smem(gdn_wy_kernel, smem, "wy_fwd")) return rc;
   WyMaps maps;
-  if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_qk_heads, "wy_fwd")) return rc;
-  if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, "wy_fwd")) return rc;
-  if (int rc = make_rows_map(&maps.v, v, d->total_tokens, d->num_v_heads, "wy_fwd")) return rc;
+  if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_qk_heads, "wy_fwd", d->qk_pitch)) return rc;
+  if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, "wy_fwd", d->qk_pitch)) return rc;
+  if (int rc = make_rows_map(&maps.v, v, d->total_tokens, d->num_v_heads, "wy_fwd", d->v_pitch)) return rc;
   gdn_wy_kernel<<<dim3(d->num_chunks, d->num_v_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
       maps, beta, g_cs, static_cast<__nv_bfloat16*>(a_out), static_cast<__nv_bfloat16*>(aqk_out),
       static_cast<__nv_bfloat16*>(w_out), static_cast<__nv_bfloat16*>(u_out), d->chunk_start, d->chunk_len,
@@ -800,11 +806,11 @@ int launch_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* 
   const size_t smem = FwdHSmem::kBytes + 1024;
   if (int rc = want_smem(gdn_fwd_h_kernel, smem, what)) return rc;
   FwdHMaps maps;
-  if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, what)) return rc;
+  if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, what, d->qk_pitch)) return rc;
   if (int rc = make_rows_map(&maps.w, w, d->total_tokens, d->num_v_heads, what)) return rc;
   if (int rc = make_rows_map(&maps.u, u, d->total_tokens, d->num_v_heads, what)) return rc;
   if (fused.o != nullptr) {
-    if (int rc = make_rows_map(&maps.q, fused.q, d->total_tokens, d->num_qk_heads, what)) return rc;
+    if (int rc = make_rows_map(&maps.q, fused.q, d->total_tokens, d->num_qk_heads, what, d->qk_pitch)) return rc;
     if (int rc = make_tiles_map(&maps.aqk, fused.aqk, int64_t(d->num_chunks) * d->num_v_heads, 64, 64, what))
       return rc;
   } else {
@@ -870,7 +876,7 @@ int mek_gdn_fwd_o(const MekGdnDims* d, const void* q, const void* aqk, const voi
   if (int rc = want_smem(gdn_fwd_o_kernel, smem, "fwd_o")) return rc;
   const int64_t tiles = int64_t(d->num_chunks) * d->num_v_heads;
   FwdOMaps maps;
-  if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_qk_heads, "fwd_o")) return rc;
+  if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_qk_heads, "fwd_o", d->qk_pitch)) return rc;
   if (int rc = make_rows_map(&maps.v_new, v_new, d->total_tokens, d->num_v_heads, "fwd_o")) return rc;
   if (int rc = make_tiles_map(&maps.h, h_tape, tiles, 128, 128, "fwd_o")) return rc;
   if (int rc = make_tiles_map(&maps.aqk, aqk, tiles, 64, 64, "fwd_o")) return rc;

@@ -42,9 +42,9 @@ inline EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// A bf16 matrix [rows, cols] (row stride = cols elements) read in boxes of 64 columns x box_rows rows.
+// A bf16 matrix [rows, cols] (row stride = `pitch` elements, 0 = cols) read in boxes of 64 columns x box_rows rows.
 inline int make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                         const char* what) {
+                         const char* what, uint64_t pitch = 0) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return fail(MEK_ERR_CUDA, "%s: the driver does not export cuTensorMapEncodeTiled", what);
   if (base == nullptr || (reinterpret_cast<uintptr_t>(base) & 15) != 0 || cols % 64 != 0 || rows == 0 ||
@@ -52,8 +52,11 @@ inline int make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint
     return fail(MEK_ERR_INVALID, "%s: a tensor map needs a 16-byte aligned base, columns in multiples of 64 and 1..256 "
                 "box rows (rows=%llu cols=%llu box_rows=%u)", what, (unsigned long long)rows,
                 (unsigned long long)cols, box_rows);
+  if (pitch != 0 && (pitch < cols || pitch % 8 != 0))
+    return fail(MEK_ERR_INVALID, "%s: a row pitch must be a multiple of 8 elements and at least the row's %llu columns, "
+                "got %llu", what, (unsigned long long)cols, (unsigned long long)pitch);
   const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint64_t strides[1] = {(pitch != 0 ? pitch : cols) * 2};
   const cuuint32_t box[2] = {64, box_rows};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
@@ -64,8 +67,9 @@ inline int make_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint
 }
 
 // rows [tokens, heads * 128], read in boxes of 64 columns x 64 tokens
-inline int make_rows_map(CUtensorMap* map, const void* base, int64_t tokens, int heads, const char* what) {
-  return make_tile_map(map, base, uint64_t(tokens), uint64_t(heads) * 128, 64, what);
+inline int make_rows_map(CUtensorMap* map, const void* base, int64_t tokens, int heads, const char* what,
+                         int64_t pitch = 0) {
+  return make_tile_map(map, base, uint64_t(tokens), uint64_t(heads) * 128, 64, what, uint64_t(pitch));
 }
 // tiles [num_tiles * rows, cols], read in boxes of 64 columns x `rows` rows
 inline int make_tiles_map(CUtensorMap* map, const void* base, int64_t num_tiles, int rows, int cols, const char* what) {

@@ -266,3 +266,39 @@ def test_forward_and_backward_replay_from_a_cuda_graph():
         package.configure()
     got = dict(zip(NAMES, (t[0].cpu() for t in outs)))
     assert_same_bits(got, {n: want[n] for n in NAMES}, "graph replay")
+
+
+@pytest.mark.parametrize("l2", [True, False], ids=["l2norm", "plain"])
+@pytest.mark.parametrize("split", ["packed_qkv_views", "torch_split"])
+def test_views_of_one_packed_row_are_read_in_place_and_give_the_contiguous_bits(l2, split):
+    """q, k, v as the column slices [q heads | k heads | v heads] of one packed row: no copy on the way in (the
+    kernels take the token stride), one packed gradient row on the way out, the bits of contiguous operands."""
+    from miles_ext_kernels_b200.cake import gdn
+    from miles_ext_kernels_b200.cake._impl.gdn import ops
+
+    dev = torch.device("cuda")
+    B, T, (H, HV) = 2, 448, (2, 4)
+    seq_lens = (T,) * B
+    x = draw(seq_lens, (H, HV), seed=51, normalised=not l2)
+    want = run(x, seq_lens, l2=l2, batch=B)
+    row = torch.cat([x["q"].reshape(B * T, -1), x["k"].reshape(B * T, -1), x["v"].reshape(B * T, -1)], dim=-1)
+    row = row.reshape(B, T, -1).to(dev).requires_grad_(True)
+    if split == "packed_qkv_views":
+        q, k, v = gdn.packed_qkv_views(row, H, HV)
+    else:
+        q, k, v = row.split([H * 128, H * 128, HV * 128], dim=-1)
+        q, k, v = q.unflatten(-1, (H, 128)), k.unflatten(-1, (H, 128)), v.unflatten(-1, (HV, 128))
+    assert not q.is_contiguous() and ops._rows(q).data_ptr() == q.data_ptr()  # read where it lies
+    assert ops._rows(v).data_ptr() == v.data_ptr() and ops._tile_one_row(ops._rows(q), ops._rows(k), ops._rows(v))
+    g = x["g"].to(dev).reshape(B, T, HV).requires_grad_(True)
+    beta = x["beta"].to(dev).bfloat16().reshape(B, T, HV).requires_grad_(True)
+    o, _ = gdn.chunk_gated_delta_rule(q, k, v, g=g, beta=beta, use_qk_l2norm_in_kernel=l2)
+    o.backward(x["do"].to(dev).reshape(o.shape))
+    torch.cuda.synchronize()
+    flat = lambda t: t.detach().reshape(B * T, *t.shape[2:]).cpu()  # noqa: E731
+    grad = flat(row.grad)
+    got = {"o": flat(o), "dq": grad[:, : H * 128].reshape(-1, H, 128), "dk": grad[:, H * 128 : 2 * H * 128].reshape(-1, H, 128),
+           "dv": grad[:, 2 * H * 128 :].reshape(-1, HV, 128), "dg": flat(g.grad), "dbeta": flat(beta.grad)}
+    assert_same_bits(got, {n: want[n] for n in NAMES}, f"packed row, {split}")
+    with pytest.raises(ValueError, match="columns"):
+        gdn.packed_qkv_views(row[..., :-128], H, HV)

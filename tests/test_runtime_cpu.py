@@ -226,7 +226,7 @@ def test_the_built_library_exports_every_declared_symbol():
 def test_native_argument_checks_run_without_a_gpu():
     """Extent checks happen before any CUDA call: a bad call reports MEK_ERR_* and its text on a CPU-only box."""
     library = loader.load_library()
-    code = library.mek_gdn_l2norm(None, None, None, ctypes.c_int64(0), None)
+    code = library.mek_gdn_l2norm(None, None, None, ctypes.c_int64(0), 1, ctypes.c_int64(0), None)
     assert code == 1 and "l2norm" in library.last_error()
 
 
