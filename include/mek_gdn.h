@@ -239,6 +239,24 @@ int mek_kda_bwd_tail(const MekGdnDims* dims, const void* q, const void* k, const
 /* out bf16 = x fp32 per row of 128, through the L2 norm's pull-back r (x - y (x . y)), y = raw r, when rstd is given. */
 int mek_qk_grad_finish(const float* x, const void* raw_rows, const float* rstd, void* out, int64_t rows, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------------
+ * SiLU-gated RMSNorm over rows of 128 (the GDN layer's output norm), forward and backward:
+ *     rstd = 1 / sqrt(mean(x^2) + eps),   y = bf16(((x rstd) weight) silu(z))
+ * x, z bf16: row (token, head) at token * token_stride + head * head_stride elements (strides multiples of 8, bases
+ * 16-byte aligned; z is usually a column slice of the layer's input projection); weight bf16 [128]; y, dy, dx, dz dense
+ * bf16 [rows, 128]; rows = tokens * heads.  The weight gradient (bf16 [128], or NULL with dw_partial NULL) is summed
+ * in a fixed order: per block in FP32 into dw_partial fp32 [mek_gated_rmsnorm_partial_rows(rows), 128], then over the
+ * blocks in FP64.  Replaces the reference's `cake_rmsnorm_silu_gate_det_train` package (reference:
+ * miles_ext_kernels/cake/_impl/gated_rmsnorm/ops.py:126-148). */
+int mek_gated_rmsnorm_partial_rows(int64_t rows);
+int mek_gated_rmsnorm_fwd(const void* x, const void* z, const void* weight, void* y, int64_t rows, int heads,
+                          int64_t x_token_stride, int64_t x_head_stride, int64_t z_token_stride, int64_t z_head_stride,
+                          float eps, void* stream);
+int mek_gated_rmsnorm_bwd(const void* dy, const void* x, const void* z, const void* weight, void* dx, void* dz,
+                          float* dw_partial, void* dw, int64_t rows, int heads, int64_t x_token_stride,
+                          int64_t x_head_stride, int64_t z_token_stride, int64_t z_head_stride, float eps,
+                          void* stream);
+
 #ifdef __cplusplus
 }
 #endif
