@@ -257,6 +257,23 @@ int mek_gated_rmsnorm_bwd(const void* dy, const void* x, const void* z, const vo
                           int64_t x_head_stride, int64_t z_token_stride, int64_t z_head_stride, float eps,
                           void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------------
+ * Packed causal depthwise conv1d (kernel size 4) + SiLU, the short convolution in front of the GDN / KDA op:
+ *     pre[t, c] = sum_{k<4} w[c, k] x[t - 3 + k, c] (inside t's document),   y = bf16(pre sigmoid(pre))
+ * x, y, dy, dx bf16 [tokens, channels] dense (channels a multiple of 8); weight [channels, 4] fp32, or bf16 when
+ * weight_is_bf16; reach uint8 [tokens] from mek_conv1d_reach (cu_seqlens int32 [num_docs + 1] on the device).
+ * Backward: SiLU' at the BF16-rounded preactivation, or at the unrounded one with FP64 weight-gradient sums when
+ * fp32_policy; dw in the weight's dtype (or NULL with dw_partial NULL); dw_partial holds
+ * mek_conv1d_runs(tokens) * channels * 4 floats (doubles under fp32_policy), summed in a fixed order.
+ * Replaces the reference's `cake_causal_conv1d_det_train` package (reference:
+ * miles_ext_kernels/cake/_impl/conv1d/ops.py:226-257). */
+int mek_conv1d_runs(int tokens);
+int mek_conv1d_reach(const int32_t* cu_seqlens, int num_docs, int tokens, uint8_t* reach, void* stream);
+int mek_conv1d_fwd(const void* x, const void* weight, int weight_is_bf16, const uint8_t* reach, void* y, int tokens,
+                   int channels, void* stream);
+int mek_conv1d_bwd(const void* x, const void* weight, int weight_is_bf16, const void* dy, const uint8_t* reach,
+                   void* dx, void* dw_partial, void* dw, int fp32_policy, int tokens, int channels, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
