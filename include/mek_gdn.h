@@ -265,14 +265,21 @@ int mek_gated_rmsnorm_bwd(const void* dy, const void* x, const void* z, const vo
  * Backward: SiLU' at the BF16-rounded preactivation, or at the unrounded one with FP64 weight-gradient sums when
  * fp32_policy; dw in the weight's dtype (or NULL with dw_partial NULL); dw_partial holds
  * mek_conv1d_runs(tokens) * channels * 4 floats (doubles under fp32_policy), summed in a fixed order.
+ * Context parallelism (reference: ops.py:267-340): a rank whose first document began on the rank before passes that
+ * rank's last 3 rows as x_prev [3, channels] and a cu_seqlens whose first entry is minus the number of those rows
+ * that belong to the document; a rank whose last document goes on passes the next rank's first 3 rows of x and dy
+ * as x_next, dy_next, a cu_seqlens whose last entry is tokens plus the number of rows that belong to the document,
+ * and a reach table of tokens + 3 entries.  NULL: nothing on that side.  y, dx and the weight-gradient sums cover
+ * the rank's own tokens only.
  * Replaces the reference's `cake_causal_conv1d_det_train` package (reference:
  * miles_ext_kernels/cake/_impl/conv1d/ops.py:226-257). */
 int mek_conv1d_runs(int tokens);
 int mek_conv1d_reach(const int32_t* cu_seqlens, int num_docs, int tokens, uint8_t* reach, void* stream);
-int mek_conv1d_fwd(const void* x, const void* weight, int weight_is_bf16, const uint8_t* reach, void* y, int tokens,
-                   int channels, void* stream);
-int mek_conv1d_bwd(const void* x, const void* weight, int weight_is_bf16, const void* dy, const uint8_t* reach,
-                   void* dx, void* dw_partial, void* dw, int fp32_policy, int tokens, int channels, void* stream);
+int mek_conv1d_fwd(const void* x, const void* x_prev, const void* weight, int weight_is_bf16, const uint8_t* reach,
+                   void* y, int tokens, int channels, void* stream);
+int mek_conv1d_bwd(const void* x, const void* x_prev, const void* x_next, const void* weight, int weight_is_bf16,
+                   const void* dy, const void* dy_next, const uint8_t* reach, void* dx, void* dw_partial, void* dw,
+                   int fp32_policy, int tokens, int channels, void* stream);
 
 #ifdef __cplusplus
 }

@@ -56,46 +56,92 @@ def _policy(silu_grad_preactivation: str | None) -> str:
     return policy
 
 
+class _Halo:
+    """What a call reads beyond its own tokens: ``cu`` (int32, on the device) with the first entry moved back by the
+    history rows that belong to the first document and the last one moved on by the continuation rows that belong to
+    the last; per tensor the rows of the rank before / after (``[3, C]`` or ``None``); ``swap_back`` sends the first
+    rows of the output gradients to the rank before and returns the rank after's (``None``: a call on its own)."""
+
+    __slots__ = ("cu", "prev", "next", "swap_back")
+
+    def __init__(self, cu, prev, next, swap_back=None):
+        self.cu, self.prev, self.next, self.swap_back = cu, prev, next, swap_back
+
+
+def _split_rows(rows: torch.Tensor | None, widths: list[int]) -> list[torch.Tensor | None]:
+    if rows is None:
+        return [None] * len(widths)
+    return [part.contiguous() for part in rows.split(widths, dim=1)]
+
+
 class _CausalConv1d(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, x, weight, cu_seqlens, policy):
-        shape = x.shape
-        x2 = x.reshape(-1, shape[-1])
-        tokens, channels = x2.shape
-        device = x.device
-        y = torch.empty_like(x2)
-        reach = None
-        if tokens:
-            reach = torch.empty(tokens, dtype=torch.uint8, device=device)
-            with torch.cuda.device(device):
-                native.launch("conv1d_reach", cu_seqlens, cu_seqlens.numel() - 1, tokens, reach, device=device)
-                native.launch("conv1d_fwd", x2, weight, int(weight.dtype == torch.bfloat16), reach, y, tokens, channels,
-                              device=device)
-        ctx.save_for_backward(x2, weight, reach)
-        ctx.policy, ctx.shape = policy, shape
-        return y.view(shape)
+    """``n`` convolutions over one token layout: ``apply(halo, policy, n, *xs, *weights) -> ys``."""
 
     @staticmethod
-    def backward(ctx, dy):
-        x2, weight, reach = ctx.saved_tensors
-        tokens, channels = x2.shape
-        device = x2.device
-        dx = torch.empty_like(x2)
-        want_dw = ctx.needs_input_grad[1]
-        dw = torch.zeros_like(weight) if want_dw else None
+    def forward(ctx, halo, policy, n, *tensors):
+        xs, weights = tensors[:n], tensors[n:]
+        tokens = xs[0].shape[0]
+        device = xs[0].device
+        ys = tuple(torch.empty_like(x) for x in xs)
+        reach = None
         if tokens:
-            dy2 = dy.reshape(tokens, channels)
-            dy2 = dy2.contiguous() if dy2.dtype == torch.bfloat16 else dy2.to(torch.bfloat16).contiguous()
-            fp32_policy = ctx.policy == "fp32"
+            entries = tokens + (KERNEL_SIZE - 1 if any(r is not None for r in halo.next) else 0)
+            reach = torch.empty(entries, dtype=torch.uint8, device=device)
             with torch.cuda.device(device):
-                partial = None
-                if want_dw:
-                    runs = native.library().mek_conv1d_runs(tokens)
-                    partial = workspace.take(OP, "dw_partial", (runs, channels, KERNEL_SIZE),
-                                             torch.float64 if fp32_policy else torch.float32, device)
-                native.launch("conv1d_bwd", x2, weight, int(weight.dtype == torch.bfloat16), dy2, reach, dx, partial,
-                              dw, int(fp32_policy), tokens, channels, device=device)
-        return dx.view(ctx.shape), dw, None, None
+                native.launch("conv1d_reach", halo.cu, halo.cu.numel() - 1, entries, reach, device=device)
+                for x, w, y, prev in zip(xs, weights, ys, halo.prev):
+                    native.launch("conv1d_fwd", x, prev, w, int(w.dtype == torch.bfloat16), reach, y, tokens,
+                                  x.shape[1], device=device)
+        ctx.save_for_backward(reach, *xs, *weights)
+        ctx.halo, ctx.policy, ctx.n = halo, policy, n
+        return ys
+
+    @staticmethod
+    def backward(ctx, *dys):
+        reach, *tensors = ctx.saved_tensors
+        n, halo = ctx.n, ctx.halo
+        xs, weights = tensors[:n], tensors[n:]
+        tokens = xs[0].shape[0]
+        device = xs[0].device
+        dys = [torch.zeros_like(x) if dy is None else dy.reshape(x.shape).to(torch.bfloat16).contiguous()
+               for x, dy in zip(xs, dys)]
+        dy_next = [None] * n
+        if halo.swap_back is not None and tokens:
+            reachable = KERNEL_SIZE - 1
+            dy_next = _split_rows(halo.swap_back(torch.cat([dy[:reachable] for dy in dys], dim=1)),
+                                  [x.shape[1] for x in xs])
+        fp32_policy = ctx.policy == "fp32"
+        dxs, dws = [], []
+        for i, (x, w, dy) in enumerate(zip(xs, weights, dys)):
+            channels = x.shape[1]
+            dx = torch.empty_like(x)
+            want_dw = ctx.needs_input_grad[3 + n + i]
+            dw = torch.zeros_like(w) if want_dw else None
+            if tokens:
+                with torch.cuda.device(device):
+                    partial = None
+                    if want_dw:
+                        runs = native.library().mek_conv1d_runs(tokens)
+                        partial = workspace.take(OP, "dw_partial", (runs, channels, KERNEL_SIZE),
+                                                 torch.float64 if fp32_policy else torch.float32, device)
+                    x_next = halo.next[i] if dy_next[i] is not None else None
+                    native.launch("conv1d_bwd", x, halo.prev[i], x_next, w, int(w.dtype == torch.bfloat16), dy,
+                                  dy_next[i] if x_next is not None else None, reach, dx, partial, dw,
+                                  int(fp32_policy), tokens, channels, device=device)
+            dxs.append(dx)
+            dws.append(dw)
+        return (None, None, None, *dxs, *dws)
+
+
+def _checked(x: torch.Tensor, weight: torch.Tensor) -> None:
+    if x.dim() not in (2, 3) or not x.is_cuda or x.dtype != torch.bfloat16:
+        raise ValueError(f"{_BACKEND} takes a BF16 CUDA tensor [1, S, C] or [S, C], got {x.dtype} {tuple(x.shape)}")
+    channels = x.shape[-1]
+    if channels % CHANNEL_MULTIPLE:
+        raise ValueError(f"{_BACKEND} needs a channel count that is a multiple of {CHANNEL_MULTIPLE}, got {channels}")
+    if tuple(weight.shape) != (channels, KERNEL_SIZE) or weight.dtype not in TAP_DTYPES:
+        raise ValueError(f"{_BACKEND} takes FP32 or BF16 taps [{channels}, {KERNEL_SIZE}], got {weight.dtype} "
+                         f"{tuple(weight.shape)}")
 
 
 def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, cu_seqlens: torch.Tensor | None = None, *,
@@ -112,14 +158,7 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, cu_seqlens: torch.Tenso
             f"{_BACKEND} takes one packed batch [1, S, C] whose documents cu_seqlens delimits, got shape "
             f"{tuple(x.shape)}"
         )
-    if x.dim() not in (2, 3) or not x.is_cuda or x.dtype != torch.bfloat16:
-        raise ValueError(f"{_BACKEND} takes a BF16 CUDA tensor [1, S, C] or [S, C], got {x.dtype} {tuple(x.shape)}")
-    channels = x.shape[-1]
-    if channels % CHANNEL_MULTIPLE:
-        raise ValueError(f"{_BACKEND} needs a channel count that is a multiple of {CHANNEL_MULTIPLE}, got {channels}")
-    if tuple(weight.shape) != (channels, KERNEL_SIZE) or weight.dtype not in TAP_DTYPES:
-        raise ValueError(f"{_BACKEND} takes FP32 or BF16 taps [{channels}, {KERNEL_SIZE}], got {weight.dtype} "
-                         f"{tuple(weight.shape)}")
+    _checked(x, weight)
     config.variant(OP)
     policy = _policy(silu_grad_preactivation)
     x = x.contiguous()
@@ -128,17 +167,107 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, cu_seqlens: torch.Tenso
         cu_seqlens = torch.arange(2, dtype=torch.int32, device=x.device).mul_(tokens)  # no host copy, no sync
     else:
         cu_seqlens = cu_seqlens.to(torch.int32).contiguous()
-    return _CausalConv1d.apply(x, weight.contiguous(), cu_seqlens, policy)
+    halo = _Halo(cu_seqlens, [None], [None])
+    (y,) = _CausalConv1d.apply(halo, policy, 1, x.view(tokens, x.shape[-1]), weight.contiguous())
+    return y.view(x.shape)
 
 
-def causal_conv1d_kcp(x_local, weight, kcp_context, *, recompute_handle=None, cooperative=None):
-    """The context-parallel route (the history tokens of a continuing fragment come from the rank that holds them) is
-    not built."""
-    raise NotImplementedError("causal_conv1d_kcp: the context-parallel short convolution is not built")
+def _kcp_taps(weight: torch.Tensor) -> torch.Tensor:
+    """FP32 taps for the context-parallel route: BF16 taps widened (exact; autograd rounds their gradient back)
+    (reference: ops.py:260-264)."""
+    return (weight.float() if weight.dtype == torch.bfloat16 else weight).contiguous()
 
 
-def causal_conv1d_kcp_multi(xs, weights, kcp_context, *, recompute_handle=None, cooperative=None):
-    raise NotImplementedError("causal_conv1d_kcp_multi: the context-parallel short convolution is not built")
+def _halo_cu(kcp_context: Any, device: torch.device) -> torch.Tensor:
+    """The rank's local boundaries with the first moved back by the history rows of the first document and the last
+    moved on by the continuation rows of the last; built once per context."""
+    cached = getattr(kcp_context, "_conv1d_cu", None)
+    if cached is None or cached.device != device:
+        before, after = kcp_context.halo
+        cu = list(kcp_context.cu_seqlens_cpu)
+        cu[0] -= before
+        cu[-1] += after
+        cached = torch.tensor(cu, dtype=torch.int32, device=device)
+        try:
+            kcp_context._conv1d_cu = cached
+        except AttributeError:
+            pass
+    return cached
+
+
+def causal_conv1d_kcp_multi(xs, weights, kcp_context: Any, *, recompute_handle: Any = None,
+                            cooperative: bool | None = None) -> tuple[torch.Tensor, ...]:
+    """The context-parallel convolutions of several tensors of one layer (for example its q, k and v) with one
+    neighbour exchange per direction instead of one per tensor.
+
+    ``xs``: ``n >= 1`` BF16 ``[T_r, C_i]`` (or ``[1, T_r, C_i]``) tensors, the rank's fragments back to back;
+    ``weights``: their ``[C_i, 4]`` taps, the same on every rank; ``kcp_context``: the rank's context of the layer's
+    GDN / KDA context-parallel route (read: ``num_tokens``, ``cu_seqlens_cpu``, ``halo``, ``world_size`` and
+    ``halo_exchange()``).  Every rank of the context's group makes this call for the same layers in the same order.
+
+    The forward sends a rank's first three rows to the rank before and its last three to the rank after, where a
+    document crosses the cut; the backward sends the first three rows of the output gradients to the rank before.  y
+    and dx are the bits of the undivided call; the weight gradient is the rank's partial sum over its own tokens (in
+    ``weight``'s dtype; BF16 taps are widened first and autograd rounds their gradient back).  ``recompute_handle``:
+    ``None`` or an object with an ``entries`` dict; the first forward stores the rows it received under ``"conv"``
+    and a recompute of the call reuses them without an exchange.  ``cooperative`` (the reference's launch form of its
+    backward program) is accepted and has no effect: the backward here is one ordinary launch per tensor.
+    (reference: ops.py:267-340)."""
+    if isinstance(xs, torch.Tensor) or isinstance(weights, torch.Tensor):
+        raise TypeError("xs and weights must be sequences of tensors (one per convolution), not a tensor")
+    xs, weights = list(xs), list(weights)
+    if not xs or len(xs) != len(weights):
+        raise ValueError(f"causal_conv1d_kcp_multi takes as many taps as tensors, got {len(xs)} and {len(weights)}")
+    if cooperative not in (None, True, False):
+        raise ValueError(f"cooperative must be None, True or False, got {cooperative!r}")
+    for x, w in zip(xs, weights):
+        _checked(x, w)
+        if x.dim() == 3 and x.shape[0] != 1:
+            raise ValueError(f"{_BACKEND} takes the rank's fragments as [T_r, C] or [1, T_r, C], got {tuple(x.shape)}")
+    config.variant(OP)
+    policy = _policy(None)
+    tokens = int(kcp_context.num_tokens)
+    shapes = [x.shape for x in xs]
+    xs = [x.contiguous().view(-1, x.shape[-1]) for x in xs]
+    if any(x.shape[0] != tokens for x in xs):
+        raise ValueError(f"causal_conv1d_kcp: the context holds {tokens} tokens on this rank, the tensors "
+                         f"{[x.shape[0] for x in xs]}")
+    reachable = KERNEL_SIZE - 1
+    world = int(kcp_context.world_size)
+    if world > 1 and tokens < reachable:
+        raise NotImplementedError(f"causal_conv1d_kcp: a rank needs at least {reachable} tokens, this one has {tokens}")
+    weights = [_kcp_taps(w) for w in weights]
+    widths = [x.shape[1] for x in xs]
+    wait_ready = getattr(kcp_context, "wait_ready", None)
+    if wait_ready is not None:
+        wait_ready()
+    prev_rows = next_rows = None
+    exchange = kcp_context.halo_exchange() if world > 1 and tokens else None
+    if exchange is not None:
+        entries = getattr(recompute_handle, "entries", None)
+        if entries is not None and "conv" in entries:
+            prev_rows, next_rows = entries["conv"]
+        else:
+            with torch.no_grad():
+                first = torch.cat([x[:reachable] for x in xs], dim=1)
+                last = torch.cat([x[-reachable:] for x in xs], dim=1)
+                prev_rows, next_rows = exchange.forward(first, last)
+            if entries is not None:
+                entries["conv"] = (prev_rows, next_rows)
+    halo = _Halo(_halo_cu(kcp_context, xs[0].device), _split_rows(prev_rows, widths), _split_rows(next_rows, widths),
+                 exchange.backward if exchange is not None else None)
+    ys = _CausalConv1d.apply(halo, policy, len(xs), *xs, *weights)
+    return tuple(y.view(shape) for y, shape in zip(ys, shapes))
+
+
+def causal_conv1d_kcp(x_local: torch.Tensor, weight: torch.Tensor, kcp_context: Any, *, recompute_handle: Any = None,
+                      cooperative: bool | None = None) -> torch.Tensor:
+    """Autograd-enabled ``silu(causal depthwise conv1d)`` of this rank's fragments under context parallelism: one
+    tensor of :func:`causal_conv1d_kcp_multi` (reference: ops.py:267-309)."""
+    if not isinstance(x_local, torch.Tensor) or not isinstance(weight, torch.Tensor):
+        raise TypeError("causal_conv1d_kcp takes one tensor and its taps; use causal_conv1d_kcp_multi for several")
+    return causal_conv1d_kcp_multi([x_local], [weight], kcp_context, recompute_handle=recompute_handle,
+                                   cooperative=cooperative)[0]
 
 
 def prebuild(*, device: Any = None, max_workers: int | None = None, weight_dtype: torch.dtype = torch.float32) -> list[Path]:

@@ -30,7 +30,7 @@ LAYOUTS = ("contiguous",)
 _CACHE_LIMIT = 32
 _CONTEXTS: OrderedDict[tuple[Any, ...], KcpContext] = OrderedDict()
 
-__all__ = ["KcpContext", "build_kcp_context", "document_run", "local_partition", "release"]
+__all__ = ["KcpContext", "build_kcp_context", "document_run", "halo_rows", "local_partition", "release"]
 
 
 def local_partition(cu_global: Sequence[int], rank: int, world_size: int):
@@ -54,6 +54,62 @@ def local_partition(cu_global: Sequence[int], rank: int, world_size: int):
     continues_in = part > 0 and lo not in bounds
     continues_out = part > 0 and hi not in bounds
     return local, continues_in, continues_out
+
+
+def halo_rows(cu_global: Sequence[int], rank: int, world_size: int, reach: int) -> tuple[int, int]:
+    """``(before, after)``: how many of the ``reach`` tokens just before this rank's slice belong to the document its
+    first fragment continues, and how many of the ``reach`` tokens just after it belong to the document its last
+    fragment continues into (what a causal convolution of width ``reach + 1`` reads across the cuts)."""
+    total = int(cu_global[-1])
+    part = total // world_size
+    lo, hi = rank * part, (rank + 1) * part
+    bounds = sorted(int(b) for b in cu_global)
+    before = after = 0
+    if part > 0 and lo not in bounds:
+        before = min(reach, lo - max(b for b in bounds if b < lo))
+    if part > 0 and hi not in bounds:
+        after = min(reach, min(b for b in bounds if b > hi) - hi)
+    return before, after
+
+
+class _HaloExchange:
+    """The rows a short causal convolution reads across this rank's cuts: three messages between neighbours, none
+    where no document crosses the cut.  Every rank of the group makes the same calls in the same order."""
+
+    def __init__(self, context: KcpContext) -> None:
+        self.context = context
+
+    def _swap(self, to_prev, to_next, want_prev: bool, want_next: bool):
+        import torch.distributed as dist
+
+        ctx = self.context
+        peer = lambda offset: (ctx.rank + offset if ctx.group is None
+                               else dist.get_global_rank(ctx.group, ctx.rank + offset))
+        ops, from_prev, from_next = [], None, None
+        template = to_prev if to_prev is not None else to_next
+        if to_next is not None and ctx.continues_out:
+            ops.append(dist.P2POp(dist.isend, to_next.contiguous(), peer(+1), ctx.group))
+        if to_prev is not None and ctx.continues_in:
+            ops.append(dist.P2POp(dist.isend, to_prev.contiguous(), peer(-1), ctx.group))
+        if want_prev and ctx.continues_in:
+            from_prev = torch.empty_like(template)
+            ops.append(dist.P2POp(dist.irecv, from_prev, peer(-1), ctx.group))
+        if want_next and ctx.continues_out:
+            from_next = torch.empty_like(template)
+            ops.append(dist.P2POp(dist.irecv, from_next, peer(+1), ctx.group))
+        if ops and ctx.world_size > 1:
+            for work in dist.batch_isend_irecv(ops):
+                work.wait()
+        return from_prev, from_next
+
+    def forward(self, first_rows: torch.Tensor, last_rows: torch.Tensor):
+        """Sends this rank's first rows to the rank before and its last rows to the rank after; returns
+        ``(rows of the rank before, rows of the rank after)``, ``None`` where no document crosses the cut."""
+        return self._swap(first_rows, last_rows, True, True)
+
+    def backward(self, first_rows: torch.Tensor):
+        """Sends the first rows of this rank's output gradient to the rank before; returns the rank after's."""
+        return self._swap(first_rows, None, False, True)[1]
 
 
 def document_run(cu_global: Sequence[int], rank: int, world_size: int) -> tuple[int, int]:
@@ -243,6 +299,11 @@ class KcpContext:
         self.num_tokens = local[-1]
         self.cu_seqlens = torch.tensor(local, dtype=torch.int32, device=self.device)
         self.fla_compatible = True  # a contiguous partition is FLA's
+        self.halo = halo_rows(self.cu_seqlens_global, self.rank, self.world_size, self.conv_kernel_size - 1)
+
+    def halo_exchange(self) -> _HaloExchange:
+        """The neighbour exchange of the layer's short convolutions."""
+        return _HaloExchange(self)
 
     def exchange(self, mode: str = "auto"):
         """The boundary-state exchange of one call: ``"sequential"`` (rank to rank; the single-rank bits on aligned

@@ -5,8 +5,8 @@ The entry points and their argument meaning follow the reference's op (reference
 miles_ext_kernels/cake/conv1d.py:30-57, miles_ext_kernels/cake/_impl/conv1d/ops.py:144-257).  Both variants (``det``,
 ``fast``) run the same kernels here: the weight gradient is summed in a fixed order, so identical inputs give
 identical bits.  miles selects the op with ``--linear-attention-conv-backend cake``.  The context-parallel entry points
-(``causal_conv1d_kcp``, ``causal_conv1d_kcp_multi``: the three history tokens of a continuing fragment come from the
-previous rank) are declared and raise ``NotImplementedError``.
+(``causal_conv1d_kcp``, ``causal_conv1d_kcp_multi``) read the three rows across each cut of a contiguous partition
+from the neighbouring rank: y and dx are the bits of the undivided call.
 
 Importing this module imports neither torch nor the implementation.
 """
@@ -17,13 +17,7 @@ from ._runtime.spec import Flag, OpSpec, lazy_exports
 
 
 def _validate(args: Namespace) -> None:
-    """No context parallelism through this op yet."""
-    size = getattr(args, "context_parallel_size", None) or 1
-    if size > 1:
-        raise ValueError(
-            "--linear-attention-conv-backend cake does not support context parallelism yet (--context-parallel-size "
-            f"{size}); use --linear-attention-conv-backend fla"
-        )
+    """Nothing to reject: context parallelism goes through ``causal_conv1d_kcp``."""
 
 
 OP = OpSpec(

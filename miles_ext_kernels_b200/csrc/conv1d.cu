@@ -10,8 +10,10 @@
 // Backward: dpre = dy silu'(p) with p the BF16-rounded preactivation ("bf16" policy, the rounding point of
 // flash-linear-attention) or the unrounded one ("fp32" policy); dx[t] = sum_k w[c, k] dpre[t + 3 - k] inside the
 // document; dw[c, k] = sum_t dpre[t] x[t - 3 + k].  The weight gradient is summed in a fixed order: per run in
-// registers (FP32; FP64 under the fp32 policy), then over the runs in FP64 by a second launch.  The number of runs is
+// registers (FP32; under the fp32 policy FP32 over four tokens, then FP64), then over the runs in FP64 by a second launch.  The number of runs is
 // a function of the token count alone: identical inputs give identical bits.
+#include <type_traits>
+
 #include "common.cuh"
 #include "umma.cuh"
 
@@ -69,11 +71,35 @@ __device__ __forceinline__ float preactivation(float w0, float x3, float w1, flo
   return __fadd_rn(pre, __fmul_rn(w3, x0));
 }
 
-// grid (runs, channel groups of 8 warps x 256); a warp owns tokens [run * run_len, + run_len) of 256 channels
+__device__ __forceinline__ uint4 load_row(const __nv_bfloat16* base, int64_t t, int channels, int c0) {
+  return __ldg(reinterpret_cast<const uint4*>(base + t * channels + c0));
+}
+
+// One token of the forward sweep.  kEdge = false: the token has three earlier tokens in its document (no selects).
+template <bool kEdge>
+__device__ __forceinline__ void conv_fwd_token(const float (&taps)[kConvTaps][8], float (&win)[3][8], uint4 raw,
+                                               int before, __nv_bfloat16* y_row) {
+  float cur[8], out[8];
+  unpack8(raw, cur);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float x1 = !kEdge || before >= 1 ? win[2][j] : 0.f, x2 = !kEdge || before >= 2 ? win[1][j] : 0.f;
+    const float x3 = !kEdge || before >= 3 ? win[0][j] : 0.f;
+    const float pre = preactivation(taps[0][j], x3, taps[1][j], x2, taps[2][j], x1, taps[3][j], cur[j]);
+    out[j] = __fdividef(pre, 1.0f + __expf(-pre));
+    win[0][j] = win[1][j], win[1][j] = win[2][j], win[2][j] = cur[j];
+  }
+  store8f(y_row, out);
+}
+
+// grid (runs, channel groups of 8 warps x 256); a warp owns tokens [run * run_len, + run_len) of 256 channels.  Tokens
+// go in batches of four; the next batch's loads are issued before the current batch's arithmetic.
 template <typename W>
-__global__ void __launch_bounds__(256) conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x, const W* __restrict__ w,
-                                                         const uint8_t* __restrict__ reach, __nv_bfloat16* __restrict__ y,
-                                                         int tokens, int channels, int run_len) {
+__global__ void __launch_bounds__(256, 2) conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ x_prev,
+                                                            const W* __restrict__ w, const uint8_t* __restrict__ reach,
+                                                            __nv_bfloat16* __restrict__ y, int tokens, int channels,
+                                                            int run_len) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c0 = (blockIdx.y * 8 + warp) * 256 + lane * 8;
   if (c0 >= channels) return;
@@ -84,46 +110,108 @@ __global__ void __launch_bounds__(256) conv1d_fwd_kernel(const __nv_bfloat16* __
   float win[3][8];  // x[t - 3], x[t - 2], x[t - 1]
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
-    const int t = t0 - 3 + i;
+    const int t = t0 - 3 + i;  // rows before the first token come from the history rows, when there are any
     if (t >= 0) load8f(x + int64_t(t) * channels + c0, win[i]);
+    else if (x_prev != nullptr) load8f(x_prev + int64_t(t + 3) * channels + c0, win[i]);
     else
 #pragma unroll
       for (int j = 0; j < 8; ++j) win[i][j] = 0.f;
   }
-  for (int tb = t0; tb < t1; tb += 4) {  // four tokens' loads in flight before any arithmetic
-    uint4 raw[4];
-    int before[4];
+  uint4 raw[4], next[4];
+  int before[4], next_before[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int t = min(tb + i, t1 - 1);
-      raw[i] = __ldg(reinterpret_cast<const uint4*>(x + int64_t(t) * channels + c0));
-      before[i] = reach[t] & 3;
-    }
+  for (int i = 0; i < 4; ++i) {
+    const int t = min(t0 + i, t1 - 1);
+    raw[i] = load_row(x, t, channels, c0);
+    before[i] = reach[t] & 3;
+  }
+  for (int tb = t0; tb < t1; tb += 4) {
+    if (tb + 4 < t1) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (tb + i >= t1) break;
-      float cur[8], out[8];
-      unpack8(raw[i], cur);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float pre = preactivation(taps[0][j], before[i] >= 3 ? win[0][j] : 0.f, taps[1][j],
-                                        before[i] >= 2 ? win[1][j] : 0.f, taps[2][j],
-                                        before[i] >= 1 ? win[2][j] : 0.f, taps[3][j], cur[j]);
-        out[j] = pre / (1.0f + __expf(-pre));
-        win[0][j] = win[1][j], win[1][j] = win[2][j], win[2][j] = cur[j];
+      for (int i = 0; i < 4; ++i) {
+        const int t = min(tb + 4 + i, t1 - 1);
+        next[i] = load_row(x, t, channels, c0);
+        next_before[i] = reach[t] & 3;
       }
-      store8f(y + int64_t(tb + i) * channels + c0, out);
     }
+    __nv_bfloat16* y_row = y + int64_t(tb) * channels + c0;
+    if (tb + 3 < t1 && (before[0] & before[1] & before[2] & before[3]) == 3) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) conv_fwd_token<false>(taps, win, raw[i], 3, y_row + int64_t(i) * channels);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (tb + i < t1) conv_fwd_token<true>(taps, win, raw[i], before[i], y_row + int64_t(i) * channels);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) raw[i] = next[i], before[i] = next_before[i];
   }
 }
 
-// One sweep over tokens [t0 - 3 ... t1 + 3): dpre of token u needs x[u - 3 .. u]; dx of token t needs dpre[t .. t + 3].
+// One step of the backward sweep: dpre of token u (needs x[u - 3 .. u]) and dx of token t = u - 3 (needs
+// dpre[t .. t + 3]).  kEdge = false: u and t are the run's own tokens with three neighbours inside their documents on
+// the side that matters, so nothing is selected or skipped.
+template <bool kEdge, bool kRoundPre, typename Sum>
+__device__ __forceinline__ void conv_bwd_token(const float (&taps)[kConvTaps][8], float (&xw)[3][8], float (&dp)[3][8],
+                                               Sum (&sum)[kConvTaps][8], uint4 raw_x, uint4 raw_g, int before,
+                                               int after, bool has_u, bool own_u, bool write_t,
+                                               __nv_bfloat16* dx_row) {
+  float cur[8], d[8];
+  if (!kEdge || has_u) {
+    float g[8];
+    unpack8(raw_x, cur);
+    unpack8(raw_g, g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float x1 = !kEdge || before >= 1 ? xw[2][j] : 0.f, x2 = !kEdge || before >= 2 ? xw[1][j] : 0.f;
+      const float x3 = !kEdge || before >= 3 ? xw[0][j] : 0.f;
+      const float pre = preactivation(taps[0][j], x3, taps[1][j], x2, taps[2][j], x1, taps[3][j], cur[j]);
+      const float p = kRoundPre ? __bfloat162float(__float2bfloat16_rn(pre)) : pre;
+      const float sg = __fdividef(1.0f, 1.0f + __expf(-p));
+      d[j] = g[j] * (sg * fmaf(p, 1.0f - sg, 1.0f));
+      if (!kEdge || own_u) {  // the run's own tokens feed the weight gradient
+        sum[3][j] += Sum(d[j]) * Sum(cur[j]);
+        sum[2][j] += Sum(d[j]) * Sum(x1);
+        sum[1][j] += Sum(d[j]) * Sum(x2);
+        sum[0][j] += Sum(d[j]) * Sum(x3);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cur[j] = 0.f, d[j] = 0.f;
+  }
+  if (!kEdge || write_t) {
+    float out[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v = taps[3][j] * dp[0][j];
+      v = fmaf(taps[2][j], !kEdge || after >= 1 ? dp[1][j] : 0.f, v);
+      v = fmaf(taps[1][j], !kEdge || after >= 2 ? dp[2][j] : 0.f, v);
+      v = fmaf(taps[0][j], !kEdge || after >= 3 ? d[j] : 0.f, v);
+      out[j] = v;
+    }
+    store8f(dx_row, out);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    xw[0][j] = xw[1][j], xw[1][j] = xw[2][j], xw[2][j] = cur[j];
+    dp[0][j] = dp[1][j], dp[1][j] = dp[2][j], dp[2][j] = d[j];
+  }
+}
+
+// One sweep over tokens [t0 ... t1 + 3) in batches of four, the next batch's loads issued before the current batch's
+// arithmetic.  The weight gradient's products are summed in FP32 inside a batch when Acc is FP64 (four terms), and the
+// batch sums in Acc.
 template <typename W, typename Acc, bool kRoundPre>
-__global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ x, const W* __restrict__ w,
-                                                         const __nv_bfloat16* __restrict__ dy,
+__global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                         const __nv_bfloat16* __restrict__ x_prev,
+                                                         const __nv_bfloat16* __restrict__ x_next,
+                                                         const W* __restrict__ w, const __nv_bfloat16* __restrict__ dy,
+                                                         const __nv_bfloat16* __restrict__ dy_next,
                                                          const uint8_t* __restrict__ reach,
                                                          __nv_bfloat16* __restrict__ dx, Acc* __restrict__ dw_partial,
                                                          int tokens, int channels, int run_len) {
+  constexpr bool kBatchSums = !std::is_same<Acc, float>::value;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c0 = (blockIdx.y * 8 + warp) * 256 + lane * 8;
   if (c0 >= channels) return;
@@ -142,74 +230,89 @@ __global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __
   for (int i = 0; i < 3; ++i) {
     const int t = t0 - 3 + i;
     if (t >= 0) load8f(x + int64_t(t) * channels + c0, xw[i]);
+    else if (x_prev != nullptr) load8f(x_prev + int64_t(t + 3) * channels + c0, xw[i]);
     else
 #pragma unroll
       for (int j = 0; j < 8; ++j) xw[i][j] = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) dp[i][j] = 0.f;  // dpre before t0 is never used: dx starts at t0
   }
-  const int u_end = min(t1 + 3, tokens);
-  for (int ub = t0; ub < t1 + 3; ub += 4) {  // four tokens' loads in flight before any arithmetic
-    uint4 raw_x[4], raw_g[4];
-    int reach_u[4], reach_t[4];
+  // rows after the last token come from the continuation rows (x_next, dy_next: 3 rows each), when there are any
+  const int u_end = x_next != nullptr ? t1 + 3 : min(t1 + 3, tokens);
+  auto row_of = [&](const __nv_bfloat16* here, const __nv_bfloat16* after, int u) {
+    return u < tokens ? load_row(here, u, channels, c0) : load_row(after, u - tokens, channels, c0);
+  };
+  uint4 raw_x[4], raw_g[4], next_x[4], next_g[4];
+  int reach_u[4], reach_t[4], next_u[4], next_t[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int u = min(ub + i, u_end - 1);
-      raw_x[i] = __ldg(reinterpret_cast<const uint4*>(x + int64_t(u) * channels + c0));
-      raw_g[i] = __ldg(reinterpret_cast<const uint4*>(dy + int64_t(u) * channels + c0));
-      reach_u[i] = reach[u];
-      reach_t[i] = reach[max(ub + i - 3, 0)];
+  for (int i = 0; i < 4; ++i) {
+    const int u = min(t0 + i, u_end - 1);
+    raw_x[i] = row_of(x, x_next, u);
+    raw_g[i] = row_of(dy, dy_next, u);
+    reach_u[i] = reach[u];
+    reach_t[i] = reach[min(max(t0 + i - 3, 0), tokens - 1)];
+  }
+  for (int ub = t0; ub < t1 + 3; ub += 4) {
+    if (ub + 4 < t1 + 3) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int u = min(ub + 4 + i, u_end - 1);
+        next_x[i] = row_of(x, x_next, u);
+        next_g[i] = row_of(dy, dy_next, u);
+        next_u[i] = reach[u];
+        next_t[i] = reach[min(ub + 1 + i, tokens - 1)];
+      }
     }
+    __nv_bfloat16* dx_row = dx + int64_t(ub - 3) * channels + c0;  // only dereferenced for tokens >= t0
+    const int all_u = reach_u[0] & reach_u[1] & reach_u[2] & reach_u[3];
+    const int all_t = reach_t[0] & reach_t[1] & reach_t[2] & reach_t[3];
+    const bool inner = ub - 3 >= t0 && ub + 3 < t1 && (all_u & 3) == 3 && (all_t >> 2 & 3) == 3;
+    if (kBatchSums) {
+      float part[kConvTaps][8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int u = ub + i;
-      if (u >= t1 + 3) break;
-      float cur[8], d[8];
-      if (u < u_end) {
-        float g[8];
-        unpack8(raw_x[i], cur);
-        unpack8(raw_g[i], g);
-        const int before = reach_u[i] & 3;
+      for (int k = 0; k < kConvTaps; ++k)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float x1 = before >= 1 ? xw[2][j] : 0.f, x2 = before >= 2 ? xw[1][j] : 0.f;
-          const float x3 = before >= 3 ? xw[0][j] : 0.f;
-          const float pre = preactivation(taps[0][j], x3, taps[1][j], x2, taps[2][j], x1, taps[3][j], cur[j]);
-          const float p = kRoundPre ? __bfloat162float(__float2bfloat16_rn(pre)) : pre;
-          const float s = 1.0f / (1.0f + __expf(-p));
-          d[j] = g[j] * (s * (1.0f + p * (1.0f - s)));
-          if (u < t1) {  // the run's own tokens feed the weight gradient
-            acc[3][j] += Acc(d[j]) * Acc(cur[j]);
-            acc[2][j] += Acc(d[j]) * Acc(x1);
-            acc[1][j] += Acc(d[j]) * Acc(x2);
-            acc[0][j] += Acc(d[j]) * Acc(x3);
-          }
-        }
+        for (int j = 0; j < 8; ++j) part[k][j] = 0.f;
+      if (inner) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          conv_bwd_token<false, kRoundPre>(taps, xw, dp, part, raw_x[i], raw_g[i], 3, 3, true, true, true,
+                                           dx_row + int64_t(i) * channels);
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) cur[j] = 0.f, d[j] = 0.f;
-      }
-      // dx of token t = u - 3: dpre[t .. t + 3] = dp[0], dp[1], dp[2], d; the later ones only inside the document
-      const int t = u - 3;
-      if (t >= t0) {
-        const int after = (reach_t[i] >> 2) & 3;
-        float out[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float v = taps[3][j] * dp[0][j];
-          v = fmaf(taps[2][j], after >= 1 ? dp[1][j] : 0.f, v);
-          v = fmaf(taps[1][j], after >= 2 ? dp[2][j] : 0.f, v);
-          v = fmaf(taps[0][j], after >= 3 ? d[j] : 0.f, v);
-          out[j] = v;
+        for (int i = 0; i < 4; ++i) {
+          const int u = ub + i;
+          if (u < t1 + 3)
+            conv_bwd_token<true, kRoundPre>(taps, xw, dp, part, raw_x[i], raw_g[i], reach_u[i] & 3,
+                                            (reach_t[i] >> 2) & 3, u < u_end, u < t1, u - 3 >= t0,
+                                            dx_row + int64_t(i) * channels);
         }
-        store8f(dx + int64_t(t) * channels + c0, out);
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        xw[0][j] = xw[1][j], xw[1][j] = xw[2][j], xw[2][j] = cur[j];
-        dp[0][j] = dp[1][j], dp[1][j] = dp[2][j], dp[2][j] = d[j];
+      for (int k = 0; k < kConvTaps; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[k][j] += Acc(part[k][j]);
+    } else {
+      auto& sum = reinterpret_cast<float(&)[kConvTaps][8]>(acc);
+      if (inner) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          conv_bwd_token<false, kRoundPre>(taps, xw, dp, sum, raw_x[i], raw_g[i], 3, 3, true, true, true,
+                                           dx_row + int64_t(i) * channels);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int u = ub + i;
+          if (u < t1 + 3)
+            conv_bwd_token<true, kRoundPre>(taps, xw, dp, sum, raw_x[i], raw_g[i], reach_u[i] & 3,
+                                            (reach_t[i] >> 2) & 3, u < u_end, u < t1, u - 3 >= t0,
+                                            dx_row + int64_t(i) * channels);
+        }
       }
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      raw_x[i] = next_x[i], raw_g[i] = next_g[i], reach_u[i] = next_u[i], reach_t[i] = next_t[i];
   }
   if (dw_partial != nullptr) {
     Acc* out = dw_partial + (int64_t(blockIdx.x) * channels + c0) * kConvTaps;
@@ -267,8 +370,8 @@ int mek_conv1d_reach(const int32_t* cu_seqlens, int num_docs, int tokens, uint8_
   return launched("conv1d_reach");
 }
 
-int mek_conv1d_fwd(const void* x, const void* weight, int weight_is_bf16, const uint8_t* reach, void* y, int tokens,
-                   int channels, void* stream) {
+int mek_conv1d_fwd(const void* x, const void* x_prev, const void* weight, int weight_is_bf16, const uint8_t* reach,
+                   void* y, int tokens, int channels, void* stream) {
   using namespace mek;
   if (!x || !weight || !reach || !y) return fail(MEK_ERR_INVALID, "conv1d_fwd: a null pointer");
   if (int rc = check_conv("conv1d_fwd", tokens, channels, 1)) return rc;
@@ -277,32 +380,40 @@ int mek_conv1d_fwd(const void* x, const void* weight, int weight_is_bf16, const 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (weight_is_bf16)
     conv1d_fwd_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
+                                           static_cast<const __nv_bfloat16*>(x_prev),
                                            static_cast<const __nv_bfloat16*>(weight), reach,
                                            static_cast<__nv_bfloat16*>(y), tokens, channels, plan.run_len);
   else
-    conv1d_fwd_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(weight),
+    conv1d_fwd_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
+                                           static_cast<const __nv_bfloat16*>(x_prev), static_cast<const float*>(weight),
                                            reach, static_cast<__nv_bfloat16*>(y), tokens, channels, plan.run_len);
   return launched("conv1d_fwd");
 }
 
-int mek_conv1d_bwd(const void* x, const void* weight, int weight_is_bf16, const void* dy, const uint8_t* reach,
-                   void* dx, void* dw_partial, void* dw, int fp32_policy, int tokens, int channels, void* stream) {
+int mek_conv1d_bwd(const void* x, const void* x_prev, const void* x_next, const void* weight, int weight_is_bf16,
+                   const void* dy, const void* dy_next, const uint8_t* reach, void* dx, void* dw_partial, void* dw,
+                   int fp32_policy, int tokens, int channels, void* stream) {
   using namespace mek;
   if (!x || !weight || !dy || !reach || !dx) return fail(MEK_ERR_INVALID, "conv1d_bwd: a null pointer");
   if ((dw == nullptr) != (dw_partial == nullptr))
     return fail(MEK_ERR_INVALID, "conv1d_bwd: dw and its partial sums go together");
+  if ((x_next == nullptr) != (dy_next == nullptr))
+    return fail(MEK_ERR_INVALID, "conv1d_bwd: the continuation rows of x and of dy go together");
   if (int rc = check_conv("conv1d_bwd", tokens, channels, 1)) return rc;
   const ConvPlan plan = conv_plan(tokens);
   const dim3 grid(plan.runs, (channels + 2047) / 2048);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   const __nv_bfloat16* gp = static_cast<const __nv_bfloat16*>(dy);
+  const __nv_bfloat16* xprev = static_cast<const __nv_bfloat16*>(x_prev);
+  const __nv_bfloat16* xnext = static_cast<const __nv_bfloat16*>(x_next);
+  const __nv_bfloat16* gnext = static_cast<const __nv_bfloat16*>(dy_next);
   __nv_bfloat16* dxp = static_cast<__nv_bfloat16*>(dx);
   const int64_t entries = int64_t(channels) * kConvTaps;
   const unsigned sum_grid = unsigned((entries + 255) / 256);
 #define MEK_CONV_BWD(WT, ACC, ROUND)                                                                                 \
-  conv1d_bwd_kernel<WT, ACC, ROUND><<<grid, 256, 0, s>>>(xp, static_cast<const WT*>(weight), gp, reach, dxp,         \
-                                                         static_cast<ACC*>(dw_partial), tokens, channels,            \
+  conv1d_bwd_kernel<WT, ACC, ROUND><<<grid, 256, 0, s>>>(xp, xprev, xnext, static_cast<const WT*>(weight), gp, gnext, \
+                                                         reach, dxp, static_cast<ACC*>(dw_partial), tokens, channels, \
                                                          plan.run_len);                                              \
   if (int rc = launched("conv1d_bwd")) return rc;                                                                    \
   if (dw != nullptr) conv1d_dw_kernel<<<sum_grid, 256, 0, s>>>(static_cast<const ACC*>(dw_partial), plan.runs, entries, \

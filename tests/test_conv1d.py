@@ -50,8 +50,22 @@ def test_the_op_declaration_and_its_checks():
         conv1d.check_supported(512, 4, "silu", has_bias=True)
     with pytest.raises(ValueError, match="multiple of 8"):
         conv1d.check_supported(516, 4, "silu")
-    with pytest.raises(NotImplementedError):
-        conv1d.causal_conv1d_kcp(None, None, None)
+    with pytest.raises(TypeError, match="one tensor and its taps"):
+        conv1d.causal_conv1d_kcp([torch.zeros(4, 8)], torch.zeros(8, 4), None)
+    with pytest.raises(TypeError, match="sequences of tensors"):
+        conv1d.causal_conv1d_kcp_multi(torch.zeros(4, 8), [torch.zeros(8, 4)], None)
+
+
+def test_the_rows_a_cut_reaches_across():
+    from miles_ext_kernels_b200.cake._impl.gdn.kcp import halo_rows
+
+    cu = (0, 7, 9, 30, 40)  # cuts at 10, 20, 30 in a world of 4
+    assert halo_rows(cu, 0, 4, 3) == (0, 3)   # tokens 10..12 of the third document follow
+    assert halo_rows(cu, 1, 4, 3) == (1, 3)   # the third document began at 9: one row of history
+    assert halo_rows(cu, 2, 4, 3) == (3, 0)   # a document ends at the cut
+    assert halo_rows(cu, 3, 4, 3) == (0, 0)
+    assert halo_rows((0, 11, 40), 0, 4, 3) == (0, 1)  # one token of the first document past the cut
+    assert halo_rows((0, 40), 2, 4, 3) == (3, 3)
 
 
 # (S, C, documents): documents of 1-3 tokens and empty ones, run boundaries, channel counts that are not multiples
@@ -136,3 +150,86 @@ def test_one_document_without_boundaries_and_the_2d_form():
         causal_conv1d(x.expand(2, -1, -1), w)
     with pytest.raises(ValueError, match="multiple of 8"):
         causal_conv1d(x[..., :100], w[:100])
+
+
+class _CutContext:
+    """A rank's context whose neighbour exchange reads the undivided tensors (ranks emulated one after another on one
+    GPU): what the context-parallel entry points read of a ``KcpContext``."""
+
+    def __init__(self, cu, rank, world, full_xs, full_dys):
+        from miles_ext_kernels_b200.cake._impl.gdn.kcp import halo_rows, local_partition
+
+        self.rank, self.world_size = rank, world
+        self.cu_seqlens_cpu, self.continues_in, self.continues_out = local_partition(cu, rank, world)
+        self.num_tokens = self.cu_seqlens_cpu[-1]
+        self.halo = halo_rows(cu, rank, world, 3)
+        self.lo = rank * self.num_tokens
+        self.full_xs, self.full_dys = full_xs, full_dys
+        self.exchanges = 0
+
+    def _rows(self, tensors, start):
+        return torch.cat([t[start:start + 3] for t in tensors], dim=1)
+
+    def halo_exchange(self):
+        ctx = self
+
+        class Loopback:
+            def forward(self, first, last):
+                ctx.exchanges += 1
+                assert torch.equal(first, ctx._rows(ctx.full_xs, ctx.lo))
+                assert torch.equal(last, ctx._rows(ctx.full_xs, ctx.lo + ctx.num_tokens - 3))
+                prev = ctx._rows(ctx.full_xs, ctx.lo - 3) if ctx.continues_in else None
+                nxt = ctx._rows(ctx.full_xs, ctx.lo + ctx.num_tokens) if ctx.continues_out else None
+                return prev, nxt
+
+            def backward(self, first):
+                assert torch.equal(first, ctx._rows(ctx.full_dys, ctx.lo))
+                return ctx._rows(ctx.full_dys, ctx.lo + ctx.num_tokens) if ctx.continues_out else None
+
+        return Loopback()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("policy", ["bf16", "fp32"])
+@pytest.mark.parametrize("world,lens", [(2, (300, 724)), (4, (1, 2, 253, 1, 2, 509, 256)), (4, (1024,)),
+                                        (8, (130, 126, 2, 766))])
+def test_the_cut_route_gives_the_bits_of_the_undivided_call(world, lens, policy):
+    """y and dx of every rank's slice are the undivided call's; the ranks' weight-gradient partials add up to its
+    weight gradient within the gate; two tensors through one exchange equal two calls."""
+    import miles_ext_kernels_b200 as package
+    from miles_ext_kernels_b200.cake.conv1d import causal_conv1d_kcp, causal_conv1d_kcp_multi
+
+    S = sum(lens)
+    x, w, cu, dy = inputs(S, 384, lens, torch.float32)
+    x2, w2, _, dy2 = inputs(S, 136, lens, torch.bfloat16)
+    package.configure(cake_conv1d_silu_grad_preactivation=policy)
+    try:
+        want, want2 = run(x, w, cu, dy, policy), run(x2, w2, cu, dy2, policy)
+        cu_host = tuple(cu.tolist())
+        ys, dxs, dws, ys2, dxs2 = [], [], [], [], []
+        for rank in range(world):
+            ctx = _CutContext(cu_host, rank, world, [x[0], x2[0]], [dy[0], dy2[0]])
+            sl = slice(ctx.lo, ctx.lo + ctx.num_tokens)
+            xa, xb = x[0, sl].clone().requires_grad_(True), x2[0, sl].clone().requires_grad_(True)
+            wa, wb = w.clone().requires_grad_(True), w2.clone().requires_grad_(True)
+            ya, yb = causal_conv1d_kcp_multi([xa, xb], [wa, wb], ctx)
+            torch.autograd.backward([ya, yb], [dy[0, sl], dy2[0, sl]])
+            assert ctx.exchanges == 1 and wb.grad.dtype == torch.bfloat16
+            ys.append(ya.detach()), dxs.append(xa.grad), dws.append(wa.grad.double())
+            ys2.append(yb.detach()), dxs2.append(xb.grad)
+            # one tensor on its own: the same bits, and a recompute handle skips the second exchange
+            class Handle:
+                entries = {}
+            single = _CutContext(cu_host, rank, world, [x[0]], [dy[0]])
+            xs_ = x[0, sl].clone().requires_grad_(True)
+            y1 = causal_conv1d_kcp(xs_, w, single, recompute_handle=Handle)
+            y1.backward(dy[0, sl])
+            assert torch.equal(y1, ya) and torch.equal(xs_.grad, xa.grad)
+            again = causal_conv1d_kcp(x[0, sl], w, single, recompute_handle=Handle)
+            assert single.exchanges == 1 and torch.equal(again, ya)
+        assert torch.equal(torch.cat(ys), want["y"][0]) and torch.equal(torch.cat(dxs), want["dx"][0])
+        assert torch.equal(torch.cat(ys2), want2["y"][0]) and torch.equal(torch.cat(dxs2), want2["dx"][0])
+        atol, rtol = (DW_ATOL, DW_RTOL) if policy == "bf16" else (DW_FP32G_ATOL, DW_FP32G_RTOL)
+        assert C.outside(sum(dws).float().cpu(), want["dw"].double().cpu(), atol=atol, rtol=rtol) == 0
+    finally:
+        package.configure()

@@ -101,3 +101,67 @@ def test_ranks_against_one_gpu(tmp_path, case):
         else:
             ok, m = O.within_budget(got.float(), ref.float(), rel_rms_max=6e-3, max_abs_rel=2e-2)
             assert ok, (name, m)
+
+
+def _conv_worker(rank: int, world: int, port: int, out_dir: str, lens, channels) -> None:
+    import torch.distributed as dist
+
+    from miles_ext_kernels_b200.cake import gdn
+    from miles_ext_kernels_b200.cake.conv1d import causal_conv1d_kcp_multi
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120),
+                            device_id=dev)
+    cu = (0, *torch.tensor(lens).cumsum(0).tolist())
+    ctx = gdn.build_kcp_context(cu, device=dev)
+    sl = slice(rank * ctx.num_tokens, (rank + 1) * ctx.num_tokens)
+    full = _conv_inputs(sum(lens), channels)
+    xs = [full[f"x{i}"][sl].to(dev).requires_grad_(True) for i in range(len(channels))]
+    ws = [full[f"w{i}"].to(dev).requires_grad_(True) for i in range(len(channels))]
+    ys = causal_conv1d_kcp_multi(xs, ws, ctx)
+    torch.autograd.backward(list(ys), [full[f"dy{i}"][sl].to(dev) for i in range(len(channels))])
+    torch.cuda.synchronize()
+    out = {}
+    for i in range(len(channels)):
+        out.update({f"y{i}": ys[i].detach().cpu(), f"dx{i}": xs[i].grad.cpu(), f"dw{i}": ws[i].grad.cpu()})
+    torch.save(out, f"{out_dir}/rank{rank}.pt")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _conv_inputs(S, channels):
+    gen = torch.Generator().manual_seed(77)
+    out = {}
+    for i, c in enumerate(channels):
+        out[f"x{i}"] = torch.randn(S, c, generator=gen).bfloat16()
+        out[f"w{i}"] = 0.5 * torch.randn(c, 4, generator=gen)
+        out[f"dy{i}"] = torch.randn(S, c, generator=gen).bfloat16()
+    return out
+
+
+@pytest.mark.parametrize("world,lens", [(2, (300, 724)), (4, (1, 2, 253, 1, 2, 509, 256))])
+def test_short_convolution_across_ranks(tmp_path, world, lens):
+    """The three rows across each cut travel between neighbours (one message per direction for the layer's
+    tensors): y and dx are the bits of one GPU's call, the ranks' weight-gradient partials add up to its sum."""
+    import torch.multiprocessing as mp
+
+    from miles_ext_kernels_b200.cake.conv1d import causal_conv1d
+
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    channels = (384, 136)
+    mp.spawn(_conv_worker, args=(world, _free_port(), str(tmp_path), lens, channels), nprocs=world, join=True)
+    dev = torch.device("cuda", 0)
+    full = _conv_inputs(sum(lens), channels)
+    cu = torch.tensor((0, *torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32, device=dev)
+    parts = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    for i in range(len(channels)):
+        x, w = full[f"x{i}"].to(dev).requires_grad_(True), full[f"w{i}"].to(dev).requires_grad_(True)
+        y = causal_conv1d(x, w, cu)
+        y.backward(full[f"dy{i}"].to(dev))
+        assert torch.equal(torch.cat([p[f"y{i}"] for p in parts]), y.detach().cpu())
+        assert torch.equal(torch.cat([p[f"dx{i}"] for p in parts]), x.grad.cpu())
+        dw = sum(p[f"dw{i}"].double() for p in parts)
+        assert torch.allclose(dw, w.grad.double().cpu(), atol=5e-2, rtol=1e-4)
