@@ -68,6 +68,44 @@ def test_the_rows_a_cut_reaches_across():
     assert halo_rows((0, 40), 2, 4, 3) == (3, 3)
 
 
+def _halo_rank(rank, world, port, out_dir):
+    import os
+
+    import torch.distributed as dist
+
+    from miles_ext_kernels_b200.cake._impl.gdn.kcp import KcpContext
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ctx = KcpContext((0, 15, 20, 30), None, rank, world, "cpu")  # cuts at 10 (inside a document) and 20 (between two)
+    rows = torch.arange(30 * 4, dtype=torch.float32).view(30, 4)[rank * 10:(rank + 1) * 10]
+    exchange = ctx.halo_exchange()
+    prev, nxt = exchange.forward(rows[:3].clone(), rows[-3:].clone())
+    back = exchange.backward(-rows[:3].clone())
+    torch.save({"halo": ctx.halo, "prev": prev, "next": nxt, "back": back}, f"{out_dir}/rank{rank}.pt")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_neighbours_exchange_rows_only_across_cut_documents(tmp_path):
+    """World of 3 over gloo: rows cross the first cut in both directions, nothing crosses the second."""
+    import socket
+
+    import torch.multiprocessing as mp
+
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    mp.spawn(_halo_rank, args=(3, port, str(tmp_path)), nprocs=3, join=True)
+    full = torch.arange(30 * 4, dtype=torch.float32).view(30, 4)
+    got = [torch.load(tmp_path / f"rank{r}.pt") for r in range(3)]
+    assert [g["halo"] for g in got] == [(0, 3), (3, 0), (0, 0)]
+    assert got[0]["prev"] is None and torch.equal(got[0]["next"], full[10:13])
+    assert torch.equal(got[0]["back"], -full[10:13])
+    assert torch.equal(got[1]["prev"], full[7:10]) and got[1]["next"] is None and got[1]["back"] is None
+    assert got[2]["prev"] is None and got[2]["next"] is None and got[2]["back"] is None
+
+
 # (S, C, documents): documents of 1-3 tokens and empty ones, run boundaries, channel counts that are not multiples
 # of a warp's 256 or of a block's 2048, and the framework's per-rank channel counts
 CASES = (
