@@ -33,10 +33,34 @@ struct TailSmem {
   static constexpr uint32_t kA = kV + 16384;           // [64][64] A
   static constexpr uint32_t kAqk = kA + 8192;          // [64][64] Aqk
   static constexpr uint32_t kB8 = kAqk + 8192;         // [64][64] dS, then bf16(beta dL D)
-  static constexpr uint32_t kScal = kB8 + 8192;        // floats: beta[2][64], g2[2][64], cs[2][4][64], red[4][64],
-                                                       //         red2[4][64], warp[8]
-  static constexpr uint32_t kBytes = kScal + (2 * 64 * 2 + 2 * 4 * 64 + 8 * 64 + 16) * 4;
+  static constexpr uint32_t kScal = kB8 + 8192;        // floats: beta[2][64], g2[2][64], cs[2][4][64], red[8][64],
+                                                       //         red2[8][64], warp[16 + 1]
+  static constexpr uint32_t kBytes = kScal + (2 * 64 * 2 + 2 * 4 * 64 + 16 * 64 + 32) * 4;
 };
+
+// Threads: kTailGroups warpgroups.  Warps w, w + 4, ... share the accumulator rows 16 (w % 4) .. + 15; a thread owns
+// kTailW columns of its row in every accumulator.
+constexpr int kTailThreads = 512;
+constexpr int kTailGroups = kTailThreads / 128;  // warpgroups
+constexpr int kTailW = 64 / kTailGroups;         // columns of a thread's piece
+constexpr int kTailJ = kTailW / 8;               // ... in 16-byte chunks of a tile row
+constexpr int kTailPieces = 2 * kTailGroups;     // column pieces of a 128-wide row
+
+__device__ __forceinline__ void tail_tmem_ld(uint32_t taddr, float* v) {
+  if constexpr (kTailW == 32) tmem_ld32(taddr, v);
+  else tmem_ld16(taddr, v);
+}
+// the pieces' partial sums of one row, added in a fixed pairwise order
+__device__ __forceinline__ float tail_row_sum(const float* pieces, int row) {
+  float level[kTailPieces];
+#pragma unroll
+  for (int i = 0; i < kTailPieces; ++i) level[i] = pieces[i * 64 + row];
+#pragma unroll
+  for (int n = kTailPieces; n > 1; n >>= 1)
+#pragma unroll
+    for (int i = 0; i < n / 2; ++i) level[i] = level[2 * i] + level[2 * i + 1];
+  return level[0];
+}
 
 // Tensor-memory columns.  A [64 x 128] accumulator takes 64 columns: its logical columns 0..63 sit in lanes 0..15 of
 // each quadrant and 64..127 in lanes 16..31 (two N = 64 instructions), so every lane of a warp owns a row piece.
@@ -66,7 +90,7 @@ struct TailMaps {
   CUtensorMap a, aqk;                    // tiles [num_tiles * 64, 64], box 64 x 64
 };
 
-__global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
+__global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
     const __grid_constant__ TailMaps maps, const float* __restrict__ beta, const float* __restrict__ g_cs,
     const __nv_bfloat16* __restrict__ q_raw, const __nv_bfloat16* __restrict__ k_raw,
     const float* __restrict__ rstd_q, const float* __restrict__ rstd_k, __nv_bfloat16* __restrict__ dq,
@@ -76,6 +100,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
   __shared__ uint64_t bar;         // tensor-core commits
+  __shared__ uint64_t bar2;        // ... of the second issuing thread
   __shared__ uint64_t bar_item;    // the item's tiles: three instalments, one arrival each
   __shared__ uint64_t bar_uw;      // the item's u and w
   __shared__ uint64_t bar_qk[2];   // q and k of a pair, one barrier per buffer
@@ -86,26 +111,27 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
   const bool loader = tid == 64;   // the thread that issues every copy
   const int group = num_v_heads / num_qk_heads;
   const int num_pairs = num_chunks * num_qk_heads;
-  // accumulator rows: warps w and w + 4 share the rows 16 (w % 4) .. + 15.  A 128-wide accumulator is split four
-  // ways: the lane half picks logical columns 0..63 / 64..127, the warpgroup the 32-column piece inside that half.
-  // A 64-wide accumulator lives in lanes 0..15 only and is split in two by the warpgroup.
+  // accumulator rows: warps w, w + 4, ... share the rows 16 (w % 4) .. + 15.  A 128-wide accumulator is split
+  // 2 x kTailGroups ways: the lane half picks logical columns 0..63 / 64..127, the warpgroup the kTailW-column piece
+  // inside that half.  A 64-wide accumulator lives in lanes 0..15 only and is split by the warpgroup.
   const int quad = warp & 3, ch = warp >> 2, lh = lane >> 4;
   const int row = quad * 16 + (lane & 15);
-  const bool owner = lane < 16;        // holds a piece of the 64-wide accumulators
-  const int cq = lh * 2 + ch;          // which 32-column quarter of a 128-wide accumulator
-  const int lcol = lh * 64 + ch * 32;  // its first logical column
+  const bool owner = lane < 16;            // holds a piece of the 64-wide accumulators
+  const int cq = lh * kTailGroups + ch;    // which piece of a 128-wide accumulator
+  const int lcol = lh * 64 + ch * kTailW;  // its first logical column
   const int lchunk = lcol >> 3;        // ... as a 16-byte chunk index of a tile row
 
   float* s_beta = reinterpret_cast<float*>(sm + TailSmem::kScal);  // [2][64]
   float* s_g2 = s_beta + 128;                                      // [2][64]
   float* s_cs = s_g2 + 128;                                        // [2][4][64] partial column sums per quadrant
-  float* s_red = s_cs + 512;                                       // [4][64]
-  float* s_red2 = s_red + 256;                                     // [4][64]
-  float* s_warp = s_red2 + 256;                                    // [8]
+  float* s_red = s_cs + 512;                                       // [kTailPieces][64]
+  float* s_red2 = s_red + 512;                                     // [kTailPieces][64]
+  float* s_warp = s_red2 + 512;                                    // [warps + 1]
   Abort abort{&abort_flag};
 
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar2, 1);
     mbar_init(&bar_item, 3);
     mbar_init(&bar_uw, 1);
     mbar_init(&bar_qk[0], 1);
@@ -204,6 +230,15 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     phase ^= 1;
     tc_fence_after();
   };
+  // Two threads of different warps issue each phase's products (independent accumulators): one thread's
+  // instructions go out every ~52 cycles, the tensor core takes ~40 for these shapes.
+  uint32_t phase2 = 0;
+  auto mma_wait2 = [&]() {
+    if (!mbar_wait(&bar2, phase2)) abort.raise();
+    phase2 ^= 1;
+    mma_wait();
+  };
+  const bool issuer = tid == 0, issuer2 = tid == 32;
   auto stage_sync = [&]() {
     fence_async_smem();
     tc_fence_before();
@@ -221,12 +256,12 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
   // the warp that halves the columns a lane carries at every step (30 shuffles instead of 128), then one partial per
   // quadrant (summed after the next block barrier).  The order of the additions is fixed.
   auto publish_column_sums = [&](float* piece, float* where) {
-    float x[32];
+    float x[kTailW];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) x[j] = owner ? piece[j] : 0.f;
+    for (int j = 0; j < kTailW; ++j) x[j] = owner ? piece[j] : 0.f;
     const int l16 = lane & 15;
 #pragma unroll
-    for (int width = 16, m = 8; width >= 2; width >>= 1, m >>= 1) {
+    for (int width = kTailW / 2, m = 8; m >= 1; width >>= 1, m >>= 1) {
       const bool up = (l16 & m) != 0;  // this lane keeps the upper half of the columns it still carries
 #pragma unroll
       for (int j = 0; j < width; ++j) {
@@ -234,18 +269,17 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
         x[j] = mine + __shfl_xor_sync(0xffffffffu, send, m);
       }
     }
-    // lane l16 now holds, over the warp's 16 rows, the sums of the two columns whose index bits 4..1 spell its
-    // butterfly path: bit 4 <- (l16 & 8), bit 3 <- (l16 & 4), bit 2 <- (l16 & 2), bit 1 <- (l16 & 1)
+    // lane l16 now holds, over the warp's 16 rows, the sums of the kTailW / 16 columns its butterfly path spells:
+    // bit 3 of l16 chose the half, bit 2 the quarter, ... -- the columns l16 (kTailW / 16) ...
     if (lane < 16) {
-      const int col = ((l16 & 8) << 1) | ((l16 & 4) << 1) | ((l16 & 2) << 1) | ((l16 & 1) << 1);
-      where[quad * 64 + ch * 32 + col] = x[0];
-      where[quad * 64 + ch * 32 + col + 1] = x[1];
+#pragma unroll
+      for (int j = 0; j < kTailW / 16; ++j) where[quad * 64 + ch * kTailW + l16 * (kTailW / 16) + j] = x[j];
     }
   };
 
-  // scaled terms of this thread's (row, 32-column quarter) that cannot accumulate in tensor memory, summed over the
+  // scaled terms of this thread's (row, column piece) that cannot accumulate in tensor memory, summed over the
   // group: dq gets qscale (do h^T); dk gets rowscale (v_new dh^T) and beta 2^G dkb
-  float dq_reg[32], dk_reg[32];
+  float dq_reg[kTailW], dk_reg[kTailW];
   int item_parity = 0, qk_buf = 0, pairs_done = 0;
   bool aborted = false;
   for (; pair_live(pair) && !aborted; pair += gridDim.x, qk_buf ^= 1, ++pairs_done) {
@@ -257,7 +291,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
     const int next_pair = pair + gridDim.x;
     const bool has_next_pair = pair_live(next_pair);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) dq_reg[j] = dk_reg[j] = 0.f;
+    for (int j = 0; j < kTailW; ++j) dq_reg[j] = dk_reg[j] = 0.f;
 
     for (int gi = 0; gi < group; ++gi, item_parity ^= 1) {
       const Item it = item_of(pair, gi);
@@ -274,13 +308,13 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       if (!mbar_wait(&bar_item, item_parity)) abort.raise();
       if (gi == 0 && !mbar_wait(&bar_qk[qk_buf], (pairs_done >> 1) & 1)) abort.raise();
       if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows
-        clear_tile_rows<256>(sm + TailSmem::kDO, len, tid);
-        clear_tile_rows<256>(sm + TailSmem::kVN, len, tid);
-        clear_tile_rows<256>(sm + TailSmem::kDVN, len, tid);
-        clear_tile_rows<256>(sm + TailSmem::kV, len, tid);
+        clear_tile_rows<kTailThreads>(sm + TailSmem::kDO, len, tid);
+        clear_tile_rows<kTailThreads>(sm + TailSmem::kVN, len, tid);
+        clear_tile_rows<kTailThreads>(sm + TailSmem::kDVN, len, tid);
+        clear_tile_rows<kTailThreads>(sm + TailSmem::kV, len, tid);
         if (gi == 0) {
-          clear_tile_rows<256>(q_tile, len, tid);
-          clear_tile_rows<256>(k_tile, len, tid);
+          clear_tile_rows<kTailThreads>(q_tile, len, tid);
+          clear_tile_rows<kTailThreads>(k_tile, len, tid);
         }
       }
       stage_sync();
@@ -292,17 +326,20 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       if (last_of_pair && has_next_pair && loader) load_qk(next_pair, qk_buf ^ 1);
 
       // ---- phase A: everything that needs only loaded tiles -------------------------------------------------------
-      if (tid == 0) {
+      if (issuer) {
         umma_gemm<64, 64>(tmem + kColTa, op_do, false, op_vn, false, 128, false);   // dAqk = do v_new^T
         gemm128(kColT0, op_vn, false, op_dh, false, 128, false);                    // dkh  = v_new dh^T
         gemm128(kColT2, op_do, false, op_h, false, 128, false);                     // dq2  = do h^T
+        umma_commit(&bar);
+      }
+      if (issuer2) {
         gemm128(kColT1, op_dvn, false, op_h, false, 128, false, /*neg_a=*/true);    // dw   = -dv_new h^T
         gemm128(kColT3, op_a, true, op_dvn, true, 64, false);                       // dvb  = A^T dv_new
-        umma_commit(&bar);
+        umma_commit(&bar2);
       }
       // meanwhile: sum(dh . h) over the whole state tile
       float hdh = 0.f;
-      for (int i = tid; i < 128 * 16; i += 256) {
+      for (int i = tid; i < 128 * 16; i += kTailThreads) {
         float a[8], b[8];
         unpack8(tile_chunk(sm + TailSmem::kH, 16384, i >> 4, i & 15), a);
         unpack8(tile_chunk(sm + TailSmem::kDH, 16384, i >> 4, i & 15), b);
@@ -314,40 +351,40 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       const float rs_row = fast_exp2(g_last - gi_row);
       const float eg = fast_exp2(gi_row), qs_row = scale * eg, sk = beta_row * eg;
       float dG = 0.f, dB = 0.f, gdot = 0.f;
-      mma_wait();
+      mma_wait2();
       __syncthreads();  // every thread is past its reads of h / dh: epilogue A overwrites operand buffers
       {
         // dAqk piece (lanes 0..15): dS, P = dAqk . Aqk
-        float s[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColTa + ch * 32), s);
+        float s[kTailW];
+        tail_tmem_ld(tmem_addr(tmem, warp, kColTa + ch * kTailW), s);
         tmem_ld_wait();
         float rowsum = 0.f;
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
+        for (int jj = 0; jj < kTailJ; ++jj) {
           float aq[8], ds[8];
-          unpack8(tile_chunk(sm + TailSmem::kAqk, 8192, row, ch * 4 + jj), aq);
+          unpack8(tile_chunk(sm + TailSmem::kAqk, 8192, row, ch * kTailJ + jj), aq);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const int col = ch * 32 + jj * 8 + e;
+            const int col = ch * kTailW + jj * 8 + e;
             const float d = col <= row ? s[jj * 8 + e] : 0.f;
             ds[e] = col <= row ? scale * d * fast_exp2(gi_row - g2[col]) : 0.f;
             s[jj * 8 + e] = d * aq[e];
             rowsum += s[jj * 8 + e];
           }
-          if (owner) set_tile_chunk(sm + TailSmem::kB8, 8192, row, ch * 4 + jj, pack8(ds));
+          if (owner) set_tile_chunk(sm + TailSmem::kB8, 8192, row, ch * kTailJ + jj, pack8(ds));
         }
         if (owner) dG += rowsum;
         publish_column_sums(s, s_cs);
       }
       {
         // dkh and dq2 pieces: the scaled terms go to the register accumulators, their row dots to the gate gradient
-        float a[32], b[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), a);
-        tmem_ld32(tmem_addr(tmem, warp, kColT2 + ch * 32), b);
+        float a[kTailW], b[kTailW];
+        tail_tmem_ld(tmem_addr(tmem, warp, kColT0 + ch * kTailW), a);
+        tail_tmem_ld(tmem_addr(tmem, warp, kColT2 + ch * kTailW), b);
         tmem_ld_wait();
         float dot_k = 0.f, dot_q = 0.f;
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
+        for (int jj = 0; jj < kTailJ; ++jj) {
           float kk[8], qq[8];
           unpack8(tile_chunk(k_tile, 8192, row, lchunk + jj), kk);
           unpack8(tile_chunk(q_tile, 8192, row, lchunk + jj), qq);
@@ -365,18 +402,18 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       }
       {
         // dw -> its tile (the h region); dvb -> dv, dbeta, and its tile (the v buffer, read first)
-        float wv[32], y[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColT1 + ch * 32), wv);
-        tmem_ld32(tmem_addr(tmem, warp, kColT3 + ch * 32), y);
+        float wv[kTailW], y[kTailW];
+        tail_tmem_ld(tmem_addr(tmem, warp, kColT1 + ch * kTailW), wv);
+        tail_tmem_ld(tmem_addr(tmem, warp, kColT3 + ch * kTailW), y);
         tmem_ld_wait();
         float dot_v = 0.f;
         __nv_bfloat16* dv_row = dv + int64_t(start + row) * dv_pitch + hv * kDim + lcol;
-        uint4 vraw[4];
+        uint4 vraw[kTailJ];
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) vraw[jj] = tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj);
+        for (int jj = 0; jj < kTailJ; ++jj) vraw[jj] = tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj);
         __syncwarp();
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
+        for (int jj = 0; jj < kTailJ; ++jj) {
           float vv[8], out[8];
           unpack8(vraw[jj], vv);
 #pragma unroll
@@ -390,7 +427,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
         dB += dot_v;
         // every thread reads only its own (row, chunk) cells of the v tile and rewrites exactly those with dvb
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) set_tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj, pack8(y + jj * 8));
+        for (int jj = 0; jj < kTailJ; ++jj) set_tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj, pack8(y + jj * 8));
       }
       stage_sync();
       // do and v_new are done with: this value head's u and w take their buffers; then the next item's Aqk
@@ -401,21 +438,24 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       if (has_next) load_scalars(nx, item_parity ^ 1);
 
       // ---- phase B: dq += dS k ; dk += dS^T q ; dkb = A^T dw ---------------------------------------------------------
-      if (tid == 0) {
+      if (issuer) {
         gemm128(kColDQ, op_b8, false, op_k, true, 64, gi > 0);
         gemm128(kColDK, op_b8, true, op_q, true, 64, gi > 0);
-        gemm128(kColT0, op_a, true, op_dw, true, 64, false);
         umma_commit(&bar);
       }
+      if (issuer2) {
+        gemm128(kColT0, op_a, true, op_dw, true, 64, false);
+        umma_commit(&bar2);
+      }
       if (owner && ch == 0) dG -= s_cs[row] + s_cs[64 + row] + s_cs[128 + row] + s_cs[192 + row];
-      mma_wait();
+      mma_wait2();
       {
-        float dkb[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColT0 + ch * 32), dkb);
+        float dkb[kTailW];
+        tail_tmem_ld(tmem_addr(tmem, warp, kColT0 + ch * kTailW), dkb);
         tmem_ld_wait();
         float dot_k = 0.f, dot_kb = 0.f;
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
+        for (int jj = 0; jj < kTailJ; ++jj) {
           float kk[8];
           unpack8(tile_chunk(k_tile, 8192, row, lchunk + jj), kk);
 #pragma unroll
@@ -432,32 +472,35 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       }
       if (!mbar_wait(&bar_uw, item_parity)) abort.raise();  // u and w have landed
       if (len < kChunk) {
-        clear_tile_rows<256>(sm + TailSmem::kDO, len, tid);
-        clear_tile_rows<256>(sm + TailSmem::kVN, len, tid);
+        clear_tile_rows<kTailThreads>(sm + TailSmem::kDO, len, tid);
+        clear_tile_rows<kTailThreads>(sm + TailSmem::kVN, len, tid);
       }
       stage_sync();
       if (has_next && loader) load_states(nx);  // h / dh (and the dw tile) and A are done with
 
       // ---- phase C: Y = bf16(dkb) w^T + bf16(dvb) u^T ; KK = k k^T ---------------------------------------------------
-      if (tid == 0) {
+      if (issuer) {
         umma_gemm<64, 64>(tmem + kColTa, op_dkb, false, op_w, false, 128, false);
         umma_gemm<64, 64>(tmem + kColTa, op_dvb, false, op_u, false, 128, true);
-        umma_gemm<64, 64>(tmem + kColTb, op_k, false, op_k, false, 128, false);
         umma_commit(&bar);
       }
-      mma_wait();
+      if (issuer2) {
+        if (gi == 0) umma_gemm<64, 64>(tmem + kColTb, op_k, false, op_k, false, 128, false);  // KK: once per pair
+        umma_commit(&bar2);
+      }
+      mma_wait2();
       {
-        float s[32], kk[32];
-        tmem_ld32(tmem_addr(tmem, warp, kColTa + ch * 32), s);
-        tmem_ld32(tmem_addr(tmem, warp, kColTb + ch * 32), kk);
+        float s[kTailW], kk[kTailW];
+        tail_tmem_ld(tmem_addr(tmem, warp, kColTa + ch * kTailW), s);
+        tail_tmem_ld(tmem_addr(tmem, warp, kColTb + ch * kTailW), kk);
         tmem_ld_wait();
         float rowsum = 0.f, dot = 0.f;
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
+        for (int jj = 0; jj < kTailJ; ++jj) {
           float out[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const int col = ch * 32 + jj * 8 + e;
+            const int col = ch * kTailW + jj * 8 + e;
             const float dl = col < row ? round_bf16(-s[jj * 8 + e]) : 0.f;
             const float dld = col < row ? dl * fast_exp2(gi_row - g2[col]) : 0.f;
             const float kij = col < row ? kk[jj * 8 + e] : 0.f;
@@ -466,7 +509,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
             s[jj * 8 + e] = out[e] * kij;  // dL . L
             rowsum += s[jj * 8 + e];
           }
-          if (owner) set_tile_chunk(sm + TailSmem::kB8, 8192, row, ch * 4 + jj, pack8(out));
+          if (owner) set_tile_chunk(sm + TailSmem::kB8, 8192, row, ch * kTailJ + jj, pack8(out));
         }
         if (owner) {
           dB += dot;
@@ -478,7 +521,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       if (has_next && loader) load_row_tiles(nx);  // w, u, bf16(dkb), bf16(dvb) are done with
 
       // ---- phase D: dk += bf16(beta dL D) k + bf16(beta dL D)^T k ------------------------------------------------
-      if (tid == 0) {
+      if (issuer) {
         gemm128(kColDK, op_b8, false, op_k, true, 64, true);
         gemm128(kColDK, op_b8, true, op_k, true, 64, true);
         if (last_of_pair) umma_commit(&bar);  // otherwise the next item's first commit covers these too
@@ -496,11 +539,11 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
       float suffix = 0.f;
       if (tid < 64) {
         if (tid < len) {
-          suffix = (s_red[tid] + s_red[64 + tid]) + (s_red[128 + tid] + s_red[192 + tid]);
+          suffix = tail_row_sum(s_red, tid);
           if (tid == len - 1) {
             float gamma_dot = 0.f;
 #pragma unroll
-            for (int wv = 0; wv < 8; ++wv) gamma_dot += s_warp[wv];
+            for (int wv = 0; wv < kTailThreads / 32; ++wv) gamma_dot += s_warp[wv];
             suffix += gamma_dot;
           }
         }
@@ -509,32 +552,31 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
           const float other = __shfl_down_sync(0xffffffffu, suffix, m);
           if (lane + m < 32) suffix += other;
         }
-        if (tid == 32) s_warp[8] = suffix;  // the total of rows 32..63
+        if (tid == 32) s_warp[kTailThreads / 32] = suffix;  // the total of rows 32..63
       }
       __syncthreads();
       if (tid < len) {
-        if (tid < 32) suffix += s_warp[8];
+        if (tid < 32) suffix += s_warp[kTailThreads / 32];
         dg[int64_t(start + tid) * num_v_heads + hv] = suffix;
-        dbeta[int64_t(start + tid) * num_v_heads + hv] =
-            (s_red2[tid] + s_red2[64 + tid]) + (s_red2[128 + tid] + s_red2[192 + tid]);
+        dbeta[int64_t(start + tid) * num_v_heads + hv] = tail_row_sum(s_red2, tid);
       }
 
       if (last_of_pair) {
         // ---- the group's dq, dk: fp32 sums, the norm's pull-back, one rounding ----------------------------------
         mma_wait();
-        // this thread's 32 columns of its row: in the raw operands and in the outputs (token pitches may differ:
+        // this thread's columns of its row: in the raw operands and in the outputs (token pitches may differ:
         // either may be a column slice of a packed row)
         const int64_t raw_at = int64_t(start + row) * raw_pitch + hq * kDim + lcol;
         const int64_t out_at = int64_t(start + row) * dqk_pitch + hq * kDim + lcol;
-        // acc: this thread's 32 columns of the fp32 group sum.  With the op's L2 norm: dx = r (D - y (D . y)),
-        // y = x r from the raw row and the saved r; the dot product spans the four column quarters.
+        // acc: this thread's columns of the fp32 group sum.  With the op's L2 norm: dx = r (D - y (D . y)),
+        // y = x r from the raw row and the saved r; the dot product spans the row's column pieces.
         auto finish = [&](float* acc, const __nv_bfloat16* raw_rows, const float* rstd, __nv_bfloat16* out) {
           if (rstd != nullptr) {
             const float r = live ? rstd[int64_t(start + row) * num_qk_heads + hq] : 0.f;
-            float y[32];
+            float y[kTailW];
             float dot = 0.f;
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
+            for (int jj = 0; jj < kTailJ; ++jj) {
               uint4 x = make_uint4(0u, 0u, 0u, 0u);
               if (live) x = ldg16(raw_rows + raw_at + jj * 8);
               unpack8(x, y + jj * 8);
@@ -547,29 +589,29 @@ __global__ void __launch_bounds__(256) gdn_bwd_tail_kernel(
             __syncthreads();  // the previous reduction has read s_red
             s_red[cq * 64 + row] = dot;
             __syncthreads();
-            dot = (s_red[row] + s_red[64 + row]) + (s_red[128 + row] + s_red[192 + row]);
+            dot = tail_row_sum(s_red, row);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[j] = r * (acc[j] - y[j] * dot);
+            for (int j = 0; j < kTailW; ++j) acc[j] = r * (acc[j] - y[j] * dot);
           }
           if (live) {
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) reinterpret_cast<uint4*>(out + out_at)[jj] = pack8(acc + jj * 8);
+            for (int jj = 0; jj < kTailJ; ++jj) reinterpret_cast<uint4*>(out + out_at)[jj] = pack8(acc + jj * 8);
           }
         };
         {
-          float b[32];
-          tmem_ld32(tmem_addr(tmem, warp, kColDQ + ch * 32), b);
+          float b[kTailW];
+          tail_tmem_ld(tmem_addr(tmem, warp, kColDQ + ch * kTailW), b);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) dq_reg[j] += b[j];
+          for (int j = 0; j < kTailW; ++j) dq_reg[j] += b[j];
         }
         finish(dq_reg, q_raw, rstd_q, dq);
         {
-          float b[32];
-          tmem_ld32(tmem_addr(tmem, warp, kColDK + ch * 32), b);
+          float b[kTailW];
+          tail_tmem_ld(tmem_addr(tmem, warp, kColDK + ch * kTailW), b);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) dk_reg[j] += b[j];
+          for (int j = 0; j < kTailW; ++j) dk_reg[j] += b[j];
         }
         finish(dk_reg, k_raw, rstd_k, dk);
       }
@@ -638,7 +680,7 @@ extern "C" int mek_gdn_bwd_tail(const MekGdnDims* d, const void* q, const void* 
       (raw_pitch | dqk_pitch | dv_pitch) % 8 != 0)
     return fail(MEK_ERR_INVALID, "bwd_tail: a token pitch is smaller than its row or not a multiple of 8 elements");
   const int pairs = d->num_chunks * d->num_qk_heads;
-  gdn_bwd_tail_kernel<<<pairs < sms ? pairs : sms, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+  gdn_bwd_tail_kernel<<<pairs < sms ? pairs : sms, kTailThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       maps, beta, g_cs, In(q_raw), In(k_raw), rstd_q, rstd_k, Out(dq), Out(dk), Out(dv), dbeta, dg, d->chunk_start,
       d->chunk_len, d->num_chunks, d->num_qk_heads, d->num_v_heads, d->scale, raw_pitch, dqk_pitch, dv_pitch, status);
   return launched("bwd_tail");
