@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
     const int32_t* __restrict__ seq_chunk_start, int num_qk_heads, int num_v_heads, float scale,
     const float* __restrict__ gl2, const ScanPlan plan, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  __shared__ uint64_t bar, bar_load[2];
+  __shared__ uint64_t bar, bar_b, bar_load[2];  // bar_b: the second issuing thread's commits
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
 
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar_b, 1);
     mbar_init(&bar_load[0], 1);
     mbar_init(&bar_load[1], 1);
     fence_mbar_init();
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
   const uint32_t tmem = tmem_slot;
   const Operand op_dv{sbase + BwdDhSmem::kDV, 8192}, op_dh{sbase + BwdDhSmem::kDH, 16384};
 
-  uint32_t phase = 0;
+  uint32_t phase = 0, phase_b = 0;
   for (int c = c_end - 1; c >= c_begin; --c) {
     const int stage = (c_end - 1 - c) & 1;
     // the next chunk's extent: requested now, needed when its tiles are (nothing on the step's path waits for it)
@@ -173,17 +174,23 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
     tc_fence_after();
     if (abort.raised()) break;
 
+    // both [64 x 128] products as two N = 64 halves: V columns 0..63 -> lanes 0..15, 64..127 -> lanes 16..31; two
+    // threads of different warps issue one half each (a thread's instructions go out every ~52 cycles, the tensor
+    // core takes ~40)
     if (tid == 0) {
-      // both [64 x 128] products as two N = 64 halves: V columns 0..63 -> lanes 0..15, 64..127 -> lanes 16..31
       umma_gemm<64, 64>(tmem + kD1, op_k, false, op_dh, true, 128, false);                        // k dh_tape
-      umma_gemm<64, 64>(tmem + kD1 + (16u << 16), op_k, false, operand_at(op_dh, 0, 1), true, 128, false);
       umma_gemm<64, 64>(tmem + kD1b, op_aqk, true, op_do, true, 64, false);                       // Aqk^T do
-      umma_gemm<64, 64>(tmem + kD1b + (16u << 16), op_aqk, true, operand_at(op_do, 0, 1), true, 64, false);
       umma_commit(&bar);
+    }
+    if (tid == 64) {
+      umma_gemm<64, 64>(tmem + kD1 + (16u << 16), op_k, false, operand_at(op_dh, 0, 1), true, 128, false);
+      umma_gemm<64, 64>(tmem + kD1b + (16u << 16), op_aqk, true, operand_at(op_do, 0, 1), true, 64, false);
+      umma_commit(&bar_b);
     }
     if (c > c_begin) prefetch(c - 1, stage ^ 1, next_start, next_len);
     if (!mbar_wait(&bar, phase)) abort.raise();
-    phase ^= 1;
+    if (!mbar_wait(&bar_b, phase_b)) abort.raise();
+    phase ^= 1, phase_b ^= 1;
     tc_fence_after();
 
     const float* g2 = s_g2 + stage * 128;

@@ -361,7 +361,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     int num_v_heads, const float* __restrict__ gl2, const ScanPlan plan, __nv_bfloat16* __restrict__ o, float scale,
     int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  __shared__ uint64_t bar, bar_o, bar_load[2];
+  __shared__ uint64_t bar, bar_b, bar_qh, bar_o, bar_load[2];  // bar_b, bar_qh: the second issuing thread's products
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -394,6 +394,8 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
   const bool fused = o != nullptr && !prescan;
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar_b, 1);
+    mbar_init(&bar_qh, 2);
     mbar_init(&bar_o, 1);
     mbar_init(&bar_load[0], 1);
     mbar_init(&bar_load[1], 1);
@@ -465,7 +467,7 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
   const int out_row = quad * 16 + (lane & 15), out_col = (lane >> 4) * 64 + half * 32;
 
   // the fused output of the previous chunk: its products were committed on bar_o a step ago
-  uint32_t phase_o = 0;
+  uint32_t phase_o = 0, phase_b = 0, phase_qh = 0;
   struct Rows {
     int start, len;
     float qs;
@@ -526,17 +528,20 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     tc_fence_after();
     if (abort.raised()) break;
 
-    if (tid == 0) {
-      // D1 = w h_tape as two N = 64 products: V columns 0..63 -> lanes 0..15, 64..127 -> lanes 16..31 (columns 0..63
-      // of tensor memory), so every lane of a warp owns a row piece in the epilogue
-      umma_gemm<64, 64>(tmem, op_w, false, op_h, true, 128, false);
-      umma_gemm<64, 64>(tmem + (16u << 16), op_w, false, operand_at(op_h, 0, 1), true, 128, false);
-      umma_commit(&bar);
-      if (fused) {  // q h_tape, behind the step's own product
+    // D1 = w h_tape as two N = 64 products: V columns 0..63 -> lanes 0..15, 64..127 -> lanes 16..31 (columns 0..63
+    // of tensor memory), so every lane of a warp owns a row piece in the epilogue.  Two threads of different warps
+    // issue one half each (a thread's instructions go out every ~52 cycles, the tensor core takes ~40); the second
+    // one also issues the fused output's products.
+    if (tid == 0 || tid == 64) {
+      const uint32_t lanes = tid == 0 ? 0u : 16u << 16;
+      const Operand h_half = tid == 0 ? op_h : operand_at(op_h, 0, 1);
+      umma_gemm<64, 64>(tmem + lanes, op_w, false, h_half, true, 128, false);
+      umma_commit(tid == 0 ? &bar : &bar_b);
+      if (fused) {  // q h_tape, behind the step's own product; waited for before the state tile is rewritten
         const Operand op_q{sbase + stage * FwdHSmem::kStage + FwdHSmem::kQ, 8192};
         const uint32_t set = tmem + kColO + uint32_t((c - c_begin) & 1) * 128;
-        umma_gemm<64, 64>(set, op_q, false, op_h, true, 128, false);
-        umma_gemm<64, 64>(set + (16u << 16), op_q, false, operand_at(op_h, 0, 1), true, 128, false);
+        umma_gemm<64, 64>(set + lanes, op_q, false, h_half, true, 128, false);
+        umma_commit(&bar_qh);
       }
     }
     // the previous chunk's output, in the shadow of this step's first wait; its products were the other stage's
@@ -544,7 +549,8 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
     if (fused && c > c_begin) write_output(c - 1, 0, cur);  // `cur` still describes chunk c - 1 here
     if (c + 1 < c_end) prefetch(c + 1, stage ^ 1, next_start, next_len);
     if (!mbar_wait(&bar, phase)) abort.raise();
-    phase ^= 1;
+    if (!mbar_wait(&bar_b, phase_b)) abort.raise();
+    phase ^= 1, phase_b ^= 1;
     tc_fence_after();
 
     const float* g2 = s_g2 + stage * 128;
@@ -607,6 +613,11 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) h[p * 32 + j] = fmaf(gamma, h[p * 32 + j], d[j]);
+    }
+    // q h_tape has read the state tile (long since: it went out before the state update's product)
+    if (fused) {
+      if (!mbar_wait(&bar_qh, phase_qh)) abort.raise();
+      phase_qh ^= 1;
     }
     start = next_start, len = next_len;
   }
