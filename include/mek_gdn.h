@@ -69,6 +69,10 @@ int mek_selftest_umma(const void* a_img, int a_bytes, const void* b_img, int b_b
  * No counterpart in the reference. */
 int mek_selftest_tma(const void* src, int64_t rows, int64_t cols, int box_rows, int x, int y, void* out,
                      int32_t* status, void* stream);
+/* Cycles the tensor core takes for `count` products of shape (M, N, kdim) issued by 1 or 2 threads, or by one thread alternating between two accumulators (operands of
+ * zeros; M in {64, 128}, N in {64, 128, 256}): the measurement behind the kernels' choice of instruction shapes. */
+int mek_selftest_umma_rate(int m, int n, int a_mn, int b_mn, int kdim, int count, int issuers, int interleave,
+                           long long* cycles, int32_t* status, void* stream);
 
 /* Extents and chunk tables of one call.  Tokens are packed: [total_tokens, heads, 128]; a batch of B equal-length
  * sequences is B sequences of one packed row.  Chunks hold at most 64 tokens and never straddle a sequence.

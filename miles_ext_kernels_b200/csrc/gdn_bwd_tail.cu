@@ -245,12 +245,13 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
     __syncthreads();
     tc_fence_after();
   };
-  // D[64 x 128] (+)= A B as two N = 64 instructions: logical columns 0..63 -> lanes 0..15, 64..127 -> lanes 16..31
+  // D[64 x 128] (+)= A B as two chains of N = 64 instructions, alternating: logical columns 0..63 -> lanes 0..15,
+  // 64..127 -> lanes 16..31
   auto gemm128 = [&](uint32_t col, const Operand& a, bool a_mn, const Operand& b, bool b_mn, uint32_t kdim,
                      bool accumulate, bool neg_a = false) {
     const Operand b_hi = b_mn ? operand_at(b, 0, 1) : operand_at(b, 64, 0);
-    umma_gemm<64, 64>(tmem + col, a, a_mn, b, b_mn, kdim, accumulate, neg_a);
-    umma_gemm<64, 64>(tmem + col + kUpperLanes, a, a_mn, b_hi, b_mn, kdim, accumulate, neg_a);
+    umma_gemm_pair<64, 64>(tmem + col, a, a_mn, b, b_mn, kdim, accumulate, neg_a, tmem + col + kUpperLanes, a, a_mn,
+                           b_hi, b_mn, kdim, accumulate, neg_a);
   };
   // column sums of a [64 x 64] matrix held one 32-column row piece per owner thread: a butterfly over the 16 rows of
   // the warp that halves the columns a lane carries at every step (30 shuffles instead of 128), then one partial per
@@ -329,12 +330,12 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
       if (issuer) {
         umma_gemm<64, 64>(tmem + kColTa, op_do, false, op_vn, false, 128, false);   // dAqk = do v_new^T
         gemm128(kColT0, op_vn, false, op_dh, false, 128, false);                    // dkh  = v_new dh^T
-        gemm128(kColT2, op_do, false, op_h, false, 128, false);                     // dq2  = do h^T
+        gemm128(kColT3, op_a, true, op_dvn, true, 64, false);                       // dvb  = A^T dv_new
         umma_commit(&bar);
       }
       if (issuer2) {
+        gemm128(kColT2, op_do, false, op_h, false, 128, false);                     // dq2  = do h^T
         gemm128(kColT1, op_dvn, false, op_h, false, 128, false, /*neg_a=*/true);    // dw   = -dv_new h^T
-        gemm128(kColT3, op_a, true, op_dvn, true, 64, false);                       // dvb  = A^T dv_new
         umma_commit(&bar2);
       }
       // meanwhile: sum(dh . h) over the whole state tile
@@ -480,8 +481,9 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
 
       // ---- phase C: Y = bf16(dkb) w^T + bf16(dvb) u^T ; KK = k k^T ---------------------------------------------------
       if (issuer) {
-        umma_gemm<64, 64>(tmem + kColTa, op_dkb, false, op_w, false, 128, false);
-        umma_gemm<64, 64>(tmem + kColTa, op_dvb, false, op_u, false, 128, true);
+        // Y as two chains into two accumulators (T1 is free by now); the epilogue adds them
+        umma_gemm_pair<64, 64>(tmem + kColTa, op_dkb, false, op_w, false, 128, false, false, tmem + kColT1, op_dvb,
+                               false, op_u, false, 128, false, false);
         umma_commit(&bar);
       }
       if (issuer2) {
@@ -491,9 +493,15 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
       mma_wait2();
       {
         float s[kTailW], kk[kTailW];
-        tail_tmem_ld(tmem_addr(tmem, warp, kColTa + ch * kTailW), s);
-        tail_tmem_ld(tmem_addr(tmem, warp, kColTb + ch * kTailW), kk);
-        tmem_ld_wait();
+        {
+          float s2[kTailW];
+          tail_tmem_ld(tmem_addr(tmem, warp, kColTa + ch * kTailW), s);
+          tail_tmem_ld(tmem_addr(tmem, warp, kColT1 + ch * kTailW), s2);
+          tail_tmem_ld(tmem_addr(tmem, warp, kColTb + ch * kTailW), kk);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < kTailW; ++j) s[j] += s2[j];
+        }
         float rowsum = 0.f, dot = 0.f;
 #pragma unroll
         for (int jj = 0; jj < kTailJ; ++jj) {

@@ -137,8 +137,8 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   // q k^T -> lanes 0..15, k k^T -> lanes 16..31 of the same 64 columns
   if (tid == 0) {
     const Operand op_q{sbase + WySmem::kQ, 8192}, op_k{sbase + WySmem::kK, 8192};
-    umma_gemm<64, 64>(tmem, op_q, false, op_k, false, 128, false);
-    umma_gemm<64, 64>(tmem + kUpper, op_k, false, op_k, false, 128, false);
+    umma_gemm_pair<64, 64>(tmem, op_q, false, op_k, false, 128, false, false, tmem + kUpper, op_k, false, op_k, false,
+                           128, false, false);  // alternating: one product's instructions wait for one another
     umma_commit(&bar);
   }
   // meanwhile: kb = bf16(beta 2^G k), vb = bf16(beta v) (in place)
@@ -292,8 +292,8 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
     const Operand a{sbase + WySmem::kA, 8192};
     const Operand kb{sbase + WySmem::kKB, 8192};
     const Operand vb{sbase + WySmem::kV, 8192};
-    umma_gemm<64, 128>(tmem, a, false, kb, true, 64, false);
-    umma_gemm<64, 128>(tmem + kUpper, a, false, vb, true, 64, false);
+    umma_gemm_pair<64, 128>(tmem, a, false, kb, true, 64, false, false, tmem + kUpper, a, false, vb, true, 64, false,
+                            false);
     umma_commit(&bar);
   }
   // A -> global while the MMAs run

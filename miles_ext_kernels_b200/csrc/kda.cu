@@ -261,8 +261,8 @@ __global__ void __launch_bounds__(288) kda_intra_kernel(
     const Operand a{sbase + KdaIntraSmem::kA, 8192};
     const Operand kb{sbase + KdaIntraSmem::kKB, 8192};
     const Operand vb{sbase + KdaIntraSmem::kVB, 8192};
-    umma_gemm<64, 128>(tmem, a, false, kb, true, 64, false);
-    umma_gemm<64, 128>(tmem + 128, a, false, vb, true, 64, false);
+    // alternating: the instructions of one product wait for one another
+    umma_gemm_pair<64, 128>(tmem, a, false, kb, true, 64, false, false, tmem + 128, a, false, vb, true, 64, false, false);
     umma_commit(&bar);
   }
   if (tid < 128) store_tile<64, 64, 128>(sm + KdaIntraSmem::kA, 8192, a_out + tile * 4096, 64, 64, tid);
@@ -396,10 +396,11 @@ __global__ void __launch_bounds__(256) kda_tail_mma_kernel(
 
   // ---- phase 1: dAqk = do v_new^T ; dkr = v_new dh^T ; dqg = (scale do) h^T ; dw = -dv_new h^T --------------------
   if (tid == 0) {
-    umma_gemm<64, 64>(tmem + cAqk, op_do, false, op_vn, false, 128, false);
-    umma_gemm<64, 128>(tmem + cDkr, op_vn, false, op_dh, false, 128, false);
-    umma_gemm<64, 128>(tmem + cDqg, op_dos, false, op_h, false, 128, false);
-    umma_gemm<64, 128>(tmem + cDw, op_dvn, false, op_h, false, 128, false, /*neg_a=*/true);
+    // in alternating pairs: the instructions of one product wait for one another
+    umma_gemm_pair<64, 64, 128>(tmem + cAqk, op_do, false, op_vn, false, 128, false, false, tmem + cDkr, op_vn, false,
+                                op_dh, false, 128, false, false);
+    umma_gemm_pair<64, 128>(tmem + cDqg, op_dos, false, op_h, false, 128, false, false, tmem + cDw, op_dvn, false, op_h,
+                            false, 128, false, /*neg=*/true);
     umma_commit(&bar);
   }
   if (tid < 128) {  // sum_v dh[k, v] h[k, v] per key channel
@@ -466,8 +467,8 @@ __global__ void __launch_bounds__(256) kda_tail_mma_kernel(
 
   // ---- phase 2: dkgb = A^T dw ; dvb = A^T dv_new ; dA = dw kb^T + dv_new vb^T -------------------------------------
   if (tid == 0) {
-    umma_gemm<64, 128>(tmem + 0, op_a, true, op_dw, true, 64, false);
-    umma_gemm<64, 128>(tmem + 128, op_a, true, op_dvn, true, 64, false);
+    umma_gemm_pair<64, 128>(tmem + 0, op_a, true, op_dw, true, 64, false, false, tmem + 128, op_a, true, op_dvn, true, 64,
+                            false, false);
     umma_gemm<64, 64>(tmem + 256, op_dw, false, op_kb, false, 128, false);
     umma_gemm<64, 64>(tmem + 256, op_dvn, false, op_vb, false, 128, true);
     umma_commit(&bar);

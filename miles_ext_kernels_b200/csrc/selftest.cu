@@ -93,6 +93,65 @@ __global__ void __launch_bounds__(128) selftest_tma_kernel(const __grid_constant
   }
 }
 
+
+// How long the tensor core takes for a run of instructions of one shape: `issuers` threads of different warps (1 or
+// 2) each issue `count` products of contraction `kdim` into an accumulator of their own (or, with `interleave`, one
+// thread issues twice as many, alternating between two accumulators), commit and wait; thread 0 reports the cycles
+// from its first instruction to the last completion.  The operands are zeros (only addresses and
+// shapes matter).
+template <int M, int N>
+__global__ void __launch_bounds__(128) umma_rate_kernel(int a_mn, int b_mn, int kdim, int count, int issuers,
+                                                       int interleave, long long* cycles, int32_t* status) {
+  extern __shared__ uint8_t raw[];
+  __shared__ uint64_t bar[2];
+  __shared__ uint32_t tmem_slot;
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x;
+  for (int i = tid; i < 196608 / 16; i += 128) reinterpret_cast<uint4*>(sm)[i] = make_uint4(0u, 0u, 0u, 0u);
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    fence_mbar_init();
+  }
+  if (tid < 32) tmem_alloc(&tmem_slot, 512);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot, sbase = smem_u32(sm);
+  // K-major: [rows][128 columns] as two blocks of rows x 128 bytes; MN-major: [kdim rows][extent columns] as
+  // blocks of 128 rows x 128 bytes
+  const Operand a{sbase, a_mn ? 16384u : uint32_t(M) * 128u};
+  const Operand b{sbase + 65536, b_mn ? 16384u : uint32_t(N) * 128u};
+  bool ok = true;
+  long long t0 = 0;
+  const int who = tid >> 5;
+  if (interleave) {  // one thread, the instructions alternating between two accumulators
+    if (tid == 0) {
+      t0 = clock64();
+      for (int i = 0; i < count * int(kdim >> 4); ++i) {
+        umma_gemm<M, N>(tmem, a, a_mn != 0, b, b_mn != 0, 16, true);
+        umma_gemm<M, N>(tmem + 256, a, a_mn != 0, b, b_mn != 0, 16, true);
+      }
+      umma_commit(&bar[0]);
+    }
+    issuers = 1;
+  } else if ((tid & 31) == 0 && who < issuers) {
+    t0 = clock64();
+    for (int i = 0; i < count; ++i) umma_gemm<M, N>(tmem + who * 256, a, a_mn != 0, b, b_mn != 0, kdim, true);
+    umma_commit(&bar[who]);
+  }
+  for (int i = 0; i < issuers; ++i) ok = mbar_wait(&bar[i], 0) && ok;
+  tc_fence_after();
+  if (tid == 0) {
+    cycles[0] = clock64() - t0;
+    if (!ok) atomicExch(status, kDevWaitTimeout | (9 << 8));
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid < 32) tmem_dealloc(tmem, 512);
+}
+
 }  // namespace mek
 
 extern "C" {
@@ -143,6 +202,25 @@ int mek_selftest_tma(const void* src, int64_t rows, int64_t cols, int box_rows, 
   selftest_tma_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(map, x, y, box_rows * 128,
                                                                           static_cast<uint4*>(out), status);
   return launched("selftest_tma");
+}
+
+int mek_selftest_umma_rate(int m, int n, int a_mn, int b_mn, int kdim, int count, int issuers, int interleave,
+                           long long* cycles, int32_t* status, void* stream) {
+  using namespace mek;
+  if (kdim < 16 || kdim > 128 || kdim % 16 || count < 1 || count > 4096 || issuers < 1 || issuers > 2)
+    return fail(MEK_ERR_INVALID, "selftest rate: kdim in 16..128, count in 1..4096, 1 or 2 issuers");
+  const size_t smem = 196608 + 1024;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define MEK_RATE(MM, NN)                                                                               \
+  if (m == MM && n == NN) {                                                                            \
+    if (int rc = want_smem(umma_rate_kernel<MM, NN>, smem, "selftest rate")) return rc;                \
+    umma_rate_kernel<MM, NN><<<1, 128, smem, s>>>(a_mn, b_mn, kdim, count, issuers, interleave, cycles, \
+                                                  status);                                             \
+    return launched("selftest rate");                                                                  \
+  }
+  MEK_RATE(64, 64) MEK_RATE(64, 128) MEK_RATE(64, 256) MEK_RATE(128, 64) MEK_RATE(128, 128) MEK_RATE(128, 256)
+#undef MEK_RATE
+  return fail(MEK_ERR_UNSUPPORTED, "selftest rate: M in {64, 128}, N in {64, 128, 256}");
 }
 
 }  // extern "C"

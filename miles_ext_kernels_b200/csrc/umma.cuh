@@ -253,6 +253,38 @@ __device__ __forceinline__ void umma_gemm(uint32_t tmem_d, const Operand& a, boo
   }
 }
 
+// Two products into two accumulators with their instructions alternating.  Consecutive instructions into ONE
+// accumulator wait for one another (~82 cycles each on a B200, whatever the shape up to N = 128); two chains keep the
+// tensor core busy (~47 cycles per M = 64, N = 64 instruction from one thread, ~41 from two threads).  The
+// contraction lengths may differ; the longer product's tail goes out alone.
+template <int M, int N, int N1 = N>
+__device__ __forceinline__ void umma_gemm_pair(uint32_t d0, const Operand& a0, bool a0_mn, const Operand& b0,
+                                               bool b0_mn, uint32_t kdim0, bool acc0, bool neg0, uint32_t d1,
+                                               const Operand& a1, bool a1_mn, const Operand& b1, bool b1_mn,
+                                               uint32_t kdim1, bool acc1, bool neg1) {
+  const uint32_t idesc0 = umma_idesc(M, N, a0_mn, b0_mn, neg0), idesc1 = umma_idesc(M, N1, a1_mn, b1_mn, neg1);
+  uint64_t da0 = a0_mn ? desc_mnmajor(a0, 0) : desc_kmajor(a0, 0), db0 = b0_mn ? desc_mnmajor(b0, 0) : desc_kmajor(b0, 0);
+  uint64_t da1 = a1_mn ? desc_mnmajor(a1, 0) : desc_kmajor(a1, 0), db1 = b1_mn ? desc_mnmajor(b1, 0) : desc_kmajor(b1, 0);
+  const uint32_t a0_step = a0_mn ? 128u : 2u, b0_step = b0_mn ? 128u : 2u;
+  const uint32_t a1_step = a1_mn ? 128u : 2u, b1_step = b1_mn ? 128u : 2u;
+  const uint32_t a0_jump = a0_mn ? 128u : (a0.block_stride >> 4) - 6u, b0_jump = b0_mn ? 128u : (b0.block_stride >> 4) - 6u;
+  const uint32_t a1_jump = a1_mn ? 128u : (a1.block_stride >> 4) - 6u, b1_jump = b1_mn ? 128u : (b1.block_stride >> 4) - 6u;
+  const uint32_t steps0 = kdim0 >> 4, steps1 = kdim1 >> 4;
+#pragma unroll
+  for (uint32_t k = 0; k < 8; ++k) {
+    if (k < steps0) {
+      umma_f16(d0, da0, db0, idesc0, (acc0 || k > 0) ? 1u : 0u);
+      da0 += (k & 3u) == 3u ? a0_jump : a0_step;
+      db0 += (k & 3u) == 3u ? b0_jump : b0_step;
+    }
+    if (k < steps1) {
+      umma_f16(d1, da1, db1, idesc1, (acc1 || k > 0) ? 1u : 0u);
+      da1 += (k & 3u) == 3u ? a1_jump : a1_step;
+      db1 += (k & 3u) == 3u ? b1_jump : b1_step;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // bf16 packing
 // ---------------------------------------------------------------------------------------------------------------

@@ -180,3 +180,36 @@ def test_tf32_operands_in_the_swizzled_layout(m, n, k, neg_a, d_lane):
     lanes = np.array([lane_of_row(m, r) + d_lane for r in range(m)])
     got = out.cpu().numpy()[lanes][:, :n]
     assert np.abs(got - want).max() <= 1e-4 * np.abs(want).max()
+
+
+@pytest.mark.gpu
+def test_two_accumulators_keep_the_tensor_core_busier_than_one():
+    """The measurement behind the kernels' issue order: instructions into one accumulator wait for one another, so a
+    thread that alternates between two accumulators, or two issuing threads, finish the same instructions sooner; and
+    one M = 128, N = 128 instruction does the work of four M = 64, N = 64 ones in less than their time."""
+    from miles_ext_kernels_b200.cake._runtime import loader
+
+    lib = loader.load_library()
+    dev = torch.device("cuda")
+    cycles = torch.zeros(1, dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def per_instruction(m, n, issuers, interleave, count=64):
+        for c in (8, count):  # a short run first: instruction cache, clocks
+            lib.check(lib.mek_selftest_umma_rate(m, n, 0, 1, 128, c, issuers, interleave,
+                                                 ctypes.c_void_p(cycles.data_ptr()),
+                                                 ctypes.c_void_p(status.data_ptr()),
+                                                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
+        chains = 2 if (issuers == 2 or interleave) else 1
+        return int(cycles.item()) / (count * 8 * chains)
+
+    one = per_instruction(64, 64, 1, 0)
+    alternating = per_instruction(64, 64, 1, 1)
+    two_threads = per_instruction(64, 64, 2, 0)
+    big = per_instruction(128, 128, 2, 0)
+    assert alternating < 0.8 * one and two_threads < 0.8 * one, (one, alternating, two_threads)
+    assert big < 0.6 * 4 * two_threads, (big, two_threads)  # four small ones' work in under 60 % of their time
+    with pytest.raises(NotImplementedError):
+        lib.check(lib.mek_selftest_umma_rate(96, 64, 0, 0, 128, 8, 1, 0, None, None, None))
