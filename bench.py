@@ -395,6 +395,88 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+def run_adjacent(args) -> None:
+    """The two row-wise ops either side of the path in a layer, at cfg1's shape on one GPU: ``--workload conv1d`` (the
+    packed causal conv1d + SiLU over the ``[q | k | v]`` row, 8,192 channels) and ``--workload gated_rmsnorm`` (the
+    SiLU-gated RMSNorm over the output's rows of 128).  Both are HBM-bound; the line's roofline entry is the backward
+    kernel's."""
+    import miles_ext_kernels_b200 as package
+    from miles_ext_kernels_b200.cake.conv1d import causal_conv1d
+    from miles_ext_kernels_b200.cake.gated_rmsnorm import rmsnorm_silu_gate
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); the kernels have no CPU fallback")
+    device = torch.device("cuda", 0)
+    package.configure()
+    tokens = args.tokens or 32768
+    gen = torch.Generator(device=device).manual_seed(11)
+    if args.workload == "conv1d":
+        channels = 8192
+        x = torch.randn(1, tokens, channels, device=device, generator=gen).bfloat16()
+        w = (0.5 * torch.randn(channels, 4, device=device, generator=gen)).requires_grad_(True)
+        dy = torch.randn(1, tokens, channels, device=device, generator=gen).bfloat16()
+        cu = torch.arange(0, tokens + 1, tokens // 4, dtype=torch.int32, device=device)
+        elements = tokens * channels
+        fwd_bytes, bwd_bytes = 4 * elements, 6 * elements  # bf16: x -> y; x, dy -> dx
+        what = f"packed causal conv1d + SiLU: {tokens} tokens x {channels} channels, 4 documents, fp32 taps"
+        z = None
+
+        def forward(leaf):
+            return causal_conv1d(leaf, w, cu)
+    else:
+        rows = tokens * 32
+        x = torch.randn(rows, 128, device=device, generator=gen).bfloat16()
+        z = torch.randn(rows, 128, device=device, generator=gen).bfloat16().requires_grad_(True)
+        w = torch.randn(128, device=device, generator=gen).bfloat16().requires_grad_(True)
+        dy = torch.randn(rows, 128, device=device, generator=gen).bfloat16()
+        elements = rows * 128
+        fwd_bytes, bwd_bytes = 6 * elements, 10 * elements  # bf16: x, z -> y; x, z, dy -> dx, dz
+        what = f"SiLU-gated RMSNorm: {rows} rows of 128 ({tokens} tokens x 32 value heads)"
+
+        def forward(leaf):
+            return rmsnorm_silu_gate(leaf, z, w, 1e-6)
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(args.steps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) / args.steps
+
+    def both():
+        leaf = x.detach().requires_grad_(True)
+        for parameter in (w, z):
+            if parameter is not None:
+                parameter.grad = None  # no accumulation kernels inside the timed region
+        forward(leaf).backward(dy)
+
+    peak, peak_kind = peaks()
+    with ClockSampler(0) as sampler:
+        with torch.no_grad():
+            ms_fwd = timed(lambda: forward(x))
+        ms_both = timed(both)
+    clocks = sampler.summary()
+    ms_bwd = ms_both - ms_fwd
+    achieved = bwd_bytes / (ms_bwd * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": f"{args.workload}_fwd_bwd_tokens_per_sec", "value": tokens / (ms_both * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_both, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": what, "l2_hygiene": "inputs are larger than the 126 MB L2"},
+        "ms_forward": ms_fwd, "ms_backward": ms_bwd,
+        "forward_gbs": fwd_bytes / (ms_fwd * 1e-3) / 1e9,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peak["hbm_gbs"], "kernel": f"{args.workload} backward (with its autograd glue)",
+                     "traffic": None, "peak_source": f"of {peak_kind}"},
+        "clocks": clocks,
+    }))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -405,7 +487,9 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
-    if args.impl == "reference":
+    if args.workload in ("conv1d", "gated_rmsnorm"):
+        run_adjacent(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
