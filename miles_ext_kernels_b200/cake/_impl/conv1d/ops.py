@@ -56,16 +56,34 @@ def _policy(silu_grad_preactivation: str | None) -> str:
     return policy
 
 
+class _Span:
+    """Tokens ``[lo, hi)`` of the call that one launch serves: ``cu`` (int32, on the device) are the boundaries of its
+    documents relative to ``lo``, the first moved back by the history rows that belong to the first document and the
+    last moved on by the continuation rows that belong to the last; ``prev`` / ``next``: per tensor the ``[3, C]``
+    rows before / after the span (``None``: nothing crosses that cut)."""
+
+    __slots__ = ("lo", "hi", "cu", "prev", "next")
+
+    def __init__(self, lo, hi, cu, prev, next):
+        self.lo, self.hi, self.cu, self.prev, self.next = lo, hi, cu, prev, next
+
+
 class _Halo:
-    """What a call reads beyond its own tokens: ``cu`` (int32, on the device) with the first entry moved back by the
-    history rows that belong to the first document and the last one moved on by the continuation rows that belong to
-    the last; per tensor the rows of the rank before / after (``[3, C]`` or ``None``); ``swap_back`` sends the first
-    rows of the output gradients to the rank before and returns the rank after's (``None``: a call on its own)."""
+    """The spans of a call and ``swap_back``, which sends the first rows of the spans' output gradients
+    (``[spans, 3, sum of C]``) to the ranks before and returns, per span, the rows after it (``None``: a call on its
+    own)."""
 
-    __slots__ = ("cu", "prev", "next", "swap_back")
+    __slots__ = ("spans", "swap_back")
 
-    def __init__(self, cu, prev, next, swap_back=None):
-        self.cu, self.prev, self.next, self.swap_back = cu, prev, next, swap_back
+    def __init__(self, spans, swap_back=None):
+        self.spans, self.swap_back = spans, swap_back
+
+
+def _stacked(rows: list[torch.Tensor], like: torch.Tensor, width: int) -> torch.Tensor:
+    """``[spans, 3, width]``; a rank without tokens still takes part in the exchange, with no spans."""
+    if rows:
+        return torch.stack(rows)
+    return like.new_zeros((0, KERNEL_SIZE - 1, width))
 
 
 def _split_rows(rows: torch.Tensor | None, widths: list[int]) -> list[torch.Tensor | None]:
@@ -80,56 +98,67 @@ class _CausalConv1d(torch.autograd.Function):
     @staticmethod
     def forward(ctx, halo, policy, n, *tensors):
         xs, weights = tensors[:n], tensors[n:]
-        tokens = xs[0].shape[0]
         device = xs[0].device
         ys = tuple(torch.empty_like(x) for x in xs)
-        reach = None
-        if tokens:
-            entries = tokens + (KERNEL_SIZE - 1 if any(r is not None for r in halo.next) else 0)
-            reach = torch.empty(entries, dtype=torch.uint8, device=device)
-            with torch.cuda.device(device):
-                native.launch("conv1d_reach", halo.cu, halo.cu.numel() - 1, entries, reach, device=device)
-                for x, w, y, prev in zip(xs, weights, ys, halo.prev):
-                    native.launch("conv1d_fwd", x, prev, w, int(w.dtype == torch.bfloat16), reach, y, tokens,
-                                  x.shape[1], device=device)
-        ctx.save_for_backward(reach, *xs, *weights)
+        reaches = []
+        with torch.cuda.device(device):
+            for span in halo.spans:
+                tokens = span.hi - span.lo
+                if tokens <= 0:
+                    reaches.append(None)
+                    continue
+                entries = tokens + (KERNEL_SIZE - 1 if any(r is not None for r in span.next) else 0)
+                reach = torch.empty(entries, dtype=torch.uint8, device=device)
+                native.launch("conv1d_reach", span.cu, span.cu.numel() - 1, entries, reach, device=device)
+                for x, w, y, prev in zip(xs, weights, ys, span.prev):
+                    native.launch("conv1d_fwd", x[span.lo : span.hi], prev, w, int(w.dtype == torch.bfloat16), reach,
+                                  y[span.lo : span.hi], tokens, x.shape[1], device=device)
+                reaches.append(reach)
+        ctx.save_for_backward(*xs, *weights, *[r for r in reaches if r is not None])
         ctx.halo, ctx.policy, ctx.n = halo, policy, n
+        ctx.have_reach = [r is not None for r in reaches]
         return ys
 
     @staticmethod
     def backward(ctx, *dys):
-        reach, *tensors = ctx.saved_tensors
         n, halo = ctx.n, ctx.halo
-        xs, weights = tensors[:n], tensors[n:]
-        tokens = xs[0].shape[0]
+        saved = ctx.saved_tensors
+        xs, weights, kept = saved[:n], saved[n : 2 * n], list(saved[2 * n :])
+        reaches = [kept.pop(0) if have else None for have in ctx.have_reach]
         device = xs[0].device
         dys = [torch.zeros_like(x) if dy is None else dy.reshape(x.shape).to(torch.bfloat16).contiguous()
                for x, dy in zip(xs, dys)]
-        dy_next = [None] * n
-        if halo.swap_back is not None and tokens:
-            reachable = KERNEL_SIZE - 1
-            dy_next = _split_rows(halo.swap_back(torch.cat([dy[:reachable] for dy in dys], dim=1)),
-                                  [x.shape[1] for x in xs])
+        reachable = KERNEL_SIZE - 1
+        widths = [x.shape[1] for x in xs]
+        after = [None] * len(halo.spans)
+        if halo.swap_back is not None:
+            firsts = _stacked([torch.cat([dy[span.lo : span.lo + reachable] for dy in dys], dim=1)
+                               for span in halo.spans], dys[0], sum(widths))
+            after = halo.swap_back(firsts)
         fp32_policy = ctx.policy == "fp32"
-        dxs, dws = [], []
-        for i, (x, w, dy) in enumerate(zip(xs, weights, dys)):
-            channels = x.shape[1]
-            dx = torch.empty_like(x)
-            want_dw = ctx.needs_input_grad[3 + n + i]
-            dw = torch.zeros_like(w) if want_dw else None
-            if tokens:
-                with torch.cuda.device(device):
-                    partial = None
-                    if want_dw:
+        dxs = [torch.empty_like(x) for x in xs]
+        dws = [torch.zeros_like(w) if ctx.needs_input_grad[3 + n + i] else None for i, w in enumerate(weights)]
+        with torch.cuda.device(device):
+            for span, reach, rows_after in zip(halo.spans, reaches, after):
+                tokens = span.hi - span.lo
+                if tokens <= 0:
+                    continue
+                dy_next = _split_rows(rows_after, widths)
+                for i, (x, w, dy, dx, dw) in enumerate(zip(xs, weights, dys, dxs, dws)):
+                    channels = x.shape[1]
+                    partial = span_dw = None
+                    if dw is not None:
                         runs = native.library().mek_conv1d_runs(tokens)
                         partial = workspace.take(OP, "dw_partial", (runs, channels, KERNEL_SIZE),
                                                  torch.float64 if fp32_policy else torch.float32, device)
-                    x_next = halo.next[i] if dy_next[i] is not None else None
-                    native.launch("conv1d_bwd", x, halo.prev[i], x_next, w, int(w.dtype == torch.bfloat16), dy,
-                                  dy_next[i] if x_next is not None else None, reach, dx, partial, dw,
-                                  int(fp32_policy), tokens, channels, device=device)
-            dxs.append(dx)
-            dws.append(dw)
+                        span_dw = dw if len(halo.spans) == 1 else torch.empty_like(dw)
+                    x_next = span.next[i] if dy_next[i] is not None else None
+                    native.launch("conv1d_bwd", x[span.lo : span.hi], span.prev[i], x_next, w,
+                                  int(w.dtype == torch.bfloat16), dy[span.lo : span.hi],
+                                  dy_next[i] if x_next is not None else None, reach, dx[span.lo : span.hi], partial,
+                                  span_dw, int(fp32_policy), tokens, channels, device=device)
+                    if dw is not None and span_dw is not dw:
+                        dw += span_dw  # the spans in order: a fixed sum
         return (None, None, None, *dxs, *dws)
 
 
@@ -167,7 +196,7 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, cu_seqlens: torch.Tenso
         cu_seqlens = torch.arange(2, dtype=torch.int32, device=x.device).mul_(tokens)  # no host copy, no sync
     else:
         cu_seqlens = cu_seqlens.to(torch.int32).contiguous()
-    halo = _Halo(cu_seqlens, [None], [None])
+    halo = _Halo([_Span(0, tokens, cu_seqlens, [None], [None])])
     (y,) = _CausalConv1d.apply(halo, policy, 1, x.view(tokens, x.shape[-1]), weight.contiguous())
     return y.view(x.shape)
 
@@ -178,16 +207,24 @@ def _kcp_taps(weight: torch.Tensor) -> torch.Tensor:
     return (weight.float() if weight.dtype == torch.bfloat16 else weight).contiguous()
 
 
-def _halo_cu(kcp_context: Any, device: torch.device) -> torch.Tensor:
-    """The rank's local boundaries with the first moved back by the history rows of the first document and the last
-    moved on by the continuation rows of the last; built once per context."""
+def _span_boundaries(kcp_context: Any, device: torch.device) -> list[torch.Tensor]:
+    """Per span of the rank's plan: the boundaries of its fragments relative to the span's first token, the first
+    moved back by the history rows of the first document and the last moved on by the continuation rows of the last;
+    built once per context (one host-to-device copy)."""
     cached = getattr(kcp_context, "_conv1d_cu", None)
-    if cached is None or cached.device != device:
-        before, after = kcp_context.halo
-        cu = list(kcp_context.cu_seqlens_cpu)
-        cu[0] -= before
-        cu[-1] += after
-        cached = torch.tensor(cu, dtype=torch.int32, device=device)
+    if cached is None or cached[0].device != device:
+        cu = kcp_context.cu_seqlens_cpu
+        flat, extents = [], []
+        for span in kcp_context.plan.spans:
+            local = [cu[i] - span.token_lo for i in range(span.first, span.last + 2)]
+            local[0] -= span.before
+            local[-1] += span.after
+            extents.append((len(flat), len(flat) + len(local)))
+            flat += local
+        table = torch.tensor(flat or [0], dtype=torch.int32)
+        if device.type == "cuda":
+            table = table.pin_memory().to(device, non_blocking=True)
+        cached = [table[a:b] for a, b in extents] or [table]
         try:
             kcp_context._conv1d_cu = cached
         except AttributeError:
@@ -202,11 +239,13 @@ def causal_conv1d_kcp_multi(xs, weights, kcp_context: Any, *, recompute_handle: 
 
     ``xs``: ``n >= 1`` BF16 ``[T_r, C_i]`` (or ``[1, T_r, C_i]``) tensors, the rank's fragments back to back;
     ``weights``: their ``[C_i, 4]`` taps, the same on every rank; ``kcp_context``: the rank's context of the layer's
-    GDN / KDA context-parallel route (read: ``num_tokens``, ``cu_seqlens_cpu``, ``halo``, ``world_size`` and
-    ``halo_exchange()``).  Every rank of the context's group makes this call for the same layers in the same order.
+    GDN / KDA context-parallel route (read: ``num_tokens``, ``cu_seqlens_cpu``, ``plan.spans``, ``world_size`` and
+    ``halo_exchange()``), under any of its layouts.  Every rank of the context's group makes this call for the same layers in the same order.
 
-    The forward sends a rank's first three rows to the rank before and its last three to the rank after, where a
-    document crosses the cut; the backward sends the first three rows of the output gradients to the rank before.  y
+    The forward sends the first three rows of every span of consecutive local fragments to the rank that holds the
+    tokens before it and the last three to the rank that holds the tokens after it, where a document crosses the cut
+    (point to point under the contiguous layout, one small all-gather under the others); the backward sends the
+    first three rows of the output gradients the same way.  A span is one launch per tensor.  y
     and dx are the bits of the undivided call; the weight gradient is the rank's partial sum over its own tokens (in
     ``weight``'s dtype; BF16 taps are widened first and autograd rounds their gradient back).  ``recompute_handle``:
     ``None`` or an object with an ``entries`` dict; the first forward stores the rows it received under ``"conv"``
@@ -234,28 +273,33 @@ def causal_conv1d_kcp_multi(xs, weights, kcp_context: Any, *, recompute_handle: 
                          f"{[x.shape[0] for x in xs]}")
     reachable = KERNEL_SIZE - 1
     world = int(kcp_context.world_size)
-    if world > 1 and tokens < reachable:
-        raise NotImplementedError(f"causal_conv1d_kcp: a rank needs at least {reachable} tokens, this one has {tokens}")
+    if world > 1 and any(sp.token_hi - sp.token_lo < reachable for sp in kcp_context.plan.spans):
+        raise NotImplementedError(f"causal_conv1d_kcp: every run of local fragments needs at least {reachable} tokens")
     weights = [_kcp_taps(w) for w in weights]
     widths = [x.shape[1] for x in xs]
     wait_ready = getattr(kcp_context, "wait_ready", None)
     if wait_ready is not None:
         wait_ready()
-    prev_rows = next_rows = None
-    exchange = kcp_context.halo_exchange() if world > 1 and tokens else None
+    plan_spans = kcp_context.plan.spans
+    prev_rows, next_rows = [None] * len(plan_spans), [None] * len(plan_spans)
+    exchange = kcp_context.halo_exchange() if world > 1 else None
     if exchange is not None:
         entries = getattr(recompute_handle, "entries", None)
         if entries is not None and "conv" in entries:
             prev_rows, next_rows = entries["conv"]
         else:
             with torch.no_grad():
-                first = torch.cat([x[:reachable] for x in xs], dim=1)
-                last = torch.cat([x[-reachable:] for x in xs], dim=1)
+                first = _stacked([torch.cat([x[sp.token_lo : sp.token_lo + reachable] for x in xs], dim=1)
+                                  for sp in plan_spans], xs[0], sum(widths))
+                last = _stacked([torch.cat([x[sp.token_hi - reachable : sp.token_hi] for x in xs], dim=1)
+                                 for sp in plan_spans], xs[0], sum(widths))
                 prev_rows, next_rows = exchange.forward(first, last)
             if entries is not None:
                 entries["conv"] = (prev_rows, next_rows)
-    halo = _Halo(_halo_cu(kcp_context, xs[0].device), _split_rows(prev_rows, widths), _split_rows(next_rows, widths),
-                 exchange.backward if exchange is not None else None)
+    boundaries = _span_boundaries(kcp_context, xs[0].device)
+    spans = [_Span(sp.token_lo, sp.token_hi, cu, _split_rows(before, widths), _split_rows(after, widths))
+             for sp, cu, before, after in zip(plan_spans, boundaries, prev_rows, next_rows)]
+    halo = _Halo(spans, exchange.backward if exchange is not None else None)
     ys = _CausalConv1d.apply(halo, policy, len(xs), *xs, *weights)
     return tuple(y.view(shape) for y, shape in zip(ys, shapes))
 

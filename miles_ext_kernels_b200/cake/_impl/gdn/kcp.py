@@ -1,5 +1,5 @@
-"""Context parallelism of the GDN op: one packed batch split into contiguous token slices, one per rank of a process
-group; the chunk state crosses rank boundaries.
+"""Context parallelism of the GDN op: one packed batch split over the ranks of a process group (contiguous slices, or
+the load-balanced zigzag layouts, or an explicit table of fragments); the chunk state crosses the cuts.
 
 :class:`KcpContext` is one rank's view of the partition (reference: miles_ext_kernels/cake/_impl/gdn/kcp.py:71-169):
 ``rank``, ``world_size``, ``num_tokens`` (this rank's), ``cu_seqlens`` / ``cu_seqlens_cpu`` (local boundaries: one
@@ -14,8 +14,10 @@ r - 1) and the parallel one (every rank summarises its boundary fragment as an a
 fold: ranks do not wait for one another; ``--cake-gdn-kcp-exchange``).  Either way the states land in this GPU's own
 memory before any kernel reads them (NCCL over NVLink between GPUs; gloo in the CPU tests).
 
-Only the ``"contiguous"`` layout is served; the load-balanced layouts of the reference (zigzag, per-document
-zigzag, explicit fragments) raise ``NotImplementedError``.
+Layouts (``layout.py``): ``contiguous``, ``zigzag``, ``zigzag_per_document`` and explicit fragment tables.  The
+sequential hand-over follows the rank chain and serves the contiguous layout only; the parallel exchange serves every
+layout: each rank publishes the summaries of its fragments whose documents go on, and folds, per fragment, the chain
+of the fragments before it in its document.
 """
 
 from __future__ import annotations
@@ -26,7 +28,9 @@ from typing import Any
 
 import torch
 
-LAYOUTS = ("contiguous",)
+from . import layout as layout_module
+
+LAYOUTS = layout_module.KCP_LAYOUTS
 _CACHE_LIMIT = 32
 _CONTEXTS: OrderedDict[tuple[Any, ...], KcpContext] = OrderedDict()
 
@@ -73,8 +77,9 @@ def halo_rows(cu_global: Sequence[int], rank: int, world_size: int, reach: int) 
 
 
 class _HaloExchange:
-    """The rows a short causal convolution reads across this rank's cuts: three messages between neighbours, none
-    where no document crosses the cut.  Every rank of the group makes the same calls in the same order."""
+    """The rows a short causal convolution reads across the cuts of a CONTIGUOUS partition: three messages between
+    neighbours, none where no document crosses the cut.  Every rank of the group makes the same calls in the same
+    order.  Rows travel stacked per span, ``[1, reach, C]`` here (a contiguous slice is one span)."""
 
     def __init__(self, context: KcpContext) -> None:
         self.context = context
@@ -103,13 +108,48 @@ class _HaloExchange:
         return from_prev, from_next
 
     def forward(self, first_rows: torch.Tensor, last_rows: torch.Tensor):
-        """Sends this rank's first rows to the rank before and its last rows to the rank after; returns
-        ``(rows of the rank before, rows of the rank after)``, ``None`` where no document crosses the cut."""
-        return self._swap(first_rows, last_rows, True, True)
+        """``first_rows``, ``last_rows``: ``[spans, reach, C]``, the first and last rows of every local span.  Sends
+        them to the ranks that hold the neighbouring spans; returns ``(rows before, rows after)``, a list per side
+        with one ``[reach, C]`` tensor per span, ``None`` where no document crosses the cut."""
+        if first_rows.shape[0] == 0:
+            return [], []
+        prev, nxt = self._swap(first_rows[0], last_rows[-1], True, True)
+        return [prev], [nxt]
 
     def backward(self, first_rows: torch.Tensor):
-        """Sends the first rows of this rank's output gradient to the rank before; returns the rank after's."""
-        return self._swap(first_rows, None, False, True)[1]
+        """Sends the first rows of the spans' output gradients to the ranks before; returns the rows after."""
+        if first_rows.shape[0] == 0:
+            return []
+        return [self._swap(first_rows[0], None, False, True)[1]]
+
+
+class _GatherHalo:
+    """The same rows under any layout: one all-gather of every span's first and last rows (a few rows per span), from
+    which a rank picks its neighbours' (``RankPlan.spans``)."""
+
+    def __init__(self, context: KcpContext) -> None:
+        self.context = context
+
+    def _gather(self, local: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+
+        ctx = self.context
+        padded = local.new_zeros((ctx.plan.max_spans, *local.shape[1:]))
+        padded[: local.shape[0]] = local
+        gathered = padded.new_empty((ctx.world_size * padded.shape[0], *padded.shape[1:]))
+        dist.all_gather_into_tensor(gathered, padded.contiguous(), group=ctx.group)
+        return gathered.view(ctx.world_size, *padded.shape)
+
+    def forward(self, first_rows: torch.Tensor, last_rows: torch.Tensor):
+        both = self._gather(torch.stack([first_rows, last_rows], dim=1))  # [W, spans, 2, reach, C]
+        spans = self.context.plan.spans
+        prev = [None if sp.prev is None else both[sp.prev[0], sp.prev[1], 1].contiguous() for sp in spans]
+        nxt = [None if sp.next is None else both[sp.next[0], sp.next[1], 0].contiguous() for sp in spans]
+        return prev, nxt
+
+    def backward(self, first_rows: torch.Tensor):
+        rows = self._gather(first_rows)  # [W, spans, reach, C]
+        return [None if sp.next is None else rows[sp.next[0], sp.next[1]].contiguous() for sp in self.context.plan.spans]
 
 
 def document_run(cu_global: Sequence[int], rank: int, world_size: int) -> tuple[int, int]:
@@ -206,70 +246,90 @@ class _Exchange:
 
 
 class _ParallelExchange:
-    """Every rank works at once: a rank summarises the fragment through which a state leaves it as ``(B, M)`` with
-    ``S_out = M S_in + B`` (pre-scan of the fragment's segments, composed by the stitch kernel), one all-gather
-    shares the summaries, and each rank folds the chain of ranks its boundary document has crossed into the state
-    that enters it (reference: the affine rank summaries of miles_ext_kernels/cake/_impl/gdn/kcp.py and
-    _vendor/cake_gdn_det_train_kcp).  The cost per rank is one pre-scan, one gather and its own scan, whatever the
-    number of ranks; the result agrees with the sequential hand-over within the accuracy budgets, not bit for bit
-    (a state crosses a rank as ``M S + B`` in fp32 instead of through the chunk steps)."""
+    """Every rank works at once: a rank summarises each of its fragments through which a state leaves it as
+    ``(B, M)`` with ``S_out = M S_in + B`` (pre-scan of the fragment's segments, composed by the stitch kernel), one
+    all-gather shares the summaries, and each rank folds, per fragment, the chain of the fragments before it in its
+    document into the state that enters it (reference: the affine summaries of
+    miles_ext_kernels/cake/_impl/gdn/kcp.py and _vendor/cake_gdn_det_train_kcp).  The cost per rank is one pre-scan
+    per published fragment, one gather and its own scan, whatever the number of ranks; the result agrees with the
+    sequential hand-over within the accuracy budgets, not bit for bit (a state crosses a fragment as ``M S + B`` in
+    fp32 instead of through the chunk steps).  Serves every layout: under the contiguous one a rank publishes at
+    most one summary per direction."""
 
     def __init__(self, context: KcpContext) -> None:
         self.context = context
-        self.first_rank, self.last_rank = document_run(context.cu_seqlens_global, context.rank, context.world_size)
 
     def _gather(self, local: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
 
         ctx = self.context
-        gathered = torch.empty((ctx.world_size, *local.shape), dtype=local.dtype, device=local.device)
+        gathered = torch.empty((ctx.world_size * local.shape[0], *local.shape[1:]), dtype=local.dtype,
+                               device=local.device)
         dist.all_gather_into_tensor(gathered, local, group=ctx.group)
-        return gathered
+        return gathered.view(ctx.world_size, *local.shape)
 
-    def forward_begin(self, dims, meta, k, w, u, g_cs, status):
-        from . import native, scan
+    @staticmethod
+    def _chain(flat: torch.Tensor, slots: int, chain) -> torch.Tensor:
+        """The summaries ``[(rank, slot), ...]`` of ``flat [W * slots, HV, 2, 128, 128]`` as one tensor, in order."""
+        index = [r * slots + s for r, s in chain]
+        if index == list(range(index[0], index[0] + len(index))):
+            return flat[index[0] : index[0] + len(index)]
+        return flat.index_select(0, torch.tensor(index, dtype=torch.int64).pin_memory().to(flat.device, non_blocking=True))
 
-        ctx = self.context
-        device, HV = w.device, w.shape[1]
-        local = torch.zeros((HV, 2, 128, 128), dtype=torch.float32, device=device)
-        if ctx.continues_out:  # the state leaves through the last fragment
-            table = meta.host_seq_chunk_start
-            plan = scan.fragment_plan(table[-2], table[-1], HV, device)
+    def _exchange(self, dims, meta, HV, device, publish, slots, chains, summarise, reverse):
+        from . import scan
+
+        local = torch.zeros((max(slots, 1), HV, 2, 128, 128), dtype=torch.float32, device=device)
+        table = meta.host_seq_chunk_start
+        for slot, f in enumerate(publish):
+            plan = scan.fragment_plan(table[f], table[f + 1], HV, device)
             seg_dims = scan.segment_dims(dims, plan)
             summary = torch.empty((plan.segments, HV, 2, 128, 128), dtype=torch.float32, device=device)
-            native.launch("gdn_fwd_h_prescan", seg_dims, k, w, u, g_cs, None, plan.flags_fwd, plan.state_row,
-                          plan.warm_chunks, plan.warm_log2, summary, status, device=device)
-            local = scan.compose_summary(seg_dims, plan, summary, g_cs, reverse=False)
+            summarise(seg_dims, plan, summary)
+            local[slot] = scan.compose_summary(seg_dims, plan, summary, self._g_cs, reverse=reverse)
         gathered = self._gather(local)
-        if not ctx.continues_in:
-            return None, False
-        h0 = torch.zeros((meta.num_seqs, HV, 128, 128), dtype=torch.float32, device=device)
-        h0[0] = scan.fold_ranks(dims, gathered, self.first_rank, ctx.rank - 1, reverse=False)[0]
+        if not any(chains):
+            return None
+        flat = gathered.view(-1, HV, 2, 128, 128)
+        states = torch.zeros((meta.num_seqs, HV, 128, 128), dtype=torch.float32, device=device)
+        for f, chain in enumerate(chains):
+            if chain:
+                run = self._chain(flat, max(slots, 1), chain)
+                states[f] = scan.fold_ranks(dims, run, 0, len(chain) - 1, reverse=reverse)[0]
+        return states
+
+    def forward_begin(self, dims, meta, k, w, u, g_cs, status):
+        from . import native
+
+        plan = self.context.plan
+        device, HV = w.device, w.shape[1]
+        self._g_cs = g_cs
+
+        def summarise(seg_dims, frag, summary):
+            native.launch("gdn_fwd_h_prescan", seg_dims, k, w, u, g_cs, None, frag.flags_fwd, frag.state_row,
+                          frag.warm_chunks, frag.warm_log2, summary, status, device=device)
+
+        h0 = self._exchange(dims, meta, HV, device, plan.publish_forward, plan.slots_forward, plan.chain_forward,
+                            summarise, reverse=False)
         return h0, False
 
     def forward_end(self, final_state) -> None:
         pass
 
     def backward_begin(self, dims, meta, tape, do):
-        from . import native, scan
+        from . import native
 
-        ctx = self.context
+        plan = self.context.plan
         device, HV = do.device, tape.v.shape[1]
-        local = torch.zeros((HV, 2, 128, 128), dtype=torch.float32, device=device)
-        if ctx.continues_in:  # the adjoint state leaves through the first fragment
-            table = meta.host_seq_chunk_start
-            plan = scan.fragment_plan(table[0], table[1], HV, device)
-            seg_dims = scan.segment_dims(dims, plan)
-            summary = torch.empty((plan.segments, HV, 2, 128, 128), dtype=torch.float32, device=device)
+        self._g_cs = tape.g_cs
+
+        def summarise(seg_dims, frag, summary):
             native.launch("gdn_bwd_dh_prescan", seg_dims, tape.qn, tape.kn, tape.w, do, tape.aqk, tape.g_cs, None,
-                          plan.flags_bwd, plan.state_row, plan.warm_chunks, plan.warm_log2, summary, tape.status,
+                          frag.flags_bwd, frag.state_row, frag.warm_chunks, frag.warm_log2, summary, tape.status,
                           device=device)
-            local = scan.compose_summary(seg_dims, plan, summary, tape.g_cs, reverse=True)
-        gathered = self._gather(local)
-        if not ctx.continues_out:
-            return None, False
-        dht = torch.zeros((meta.num_seqs, HV, 128, 128), dtype=torch.float32, device=device)
-        dht[-1] = scan.fold_ranks(dims, gathered, ctx.rank + 1, self.last_rank, reverse=True)[0]
+
+        dht = self._exchange(dims, meta, HV, device, plan.publish_backward, plan.slots_backward, plan.chain_backward,
+                             summarise, reverse=True)
         return dht, False
 
     def backward_end(self, dh0) -> None:
@@ -277,40 +337,54 @@ class _ParallelExchange:
 
 
 class KcpContext:
-    """One rank's view of a contiguous partition of a packed batch."""
+    """One rank's view of a partition of a packed batch (reference:
+    miles_ext_kernels/cake/_impl/gdn/kcp.py:71-169): ``rank``, ``world_size``, ``num_tokens`` (this rank's),
+    ``cu_seqlens`` / ``cu_seqlens_cpu`` (local boundaries, one sequence per fragment), ``fragments``, ``layout``,
+    ``group``, ``fla_compatible`` and the ``plan`` of what crosses the cuts (``layout.RankPlan``)."""
 
     def __init__(self, cu_seqlens_global, group, rank: int, world_size: int, device, conv_kernel_size: int = 4,
                  layout: str = "contiguous", fragments=None) -> None:
-        if layout not in LAYOUTS or fragments is not None:
-            raise NotImplementedError(
-                f"KcpContext: only the {LAYOUTS} layout without explicit fragments is served, not {layout!r}"
-            )
         self.cu_seqlens_global = tuple(int(b) for b in cu_seqlens_global)
         if not self.cu_seqlens_global or self.cu_seqlens_global[0] != 0:
             raise ValueError("KcpContext: cu_seqlens_global must start at 0")
         self.group = group
         self.rank, self.world_size = int(rank), int(world_size)
+        if not 0 <= self.rank < self.world_size:
+            raise ValueError(f"rank {rank} is not in a world of {world_size}")
         self.device = torch.device(device)
         self.conv_kernel_size = int(conv_kernel_size)
-        self.layout = layout
-        local, self.continues_in, self.continues_out = local_partition(self.cu_seqlens_global, self.rank,
-                                                                       self.world_size)
-        self.cu_seqlens_cpu = local
-        self.num_tokens = local[-1]
-        self.cu_seqlens = torch.tensor(local, dtype=torch.int32, device=self.device)
-        self.fla_compatible = True  # a contiguous partition is FLA's
-        self.halo = halo_rows(self.cu_seqlens_global, self.rank, self.world_size, self.conv_kernel_size - 1)
+        self.layout = "explicit" if fragments is not None else layout
+        table = layout_module.partition(self.cu_seqlens_global, self.world_size, layout, fragments)
+        self.plan = layout_module.rank_plan(self.cu_seqlens_global, table, self.rank, self.conv_kernel_size - 1)
+        self.fragments = self.plan.fragments
+        self.cu_seqlens_cpu = self.plan.cu_seqlens
+        self.num_tokens = self.cu_seqlens_cpu[-1]
+        lengths = [b - a for a, b in zip(self.cu_seqlens_global, self.cu_seqlens_global[1:])]
+        # of the slice as a whole: what the rank-to-rank hand-over of the contiguous layout looks at
+        self.continues_in = bool(self.fragments) and self.fragments[0].offset > 0
+        self.continues_out = bool(self.fragments) and self.fragments[-1].end < lengths[self.fragments[-1].doc]
+        self.cu_seqlens = torch.tensor(self.cu_seqlens_cpu, dtype=torch.int32, device=self.device)
+        self.fla_compatible = self.layout == "contiguous"  # a contiguous partition is FLA's
+        spans = self.plan.spans
+        self.halo = (spans[0].before, spans[-1].after) if spans else (0, 0)
 
-    def halo_exchange(self) -> _HaloExchange:
-        """The neighbour exchange of the layer's short convolutions."""
-        return _HaloExchange(self)
+    def halo_exchange(self):
+        """The neighbour exchange of the layer's short convolutions: point to point along the rank chain under the
+        contiguous layout, one small all-gather under the others."""
+        return _HaloExchange(self) if self.layout == "contiguous" else _GatherHalo(self)
 
     def exchange(self, mode: str = "auto"):
         """The boundary-state exchange of one call: ``"sequential"`` (rank to rank; the single-rank bits on aligned
-        boundaries), ``"parallel"`` (affine rank summaries, one all-gather; every rank works at once) or ``"auto"``
-        (parallel from three ranks on)."""
+        boundaries; contiguous layout only), ``"parallel"`` (affine fragment summaries, one all-gather; every rank
+        works at once) or ``"auto"`` (parallel from three ranks on and under every other layout)."""
         if mode not in ("auto", "sequential", "parallel"):
             raise ValueError(f"unknown exchange mode {mode!r}")
+        if self.layout != "contiguous" and self.world_size > 1:
+            if mode == "sequential":
+                raise NotImplementedError(
+                    f"the sequential hand-over follows the rank chain of the contiguous layout; the {self.layout} "
+                    "layout takes the parallel exchange")
+            return _ParallelExchange(self)
         if mode == "auto":
             mode = "parallel" if self.world_size > 2 else "sequential"
         if mode == "parallel" and self.world_size > 1:
@@ -341,7 +415,10 @@ def build_kcp_context(cu_seqlens_global, group=None, *, device=None, conv_kernel
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else "cpu"
     device = torch.device(device)
-    key = (boundaries, id(group), rank, world, str(device), conv_kernel_size, layout)
+    if layout not in LAYOUTS:
+        raise ValueError(f"build_kcp_context: layout must be one of {LAYOUTS}, not {layout!r}")
+    frozen = None if fragments is None else tuple(tuple(tuple(int(x) for x in f) for f in rank_) for rank_ in fragments)
+    key = (boundaries, id(group), rank, world, str(device), conv_kernel_size, layout, frozen)
     found = _CONTEXTS.get(key)
     if found is not None:
         _CONTEXTS.move_to_end(key)

@@ -80,9 +80,14 @@ def _halo_rank(rank, world, port, out_dir):
     ctx = KcpContext((0, 15, 20, 30), None, rank, world, "cpu")  # cuts at 10 (inside a document) and 20 (between two)
     rows = torch.arange(30 * 4, dtype=torch.float32).view(30, 4)[rank * 10:(rank + 1) * 10]
     exchange = ctx.halo_exchange()
-    prev, nxt = exchange.forward(rows[:3].clone(), rows[-3:].clone())
-    back = exchange.backward(-rows[:3].clone())
-    torch.save({"halo": ctx.halo, "prev": prev, "next": nxt, "back": back}, f"{out_dir}/rank{rank}.pt")
+    (prev,), (nxt,) = exchange.forward(rows[None, :3].clone(), rows[None, -3:].clone())  # one span per rank
+    (back,) = exchange.backward(-rows[None, :3].clone())
+    # the same rows through the all-gather exchange of the other layouts
+    from miles_ext_kernels_b200.cake._impl.gdn.kcp import _GatherHalo
+
+    (prev2,), (nxt2,) = _GatherHalo(ctx).forward(rows[None, :3].clone(), rows[None, -3:].clone())
+    same = all((a is None and b is None) or torch.equal(a, b) for a, b in ((prev, prev2), (nxt, nxt2)))
+    torch.save({"halo": ctx.halo, "prev": prev, "next": nxt, "back": back, "same": same}, f"{out_dir}/rank{rank}.pt")
     dist.barrier()
     dist.destroy_process_group()
 
@@ -99,7 +104,7 @@ def test_neighbours_exchange_rows_only_across_cut_documents(tmp_path):
     mp.spawn(_halo_rank, args=(3, port, str(tmp_path)), nprocs=3, join=True)
     full = torch.arange(30 * 4, dtype=torch.float32).view(30, 4)
     got = [torch.load(tmp_path / f"rank{r}.pt") for r in range(3)]
-    assert [g["halo"] for g in got] == [(0, 3), (3, 0), (0, 0)]
+    assert [g["halo"] for g in got] == [(0, 3), (3, 0), (0, 0)] and all(g["same"] for g in got)
     assert got[0]["prev"] is None and torch.equal(got[0]["next"], full[10:13])
     assert torch.equal(got[0]["back"], -full[10:13])
     assert torch.equal(got[1]["prev"], full[7:10]) and got[1]["next"] is None and got[1]["back"] is None
@@ -190,49 +195,69 @@ def test_one_document_without_boundaries_and_the_2d_form():
         causal_conv1d(x[..., :100], w[:100])
 
 
-class _CutContext:
-    """A rank's context whose neighbour exchange reads the undivided tensors (ranks emulated one after another on one
-    GPU): what the context-parallel entry points read of a ``KcpContext``."""
+def _cut_context(cu, rank, world, full_xs, full_dys, layout="contiguous"):
+    """A rank's ``KcpContext`` whose neighbour exchange reads the undivided tensors (ranks emulated one after another
+    on one GPU)."""
+    from miles_ext_kernels_b200.cake._impl.gdn.kcp import KcpContext
 
-    def __init__(self, cu, rank, world, full_xs, full_dys):
-        from miles_ext_kernels_b200.cake._impl.gdn.kcp import halo_rows, local_partition
+    class Cut(KcpContext):
+        exchanges = 0
 
-        self.rank, self.world_size = rank, world
-        self.cu_seqlens_cpu, self.continues_in, self.continues_out = local_partition(cu, rank, world)
-        self.num_tokens = self.cu_seqlens_cpu[-1]
-        self.halo = halo_rows(cu, rank, world, 3)
-        self.lo = rank * self.num_tokens
-        self.full_xs, self.full_dys = full_xs, full_dys
-        self.exchanges = 0
+        def rows(self, tensors, doc, at):
+            """Rows ``at .. at + 3`` of document ``doc`` (zeros outside the batch)."""
+            lo = cu[doc] + at
+            out = torch.zeros(3, sum(t.shape[1] for t in tensors), dtype=tensors[0].dtype, device=tensors[0].device)
+            a, b = max(lo, 0), min(lo + 3, tensors[0].shape[0])
+            if b > a:
+                out[a - lo : b - lo] = torch.cat([t[a:b] for t in tensors], dim=1)
+            return out
 
-    def _rows(self, tensors, start):
-        return torch.cat([t[start:start + 3] for t in tensors], dim=1)
+        def halo_exchange(self):
+            ctx = self
 
-    def halo_exchange(self):
-        ctx = self
+            class Loopback:
+                def forward(self, first, last):
+                    ctx.exchanges += 1
+                    heads = [ctx.fragments[sp.first] for sp in ctx.plan.spans]
+                    tails = [ctx.fragments[sp.last] for sp in ctx.plan.spans]
+                    for i, (h, t) in enumerate(zip(heads, tails)):
+                        assert torch.equal(first[i], ctx.rows(full_xs, h.doc, h.offset))
+                        assert torch.equal(last[i], ctx.rows(full_xs, t.doc, t.end - 3))
+                    prev = [None if sp.prev is None else ctx.rows(full_xs, h.doc, h.offset - 3)
+                            for sp, h in zip(ctx.plan.spans, heads)]
+                    nxt = [None if sp.next is None else ctx.rows(full_xs, t.doc, t.end)
+                           for sp, t in zip(ctx.plan.spans, tails)]
+                    return prev, nxt
 
-        class Loopback:
-            def forward(self, first, last):
-                ctx.exchanges += 1
-                assert torch.equal(first, ctx._rows(ctx.full_xs, ctx.lo))
-                assert torch.equal(last, ctx._rows(ctx.full_xs, ctx.lo + ctx.num_tokens - 3))
-                prev = ctx._rows(ctx.full_xs, ctx.lo - 3) if ctx.continues_in else None
-                nxt = ctx._rows(ctx.full_xs, ctx.lo + ctx.num_tokens) if ctx.continues_out else None
-                return prev, nxt
+                def backward(self, first):
+                    tails = [ctx.fragments[sp.last] for sp in ctx.plan.spans]
+                    return [None if sp.next is None else ctx.rows(full_dys, t.doc, t.end)
+                            for sp, t in zip(ctx.plan.spans, tails)]
 
-            def backward(self, first):
-                assert torch.equal(first, ctx._rows(ctx.full_dys, ctx.lo))
-                return ctx._rows(ctx.full_dys, ctx.lo + ctx.num_tokens) if ctx.continues_out else None
+            return Loopback()
 
-        return Loopback()
+        def take(self, full):
+            """This rank's tokens of an undivided ``[S, ...]`` tensor, in local order."""
+            return torch.cat([full[cu[f.doc] + f.offset : cu[f.doc] + f.end] for f in self.fragments])
+
+        def scatter(self, full, local):
+            at = 0
+            for f in self.fragments:
+                full[cu[f.doc] + f.offset : cu[f.doc] + f.end] = local[at : at + f.length]
+                at += f.length
+
+    return Cut(cu, None, rank, world, "cuda", layout=layout)
 
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("policy", ["bf16", "fp32"])
-@pytest.mark.parametrize("world,lens", [(2, (300, 724)), (4, (1, 2, 253, 1, 2, 509, 256)), (4, (1024,)),
-                                        (8, (130, 126, 2, 766))])
-def test_the_cut_route_gives_the_bits_of_the_undivided_call(world, lens, policy):
-    """y and dx of every rank's slice are the undivided call's; the ranks' weight-gradient partials add up to its
+@pytest.mark.parametrize("world,lens,layout", [
+    (2, (300, 724), "contiguous"), (4, (1, 2, 253, 1, 2, 509, 256), "contiguous"), (4, (1024,), "contiguous"),
+    (8, (130, 126, 2, 766), "contiguous"), (2, (300, 724), "zigzag"), (4, (1, 2, 253, 1, 2, 509, 256), "zigzag"),
+    (4, (1024,), "zigzag"), (2, (256, 64, 704), "zigzag_per_document"), (4, (512, 512), "zigzag_per_document"),
+])
+def test_the_cut_route_gives_the_bits_of_the_undivided_call(world, lens, layout, policy):
+    """y and dx of every rank's tokens are the undivided call's; the ranks' weight-gradient partials add up to its
     weight gradient within the gate; two tensors through one exchange equal two calls."""
     import miles_ext_kernels_b200 as package
     from miles_ext_kernels_b200.cake.conv1d import causal_conv1d_kcp, causal_conv1d_kcp_multi
@@ -244,29 +269,30 @@ def test_the_cut_route_gives_the_bits_of_the_undivided_call(world, lens, policy)
     try:
         want, want2 = run(x, w, cu, dy, policy), run(x2, w2, cu, dy2, policy)
         cu_host = tuple(cu.tolist())
-        ys, dxs, dws, ys2, dxs2 = [], [], [], [], []
+        got = {n: torch.zeros_like(x[0]) for n in ("y", "dx")} | {n: torch.zeros_like(x2[0]) for n in ("y2", "dx2")}
+        dws = []
         for rank in range(world):
-            ctx = _CutContext(cu_host, rank, world, [x[0], x2[0]], [dy[0], dy2[0]])
-            sl = slice(ctx.lo, ctx.lo + ctx.num_tokens)
-            xa, xb = x[0, sl].clone().requires_grad_(True), x2[0, sl].clone().requires_grad_(True)
+            ctx = _cut_context(cu_host, rank, world, [x[0], x2[0]], [dy[0], dy2[0]], layout)
+            xa, xb = ctx.take(x[0]).requires_grad_(True), ctx.take(x2[0]).requires_grad_(True)
             wa, wb = w.clone().requires_grad_(True), w2.clone().requires_grad_(True)
             ya, yb = causal_conv1d_kcp_multi([xa, xb], [wa, wb], ctx)
-            torch.autograd.backward([ya, yb], [dy[0, sl], dy2[0, sl]])
+            torch.autograd.backward([ya, yb], [ctx.take(dy[0]), ctx.take(dy2[0])])
             assert ctx.exchanges == 1 and wb.grad.dtype == torch.bfloat16
-            ys.append(ya.detach()), dxs.append(xa.grad), dws.append(wa.grad.double())
-            ys2.append(yb.detach()), dxs2.append(xb.grad)
+            for name, local in (("y", ya.detach()), ("dx", xa.grad), ("y2", yb.detach()), ("dx2", xb.grad)):
+                ctx.scatter(got[name], local)
+            dws.append(wa.grad.double())
             # one tensor on its own: the same bits, and a recompute handle skips the second exchange
             class Handle:
                 entries = {}
-            single = _CutContext(cu_host, rank, world, [x[0]], [dy[0]])
-            xs_ = x[0, sl].clone().requires_grad_(True)
+            single = _cut_context(cu_host, rank, world, [x[0]], [dy[0]], layout)
+            xs_ = single.take(x[0]).requires_grad_(True)
             y1 = causal_conv1d_kcp(xs_, w, single, recompute_handle=Handle)
-            y1.backward(dy[0, sl])
+            y1.backward(single.take(dy[0]))
             assert torch.equal(y1, ya) and torch.equal(xs_.grad, xa.grad)
-            again = causal_conv1d_kcp(x[0, sl], w, single, recompute_handle=Handle)
+            again = causal_conv1d_kcp(single.take(x[0]), w, single, recompute_handle=Handle)
             assert single.exchanges == 1 and torch.equal(again, ya)
-        assert torch.equal(torch.cat(ys), want["y"][0]) and torch.equal(torch.cat(dxs), want["dx"][0])
-        assert torch.equal(torch.cat(ys2), want2["y"][0]) and torch.equal(torch.cat(dxs2), want2["dx"][0])
+        assert torch.equal(got["y"], want["y"][0]) and torch.equal(got["dx"], want["dx"][0])
+        assert torch.equal(got["y2"], want2["y"][0]) and torch.equal(got["dx2"], want2["dx"][0])
         atol, rtol = (DW_ATOL, DW_RTOL) if policy == "bf16" else (DW_FP32G_ATOL, DW_FP32G_RTOL)
         assert C.outside(sum(dws).float().cpu(), want["dw"].double().cpu(), atol=atol, rtol=rtol) == 0
     finally:

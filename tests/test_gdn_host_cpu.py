@@ -97,8 +97,8 @@ def test_contiguous_partition_is_flas():
             assert ctx.fla_compatible and ctx.layout == "contiguous"
     with pytest.raises(ValueError, match="divide by the world size"):
         kcp.KcpContext((0, 10), None, 0, 3, "cpu")
-    with pytest.raises(NotImplementedError):
-        kcp.KcpContext(cu, None, 0, 2, "cpu", layout="zigzag")
+    zig = kcp.KcpContext(cu, None, 0, 2, "cpu", layout="zigzag")  # pieces 0 and 3 of four
+    assert zig.cu_seqlens_cpu == (0, 128, 204, 256) and not zig.fla_compatible
 
 
 def test_document_runs_across_ranks():

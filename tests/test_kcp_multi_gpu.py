@@ -30,6 +30,12 @@ CASES = {
     "4-long-parallel-weak": (4, (6000, 2192), "parallel", "weak"),
     "4-long-parallel-strong": (4, (6000, 2192), "parallel", "strong"),
     "4-long-sequential": (4, (6016, 2176), "sequential", "weak"),
+    # the load-balanced layouts: rank r holds pieces r and 2 W - 1 - r (of the batch / of every document); a rank
+    # publishes up to two summaries per direction and folds chains that pass through its own other piece
+    "2-zigzag": (2, (3000, 1096), "auto", "weak", "zigzag"),
+    "4-zigzag": (4, (6000, 2192), "auto", "weak", "zigzag"),
+    "4-zigzag-strong-gate": (4, (6000, 2192), "auto", "strong", "zigzag"),
+    "2-zigzag-per-document": (2, (3072, 1024), "auto", "weak", "zigzag_per_document"),
 }
 HEADS = (2, 4)
 
@@ -40,7 +46,13 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, out_dir: str, seq_lens, exchange: str, gate: str) -> None:
+def _take(full: torch.Tensor, cu, fragments) -> torch.Tensor:
+    """A rank's tokens of an undivided ``[S, ...]`` tensor, in local order."""
+    return torch.cat([full[cu[f.doc] + f.offset : cu[f.doc] + f.end] for f in fragments])
+
+
+def _worker(rank: int, world: int, port: int, out_dir: str, seq_lens, exchange: str, gate: str,
+            layout: str = "contiguous") -> None:
     import torch.distributed as dist
 
     import miles_ext_kernels_b200 as package
@@ -54,17 +66,17 @@ def _worker(rank: int, world: int, port: int, out_dir: str, seq_lens, exchange: 
     package.configure(cake_gdn_kcp_exchange=exchange)
     x = draw(seq_lens, HEADS, seed=9, gate=gate)
     cu = (0, seq_lens[0], sum(seq_lens))
-    ctx = gdn.build_kcp_context(cu, device=dev)
-    lo = rank * ctx.num_tokens
-    sl = slice(lo, lo + ctx.num_tokens)
-    leaves = {n: x[n][sl].unsqueeze(0).to(dev).requires_grad_(True) for n in ("q", "k", "v", "g")}
-    beta = x["beta"][sl].unsqueeze(0).to(dev).bfloat16().requires_grad_(True)
+    ctx = gdn.build_kcp_context(cu, device=dev, layout=layout)
+    mine = lambda t: _take(t, cu, ctx.fragments).unsqueeze(0).to(dev)  # noqa: E731
+    leaves = {n: mine(x[n]).requires_grad_(True) for n in ("q", "k", "v", "g")}
+    beta = mine(x["beta"]).bfloat16().requires_grad_(True)
     o = gdn.kcp_chunk_gated_delta_rule(leaves["q"], leaves["k"], leaves["v"], leaves["g"], beta, ctx,
                                        use_qk_l2norm_in_kernel=True)
-    o.backward(x["do"][sl].unsqueeze(0).to(dev))
+    o.backward(mine(x["do"]))
     torch.cuda.synchronize()
     torch.save({"o": o.detach().cpu()[0], **{f"d{n}": t.grad.cpu()[0] for n, t in leaves.items()},
-                "dbeta": beta.grad.cpu()[0]}, f"{out_dir}/rank{rank}.pt")
+                "dbeta": beta.grad.cpu()[0], "fragments": [(f.doc, f.offset, f.length) for f in ctx.fragments]},
+               f"{out_dir}/rank{rank}.pt")
     dist.barrier()
     dist.destroy_process_group()
 
@@ -76,10 +88,12 @@ def test_ranks_against_one_gpu(tmp_path, case):
     from miles_ext_kernels_b200.cake import gdn
     from oracle import gdn_oracle as O
 
-    world, seq_lens, exchange, gate = CASES[case]
+    world, seq_lens, exchange, gate, *rest = CASES[case]
+    layout = rest[0] if rest else "contiguous"
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), seq_lens, exchange, gate), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), seq_lens, exchange, gate, layout), nprocs=world,
+             join=True)
     dev = torch.device("cuda", 0)
     x = draw(seq_lens, HEADS, seed=9, gate=gate)
     cu = (0, seq_lens[0], sum(seq_lens))
@@ -94,7 +108,12 @@ def test_ranks_against_one_gpu(tmp_path, case):
             "dbeta": beta.grad.cpu()[0]}
     parts = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
     for name, ref in want.items():
-        got = torch.cat([p[name] for p in parts], 0)
+        got = torch.zeros_like(ref)  # every rank's tokens back at their places in the batch
+        for part in parts:
+            at = 0
+            for doc, offset, length in part["fragments"]:
+                got[cu[doc] + offset : cu[doc] + offset + length] = part[name][at : at + length]
+                at += length
         if case == "2-aligned-sequential":
             # the same chunks in the same order with the exact fp32 state at the boundary: the same bits
             assert torch.equal(got, ref), name
@@ -103,7 +122,7 @@ def test_ranks_against_one_gpu(tmp_path, case):
             assert ok, (name, m)
 
 
-def _conv_worker(rank: int, world: int, port: int, out_dir: str, lens, channels) -> None:
+def _conv_worker(rank: int, world: int, port: int, out_dir: str, lens, channels, layout) -> None:
     import torch.distributed as dist
 
     from miles_ext_kernels_b200.cake import gdn
@@ -115,15 +134,15 @@ def _conv_worker(rank: int, world: int, port: int, out_dir: str, lens, channels)
     dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120),
                             device_id=dev)
     cu = (0, *torch.tensor(lens).cumsum(0).tolist())
-    ctx = gdn.build_kcp_context(cu, device=dev)
-    sl = slice(rank * ctx.num_tokens, (rank + 1) * ctx.num_tokens)
+    ctx = gdn.build_kcp_context(cu, device=dev, layout=layout)
+    mine = lambda t: _take(t, cu, ctx.fragments).to(dev)  # noqa: E731
     full = _conv_inputs(sum(lens), channels)
-    xs = [full[f"x{i}"][sl].to(dev).requires_grad_(True) for i in range(len(channels))]
+    xs = [mine(full[f"x{i}"]).requires_grad_(True) for i in range(len(channels))]
     ws = [full[f"w{i}"].to(dev).requires_grad_(True) for i in range(len(channels))]
     ys = causal_conv1d_kcp_multi(xs, ws, ctx)
-    torch.autograd.backward(list(ys), [full[f"dy{i}"][sl].to(dev) for i in range(len(channels))])
+    torch.autograd.backward(list(ys), [mine(full[f"dy{i}"]) for i in range(len(channels))])
     torch.cuda.synchronize()
-    out = {}
+    out = {"fragments": [(f.doc, f.offset, f.length) for f in ctx.fragments]}
     for i in range(len(channels)):
         out.update({f"y{i}": ys[i].detach().cpu(), f"dx{i}": xs[i].grad.cpu(), f"dw{i}": ws[i].grad.cpu()})
     torch.save(out, f"{out_dir}/rank{rank}.pt")
@@ -141,8 +160,10 @@ def _conv_inputs(S, channels):
     return out
 
 
-@pytest.mark.parametrize("world,lens", [(2, (300, 724)), (4, (1, 2, 253, 1, 2, 509, 256))])
-def test_short_convolution_across_ranks(tmp_path, world, lens):
+@pytest.mark.parametrize("world,lens,layout", [(2, (300, 724), "contiguous"),
+                                               (4, (1, 2, 253, 1, 2, 509, 256), "contiguous"),
+                                               (2, (300, 724), "zigzag"), (4, (1, 2, 253, 1, 2, 509, 256), "zigzag")])
+def test_short_convolution_across_ranks(tmp_path, world, lens, layout):
     """The three rows across each cut travel between neighbours (one message per direction for the layer's
     tensors): y and dx are the bits of one GPU's call, the ranks' weight-gradient partials add up to its sum."""
     import torch.multiprocessing as mp
@@ -152,16 +173,27 @@ def test_short_convolution_across_ranks(tmp_path, world, lens):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     channels = (384, 136)
-    mp.spawn(_conv_worker, args=(world, _free_port(), str(tmp_path), lens, channels), nprocs=world, join=True)
+    mp.spawn(_conv_worker, args=(world, _free_port(), str(tmp_path), lens, channels, layout), nprocs=world, join=True)
     dev = torch.device("cuda", 0)
     full = _conv_inputs(sum(lens), channels)
-    cu = torch.tensor((0, *torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32, device=dev)
+    cu_host = (0, *torch.tensor(lens).cumsum(0).tolist())
+    cu = torch.tensor(cu_host, dtype=torch.int32, device=dev)
     parts = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+
+    def whole(name, like):
+        out = torch.zeros_like(like)
+        for part in parts:
+            at = 0
+            for doc, offset, length in part["fragments"]:
+                out[cu_host[doc] + offset : cu_host[doc] + offset + length] = part[name][at : at + length]
+                at += length
+        return out
+
     for i in range(len(channels)):
         x, w = full[f"x{i}"].to(dev).requires_grad_(True), full[f"w{i}"].to(dev).requires_grad_(True)
         y = causal_conv1d(x, w, cu)
         y.backward(full[f"dy{i}"].to(dev))
-        assert torch.equal(torch.cat([p[f"y{i}"] for p in parts]), y.detach().cpu())
-        assert torch.equal(torch.cat([p[f"dx{i}"] for p in parts]), x.grad.cpu())
+        assert torch.equal(whole(f"y{i}", y.detach().cpu()), y.detach().cpu())
+        assert torch.equal(whole(f"dx{i}", x.grad.cpu()), x.grad.cpu())
         dw = sum(p[f"dw{i}"].double() for p in parts)
         assert torch.allclose(dw, w.grad.double().cpu(), atol=5e-2, rtol=1e-4)
