@@ -7,8 +7,10 @@ miles_ext_kernels/cake/_impl/gdn/ops.py:2420-2501).  A call runs, by its ``cp_co
 
 - no ``cp_context``: the single-GPU kernels (forward: prep, WY transform, state scan, output; backward: adjoint scan
   and the fused gradient tail);
-- a :class:`KcpContext` (:func:`build_kcp_context`): this rank's contiguous slice of every sequence, with the chunk
-  state passed rank to rank (:func:`kcp_chunk_gated_delta_rule` calls it directly).
+- a :class:`KcpContext` (:func:`build_kcp_context`; layouts ``contiguous``, ``zigzag``, ``zigzag_per_document`` or an
+  explicit fragment table): this rank's fragments of the packed batch, with the chunk state crossing the cuts -- rank
+  to rank, or as affine fragment summaries that one all-gather shares (:func:`kcp_chunk_gated_delta_rule` calls it
+  directly).
 
 :func:`packed_qkv_views` splits one packed row ``[.., (2 H + HV) * 128]`` into q, k, v views that the op reads in place
 and whose gradients come back as one packed row (no copies on either side; not among the reference's exports of
