@@ -52,10 +52,10 @@ __device__ __forceinline__ void store8f(__nv_bfloat16* p, const float* v) {
       make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
 }
 // w [C, 4] (fp32 or bf16) -> taps[k][j] of this lane's 8 channels
-template <typename W>
-__device__ __forceinline__ void load_taps(const W* w, int c0, float taps[kConvTaps][8]) {
+template <typename W, int CH = 8>
+__device__ __forceinline__ void load_taps(const W* w, int c0, float taps[kConvTaps][CH]) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
+  for (int j = 0; j < CH; ++j)
 #pragma unroll
     for (int k = 0; k < kConvTaps; ++k) taps[k][j] = float(w[(c0 + j) * kConvTaps + k]);
 }
@@ -148,21 +148,50 @@ __global__ void __launch_bounds__(256, 2) conv1d_fwd_kernel(const __nv_bfloat16*
   }
 }
 
+// A thread's CH channels of one token: 16 bytes (CH = 8) or 8 bytes (CH = 4; half the registers per thread, so that
+// two blocks fit an SM)
+template <int CH>
+struct ConvRow;
+template <>
+struct ConvRow<8> {
+  typedef uint4 type;
+  static __device__ __forceinline__ type load(const __nv_bfloat16* base, int64_t t, int channels, int c0) {
+    return __ldg(reinterpret_cast<const uint4*>(base + t * channels + c0));
+  }
+  static __device__ __forceinline__ void unpack(type raw, float* v) { unpack8(raw, v); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) { store8f(p, v); }
+};
+template <>
+struct ConvRow<4> {
+  typedef uint2 type;
+  static __device__ __forceinline__ type load(const __nv_bfloat16* base, int64_t t, int channels, int c0) {
+    return __ldg(reinterpret_cast<const uint2*>(base + t * channels + c0));
+  }
+  static __device__ __forceinline__ void unpack(type raw, float* v) {
+    const float2 a = unpack_bf16(raw.x), b = unpack_bf16(raw.y);
+    v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+  }
+};
+
 // One step of the backward sweep: dpre of token u (needs x[u - 3 .. u]) and dx of token t = u - 3 (needs
 // dpre[t .. t + 3]).  kEdge = false: u and t are the run's own tokens with three neighbours inside their documents on
 // the side that matters, so nothing is selected or skipped.
-template <bool kEdge, bool kRoundPre, typename Sum>
-__device__ __forceinline__ void conv_bwd_token(const float (&taps)[kConvTaps][8], float (&xw)[3][8], float (&dp)[3][8],
-                                               Sum (&sum)[kConvTaps][8], uint4 raw_x, uint4 raw_g, int before,
+template <bool kEdge, bool kRoundPre, int CH, typename Sum>
+__device__ __forceinline__ void conv_bwd_token(const float (&taps)[kConvTaps][CH], float (&xw)[3][CH], float (&dp)[3][CH],
+                                               Sum (&sum)[kConvTaps][CH], typename ConvRow<CH>::type raw_x,
+                                               typename ConvRow<CH>::type raw_g, int before,
                                                int after, bool has_u, bool own_u, bool write_t,
                                                __nv_bfloat16* dx_row) {
-  float cur[8], d[8];
+  float cur[CH], d[CH];
   if (!kEdge || has_u) {
-    float g[8];
-    unpack8(raw_x, cur);
-    unpack8(raw_g, g);
+    float g[CH];
+    ConvRow<CH>::unpack(raw_x, cur);
+    ConvRow<CH>::unpack(raw_g, g);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < CH; ++j) {
       const float x1 = !kEdge || before >= 1 ? xw[2][j] : 0.f, x2 = !kEdge || before >= 2 ? xw[1][j] : 0.f;
       const float x3 = !kEdge || before >= 3 ? xw[0][j] : 0.f;
       const float pre = preactivation(taps[0][j], x3, taps[1][j], x2, taps[2][j], x1, taps[3][j], cur[j]);
@@ -178,22 +207,22 @@ __device__ __forceinline__ void conv_bwd_token(const float (&taps)[kConvTaps][8]
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) cur[j] = 0.f, d[j] = 0.f;
+    for (int j = 0; j < CH; ++j) cur[j] = 0.f, d[j] = 0.f;
   }
   if (!kEdge || write_t) {
-    float out[8];
+    float out[CH];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < CH; ++j) {
       float v = taps[3][j] * dp[0][j];
       v = fmaf(taps[2][j], !kEdge || after >= 1 ? dp[1][j] : 0.f, v);
       v = fmaf(taps[1][j], !kEdge || after >= 2 ? dp[2][j] : 0.f, v);
       v = fmaf(taps[0][j], !kEdge || after >= 3 ? d[j] : 0.f, v);
       out[j] = v;
     }
-    store8f(dx_row, out);
+    ConvRow<CH>::store(dx_row, out);
   }
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < CH; ++j) {
     xw[0][j] = xw[1][j], xw[1][j] = xw[2][j], xw[2][j] = cur[j];
     dp[0][j] = dp[1][j], dp[1][j] = dp[2][j], dp[2][j] = d[j];
   }
@@ -202,8 +231,8 @@ __device__ __forceinline__ void conv_bwd_token(const float (&taps)[kConvTaps][8]
 // One sweep over tokens [t0 ... t1 + 3) in batches of four, the next batch's loads issued before the current batch's
 // arithmetic.  The weight gradient's products are summed in FP32 inside a batch when Acc is FP64 (four terms), and the
 // batch sums in Acc.
-template <typename W, typename Acc, bool kRoundPre>
-__global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+template <typename W, typename Acc, bool kRoundPre, int CH>
+__global__ void __launch_bounds__(256, CH == 4 ? 2 : 1) conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ x,
                                                          const __nv_bfloat16* __restrict__ x_prev,
                                                          const __nv_bfloat16* __restrict__ x_next,
                                                          const W* __restrict__ w, const __nv_bfloat16* __restrict__ dy,
@@ -213,36 +242,36 @@ __global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __
                                                          int tokens, int channels, int run_len) {
   constexpr bool kBatchSums = !std::is_same<Acc, float>::value;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int c0 = (blockIdx.y * 8 + warp) * 256 + lane * 8;
+  const int c0 = (blockIdx.y * 8 + warp) * (32 * CH) + lane * CH;
   if (c0 >= channels) return;
   const int t0 = blockIdx.x * run_len, t1 = min(t0 + run_len, tokens);
   if (t0 >= t1) return;
-  float taps[kConvTaps][8];
-  load_taps(w, c0, taps);
-  Acc acc[kConvTaps][8];
+  float taps[kConvTaps][CH];
+  load_taps<W, CH>(w, c0, taps);
+  Acc acc[kConvTaps][CH];
 #pragma unroll
   for (int k = 0; k < kConvTaps; ++k)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[k][j] = Acc(0);
-  float xw[3][8];   // x[u - 3], x[u - 2], x[u - 1]
-  float dp[3][8];   // dpre[u - 3], dpre[u - 2], dpre[u - 1]
+    for (int j = 0; j < CH; ++j) acc[k][j] = Acc(0);
+  float xw[3][CH];   // x[u - 3], x[u - 2], x[u - 1]
+  float dp[3][CH];   // dpre[u - 3], dpre[u - 2], dpre[u - 1]
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
     const int t = t0 - 3 + i;
-    if (t >= 0) load8f(x + int64_t(t) * channels + c0, xw[i]);
-    else if (x_prev != nullptr) load8f(x_prev + int64_t(t + 3) * channels + c0, xw[i]);
+    if (t >= 0) ConvRow<CH>::unpack(ConvRow<CH>::load(x, t, channels, c0), xw[i]);
+    else if (x_prev != nullptr) ConvRow<CH>::unpack(ConvRow<CH>::load(x_prev, t + 3, channels, c0), xw[i]);
     else
 #pragma unroll
-      for (int j = 0; j < 8; ++j) xw[i][j] = 0.f;
+      for (int j = 0; j < CH; ++j) xw[i][j] = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dp[i][j] = 0.f;  // dpre before t0 is never used: dx starts at t0
+    for (int j = 0; j < CH; ++j) dp[i][j] = 0.f;  // dpre before t0 is never used: dx starts at t0
   }
   // rows after the last token come from the continuation rows (x_next, dy_next: 3 rows each), when there are any
   const int u_end = x_next != nullptr ? t1 + 3 : min(t1 + 3, tokens);
   auto row_of = [&](const __nv_bfloat16* here, const __nv_bfloat16* after, int u) {
-    return u < tokens ? load_row(here, u, channels, c0) : load_row(after, u - tokens, channels, c0);
+    return u < tokens ? ConvRow<CH>::load(here, u, channels, c0) : ConvRow<CH>::load(after, u - tokens, channels, c0);
   };
-  uint4 raw_x[4], raw_g[4], next_x[4], next_g[4];
+  typename ConvRow<CH>::type raw_x[4], raw_g[4], next_x[4], next_g[4];
   int reach_u[4], reach_t[4], next_u[4], next_t[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -268,22 +297,22 @@ __global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __
     const int all_t = reach_t[0] & reach_t[1] & reach_t[2] & reach_t[3];
     const bool inner = ub - 3 >= t0 && ub + 3 < t1 && (all_u & 3) == 3 && (all_t >> 2 & 3) == 3;
     if (kBatchSums) {
-      float part[kConvTaps][8];
+      float part[kConvTaps][CH];
 #pragma unroll
       for (int k = 0; k < kConvTaps; ++k)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) part[k][j] = 0.f;
+        for (int j = 0; j < CH; ++j) part[k][j] = 0.f;
       if (inner) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          conv_bwd_token<false, kRoundPre>(taps, xw, dp, part, raw_x[i], raw_g[i], 3, 3, true, true, true,
+          conv_bwd_token<false, kRoundPre, CH>(taps, xw, dp, part, raw_x[i], raw_g[i], 3, 3, true, true, true,
                                            dx_row + int64_t(i) * channels);
       } else {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int u = ub + i;
           if (u < t1 + 3)
-            conv_bwd_token<true, kRoundPre>(taps, xw, dp, part, raw_x[i], raw_g[i], reach_u[i] & 3,
+            conv_bwd_token<true, kRoundPre, CH>(taps, xw, dp, part, raw_x[i], raw_g[i], reach_u[i] & 3,
                                             (reach_t[i] >> 2) & 3, u < u_end, u < t1, u - 3 >= t0,
                                             dx_row + int64_t(i) * channels);
         }
@@ -291,20 +320,20 @@ __global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __
 #pragma unroll
       for (int k = 0; k < kConvTaps; ++k)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[k][j] += Acc(part[k][j]);
+        for (int j = 0; j < CH; ++j) acc[k][j] += Acc(part[k][j]);
     } else {
-      auto& sum = reinterpret_cast<float(&)[kConvTaps][8]>(acc);
+      auto& sum = reinterpret_cast<float(&)[kConvTaps][CH]>(acc);
       if (inner) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          conv_bwd_token<false, kRoundPre>(taps, xw, dp, sum, raw_x[i], raw_g[i], 3, 3, true, true, true,
+          conv_bwd_token<false, kRoundPre, CH>(taps, xw, dp, sum, raw_x[i], raw_g[i], 3, 3, true, true, true,
                                            dx_row + int64_t(i) * channels);
       } else {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int u = ub + i;
           if (u < t1 + 3)
-            conv_bwd_token<true, kRoundPre>(taps, xw, dp, sum, raw_x[i], raw_g[i], reach_u[i] & 3,
+            conv_bwd_token<true, kRoundPre, CH>(taps, xw, dp, sum, raw_x[i], raw_g[i], reach_u[i] & 3,
                                             (reach_t[i] >> 2) & 3, u < u_end, u < t1, u - 3 >= t0,
                                             dx_row + int64_t(i) * channels);
         }
@@ -317,7 +346,7 @@ __global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __
   if (dw_partial != nullptr) {
     Acc* out = dw_partial + (int64_t(blockIdx.x) * channels + c0) * kConvTaps;
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < CH; ++j)
 #pragma unroll
       for (int k = 0; k < kConvTaps; ++k) out[j * kConvTaps + k] = acc[k][j];
   }
@@ -401,7 +430,8 @@ int mek_conv1d_bwd(const void* x, const void* x_prev, const void* x_next, const 
     return fail(MEK_ERR_INVALID, "conv1d_bwd: the continuation rows of x and of dy go together");
   if (int rc = check_conv("conv1d_bwd", tokens, channels, 1)) return rc;
   const ConvPlan plan = conv_plan(tokens);
-  const dim3 grid(plan.runs, (channels + 2047) / 2048);
+  constexpr int kBwdCh = 4;  // channels per thread of the backward kernel
+  const dim3 grid(plan.runs, (channels + 256 * kBwdCh - 1) / (256 * kBwdCh));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   const __nv_bfloat16* gp = static_cast<const __nv_bfloat16*>(dy);
@@ -412,7 +442,7 @@ int mek_conv1d_bwd(const void* x, const void* x_prev, const void* x_next, const 
   const int64_t entries = int64_t(channels) * kConvTaps;
   const unsigned sum_grid = unsigned((entries + 255) / 256);
 #define MEK_CONV_BWD(WT, ACC, ROUND)                                                                                 \
-  conv1d_bwd_kernel<WT, ACC, ROUND><<<grid, 256, 0, s>>>(xp, xprev, xnext, static_cast<const WT*>(weight), gp, gnext, \
+  conv1d_bwd_kernel<WT, ACC, ROUND, kBwdCh><<<grid, 256, 0, s>>>(xp, xprev, xnext, static_cast<const WT*>(weight), gp, gnext, \
                                                          reach, dxp, static_cast<ACC*>(dw_partial), tokens, channels, \
                                                          plan.run_len);                                              \
   if (int rc = launched("conv1d_bwd")) return rc;                                                                    \

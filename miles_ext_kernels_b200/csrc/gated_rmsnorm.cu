@@ -59,9 +59,9 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_fwd_kernel(RowView x, RowVi
     float ss = 0.f, out[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) ss = fmaf(xv[i][j], xv[i][j], ss);
-    const float rstd = 1.0f / sqrtf(half_warp_sum(ss) * (1.0f / 128.0f) + eps);
+    const float rstd = rsqrtf(half_warp_sum(ss) * (1.0f / 128.0f) + eps);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) out[j] = ((xv[i][j] * rstd) * wv[j]) * (zv[i][j] / (1.0f + __expf(-zv[i][j])));
+    for (int j = 0; j < 8; ++j) out[j] = ((xv[i][j] * rstd) * wv[j]) * __fdividef(zv[i][j], 1.0f + __expf(-zv[i][j]));
     if (r0 + i < rows) store8(y + (r0 + i) * 128, l16, out);
   }
 }
@@ -94,11 +94,11 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_bwd_kernel(const __nv_bfloa
       float ss = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss = fmaf(xv[i][j], xv[i][j], ss);
-      const float rstd = 1.0f / sqrtf(half_warp_sum(ss) * (1.0f / 128.0f) + eps);
+      const float rstd = rsqrtf(half_warp_sum(ss) * (1.0f / 128.0f) + eps);
       float dot = 0.f, dn[8], dzv[8], dxv[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float s = 1.0f / (1.0f + __expf(-zv[i][j]));
+        const float s = __fdividef(1.0f, 1.0f + __expf(-zv[i][j]));
         const float a = gv[i][j] * (zv[i][j] * s);
         const float n = xv[i][j] * rstd;
         dn[j] = a * wv[j];
