@@ -75,79 +75,6 @@ __device__ __forceinline__ uint4 load_row(const __nv_bfloat16* base, int64_t t, 
   return __ldg(reinterpret_cast<const uint4*>(base + t * channels + c0));
 }
 
-// One token of the forward sweep.  kEdge = false: the token has three earlier tokens in its document (no selects).
-template <bool kEdge>
-__device__ __forceinline__ void conv_fwd_token(const float (&taps)[kConvTaps][8], float (&win)[3][8], uint4 raw,
-                                               int before, __nv_bfloat16* y_row) {
-  float cur[8], out[8];
-  unpack8(raw, cur);
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float x1 = !kEdge || before >= 1 ? win[2][j] : 0.f, x2 = !kEdge || before >= 2 ? win[1][j] : 0.f;
-    const float x3 = !kEdge || before >= 3 ? win[0][j] : 0.f;
-    const float pre = preactivation(taps[0][j], x3, taps[1][j], x2, taps[2][j], x1, taps[3][j], cur[j]);
-    out[j] = __fdividef(pre, 1.0f + __expf(-pre));
-    win[0][j] = win[1][j], win[1][j] = win[2][j], win[2][j] = cur[j];
-  }
-  store8f(y_row, out);
-}
-
-// grid (runs, channel groups of 8 warps x 256); a warp owns tokens [run * run_len, + run_len) of 256 channels.  Tokens
-// go in batches of four; the next batch's loads are issued before the current batch's arithmetic.
-template <typename W>
-__global__ void __launch_bounds__(256, 2) conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x,
-                                                            const __nv_bfloat16* __restrict__ x_prev,
-                                                            const W* __restrict__ w, const uint8_t* __restrict__ reach,
-                                                            __nv_bfloat16* __restrict__ y, int tokens, int channels,
-                                                            int run_len) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int c0 = (blockIdx.y * 8 + warp) * 256 + lane * 8;
-  if (c0 >= channels) return;
-  const int t0 = blockIdx.x * run_len, t1 = min(t0 + run_len, tokens);
-  if (t0 >= t1) return;
-  float taps[kConvTaps][8];
-  load_taps(w, c0, taps);
-  float win[3][8];  // x[t - 3], x[t - 2], x[t - 1]
-#pragma unroll
-  for (int i = 0; i < 3; ++i) {
-    const int t = t0 - 3 + i;  // rows before the first token come from the history rows, when there are any
-    if (t >= 0) load8f(x + int64_t(t) * channels + c0, win[i]);
-    else if (x_prev != nullptr) load8f(x_prev + int64_t(t + 3) * channels + c0, win[i]);
-    else
-#pragma unroll
-      for (int j = 0; j < 8; ++j) win[i][j] = 0.f;
-  }
-  uint4 raw[4], next[4];
-  int before[4], next_before[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int t = min(t0 + i, t1 - 1);
-    raw[i] = load_row(x, t, channels, c0);
-    before[i] = reach[t] & 3;
-  }
-  for (int tb = t0; tb < t1; tb += 4) {
-    if (tb + 4 < t1) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int t = min(tb + 4 + i, t1 - 1);
-        next[i] = load_row(x, t, channels, c0);
-        next_before[i] = reach[t] & 3;
-      }
-    }
-    __nv_bfloat16* y_row = y + int64_t(tb) * channels + c0;
-    if (tb + 3 < t1 && (before[0] & before[1] & before[2] & before[3]) == 3) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) conv_fwd_token<false>(taps, win, raw[i], 3, y_row + int64_t(i) * channels);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (tb + i < t1) conv_fwd_token<true>(taps, win, raw[i], before[i], y_row + int64_t(i) * channels);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) raw[i] = next[i], before[i] = next_before[i];
-  }
-}
-
 // A thread's CH channels of one token: 16 bytes (CH = 8) or 8 bytes (CH = 4; half the registers per thread, so that
 // two blocks fit an SM)
 template <int CH>
@@ -175,6 +102,80 @@ struct ConvRow<4> {
     *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
   }
 };
+
+// One token of the forward sweep.  kEdge = false: the token has three earlier tokens in its document (no selects).
+template <bool kEdge, int CH>
+__device__ __forceinline__ void conv_fwd_token(const float (&taps)[kConvTaps][CH], float (&win)[3][CH],
+                                               typename ConvRow<CH>::type raw,
+                                               int before, __nv_bfloat16* y_row) {
+  float cur[CH], out[CH];
+  ConvRow<CH>::unpack(raw, cur);
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const float x1 = !kEdge || before >= 1 ? win[2][j] : 0.f, x2 = !kEdge || before >= 2 ? win[1][j] : 0.f;
+    const float x3 = !kEdge || before >= 3 ? win[0][j] : 0.f;
+    const float pre = preactivation(taps[0][j], x3, taps[1][j], x2, taps[2][j], x1, taps[3][j], cur[j]);
+    out[j] = __fdividef(pre, 1.0f + __expf(-pre));
+    win[0][j] = win[1][j], win[1][j] = win[2][j], win[2][j] = cur[j];
+  }
+  ConvRow<CH>::store(y_row, out);
+}
+
+// grid (runs, channel groups of 8 warps x 256); a warp owns tokens [run * run_len, + run_len) of 256 channels.  Tokens
+// go in batches of four; the next batch's loads are issued before the current batch's arithmetic.
+template <typename W, int CH>
+__global__ void __launch_bounds__(256, CH == 4 ? 4 : 2) conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ x_prev,
+                                                            const W* __restrict__ w, const uint8_t* __restrict__ reach,
+                                                            __nv_bfloat16* __restrict__ y, int tokens, int channels,
+                                                            int run_len) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = (blockIdx.y * 8 + warp) * (32 * CH) + lane * CH;
+  if (c0 >= channels) return;
+  const int t0 = blockIdx.x * run_len, t1 = min(t0 + run_len, tokens);
+  if (t0 >= t1) return;
+  float taps[kConvTaps][CH];
+  load_taps<W, CH>(w, c0, taps);
+  float win[3][CH];  // x[t - 3], x[t - 2], x[t - 1]
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    const int t = t0 - 3 + i;  // rows before the first token come from the history rows, when there are any
+    if (t >= 0) ConvRow<CH>::unpack(ConvRow<CH>::load(x, t, channels, c0), win[i]);
+    else if (x_prev != nullptr) ConvRow<CH>::unpack(ConvRow<CH>::load(x_prev, t + 3, channels, c0), win[i]);
+    else
+#pragma unroll
+      for (int j = 0; j < CH; ++j) win[i][j] = 0.f;
+  }
+  typename ConvRow<CH>::type raw[4], next[4];
+  int before[4], next_before[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = min(t0 + i, t1 - 1);
+    raw[i] = ConvRow<CH>::load(x, t, channels, c0);
+    before[i] = reach[t] & 3;
+  }
+  for (int tb = t0; tb < t1; tb += 4) {
+    if (tb + 4 < t1) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = min(tb + 4 + i, t1 - 1);
+        next[i] = ConvRow<CH>::load(x, t, channels, c0);
+        next_before[i] = reach[t] & 3;
+      }
+    }
+    __nv_bfloat16* y_row = y + int64_t(tb) * channels + c0;
+    if (tb + 3 < t1 && (before[0] & before[1] & before[2] & before[3]) == 3) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) conv_fwd_token<false, CH>(taps, win, raw[i], 3, y_row + int64_t(i) * channels);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (tb + i < t1) conv_fwd_token<true, CH>(taps, win, raw[i], before[i], y_row + int64_t(i) * channels);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) raw[i] = next[i], before[i] = next_before[i];
+  }
+}
 
 // One step of the backward sweep: dpre of token u (needs x[u - 3 .. u]) and dx of token t = u - 3 (needs
 // dpre[t .. t + 3]).  kEdge = false: u and t are the run's own tokens with three neighbours inside their documents on
@@ -405,17 +406,17 @@ int mek_conv1d_fwd(const void* x, const void* x_prev, const void* weight, int we
   if (!x || !weight || !reach || !y) return fail(MEK_ERR_INVALID, "conv1d_fwd: a null pointer");
   if (int rc = check_conv("conv1d_fwd", tokens, channels, 1)) return rc;
   const ConvPlan plan = conv_plan(tokens);
-  const dim3 grid(plan.runs, (channels + 2047) / 2048);
+  constexpr int kFwdCh = 4;  // channels per thread
+  const dim3 grid(plan.runs, (channels + 256 * kFwdCh - 1) / (256 * kFwdCh));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (weight_is_bf16)
-    conv1d_fwd_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
-                                           static_cast<const __nv_bfloat16*>(x_prev),
-                                           static_cast<const __nv_bfloat16*>(weight), reach,
-                                           static_cast<__nv_bfloat16*>(y), tokens, channels, plan.run_len);
+    conv1d_fwd_kernel<__nv_bfloat16, kFwdCh><<<grid, 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(x_prev),
+        static_cast<const __nv_bfloat16*>(weight), reach, static_cast<__nv_bfloat16*>(y), tokens, channels, plan.run_len);
   else
-    conv1d_fwd_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
-                                           static_cast<const __nv_bfloat16*>(x_prev), static_cast<const float*>(weight),
-                                           reach, static_cast<__nv_bfloat16*>(y), tokens, channels, plan.run_len);
+    conv1d_fwd_kernel<float, kFwdCh><<<grid, 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(x_prev),
+        static_cast<const float*>(weight), reach, static_cast<__nv_bfloat16*>(y), tokens, channels, plan.run_len);
   return launched("conv1d_fwd");
 }
 
