@@ -1,0 +1,100 @@
+"""The context-parallel layouts on ONE GPU: the ranks of a group run one after another and the all-gather of the
+parallel state exchange is stood in for by the summaries the ranks published in an earlier pass (every rank's
+publication depends on its own tokens only).  Against the undivided call on the same GPU, within the budgets of the
+multi-GPU test (reference: tests/cake/gdn/test_gdn_kcp_gpu.py:404-634)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from gdn_cases import draw
+
+pytestmark = pytest.mark.gpu
+HEADS = (2, 4)
+
+
+class _Published(Exception):
+    """A rank has handed over its summaries; the pass that collects them ends the rank's call here."""
+
+
+def _emulated_context(cu, rank, world, layout, board):
+    """A rank's context whose exchanges read and write ``board``: ``board[direction]`` is a list of the ranks'
+    published summaries (``None``: not collected yet)."""
+    from miles_ext_kernels_b200.cake._impl.gdn import kcp
+
+    class Exchange(kcp._ParallelExchange):
+        def _gather(self, local):
+            direction = "backward" if self._reverse else "forward"
+            slots = board[direction]
+            if any(s is None for s in slots):
+                slots[rank] = local.clone()
+                raise _Published
+            return torch.stack(slots)
+
+        def forward_begin(self, *args):
+            self._reverse = False
+            return super().forward_begin(*args)
+
+        def backward_begin(self, *args):
+            self._reverse = True
+            return super().backward_begin(*args)
+
+    class Context(kcp.KcpContext):
+        def exchange(self, mode="auto"):
+            return Exchange(self)
+
+    return Context(cu, None, rank, world, "cuda", layout=layout)
+
+
+def _take(full, cu, fragments):
+    return torch.cat([full[cu[f.doc] + f.offset : cu[f.doc] + f.end] for f in fragments])
+
+
+@pytest.mark.parametrize("world,seq_lens,layout,gate", [
+    (4, (6000, 2192), "zigzag", "weak"), (4, (6000, 2192), "zigzag", "strong"), (4, (6000, 2192), "contiguous", "weak"),
+    (2, (3072, 1024), "zigzag_per_document", "weak"), (4, (2048, 4096, 2048), "zigzag_per_document", "weak"),
+    (3, (1200, 3408), "zigzag", "weak"),
+])
+def test_layouts_against_the_undivided_call(world, seq_lens, layout, gate):
+    from miles_ext_kernels_b200.cake import gdn
+    from oracle import gdn_oracle as O
+
+    dev = torch.device("cuda")
+    x = draw(seq_lens, HEADS, seed=9, gate=gate)
+    cu = (0, *torch.tensor(seq_lens).cumsum(0).tolist())
+    board = {"forward": [None] * world, "backward": [None] * world}
+
+    def run_rank(rank):
+        ctx = _emulated_context(cu, rank, world, layout, board)
+        mine = lambda t: _take(t, cu, ctx.fragments).unsqueeze(0).to(dev)  # noqa: E731
+        leaves = {n: mine(x[n]).requires_grad_(True) for n in ("q", "k", "v", "g")}
+        beta = mine(x["beta"]).bfloat16().requires_grad_(True)
+        o = gdn.kcp_chunk_gated_delta_rule(leaves["q"], leaves["k"], leaves["v"], leaves["g"], beta, ctx,
+                                           use_qk_l2norm_in_kernel=True)
+        o.backward(mine(x["do"]))
+        return ctx, {"o": o.detach()[0], **{f"d{n}": t.grad[0] for n, t in leaves.items()}, "dbeta": beta.grad[0]}
+
+    for _ in range(2):  # the passes that collect the forward, then the backward summaries
+        for rank in range(world):
+            with pytest.raises(_Published):
+                run_rank(rank)
+    assert all(s is not None for s in board["forward"] + board["backward"])
+    results = [run_rank(rank) for rank in range(world)]
+
+    leaves = {n: x[n].unsqueeze(0).to(dev).requires_grad_(True) for n in ("q", "k", "v", "g")}
+    beta = x["beta"].unsqueeze(0).to(dev).bfloat16().requires_grad_(True)
+    o, _ = gdn.chunk_gated_delta_rule(leaves["q"], leaves["k"], leaves["v"], leaves["g"], beta,
+                                      cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=dev), cu_seqlens_cpu=cu,
+                                      use_qk_l2norm_in_kernel=True)
+    o.backward(x["do"].unsqueeze(0).to(dev))
+    want = {"o": o.detach()[0], **{f"d{n}": t.grad[0] for n, t in leaves.items()}, "dbeta": beta.grad[0]}
+    for name, ref in want.items():
+        got = torch.zeros_like(ref)
+        for ctx, out in results:
+            at = 0
+            for f in ctx.fragments:
+                got[cu[f.doc] + f.offset : cu[f.doc] + f.end] = out[name][at : at + f.length]
+                at += f.length
+        ok, m = O.within_budget(got.float().cpu(), ref.float().cpu(), rel_rms_max=6e-3, max_abs_rel=2e-2)
+        assert ok, (name, m)
