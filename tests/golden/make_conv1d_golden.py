@@ -35,4 +35,6 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit(f"usage: python {sys.argv[0]} <reference root>")
+    main(sys.argv[1])
