@@ -240,7 +240,7 @@ def run_ours(args) -> None:
         g, beta = t["g"].detach().requires_grad_(True), t["beta"].detach().requires_grad_(True)
         h0 = t["h0"].detach().requires_grad_(True) if "h0" in t else None
         if cfg.op == "kda":
-            o, final = kda.chunk_kda(q, k, v, g, beta, cu_gpu), None
+            o, final = kda.chunk_kda(q, k, v, g, beta, cu_gpu, cu_seqlens_cpu=cu_cpu), None
         else:
             o, final = gdn.chunk_gated_delta_rule(q, k, v, g=g, beta=beta, initial_state=h0,
                                                   output_final_state=cfg.final_state, cu_seqlens=cu_gpu,

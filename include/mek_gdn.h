@@ -230,6 +230,16 @@ int mek_kda_fwd_o(const MekGdnDims* dims, const void* qg, const void* aqk, const
 int mek_kda_bwd_dh(const MekGdnDims* dims, const void* qg, const void* kr, const void* w, const void* d_o,
                    const void* aqk, const float* gl2, const float* dht, void* dh_tape, void* dv_new, float* dh0,
                    int32_t* status, void* stream);
+/* Their pre-scans over the segments of a scan plan (dims describe the segments as sequences; the tables and the
+ * summary as in mek_gdn_fwd_h_prescan; no warm-up rule): with mek_gdn_scan_stitch and a walk over the segments from
+ * their stitched start states, a long sequence's scan runs in parallel pieces (reference: the scan plans of
+ * miles_ext_kernels/cake/_impl/gdn/ops.py:405-531, which the reference applies to GDN only). */
+int mek_kda_fwd_h_prescan(const MekGdnDims* dims, const void* kr, const void* w, const void* u, const float* gl2,
+                          const float* boundary, const int32_t* seg_flags, const int32_t* state_row, float* summary,
+                          int32_t* status, void* stream);
+int mek_kda_bwd_dh_prescan(const MekGdnDims* dims, const void* qg, const void* kr, const void* w, const void* d_o,
+                           const void* aqk, const float* gl2, const float* boundary, const int32_t* seg_flags,
+                           const int32_t* state_row, float* summary, int32_t* status, void* stream);
 
 /* Gradient tail: dq32, dk32 fp32 [T, H, 128] (before the norm's pull-back and the rounding), dv bf16 [T, H, 128],
  * dg fp32 [T, H, 128] (in-chunk suffix sum included), dbeta fp32 [T, H].  Scratch the caller provides: m1, m2 fp32

@@ -23,7 +23,7 @@ import torch
 
 from ..._runtime import config, loader, registry, workspace
 from ..gdn import meta as meta_module
-from ..gdn import native
+from ..gdn import native, scan
 from ..gdn.stages import check_status, dims_of
 
 OP = "kda"
@@ -129,6 +129,64 @@ class Saved:
     status: torch.Tensor
 
 
+def _scan_segments() -> int:
+    """0: the scan planner decides; 1: serial walks; more: that many segments per long sequence (the GDN op's
+    ``--cake-gdn-scan-segments``, which the two ops share with the planner)."""
+    try:
+        return int(config.option("gdn", "cake_gdn_scan_segments") or 0)
+    except (KeyError, ValueError):
+        return 0
+
+
+def _scan_forward(dims, meta, kr, w, u, gl2, h0, h, v_new, want_final: bool, status):
+    """The state scan: one serial walk per (sequence, head), or -- when the call has fewer chains than half the SMs
+    and the planner's cost model gains -- pre-scan, stitch and a walk over segments from their true start states
+    (every summary exact: the gate-adaptive warm-up reads scalar gates and stays off).  Returns the final states or
+    None."""
+    device = kr.device
+    H = w.shape[1]
+    plan = scan.plan_for(meta, H, device, _scan_segments())
+    shape = (HEAD_DIM, HEAD_DIM)
+    if plan is None:
+        final = torch.empty((meta.num_seqs, H, *shape), dtype=F32, device=device) if want_final else None
+        native.launch("kda_fwd_h", dims, kr, w, u, gl2, h0, h, v_new, final, status, device=device)
+        return final
+    seg_dims = scan.segment_dims(dims, plan)
+    summary = workspace.take(OP, "scan_summary", (plan.segments, H, 2, *shape), F32, device)
+    seg_state = workspace.take(OP, "scan_state", (plan.segments, H, *shape), F32, device)
+    native.launch("kda_fwd_h_prescan", seg_dims, kr, w, u, gl2, h0, plan.flags_fwd, plan.state_row, summary, status,
+                  device=device)
+    native.launch("gdn_scan_stitch", seg_dims, plan.num_seqs, plan.seq_seg_start, summary, h0, None, seg_state, None, 0,
+                  0, 0.0, 0, device=device)
+    seg_final = workspace.take(OP, "scan_final", (plan.segments, H, *shape), F32, device) if want_final else None
+    native.launch("kda_fwd_h", seg_dims, kr, w, u, gl2, seg_state, h, v_new, seg_final, status, device=device)
+    return seg_final.index_select(0, plan.last_index) if want_final else None
+
+
+def _scan_backward(dims, meta, s, do, dht, dh, dv_new, want_dh0: bool):
+    """The adjoint scan, serial or segmented like the forward's.  Returns dh0 or None."""
+    device = do.device
+    H = do.shape[1]
+    plan = scan.plan_for(meta, H, device, _scan_segments())
+    shape = (HEAD_DIM, HEAD_DIM)
+    if plan is None:
+        dh0 = torch.empty((meta.num_seqs, H, *shape), dtype=F32, device=device) if want_dh0 else None
+        native.launch("kda_bwd_dh", dims, s.qg, s.kr, s.w, do, s.aqk, s.gl2, dht, dh, dv_new, dh0, s.status,
+                      device=device)
+        return dh0
+    seg_dims = scan.segment_dims(dims, plan)
+    summary = workspace.take(OP, "scan_summary", (plan.segments, H, 2, *shape), F32, device)
+    seg_state = workspace.take(OP, "scan_state", (plan.segments, H, *shape), F32, device)
+    native.launch("kda_bwd_dh_prescan", seg_dims, s.qg, s.kr, s.w, do, s.aqk, s.gl2, dht, plan.flags_bwd,
+                  plan.state_row, summary, s.status, device=device)
+    native.launch("gdn_scan_stitch", seg_dims, plan.num_seqs, plan.seq_seg_start, summary, dht, None, seg_state, None,
+                  1, 0, 0.0, 0, device=device)
+    seg_dh0 = workspace.take(OP, "scan_final", (plan.segments, H, *shape), F32, device) if want_dh0 else None
+    native.launch("kda_bwd_dh", seg_dims, s.qg, s.kr, s.w, do, s.aqk, s.gl2, seg_state, dh, dv_new, seg_dh0, s.status,
+                  device=device)
+    return seg_dh0.index_select(0, plan.first_index) if want_dh0 else None
+
+
 def _forward(q, k, v, g, beta32, cu_seqlens, scale, use_qk_l2norm, *, cu_seqlens_cpu=None, h0=None,
              want_final=False):
     """q, k, v ``[S, H, 128]`` bf16 contiguous; g fp32 ``[S, H, 128]``; beta32 fp32 ``[S, H]``.  ``h0`` (fp32
@@ -157,10 +215,7 @@ def _forward(q, k, v, g, beta32, cu_seqlens, scale, use_qk_l2norm, *, cu_seqlens
     native.launch("kda_intra", dims, q, k, v, kg, g2, beta32, a, aqk, w, u, status, device=device)
     h = torch.zeros((NC, H, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
     v_new = torch.empty_like(v)
-    final = None
-    if want_final:
-        final = torch.empty((meta.num_seqs, H, HEAD_DIM, HEAD_DIM), dtype=F32, device=device)
-    native.launch("kda_fwd_h", dims, kr, w, u, gl2, h0, h, v_new, final, status, device=device)
+    final = _scan_forward(dims, meta, kr, w, u, gl2, h0, h, v_new, want_final, status)
     o = torch.empty_like(v)
     native.launch("kda_fwd_o", dims, qg, aqk, v_new, h, o, status, device=device)
     saved = Saved(meta, scale, q, k, q_raw, k_raw, rstd_q, rstd_k, g2, gl2, qg, kg, kr, a, aqk, w, h, v_new, status)
@@ -178,9 +233,7 @@ def _backward(s: Saved, v, beta32, do, *, dht=None, want_dh0=False):
     take = lambda role, shape, dtype: workspace.take(OP, role, shape, dtype, device)  # noqa: E731
     dh = torch.zeros((NC, H, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)  # pad chunks are never written
     dv_new = take("dv_new", (S, H, HEAD_DIM), BF16)
-    dh0 = torch.empty((meta.num_seqs, H, HEAD_DIM, HEAD_DIM), dtype=F32, device=device) if want_dh0 else None
-    native.launch("kda_bwd_dh", dims, s.qg, s.kr, s.w, do, s.aqk, s.gl2, dht, dh, dv_new, dh0, s.status,
-                  device=device)
+    dh0 = _scan_backward(dims, meta, s, do, dht, dh, dv_new, want_dh0)
     m1 = take("m1", (NC, H, 64, 64), F32)
     m2 = take("m2", (NC, H, 64, 64), F32)
     dqg, dkr, dkg = (take(role, (S, H, HEAD_DIM), F32) for role in ("dqg", "dkr", "dkg"))
@@ -200,7 +253,7 @@ def _backward(s: Saved, v, beta32, do, *, dht=None, want_dh0=False):
 
 class _ChunkKda(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, cu_seqlens, scale, use_qk_l2norm):
+    def forward(ctx, q, k, v, g, beta, cu_seqlens, scale, use_qk_l2norm, cu_seqlens_cpu=None):
         shape = q.shape
         q3, k3, v3, g3 = (_packed3(t, n).contiguous() for t, n in ((q, "q"), (k, "k"), (v, "v"), (g, "g")))
         beta3 = _packed_beta(beta)
@@ -208,7 +261,8 @@ class _ChunkKda(torch.autograd.Function):
         _check(q3, k3, v3, g3, beta3, cu_seqlens)
         beta32 = beta3.float().contiguous()
         with torch.cuda.device(q.device):
-            o, saved, _ = _forward(q3, k3, v3, g3, beta32, cu_seqlens, scale, use_qk_l2norm)
+            o, saved, _ = _forward(q3, k3, v3, g3, beta32, cu_seqlens, scale, use_qk_l2norm,
+                                   cu_seqlens_cpu=cu_seqlens_cpu)
         ctx.saved, ctx.v, ctx.beta32 = saved, v3, beta32
         ctx.shapes = (shape, g.shape, beta.shape)
         ctx.dtypes = (g.dtype, beta.dtype)
@@ -224,7 +278,7 @@ class _ChunkKda(torch.autograd.Function):
             dq, dk, dv, dg, dbeta, _ = _backward(ctx.saved, ctx.v, ctx.beta32, do3)
         g_dtype, beta_dtype = ctx.dtypes
         return (dq.view(shape), dk.view(shape), dv.view(shape), dg.view(g_shape).to(g_dtype),
-                dbeta.view(beta_shape).to(beta_dtype), None, None, None)
+                dbeta.view(beta_shape).to(beta_dtype), None, None, None, None)
 
 
 def _gate(g, use_gate_in_kernel, A_log, dt_bias, lower_bound):
@@ -232,15 +286,20 @@ def _gate(g, use_gate_in_kernel, A_log, dt_bias, lower_bound):
 
 
 def chunk_kda(q, k, v, g, beta, cu_seqlens, *, scale=None, use_gate_in_kernel=False, A_log=None, dt_bias=None,
-              lower_bound=None, use_qk_l2norm_in_kernel=False):
+              lower_bound=None, use_qk_l2norm_in_kernel=False, cu_seqlens_cpu=None):
     """Packed KDA chunked training as an autograd node: ``out`` BF16 like ``v``, with gradients to ``q, k, v, g, beta``
-    and, with ``use_gate_in_kernel=True``, to ``A_log`` / ``dt_bias`` (reference: ops.py:142-165)."""
+    and, with ``use_gate_in_kernel=True``, to ``A_log`` / ``dt_bias`` (reference: ops.py:142-165).
+    ``cu_seqlens_cpu`` (not in the reference's signature; the GDN op's FLA signature has it): the same boundaries on
+    the host, a tuple or a CPU tensor.  With them the chunk tables are built on the host without a device read, and
+    the scan planner may cut the scans of a call with few long documents into parallel segments."""
     check_heads(int(v.shape[-2]))
     config.variant(OP)
     v, beta = seam(v, beta)
     gate = _gate(g, use_gate_in_kernel, A_log, dt_bias, lower_bound)
+    if cu_seqlens_cpu is not None and isinstance(cu_seqlens_cpu, torch.Tensor):
+        cu_seqlens_cpu = tuple(int(b) for b in cu_seqlens_cpu.tolist())
     return _ChunkKda.apply(q, k, v, gate, beta, cu_seqlens, DEFAULT_SCALE if scale is None else float(scale),
-                           bool(use_qk_l2norm_in_kernel))
+                           bool(use_qk_l2norm_in_kernel), None if cu_seqlens_cpu is None else tuple(cu_seqlens_cpu))
 
 
 def chunk_kda_fwd(q, k, v, g, beta, cu_seqlens, *, scale=None, save_for_backward=True, use_gate_in_kernel=False,

@@ -329,3 +329,19 @@ extern "C" int mek_kda_bwd_dh(const MekGdnDims* d, const void* qg, const void* k
   return launch_bwd_dh(d, qg, kr, w, d_o, aqk, nullptr, dht, dh_tape, dv_new, dh0, gl2, kNoPlan, status, stream,
                        "kda_bwd_dh");
 }
+
+// The per-channel-decay variant's pre-scan over the segments of a plan (no warm-up rule: it reads scalar gates).
+extern "C" int mek_kda_bwd_dh_prescan(const MekGdnDims* d, const void* qg, const void* kr, const void* w,
+                                      const void* d_o, const void* aqk, const float* gl2, const float* boundary,
+                                      const int32_t* seg_flags, const int32_t* state_row, float* summary,
+                                      int32_t* status, void* stream) {
+  using namespace mek;
+  if (int rc = check_bwd_dh(d, "kda_bwd_dh_prescan")) return rc;
+  if (d->num_qk_heads != d->num_v_heads)
+    return fail(MEK_ERR_INVALID, "kda_bwd_dh_prescan: KDA has one value head per key head");
+  if (!gl2 || !seg_flags || !state_row || !summary)
+    return fail(MEK_ERR_INVALID, "kda_bwd_dh_prescan: gl2, a table or the summary is null");
+  const ScanPlan plan = {seg_flags, state_row, summary, 0, 0.f};
+  return launch_bwd_dh(d, qg, kr, w, d_o, aqk, nullptr, boundary, nullptr, nullptr, nullptr, gl2, plan, status, stream,
+                       "kda_bwd_dh_prescan");
+}

@@ -879,6 +879,21 @@ int mek_kda_fwd_h(const MekGdnDims* d, const void* kr, const void* w, const void
                       "kda_fwd_h");
 }
 
+// The per-channel-decay variant's pre-scan over the segments of a plan (no warm-up rule: it reads scalar gates).
+int mek_kda_fwd_h_prescan(const MekGdnDims* d, const void* kr, const void* w, const void* u, const float* gl2,
+                          const float* boundary, const int32_t* seg_flags, const int32_t* state_row, float* summary,
+                          int32_t* status, void* stream) {
+  using namespace mek;
+  if (int rc = check_dims(d, "kda_fwd_h_prescan")) return rc;
+  if (d->num_qk_heads != d->num_v_heads)
+    return fail(MEK_ERR_INVALID, "kda_fwd_h_prescan: KDA has one value head per key head");
+  if (!gl2 || !seg_flags || !state_row || !summary)
+    return fail(MEK_ERR_INVALID, "kda_fwd_h_prescan: gl2, a table or the summary is null");
+  const ScanPlan plan = {seg_flags, state_row, summary, 0, 0.f};
+  return launch_fwd_h(d, kr, w, u, nullptr, boundary, nullptr, nullptr, nullptr, gl2, plan, kNoOutput, status, stream,
+                      "kda_fwd_h_prescan");
+}
+
 int mek_gdn_fwd_o(const MekGdnDims* d, const void* q, const void* aqk, const void* v_new, const void* h_tape,
                   const float* g_cs, void* o, int32_t* status, void* stream) {
   using namespace mek;

@@ -34,6 +34,8 @@ def draw(seq_lens, H, seed, gate="weak", normalised=True):
     a = torch.randn(T, H, 128, generator=gen)
     if gate == "weak":
         g = -0.3 * torch.rand(T, H, 128, generator=gen)
+    elif gate == "faint":  # a state still counts a thousand tokens later
+        g = -0.004 * torch.rand(T, H, 128, generator=gen)
     else:  # the benchmark generator: unbounded
         a_log = torch.rand(H, generator=gen) * math.log(16.0)
         g = -torch.nn.functional.softplus(a) * torch.exp(a_log)[None, :, None]
@@ -57,6 +59,8 @@ def run(x, seq_lens, **modes):
     leaves = {n: x[n].to(dev).requires_grad_(True) for n in ("q", "k", "v", "g", "beta")}
     extra = {n: modes[n].to(dev).requires_grad_(True) for n in ("A_log", "dt_bias") if n in modes}
     flags = {n: v for n, v in modes.items() if n not in extra}
+    if flags.pop("host_boundaries", False):
+        flags["cu_seqlens_cpu"] = tuple(cu)
     out = kda.chunk_kda(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"],
                         torch.tensor(cu, dtype=torch.int32, device=dev), **flags, **extra)
     out.backward(x["do"].to(dev))
@@ -172,3 +176,35 @@ def test_head_count_and_shape_rejections():
         kda.chunk_kda(q, q, q, q.float(), q[..., :3], cu)
     with pytest.raises(ValueError, match="needs A_log and dt_bias"):
         kda.chunk_kda(q, q, q, q, q[..., 0], cu, use_gate_in_kernel=True)
+
+
+@pytest.mark.parametrize("gate", ["faint", "weak", "strong"])
+def test_segmented_scans_agree_with_the_serial_walk(gate):
+    """One long document and a short one on few heads: the planner cuts the long scan into segments (pre-scan,
+    stitch, walk from the stitched start states); forced to 1, 3 and 4 segments the outputs and gradients agree within
+    a fraction of the accuracy budget, and the serial form stays within the budgets of the FP64 recurrence."""
+    import miles_ext_kernels_b200 as package
+
+    seq_lens = (4096 + 37, 200)
+    x = draw(seq_lens, 2, seed=44, gate=gate)
+    results = {}
+    try:
+        for segments in (1, 3, 4, 0):
+            package.configure(cake_gdn_scan_segments=segments)
+            results[segments] = run(x, seq_lens, host_boundaries=True)
+        device_tables = run(x, seq_lens)  # without the host's boundaries: tables built on the device, serial walks
+    finally:
+        package.configure()
+    for name in NAMES:
+        assert torch.equal(device_tables[name], results[1][name]), name
+    if gate == "faint":  # under the other gates nothing of a state survives a segment: the same bits either way
+        assert any(not torch.equal(results[4][name], results[1][name]) for name in NAMES)  # the plan was taken
+    for segments in (3, 4, 0):
+        for name in NAMES:
+            ok, m = O.within_budget(results[segments][name].float(), results[1][name].float(), rel_rms_max=4e-3,
+                                    max_abs_rel=1e-2)
+            assert ok, (segments, name, m)
+    ref = K.recurrence_fp64(x["q"], x["k"], x["v"], x["g"], x["beta"], seq_lens, do=x["do"])
+    for name in NAMES:
+        ok, m = O.within_budget(results[4][name].float(), ref[name])
+        assert ok, (name, m)
