@@ -58,17 +58,19 @@ struct KdaIntraSmem {
   static constexpr uint32_t kQ = 0;                                 // fp32 [64][129]; later the bf16 tiles below
   static constexpr uint32_t kK = kQ + 64 * kRow * 4;
   static constexpr uint32_t kG = kK + 64 * kRow * 4;
-  static constexpr uint32_t kA = 0;                                 // [64][64] bf16 (after the pair phase)
+  // after the pair phase (the copies above are dead; about 100 KB in all, so that two CTAs share an SM):
+  static constexpr uint32_t kA = 0;                                 // [64][64] bf16
   static constexpr uint32_t kKB = 8192;                             // [64][128] beta kg
   static constexpr uint32_t kVB = kKB + 16384;                      // [64][128] beta v
-  static constexpr uint32_t kSqk = ((kG + 64 * kRow * 4 + 1023) / 1024) * 1024;  // fp32 [2][64][65]: one per channel half
-  static constexpr uint32_t kSkk = kSqk + 2 * 64 * 65 * 4;
-  static constexpr uint32_t kL = kSkk + 2 * 64 * 65 * 4;            // fp32 [64][68]
-  static constexpr uint32_t kBeta = kL + 64 * 68 * 4;               // beta[64]
+  static constexpr uint32_t kSqk = kVB + 16384;                     // fp32 [64][65]
+  static constexpr uint32_t kSkk = kSqk + 64 * 65 * 4;
+  static constexpr uint32_t kL = kSkk + 64 * 65 * 4;                // fp32 [64][68]
+  static constexpr uint32_t kBeta = ((kG + 64 * kRow * 4 + 255) / 256) * 256;  // beta[64]
   static constexpr uint32_t kBytes = kBeta + 256;
+  static_assert(kL + 64 * 68 * 4 <= kBeta, "the results of the pair phase fit the dead copies");
 };
 
-__global__ void __launch_bounds__(288) kda_intra_kernel(
+__global__ void __launch_bounds__(288, 2) kda_intra_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
     const __nv_bfloat16* __restrict__ kg, const float* __restrict__ g2, const float* __restrict__ beta,
     __nv_bfloat16* __restrict__ a_out, __nv_bfloat16* __restrict__ aqk_out, __nv_bfloat16* __restrict__ w_out,
@@ -98,13 +100,23 @@ __global__ void __launch_bounds__(288) kda_intra_kernel(
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 256);
-  for (int i = tid; i < 64 * 128; i += 288) {
-    const int r = i >> 7, d = i & 127;
+  for (int i = tid; i < 64 * 16; i += 288) {  // 8 channels of one row per step, 16-byte loads
+    const int r = i >> 4, d = (i & 15) * 8;
     const bool live = r < len;
     const int64_t at = int64_t(start + (live ? r : len - 1)) * stride + h * kDim + d;
-    sq[r * kRow + d] = live ? __bfloat162float(q[at]) : 0.f;
-    sk[r * kRow + d] = live ? __bfloat162float(k[at]) : 0.f;
-    sg[r * kRow + d] = g2[at];  // rows past the chunk's length keep the last gate: every pair exponent stays <= 0
+    float qv[8], kv[8];
+    unpack8(live ? ldg16(q + at) : make_uint4(0u, 0u, 0u, 0u), qv);
+    unpack8(live ? ldg16(k + at) : make_uint4(0u, 0u, 0u, 0u), kv);
+    // rows past the chunk's length keep the last gate: every pair exponent stays <= 0
+    const float4 g_lo = __ldg(reinterpret_cast<const float4*>(g2 + at));
+    const float4 g_hi = __ldg(reinterpret_cast<const float4*>(g2 + at + 4));
+    const float gv[8] = {g_lo.x, g_lo.y, g_lo.z, g_lo.w, g_hi.x, g_hi.y, g_hi.z, g_hi.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      sq[r * kRow + d + j] = qv[j];
+      sk[r * kRow + d + j] = kv[j];
+      sg[r * kRow + d + j] = gv[j];
+    }
   }
   if (tid < 64) s_beta[tid] = tid < len ? beta[int64_t(start + tid) * num_heads + h] : 0.f;
   tc_fence_before();
@@ -116,18 +128,19 @@ __global__ void __launch_bounds__(288) kda_intra_kernel(
   // threads 0..239 the 120 blocks below the diagonal, threads 256..287 (one warp) the 16 diagonal blocks.
   // Below the diagonal every pair of a block is valid and 2^{G_i - G_j} factors as 2^{G_i - G_{j0+3}} 2^{G_{j0+3} - G_j}
   // with both exponents <= 0: 7 exponentials per channel instead of 16.
+  float aqk[4][4], akk[4][4];
+  int i0 = 0, j0 = 0;
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) aqk[a][b] = akk[a][b] = 0.f;
   if (tid < 240) {
     const int t = tid >> 1, half = tid & 1;
     int bi = int((sqrtf(8.f * t + 1.f) + 1.f) * 0.5f);
     while (bi * (bi + 1) / 2 <= t) ++bi;
     while (bi * (bi - 1) / 2 > t) --bi;
     const int bj = t - bi * (bi - 1) / 2;
-    const int i0 = 4 * bi, j0 = 4 * bj;
-    float aqk[4][4], akk[4][4];
-#pragma unroll
-    for (int a = 0; a < 4; ++a)
-#pragma unroll
-      for (int b = 0; b < 4; ++b) aqk[a][b] = akk[a][b] = 0.f;
+    i0 = 4 * bi, j0 = 4 * bj;
     for (int d = half * 64; d < half * 64 + 64; ++d) {
       float qe[4], ke[4], kj[4], gj[4];
 #pragma unroll
@@ -151,21 +164,9 @@ __global__ void __launch_bounds__(288) kda_intra_kernel(
           akk[a][b] = fmaf(ke[a], kj[b], akk[a][b]);
         }
     }
-#pragma unroll
-    for (int a = 0; a < 4; ++a)
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        s_qk[half * 4160 + (i0 + a) * 65 + j0 + b] = aqk[a][b];
-        s_kk[half * 4160 + (i0 + a) * 65 + j0 + b] = akk[a][b];
-      }
   } else if (tid >= 256) {
     const int bi = (tid - 256) >> 1, half = tid & 1;
-    const int i0 = 4 * bi;
-    float aqk[4][4], akk[4][4];
-#pragma unroll
-    for (int a = 0; a < 4; ++a)
-#pragma unroll
-      for (int b = 0; b < 4; ++b) aqk[a][b] = akk[a][b] = 0.f;
+    i0 = j0 = 4 * bi;
     for (int d = half * 64; d < half * 64 + 64; ++d) {
       float qi[4], ki[4], gi[4];
 #pragma unroll
@@ -183,12 +184,25 @@ __global__ void __launch_bounds__(288) kda_intra_kernel(
           akk[a][b] = fmaf(ki[a], e, akk[a][b]);
         }
     }
+  }
+  // the two channel halves of a block sit in neighbouring lanes: half 0 + half 1, then one of them writes -- after a
+  // block barrier, because the results take the place of the q / k / G copies
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const float oq = __shfl_xor_sync(0xffffffffu, aqk[a][b], 1), ok_ = __shfl_xor_sync(0xffffffffu, akk[a][b], 1);
+      aqk[a][b] = (tid & 1) ? oq + aqk[a][b] : aqk[a][b] + oq;
+      akk[a][b] = (tid & 1) ? ok_ + akk[a][b] : akk[a][b] + ok_;
+    }
+  __syncthreads();
+  if ((tid < 240 || tid >= 256) && (tid & 1) == 0) {
 #pragma unroll
     for (int a = 0; a < 4; ++a)
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        s_qk[half * 4160 + (i0 + a) * 65 + i0 + b] = aqk[a][b];
-        s_kk[half * 4160 + (i0 + a) * 65 + i0 + b] = akk[a][b];
+        s_qk[(i0 + a) * 65 + j0 + b] = aqk[a][b];
+        s_kk[(i0 + a) * 65 + j0 + b] = akk[a][b];
       }
   }
   __syncthreads();
@@ -204,13 +218,13 @@ __global__ void __launch_bounds__(288) kda_intra_kernel(
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const int j = jj * 8 + e;
-        x[e] = j <= i ? scale * (s_qk[i * 65 + j] + s_qk[4160 + i * 65 + j]) : 0.f;
-        s_l[i * 68 + j] = j < i ? bi * (s_kk[i * 65 + j] + s_kk[4160 + i * 65 + j]) : 0.f;
+        x[e] = j <= i ? scale * s_qk[i * 65 + j] : 0.f;
+        s_l[i * 68 + j] = j < i ? bi * s_kk[i * 65 + j] : 0.f;
       }
       reinterpret_cast<uint4*>(dst)[jj] = pack8(x);
     }
   }
-  __syncthreads();  // the fp32 copies of q / k / G are dead: their space holds the operand tiles from here on
+  __syncthreads();
 
   // kb = bf16(beta kg), vb = bf16(beta v)
   for (int i = tid; i < 64 * 16; i += 288) {
