@@ -114,7 +114,9 @@ __device__ __forceinline__ void conv_fwd_token(const float (&taps)[kConvTaps][CH
   for (int j = 0; j < CH; ++j) {
     const float x1 = !kEdge || before >= 1 ? win[2][j] : 0.f, x2 = !kEdge || before >= 2 ? win[1][j] : 0.f;
     const float x3 = !kEdge || before >= 3 ? win[0][j] : 0.f;
-    const float pre = preactivation(taps[0][j], x3, taps[1][j], x2, taps[2][j], x1, taps[3][j], cur[j]);
+    // fused multiply-adds here (oldest tap first): y is rounded to BF16 and the backward, whose SiLU' must see the
+    // reference's rounding of the preactivation, recomputes it in the reference's order
+    const float pre = fmaf(taps[3][j], cur[j], fmaf(taps[2][j], x1, fmaf(taps[1][j], x2, taps[0][j] * x3)));
     out[j] = __fdividef(pre, 1.0f + __expf(-pre));
     win[0][j] = win[1][j], win[1][j] = win[2][j], win[2][j] = cur[j];
   }
