@@ -97,6 +97,9 @@ typedef struct MekGdnDims {
   int64_t raw_pitch;              /* of q_raw and k_raw (gradient tail) */
   int64_t dqk_pitch;              /* of the dq and dk outputs */
   int64_t dv_pitch;               /* of the dv output */
+  /* Optional, device [N]: the order in which the scans' CTAs take the sequences (a permutation; longest first
+   * balances a packed batch of uneven documents over the SMs).  NULL: as numbered.  Results do not depend on it. */
+  const int32_t* seq_order;
 } MekGdnDims;
 
 /* Chunk tables from a device cu_seqlens (int32, or int64 when offsets_are_int64) [num_seqs + 1], in one launch and

@@ -41,6 +41,7 @@ class ChunkMeta:
     exact: bool  # False: built on the device, padded
     max_seq_chunks: int  # most chunks of one sequence (an upper bound on the device route)
     host_seq_chunk_start: tuple[int, ...] | None = None  # the host route's copy of seq_chunk_start (scan planner)
+    seq_order: torch.Tensor | None = None  # int32 [N]: sequences by falling chunk count, when they differ (host route)
 
 
 def host_tables(seq_lens: Sequence[int]) -> tuple[list[int], list[int], list[int], list[int]]:
@@ -84,12 +85,17 @@ def _from_host(seq_lens: tuple[int, ...], device: torch.device) -> ChunkMeta:
         return cached
     starts, lens, seqs, first = host_tables(seq_lens)
     nc = len(starts)
-    flat = torch.tensor([*starts, *lens, *seqs, *first], dtype=torch.int32)
+    # the scans take one CTA per (sequence, head) and a CTA's duration is its sequence's chunk count: with uneven
+    # documents the longest go first, so that no long walk starts when the others are done
+    counts = [first[n + 1] - first[n] for n in range(len(seq_lens))]
+    order = sorted(range(len(counts)), key=lambda n: -counts[n]) if len(set(counts)) > 1 else []
+    flat = torch.tensor([*starts, *lens, *seqs, *first, *order], dtype=torch.int32)
     if device.type == "cuda":
         flat = flat.pin_memory().to(device, non_blocking=True)
+    ends = 3 * nc + len(first)
     meta = ChunkMeta(
-        flat[:nc], flat[nc : 2 * nc], flat[2 * nc : 3 * nc], flat[3 * nc :], nc, len(seq_lens), sum(seq_lens), True,
-        max((first[n + 1] - first[n] for n in range(len(seq_lens))), default=0), tuple(first),
+        flat[:nc], flat[nc : 2 * nc], flat[2 * nc : 3 * nc], flat[3 * nc : ends], nc, len(seq_lens), sum(seq_lens), True,
+        max(counts, default=0), tuple(first), flat[ends:] if order else None,
     )
     _HOST_BUILDS += 1
     _HOST_CACHE[key] = meta

@@ -40,6 +40,8 @@ class Dims(ctypes.Structure):
         ("raw_pitch", ctypes.c_int64),
         ("dqk_pitch", ctypes.c_int64),
         ("dv_pitch", ctypes.c_int64),
+        # optional device table: the order in which the scans take the sequences (longest first)
+        ("seq_order", ctypes.c_void_p),
     ]
 
 

@@ -164,7 +164,8 @@ def segment_dims(dims: native.Dims, plan: ScanPlan) -> native.Dims:
     """The call's extents with the segments in place of the sequences."""
     return native.Dims(dims.total_tokens, dims.num_qk_heads, dims.num_v_heads, dims.head_dim, plan.segments,
                        dims.num_chunks, dims.scale, dims.chunk_start, dims.chunk_len, dims.chunk_seq,
-                       plan.seg_chunk_start.data_ptr())
+                       plan.seg_chunk_start.data_ptr(), dims.qk_pitch, dims.v_pitch, dims.raw_pitch, dims.dqk_pitch,
+                       dims.dv_pitch, None)  # the operands' pitches stay; the segments are taken as numbered
 
 
 # --------------------------------------------------------------------------------------------------------------------

@@ -43,6 +43,7 @@ def dims_of(meta: ChunkMeta, num_qk_heads: int, num_v_heads: int, scale: float, 
         meta.total_tokens, num_qk_heads, num_v_heads, HEAD_DIM, meta.num_seqs, meta.num_chunks, float(scale),
         meta.chunk_start.data_ptr(), meta.chunk_len.data_ptr(), meta.chunk_seq.data_ptr(),
         meta.seq_chunk_start.data_ptr(), qk_pitch, v_pitch, raw_pitch, dqk_pitch, dv_pitch,
+        None if meta.seq_order is None else meta.seq_order.data_ptr(),
     )
 
 

@@ -52,7 +52,10 @@ __global__ void __launch_bounds__(256) gdn_bwd_dh_kernel(
   const bool kda = gl2 != nullptr;
   const int quad = warp & 3, half = warp >> 2;
   const int krow = quad * 32 + lane;
-  const int n = blockIdx.x, hv = blockIdx.y, hq = hv / (num_v_heads / num_qk_heads);
+  // grid (heads, sequences): the heads of one sequence are neighbours in launch order, so that with `seq_order`
+  // (longest first) every long walk starts before any short one
+  const int n = plan.seq_order != nullptr ? plan.seq_order[blockIdx.y] : int(blockIdx.y);
+  const int hv = blockIdx.x, hq = hv / (num_v_heads / num_qk_heads);
   float* s_g2 = reinterpret_cast<float*>(sm + BwdDhSmem::kG);
   Abort abort{&abort_flag};
 
@@ -279,10 +282,15 @@ int launch_bwd_dh(const MekGdnDims* d, const void* q, const void* k, const void*
   if (int rc = make_rows_map(&maps.w, w, d->total_tokens, d->num_v_heads, what)) return rc;
   if (int rc = make_rows_map(&maps.d_o, d_o, d->total_tokens, d->num_v_heads, what)) return rc;
   if (int rc = make_tiles_map(&maps.aqk, aqk, int64_t(d->num_chunks) * d->num_v_heads, 64, 64, what)) return rc;
-  const dim3 grid(d->num_seqs, d->num_v_heads, plan.seg_flags != nullptr ? 2 : 1);
+  if (d->num_seqs > 65535)
+    return fail(MEK_ERR_UNSUPPORTED, "%s: at most 65,535 sequences (or scan segments) per call, got %d", what,
+                d->num_seqs);
+  const dim3 grid(d->num_v_heads, d->num_seqs, plan.seg_flags != nullptr ? 2 : 1);
+  ScanPlan ordered = plan;
+  ordered.seq_order = d->seq_order;
   gdn_bwd_dh_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(
       maps, g_cs, dht, static_cast<__nv_bfloat16*>(dh_tape), static_cast<__nv_bfloat16*>(dv_new), dh0, d->chunk_start,
-      d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, d->scale, gl2, plan, status);
+      d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, d->scale, gl2, ordered, status);
   return launched(what);
 }
 const mek::ScanPlan kNoPlan = {nullptr, nullptr, nullptr, 0, 0.f};

@@ -369,7 +369,10 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
   const bool kda = gl2 != nullptr;
   const int quad = warp & 3, half = warp >> 2;   // tensor-memory lane quadrant; V half of this warpgroup
   const int krow = quad * 32 + lane;             // row of h this thread holds
-  const int n = blockIdx.x, hv = blockIdx.y, hq = hv / (num_v_heads / num_qk_heads);
+  // grid (heads, sequences): the heads of one sequence are neighbours in launch order, so that with `seq_order`
+  // (longest first) every long walk starts before any short one
+  const int n = plan.seq_order != nullptr ? plan.seq_order[blockIdx.y] : int(blockIdx.y);
+  const int hv = blockIdx.x, hq = hv / (num_v_heads / num_qk_heads);
   float* s_g2 = reinterpret_cast<float*>(sm + FwdHSmem::kG);
   Abort abort{&abort_flag};
 
@@ -828,10 +831,15 @@ int launch_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* 
     maps.q = maps.k;  // never read
     maps.aqk = maps.k;
   }
-  const dim3 grid(d->num_seqs, d->num_v_heads, plan.seg_flags != nullptr ? 2 : 1);
+  if (d->num_seqs > 65535)
+    return fail(MEK_ERR_UNSUPPORTED, "%s: at most 65,535 sequences (or scan segments) per call, got %d", what,
+                d->num_seqs);
+  const dim3 grid(d->num_v_heads, d->num_seqs, plan.seg_flags != nullptr ? 2 : 1);
+  ScanPlan ordered = plan;
+  ordered.seq_order = d->seq_order;
   gdn_fwd_h_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(
       maps, g_cs, h0, static_cast<__nv_bfloat16*>(h_tape), static_cast<__nv_bfloat16*>(v_new), final_state,
-      d->chunk_start, d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, gl2, plan,
+      d->chunk_start, d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, gl2, ordered,
       static_cast<__nv_bfloat16*>(fused.o), d->scale, status);
   return launched(what);
 }

@@ -26,6 +26,7 @@ struct ScanPlan {
   float* summary;            // pre-scan: fp32 [segments][HV][2][128][128]: B, then M
   int warm_chunks;           // 0 switches the warm-up rule off
   float warm_log2;
+  const int32_t* seq_order;  // any walk: which sequence the CTA with blockIdx.x = i takes (null: sequence i)
 };
 
 // The gate a state accumulates over chunks [first, last): the chunk-end values of the chunk-local cumulative gate.

@@ -270,16 +270,27 @@ def test_forward_and_backward_replay_from_a_cuda_graph():
 
 @pytest.mark.parametrize("l2", [True, False], ids=["l2norm", "plain"])
 @pytest.mark.parametrize("split", ["packed_qkv_views", "torch_split"])
-def test_views_of_one_packed_row_are_read_in_place_and_give_the_contiguous_bits(l2, split):
+@pytest.mark.parametrize("segments", [0, 2], ids=["serial_scans", "segmented_scans"])
+def test_views_of_one_packed_row_are_read_in_place_and_give_the_contiguous_bits(l2, split, segments):
     """q, k, v as the column slices [q heads | k heads | v heads] of one packed row: no copy on the way in (the
-    kernels take the token stride), one packed gradient row on the way out, the bits of contiguous operands."""
+    kernels take the token stride), one packed gradient row on the way out, the bits of contiguous operands --
+    also when the scans are cut into segments (the segments' extents keep the operands' strides)."""
+    import miles_ext_kernels_b200 as package
     from miles_ext_kernels_b200.cake import gdn
     from miles_ext_kernels_b200.cake._impl.gdn import ops
 
     dev = torch.device("cuda")
-    B, T, (H, HV) = 2, 448, (2, 4)
+    B, T, (H, HV) = 2, (2304 if segments else 448), (2, 4)
     seq_lens = (T,) * B
     x = draw(seq_lens, (H, HV), seed=51, normalised=not l2)
+    package.configure(cake_gdn_scan_segments=segments)
+    try:
+        _packed_row_case(x, seq_lens, l2, split, B, T, H, HV, dev, gdn, ops)
+    finally:
+        package.configure()
+
+
+def _packed_row_case(x, seq_lens, l2, split, B, T, H, HV, dev, gdn, ops):
     want = run(x, seq_lens, l2=l2, batch=B)
     row = torch.cat([x["q"].reshape(B * T, -1), x["k"].reshape(B * T, -1), x["v"].reshape(B * T, -1)], dim=-1)
     row = row.reshape(B, T, -1).to(dev).requires_grad_(True)

@@ -49,6 +49,15 @@ def test_device_route_equals_host_route_on_the_real_chunks(seq_lens):
     assert dev.chunk_len[n:].sum().item() == 0  # pad chunks are empty
 
 
+def test_uneven_documents_are_walked_longest_first():
+    cu = (0, 100, 1000, 1064, 5000, 5010)  # chunk counts 2, 15, 1, 62, 1
+    meta = M.chunk_meta(torch.tensor(cu), cu, 1, cu[-1], "cpu")
+    assert meta.seq_order.tolist() == [3, 1, 0, 2, 4] and meta.seq_order.dtype == torch.int32
+    assert meta.seq_chunk_start.tolist() == [0, 2, 17, 18, 80, 81]
+    even = M.chunk_meta(None, None, 3, 100, "cpu")
+    assert even.seq_order is None  # nothing to balance
+
+
 def test_equal_length_batches_and_boundary_errors():
     meta = M.chunk_meta(None, None, 3, 100, "cpu")
     assert meta.num_seqs == 3 and meta.chunk_len.tolist() == [64, 36] * 3
