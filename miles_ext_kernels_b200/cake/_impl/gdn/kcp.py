@@ -22,6 +22,7 @@ of the fragments before it in its document.
 
 from __future__ import annotations
 
+import dataclasses
 from collections import OrderedDict
 from collections.abc import Sequence
 from typing import Any
@@ -283,6 +284,8 @@ class _ParallelExchange:
         table = meta.host_seq_chunk_start
         for slot, f in enumerate(publish):
             plan = scan.fragment_plan(table[f], table[f + 1], HV, device)
+            if getattr(self, "_exact", False):
+                plan = dataclasses.replace(plan, warm_chunks=0)
             seg_dims = scan.segment_dims(dims, plan)
             summary = torch.empty((plan.segments, HV, 2, 128, 128), dtype=torch.float32, device=device)
             summarise(seg_dims, plan, summary)
@@ -303,7 +306,7 @@ class _ParallelExchange:
 
         plan = self.context.plan
         device, HV = w.device, w.shape[1]
-        self._g_cs = g_cs
+        self._g_cs, self._exact = g_cs, False
 
         def summarise(seg_dims, frag, summary):
             native.launch("gdn_fwd_h_prescan", seg_dims, k, w, u, g_cs, None, frag.flags_fwd, frag.state_row,
@@ -316,12 +319,41 @@ class _ParallelExchange:
     def forward_end(self, final_state) -> None:
         pass
 
+    # the per-channel-decay variant (KDA): the same exchange on its scan operands; its pre-scans have no warm-up rule
+    def kda_forward_state(self, dims, meta, kr, w, u, gl2, status):
+        from . import native
+
+        plan = self.context.plan
+        device, H = w.device, w.shape[1]
+        self._g_cs, self._exact = None, True
+
+        def summarise(seg_dims, frag, summary):
+            native.launch("kda_fwd_h_prescan", seg_dims, kr, w, u, gl2, None, frag.flags_fwd, frag.state_row, summary,
+                          status, device=device)
+
+        return self._exchange(dims, meta, H, device, plan.publish_forward, plan.slots_forward, plan.chain_forward,
+                              summarise, reverse=False)
+
+    def kda_backward_state(self, dims, meta, saved, do):
+        from . import native
+
+        plan = self.context.plan
+        device, H = do.device, do.shape[1]
+        self._g_cs, self._exact = None, True
+
+        def summarise(seg_dims, frag, summary):
+            native.launch("kda_bwd_dh_prescan", seg_dims, saved.qg, saved.kr, saved.w, do, saved.aqk, saved.gl2, None,
+                          frag.flags_bwd, frag.state_row, summary, saved.status, device=device)
+
+        return self._exchange(dims, meta, H, device, plan.publish_backward, plan.slots_backward, plan.chain_backward,
+                              summarise, reverse=True)
+
     def backward_begin(self, dims, meta, tape, do):
         from . import native
 
         plan = self.context.plan
         device, HV = do.device, tape.v.shape[1]
-        self._g_cs = tape.g_cs
+        self._g_cs, self._exact = tape.g_cs, False
 
         def summarise(seg_dims, frag, summary):
             native.launch("gdn_bwd_dh_prescan", seg_dims, tape.qn, tape.kn, tape.w, do, tape.aqk, tape.g_cs, None,

@@ -1,5 +1,5 @@
-"""Context-parallel packed KDA: one packed batch split into contiguous token slices over the ranks of a process group,
-with the per-document state crossing the rank boundaries exactly.
+"""Context-parallel packed KDA: one packed batch split over the ranks of a process group (contiguous slices, the
+zigzag layouts or an explicit fragment table), with the per-document state crossing the cuts.
 
 Entry points and argument meaning follow the reference (reference: miles_ext_kernels/cake/_impl/kda/kcp.py:86-230)::
 
@@ -8,14 +8,15 @@ Entry points and argument meaning follow the reference (reference: miles_ext_ker
     out_local = chunk_kda_kcp(q_local, k_local, v_local, g_local, beta_local, ctx)   # autograd
 
 A rank's operands are its shard (the tokens of its slice), with the shapes, dtypes and modes of the single-rank
-:func:`chunk_kda`.  Forward: the ``[H, 128, 128]`` fp32 state at the end of this rank's last fragment goes to the next
-rank when the document continues there; backward: the adjoint state at the start of this rank's first fragment goes
-to the previous rank.  The hand-over is sequential along the rank chain (point to point on the group's backend) and
-reproduces the single-rank recurrence: bit for bit when the rank boundaries fall on multiples of 64 tokens inside
-their documents, within the accuracy budgets otherwise (the chunking restarts at a boundary).
+:func:`chunk_kda`.  Forward: the ``[H, 128, 128]`` fp32 state at the end of a fragment goes to the rank that holds the
+document's next tokens; backward: the adjoint state at the start of a fragment goes to the rank that holds the tokens
+before.  Two exchanges, chosen like the GDN op's (``--cake-gdn-kcp-exchange``): the sequential hand-over along the
+rank chain of the contiguous layout (point to point; bit for bit the single-rank recurrence when the cuts fall on
+multiples of 64 tokens inside their documents, within the accuracy budgets otherwise), and the parallel exchange of
+affine fragment summaries (pre-scan of a fragment's segments, one all-gather, a fold per fragment; every layout;
+within the accuracy budgets).
 
-Only the ``"contiguous"`` layout is served (``"zigzag"``, ``"zigzag_per_document"`` and explicit fragments raise
-``NotImplementedError``), and no package options (``save_mode``, ``graph``, ...).
+No package options (``save_mode``, ``graph``, ...).
 
 In the raw gate mode the gradients of ``A_log`` / ``dt_bias`` are this rank's partial sums;
 :func:`reduce_gate_param_grads_kcp` sums them over the group in rank order, the same bits on every rank.
@@ -50,17 +51,19 @@ class KcpPartition:
     cu_seqlens_global: tuple[int, ...]
     world_size: int
     layout: str = "contiguous"
+    fragments: tuple | None = None  # an explicit table per rank, instead of a layout
 
 
 def partition_kcp(cu_seqlens_global_cpu: Any, world_size: int, layout: str = "contiguous", fragments: Any = None, *,
                   cut_points: Any = None) -> KcpPartition:
-    """The context-parallel partition of one packed batch over ``world_size`` ranks (equal token shares in order).
-    ``cu_seqlens_global_cpu``: the whole batch's ``[num_docs + 1]`` document offsets on the host."""
-    if layout != "contiguous" or fragments is not None or cut_points is not None:
-        raise NotImplementedError(
-            f"partition_kcp: only the 'contiguous' layout without explicit fragments or cut points is served, not "
-            f"{layout!r}"
-        )
+    """The context-parallel partition of one packed batch over ``world_size`` ranks: ``layout`` ``contiguous`` (equal
+    token shares in order), ``zigzag``, ``zigzag_per_document``, or an explicit table ``fragments``
+    (``[[(doc, offset, length), ...], ...]``, one list per rank).  ``cu_seqlens_global_cpu``: the whole batch's
+    ``[num_docs + 1]`` document offsets on the host."""
+    from ..gdn import layout as layout_module
+
+    if cut_points is not None:
+        raise NotImplementedError("partition_kcp: cut points are not served; give an explicit fragment table")
     if isinstance(cu_seqlens_global_cpu, torch.Tensor):
         if cu_seqlens_global_cpu.is_cuda:
             raise ValueError("partition_kcp: cu_seqlens_global_cpu must be on the host")
@@ -71,10 +74,11 @@ def partition_kcp(cu_seqlens_global_cpu: Any, world_size: int, layout: str = "co
     world_size = int(world_size)
     if world_size < 1:
         raise ValueError(f"partition_kcp: world_size must be positive, got {world_size}")
-    if cu[-1] % world_size:
-        raise ValueError(f"partition_kcp: a contiguous partition needs the token count ({cu[-1]}) to divide by the "
-                         f"world size ({world_size})")
-    return KcpPartition(cu, world_size, layout)
+    frozen = None
+    if fragments is not None:
+        frozen = tuple(tuple(tuple(int(x) for x in f) for f in rank) for rank in fragments)
+    layout_module.partition(cu, world_size, layout, frozen)  # raises for a layout the batch does not fit
+    return KcpPartition(cu, world_size, "explicit" if frozen is not None else layout, frozen)
 
 
 def build_context_kcp(part: KcpPartition, group: Any, rank: int, device: Any, conv_kernel_size: int = 4, *,
@@ -90,7 +94,8 @@ def build_context_kcp(part: KcpPartition, group: Any, rank: int, device: Any, co
     if heads is not None:
         for count in (heads if isinstance(heads, (list, tuple)) else (heads,)):
             ops.check_heads(count)
-    return KcpContext(part.cu_seqlens_global, group, int(rank), part.world_size, device, conv_kernel_size, part.layout)
+    return KcpContext(part.cu_seqlens_global, group, int(rank), part.world_size, device, conv_kernel_size,
+                      "contiguous" if part.fragments is not None else part.layout, part.fragments)
 
 
 def _no_options(options: dict[str, Any]) -> None:
@@ -114,9 +119,20 @@ def _shard(q, k, v, g, beta, ctx: KcpContext):
     return q3, k3, v3, g3, beta3.float().contiguous()
 
 
+def _exchange_of(ctx: KcpContext):
+    """The state exchange of a call: the GDN op's ``--cake-gdn-kcp-exchange`` (``auto``: sequential on two ranks of
+    the contiguous layout, else the parallel exchange of fragment summaries, which serves every layout)."""
+    return ctx.exchange(str(config.option("gdn", "cake_gdn_kcp_exchange") or "auto"))
+
+
 def _forward_kcp(q3, k3, v3, g3, beta32, ctx: KcpContext, scale: float, l2norm: bool):
-    exchange = ctx.exchange("sequential")
+    exchange = _exchange_of(ctx)
     num_seqs, heads = len(ctx.cu_seqlens_cpu) - 1, q3.shape[1]
+    if hasattr(exchange, "kda_forward_state"):  # every rank works at once
+        with torch.cuda.device(q3.device):
+            o, saved, _ = ops._forward(q3, k3, v3, g3, beta32, ctx.cu_seqlens, scale, l2norm,
+                                       cu_seqlens_cpu=ctx.cu_seqlens_cpu, state_provider=exchange.kda_forward_state)
+        return o, saved
     with torch.cuda.device(q3.device):
         h0 = exchange.incoming_state(num_seqs, heads, q3.device)
         want_final = ctx.continues_out and ctx.world_size > 1
@@ -128,8 +144,13 @@ def _forward_kcp(q3, k3, v3, g3, beta32, ctx: KcpContext, scale: float, l2norm: 
 
 
 def _backward_kcp(saved, v3, beta32, do3, ctx: KcpContext):
-    exchange = ctx.exchange("sequential")
+    exchange = _exchange_of(ctx)
     num_seqs, heads = len(ctx.cu_seqlens_cpu) - 1, v3.shape[1]
+    if hasattr(exchange, "kda_backward_state"):
+        with torch.cuda.device(v3.device):
+            dq, dk, dv, dg, dbeta, _ = ops._backward(saved, v3, beta32, do3,
+                                                     adjoint_provider=exchange.kda_backward_state)
+        return dq, dk, dv, dg, dbeta
     with torch.cuda.device(v3.device):
         dht = exchange.incoming_adjoint(num_seqs, heads, v3.device)
         want_dh0 = ctx.continues_in and ctx.world_size > 1

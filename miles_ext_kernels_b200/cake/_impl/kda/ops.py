@@ -188,10 +188,11 @@ def _scan_backward(dims, meta, s, do, dht, dh, dv_new, want_dh0: bool):
 
 
 def _forward(q, k, v, g, beta32, cu_seqlens, scale, use_qk_l2norm, *, cu_seqlens_cpu=None, h0=None,
-             want_final=False):
+             want_final=False, state_provider=None):
     """q, k, v ``[S, H, 128]`` bf16 contiguous; g fp32 ``[S, H, 128]``; beta32 fp32 ``[S, H]``.  ``h0`` (fp32
-    ``[N, H, 128, 128]`` or None) and ``want_final`` are the boundary states of a context-parallel call; returns
-    ``(o, saved, final_state | None)``."""
+    ``[N, H, 128, 128]`` or None) and ``want_final`` are the boundary states of a context-parallel call;
+    ``state_provider(dims, meta, kr, w, u, gl2, status) -> h0`` computes them from the scan's operands instead (the
+    parallel exchange, which summarises this rank's fragments first).  Returns ``(o, saved, final_state | None)``."""
     device = q.device
     S, H = q.shape[0], q.shape[1]
     meta = meta_module.chunk_meta(cu_seqlens, cu_seqlens_cpu, 1, S, device)
@@ -215,6 +216,8 @@ def _forward(q, k, v, g, beta32, cu_seqlens, scale, use_qk_l2norm, *, cu_seqlens
     native.launch("kda_intra", dims, q, k, v, kg, g2, beta32, a, aqk, w, u, status, device=device)
     h = torch.zeros((NC, H, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
     v_new = torch.empty_like(v)
+    if state_provider is not None:
+        h0 = state_provider(dims, meta, kr, w, u, gl2, status)
     final = _scan_forward(dims, meta, kr, w, u, gl2, h0, h, v_new, want_final, status)
     o = torch.empty_like(v)
     native.launch("kda_fwd_o", dims, qg, aqk, v_new, h, o, status, device=device)
@@ -222,7 +225,7 @@ def _forward(q, k, v, g, beta32, cu_seqlens, scale, use_qk_l2norm, *, cu_seqlens
     return o, saved, final
 
 
-def _backward(s: Saved, v, beta32, do, *, dht=None, want_dh0=False):
+def _backward(s: Saved, v, beta32, do, *, dht=None, want_dh0=False, adjoint_provider=None):
     """Returns ``(dq, dk, dv, dg, dbeta, dh0 | None)``; ``dht`` / ``want_dh0``: the boundary adjoint states of a
     context-parallel call (fp32 ``[N, H, 128, 128]``)."""
     device = do.device
@@ -233,6 +236,8 @@ def _backward(s: Saved, v, beta32, do, *, dht=None, want_dh0=False):
     take = lambda role, shape, dtype: workspace.take(OP, role, shape, dtype, device)  # noqa: E731
     dh = torch.zeros((NC, H, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)  # pad chunks are never written
     dv_new = take("dv_new", (S, H, HEAD_DIM), BF16)
+    if adjoint_provider is not None:
+        dht = adjoint_provider(dims, meta, s, do)
     dh0 = _scan_backward(dims, meta, s, do, dht, dh, dv_new, want_dh0)
     m1 = take("m1", (NC, H, 64, 64), F32)
     m2 = take("m2", (NC, H, 64, 64), F32)

@@ -40,6 +40,14 @@ def _emulated_context(cu, rank, world, layout, board):
             self._reverse = True
             return super().backward_begin(*args)
 
+        def kda_forward_state(self, *args):
+            self._reverse = False
+            return super().kda_forward_state(*args)
+
+        def kda_backward_state(self, *args):
+            self._reverse = True
+            return super().kda_backward_state(*args)
+
     class Context(kcp.KcpContext):
         def exchange(self, mode="auto"):
             return Exchange(self)
@@ -90,6 +98,52 @@ def test_layouts_against_the_undivided_call(world, seq_lens, layout, gate):
     o.backward(x["do"].unsqueeze(0).to(dev))
     want = {"o": o.detach()[0], **{f"d{n}": t.grad[0] for n, t in leaves.items()}, "dbeta": beta.grad[0]}
     for name, ref in want.items():
+        got = torch.zeros_like(ref)
+        for ctx, out in results:
+            at = 0
+            for f in ctx.fragments:
+                got[cu[f.doc] + f.offset : cu[f.doc] + f.end] = out[name][at : at + f.length]
+                at += f.length
+        ok, m = O.within_budget(got.float().cpu(), ref.float().cpu(), rel_rms_max=6e-3, max_abs_rel=2e-2)
+        assert ok, (name, m)
+
+
+@pytest.mark.parametrize("world,seq_lens,layout", [
+    (2, (1500, 548), "contiguous"), (4, (3000, 1096), "zigzag"), (2, (1024, 2048), "zigzag_per_document"),
+])
+def test_kda_layouts_against_the_undivided_call(world, seq_lens, layout):
+    """The per-channel-decay variant through the same exchange: its fragments' summaries come from its own pre-scans
+    (every summary exact, no warm-up rule)."""
+    from miles_ext_kernels_b200.cake import kda
+    from oracle import gdn_oracle as O
+    from test_kda_gpu import NAMES, draw as draw_kda
+
+    dev = torch.device("cuda")
+    H = 2
+    x = draw_kda(seq_lens, H, seed=61, gate="faint")
+    cu = (0, *torch.tensor(seq_lens).cumsum(0).tolist())
+    board = {"forward": [None] * world, "backward": [None] * world}
+
+    def run_rank(rank):
+        ctx = _emulated_context(cu, rank, world, layout, board)
+        mine = lambda t: _take(t, cu, ctx.fragments).to(dev)  # noqa: E731
+        leaves = {n: mine(x[n]).requires_grad_(True) for n in ("q", "k", "v", "g", "beta")}
+        o = kda.chunk_kda_kcp(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"], ctx)
+        o.backward(mine(x["do"]))
+        return ctx, {"o": o.detach(), **{f"d{n}": t.grad for n, t in leaves.items()}}
+
+    for _ in range(2):
+        for rank in range(world):
+            with pytest.raises(_Published):
+                run_rank(rank)
+    results = [run_rank(rank) for rank in range(world)]
+    leaves = {n: x[n].to(dev).requires_grad_(True) for n in ("q", "k", "v", "g", "beta")}
+    o = kda.chunk_kda(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves["beta"],
+                      torch.tensor(cu, dtype=torch.int32, device=dev))
+    o.backward(x["do"].to(dev))
+    want = {"o": o.detach(), **{f"d{n}": t.grad for n, t in leaves.items()}}
+    for name in NAMES:
+        ref = want[name]
         got = torch.zeros_like(ref)
         for ctx, out in results:
             at = 0

@@ -44,11 +44,14 @@ def test_partition_and_context_on_the_host():
     assert first.cu_seqlens_cpu == (0, 320, 512) and not first.continues_in and first.continues_out
     assert second.cu_seqlens_cpu == (0, 512) and second.continues_in and not second.continues_out
     assert first.num_tokens == second.num_tokens == 512
-    for layout in ("zigzag", "zigzag_per_document"):
-        with pytest.raises(NotImplementedError, match="contiguous"):
-            kda.partition_kcp((0, 1024), 2, layout)
-    with pytest.raises(NotImplementedError):
-        kda.partition_kcp((0, 1024), 2, fragments=[[(0, 0, 512)], [(0, 512, 1024)]])
+    zig = kda.build_context_kcp(kda.partition_kcp((0, 320, 1024), 2, "zigzag"), object(), 0, "cpu")
+    assert zig.layout == "zigzag" and zig.cu_seqlens_cpu == (0, 256, 512)  # pieces 0 and 3 of four
+    table = kda.partition_kcp((0, 1024), 2, fragments=[[(0, 0, 512)], [(0, 512, 512)]])
+    assert table.layout == "explicit" and kda.build_context_kcp(table, object(), 1, "cpu").continues_in
+    with pytest.raises(ValueError, match="held by no rank"):
+        kda.partition_kcp((0, 1024), 2, fragments=[[(0, 0, 512)], [(0, 512, 256)]])
+    with pytest.raises(NotImplementedError, match="cut points"):
+        kda.partition_kcp((0, 1024), 2, cut_points=(512,))
     with pytest.raises(ValueError, match="divide"):
         kda.partition_kcp((0, 1023), 2)
     with pytest.raises(ValueError, match="start at 0"):
