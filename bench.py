@@ -189,10 +189,10 @@ KERNEL_BYTES.update({
 # (H=16, HV=32; profiles/gdn_kernels_8192_tokens_full_set.md).  Every tensor is per token or per chunk, so traffic
 # grows in proportion to the tokens: `roofline.traffic` scales these to the launch that was timed.
 NCU_TRAFFIC_BYTES_AT_8192_TOKENS = {
-    "gdn_wy_fwd": 136.9e6 + 149.8e6,
-    "gdn_fwd_ho": 237.4e6 + 224.8e6,
-    "gdn_bwd_dh": 237.4e6 + 154.8e6,
-    "gdn_bwd_tail": 807.9e6 + 123.8e6,
+    "gdn_wy_fwd": 136.9e6 + 149.2e6,
+    "gdn_fwd_ho": 237.5e6 + 225.8e6,
+    "gdn_bwd_dh": 237.4e6 + 154.6e6,
+    "gdn_bwd_tail": 807.5e6 + 122.8e6,
 }
 KERNEL_FLOPS = {  # per (chunk, value head): dense contractions as 2 m n k
     "gdn_wy_fwd": 2 * 128 * 64 * 128 + 2 * 64**3 / 3 + 2 * 2 * 64 * 128 * 64,
