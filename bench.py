@@ -6,6 +6,14 @@ One "step" is one forward + backward of ``chunk_gated_delta_rule`` over one synt
 runs the whole workload (the path has no cross-(sequence, head) coupling: ranks shard independent batches, no
 collective on the data path), so scaling is weak and ``value`` is ``N x tokens / max-over-ranks time``.
 
+The one configuration with a real exchange between ranks -- one long sequence split context-parallel -- is timed and
+checked on the same line when N >= 2:
+  cp            one sequence of N x 32,768 tokens (H = HV = 32) in contiguous slices through
+                ``kcp_chunk_gated_delta_rule``: ms per step (max over ranks), whole-job tokens/s, efficiency = the
+                slice alone / the N-rank step, the exchange's own device time and the bytes each rank receives
+  cp_parity     o and every gradient of a short case (N x 2,048 tokens) gathered to rank 0, against the undivided call
+  kda_sharded   the per-channel-decay variant with one 4,096-token sequence per rank (no exchange)
+
 Printed JSON line (rank 0):
   value         tokens/s with the inputs resident in HBM, device-timed (CUDA events), K steps, max over ranks
   e2e           the same metric through the public entry point with HOST (pinned) buffers: every step copies its
@@ -13,11 +21,12 @@ Printed JSON line (rank 0):
   roofline      the dominant kernel: achieved = its algorithmic HBM bytes (or FLOPs) per launch / its mean device
                 time, measured live with CUDA events around each launch in a separate profiled pass of the same steps
   path_roofline the whole step against max(FLOPs / tensor peak, compulsory bytes / HBM peak)
-  cpu_baseline  the CPU oracle (a port of the reference's torch path) timed on this host's cores on a bounded sample
+  cpu_baseline  the reference's own CPU path (its torch emulation through its public entry point, from
+                ``oracle/_ref``; the oracle port where that cannot run) timed on this host's cores on a bounded sample
   clocks        SM clocks and throttle reasons sampled with nvidia-smi during the timed region
 
-``--impl reference`` times the CPU oracle alone (the reference's own kernels need CUDA >= 13.4 and cannot be built
-with this toolkit; its torch emulation path is what the oracle restates), on rank 0 only.
+``--impl reference`` times that CPU path alone, on rank 0 only (the reference's own kernels need CUDA >= 13.4 and
+cannot be built with this toolkit).  Both CPU legs use the same sample of the workload, named in ``config``.
 """
 
 from __future__ import annotations
@@ -100,29 +109,44 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------------------------------------
-# the CPU arm (oracle port): the only place bench.py touches oracle/
+# the CPU arm: the only place bench.py touches oracle/
 # --------------------------------------------------------------------------------------------------------------------
-def cpu_tokens_per_sec(workload_name: str, sample_tokens: int, steps: int, warmup: int) -> dict:
+CPU_SAMPLE_TOKENS = 2048  # of the workload, for both CPU legs (the reference's CPU path does ~0.4-1 k tokens/s)
+
+
+def cpu_tokens_per_sec(workload_name: str, steps: int, warmup: int) -> dict:
+    """Forward + backward on the host's cores over the first ``CPU_SAMPLE_TOKENS`` tokens of the workload: through the
+    reference's own CPU path (``oracle/_ref``: packed call, no initial / final state, as its context-parallel
+    contract has it) when it is there and can run the workload, else through the oracle port."""
     from oracle import gdn_oracle as oracle
+    from oracle import reference_arm
 
     from miles_ext_kernels_b200.workloads import make_workload
 
     cores = len(os.sched_getaffinity(0))
     torch.set_num_threads(cores)
-    work = make_workload(workload_name, tokens=sample_tokens)
+    work = make_workload(workload_name, tokens=CPU_SAMPLE_TOKENS)
     B, T = work.q.shape[:2]
-    flat = lambda t: t.reshape(B * T, *t.shape[2:]).float()  # noqa: E731
+    flat = lambda t: t.reshape(B * T, *t.shape[2:])  # noqa: E731
     seq_lens = tuple(b - a for a, b in zip(work.cu_seqlens[:-1], work.cu_seqlens[1:])) if work.cu_seqlens else (T,) * B
-    args = [flat(t) for t in (work.q, work.k, work.v, work.g, work.beta)]
+    use_reference = reference_arm.available() and work.config.op == "gdn" and work.h0 is None
+    if use_reference:
+        cu = (0, *(sum(seq_lens[: i + 1]) for i in range(len(seq_lens))))
+        args = [flat(t) for t in (work.q, work.k, work.v, work.g, work.beta, work.do)]
 
-    def step():
-        if work.config.op == "kda":
-            from oracle import kda_oracle
+        def step():
+            reference_arm.forward_backward(*args, cu)
+    else:
+        args = [flat(t).float() for t in (work.q, work.k, work.v, work.g, work.beta)]
 
-            kda_oracle.chunked_forward_backward(*args, seq_lens, flat(work.do))
-        else:
-            oracle.chunked_forward_backward(*args, seq_lens, flat(work.do), h0=work.h0, dht=work.dht,
-                                            output_final_state=work.config.final_state)
+        def step():
+            if work.config.op == "kda":
+                from oracle import kda_oracle
+
+                kda_oracle.chunked_forward_backward(*args, seq_lens, flat(work.do).float())
+            else:
+                oracle.chunked_forward_backward(*args, seq_lens, flat(work.do).float(), h0=work.h0, dht=work.dht,
+                                                output_final_state=work.config.final_state)
 
     for _ in range(warmup):
         step()
@@ -130,9 +154,11 @@ def cpu_tokens_per_sec(workload_name: str, sample_tokens: int, steps: int, warmu
     for _ in range(steps):
         step()
     seconds = time.perf_counter() - start
+    how = ("the reference's own torch emulation through its public entry point (oracle/_ref), packed, no final state"
+           if use_reference else "the oracle port, fp32 torch")
     return {
-        "value": B * T * steps / seconds, "unit": UNIT, "cores": cores, "kind": "port",
-        "sample": f"{workload_name} cut to {B * T} tokens (B={B}, T={T}), all heads, fp32 torch on the host, "
+        "value": B * T * steps / seconds, "unit": UNIT, "cores": cores, "kind": "reference" if use_reference else "port",
+        "sample": f"{workload_name} cut to {B * T} tokens (B={B}, T={T}), all heads, {how}, on the host, "
                   f"{steps} step(s) after {warmup} warm-up",
         "seconds_per_step": seconds / steps, "tokens": B * T,
     }
@@ -142,13 +168,12 @@ def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 4096 if args.steps + args.warmup <= 8 else 1024
-    cpu = cpu_tokens_per_sec(args.workload, sample, args.steps, args.warmup)
+    cpu = cpu_tokens_per_sec(args.workload, args.steps, args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * cpu["seconds_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "sample": cpu["sample"]},
+        "config": {"workload": args.workload, "sample": cpu["sample"], "cpu_processes": 1},
         "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -185,14 +210,17 @@ KERNEL_BYTES.update({
                                    + 2 * 512 + 256 + 512 + 4) * HV,
     "qk_grad_finish": lambda H, HV: (512 + 256) * HV,
 })
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch in the committed ncu capture of an 8,192-token cut of cfg1
-# (H=16, HV=32; profiles/gdn_kernels_8192_tokens_full_set.md).  Every tensor is per token or per chunk, so traffic
-# grows in proportion to the tokens: `roofline.traffic` scales these to the launch that was timed.
-NCU_TRAFFIC_BYTES_AT_8192_TOKENS = {
-    "gdn_wy_fwd": 136.9e6 + 149.2e6,
-    "gdn_fwd_ho": 237.5e6 + 225.8e6,
-    "gdn_bwd_dh": 237.4e6 + 154.6e6,
-    "gdn_bwd_tail": 807.5e6 + 122.8e6,
+# Measured DRAM traffic per token (dram__bytes_read.sum + dram__bytes_write.sum of one launch under ncu, divided by
+# the launch's tokens), keyed by the head counts of the capture and the kernel.  Every tensor of the path is per
+# token or per chunk, so traffic grows in proportion to the tokens: `roofline.traffic` scales these to the launch that
+# was timed; a head configuration that was never captured reports null.
+NCU_TRAFFIC_BYTES_PER_TOKEN = {
+    (16, 32): {  # an 8,192-token cut of cfg1
+        "gdn_wy_fwd": (136.9e6 + 149.2e6) / 8192,
+        "gdn_fwd_ho": (237.5e6 + 225.8e6) / 8192,
+        "gdn_bwd_dh": (237.4e6 + 154.6e6) / 8192,
+        "gdn_bwd_tail": (807.5e6 + 122.8e6) / 8192,
+    },
 }
 KERNEL_FLOPS = {  # per (chunk, value head): dense contractions as 2 m n k
     "gdn_wy_fwd": 2 * 128 * 64 * 128 + 2 * 64**3 / 3 + 2 * 2 * 64 * 128 * 64,
@@ -203,6 +231,194 @@ KERNEL_FLOPS = {  # per (chunk, value head): dense contractions as 2 m n k
     # 4 products [64 x 128, K = 128], 3 of [64 x 64, K = 128], 6 of [64 x 128, K = 64], 2 of [64 x 64, K = 64]
     "gdn_bwd_tail": 4 * 2 * 64 * 128 * 128 + 3 * 2 * 64 * 64 * 128 + 6 * 2 * 64 * 128 * 64 + 2 * 2 * 64**3,
 }
+
+
+class Clock:
+    """Device time of a run of steps, max over ranks, with a barrier and a synchronisation on both sides."""
+
+    def __init__(self, device, world: int) -> None:
+        self.device, self.world = device, world
+
+    def barrier(self) -> None:
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, value: float) -> float:
+        t = torch.tensor([value], dtype=torch.float64, device=self.device)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(self, fn, steps: int) -> float:
+        """Device milliseconds of `steps` calls of fn, max over ranks."""
+        self.barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        self.barrier()
+        return self.max_over_ranks(start.elapsed_time(end))
+
+
+def _leaves(x: dict, names=("q", "k", "v", "g", "beta")):
+    return [x[n].detach().requires_grad_(True) for n in names]
+
+
+def context_parallel(clock: Clock, device, rank: int, world: int, steps: int) -> dict:
+    """One sequence of ``world x 32,768`` tokens, H = HV = 32, in contiguous slices, one per rank: forward + backward
+    through ``kcp_chunk_gated_delta_rule`` with each of the two boundary-state exchanges, against the same slice run
+    alone (no context, no exchange) on every rank."""
+    import miles_ext_kernels_b200 as package
+    from miles_ext_kernels_b200.cake import gdn
+    from miles_ext_kernels_b200.cake._impl.gdn import kcp
+    from miles_ext_kernels_b200.workloads import make_workload
+
+    work = make_workload("cfg4", seed=4 + 1000 * rank)  # this rank's slice: the same distributions, its own values
+    T, H, HV = work.q.shape[1], work.q.shape[2], work.v.shape[2]
+    x = {n: getattr(work, n).to(device) for n in ("q", "k", "v", "g", "beta", "do")}
+    cu_local = (0, T)
+    cu_dev = torch.tensor(cu_local, dtype=torch.int32, device=device)
+    context = gdn.build_kcp_context((0, world * T), device=device)
+
+    def alone():
+        q, k, v, g, beta = _leaves(x)
+        o, _ = gdn.chunk_gated_delta_rule(q, k, v, g=g, beta=beta, cu_seqlens=cu_dev, cu_seqlens_cpu=cu_local)
+        o.backward(x["do"])
+
+    def together():
+        q, k, v, g, beta = _leaves(x)
+        gdn.kcp_chunk_gated_delta_rule(q, k, v, g, beta, context).backward(x["do"])
+
+    for _ in range(3):
+        alone()
+    ms_alone = clock.timed(alone, steps) / steps
+    out = {"workload": f"cfg4: one sequence of {world * T} tokens, H=HV={HV}, d=128, {world} contiguous slices of {T}",
+           "slice_alone_ms": ms_alone, "modes": {}}
+    for mode in ("parallel", "sequential"):
+        package.configure(cake_gdn_variant="det", cake_gdn_kcp_exchange=mode)
+        for _ in range(3):
+            together()
+        ms = clock.timed(together, steps) / steps
+        log = kcp.ExchangeLog()
+        kcp.set_exchange_log(log)
+        for _ in range(steps):
+            together()
+        torch.cuda.synchronize()
+        kcp.set_exchange_log(None)
+        spent = log.milliseconds()
+        out["modes"][mode] = {
+            "ms_per_step": ms, "value": world * T / (ms * 1e-3), "unit": UNIT, "efficiency": ms_alone / ms,
+            "exchange_ms_forward": clock.max_over_ranks(spent.get("forward", 0.0) / steps),
+            "exchange_ms_backward": clock.max_over_ranks(spent.get("backward", 0.0) / steps),
+            "bytes_received_per_rank_per_step": clock.max_over_ranks(log.bytes_received / steps),
+        }
+    package.configure(cake_gdn_variant="det")
+    best = min(out["modes"], key=lambda m: out["modes"][m]["ms_per_step"])
+    out.update(exchange=best, **out["modes"][best])
+    out["what"] = ("exchange_ms_*: pre-scan of the rank's fragment + all-gather of the (B, M) summaries + fold (parallel), "
+                   "or the wait for the neighbour's state + its transfer (sequential); device time, max over ranks")
+    return out
+
+
+def context_parallel_parity(device, rank: int, world: int) -> dict:
+    """A short sequence (``world x 2,048`` tokens, H = HV = 32) split over the ranks: o and every gradient gathered to
+    rank 0 and compared with the undivided call on rank 0.  Budgets: relative RMS error <= 6e-3 and largest error <=
+    2e-2 of the largest reference magnitude, per tensor.  Weak gates (g = -0.5 U(0, 1)) carry state across every
+    cut; the benchmark's strong gates are checked too."""
+    import torch.distributed as dist
+
+    import miles_ext_kernels_b200 as package
+    from miles_ext_kernels_b200.cake import gdn
+
+    T, H, HV = 2048, 32, 32
+    S = world * T
+    names = ("q", "k", "v", "g", "beta", "do")
+    cases, ok = {}, True
+    for gate in ("weak", "strong"):
+        gen = torch.Generator(device=device).manual_seed(40 if gate == "weak" else 41)
+        full = {}
+        if rank == 0:
+            unit = lambda t: t / torch.sqrt((t * t).sum(-1, keepdim=True) + 1e-6)  # noqa: E731
+            full["q"] = unit(torch.randn(1, S, H, 128, device=device, generator=gen)).bfloat16()
+            full["k"] = unit(torch.randn(1, S, H, 128, device=device, generator=gen)).bfloat16()
+            full["v"] = torch.randn(1, S, HV, 128, device=device, generator=gen).bfloat16()
+            full["beta"] = torch.sigmoid(torch.randn(1, S, HV, device=device, generator=gen)).bfloat16()
+            u = torch.rand(1, S, HV, device=device, generator=gen)
+            if gate == "weak":
+                full["g"] = -0.5 * u
+            else:
+                a = torch.randn(1, S, HV, device=device, generator=gen)
+                full["g"] = -torch.nn.functional.softplus(a) * torch.exp(u * math.log(16.0))
+            full["do"] = torch.randn(1, S, HV, 128, device=device, generator=gen).bfloat16()
+        else:
+            for n in names:
+                heads = H if n in ("q", "k") else HV
+                shape = (1, S, heads, 128) if n in ("q", "k", "v", "do") else (1, S, heads)
+                full[n] = torch.empty(shape, dtype=torch.float32 if n == "g" else torch.bfloat16, device=device)
+        for n in names:
+            dist.broadcast(full[n], src=0)
+        mine = {n: full[n][:, rank * T:(rank + 1) * T].contiguous() for n in names}
+        want = None
+        if rank == 0:
+            leaves = _leaves(full)
+            cu = (0, S)
+            o, _ = gdn.chunk_gated_delta_rule(*leaves[:3], g=leaves[3], beta=leaves[4], cu_seqlens_cpu=cu,
+                                              cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=device))
+            o.backward(full["do"])
+            want = [o.detach()] + [t.grad for t in leaves]
+        context = gdn.build_kcp_context((0, S), device=device)
+        for mode in ("parallel", "sequential"):
+            package.configure(cake_gdn_variant="det", cake_gdn_kcp_exchange=mode)
+            leaves = _leaves(mine)
+            o = gdn.kcp_chunk_gated_delta_rule(*leaves, context)
+            o.backward(mine["do"])
+            worst_rms = worst_abs = 0.0
+            for i, local in enumerate([o.detach()] + [t.grad for t in leaves]):
+                whole = torch.empty((world * local.shape[1], *local.shape[2:]), dtype=local.dtype, device=device)
+                dist.all_gather_into_tensor(whole, local[0].contiguous())
+                if rank == 0:
+                    ref, got = want[i][0].float(), whole.float()
+                    err = got - ref
+                    worst_rms = max(worst_rms, float(err.norm() / ref.norm().clamp_min(1e-30)))
+                    worst_abs = max(worst_abs, float(err.abs().max() / ref.abs().max().clamp_min(1e-30)))
+            passed = worst_rms <= 6e-3 and worst_abs <= 2e-2
+            ok = ok and passed
+            cases[f"{gate}/{mode}"] = {"rel_rms": worst_rms, "max_abs_rel": worst_abs, "ok": passed}
+        del full, mine, want
+    package.configure(cake_gdn_variant="det")
+    return {"ok": ok, "tokens": S, "num_heads": HV, "tensors": "o, dq, dk, dv, dg, dbeta", "worst_over_tensors": cases,
+            "budget": {"rel_rms": 6e-3, "max_abs_rel": 2e-2}}
+
+
+def kda_one_sequence_per_rank(clock: Clock, device, rank: int, world: int, steps: int) -> dict:
+    """The per-channel-decay variant sharded by batch: one 4,096-token sequence (H = 32) per rank, no exchange."""
+    from miles_ext_kernels_b200.cake import kda
+    from miles_ext_kernels_b200.workloads import bytes_per_token, flops_per_token, make_workload
+
+    work = make_workload("cfg3", seed=3 + 1000 * rank)
+    x = {n: getattr(work, n).to(device) for n in ("q", "k", "v", "g", "beta", "do")}
+    cu_dev = torch.tensor(work.cu_seqlens, dtype=torch.int32, device=device)
+    tokens, H = work.num_tokens, work.q.shape[2]
+
+    def step():
+        q, k, v, g, beta = _leaves(x)
+        kda.chunk_kda(q, k, v, g, beta, cu_dev, cu_seqlens_cpu=work.cu_seqlens).backward(x["do"])
+
+    for _ in range(3):
+        step()
+    ms = clock.timed(step, steps) / steps
+    peak, peak_kind = peaks()
+    t_roof = max(flops_per_token(H) * tokens / (peak["bf16_tflops_sustained"] * 1e12),
+                 bytes_per_token(H, H, op="kda") * tokens / (peak["hbm_gbs"] * 1e9))
+    return {"workload": f"cfg3: KDA, one sequence of {tokens} tokens per GPU, H={H}, d=128", "ms_per_step": ms,
+            "value": world * tokens / (ms * 1e-3), "unit": UNIT,
+            "path_roofline_frac": t_roof / (ms * 1e-3), "peak_source": f"of {peak_kind}"}
 
 
 def run_ours(args) -> None:
@@ -253,24 +469,8 @@ def run_ours(args) -> None:
             [final] if final is not None else [])
         return outs
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps: int) -> float:
-        """Device milliseconds of `steps` calls of fn, max over ranks."""
-        barrier()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            fn()
-        end.record()
-        barrier()
-        ms = torch.tensor([start.elapsed_time(end)], device=device)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+    clock = Clock(device, world)
+    timed = clock.timed
 
     # clocks are sampled from the warm-up on (a 10-step timed region is shorter than nvidia-smi's sampling period);
     # only samples taken under load enter the median
@@ -305,11 +505,30 @@ def run_ours(args) -> None:
     def e2e_step():
         return pipeline.run(host, lambda part, t: step(t, part_cu.get(id(part))), range(6), total)
 
-    e2e_step()
+    landing = e2e_step()
     ms_e2e = timed(e2e_step, args.steps)
     h2d = sum(t.numel() * t.element_size() for t in host.values())
-    d2h = sum(x.numel() * x.element_size() for x in e2e_step())
+    d2h = sum(x.numel() * x.element_size() for x in landing)
     torch.cuda.synchronize()
+
+    # the copy floor of this box at this N: the step's bytes in and out on two streams at once, no kernel in between
+    # (every rank at the same time; the ranks share the host's memory and its PCIe root ports)
+    side = torch.cuda.Stream(device)
+    sources = [torch.empty(x.shape, dtype=x.dtype, device=device) for x in landing]
+
+    def copies_only():
+        main = torch.cuda.current_stream(device)
+        side.wait_stream(main)
+        for n, t in host.items():
+            resident[n].copy_(t, non_blocking=True)
+        with torch.cuda.stream(side):
+            for src, dst in zip(sources, landing):
+                dst.copy_(src, non_blocking=True)
+        main.wait_stream(side)
+
+    copies_only()
+    ms_floor = timed(copies_only, args.steps)
+    del sources
 
     # the form the training framework calls (GDN only): q, k, v as views of one packed row [q heads | k heads |
     # v heads] (what a fused projection writes), raw q / k with the L2 norm inside the op; the op reads the views in
@@ -358,10 +577,10 @@ def run_ours(args) -> None:
     else:
         roofline = {"bound": "hbm", "achieved": gbs, "peak": peak["hbm_gbs"], "unit": "GB/s", "frac": frac_hbm}
     traffic = None
-    if (H, HV) == (16, 32) and top in NCU_TRAFFIC_BYTES_AT_8192_TOKENS:
-        traffic = NCU_TRAFFIC_BYTES_AT_8192_TOKENS[top] * tokens / 8192
+    if top in NCU_TRAFFIC_BYTES_PER_TOKEN.get((H, HV), {}):
+        traffic = NCU_TRAFFIC_BYTES_PER_TOKEN[(H, HV)][top] * tokens
     roofline.update(kernel=top, ms_per_launch=mean_ms, traffic=traffic, traffic_unit="bytes per launch",
-                    traffic_source="ncu capture at 8,192 tokens, scaled by tokens", peak_source=f"of {peak_kind}",
+                    traffic_source="ncu capture of a smaller cut, scaled by tokens", peak_source=f"of {peak_kind}",
                     share_of_step=per_kernel[top][2] / sum(v[2] for v in per_kernel.values()))
 
     step_s = ms * 1e-3 / args.steps
@@ -375,9 +594,17 @@ def run_ours(args) -> None:
         "config": {"workload": f"{cfg.name}: {cfg.description}", "tokens_per_gpu": tokens, "num_qk_heads": H,
                    "num_v_heads": HV, "head_dim": 128, "chunk": 64, "state": "fp32",
                    "l2_hygiene": "inputs (q+k+v+dO = 768 MiB at cfg1) are larger than the 126 MB L2",
-                   "sharding": "each rank runs the whole workload; no collective on the data path"},
+                   "sharding": "each rank runs the whole workload; no collective on the data path (the context-parallel "
+                               "configuration, which has one, is the `cp` block of this line when N >= 2)",
+                   "cpu_sample_tokens": CPU_SAMPLE_TOKENS},
         "e2e": {"value": world * tokens / (ms_e2e * 1e-3 / args.steps), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps, "parts": len(parts)},
+                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps, "parts": len(parts),
+                "copy_floor_ms": ms_floor / args.steps,
+                "copy_floor_gbs_per_rank": {"h2d": h2d / (ms_floor * 1e-3 / args.steps) / 1e9,
+                                            "d2h": d2h / (ms_floor * 1e-3 / args.steps) / 1e9},
+                "copy_floor_what": "the step's bytes in and out on two streams at once with no kernel between them, "
+                                   "every rank at the same time (max over ranks): what this host's PCIe and memory "
+                                   "allow at this N"},
         "gpu_launches": launches,
         "roofline": roofline,
         "path_roofline": {"t_roof_ms": 1e3 * t_roof, "frac": t_roof / step_s, "flops_per_token": flops_per_token(HV),
@@ -386,8 +613,17 @@ def run_ours(args) -> None:
         "kernels_ms": {n: {"mean": v[0], "launches": v[1], "total": v[2]} for n, v in per_kernel.items()},
         "clocks": clocks,
     }
+    # free this workload before the others
+    del resident, host, work, pipeline, landing
+    torch.cuda.empty_cache()
+    if not args.no_extra:
+        line["kda_sharded"] = kda_one_sequence_per_rank(clock, device, rank, world, args.steps)
+        if world > 1:
+            line["cp"] = context_parallel(clock, device, rank, world, args.steps)
+            torch.cuda.empty_cache()
+            line["cp_parity"] = context_parallel_parity(device, rank, world)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_tokens_per_sec(args.workload, 8192, 1, 1)
+        cpu = cpu_tokens_per_sec(args.workload, 1, 1)
         line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if rank == 0:
         print(json.dumps(line))
@@ -486,6 +722,7 @@ def main() -> None:
     parser.add_argument("--tokens", type=int, default=None, help="cut the workload to this many tokens (profiling)")
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-extra", action="store_true", help="skip the kda_sharded / cp / cp_parity blocks")
     args = parser.parse_args()
     if args.workload in ("conv1d", "gated_rmsnorm"):
         run_adjacent(args)

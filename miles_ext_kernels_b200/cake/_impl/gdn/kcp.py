@@ -35,7 +35,52 @@ LAYOUTS = layout_module.KCP_LAYOUTS
 _CACHE_LIMIT = 32
 _CONTEXTS: OrderedDict[tuple[Any, ...], KcpContext] = OrderedDict()
 
-__all__ = ["KcpContext", "build_kcp_context", "document_run", "halo_rows", "local_partition", "release"]
+__all__ = ["ExchangeLog", "KcpContext", "build_kcp_context", "document_run", "halo_rows", "local_partition", "release",
+           "set_exchange_log"]
+
+
+class ExchangeLog:
+    """Brackets every boundary-state exchange (pre-scan, gather, fold; or the point-to-point hand-over) with CUDA
+    events on the launching stream and counts the bytes a rank receives.  ``bench.py`` reads the exchange's own device
+    time from it; ordinary calls never time."""
+
+    def __init__(self) -> None:
+        self.events: list[tuple[str, Any, Any]] = []
+        self.bytes_received = 0
+
+    def milliseconds(self) -> dict[str, float]:
+        """Total device time per direction (call after synchronising)."""
+        total: dict[str, float] = {}
+        for name, start, end in self.events:
+            total[name] = total.get(name, 0.0) + start.elapsed_time(end)
+        return total
+
+
+_exchange_log: ExchangeLog | None = None
+
+
+def set_exchange_log(log: ExchangeLog | None) -> None:
+    global _exchange_log
+    _exchange_log = log
+
+
+class _Timed:
+    """``with _Timed("forward"):`` records the bracket in the active :class:`ExchangeLog`, if any."""
+
+    def __init__(self, name: str) -> None:
+        self.name, self.log = name, _exchange_log
+
+    def __enter__(self):
+        if self.log is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        if self.log is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            self.log.events.append((self.name, self.start, end))
 
 
 def local_partition(cu_global: Sequence[int], rank: int, world_size: int):
@@ -183,7 +228,9 @@ class _Exchange:
     def forward_begin(self, dims, meta, k, w, u, g_cs, status):
         """-> ``(h0 or None, keep the final state?)``"""
         ctx = self.context
-        return self.incoming_state(meta.num_seqs, w.shape[1], w.device), ctx.continues_out and ctx.world_size > 1
+        with _Timed("forward"):  # includes the wait for the rank before
+            h0 = self.incoming_state(meta.num_seqs, w.shape[1], w.device)
+        return h0, ctx.continues_out and ctx.world_size > 1
 
     def forward_end(self, final_state) -> None:
         if final_state is not None:
@@ -193,7 +240,8 @@ class _Exchange:
     def backward_begin(self, dims, meta, tape, do):
         """-> ``(dht or None, keep dh0?)``"""
         ctx = self.context
-        dht = self.incoming_adjoint(meta.num_seqs, tape.v.shape[1], do.device)
+        with _Timed("backward"):  # includes the wait for the rank after
+            dht = self.incoming_adjoint(meta.num_seqs, tape.v.shape[1], do.device)
         return dht, ctx.continues_in and ctx.world_size > 1
 
     def backward_end(self, dh0) -> None:
@@ -216,6 +264,8 @@ class _Exchange:
 
         h0 = torch.zeros(num_local_seqs, num_v_heads, 128, 128, dtype=torch.float32, device=device)
         dist.recv(h0[0], src=self._peer(-1), group=ctx.group)
+        if _exchange_log is not None:
+            _exchange_log.bytes_received += h0[0].numel() * 4
         return h0
 
     def outgoing_state(self, final_state: torch.Tensor) -> None:
@@ -235,6 +285,8 @@ class _Exchange:
 
         dht = torch.zeros(num_local_seqs, num_v_heads, 128, 128, dtype=torch.float32, device=device)
         dist.recv(dht[-1], src=self._peer(+1), group=ctx.group)
+        if _exchange_log is not None:
+            _exchange_log.bytes_received += dht[-1].numel() * 4
         return dht
 
     def outgoing_adjoint(self, dh0: torch.Tensor) -> None:
@@ -267,6 +319,8 @@ class _ParallelExchange:
         gathered = torch.empty((ctx.world_size * local.shape[0], *local.shape[1:]), dtype=local.dtype,
                                device=local.device)
         dist.all_gather_into_tensor(gathered, local, group=ctx.group)
+        if _exchange_log is not None:
+            _exchange_log.bytes_received += (ctx.world_size - 1) * local.numel() * local.element_size()
         return gathered.view(ctx.world_size, *local.shape)
 
     @staticmethod
@@ -312,8 +366,9 @@ class _ParallelExchange:
             native.launch("gdn_fwd_h_prescan", seg_dims, k, w, u, g_cs, None, frag.flags_fwd, frag.state_row,
                           frag.warm_chunks, frag.warm_log2, summary, status, device=device)
 
-        h0 = self._exchange(dims, meta, HV, device, plan.publish_forward, plan.slots_forward, plan.chain_forward,
-                            summarise, reverse=False)
+        with _Timed("forward"):
+            h0 = self._exchange(dims, meta, HV, device, plan.publish_forward, plan.slots_forward, plan.chain_forward,
+                                summarise, reverse=False)
         return h0, False
 
     def forward_end(self, final_state) -> None:
@@ -360,8 +415,9 @@ class _ParallelExchange:
                           frag.flags_bwd, frag.state_row, frag.warm_chunks, frag.warm_log2, summary, tape.status,
                           device=device)
 
-        dht = self._exchange(dims, meta, HV, device, plan.publish_backward, plan.slots_backward, plan.chain_backward,
-                             summarise, reverse=True)
+        with _Timed("backward"):
+            dht = self._exchange(dims, meta, HV, device, plan.publish_backward, plan.slots_backward,
+                                 plan.chain_backward, summarise, reverse=True)
         return dht, False
 
     def backward_end(self, dh0) -> None:

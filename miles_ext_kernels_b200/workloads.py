@@ -79,9 +79,11 @@ class Workload:
         return self.q.shape[0] * self.q.shape[1]
 
 
-def make_workload(name: str, *, tokens: int | None = None, heads: tuple[int, int] | None = None) -> Workload:
+def make_workload(name: str, *, tokens: int | None = None, heads: tuple[int, int] | None = None,
+                  seed: int | None = None) -> Workload:
     """The workload of configuration ``name``; ``tokens`` / ``heads`` cut it down to a bounded sample of the same
-    distributions (used by the CPU baseline and by small parity cases)."""
+    distributions (used by the CPU baseline and by small parity cases); ``seed`` replaces the configuration's own
+    (ranks that each hold their own piece of a sharded workload draw different values)."""
     cfg = CONFIGS[name]
     H, HV = heads or (cfg.num_qk_heads, cfg.num_v_heads)
     d = cfg.head_dim
@@ -102,7 +104,7 @@ def make_workload(name: str, *, tokens: int | None = None, heads: tuple[int, int
         B, T = 1, sum(seq_lens)
     else:
         B, T = cfg.batch, seq_lens[0]
-    gen = torch.Generator().manual_seed(cfg.seed)
+    gen = torch.Generator().manual_seed(cfg.seed if seed is None else seed)
     q = torch.randn(B, T, H, d, generator=gen)
     k = torch.randn(B, T, H, d, generator=gen)
     v = torch.randn(B, T, HV, d, generator=gen)

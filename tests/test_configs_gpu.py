@@ -59,17 +59,18 @@ def test_cfg1_full_size():
     for name in NAMES:
         assert torch.equal(alone[name][0], first[name][2]), f"batch element alone: {name}"
     assert torch.equal(alone["final_state"][0], first["final_state"][2])
-    # oracle on one sequence and one key-head group (hq = 5 -> value heads 10, 11)
-    b, hq = 1, 5
-    ref = O.chunked_forward_backward(w.q[b, :, hq:hq + 1].float(), w.k[b, :, hq:hq + 1].float(),
-                                     w.v[b, :, 2 * hq:2 * hq + 2].float(), w.g[b, :, 2 * hq:2 * hq + 2],
-                                     w.beta[b, :, 2 * hq:2 * hq + 2].float(), (w.q.shape[1],),
-                                     w.do[b, :, 2 * hq:2 * hq + 2].float(), output_final_state=True)
-    got = {"o": first["o"][b, :, 2 * hq:2 * hq + 2], "dq": first["dq"][b, :, hq:hq + 1],
-           "dk": first["dk"][b, :, hq:hq + 1], "dv": first["dv"][b, :, 2 * hq:2 * hq + 2],
-           "dg": first["dg"][b, :, 2 * hq:2 * hq + 2], "dbeta": first["dbeta"][b, :, 2 * hq:2 * hq + 2],
-           "final_state": first["final_state"][b:b + 1, 2 * hq:2 * hq + 2]}
-    check(got, ref, "cfg1 slice")
+    # the oracle on a sequence and a key-head group (hq -> value heads 2 hq, 2 hq + 1): the first, a middle and the
+    # last key head, each on another batch element
+    for b, hq in ((0, 0), (1, 5), (3, 15)):
+        ref = O.chunked_forward_backward(w.q[b, :, hq:hq + 1].float(), w.k[b, :, hq:hq + 1].float(),
+                                         w.v[b, :, 2 * hq:2 * hq + 2].float(), w.g[b, :, 2 * hq:2 * hq + 2],
+                                         w.beta[b, :, 2 * hq:2 * hq + 2].float(), (w.q.shape[1],),
+                                         w.do[b, :, 2 * hq:2 * hq + 2].float(), output_final_state=True)
+        got = {"o": first["o"][b, :, 2 * hq:2 * hq + 2], "dq": first["dq"][b, :, hq:hq + 1],
+               "dk": first["dk"][b, :, hq:hq + 1], "dv": first["dv"][b, :, 2 * hq:2 * hq + 2],
+               "dg": first["dg"][b, :, 2 * hq:2 * hq + 2], "dbeta": first["dbeta"][b, :, 2 * hq:2 * hq + 2],
+               "final_state": first["final_state"][b:b + 1, 2 * hq:2 * hq + 2]}
+        check(got, ref, f"cfg1 slice b={b} hq={hq}")
 
 
 def test_cfg2_full_size_varlen_with_states():
@@ -78,26 +79,31 @@ def test_cfg2_full_size_varlen_with_states():
     again = run_gdn(w)
     for name in first:
         assert torch.equal(first[name], again[name]), name
-    n, h = 1, 7  # one sequence, one head
-    lo, hi = w.cu_seqlens[n], w.cu_seqlens[n + 1]
-    ref = O.chunked_forward_backward(w.q[0, lo:hi, h:h + 1].float(), w.k[0, lo:hi, h:h + 1].float(),
-                                     w.v[0, lo:hi, h:h + 1].float(), w.g[0, lo:hi, h:h + 1],
-                                     w.beta[0, lo:hi, h:h + 1].float(), (hi - lo,), w.do[0, lo:hi, h:h + 1].float(),
-                                     h0=w.h0[n:n + 1, h:h + 1], dht=w.dht[n:n + 1, h:h + 1], output_final_state=True)
-    got = {name: first[name][0, lo:hi, h:h + 1] for name in NAMES}
-    got["final_state"] = first["final_state"][n:n + 1, h:h + 1]
-    got["dh0"] = first["dh0"][n:n + 1, h:h + 1]
-    check(got, ref, "cfg2 slice")
+    # the shortest and the longest document and one in between; the first, a middle and the last head
+    lengths = [b - a for a, b in zip(w.cu_seqlens, w.cu_seqlens[1:])]
+    shortest, longest = lengths.index(min(lengths)), lengths.index(max(lengths))
+    other = next(n for n in range(len(lengths)) if n not in (shortest, longest))
+    for n, h in ((shortest, 0), (other, 17), (longest, 31)):
+        lo, hi = w.cu_seqlens[n], w.cu_seqlens[n + 1]
+        ref = O.chunked_forward_backward(w.q[0, lo:hi, h:h + 1].float(), w.k[0, lo:hi, h:h + 1].float(),
+                                         w.v[0, lo:hi, h:h + 1].float(), w.g[0, lo:hi, h:h + 1],
+                                         w.beta[0, lo:hi, h:h + 1].float(), (hi - lo,),
+                                         w.do[0, lo:hi, h:h + 1].float(), h0=w.h0[n:n + 1, h:h + 1],
+                                         dht=w.dht[n:n + 1, h:h + 1], output_final_state=True)
+        got = {name: first[name][0, lo:hi, h:h + 1] for name in NAMES}
+        got["final_state"] = first["final_state"][n:n + 1, h:h + 1]
+        got["dh0"] = first["dh0"][n:n + 1, h:h + 1]
+        check(got, ref, f"cfg2 document {n} ({hi - lo} tokens) head {h}")
 
 
 def test_cfg4_one_rank_slice_of_the_long_sequence():
     w = make_workload("cfg4")  # one 32,768-token sequence, H = HV = 32
     first = run_gdn(w)
-    h = 3
-    ref = O.chunked_forward_backward(w.q[0, :, h:h + 1].float(), w.k[0, :, h:h + 1].float(),
-                                     w.v[0, :, h:h + 1].float(), w.g[0, :, h:h + 1], w.beta[0, :, h:h + 1].float(),
-                                     (w.q.shape[1],), w.do[0, :, h:h + 1].float())
-    check({name: first[name][0, :, h:h + 1] for name in NAMES}, ref, "cfg4 slice")
+    for h in (0, 13, 31):  # the first, a middle and the last head
+        ref = O.chunked_forward_backward(w.q[0, :, h:h + 1].float(), w.k[0, :, h:h + 1].float(),
+                                         w.v[0, :, h:h + 1].float(), w.g[0, :, h:h + 1], w.beta[0, :, h:h + 1].float(),
+                                         (w.q.shape[1],), w.do[0, :, h:h + 1].float())
+        check({name: first[name][0, :, h:h + 1] for name in NAMES}, ref, f"cfg4 slice head {h}")
 
 
 def test_cfg3_kda_full_size():
@@ -122,8 +128,8 @@ def test_cfg3_kda_full_size():
     first, again = once(), once()
     for name in first:
         assert torch.equal(first[name], again[name]), name
-    h = 9
-    ref = K.chunked_forward_backward(w.q[0, :, h:h + 1].float(), w.k[0, :, h:h + 1].float(),
-                                     w.v[0, :, h:h + 1].float(), g[:, h:h + 1], w.beta[0, :, h:h + 1].float(), (T,),
-                                     w.do[0, :, h:h + 1].float())
-    check({name: first[name][:, h:h + 1] for name in NAMES}, ref, "cfg3 slice")
+    for h in (0, 9, 31):  # the first, a middle and the last head
+        ref = K.chunked_forward_backward(w.q[0, :, h:h + 1].float(), w.k[0, :, h:h + 1].float(),
+                                         w.v[0, :, h:h + 1].float(), g[:, h:h + 1], w.beta[0, :, h:h + 1].float(), (T,),
+                                         w.do[0, :, h:h + 1].float())
+        check({name: first[name][:, h:h + 1] for name in NAMES}, ref, f"cfg3 slice head {h}")

@@ -2,8 +2,8 @@
 
 Accuracy budgets are the reference's (reference: tests/cake/gdn/test_gdn_det_gpu.py:58-59, 213-223): per output
 tensor, relative RMS error <= 1e-2 and largest absolute error <= 2e-2 x the largest reference magnitude, against the
-FP64 token recurrence; the FP32 final state and dh0 are held to 1e-3 x their largest magnitude against the chunked
-FP32-state oracle.  Determinism is bitwise.
+FP64 token recurrence; the FP32 final state and dh0 are held to 8e-3 x their largest magnitude against the FP64
+recurrence and to 1e-3 against the chunked FP32-state oracle (the reference's torch path).  Determinism is bitwise.
 """
 
 from __future__ import annotations
@@ -91,14 +91,18 @@ def test_within_the_reference_budgets_of_the_fp64_recurrence(heads, state):
                             dht=x.get("dht"), use_qk_l2norm=True, output_final_state=state)
     assert_within(got, ref, f"{heads} state={state}")
     if state:
-        # fp32 state outputs: 1e-3 of the largest magnitude, against the oracle that rounds where the kernels round
+        # fp32 state outputs, two bounds.  Against the FP64 recurrence: 8e-3 of the largest magnitude -- what a
+        # path with the reference's BF16 rounding points (w, u, h_tape, v_new stored in BF16) can hold: the
+        # reference's own CPU path, restated by the chunked oracle, is 2.4e-3 .. 6.1e-3 away from FP64 on these
+        # inputs, so 1e-3 against FP64 is out of reach for it and for any implementation that matches it.  Against
+        # the chunked oracle (the reference's torch path, rounding where the kernels round): 1e-3.
         chunked = O.chunked_forward_backward(x["q"], x["k"], x["v"], x["g"], x["beta"], REF_LAYOUT, x["do"].float(),
                                              h0=x["h0"], dht=x["dht"], use_qk_l2norm=True, output_final_state=True)
         for name in ("final_state", "dh0"):
+            m64 = O.metrics(got[name], ref[name])
+            assert m64["finite"] and m64["max_abs"] <= 8e-3 * m64["max_ref"] and m64["rel_rms"] <= 5e-3, (name, m64)
             m = O.metrics(got[name], chunked[name])
             assert m["finite"] and m["max_abs"] <= 1e-3 * m["max_ref"], (name, m)
-            ok, m64 = O.within_budget(got[name], ref[name])
-            assert ok, (name, m64)
 
 
 def test_strong_gates_of_the_benchmark_generator():

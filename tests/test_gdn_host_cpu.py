@@ -176,3 +176,16 @@ def test_two_gloo_ranks_reproduce_the_single_rank_result(tmp_path):
         got = torch.cat([p[name] for p in parts], 0)
         m = O.metrics(got, ref[name])
         assert m["finite"] and m["max_abs"] <= 1e-5 * max(m["max_ref"], 1e-3), (name, m)
+
+
+def test_config0_is_rejected_with_the_reference_messages():
+    """The benchmark's configuration 0 (fp32, dk = dv = 64) is outside what the kernels serve, as it is outside what
+    the reference's serve (reference: miles_ext_kernels/cake/_impl/gdn/ops.py:2307-2310): the entry point says so
+    with the reference's exception class and words before it looks at anything else; only the oracles run it."""
+    from miles_ext_kernels_b200.workloads import make_workload
+
+    w = make_workload("cfg0")
+    with pytest.raises(NotImplementedError, match="q/k/v must be bfloat16"):
+        ops.chunk_gated_delta_rule(w.q, w.k, w.v, w.g, w.beta)
+    with pytest.raises(NotImplementedError, match="head dims must be 128"):
+        ops.chunk_gated_delta_rule(w.q.bfloat16(), w.k.bfloat16(), w.v.bfloat16(), w.g, w.beta.bfloat16())

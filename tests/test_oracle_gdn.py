@@ -47,6 +47,28 @@ def test_fp64_recurrence_matches_the_reference_emulation_within_its_budgets(path
         assert ok, (name, m)
 
 
+def test_chunked_oracle_matches_the_reference_cpu_path_run_live():
+    """Where ``oracle/_ref`` (the files of the reference's own CPU path, put there by ``oracle/make_ref.py``) is at
+    hand, the restatement is checked against the reference itself on inputs the stored fixtures do not hold: the
+    benchmark's strong gates on GVA heads with a ragged layout."""
+    from oracle import reference_arm
+
+    if not reference_arm.available():
+        pytest.skip("oracle/_ref is absent (no reference checkout on this machine)")
+    from gdn_cases import draw
+
+    seq_lens = (65, 200, 31)
+    cu = (0, 65, 265, 296)
+    x = draw(seq_lens, (2, 4), seed=21, gate="strong", normalised=True)
+    want = reference_arm.forward_backward(x["q"], x["k"], x["v"], x["g"], x["beta"].bfloat16(), x["do"], cu)
+    got = O.chunked_forward_backward(x["q"].float(), x["k"].float(), x["v"].float(), x["g"], x["beta"], seq_lens,
+                                     x["do"].float())
+    for name in NAMES:
+        have = got[name].bfloat16().float() if name == "dbeta" else got[name]
+        m = O.metrics(have, want[name].float())
+        assert m["finite"] and m["rel_rms"] <= 1e-3 and m["max_abs"] <= 8e-3 * m["max_ref"], (name, m)
+
+
 CASES = {
     "single_token": ((1,), (1, 1), False),
     "ragged": ((1, 63, 64, 65, 130), (2, 4), True),
@@ -89,6 +111,22 @@ def test_config0_fp32_small_heads():
     do = torch.randn(T, H, d, generator=gen)
     ref = O.recurrence_fp64(q, k, v, g, beta, (T,), do=do)
     got = O.chunked_forward_backward(q, k, v, g, beta, (T,), do, rounding=None)
+    for key in got:
+        m = O.metrics(got[key], ref[key])
+        assert m["finite"] and m["max_abs"] <= 2e-5 * max(m["max_ref"], 1e-3), (key, m)
+
+
+def test_config0_workload_through_both_oracles():
+    """The benchmark's configuration 0 as ``make_workload`` draws it (fp32, dk = dv = 64): the chunked oracle without
+    rounding agrees with the FP64 recurrence.  It is an oracle-only configuration: the product, like the reference's
+    kernels (reference: miles_ext_kernels/cake/_impl/gdn/ops.py:2307-2310), serves head dims of 128 in bf16 only."""
+    from miles_ext_kernels_b200.workloads import make_workload
+
+    w = make_workload("cfg0")
+    assert w.q.dtype == torch.float32 and w.q.shape == (1, 256, 4, 64) and w.v.shape == (1, 256, 4, 64)
+    args = (w.q[0], w.k[0], w.v[0], w.g[0], w.beta[0], (256,))
+    ref = O.recurrence_fp64(*args, do=w.do[0])
+    got = O.chunked_forward_backward(*args, w.do[0], rounding=None)
     for key in got:
         m = O.metrics(got[key], ref[key])
         assert m["finite"] and m["max_abs"] <= 2e-5 * max(m["max_ref"], 1e-3), (key, m)
