@@ -202,7 +202,8 @@ int mek_gdn_bwd_tail(const MekGdnDims* dims, const void* q, const void* k, const
  * caller-allocated tensors, for hosts that may not allocate once their memory plan is set.  Limits:
  * total_tokens * num_v_heads <= 8192 and num_chunks * num_v_heads <= 256 (MEK_ERR_INVALID beyond).  The first call on
  * a device looks up the array's address and should come before any stream capture; calls that overlap on one GPU
- * share the array and race.  Same results as mek_gdn_gate_cumsum + mek_gdn_wy_fwd + mek_gdn_fwd_h + mek_gdn_fwd_o.
+ * share the array and race.  The array used is the current device's, so the caller's current device must be the one
+ * that owns the operands and the stream (MEK_ERR_INVALID otherwise); no required pointer may be NULL.  Same results as mek_gdn_gate_cumsum + mek_gdn_wy_fwd + mek_gdn_fwd_h + mek_gdn_fwd_o.
  * This entry point has no counterpart in the reference. */
 int mek_gdn_forward_static(const MekGdnDims* dims, const void* q, const void* k, const void* v, const float* beta,
                            const float* g, const float* h0, void* o, float* final_state, int32_t* status,

@@ -8,6 +8,9 @@ dispatch seam, e.g. ``from miles_ext_kernels_b200.cake.gdn import chunk_gated_de
 
 Every import inside the package is relative, so the directory also works under the name ``miles_ext_kernels``.
 Importing this module imports neither torch, the native library nor any op.
+
+The hook names and signatures are the public interface of radixark/miles-ext-kernels (Apache-2.0; see NOTICE): a
+drop-in has to match them.
 """
 
 from __future__ import annotations

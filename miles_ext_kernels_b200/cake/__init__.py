@@ -2,6 +2,9 @@
 op implementations (``_impl``).  The names below are the runtime's public API (reference:
 miles_ext_kernels/cake/__init__.py:13-51).  Importing this package or an op module imports neither torch nor the
 native library; an op's entry points import its implementation on first use.
+
+The export list is the public interface of radixark/miles-ext-kernels (Apache-2.0; see NOTICE): a drop-in has to
+match it name for name.
 """
 
 from ._runtime import (

@@ -211,7 +211,12 @@ def _span_boundaries(kcp_context: Any, device: torch.device) -> list[torch.Tenso
     """Per span of the rank's plan: the boundaries of its fragments relative to the span's first token, the first
     moved back by the history rows of the first document and the last moved on by the continuation rows of the last;
     built once per context (one host-to-device copy)."""
+    from ..gdn.meta import upload
+
     cached = getattr(kcp_context, "_conv1d_cu", None)
+    guard = getattr(kcp_context, "_conv1d_cu_guard", None)
+    if cached is not None and cached[0].device == device and guard is not None:
+        guard.wait()  # a call on another stream than the one that uploaded the table
     if cached is None or cached[0].device != device:
         cu = kcp_context.cu_seqlens_cpu
         flat, extents = [], []
@@ -221,12 +226,11 @@ def _span_boundaries(kcp_context: Any, device: torch.device) -> list[torch.Tenso
             local[-1] += span.after
             extents.append((len(flat), len(flat) + len(local)))
             flat += local
-        table = torch.tensor(flat or [0], dtype=torch.int32)
-        if device.type == "cuda":
-            table = table.pin_memory().to(device, non_blocking=True)
+        table, guard = upload(torch.tensor(flat or [0], dtype=torch.int32), device)
         cached = [table[a:b] for a, b in extents] or [table]
         try:
             kcp_context._conv1d_cu = cached
+            kcp_context._conv1d_cu_guard = guard
         except AttributeError:
             pass
     return cached

@@ -24,7 +24,48 @@ import torch
 CHUNK = 64
 _CACHE_LIMIT = 64
 
-__all__ = ["CHUNK", "ChunkMeta", "chunk_meta", "host_cache_clear", "host_meta_builds", "host_tables"]
+__all__ = ["CHUNK", "ChunkMeta", "UploadGuard", "chunk_meta", "device_index", "host_cache_clear", "host_meta_builds",
+           "host_tables", "upload"]
+
+
+def device_index(device: torch.device) -> int | None:
+    """The ordinal a cache key uses: ``torch.device("cuda")`` means the current device, whichever that is now."""
+    if device.type != "cuda":
+        return None
+    return torch.cuda.current_device() if device.index is None else device.index
+
+
+class UploadGuard:
+    """Orders later users of a cached device table after its one host-to-device copy.  The copy is enqueued on the
+    stream that was current when the table was built; a later call on ANOTHER stream waits for the copy's event (on
+    the device, no host synchronisation) until the copy is seen to be complete, after which the guard costs nothing."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        stream = torch.cuda.current_stream(device)
+        self.stream_id = stream.cuda_stream
+        self.event: torch.cuda.Event | None = torch.cuda.Event()
+        self.event.record(stream)
+
+    def wait(self) -> None:
+        event = self.event
+        if event is None:
+            return
+        current = torch.cuda.current_stream(self.device)
+        if current.cuda_stream == self.stream_id:
+            return  # stream order already covers it
+        if event.query():
+            self.event = None
+        else:
+            current.wait_event(event)
+
+
+def upload(table: torch.Tensor, device: torch.device) -> tuple[torch.Tensor, UploadGuard | None]:
+    """A host table on ``device`` (through pinned memory, asynchronously) and the guard its cache entry keeps."""
+    if device.type != "cuda":
+        return table, None
+    on_device = table.pin_memory().to(device, non_blocking=True)
+    return on_device, UploadGuard(device)
 
 
 @dataclass(frozen=True)
@@ -42,6 +83,7 @@ class ChunkMeta:
     max_seq_chunks: int  # most chunks of one sequence (an upper bound on the device route)
     host_seq_chunk_start: tuple[int, ...] | None = None  # the host route's copy of seq_chunk_start (scan planner)
     seq_order: torch.Tensor | None = None  # int32 [N]: sequences by falling chunk count, when they differ (host route)
+    guard: Any = None  # UploadGuard of a cached host-route table
 
 
 def host_tables(seq_lens: Sequence[int]) -> tuple[list[int], list[int], list[int], list[int]]:
@@ -78,10 +120,12 @@ def host_cache_clear() -> None:
 
 def _from_host(seq_lens: tuple[int, ...], device: torch.device) -> ChunkMeta:
     global _HOST_BUILDS
-    key = (seq_lens, device.type, device.index)
+    key = (seq_lens, device.type, device_index(device))
     cached = _HOST_CACHE.get(key)
     if cached is not None:
         _HOST_CACHE.move_to_end(key)
+        if cached.guard is not None:
+            cached.guard.wait()
         return cached
     starts, lens, seqs, first = host_tables(seq_lens)
     nc = len(starts)
@@ -89,13 +133,11 @@ def _from_host(seq_lens: tuple[int, ...], device: torch.device) -> ChunkMeta:
     # documents the longest go first, so that no long walk starts when the others are done
     counts = [first[n + 1] - first[n] for n in range(len(seq_lens))]
     order = sorted(range(len(counts)), key=lambda n: -counts[n]) if len(set(counts)) > 1 else []
-    flat = torch.tensor([*starts, *lens, *seqs, *first, *order], dtype=torch.int32)
-    if device.type == "cuda":
-        flat = flat.pin_memory().to(device, non_blocking=True)
+    flat, guard = upload(torch.tensor([*starts, *lens, *seqs, *first, *order], dtype=torch.int32), device)
     ends = 3 * nc + len(first)
     meta = ChunkMeta(
         flat[:nc], flat[nc : 2 * nc], flat[2 * nc : 3 * nc], flat[3 * nc : ends], nc, len(seq_lens), sum(seq_lens), True,
-        max(counts, default=0), tuple(first), flat[ends:] if order else None,
+        max(counts, default=0), tuple(first), flat[ends:] if order else None, guard,
     )
     _HOST_BUILDS += 1
     _HOST_CACHE[key] = meta

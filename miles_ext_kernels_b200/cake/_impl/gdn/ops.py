@@ -4,7 +4,9 @@ Mirrors the reference's entry layer (reference: miles_ext_kernels/cake/_impl/gdn
 :1746-1805 shape checks, :1877-2048 autograd function, :2051-2081 the empty call, :2507-2537 prebuild / release):
 same argument names and meaning, same exception classes and messages, checks on tensor metadata only (no device
 synchronisation), outputs and gradients as fresh allocations owned by the caller, kernels enqueued on torch's
-current stream of q's device.
+current stream of q's device.  The entry checks (``_checked``, ``_check_inputs``, ``_cp_contract``, the empty call) are
+derived from the reference's (Apache-2.0; see NOTICE): same order of checks, same words, because callers and tests
+match them.
 """
 
 from __future__ import annotations
@@ -19,6 +21,7 @@ import torch
 from ..._runtime import config, loader, registry
 from . import meta as meta_module
 from . import native, stages
+from . import tape as tape_module
 from .kcp import KcpContext
 
 OP = "gdn"
@@ -231,7 +234,9 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             o, final_state, tape, h0 = stages.forward(qp, kp, vp, gp, beta32, meta, scale, h0, want_final,
                                                       bool(use_qk_l2norm), keep_state=bool(save_state),
                                                       scan_segments=ctx.scan_segments, exchange=exchange)
-        ctx.tape, ctx.meta, ctx.scale, ctx.h0 = tape, meta, scale, h0
+        # every tensor of the tape through save_for_backward (version checks, saved-tensor hooks); metadata as attributes
+        tape_module.keep(ctx, tape, h0=h0)
+        ctx.meta, ctx.scale = meta, scale
         ctx.exchange = exchange
         ctx.shapes = (q.shape, v.shape, g.shape)
         ctx.g_dtype, ctx.beta_dtype = g.dtype, beta.dtype
@@ -243,7 +248,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, dht):
         q_shape, v_shape, g_shape = ctx.shapes
-        tape, meta = ctx.tape, ctx.meta
+        tape, kept = tape_module.restore(ctx)
+        meta = ctx.meta
         device = tape.qn.device
         with torch.cuda.device(device):
             if do is None:
@@ -251,7 +257,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             dop = _packed(do if do.dtype == torch.bfloat16 else do.bfloat16())
             dhtp = None if dht is None else dht.float().contiguous()
             want_dh0 = ctx.has_initial_state
-            dq, dk, dv, dg, dbeta, dh0, _, _ = stages.backward(tape, meta, ctx.scale, dop, dhtp, ctx.h0, want_dh0,
+            dq, dk, dv, dg, dbeta, dh0 = stages.backward(tape, meta, ctx.scale, dop, dhtp, kept["h0"], want_dh0,
                                                                scan_segments=ctx.scan_segments, exchange=ctx.exchange,
                                                                packed_grads=ctx.packed_grads)
         dq, dk, dv = dq.view(q_shape), dk.view(q_shape), dv.view(v_shape)

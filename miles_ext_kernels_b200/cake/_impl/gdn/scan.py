@@ -22,6 +22,7 @@ from functools import lru_cache
 import torch
 
 from . import native
+from .meta import device_index, upload
 
 MIN_SEGMENT_CHUNKS = 16  # a segment shorter than this does not pay for its summary
 MAX_PARTS = 16
@@ -108,15 +109,18 @@ class ScanPlan:
     last_index: torch.Tensor  # int64 [N]: each sequence's last segment
     warm_chunks: int = WARM_CHUNKS
     warm_log2: float = WARM_NATS * math.log2(math.e)
+    guards: tuple = ()  # UploadGuards of the cached tables
 
 
 _PLANS: dict[tuple, ScanPlan] = {}
 
 
 def device_plan(seg: Segmentation, device: torch.device) -> ScanPlan:
-    key = (seg, device.type, device.index)
+    key = (seg, device.type, device_index(device))
     found = _PLANS.get(key)
     if found is not None:
+        for guard in found.guards:
+            guard.wait()
         return found
     first, last, rows, fwd, bwd = [], [], [], [], []
     for n, (a, b) in enumerate(zip(seg.seq_seg_start, seg.seq_seg_start[1:])):
@@ -126,15 +130,14 @@ def device_plan(seg: Segmentation, device: torch.device) -> ScanPlan:
             rows.append(n)
             fwd.append((1 if s > a else 0) | (2 if s == b - 1 else 0))
             bwd.append((1 if s < b - 1 else 0) | (2 if s == a else 0))
-    flat = torch.tensor([*seg.seg_chunk_start, *seg.seq_seg_start, *fwd, *bwd, *rows], dtype=torch.int32)
-    index = torch.tensor([*first, *last], dtype=torch.int64)
-    if device.type == "cuda":
-        flat = flat.pin_memory().to(device, non_blocking=True)
-        index = index.pin_memory().to(device, non_blocking=True)
+    flat, guard_a = upload(torch.tensor([*seg.seg_chunk_start, *seg.seq_seg_start, *fwd, *bwd, *rows],
+                                        dtype=torch.int32), device)
+    index, guard_b = upload(torch.tensor([*first, *last], dtype=torch.int64), device)
     ns, n = seg.segments, len(seg.seq_seg_start) - 1
     at = [0, ns + 1, ns + n + 2, 2 * ns + n + 2, 3 * ns + n + 2, 4 * ns + n + 2]
     plan = ScanPlan(ns, n, flat[at[0]:at[1]], flat[at[1]:at[2]], flat[at[2]:at[3]], flat[at[3]:at[4]],
-                    flat[at[4]:at[5]], index[:n], index[n:])
+                    flat[at[4]:at[5]], index[:n], index[n:],
+                    guards=tuple(g for g in (guard_a, guard_b) if g is not None))
     if len(_PLANS) >= 64:
         _PLANS.clear()
     _PLANS[key] = plan
@@ -151,7 +154,7 @@ def plan_for(meta, num_v_heads: int, device: torch.device, forced: int = 0) -> S
     the device: the planner needs the chunk counts on the host)."""
     if meta.host_seq_chunk_start is None or device.type != "cuda":
         return None
-    parts = choose_parts(meta.host_seq_chunk_start, num_v_heads, sm_count(device.index or 0), forced)
+    parts = choose_parts(meta.host_seq_chunk_start, num_v_heads, sm_count(device_index(device) or 0), forced)
     if parts <= 1:
         return None
     seg = segment(meta.host_seq_chunk_start, parts)
@@ -175,20 +178,21 @@ def fragment_plan(chunk_begin: int, chunk_end: int, num_v_heads: int, device: to
     """Segments of the chunk range of one document fragment, every segment walked from zero / the identity and none
     skipped: what a rank's summary ``(B, M)`` of the fragment is composed from."""
     chunks = chunk_end - chunk_begin
-    sms = sm_count(device.index or 0)
+    sms = sm_count(device_index(device) or 0)
     parts = max(1, min(MAX_PARTS, chunks // MIN_SEGMENT_CHUNKS, sms // max(1, num_v_heads)))
     seg = Segmentation(-parts, tuple(chunk_begin + (chunks * p) // parts for p in range(parts)) + (chunk_end,),
                        (0, parts))
-    key = (seg, device.type, device.index)
+    key = (seg, device.type, device_index(device))
     found = _PLANS.get(key)
     if found is not None:
+        for guard in found.guards:
+            guard.wait()
         return found
     ns = parts
-    flat = torch.tensor([*seg.seg_chunk_start, 0, ns, *([1] * ns), *([0] * ns)], dtype=torch.int32)
-    if device.type == "cuda":
-        flat = flat.pin_memory().to(device, non_blocking=True)
+    flat, guard = upload(torch.tensor([*seg.seg_chunk_start, 0, ns, *([1] * ns), *([0] * ns)], dtype=torch.int32),
+                         device)
     plan = ScanPlan(ns, 1, flat[: ns + 1], flat[ns + 1 : ns + 3], flat[ns + 3 : 2 * ns + 3], flat[ns + 3 : 2 * ns + 3],
-                    flat[2 * ns + 3 :], None, None)
+                    flat[2 * ns + 3 :], None, None, guards=() if guard is None else (guard,))
     if len(_PLANS) >= 64:
         _PLANS.clear()
     _PLANS[key] = plan

@@ -215,10 +215,13 @@ def recompute_state(tape: ForwardTape, meta: ChunkMeta, scale: float, h0, scan_s
 
 
 def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want_dh0: bool, scan_segments: int = 0,
-             exchange=None, packed_grads: bool = False):
+             exchange=None, packed_grads: bool = False, inspect: dict | None = None):
     """``do [T, HV, 128]`` bf16, ``dht [N, HV, 128, 128]`` fp32 or None.  Returns ``(dq, dk [T, H, 128] bf16, dv
     [T, HV, 128] bf16, dg, dbeta [T, HV] fp32, dh0 [N, HV, 128, 128] fp32 or None)``.  With ``packed_grads`` dq, dk
-    and dv are the column slices ``[q heads | k heads | v heads]`` of one ``[T, (2 H + HV) * 128]`` row."""
+    and dv are the column slices ``[q heads | k heads | v heads]`` of one ``[T, (2 H + HV) * 128]`` row.
+
+    The adjoint scan's tapes (``dh_tape``, ``dv_new``) are pooled scratch, which never leaves this function; a stage
+    test that wants to look at them passes a dict as ``inspect`` and finds them there as fresh allocations."""
     device = do.device
     T, H = tape.qn.shape[0], tape.qn.shape[1]
     HV = tape.v.shape[1]
@@ -239,11 +242,16 @@ def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want
                    dqk_pitch=pitch_of(dq), dv_pitch=pitch_of(dv))
     if tape.w is None:
         recompute_state(tape, meta, scale, h0, scan_segments)
-    if meta.exact:
-        dh_tape = workspace.take(OP, "dh_tape", (NC, HV, HEAD_DIM, HEAD_DIM), BF16, device)
-    else:  # pad chunks are never written
+    if inspect is not None:
         dh_tape = torch.zeros((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
-    dv_new = workspace.take(OP, "dv_new", (T, HV, HEAD_DIM), BF16, device)
+        dv_new = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+        inspect.update(dh_tape=dh_tape, dv_new=dv_new)
+    else:
+        if meta.exact:
+            dh_tape = workspace.take(OP, "dh_tape", (NC, HV, HEAD_DIM, HEAD_DIM), BF16, device)
+        else:  # pad chunks are never written
+            dh_tape = torch.zeros((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
+        dv_new = workspace.take(OP, "dv_new", (T, HV, HEAD_DIM), BF16, device)
     if exchange is not None:
         dht, want_dh0 = exchange.backward_begin(dims, meta, tape, do)
     dh0 = _scan_backward(dims, meta, tape, do, dht, dh_tape, dv_new, want_dh0, scan_segments)
@@ -255,4 +263,4 @@ def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want
     native.launch("gdn_bwd_tail", dims, tape.qn, tape.kn, tape.v, tape.beta32, tape.g_cs, tape.a, tape.aqk, tape.w, tape.u,
                   tape.h, dh_tape, tape.v_new, dv_new, do, tape.q_raw, tape.k_raw, tape.rstd_q, tape.rstd_k, dq, dk, dv,
                   dbeta, dg, tape.status, device=device)
-    return dq, dk, dv, dg, dbeta, dh0, dh_tape, dv_new
+    return dq, dk, dv, dg, dbeta, dh0

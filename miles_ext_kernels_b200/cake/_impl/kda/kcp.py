@@ -30,6 +30,7 @@ from typing import Any
 import torch
 
 from ..._runtime import config
+from ..gdn import tape as tape_module
 from ..gdn.kcp import KcpContext
 from . import ops
 
@@ -165,7 +166,8 @@ class _ChunkKdaKcp(torch.autograd.Function):
     def forward(fn, q, k, v, g, beta, ctx, scale, l2norm):
         q3, k3, v3, g3, beta32 = _shard(q, k, v, g, beta, ctx)
         o, saved = _forward_kcp(q3, k3, v3, g3, beta32, ctx, scale, l2norm)
-        fn.saved, fn.v, fn.beta32, fn.kcp = saved, v3, beta32, ctx
+        tape_module.keep(fn, saved, v=v3, beta32=beta32)
+        fn.kcp = ctx
         fn.shapes = (q.shape, g.shape, beta.shape)
         fn.dtypes = (g.dtype, beta.dtype)
         return o.view(q.shape)
@@ -174,7 +176,8 @@ class _ChunkKdaKcp(torch.autograd.Function):
     def backward(fn, do):
         shape, g_shape, beta_shape = fn.shapes
         do3 = ops._packed3(do, "dout").contiguous().to(torch.bfloat16)
-        dq, dk, dv, dg, dbeta = _backward_kcp(fn.saved, fn.v, fn.beta32, do3, fn.kcp)
+        saved, kept = tape_module.restore(fn)
+        dq, dk, dv, dg, dbeta = _backward_kcp(saved, kept["v"], kept["beta32"], do3, fn.kcp)
         g_dtype, beta_dtype = fn.dtypes
         return (dq.view(shape), dk.view(shape), dv.view(shape), dg.view(g_shape).to(g_dtype),
                 dbeta.view(beta_shape).to(beta_dtype), None, None, None)

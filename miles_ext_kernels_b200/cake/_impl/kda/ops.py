@@ -24,6 +24,7 @@ import torch
 from ..._runtime import config, loader, registry, workspace
 from ..gdn import meta as meta_module
 from ..gdn import native, scan
+from ..gdn import tape as tape_module
 from ..gdn.stages import check_status, dims_of
 
 OP = "kda"
@@ -268,7 +269,7 @@ class _ChunkKda(torch.autograd.Function):
         with torch.cuda.device(q.device):
             o, saved, _ = _forward(q3, k3, v3, g3, beta32, cu_seqlens, scale, use_qk_l2norm,
                                    cu_seqlens_cpu=cu_seqlens_cpu)
-        ctx.saved, ctx.v, ctx.beta32 = saved, v3, beta32
+        tape_module.keep(ctx, saved, v=v3, beta32=beta32)
         ctx.shapes = (shape, g.shape, beta.shape)
         ctx.dtypes = (g.dtype, beta.dtype)
         return o.view(shape)
@@ -279,8 +280,9 @@ class _ChunkKda(torch.autograd.Function):
         do3 = _packed3(do, "dout").contiguous()
         if do3.dtype != BF16:
             do3 = do3.to(BF16)
+        saved, kept = tape_module.restore(ctx)
         with torch.cuda.device(do.device):
-            dq, dk, dv, dg, dbeta, _ = _backward(ctx.saved, ctx.v, ctx.beta32, do3)
+            dq, dk, dv, dg, dbeta, _ = _backward(saved, kept["v"], kept["beta32"], do3)
         g_dtype, beta_dtype = ctx.dtypes
         return (dq.view(shape), dk.view(shape), dv.view(shape), dg.view(g_shape).to(g_dtype),
                 dbeta.view(beta_shape).to(beta_dtype), None, None, None, None)

@@ -5,6 +5,9 @@
 - :mod:`.config`: the argument surface, the configuration of the process and the variant each op runs.
 - :mod:`.loader`: nvcc build, file-locked cache and ctypes load of the native library.
 - :mod:`.workspace`: the bounded scratch pool.
+
+The export list is the public interface of radixark/miles-ext-kernels (Apache-2.0; see NOTICE): a drop-in has to
+match it name for name.
 """
 
 from .config import add_arguments, configure, deterministic_mode, option, validate_args, variant, warn_runs_det

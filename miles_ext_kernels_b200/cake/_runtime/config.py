@@ -71,12 +71,17 @@ RUNTIME_FLAGS = (
 
 logger = logging.getLogger("miles_ext_kernels")
 
-_state: Mapping[str, Any] = MappingProxyType({})
-_warned: set[tuple[str, str]] = set()
+
+class _Process:
+    """What this process is configured to: one read-only mapping, replaced as a whole."""
+
+    settings: Mapping[str, Any] = MappingProxyType({})
+    warned: set[tuple[str, str]] = set()
 
 
-def _all_specs() -> list[OpSpec]:
-    return [registry.op_spec(name) for name in registry.OPS]
+def _selectable_ops() -> list[OpSpec]:
+    """The ops miles can switch on from its command line, in registry order."""
+    return [spec for spec in map(registry.op_spec, registry.OPS) if spec.selected_by]
 
 
 def deterministic_mode(args: Any) -> bool:
@@ -86,59 +91,58 @@ def deterministic_mode(args: Any) -> bool:
     configuration as ``args.backend.deterministic_mode``.  ``args.cake_deterministic`` (this package's alias) counts
     too.  Anything else is not deterministic mode.
     """
-    flag = getattr(args, "deterministic_mode", None)
-    if flag is None:
-        flag = getattr(getattr(args, "backend", None), "deterministic_mode", False)
-    return bool(flag) or bool(getattr(args, "cake_deterministic", False))
+    if getattr(args, "cake_deterministic", False):
+        return True
+    flat = getattr(args, "deterministic_mode", None)
+    if flat is not None:
+        return bool(flat)
+    return bool(getattr(getattr(args, "backend", None), "deterministic_mode", False))
+
+
+def _variant_help(spec: OpSpec) -> str:
+    preferred = "fast" if "fast" in spec.cli_choices else "det"
+    return (f"Variant of the cake {spec.name} kernels ({spec.summary}) under {spec.selector}: 'det' repeats bit "
+            f"for bit for identical inputs, 'fast' is faster. Default: '{preferred}', or 'det' under "
+            "--deterministic-mode, which rejects 'fast'.")
 
 
 def add_arguments(parser: Any) -> None:
     """Register the ops' arguments and the runtime options on ``parser`` (a parser or an argument group)."""
-    for spec in _all_specs():
-        if not spec.selected_by:
-            continue
+    for spec in _selectable_ops():
         if spec.has_variant_flag:
-            cli_default = "fast" if "fast" in spec.cli_choices else "det"
-            text = (
-                f"Variant of the cake {spec.name} kernels ({spec.summary}) under {spec.selector}: 'det' repeats bit "
-                f"for bit for identical inputs, 'fast' is faster. Default: '{cli_default}', or 'det' under "
-                "--deterministic-mode, which rejects 'fast'."
-            )
-            parser.add_argument(
-                spec.variant_flag,
-                choices=spec.cli_choices,
-                default=None,
-                help=text if spec.shows_variant_flag else argparse.SUPPRESS,
-            )
-        for flag in spec.flags:
-            parser.add_argument(flag.name, **flag.kwargs)
-    for flag in RUNTIME_FLAGS:
-        parser.add_argument(flag.name, **flag.kwargs)
+            shown = _variant_help(spec) if spec.shows_variant_flag else argparse.SUPPRESS
+            parser.add_argument(spec.variant_flag, choices=spec.cli_choices, default=None, help=shown)
+        for own in spec.flags:
+            parser.add_argument(own.name, **own.kwargs)
+    for own in RUNTIME_FLAGS:
+        parser.add_argument(own.name, **own.kwargs)
 
 
 def _no_det(spec: OpSpec) -> ValueError:
-    why = f": {spec.selector} is not deterministic" if spec.selector else ": it cannot run in deterministic mode"
-    return ValueError(f"the cake {spec.name} kernels have no det variant{why}")
+    if spec.selector:
+        return ValueError(f"the cake {spec.name} kernels have no det variant: {spec.selector} is not deterministic")
+    return ValueError(f"the cake {spec.name} kernels have no det variant: it cannot run in deterministic mode")
 
 
-def _resolve(spec: OpSpec, requested: str | None, deterministic: bool, *, cli: bool) -> str | None:
-    """The variant ``spec`` runs, ``None`` to leave it unset.  ``cli``: apply the command line's default."""
-    if requested is None:
-        if deterministic:
-            if "det" not in spec.variants:
-                raise _no_det(spec)
+def _pick_variant(spec: OpSpec, asked: str | None, deterministic: bool, from_cli: bool) -> str | None:
+    """The variant of ``spec`` a configuration stands for.  An explicit request must be one the op ships (on the
+    command line: one miles may choose) and must not be ``fast`` in deterministic mode; no request means ``det`` in
+    deterministic mode, the command line's preference on the command line, and "unset" (``None``) otherwise."""
+    if asked is not None:
+        choices = spec.cli_choices if from_cli else spec.variants
+        if asked not in choices:
+            raise ValueError(f"{spec.variant_flag} must be one of {choices}, not {asked!r}")
+        if asked == "fast" and deterministic:
+            raise ValueError(f"{spec.variant_flag} fast is not bit-reproducible under --deterministic-mode: use det or "
+                             "leave it unset")
+        return asked
+    if deterministic:
+        if "det" in spec.variants:
             return "det"
-        if not cli:
-            return None
+        raise _no_det(spec)
+    if from_cli:
         return "fast" if "fast" in spec.cli_choices else "det"
-    allowed = spec.cli_choices if cli else spec.variants
-    if requested not in allowed:
-        raise ValueError(f"{spec.variant_flag} must be one of {allowed}, not {requested!r}")
-    if deterministic and requested == "fast":
-        raise ValueError(
-            f"{spec.variant_flag} fast is not bit-reproducible under --deterministic-mode: use det or leave it unset"
-        )
-    return requested
+    return None
 
 
 def _check_runtime(dest: str, value: Any) -> None:
@@ -146,28 +150,42 @@ def _check_runtime(dest: str, value: Any) -> None:
         raise ValueError(f"--cake-workspace-pool-bytes must be >= 0, not {value}")
 
 
+def _is_selected(spec: OpSpec, args: Namespace) -> bool:
+    return any(getattr(args, dest, None) == wanted for dest, wanted in spec.selected_by)
+
+
+def _reject_stray_options(spec: OpSpec, args: Namespace) -> None:
+    """An op that is not switched on must have none of its options set."""
+    if spec.has_variant_flag and getattr(args, spec.variant_dest, None) is not None:
+        raise ValueError(f"{spec.variant_flag} requires {spec.selector}")
+    for own in spec.flags:
+        if getattr(args, own.dest, own.default) != own.default:
+            raise ValueError(f"{own.name} requires {spec.selector}")
+
+
 def validate_args(args: Namespace) -> None:
     """Check miles' parsed flat namespace; write the resolved variant of every selected op back to it."""
     deterministic = deterministic_mode(args)
-    for spec in _all_specs():
-        if not spec.selected_by:
+    for spec in _selectable_ops():
+        if not _is_selected(spec, args):
+            _reject_stray_options(spec, args)
             continue
-        if any(getattr(args, dest, None) == value for dest, value in spec.selected_by):
-            resolved = _resolve(spec, getattr(args, spec.variant_dest, None), deterministic, cli=True)
-            if spec.has_variant_flag:
-                setattr(args, spec.variant_dest, resolved)
-            if spec.validate is not None:
-                spec.validate(args)
-            continue
-        # the op is not selected: none of its options may be set
-        owned = [(flag.name, flag.dest, flag.default) for flag in spec.flags]
+        chosen = _pick_variant(spec, getattr(args, spec.variant_dest, None), deterministic, from_cli=True)
         if spec.has_variant_flag:
-            owned.insert(0, (spec.variant_flag, spec.variant_dest, None))
-        for name, dest, default in owned:
-            if getattr(args, dest, default) != default:
-                raise ValueError(f"{name} requires {spec.selector}")
-    for flag in RUNTIME_FLAGS:
-        _check_runtime(flag.dest, getattr(args, flag.dest, flag.default))
+            setattr(args, spec.variant_dest, chosen)
+        if spec.validate is not None:
+            spec.validate(args)
+    for own in RUNTIME_FLAGS:
+        _check_runtime(own.dest, getattr(args, own.dest, own.default))
+
+
+def _known_keys() -> tuple[dict[str, OpSpec], set[str]]:
+    """``(variant key -> its op, every option key)`` over all ops and the runtime."""
+    variants = {spec.variant_dest: spec for spec in map(registry.op_spec, registry.OPS)}
+    options = {own.dest for own in RUNTIME_FLAGS}
+    for spec in variants.values():
+        options.update(own.dest for own in spec.flags)
+    return variants, options
 
 
 def configure(args: Namespace | Mapping[str, Any] | None = None, /, **values: Any) -> None:
@@ -178,60 +196,52 @@ def configure(args: Namespace | Mapping[str, Any] | None = None, /, **values: An
     ``ValueError`` for an unknown ``cake_*`` key, for a variant the op does not ship, and for ``fast`` when
     deterministic mode is on.  Each call starts again from the defaults.
     """
-    merged: dict[str, Any] = {}
-    if isinstance(args, Mapping):
-        merged.update(args)
-    elif args is not None:
-        merged.update(vars(args))
-    merged.update(values)
-    deterministic = deterministic_mode(Namespace(**merged))
-
-    accepted: dict[str, OpSpec | Flag] = {flag.dest: flag for flag in RUNTIME_FLAGS}
-    for spec in _all_specs():
-        accepted[spec.variant_dest] = spec
-        for flag in spec.flags:
-            accepted[flag.dest] = flag
-
-    fresh: dict[str, Any] = {"deterministic_mode": deterministic}
-    for key, value in merged.items():
+    given = dict(args) if isinstance(args, Mapping) else ({} if args is None else dict(vars(args)))
+    given.update(values)
+    deterministic = deterministic_mode(Namespace(**given))
+    variants, options = _known_keys()
+    settings: dict[str, Any] = {"deterministic_mode": deterministic}
+    for key, value in given.items():
         if value is None or not key.startswith("cake_"):
             continue
-        owner = accepted.get(key)
-        if owner is None:
-            raise ValueError(f"unknown cake option {key!r}")
-        if isinstance(owner, OpSpec):
-            value = _resolve(owner, value, deterministic, cli=False)
-        else:
+        if key in variants:
+            settings[key] = _pick_variant(variants[key], value, deterministic, from_cli=False)
+        elif key in options:
             _check_runtime(key, value)
-        fresh[key] = value
-    global _state
-    _state = MappingProxyType(fresh)
+            settings[key] = value
+        else:
+            raise ValueError(f"unknown cake option {key!r}")
+    _Process.settings = MappingProxyType(settings)
 
 
 def variant(op: str) -> str:
     """The variant ``op`` runs now: the configured one, else ``det`` (or the op's only variant).  In a process
     configured with deterministic mode, ``ValueError`` for an op that ships no ``det``."""
-    chosen = _state.get(f"cake_{op}_variant")
-    if chosen is not None:
-        return chosen
+    settings = _Process.settings
+    configured = settings.get(f"cake_{op}_variant")
+    if configured is not None:
+        return configured
     spec = registry.op_spec(op)
-    if _state.get("deterministic_mode"):
-        if "det" not in spec.variants:
-            raise _no_det(spec)
+    if not settings.get("deterministic_mode"):
+        return spec.default_variant
+    if "det" in spec.variants:
         return "det"
-    return spec.default_variant
+    raise _no_det(spec)
 
 
 def option(op: str | None, dest: str) -> Any:
     """The configured value of option ``dest`` of ``op`` (``None``: a runtime option), else its default."""
-    for flag in RUNTIME_FLAGS if op is None else registry.op_spec(op).flags:
-        if flag.dest == dest:
-            return _state.get(dest, flag.default)
-    raise KeyError(f"{'the runtime' if op is None else op} has no option {dest!r}")
+    owned = RUNTIME_FLAGS if op is None else registry.op_spec(op).flags
+    defaults = {own.dest: own.default for own in owned}
+    if dest not in defaults:
+        raise KeyError(f"{'the runtime' if op is None else op} has no option {dest!r}")
+    return _Process.settings.get(dest, defaults[dest])
 
 
 def warn_runs_det(op: str, reason: str) -> None:
     """Log, once per ``(op, reason)``, that a call the ``fast`` variant does not serve runs ``det``."""
-    if (op, reason) not in _warned:
-        _warned.add((op, reason))
-        logger.warning("miles_ext_kernels.cake.%s: the fast variant does not serve %s; running det", op, reason)
+    seen = (op, reason)
+    if seen in _Process.warned:
+        return
+    _Process.warned.add(seen)
+    logger.warning("miles_ext_kernels.cake.%s: the fast variant does not serve %s; running det", op, reason)

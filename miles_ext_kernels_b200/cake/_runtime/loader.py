@@ -26,8 +26,8 @@ Importing this module imports neither torch nor the library.
 from __future__ import annotations
 
 import ctypes
+import dataclasses
 import fcntl
-import functools
 import hashlib
 import json
 import logging
@@ -42,7 +42,7 @@ import uuid
 from collections.abc import Iterable, Iterator
 from contextlib import contextmanager
 from pathlib import Path
-from typing import Any, NamedTuple
+from typing import Any
 
 __all__ = [
     "ARCH_BY_CAPABILITY",
@@ -103,8 +103,9 @@ _COMMON_FLAGS = (
 )
 
 
-class CudaVersion(NamedTuple):
-    """The toolkit of ``nvcc --version``: ``release X.Y`` and the full ``VX.Y.Z``."""
+@dataclasses.dataclass(frozen=True, order=True)
+class CudaVersion:
+    """A CUDA toolkit as its compiler names it: the release pair and the full build string (``12.9.86``)."""
 
     major: int
     minor: int
@@ -112,47 +113,76 @@ class CudaVersion(NamedTuple):
 
     @property
     def cudart(self) -> int:
-        """``CUDART_VERSION`` of the toolkit: ``1000 * major + 10 * minor``."""
-        return 1000 * self.major + 10 * self.minor
+        """The integer ``CUDART_VERSION`` takes for this release (12.9 -> 12090)."""
+        return self.major * 1000 + self.minor * 10
+
+    @classmethod
+    def parse(cls, banner: str) -> CudaVersion | None:
+        """From the text of ``nvcc --version``; ``None`` when it names no release and build."""
+        release_, build = _NVCC_RELEASE.search(banner), _NVCC_BUILD.search(banner)
+        if not (release_ and build):
+            return None
+        return cls(int(release_[1]), int(release_[2]), build[1])
+
+
+def _nvcc_candidates() -> Iterator[Path]:
+    home = os.environ.get("CUDA_HOME")
+    if home:  # an explicit toolkit wins, whether or not it exists: a wrong CUDA_HOME should be reported, not skipped
+        yield Path(home, "bin", "nvcc")
+        return
+    on_path = shutil.which("nvcc")
+    if on_path:
+        yield Path(on_path)
+    yield Path("/usr/local/cuda/bin/nvcc")
 
 
 def find_nvcc() -> str:
-    """``$CUDA_HOME/bin/nvcc``, else ``nvcc`` on ``PATH``, else ``/usr/local/cuda/bin/nvcc``."""
-    cuda_home = os.environ.get("CUDA_HOME")
-    if cuda_home:
-        return str(Path(cuda_home) / "bin" / "nvcc")
-    found = shutil.which("nvcc")
-    if found is None:
-        fallback = Path("/usr/local/cuda/bin/nvcc")
-        if fallback.is_file():
-            return str(fallback)
-        raise RuntimeError("no nvcc to build the kernels: set CUDA_HOME or put nvcc on PATH")
-    return found
+    """The compiler to use: ``$CUDA_HOME/bin/nvcc`` when ``CUDA_HOME`` is set, else the first of ``nvcc`` on ``PATH``
+    and ``/usr/local/cuda/bin/nvcc`` that exists.  ``RuntimeError`` when there is none."""
+    explicit = bool(os.environ.get("CUDA_HOME"))
+    for candidate in _nvcc_candidates():
+        if explicit or candidate.is_file():
+            return str(candidate)
+    raise RuntimeError("no nvcc to build the kernels: set CUDA_HOME or put nvcc on PATH")
 
 
-@functools.lru_cache(maxsize=None)
-def _nvcc_version(nvcc: str, stamp: tuple[int, int]) -> CudaVersion:
-    # ``stamp`` (mtime, size) re-runs nvcc when the file at that path changes
-    try:
-        proc = subprocess.run([nvcc, "--version"], capture_output=True, text=True, check=False)
-    except OSError as exc:
-        raise RuntimeError(f"cannot run {nvcc} --version: {exc}") from exc
-    release_ = _NVCC_RELEASE.search(proc.stdout)
-    build = _NVCC_BUILD.search(proc.stdout)
-    if proc.returncode or release_ is None or build is None:
-        raise RuntimeError(
-            f"{nvcc} --version (exit {proc.returncode}) reports no 'release X.Y, VX.Y.Z':\n{proc.stdout}{proc.stderr}"
-        )
-    return CudaVersion(int(release_.group(1)), int(release_.group(2)), build.group(1))
+class _Toolkits:
+    """Remembers what each compiler binary reported, per (path, modification time, size): swapping the file at a
+    path asks it again, an unchanged one is never run twice."""
+
+    def __init__(self) -> None:
+        self._seen: dict[tuple[str, int, int], CudaVersion] = {}
+
+    def version_of(self, nvcc: str) -> CudaVersion:
+        try:
+            info = os.stat(nvcc)
+        except OSError as exc:
+            raise RuntimeError(f"cannot run {nvcc}: {exc}") from exc
+        identity = (nvcc, info.st_mtime_ns, info.st_size)
+        if identity not in self._seen:
+            self._seen[identity] = self._ask(nvcc)
+        return self._seen[identity]
+
+    @staticmethod
+    def _ask(nvcc: str) -> CudaVersion:
+        try:
+            done = subprocess.run([nvcc, "--version"], capture_output=True, text=True, check=False)
+        except OSError as exc:
+            raise RuntimeError(f"cannot run {nvcc} --version: {exc}") from exc
+        version = None if done.returncode else CudaVersion.parse(done.stdout)
+        if version is None:
+            raise RuntimeError(f"{nvcc} --version (exit {done.returncode}) reports no 'release X.Y, VX.Y.Z':\n"
+                               f"{done.stdout}{done.stderr}")
+        return version
+
+
+_TOOLKITS = _Toolkits()
 
 
 def _toolkit(nvcc: str | None = None) -> tuple[str, CudaVersion]:
-    nvcc = nvcc or find_nvcc()
-    try:
-        stat = os.stat(nvcc)
-    except OSError as exc:
-        raise RuntimeError(f"cannot run {nvcc}: {exc}") from exc
-    return nvcc, _nvcc_version(nvcc, (stat.st_mtime_ns, stat.st_size))
+    """``(compiler path, its version)`` for ``nvcc`` or, without one, for :func:`find_nvcc`."""
+    path = find_nvcc() if nvcc is None else nvcc
+    return path, _TOOLKITS.version_of(path)
 
 
 def get_cuda_version() -> CudaVersion:
@@ -162,14 +192,13 @@ def get_cuda_version() -> CudaVersion:
 
 def check_toolkit(arch: str, what: str, nvcc: str | None = None) -> CudaVersion:
     """The toolkit of ``nvcc``, checked to compile ``arch`` (:data:`MIN_CUDA`); ``RuntimeError`` when it is older."""
-    nvcc, cuda = _toolkit(nvcc)
-    need = MIN_CUDA.get(arch)
-    if need is not None and (cuda.major, cuda.minor) < need:
-        raise RuntimeError(
-            f"compiling {what} for {arch} needs CUDA {need[0]}.{need[1]} or newer, but {nvcc} is CUDA {cuda.full}: "
-            f"set CUDA_HOME to a CUDA {need[0]}.{need[1]} or newer toolkit"
-        )
-    return cuda
+    path, have = _toolkit(nvcc)
+    oldest = MIN_CUDA.get(arch)
+    if oldest is None or (have.major, have.minor) >= tuple(oldest):
+        return have
+    wanted = ".".join(str(part) for part in oldest)
+    raise RuntimeError(f"compiling {what} for {arch} needs CUDA {wanted} or newer, but {path} is CUDA {have.full}: "
+                       f"set CUDA_HOME to a CUDA {wanted} or newer toolkit")
 
 
 def cache_dir() -> Path:
@@ -198,26 +227,42 @@ def declared_symbols(header: Path | None = None) -> tuple[str, ...]:
     return tuple(dict.fromkeys(re.findall(r"\b(mek_[a-z0-9_]+)\s*\(", text)))
 
 
-def _lock_exclusive(lock: Any, lock_path: Path, name: str) -> None:
-    """Take the exclusive flock of the open file ``lock``, waiting at most ``_LOCK_TIMEOUT_SECONDS``."""
-    start = time.monotonic()
-    logged = start
-    while True:
-        try:
-            fcntl.flock(lock, fcntl.LOCK_EX | fcntl.LOCK_NB)
-            return
-        except BlockingIOError:
-            pass
-        now = time.monotonic()
-        if now - start >= _LOCK_TIMEOUT_SECONDS:
-            raise RuntimeError(
-                f"gave up building {name} after waiting {now - start:.0f} s for the build lock {lock_path}: another "
-                "process holds it. Retry, or point MILES_EXT_KERNELS_CACHE_DIR at a node-local directory."
-            )
-        if now - logged >= _LOCK_LOG_SECONDS:
-            logged = now
-            logger.warning("waiting %.0f s for the build lock %s of %s", now - start, lock_path, name)
-        time.sleep(_LOCK_POLL_SECONDS)
+@contextmanager
+def _build_lock(target: Path, what: str) -> Iterator[None]:
+    """Hold the exclusive ``flock`` of ``<target>.lock`` for the block: one process per node builds ``target``, the
+    others wait here (a line in the log every ``_LOCK_LOG_SECONDS``) and give up after ``_LOCK_TIMEOUT_SECONDS``."""
+    lock_path = target.with_suffix(".lock")
+    began = time.monotonic()
+    next_report = began + _LOCK_LOG_SECONDS
+    with open(lock_path, "a") as handle:
+        while True:
+            try:
+                fcntl.flock(handle, fcntl.LOCK_EX | fcntl.LOCK_NB)
+                break
+            except BlockingIOError:
+                waited = time.monotonic() - began
+            if waited >= _LOCK_TIMEOUT_SECONDS:
+                raise RuntimeError(
+                    f"gave up building {what} after waiting {waited:.0f} s for the build lock {lock_path}: another "
+                    "process holds it. Retry, or point MILES_EXT_KERNELS_CACHE_DIR at a node-local directory.")
+            if time.monotonic() >= next_report:
+                next_report += _LOCK_LOG_SECONDS
+                logger.warning("waiting %.0f s for the build lock %s of %s", waited, lock_path, what)
+            time.sleep(_LOCK_POLL_SECONDS)
+        yield  # closing the file drops the lock
+
+
+def _run_compiler(command: list[str], output: Path, what: str) -> None:
+    """Run ``command`` (which writes ``output``); ``RuntimeError`` with the command and the head of nvcc's stderr when
+    it fails or writes nothing."""
+    try:
+        done = subprocess.run(command, capture_output=True, text=True, check=False)
+    except OSError as exc:
+        raise RuntimeError(f"cannot run {command[0]} to build {what}: {exc}") from exc
+    if done.returncode == 0 and output.is_file():
+        return
+    head = "\n".join(done.stderr.splitlines()[:_STDERR_LINES])
+    raise RuntimeError(f"nvcc failed to build {what} (exit {done.returncode}):\n{' '.join(command)}\n{head}")
 
 
 class LibrarySpec:
@@ -270,41 +315,31 @@ class LibrarySpec:
 
     def build(self, *, in_tree: bool = False) -> Path:
         """Compile the library unless it exists; return its path."""
-        found = self.find()
-        if found is not None and not (in_tree and found != self.in_tree_path()):
-            return found
+        target = self.in_tree_path() if in_tree else self.cache_path()
+        existing = target if (in_tree and target.is_file()) else (None if in_tree else self.find())
+        if existing is not None:
+            return existing
         if _NO_BUILD:
-            ops = sorted(op for op, names in _OP_LIBRARIES.items() if self.name in names) or [self.name]
-            raise RuntimeError(f"{self.name} would compile inside a call: prebuild({ops[0]!r}, ...) first")
+            users = sorted(op for op, names in _OP_LIBRARIES.items() if self.name in names)
+            raise RuntimeError(f"{self.name} would compile inside a call: prebuild({(users or [self.name])[0]!r}, ...) "
+                               "first")
         check_toolkit(self.arch, self.name, self.nvcc)
-        path = self.in_tree_path() if in_tree else self.cache_path()
-        path.parent.mkdir(parents=True, exist_ok=True)
-        lock_path = path.with_suffix(".lock")
-        with open(lock_path, "a") as lock:
-            _lock_exclusive(lock, lock_path, self.name)  # released when the file closes
-            if path.is_file():  # another rank built it while this one waited
-                return path
-            temporary = path.with_name(f"{path.stem}.{os.getpid()}.{uuid.uuid4().hex[:8]}.tmp.so")
-            command = self.command(temporary)
-            try:
+        target.parent.mkdir(parents=True, exist_ok=True)
+        with _build_lock(target, self.name):
+            if not target.is_file():  # else another rank built it while this one waited
+                # compile beside the target and rename: a reader never sees half a library
+                scratch = target.with_name(f"{target.stem}.{os.getpid()}.{uuid.uuid4().hex[:8]}.tmp.so")
                 try:
-                    proc = subprocess.run(command, capture_output=True, text=True, check=False)
-                except OSError as exc:
-                    raise RuntimeError(f"cannot run {self.nvcc} to build {self.name}: {exc}") from exc
-                if proc.returncode or not temporary.is_file():
-                    stderr = "\n".join(proc.stderr.splitlines()[:_STDERR_LINES])
-                    raise RuntimeError(
-                        f"nvcc failed to build {self.name} (exit {proc.returncode}):\n{' '.join(command)}\n{stderr}"
-                    )
-                os.replace(temporary, path)
-            finally:
-                temporary.unlink(missing_ok=True)
-        if in_tree:  # drop builds of older sources so the tree ships one library
-            for stale in _IN_TREE.glob(f"{self.name}_{self.arch}_*.so"):
-                if stale != path:
-                    stale.unlink(missing_ok=True)
-                    stale.with_suffix(".lock").unlink(missing_ok=True)
-        return path
+                    _run_compiler(self.command(scratch), scratch, self.name)
+                    os.replace(scratch, target)
+                finally:
+                    scratch.unlink(missing_ok=True)
+        if in_tree:  # the tree ships one library: builds of older sources go
+            for other in _IN_TREE.glob(f"{self.name}_{self.arch}_*.so"):
+                if other != target:
+                    other.unlink(missing_ok=True)
+                    other.with_suffix(".lock").unlink(missing_ok=True)
+        return target
 
 
 class NativeLibrary:

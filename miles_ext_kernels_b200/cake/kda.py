@@ -15,8 +15,14 @@ from ._runtime.spec import OpSpec, lazy_exports
 
 
 def _validate(args: Namespace) -> None:
-    """Under ``--kda-backend cake``: no context parallelism (miles shards every document over the ranks, the kernels
-    run whole documents of one packed row) and the packed ``thd`` layout only."""
+    """Under ``--kda-backend cake`` miles' command line may not ask for context parallelism, and the layout must be
+    the packed ``thd`` one.
+
+    The op itself does run context-parallel: ``chunk_kda_kcp`` and its twins take this rank's slice of a partition of
+    the packed batch that ``build_context_kcp`` describes.  What is rejected here is miles' own context-parallel KDA
+    path, which hands every rank a shard of every document under flash-linear-attention's context instead of such a
+    partition -- the same rule, in the same words, as the reference's op (reference:
+    miles_ext_kernels/cake/kda.py:35-50).  ``bshd`` is not a packed sequence."""
     ranks = getattr(args, "context_parallel_size", None) or 1
     if ranks > 1:
         raise ValueError(

@@ -12,6 +12,8 @@
 //     GPU that loads the library until the process exits); larger calls are rejected with MEK_ERR_INVALID;
 //   * the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that first call
 //     before any stream capture;
+//   * the array that is used is the CURRENT device's: the host thread's current device must be the one that owns the
+//     operands and the stream (checked against q; a mismatch is MEK_ERR_INVALID);
 //   * every call on a device uses the same array: two calls that overlap on the GPU (different streams) race, so
 //     order them on one stream or with events; the array keeps the previous call's contents, and nothing in it has to
 //     start at zero (every element a kernel reads was written earlier in the same call);
@@ -72,6 +74,8 @@ extern "C" int mek_gdn_forward_static(const MekGdnDims* d, const void* q, const 
                                       int32_t* status, void* stream) {
   using namespace mek;
   if (d == nullptr) return fail(MEK_ERR_INVALID, "forward_static: dims is null");
+  if (!q || !k || !v || !beta || !g || !o || !status)
+    return fail(MEK_ERR_INVALID, "forward_static: q, k, v, beta, g, o and status must not be null");
   if (d->total_tokens <= 0 || d->num_chunks <= 0 || d->num_v_heads <= 0)
     return fail(MEK_ERR_INVALID, "forward_static: no tokens");
   const int64_t token_heads = d->total_tokens * d->num_v_heads;
@@ -82,6 +86,18 @@ extern "C" int mek_gdn_forward_static(const MekGdnDims* d, const void* q, const 
                 "(limit %lld): the call does not fit the fixed scratch; use the forward stages with caller-allocated "
                 "tensors",
                 (long long)token_heads, (long long)kMaxTokenHeads, (long long)chunk_heads, (long long)kMaxChunkHeads);
+  {  // the scratch is the current device's: the operands must live there too
+    int current = -1;
+    cudaPointerAttributes where;
+    if (cudaGetDevice(&current) != cudaSuccess || cudaPointerGetAttributes(&where, q) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(MEK_ERR_CUDA, "forward_static: cannot tell which device holds q");
+    }
+    if (where.type != cudaMemoryTypeDevice || where.device != current)
+      return fail(MEK_ERR_INVALID,
+                  "forward_static: q is not in the memory of the current device (%d): set the device that owns the "
+                  "operands and the stream before the call", current);
+  }
   unsigned char* base = nullptr;
   if (int rc = scratch_for_current_device(&base)) return rc;
   float* g_cs = reinterpret_cast<float*>(base + kOffGcs);

@@ -61,8 +61,11 @@ __global__ void __launch_bounds__(256) scan_stitch_kernel(
     const float* b_mat = summary + (int64_t(s) * num_v_heads + hv) * 2 * 16384;
     const float* m_mat = b_mat + 16384;
     const bool inner = (mode & 4) != 0 || step > 0;
-    const bool replace = !inner || warm_up_suffices(plan, g_cs, chunk_start, chunk_len, seg_chunk_start[s],
-                                                    seg_chunk_start[s + 1], num_v_heads, hv, reverse != 0);
+    // the segment table is read only under the warm-up rule: a fold over rank summaries (warm_chunks = 0) numbers
+    // its "segments" along the gathered chain, which can be longer than any local table
+    const bool replace = !inner || (warm_chunks > 0 &&
+                                    warm_up_suffices(plan, g_cs, chunk_start, chunk_len, seg_chunk_start[s],
+                                                     seg_chunk_start[s + 1], num_v_heads, hv, reverse != 0));
     float acc[kHalf];
 #pragma unroll
     for (int j = 0; j < kVec; ++j) {

@@ -317,3 +317,46 @@ def _packed_row_case(x, seq_lens, l2, split, B, T, H, HV, dev, gdn, ops):
     assert_same_bits(got, {n: want[n] for n in NAMES}, f"packed row, {split}")
     with pytest.raises(ValueError, match="columns"):
         gdn.packed_qkv_views(row[..., :-128], H, HV)
+
+
+def test_the_tape_goes_through_autograd_saved_tensors():
+    """Every tensor the backward reads is kept with ``save_for_backward``: an in-place write to an operand between
+    forward and backward is caught by autograd's version check instead of giving silently wrong gradients, and a
+    saved-tensor hook (what activation checkpointing and CPU offload use) sees the whole tape."""
+    from miles_ext_kernels_b200.cake import gdn
+
+    dev = torch.device("cuda")
+    seq_lens = (70, 130)
+    x = draw(seq_lens, (2, 4), seed=6)
+    cu = _cu(seq_lens)
+
+    def call(packed_bytes=None):
+        t = {n: x[n].unsqueeze(0).to(dev).requires_grad_(True) for n in ("q", "k", "v", "g")}
+        beta = x["beta"].unsqueeze(0).to(dev).bfloat16().requires_grad_(True)
+        o, _ = gdn.chunk_gated_delta_rule(t["q"], t["k"], t["v"], g=t["g"], beta=beta,
+                                          cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=dev), cu_seqlens_cpu=cu)
+        return t, o
+
+    t, o = call()
+    with torch.no_grad():
+        t["q"].mul_(2.0)
+    # autograd words it in one of two ways, depending on whether the saved tensor is the operand or a view of it
+    with pytest.raises(RuntimeError, match="modified (by an )?inplace"):
+        o.backward(x["do"].unsqueeze(0).to(dev))
+
+    seen = []
+
+    def pack(tensor):
+        seen.append(tensor.numel() * tensor.element_size())
+        return tensor
+
+    with torch.autograd.graph.saved_tensors_hooks(pack, lambda tensor: tensor):
+        t, o = call()
+    o.backward(x["do"].unsqueeze(0).to(dev))
+    torch.cuda.synchronize()
+    T, H, HV = sum(seq_lens), 2, 4
+    chunks = sum(-(-n // 64) for n in seq_lens)
+    # q, k, v, w, u, v_new rows; A, Aqk and the h tape per chunk; the gate and beta columns
+    floor = 2 * T * H * 256 + 4 * T * HV * 256 + chunks * HV * (2 * 8192 + 32768) + 2 * T * HV * 4
+    assert sum(seen) >= floor, (sum(seen), floor)
+    assert t["q"].grad is not None and torch.isfinite(t["q"].grad.float()).all()

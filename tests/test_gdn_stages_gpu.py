@@ -81,8 +81,10 @@ def test_backward_stages(name):
     scale = 1.0 / math.sqrt(128)
     d = {n: t.to(dev) for n, t in x.items()}
     o, final, tape, _ = stages.forward(d["q"], d["k"], d["v"], d["g"], d["beta"], meta, scale, d.get("h0"), state, l2)
-    dq, dk, dv, dg, dbeta, dh0, dh_tape, dv_new = stages.backward(tape, meta, scale, d["do"], d.get("dht"),
-                                                                  d.get("h0"), state)
+    seen = {}
+    dq, dk, dv, dg, dbeta, dh0 = stages.backward(tape, meta, scale, d["do"], d.get("dht"), d.get("h0"), state,
+                                                 inspect=seen)
+    dh_tape, dv_new = seen["dh_tape"], seen["dv_new"]
     torch.cuda.synchronize()
     stages.check_status(tape.status)
 

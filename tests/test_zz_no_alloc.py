@@ -52,6 +52,35 @@ def test_two_calls_in_a_row_give_the_regular_forward_bits():
             assert torch.equal(final, final_ref)
 
 
+def test_calls_at_the_limits_of_the_fixed_scratch():
+    """One sequence of 2,048 tokens on four value heads fills the 8,192 token-heads; 68 ragged documents on two
+    value heads fill the 256 chunk-heads (sixty of 65 tokens, two chunks each, and eight of one token)."""
+    for seq_lens, heads, seed, state in (((2048,), (2, 4), 23, True), ((65,) * 60 + (1,) * 8, (1, 2), 24, False)):
+        chunks = sum(-(-n // 64) for n in seq_lens)
+        assert sum(seq_lens) * heads[1] <= 8192 and chunks * heads[1] <= 256
+        assert sum(seq_lens) * heads[1] == 8192 or chunks * heads[1] == 256
+        (o, final), (o_ref, final_ref) = _forward_both(seq_lens, heads, seed, state)
+        assert torch.equal(o, o_ref)
+        if state:
+            assert torch.equal(final, final_ref)
+
+
+def test_null_operands_are_rejected():
+    from miles_ext_kernels_b200.cake._impl.gdn import meta as M
+    from miles_ext_kernels_b200.cake._impl.gdn import native, stages
+
+    dev = torch.device("cuda")
+    meta = M.chunk_meta(None, None, 1, 64, dev)
+    dims = stages.dims_of(meta, 1, 1, 1.0)
+    z = torch.zeros(64 * 128, dtype=torch.bfloat16, device=dev)
+    f = torch.zeros(64, device=dev)
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    with pytest.raises(ValueError, match="must not be null"):
+        native.launch("gdn_forward_static", dims, z, z, z, f, f, None, None, None, st, device=dev)
+    with pytest.raises(ValueError, match="must not be null"):
+        native.launch("gdn_forward_static", dims, z, z, z, f, f, None, z, None, None, device=dev)
+
+
 def test_a_call_beyond_the_fixed_scratch_is_rejected():
     from miles_ext_kernels_b200.cake._impl.gdn import meta as M
     from miles_ext_kernels_b200.cake._impl.gdn import native, stages
