@@ -326,18 +326,24 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
 // ---------------------------------------------------------------------------------------------------------------
 // fwd_h : the state recurrence
 // ---------------------------------------------------------------------------------------------------------------
-// One CTA of two warpgroups per (sequence, value head).  The fp32 state h [K, V] lives in registers: thread (k, half)
-// holds row k of one half of the V columns (warpgroup 0: columns 0..63, warpgroup 1: 64..127).  Per chunk:
-//   1. h_tape = bf16(h) -> shared (MN-major B operand) and the tape;            2. D1 = w h_tape        (M=64,N=128,K=128)
-//   3. v_new = u - D1 -> tape; vs = bf16(rowscale v_new) -> shared;              4. D2 = k^T vs         (M=128,N=128,K=64)
-//   5. h = gamma h + D2.
-// The next chunk's w / k / u tiles and gates arrive by cp.async while the current chunk computes (two stages).
+// One CTA per (sequence, value head), warp-specialised: two epilogue warpgroups (256 threads), one MMA-issuing warp
+// and one copy warp.  The fp32 state h [K, V] lives in the epilogue threads' registers: thread (k, half) holds row k
+// of one half of the V columns (warpgroup 0: columns 0..63, warpgroup 1: 64..127).  Per chunk:
+//   A  epilogue   h_tape = bf16(h) -> shared (MN-major B operand)                 -> "state tile ready"
+//      issuer     D1 = w h_tape (M=64,N=128,K=128) [+ q h_tape for the fused output]
+//      copy warp  h_tape tile -> the tape (TMA store); next chunk's w / k / u (/ q / Aqk) tiles (TMA loads)
+//   B  epilogue   v_new = u - D1 -> shared; vs = bf16(rowscale v_new) -> shared   -> "v tiles ready"
+//      issuer     D2 = k^T vs (M=128,N=128,K=64) [+ Aqk v_new for the fused output]
+//      copy warp  v_new tile -> the tape (TMA store; a ragged chunk's rows are stored by the epilogue threads)
+//   C  epilogue   h = gamma h + D2.
+// The roles meet on mbarriers only (no block barrier inside the walk): the epilogue threads never wait for an
+// instruction to be issued or for a store to leave, only for the two products on the step's dependency chain.
 struct FwdHSmem {
   static constexpr uint32_t kStage = 4 * 16384 + 8192;   // w, k, u, q tiles and Aqk of one chunk
   static constexpr uint32_t kW = 0, kK = 16384, kU = 32768, kQ = 49152, kAqk = 65536;
   static constexpr uint32_t kH = 2 * kStage;      // [128 k][128 v] bf16(h), 2 blocks of 16 KiB (one per V half)
   static constexpr uint32_t kVS = kH + 32768;     // [64][128] bf16(rowscale v_new)
-  static constexpr uint32_t kVN = kVS + 16384;    // [64][128] v_new (the fused output's operand)
+  static constexpr uint32_t kVN = kVS + 16384;    // [64][128] v_new (the tape's source; the fused output's operand)
   static constexpr uint32_t kG = kVN + 16384;     // gates[2][128]: GDN g2 per token [64]; KDA chunk-end gate per channel
   static constexpr uint32_t kBytes = kG + 1024;
 };
@@ -345,30 +351,42 @@ struct FwdHSmem {
 // With `o` != nullptr the walk also writes the op's output, chunk by chunk (the reference's fused `fwd_ho`):
 //   o = bf16(qscale (q h_tape) + Aqk v_new)
 // Both products read what the step already holds in shared memory (h_tape, v_new) and run on the tensor core behind
-// the step's own products; their epilogue runs one step later, in the shadow of the next step's first wait, on a
-// second set of tensor-memory columns -- the chain of dependent steps does not get longer and h is not read back.
+// the step's own products; their epilogue runs one step later, while the epilogue threads wait for the next step's
+// products, on a second set of tensor-memory columns -- the chain of dependent steps does not get longer and h is not
+// read back.
 // `gl2` != nullptr selects the per-channel-decay variant (KDA): `k` then holds k 2^{G_L - G} (the decay to the chunk
 // end is folded into the operand, so rowscale = 1) and the state decays per key channel: row k by 2^{gl2[c, hv, k]}.
 struct FwdHMaps {
   CUtensorMap k, w, u, q;  // rows, box 64 x 64 (q: the fused output only)
   CUtensorMap aqk;         // tiles [num_tiles * 64, 64], box 64 x 64 (the fused output only)
+  CUtensorMap h_out;       // tiles [num_tiles * 128, 128], box 64 x 128: the state tape (stores)
+  CUtensorMap v_new_out;   // rows, box 64 x 64: the corrected values' tape (stores)
 };
 
-__global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
-    const __grid_constant__ FwdHMaps maps, const float* __restrict__ g_cs, const float* __restrict__ h0, __nv_bfloat16* __restrict__ h_tape,
+constexpr int kScanEpilogueThreads = 256;            // warps 0..7
+constexpr int kScanIssuer = kScanEpilogueThreads;    // warp 8, lane 0: every tcgen05.mma of the walk
+constexpr int kScanMover = kScanEpilogueThreads + 32;  // warp 9, lane 0: every TMA load and store
+constexpr int kScanThreads = kScanEpilogueThreads + 64;
+
+__global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
+    const __grid_constant__ FwdHMaps maps, const float* __restrict__ g_cs, const float* __restrict__ h0,
     __nv_bfloat16* __restrict__ v_new, float* __restrict__ final_state, const int32_t* __restrict__ chunk_start,
     const int32_t* __restrict__ chunk_len, const int32_t* __restrict__ seq_chunk_start, int num_qk_heads,
     int num_v_heads, const float* __restrict__ gl2, const ScanPlan plan, __nv_bfloat16* __restrict__ o, float scale,
     int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  __shared__ uint64_t bar, bar_b, bar_qh, bar_o, bar_load[2];  // bar_b, bar_qh: the second issuing thread's products
+  // bar_h: the state tile (and this chunk's operand tiles) are ready -- every epilogue thread arrives
+  // bar_vs: the v tiles are ready -- every epilogue thread arrives
+  // bar_d1 / bar_d2 / bar_o: commits of the step's two products and of the fused output's products
+  // bar_free_h / bar_free_vn: the copy warp's store of this step has read the state tile / the v_new tile
+  __shared__ uint64_t bar_load[2], bar_h, bar_vs, bar_d1, bar_d2, bar_o, bar_free_h, bar_free_vn;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool kda = gl2 != nullptr;
-  const int quad = warp & 3, half = warp >> 2;   // tensor-memory lane quadrant; V half of this warpgroup
-  const int krow = quad * 32 + lane;             // row of h this thread holds
+  const int quad = warp & 3, half = (warp >> 2) & 1;   // tensor-memory lane quadrant; V half of this warpgroup
+  const int krow = quad * 32 + lane;                   // row of h this (epilogue) thread holds
   // grid (heads, sequences): the heads of one sequence are neighbours in launch order, so that with `seq_order`
   // (longest first) every long walk starts before any short one
   const int n = plan.seq_order != nullptr ? plan.seq_order[blockIdx.y] : int(blockIdx.y);
@@ -395,13 +413,17 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
   }
 
   const bool fused = o != nullptr && !prescan;
+  const bool tapes = !prescan;  // the walk writes h_tape and v_new
   if (tid == 0) {
-    mbar_init(&bar, 1);
-    mbar_init(&bar_b, 1);
-    mbar_init(&bar_qh, 2);
-    mbar_init(&bar_o, 1);
     mbar_init(&bar_load[0], 1);
     mbar_init(&bar_load[1], 1);
+    mbar_init(&bar_h, kScanEpilogueThreads);
+    mbar_init(&bar_vs, kScanEpilogueThreads);
+    mbar_init(&bar_d1, 1);
+    mbar_init(&bar_d2, 1);
+    mbar_init(&bar_o, 1);
+    mbar_init(&bar_free_h, 1);
+    mbar_init(&bar_free_vn, 1);
     fence_mbar_init();
     abort_flag = 0;
   }
@@ -409,13 +431,53 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
   const uint32_t sbase = smem_u32(sm);
   const int64_t v_stride = int64_t(num_v_heads) * kDim;
   const int c_begin = c_first, c_end = c_last;
-  __syncthreads();  // the barriers' initialisation is visible before the first copy is issued
+  tc_fence_before();
+  __syncthreads();  // the barriers' initialisation and the tensor-memory base are visible to every role
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const Operand op_h{sbase + FwdHSmem::kH, 16384}, op_vs{sbase + FwdHSmem::kVS, 8192};
+  const Operand op_vn{sbase + FwdHSmem::kVN, 8192};
+  // tensor-memory columns: D1 0..63 (lane split), D2 128..255, the fused output's two accumulators (q h_tape at +0,
+  // Aqk v_new at +64, both lane split) in one of two sets at 256 and 384
+  constexpr uint32_t kColO = 256;
+  constexpr uint32_t kUpper = 16u << 16;
 
-  // the tiles of chunk c by TMA (one issuing thread), its gates by cp.async
-  // (warps 2.. issue the gate copies: warp 0 also issues the MMAs and must not wait on anything here)
-  auto prefetch = [&](int c, int stage, int start, int len) {
-    const uint32_t base = sbase + stage * FwdHSmem::kStage;
-    if (tid == 32) {
+  if (tid == kScanIssuer) {
+    // ---- every product of the walk, in the order of the step's dependency chain ----------------------------------
+    for (int c = c_begin; c < c_end; ++c) {
+      const uint32_t step = uint32_t(c - c_begin), par = step & 1u;
+      const uint32_t sst = sbase + par * FwdHSmem::kStage;
+      const Operand op_w{sst + FwdHSmem::kW, 8192}, op_k{sst + FwdHSmem::kK, 8192};
+      if (!abort.wait(&bar_h, par)) break;
+      tc_fence_after();
+      // D1 = w h_tape as two N = 64 products with alternating instructions: V columns 0..63 -> lanes 0..15,
+      // 64..127 -> lanes 16..31 (columns 0..63 of tensor memory), so every lane of a warp owns a row piece
+      umma_gemm_pair<64, 64>(tmem, op_w, false, op_h, true, 128, false, false, tmem + kUpper, op_w, false,
+                             operand_at(op_h, 0, 1), true, 128, false, false);
+      umma_commit(&bar_d1);
+      if (fused) {  // q h_tape behind it; the state update's commit covers it (commits are cumulative)
+        const Operand op_q{sst + FwdHSmem::kQ, 8192};
+        const uint32_t set = tmem + kColO + par * 128;
+        umma_gemm_pair<64, 64>(set, op_q, false, op_h, true, 128, false, false, set + kUpper, op_q, false,
+                               operand_at(op_h, 0, 1), true, 128, false, false);
+      }
+      if (!abort.wait(&bar_vs, par)) break;
+      tc_fence_after();
+      umma_gemm<128, 128>(tmem + 128, op_k, true, op_vs, true, 64, false);
+      umma_commit(&bar_d2);
+      if (fused) {  // Aqk v_new, behind the state update's product
+        const Operand op_a{sst + FwdHSmem::kAqk, 8192};
+        const uint32_t set = tmem + kColO + par * 128 + 64;
+        umma_gemm_pair<64, 64>(set, op_a, false, op_vn, true, 64, false, false, set + kUpper, op_a, false,
+                               operand_at(op_vn, 0, 1), true, 64, false, false);
+        umma_commit(&bar_o);
+      }
+    }
+  } else if (tid == kScanMover) {
+    // ---- every copy of the walk: operand tiles in, tapes out ------------------------------------------------------
+    auto load = [&](int c, uint32_t stage) {
+      const uint32_t base = sbase + stage * FwdHSmem::kStage;
+      const int start = chunk_start[c];
       mbar_arrive_expect(&bar_load[stage], fused ? 4 * 16384 + 8192 : 3 * 16384);
       tma_load_tile128(base + FwdHSmem::kW, 8192, &maps.w, hv * kDim, start, &bar_load[stage]);
       tma_load_tile128(base + FwdHSmem::kK, 8192, &maps.k, hq * kDim, start, &bar_load[stage]);
@@ -425,220 +487,208 @@ __global__ void __launch_bounds__(256) gdn_fwd_h_kernel(
         tma_load_box(base + FwdHSmem::kAqk, &maps.aqk, 0, int((int64_t(c) * num_v_heads + hv) * 64),
                      &bar_load[stage]);
       }
-    }
-    const int t = tid - 64;
-    if (kda) {
-      if (t >= 0 && t < 128) cp_async4(smem_u32(s_g2 + stage * 128 + t), gl2 + (int64_t(c) * num_v_heads + hv) * kDim + t);
-    } else if (t >= 0 && t < 64) {
-      cp_async4(smem_u32(s_g2 + stage * 128 + t), g_cs + int64_t(start + (t < len ? t : len - 1)) * num_v_heads + hv);
-    }
-    cp_async_commit();
-  };
-  int start = 0, len = 0;
-  if (c_begin < c_end) {
-    start = chunk_start[c_begin], len = chunk_len[c_begin];
-    prefetch(c_begin, 0, start, len);
-  }
-
-  // fp32 state: 64 columns of row krow
-  float h[64];
-  if (transfer) {
-#pragma unroll
-    for (int j = 0; j < 64; ++j) h[j] = (krow == half * 64 + j) ? 1.f : 0.f;
-  } else if (h0 != nullptr && state_row >= 0) {
-    const float4* src = reinterpret_cast<const float4*>(
-        h0 + ((int64_t(state_row) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float4 t = __ldg(src + j);
-      h[4 * j] = t.x, h[4 * j + 1] = t.y, h[4 * j + 2] = t.z, h[4 * j + 3] = t.w;
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 64; ++j) h[j] = 0.f;
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_slot;
-  const Operand op_h{sbase + FwdHSmem::kH, 16384}, op_vs{sbase + FwdHSmem::kVS, 8192};
-  const Operand op_vn{sbase + FwdHSmem::kVN, 8192};
-  // tensor-memory columns: D1 0..63 (lane split), D2 128..255, the fused output's two accumulators (q h_tape at +0,
-  // Aqk v_new at +64, both lane split) in one of two sets at 256 and 384
-  constexpr uint32_t kColO = 256;
-  // this thread's piece of a [64 x 128] lane-split accumulator: row out_row, logical columns out_col .. + 32
-  const int out_row = quad * 16 + (lane & 15), out_col = (lane >> 4) * 64 + half * 32;
-
-  // the fused output of the previous chunk: its products were committed on bar_o a step ago
-  uint32_t phase_o = 0, phase_b = 0, phase_qh = 0;
-  struct Rows {
-    int start, len;
-    float qs;
-  } cur = {0, 0, 0.f}, prev = {0, 0, 0.f};  // of the chunk the walk is at / of the one before it
-  // in two parts (16 of this thread's 32 columns each), one per wait shadow of the step: a part is about as long
-  // as the wait it hides in
-  auto write_output = [&](int c_prev, int part, const Rows& rows) {
-    if (part == 0) {
-      if (!mbar_wait(&bar_o, phase_o)) abort.raise();
-      phase_o ^= 1;
-      tc_fence_after();
-    }
-    const uint32_t set = kColO + uint32_t((c_prev - c_begin) & 1) * 128;
-    float a[16], b[16];
-    tmem_ld16(tmem_addr(tmem, warp, set + half * 32 + part * 16), a);
-    tmem_ld16(tmem_addr(tmem, warp, set + 64 + half * 32 + part * 16), b);
-    tmem_ld_wait();
-#pragma unroll
-    for (int j = 0; j < 16; ++j) a[j] = fmaf(rows.qs, a[j], b[j]);
-    if (out_row < rows.len) {
-      __nv_bfloat16* dst = o + int64_t(rows.start + out_row) * v_stride + hv * kDim + out_col + part * 16;
-      reinterpret_cast<uint4*>(dst)[0] = pack8(a);
-      reinterpret_cast<uint4*>(dst)[1] = pack8(a + 8);
-    }
-  };
-
-  uint32_t phase = 0;
-  for (int c = c_begin; c < c_end; ++c) {
-    const int stage = (c - c_begin) & 1;
-    // the next chunk's extent: requested now, needed when its tiles are (nothing on the step's path waits for it)
-    int next_start = 0, next_len = 0;
-    if (c + 1 < c_end) next_start = chunk_start[c + 1], next_len = chunk_len[c + 1];
-    uint8_t* st = sm + stage * FwdHSmem::kStage;
-    const Operand op_w{sbase + stage * FwdHSmem::kStage + FwdHSmem::kW, 8192};
-    const Operand op_k{sbase + stage * FwdHSmem::kStage + FwdHSmem::kK, 8192};
-    // 1. h_tape = bf16(h): this thread's half row -> shared (block `half`) and the tape
-    {
-      __nv_bfloat16* tape = h_tape + ((int64_t(c) * num_v_heads + hv) * kDim + krow) * kDim + half * 64;
-#pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
-        const uint4 packed = pack8(h + 8 * cc);
-        set_tile_chunk(sm + FwdHSmem::kH, 16384, krow, half * 8 + cc, packed);
-        if (!prescan) reinterpret_cast<uint4*>(tape)[cc] = packed;
+    };
+    if (c_begin < c_end) load(c_begin, 0);
+    for (int c = c_begin; c < c_end; ++c) {
+      const uint32_t step = uint32_t(c - c_begin), par = step & 1u;
+      if (c + 1 < c_end) {
+        // the other stage's last readers were the previous chunk's products (and its epilogue, which ended before
+        // they were issued)
+        if (c > c_begin && !abort.wait(fused ? &bar_o : &bar_d2, par ^ 1u)) break;
+        load(c + 1, par ^ 1u);
       }
-    }
-    cp_async_wait_all();  // this chunk's gates and tiles have landed (issued one step ago)
-    if (!mbar_wait(&bar_load[stage], ((c - c_begin) >> 1) & 1)) abort.raise();
-    if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows
-      clear_tile_rows<256>(st + FwdHSmem::kW, len, tid);
-      clear_tile_rows<256>(st + FwdHSmem::kK, len, tid);
-      clear_tile_rows<256>(st + FwdHSmem::kU, len, tid);
-      if (fused) clear_tile_rows<256>(st + FwdHSmem::kQ, len, tid);
-    }
-    if (transfer) clear_tile_rows<256>(st + FwdHSmem::kU, 0, tid);  // the homogeneous recurrence: u = 0
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    if (abort.raised()) break;
-
-    // D1 = w h_tape as two N = 64 products: V columns 0..63 -> lanes 0..15, 64..127 -> lanes 16..31 (columns 0..63
-    // of tensor memory), so every lane of a warp owns a row piece in the epilogue.  Two threads of different warps
-    // issue one half each (a thread's instructions go out every ~52 cycles, the tensor core takes ~40); the second
-    // one also issues the fused output's products.
-    if (tid == 0 || tid == 64) {
-      const uint32_t lanes = tid == 0 ? 0u : 16u << 16;
-      const Operand h_half = tid == 0 ? op_h : operand_at(op_h, 0, 1);
-      umma_gemm<64, 64>(tmem + lanes, op_w, false, h_half, true, 128, false);
-      umma_commit(tid == 0 ? &bar : &bar_b);
-      if (fused) {  // q h_tape, behind the step's own product; waited for before the state tile is rewritten
-        const Operand op_q{sbase + stage * FwdHSmem::kStage + FwdHSmem::kQ, 8192};
-        const uint32_t set = tmem + kColO + uint32_t((c - c_begin) & 1) * 128;
-        umma_gemm<64, 64>(set + lanes, op_q, false, h_half, true, 128, false);
-        umma_commit(&bar_qh);
-      }
-    }
-    // the previous chunk's output, in the shadow of this step's first wait; its products were the other stage's
-    // last readers, so the next chunk's tiles may only be requested after them
-    if (fused && c > c_begin) write_output(c - 1, 0, cur);  // `cur` still describes chunk c - 1 here
-    if (c + 1 < c_end) prefetch(c + 1, stage ^ 1, next_start, next_len);
-    if (!mbar_wait(&bar, phase)) abort.raise();
-    if (!mbar_wait(&bar_b, phase_b)) abort.raise();
-    phase ^= 1, phase_b ^= 1;
-    tc_fence_after();
-
-    const float* g2 = s_g2 + stage * 128;
-    const float g_last = kda ? g2[krow] : g2[len - 1];  // KDA: this thread's key channel
-    {
-      // row i = 16 quad + lane % 16; logical V columns (lane / 16) * 64 + half * 32 .. + 32
-      const int i = quad * 16 + (lane & 15);
-      const int lcol = (lane >> 4) * 64 + half * 32;
-      const bool live = i < len;
-      const float rs = live ? (kda ? 1.f : fast_exp2(g_last - g2[i])) : 0.f;
-      __nv_bfloat16* vrow = v_new + int64_t(start + i) * v_stride + hv * kDim + lcol;
-      float d[32];
-      tmem_ld32(tmem_addr(tmem, warp, half * 32), d);
-      tmem_ld_wait();
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        float uv[8], vs[8];
-        unpack8(tile_chunk(st + FwdHSmem::kU, 8192, i, (lcol >> 3) + jj), uv);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          uv[e] = live ? uv[e] - d[jj * 8 + e] : 0.f;
-          vs[e] = rs * uv[e];
+      if (tapes) {
+        if (!abort.wait(&bar_h, par)) break;
+        tma_store_tile128(&maps.h_out, 0, int((int64_t(c) * num_v_heads + hv) * 128), sbase + FwdHSmem::kH, 16384);
+        tma_store_commit();
+        tma_store_wait_read();
+        mbar_arrive(&bar_free_h);
+        if (!abort.wait(&bar_vs, par)) break;
+        if (chunk_len[c] == kChunk) {  // a ragged chunk's rows are stored by the epilogue threads
+          tma_store_tile128(&maps.v_new_out, hv * kDim, chunk_start[c], sbase + FwdHSmem::kVN, 8192);
+          tma_store_commit();
+          tma_store_wait_read();
         }
-        const uint4 packed = pack8(uv);
-        if (live && !prescan) reinterpret_cast<uint4*>(vrow)[jj] = packed;
-        set_tile_chunk(sm + FwdHSmem::kVS, 8192, i, (lcol >> 3) + jj, pack8(vs));
-        if (fused) set_tile_chunk(sm + FwdHSmem::kVN, 8192, i, (lcol >> 3) + jj, packed);
-      }
-      if (fused) {  // what the output's epilogue needs one step from now
-        prev = cur;
-        cur = {start, len, kda ? scale : scale * fast_exp2(g2[i])};
+        mbar_arrive(&bar_free_vn);
       }
     }
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    if (tid == 0) {
-      umma_gemm<128, 128>(tmem + 128, op_k, true, op_vs, true, 64, false);
-      umma_commit(&bar);
-      if (fused) {  // Aqk v_new, behind the state update's product
-        const Operand op_a{sbase + stage * FwdHSmem::kStage + FwdHSmem::kAqk, 8192};
-        const uint32_t set = tmem + kColO + uint32_t((c - c_begin) & 1) * 128 + 64;
-        umma_gemm<64, 64>(set, op_a, false, op_vn, true, 64, false);
-        umma_gemm<64, 64>(set + (16u << 16), op_a, false, operand_at(op_vn, 0, 1), true, 64, false);
-        umma_commit(&bar_o);
+    tma_store_wait_all();
+  } else if (tid < kScanEpilogueThreads) {
+    // ---- the state and the epilogues ---------------------------------------------------------------------------------
+    // the gates of chunk c by cp.async (the tiles come from the copy warp)
+    auto prefetch_gates = [&](int c, int stage, int start, int len) {
+      const int t = tid - 64;
+      if (kda) {
+        if (t >= 0 && t < 128) cp_async4(smem_u32(s_g2 + stage * 128 + t), gl2 + (int64_t(c) * num_v_heads + hv) * kDim + t);
+      } else if (t >= 0 && t < 64) {
+        cp_async4(smem_u32(s_g2 + stage * 128 + t), g_cs + int64_t(start + (t < len ? t : len - 1)) * num_v_heads + hv);
       }
+      cp_async_commit();
+    };
+    int start = 0, len = 0;
+    if (c_begin < c_end) {
+      start = chunk_start[c_begin], len = chunk_len[c_begin];
+      prefetch_gates(c_begin, 0, start, len);
     }
-    if (fused && c > c_begin) write_output(c - 1, 1, prev);
-    if (!mbar_wait(&bar, phase)) abort.raise();
-    phase ^= 1;
-    tc_fence_after();
 
-    const float gamma = fast_exp2(g_last);
+    // fp32 state: 64 columns of row krow
+    float h[64];
+    if (transfer) {
 #pragma unroll
-    for (int p = 0; p < 2; ++p) {
-      float d[32];
-      tmem_ld32(tmem_addr(tmem, warp, 128 + half * 64 + p * 32), d);
+      for (int j = 0; j < 64; ++j) h[j] = (krow == half * 64 + j) ? 1.f : 0.f;
+    } else if (h0 != nullptr && state_row >= 0) {
+      const float4* src = reinterpret_cast<const float4*>(
+          h0 + ((int64_t(state_row) * num_v_heads + hv) * kDim + krow) * kDim + half * 64);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float4 t = __ldg(src + j);
+        h[4 * j] = t.x, h[4 * j + 1] = t.y, h[4 * j + 2] = t.z, h[4 * j + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) h[j] = 0.f;
+    }
+    // this thread's piece of a [64 x 128] lane-split accumulator: row out_row, logical columns out_col .. + 32
+    const int out_row = quad * 16 + (lane & 15), out_col = (lane >> 4) * 64 + half * 32;
+
+    // the fused output of the previous chunk: its products were committed on bar_o a step ago
+    uint32_t phase_o = 0;
+    struct Rows {
+      int start, len;
+      float qs;
+    } cur = {0, 0, 0.f}, prev = {0, 0, 0.f};  // of the chunk the walk is at / of the one before it
+    // in two parts (16 of this thread's 32 columns each), one per wait of the step: a part is about as long as the
+    // wait it fills
+    bool alive = true;
+    auto write_output = [&](int c_prev, int part, const Rows& rows) {
+      if (part == 0) {
+        if (!abort.wait(&bar_o, phase_o)) alive = false;
+        phase_o ^= 1;
+        tc_fence_after();
+      }
+      if (!alive) return;
+      const uint32_t set = kColO + uint32_t((c_prev - c_begin) & 1) * 128;
+      float a[16], b[16];
+      tmem_ld16(tmem_addr(tmem, warp, set + half * 32 + part * 16), a);
+      tmem_ld16(tmem_addr(tmem, warp, set + 64 + half * 32 + part * 16), b);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) h[p * 32 + j] = fmaf(gamma, h[p * 32 + j], d[j]);
+      for (int j = 0; j < 16; ++j) a[j] = fmaf(rows.qs, a[j], b[j]);
+      if (out_row < rows.len) {
+        __nv_bfloat16* dst = o + int64_t(rows.start + out_row) * v_stride + hv * kDim + out_col + part * 16;
+        reinterpret_cast<uint4*>(dst)[0] = pack8(a);
+        reinterpret_cast<uint4*>(dst)[1] = pack8(a + 8);
+      }
+    };
+
+    for (int c = c_begin; c < c_end && alive; ++c) {
+      const uint32_t step = uint32_t(c - c_begin), par = step & 1u;
+      const int stage = int(par);
+      // the next chunk's extent: requested now, needed when its gates are (nothing on the step's path waits for it)
+      int next_start = 0, next_len = 0;
+      if (c + 1 < c_end) next_start = chunk_start[c + 1], next_len = chunk_len[c + 1];
+      uint8_t* st = sm + stage * FwdHSmem::kStage;
+      // the previous step's tape store has read the state tile
+      if (tapes && step > 0 && !abort.wait(&bar_free_h, par ^ 1u)) break;
+      // A. h_tape = bf16(h): this thread's half row -> shared (block `half`)
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) set_tile_chunk(sm + FwdHSmem::kH, 16384, krow, half * 8 + cc, pack8(h + 8 * cc));
+      cp_async_wait_all();  // this chunk's gates have landed (issued one step ago) ...
+      if (!abort.wait(&bar_load[stage], (step >> 1) & 1u)) break;  // ... and so have its tiles
+      if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows
+        clear_tile_rows<kScanEpilogueThreads>(st + FwdHSmem::kW, len, tid);
+        clear_tile_rows<kScanEpilogueThreads>(st + FwdHSmem::kK, len, tid);
+        clear_tile_rows<kScanEpilogueThreads>(st + FwdHSmem::kU, len, tid);
+        if (fused) clear_tile_rows<kScanEpilogueThreads>(st + FwdHSmem::kQ, len, tid);
+      }
+      if (transfer) clear_tile_rows<kScanEpilogueThreads>(st + FwdHSmem::kU, 0, tid);  // the homogeneous recurrence: u = 0
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bar_h);
+      // while the first product runs: the previous chunk's output, the next chunk's gates
+      if (fused && step > 0) write_output(c - 1, 0, cur);  // `cur` still describes chunk c - 1 here
+      if (c + 1 < c_end) prefetch_gates(c + 1, stage ^ 1, next_start, next_len);
+      if (!alive || !abort.wait(&bar_d1, par)) break;
+      // every epilogue thread's writes of this step (cleared rows, gates) are visible past the barrier they all
+      // arrived on
+      if (!abort.wait(&bar_h, par)) break;
+      tc_fence_after();
+
+      // B. v_new = u - D1; vs = bf16(rowscale v_new)  (the previous step's tape store has read the v_new tile)
+      if (tapes && step > 0 && !abort.wait(&bar_free_vn, par ^ 1u)) break;
+      const float* g2 = s_g2 + stage * 128;
+      const float g_last = kda ? g2[krow] : g2[len - 1];  // KDA: this thread's key channel
+      {
+        // row i = 16 quad + lane % 16; logical V columns (lane / 16) * 64 + half * 32 .. + 32
+        const int i = quad * 16 + (lane & 15);
+        const int lcol = (lane >> 4) * 64 + half * 32;
+        const bool live = i < len;
+        const bool by_hand = tapes && len < kChunk;  // a ragged chunk: no 64-row box may be stored
+        const float rs = live ? (kda ? 1.f : fast_exp2(g_last - g2[i])) : 0.f;
+        __nv_bfloat16* vrow = v_new + int64_t(start + i) * v_stride + hv * kDim + lcol;
+        float d[32];
+        tmem_ld32(tmem_addr(tmem, warp, half * 32), d);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          float uv[8], vs[8];
+          unpack8(tile_chunk(st + FwdHSmem::kU, 8192, i, (lcol >> 3) + jj), uv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            uv[e] = live ? uv[e] - d[jj * 8 + e] : 0.f;
+            vs[e] = rs * uv[e];
+          }
+          const uint4 packed = pack8(uv);
+          if (by_hand && live) reinterpret_cast<uint4*>(vrow)[jj] = packed;
+          set_tile_chunk(sm + FwdHSmem::kVS, 8192, i, (lcol >> 3) + jj, pack8(vs));
+          if (tapes) set_tile_chunk(sm + FwdHSmem::kVN, 8192, i, (lcol >> 3) + jj, packed);
+        }
+        if (fused) {  // what the output's epilogue needs one step from now
+          prev = cur;
+          cur = {start, len, kda ? scale : scale * fast_exp2(g2[i])};
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bar_vs);
+      if (fused && step > 0) write_output(c - 1, 1, prev);
+      if (!abort.wait(&bar_d2, par)) break;
+      tc_fence_after();
+
+      // C. h = gamma h + D2
+      const float gamma = fast_exp2(g_last);
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        float d[32];
+        tmem_ld32(tmem_addr(tmem, warp, 128 + half * 64 + p * 32), d);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) h[p * 32 + j] = fmaf(gamma, h[p * 32 + j], d[j]);
+      }
+      tc_fence_before();
+      start = next_start, len = next_len;
     }
-    // q h_tape has read the state tile (long since: it went out before the state update's product)
-    if (fused) {
-      if (!mbar_wait(&bar_qh, phase_qh)) abort.raise();
-      phase_qh ^= 1;
+    if (fused && c_end > c_begin && alive && !abort.raised()) {
+      write_output(c_end - 1, 0, cur);
+      write_output(c_end - 1, 1, cur);
     }
-    start = next_start, len = next_len;
+    cp_async_wait_all();
+
+    float* out_state = prescan ? plan.summary + ((int64_t(n) * num_v_heads + hv) * 2 + (transfer ? 1 : 0)) * kDim * kDim
+                               : (final_state ? final_state + (int64_t(n) * num_v_heads + hv) * kDim * kDim : nullptr);
+    if (out_state != nullptr && alive && !abort.raised()) {
+      float4* dst = reinterpret_cast<float4*>(out_state + krow * kDim + half * 64);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) dst[j] = make_float4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+    }
   }
-  if (fused && c_end > c_begin && !abort.raised()) {
-    write_output(c_end - 1, 0, cur);
-    write_output(c_end - 1, 1, cur);
+  if (abort.raised()) {  // copies may still be in flight: give them time to land before the CTA's memory goes
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 100000ull) {
+    }
   }
-  cp_async_wait_all();
   tc_fence_before();
   __syncthreads();
-
-  float* out_state = prescan ? plan.summary + ((int64_t(n) * num_v_heads + hv) * 2 + (transfer ? 1 : 0)) * kDim * kDim
-                             : (final_state ? final_state + (int64_t(n) * num_v_heads + hv) * kDim * kDim : nullptr);
-  if (out_state != nullptr && !abort.raised()) {
-    float4* dst = reinterpret_cast<float4*>(out_state + krow * kDim + half * 64);
-#pragma unroll
-    for (int j = 0; j < 16; ++j) dst[j] = make_float4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
-  }
   if (abort.raised() && tid == 0) atomicExch(status, kDevWaitTimeout | (2 << 8));
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
@@ -831,14 +881,22 @@ int launch_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* 
     maps.q = maps.k;  // never read
     maps.aqk = maps.k;
   }
+  if (plan.seg_flags == nullptr) {  // an ordinary walk writes the two tapes
+    if (!h_tape || !v_new) return fail(MEK_ERR_INVALID, "%s: h_tape or v_new is null", what);
+    if (int rc = make_tiles_map(&maps.h_out, h_tape, int64_t(d->num_chunks) * d->num_v_heads, 128, 128, what)) return rc;
+    if (int rc = make_rows_map(&maps.v_new_out, v_new, d->total_tokens, d->num_v_heads, what)) return rc;
+  } else {
+    maps.h_out = maps.k;  // a pre-scan writes no tape
+    maps.v_new_out = maps.k;
+  }
   if (d->num_seqs > 65535)
     return fail(MEK_ERR_UNSUPPORTED, "%s: at most 65,535 sequences (or scan segments) per call, got %d", what,
                 d->num_seqs);
   const dim3 grid(d->num_v_heads, d->num_seqs, plan.seg_flags != nullptr ? 2 : 1);
   ScanPlan ordered = plan;
   ordered.seq_order = d->seq_order;
-  gdn_fwd_h_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      maps, g_cs, h0, static_cast<__nv_bfloat16*>(h_tape), static_cast<__nv_bfloat16*>(v_new), final_state,
+  gdn_fwd_h_kernel<<<grid, kScanThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      maps, g_cs, h0, static_cast<__nv_bfloat16*>(v_new), final_state,
       d->chunk_start, d->chunk_len, d->seq_chunk_start, d->num_qk_heads, d->num_v_heads, gl2, ordered,
       static_cast<__nv_bfloat16*>(fused.o), d->scale, status);
   return launched(what);

@@ -93,6 +93,21 @@ struct Abort {
   volatile int* flag;
   __device__ __forceinline__ void raise() { *flag = 1; }
   __device__ __forceinline__ bool raised() const { return *flag != 0; }
+  // A bounded wait that also gives up as soon as another thread of the block has raised the flag (warp-specialised
+  // kernels, whose roles wait on one another through mbarriers: when one role gives up the others follow at once
+  // instead of each running out its own second).  Returns false when the walk must stop.
+  __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity) const {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if (*flag != 0) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *flag = 1;
+        return false;
+      }
+    }
+  }
 };
 
 }  // namespace mek

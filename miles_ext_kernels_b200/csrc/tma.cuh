@@ -104,6 +104,26 @@ __device__ __forceinline__ void tma_load_tile128(uint32_t dst, uint32_t block_st
   tma_load_box(dst + block_stride, map, x + 64, y, bar);
 }
 
+// One box (64 columns x the map's box rows) from shared memory at `src` (1024-byte aligned, the swizzled block
+// layout) to the tensor at (x, y); joins the issuing thread's current bulk group.  Generic-proxy writes to the block
+// must have been fenced (fence.proxy.async) by their writers before the issuing thread learns of them.
+__device__ __forceinline__ void tma_store_box(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_tile128(const CUtensorMap* map, int x, int y, uint32_t src,
+                                                  uint32_t block_stride) {
+  tma_store_box(map, x, y, src);
+  tma_store_box(map, x + 64, y, src + block_stride);
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until the bulk stores this thread committed have READ their shared-memory source (the source may be rewritten).
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Until they have completed (the data is in global memory).
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // Clears the rows [first, 64) of a [64 x 128] tile (two 8 KiB blocks): the part of a ragged chunk's box that holds
 // another sequence's tokens.  Every thread of the `NT` calling threads takes part.
 template <int NT>

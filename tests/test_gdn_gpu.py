@@ -327,10 +327,10 @@ def test_the_tape_goes_through_autograd_saved_tensors():
 
     dev = torch.device("cuda")
     seq_lens = (70, 130)
-    x = draw(seq_lens, (2, 4), seed=6)
+    x = draw(seq_lens, (2, 4), seed=6, normalised=True)  # the call below does not normalise q / k itself
     cu = _cu(seq_lens)
 
-    def call(packed_bytes=None):
+    def call():
         t = {n: x[n].unsqueeze(0).to(dev).requires_grad_(True) for n in ("q", "k", "v", "g")}
         beta = x["beta"].unsqueeze(0).to(dev).bfloat16().requires_grad_(True)
         o, _ = gdn.chunk_gated_delta_rule(t["q"], t["k"], t["v"], g=t["g"], beta=beta,
@@ -358,5 +358,5 @@ def test_the_tape_goes_through_autograd_saved_tensors():
     chunks = sum(-(-n // 64) for n in seq_lens)
     # q, k, v, w, u, v_new rows; A, Aqk and the h tape per chunk; the gate and beta columns
     floor = 2 * T * H * 256 + 4 * T * HV * 256 + chunks * HV * (2 * 8192 + 32768) + 2 * T * HV * 4
-    assert sum(seen) >= floor, (sum(seen), floor)
+    assert sum(seen) >= floor, (sum(seen), floor, seen)
     assert t["q"].grad is not None and torch.isfinite(t["q"].grad.float()).all()
