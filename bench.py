@@ -330,7 +330,8 @@ def context_parallel_parity(device, rank: int, world: int) -> dict:
     """A short sequence (``world x 2,048`` tokens, H = HV = 32) split over the ranks: o and every gradient gathered to
     rank 0 and compared with the undivided call on rank 0.  Budgets: relative RMS error <= 6e-3 and largest error <=
     2e-2 of the largest reference magnitude, per tensor.  Weak gates (g = -0.5 U(0, 1)) carry state across every
-    cut; the benchmark's strong gates are checked too."""
+    cut; the benchmark's strong gates are checked too.  A control run in which nothing crosses the cuts (every slice
+    as a sequence of its own) goes through the same comparison and has to be rejected under the weak gates."""
     import torch.distributed as dist
 
     import miles_ext_kernels_b200 as package
@@ -374,14 +375,26 @@ def context_parallel_parity(device, rank: int, world: int) -> dict:
             want = [o.detach()] + [t.grad for t in leaves]
             magnitudes = [float(t.float().abs().max()) for t in want]
         context = gdn.build_kcp_context((0, S), device=device)
-        for mode in ("parallel", "sequential"):
-            package.configure(cake_gdn_variant="det", cake_gdn_kcp_exchange=mode)
+        cu_mine = (0, T)
+        cu_mine_dev = torch.tensor(cu_mine, dtype=torch.int32, device=device)
+
+        def run(mode):
+            """This rank's slice: under the context with the exchange `mode`, or (mode None) as a sequence of its own
+            with nothing crossing the cuts -- the control that the comparison below must reject."""
             leaves = _leaves(mine)
-            o = gdn.kcp_chunk_gated_delta_rule(*leaves, context)
+            if mode is None:
+                o, _ = gdn.chunk_gated_delta_rule(*leaves[:3], g=leaves[3], beta=leaves[4], cu_seqlens=cu_mine_dev,
+                                                  cu_seqlens_cpu=cu_mine)
+            else:
+                package.configure(cake_gdn_variant="det", cake_gdn_kcp_exchange=mode)
+                o = gdn.kcp_chunk_gated_delta_rule(*leaves, context)
             o.backward(mine["do"])
+            return [o.detach()] + [t.grad for t in leaves]
+
+        for mode in ("parallel", "sequential", None):
             worst_rms = worst_abs = 0.0
             finite, same_bits = True, True
-            for i, local in enumerate([o.detach()] + [t.grad for t in leaves]):
+            for i, local in enumerate(run(mode)):
                 whole = torch.empty((world * local.shape[1], *local.shape[2:]), dtype=local.dtype, device=device)
                 dist.all_gather_into_tensor(whole, local[0].contiguous())
                 if rank == 0:
@@ -395,9 +408,17 @@ def context_parallel_parity(device, rank: int, world: int) -> dict:
                     worst_rms = rms if rms > worst_rms or rms != rms else worst_rms
                     worst_abs = top if top > worst_abs or top != top else worst_abs
             passed = finite and worst_rms <= 6e-3 and worst_abs <= 2e-2
-            ok = ok and passed
-            cases[f"{gate}/{mode}"] = {"rel_rms": worst_rms, "max_abs_rel": worst_abs, "finite": finite,
-                                       "same_bits": same_bits, "ok": passed}
+            record = {"rel_rms": worst_rms, "max_abs_rel": worst_abs, "finite": finite, "same_bits": same_bits}
+            if mode is None:
+                # nothing crossed the cuts: with gates that carry state the comparison must say so, or it proves nothing
+                record["rejected"] = not passed
+                if gate == "weak":
+                    ok = ok and not passed
+                cases[f"{gate}/control: no exchange"] = record
+            else:
+                record["ok"] = passed
+                ok = ok and passed
+                cases[f"{gate}/{mode}"] = record
         del full, mine, want
     package.configure(cake_gdn_variant="det")
     return {"ok": ok, "tokens": S, "num_heads": HV, "tensors": "o, dq, dk, dv, dg, dbeta", "worst_over_tensors": cases,

@@ -329,7 +329,9 @@ class _ParallelExchange:
         index = [r * slots + s for r, s in chain]
         if index == list(range(index[0], index[0] + len(index))):
             return flat[index[0] : index[0] + len(index)]
-        return flat.index_select(0, torch.tensor(index, dtype=torch.int64).pin_memory().to(flat.device, non_blocking=True))
+        from . import scan
+
+        return flat.index_select(0, scan._small_table(tuple(index), torch.int64, flat.device))
 
     def _exchange(self, dims, meta, HV, device, publish, slots, chains, summarise, reverse):
         from . import scan

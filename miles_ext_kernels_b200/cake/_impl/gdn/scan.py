@@ -216,13 +216,33 @@ def fold_ranks(dims: native.Dims, gathered: torch.Tensor, first: int, last: int,
     down to ``first``).  ``[1, HV, 128, 128]``."""
     device = gathered.device
     HV = gathered.shape[1]
-    span = torch.tensor([first, last + 1], dtype=torch.int32).pin_memory().to(device, non_blocking=True)
+    span = _small_table((first, last + 1), torch.int32, device)
     out = torch.empty((1, HV, 128, 128), dtype=torch.float32, device=device)
     native.launch("gdn_scan_stitch", dims, 1, span, gathered, None, None, None, out, int(reverse), 0, 0.0, 0,
                   device=device)
     return out
 
 
+_TABLES: dict[tuple, tuple] = {}
+
+
+def _small_table(values: tuple[int, ...], dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+    """A few integers on the device, uploaded once per distinct content and kept: a call neither allocates pinned
+    memory nor copies from a temporary (so it can be captured in a CUDA graph and replayed)."""
+    key = (values, dtype, device.type, device_index(device))
+    found = _TABLES.get(key)
+    if found is not None:
+        if found[1] is not None:
+            found[1].wait()
+        return found[0]
+    if len(_TABLES) >= 256:
+        _TABLES.clear()
+    table, guard = upload(torch.tensor(values, dtype=dtype), device)
+    _TABLES[key] = (table, guard)
+    return table
+
+
 def release() -> None:
     _PLANS.clear()
+    _TABLES.clear()
     choose_parts.cache_clear()

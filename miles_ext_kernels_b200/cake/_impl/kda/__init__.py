@@ -5,6 +5,7 @@ from ..._runtime import loader
 loader.install_op("kda")
 
 from .kcp import (  # noqa: E402
+    RecomputeHandle,
     build_context_kcp,
     chunk_kda_bwd_kcp,
     chunk_kda_fwd_kcp,
@@ -25,6 +26,7 @@ from .ops import (  # noqa: E402
 __all__ = [
     "DEFAULT_SCALE",
     "MAX_HEADS",
+    "RecomputeHandle",
     "build_context_kcp",
     "chunk_kda",
     "chunk_kda_bwd",

@@ -16,7 +16,14 @@ multiples of 64 tokens inside their documents, within the accuracy budgets other
 affine fragment summaries (pre-scan of a fragment's segments, one all-gather, a fold per fragment; every layout;
 within the accuracy budgets).
 
-No package options (``save_mode``, ``graph``, ...).
+Options of the ``*_kcp`` entry points (the reference passes them on to its packages; reference:
+miles_ext_kernels/cake/_impl/kda/kcp.py:144-146): ``save_mode`` (``"full"`` keeps the forward's tapes for the backward,
+``"light"`` keeps the operands and the states that entered this rank's fragments and replays the local kernels in the
+backward, without a second exchange), ``recompute_handle`` (a :class:`RecomputeHandle`: under activation
+checkpointing the region's replayed forward binds the states the original forward received instead of exchanging
+again), ``checkpoint_keep`` (``"states"``: what a handle keeps) and ``exchange`` (``"auto"``, ``"sequential"``,
+``"parallel"``: this call's boundary-state exchange instead of the configured one).  The packages' other options
+(``boundary_mode``, ``workspace``, ``save_transfer``, ``graph``) have no counterpart here and are refused.
 
 In the raw gate mode the gradients of ``A_log`` / ``dt_bias`` are this rank's partial sums;
 :func:`reduce_gate_param_grads_kcp` sums them over the group in rank order, the same bits on every rank.
@@ -36,6 +43,7 @@ from . import ops
 
 __all__ = [
     "KcpPartition",
+    "RecomputeHandle",
     "build_context_kcp",
     "chunk_kda_bwd_kcp",
     "chunk_kda_fwd_kcp",
@@ -99,9 +107,58 @@ def build_context_kcp(part: KcpPartition, group: Any, rank: int, device: Any, co
                       "contiguous" if part.fragments is not None else part.layout, part.fragments)
 
 
-def _no_options(options: dict[str, Any]) -> None:
-    if options:
-        raise NotImplementedError(f"the KCP entry points take no package options here, got {sorted(options)}")
+class RecomputeHandle:
+    """What the original forward of a checkpointed region received over the exchange, kept for the region's replay.
+
+    Under ``torch.utils.checkpoint`` the backward re-runs the region's forward, and with it the forward's state
+    exchange -- a collective inside the backward of every rank.  A call that is given a handle stores the states that
+    entered this rank's fragments in it; the replayed forward (a forward that runs while autograd's backward is
+    executing) finds them and launches only this rank's kernels.  One handle per layer and micro-step, created
+    outside the checkpointed region; every rank passes a handle for the same call or none (reference: the
+    ``recompute_handle`` option of the reference's KCP packages)."""
+
+    def __init__(self) -> None:
+        self.entries: dict[str, Any] = {}
+
+    def drop(self) -> None:
+        self.entries.clear()
+
+
+_OPTION_NAMES = ("save_mode", "recompute_handle", "checkpoint_keep", "exchange")
+
+
+@dataclass(frozen=True)
+class _Options:
+    save_mode: str = "full"
+    recompute_handle: RecomputeHandle | None = None
+    exchange: str | None = None
+
+
+def _options(options: dict[str, Any]) -> _Options:
+    unknown = sorted(set(options) - set(_OPTION_NAMES))
+    if unknown:
+        raise NotImplementedError(f"the KCP entry points take the options {_OPTION_NAMES} here, not {unknown}")
+    save_mode = options.get("save_mode") or "full"
+    if save_mode not in ("full", "light"):
+        raise ValueError(f"save_mode must be 'full' or 'light', not {save_mode!r}")
+    keep = options.get("checkpoint_keep") or "states"
+    if keep != "states":
+        raise NotImplementedError(f"checkpoint_keep={keep!r}: a handle keeps the incoming states only ('states')")
+    handle = options.get("recompute_handle")
+    if handle is not None and not isinstance(handle, RecomputeHandle):
+        raise TypeError(f"recompute_handle must be a RecomputeHandle, not {type(handle).__name__}")
+    exchange = options.get("exchange")
+    if exchange is not None and exchange not in ("auto", "sequential", "parallel"):
+        raise ValueError(f"exchange must be 'auto', 'sequential' or 'parallel', not {exchange!r}")
+    return _Options(save_mode, handle, exchange)
+
+
+def _replaying() -> bool:
+    """Whether autograd's backward is executing: a forward that runs now is a checkpointed region's replay."""
+    current = getattr(torch._C, "_current_graph_task_id", None)
+    if current is None:
+        raise NotImplementedError("this torch cannot tell a checkpoint's replay from a forward: no recompute handles")
+    return current() != -1
 
 
 def _context(ctx: Any) -> KcpContext:
@@ -120,14 +177,41 @@ def _shard(q, k, v, g, beta, ctx: KcpContext):
     return q3, k3, v3, g3, beta3.float().contiguous()
 
 
-def _exchange_of(ctx: KcpContext):
-    """The state exchange of a call: the GDN op's ``--cake-gdn-kcp-exchange`` (``auto``: sequential on two ranks of
-    the contiguous layout, else the parallel exchange of fragment summaries, which serves every layout)."""
-    return ctx.exchange(str(config.option("gdn", "cake_gdn_kcp_exchange") or "auto"))
+def _exchange_of(ctx: KcpContext, mode: str | None = None):
+    """The state exchange of a call: ``mode``, else the GDN op's ``--cake-gdn-kcp-exchange`` (``auto``: sequential on
+    two ranks of the contiguous layout, else the parallel exchange of fragment summaries, which serves every
+    layout)."""
+    return ctx.exchange(mode or str(config.option("gdn", "cake_gdn_kcp_exchange") or "auto"))
 
 
-def _forward_kcp(q3, k3, v3, g3, beta32, ctx: KcpContext, scale: float, l2norm: bool):
-    exchange = _exchange_of(ctx)
+def _forward_local(q3, k3, v3, g3, beta32, ctx: KcpContext, scale: float, l2norm: bool, h0):
+    """This rank's kernels from known incoming states (no exchange): the replay of a forward."""
+    with torch.cuda.device(q3.device):
+        o, saved, _ = ops._forward(q3, k3, v3, g3, beta32, ctx.cu_seqlens, scale, l2norm,
+                                   cu_seqlens_cpu=ctx.cu_seqlens_cpu, h0=h0)
+    return o, saved
+
+
+def _forward_kcp(q3, k3, v3, g3, beta32, ctx: KcpContext, scale: float, l2norm: bool, options: _Options = _Options()):
+    handle = options.recompute_handle
+    if handle is not None:
+        entry = handle.entries.get("kda")
+        if _replaying():
+            if entry is not None:  # the region's replay: what the original forward received, no collective
+                owner, shape, h0 = entry
+                if owner is not ctx or shape != tuple(q3.shape):
+                    raise RuntimeError("the recompute handle was filled by another context or call")
+                return _forward_local(q3, k3, v3, g3, beta32, ctx, scale, l2norm, h0)
+        elif entry is not None:
+            raise RuntimeError("the recompute handle already holds a forward: one handle per layer and micro-step")
+    o, saved = _forward_exchanging(q3, k3, v3, g3, beta32, ctx, scale, l2norm, options.exchange)
+    if handle is not None and not _replaying():
+        handle.entries["kda"] = (ctx, tuple(q3.shape), saved.h0)
+    return o, saved
+
+
+def _forward_exchanging(q3, k3, v3, g3, beta32, ctx: KcpContext, scale: float, l2norm: bool, mode: str | None):
+    exchange = _exchange_of(ctx, mode)
     num_seqs, heads = len(ctx.cu_seqlens_cpu) - 1, q3.shape[1]
     if hasattr(exchange, "kda_forward_state"):  # every rank works at once
         with torch.cuda.device(q3.device):
@@ -144,8 +228,8 @@ def _forward_kcp(q3, k3, v3, g3, beta32, ctx: KcpContext, scale: float, l2norm: 
     return o, saved
 
 
-def _backward_kcp(saved, v3, beta32, do3, ctx: KcpContext):
-    exchange = _exchange_of(ctx)
+def _backward_kcp(saved, v3, beta32, do3, ctx: KcpContext, mode: str | None = None):
+    exchange = _exchange_of(ctx, mode)
     num_seqs, heads = len(ctx.cu_seqlens_cpu) - 1, v3.shape[1]
     if hasattr(exchange, "kda_backward_state"):
         with torch.cuda.device(v3.device):
@@ -161,13 +245,25 @@ def _backward_kcp(saved, v3, beta32, do3, ctx: KcpContext):
     return dq, dk, dv, dg, dbeta
 
 
+@dataclass
+class _LightTape:
+    """What ``save_mode="light"`` keeps: the operands as the kernels read them; the incoming states ride along."""
+
+    q: torch.Tensor
+    k: torch.Tensor
+    g: torch.Tensor
+
+
 class _ChunkKdaKcp(torch.autograd.Function):
     @staticmethod
-    def forward(fn, q, k, v, g, beta, ctx, scale, l2norm):
+    def forward(fn, q, k, v, g, beta, ctx, scale, l2norm, options):
         q3, k3, v3, g3, beta32 = _shard(q, k, v, g, beta, ctx)
-        o, saved = _forward_kcp(q3, k3, v3, g3, beta32, ctx, scale, l2norm)
-        tape_module.keep(fn, saved, v=v3, beta32=beta32)
-        fn.kcp = ctx
+        o, saved = _forward_kcp(q3, k3, v3, g3, beta32, ctx, scale, l2norm, options)
+        if options.save_mode == "light":
+            tape_module.keep(fn, _LightTape(q3, k3, g3), v=v3, beta32=beta32, h0=saved.h0)
+        else:
+            tape_module.keep(fn, saved, v=v3, beta32=beta32)
+        fn.kcp, fn.call = ctx, (scale, l2norm, options)
         fn.shapes = (q.shape, g.shape, beta.shape)
         fn.dtypes = (g.dtype, beta.dtype)
         return o.view(q.shape)
@@ -175,33 +271,38 @@ class _ChunkKdaKcp(torch.autograd.Function):
     @staticmethod
     def backward(fn, do):
         shape, g_shape, beta_shape = fn.shapes
+        scale, l2norm, options = fn.call
         do3 = ops._packed3(do, "dout").contiguous().to(torch.bfloat16)
         saved, kept = tape_module.restore(fn)
-        dq, dk, dv, dg, dbeta = _backward_kcp(saved, kept["v"], kept["beta32"], do3, fn.kcp)
+        if isinstance(saved, _LightTape):  # replay this rank's kernels from the states the forward received
+            _, saved = _forward_local(saved.q, saved.k, kept["v"], saved.g, kept["beta32"], fn.kcp, scale, l2norm,
+                                      kept["h0"])
+        dq, dk, dv, dg, dbeta = _backward_kcp(saved, kept["v"], kept["beta32"], do3, fn.kcp, options.exchange)
         g_dtype, beta_dtype = fn.dtypes
         return (dq.view(shape), dk.view(shape), dv.view(shape), dg.view(g_shape).to(g_dtype),
-                dbeta.view(beta_shape).to(beta_dtype), None, None, None)
+                dbeta.view(beta_shape).to(beta_dtype), None, None, None, None)
 
 
 def chunk_kda_kcp(q, k, v, g, beta, ctx, *, scale=None, use_gate_in_kernel=False, A_log=None, dt_bias=None,
                   lower_bound=None, use_qk_l2norm_in_kernel=False, **options):
     """The context-parallel autograd node of this rank's slice: ``out`` BF16 like ``v`` (this rank's tokens), with
     gradients to ``q, k, v, g, beta`` and, in the raw gate mode, to ``A_log`` / ``dt_bias`` (this rank's partial sums).
-    Every rank of the group calls it in the same order (reference: kcp.py:126-155)."""
-    _no_options(options)
+    Every rank of the group calls it in the same order.  ``options``: ``save_mode``, ``recompute_handle``,
+    ``checkpoint_keep``, ``exchange`` (see the module's notes; reference: kcp.py:126-155)."""
+    chosen = _options(options)
     ctx = _context(ctx)
     ops.check_heads(int(v.shape[-2]))
     config.variant(ops.OP)
     v, beta = ops.seam(v, beta)
     gate = ops._gate(g, use_gate_in_kernel, A_log, dt_bias, lower_bound)
     return _ChunkKdaKcp.apply(q, k, v, gate, beta, ctx, ops.DEFAULT_SCALE if scale is None else float(scale),
-                              bool(use_qk_l2norm_in_kernel))
+                              bool(use_qk_l2norm_in_kernel), chosen)
 
 
 def chunk_kda_fwd_kcp(q, k, v, g, beta, ctx, *, scale=None, save_for_backward=True, use_gate_in_kernel=False,
                       A_log=None, dt_bias=None, lower_bound=None, use_qk_l2norm_in_kernel=False, **options):
     """The context-parallel forward alone: ``(out, saved)`` (reference: kcp.py:158-184)."""
-    _no_options(options)
+    chosen = _options(options)
     ctx = _context(ctx)
     ops.check_heads(int(v.shape[-2]))
     v, beta = ops.seam(v, beta)
@@ -209,7 +310,7 @@ def chunk_kda_fwd_kcp(q, k, v, g, beta, ctx, *, scale=None, save_for_backward=Tr
         gate = ops._gate(g, use_gate_in_kernel, A_log, dt_bias, lower_bound)
         q3, k3, v3, g3, beta32 = _shard(q, k, v, gate, beta, ctx)
         o, saved = _forward_kcp(q3, k3, v3, g3, beta32, ctx, ops.DEFAULT_SCALE if scale is None else float(scale),
-                                bool(use_qk_l2norm_in_kernel))
+                                bool(use_qk_l2norm_in_kernel), chosen)
     return o.view(q.shape), (saved if save_for_backward else None)
 
 
@@ -218,7 +319,7 @@ def chunk_kda_bwd_kcp(q, k, v, g, beta, ctx, dout, *, saved=None, scale=None, us
     """The context-parallel backward alone: ``(dq, dk, dv, dbeta, dg)`` and, in the raw gate mode,
     ``(..., dA_log, ddt_bias)`` (this rank's partial sums); ``saved=None`` replays the forward, its exchange
     included (reference: kcp.py:187-220)."""
-    _no_options(options)
+    chosen = _options(options)
     ctx = _context(ctx)
     ops.check_heads(int(v.shape[-2]))
     beta_dtype = beta.dtype
@@ -226,12 +327,12 @@ def chunk_kda_bwd_kcp(q, k, v, g, beta, ctx, dout, *, saved=None, scale=None, us
     if saved is None:
         _, saved = chunk_kda_fwd_kcp(q, k, v, g, beta, ctx, scale=scale, use_gate_in_kernel=use_gate_in_kernel,
                                      A_log=A_log, dt_bias=dt_bias, lower_bound=lower_bound,
-                                     use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel)
+                                     use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel, **options)
     v3 = ops._packed3(v, "v").contiguous()
     beta32 = ops._packed_beta(beta).float().contiguous()
     do3 = ops._packed3(dout, "dout").contiguous().to(torch.bfloat16)
     with torch.no_grad():
-        dq, dk, dv, dg, dbeta = _backward_kcp(saved, v3, beta32, do3, ctx)
+        dq, dk, dv, dg, dbeta = _backward_kcp(saved, v3, beta32, do3, ctx, chosen.exchange)
     grads = [dq.view(q.shape), dk.view(q.shape), dv.view(v.shape), dbeta.view(beta.shape).to(beta_dtype),
              dg.view(g.shape)]
     if use_gate_in_kernel:

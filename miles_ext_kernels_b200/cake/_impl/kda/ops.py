@@ -128,6 +128,7 @@ class Saved:
     h: torch.Tensor
     v_new: torch.Tensor
     status: torch.Tensor
+    h0: torch.Tensor | None = None  # the states that entered this rank's fragments (context parallelism), else None
 
 
 def _scan_segments() -> int:
@@ -222,7 +223,7 @@ def _forward(q, k, v, g, beta32, cu_seqlens, scale, use_qk_l2norm, *, cu_seqlens
     final = _scan_forward(dims, meta, kr, w, u, gl2, h0, h, v_new, want_final, status)
     o = torch.empty_like(v)
     native.launch("kda_fwd_o", dims, qg, aqk, v_new, h, o, status, device=device)
-    saved = Saved(meta, scale, q, k, q_raw, k_raw, rstd_q, rstd_k, g2, gl2, qg, kg, kr, a, aqk, w, h, v_new, status)
+    saved = Saved(meta, scale, q, k, q_raw, k_raw, rstd_q, rstd_k, g2, gl2, qg, kg, kr, a, aqk, w, h, v_new, status, h0)
     return o, saved, final
 
 

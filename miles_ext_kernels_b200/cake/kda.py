@@ -44,6 +44,7 @@ OP = OpSpec(
     exports=(
         "DEFAULT_SCALE",
         "MAX_HEADS",
+        "RecomputeHandle",
         "build_context_kcp",
         "chunk_kda",
         "chunk_kda_bwd",

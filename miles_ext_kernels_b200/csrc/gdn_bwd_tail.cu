@@ -205,8 +205,13 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
   };
 
   int pair = blockIdx.x;
-  if (pair_live(pair)) {  // prologue: everything of the first item
+  // The chunk-table reads of an item (global memory, two dependent loads) are issued one item ahead and carried in
+  // registers: `ahead` is the item the walk takes next, `pair_ahead_live` whether the next pair exists.
+  Item ahead = {0, 0, 0, 0, 0};
+  bool this_pair_live = pair_live(pair);
+  if (this_pair_live) {  // prologue: everything of the first item
     const Item it = item_of(pair, 0);
+    ahead = it;
     if (loader) {
       load_qk(pair, 0);
       load_aqk(it);
@@ -283,24 +288,28 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
   float dq_reg[kTailW], dk_reg[kTailW];
   int item_parity = 0, qk_buf = 0, pairs_done = 0;
   bool aborted = false;
-  for (; pair_live(pair) && !aborted; pair += gridDim.x, qk_buf ^= 1, ++pairs_done) {
+  bool next_pair_live = pair_live(pair + int(gridDim.x)), pair_after_live = false;
+  for (; this_pair_live && !aborted; pair += gridDim.x, qk_buf ^= 1, ++pairs_done, this_pair_live = next_pair_live,
+                                      next_pair_live = pair_after_live) {
     const int hq = pair % num_qk_heads;
     const uint32_t qk_base = sbase + TailSmem::kQK + qk_buf * TailSmem::kQKStride;
     uint8_t* q_tile = sm + TailSmem::kQK + qk_buf * TailSmem::kQKStride;
     uint8_t* k_tile = q_tile + 16384;
     const Operand op_q{qk_base, 8192}, op_k{qk_base + 16384, 8192};
     const int next_pair = pair + gridDim.x;
-    const bool has_next_pair = pair_live(next_pair);
+    const bool has_next_pair = next_pair_live;
+    pair_after_live = pair_live(next_pair + int(gridDim.x));  // read now, needed when this pair is done
 #pragma unroll
     for (int j = 0; j < kTailW; ++j) dq_reg[j] = dk_reg[j] = 0.f;
 
     for (int gi = 0; gi < group; ++gi, item_parity ^= 1) {
-      const Item it = item_of(pair, gi);
+      const Item it = ahead;
       const int start = it.start, len = it.len, hv = it.hv;
       const bool live = row < len;
       const bool last_of_pair = gi + 1 == group;
       const bool has_next = !last_of_pair || has_next_pair;
       const Item nx = has_next ? (last_of_pair ? item_of(next_pair, 0) : item_of(pair, gi + 1)) : it;
+      ahead = nx;
       const float* beta_s = s_beta + item_parity * 64;
       const float* g2 = s_g2 + item_parity * 64;
 

@@ -66,8 +66,16 @@ def test_partition_and_context_on_the_host():
     x = torch.zeros(1)
     with pytest.raises(TypeError, match="build_context_kcp"):
         kda.chunk_kda_kcp(x, x, torch.zeros(64, 2, 128), x, x, "not a context")
-    with pytest.raises(NotImplementedError, match="save_mode"):
-        kda.chunk_kda_kcp(x, x, torch.zeros(64, 2, 128), x, x, one, save_mode="full")
+    with pytest.raises(NotImplementedError, match="boundary_mode"):
+        kda.chunk_kda_kcp(x, x, torch.zeros(64, 2, 128), x, x, one, boundary_mode="replay")
+    with pytest.raises(ValueError, match="save_mode"):
+        kda.chunk_kda_kcp(x, x, torch.zeros(64, 2, 128), x, x, one, save_mode="medium")
+    with pytest.raises(NotImplementedError, match="checkpoint_keep"):
+        kda.chunk_kda_kcp(x, x, torch.zeros(64, 2, 128), x, x, one, checkpoint_keep="transfer")
+    with pytest.raises(TypeError, match="RecomputeHandle"):
+        kda.chunk_kda_kcp(x, x, torch.zeros(64, 2, 128), x, x, one, recompute_handle=object())
+    with pytest.raises(ValueError, match="exchange"):
+        kda.chunk_kda_kcp(x, x, torch.zeros(64, 2, 128), x, x, one, exchange="ring")
 
 
 def _reduce_main(rank: int, world: int, port: int, out_dir: str) -> None:
