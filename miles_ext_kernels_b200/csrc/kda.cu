@@ -8,15 +8,19 @@
 // so the state scan, the output and the adjoint scan are the GDN kernels run on (kr, qg) with a per-channel chunk
 // decay (mek_kda_fwd_h / mek_kda_fwd_o / mek_kda_bwd_dh).  What is new here:
 //   kda_prep        G, qg, kg, kr and the chunk-end gate                                  [CUDA cores, coalesced]
-//   kda_intra       Aqk_ij = scale sum_d q_id k_jd 2^{G_id - G_jd}, L_ij = beta_i sum_d k_id k_jd 2^{G_id - G_jd}
-//                   pair by pair (each exponent is formed from a non-positive difference: finite for any gate),
-//                   then A = (I + L)^-1, w = A (beta kg), u = A (beta v)                    [CUDA cores + tcgen05]
+//   kda_intra       Aqk_ij = scale sum_d q_id k_jd 2^{G_id - G_jd}, L_ij = beta_i sum_d k_id k_jd 2^{G_id - G_jd}:
+//                   blocks of 16 rows; below the block diagonal one tensor-core product of operands scaled against
+//                   the gate at the block's first row, on it pair by pair (every exponent is formed from a
+//                   non-positive difference: finite for any gate); then A = (I + L)^-1, w = A (beta kg),
+//                   u = A (beta v)                                                          [tcgen05 + CUDA cores]
 //   kda_tail_mma    the state-side gradient contractions of one (chunk, head)               [tcgen05]
-//   kda_tail_pair   the pairwise decayed gradient contractions, dq, dk and the per-channel gate gradient with its
-//                   in-chunk suffix sum                                                     [CUDA cores]
+//   kda_tail_pair   the decayed gradient contractions (the same split: tensor core below the block diagonal,
+//                   running products on it), dq, dk and the per-channel gate gradient with its in-chunk suffix
+//                   sum                                                                     [tcgen05 + CUDA cores]
 //   qk_grad_finish  fp32 dq / dk -> the L2 norm's pull-back (optional) -> bf16
 #include "common.cuh"
 #include "tiles.cuh"
+#include "tma.cuh"
 
 namespace mek {
 
@@ -53,40 +57,61 @@ __global__ void __launch_bounds__(128) kda_prep_kernel(
 // ---------------------------------------------------------------------------------------------------------------
 // intra: Aqk, A, w, u of one (chunk, head)
 // ---------------------------------------------------------------------------------------------------------------
+// The two pairwise matrices  S_qk[i][j] = sum_d q_id k_jd 2^{G_id - G_jd}  and  S_kk (k in place of q), j <= i, are
+// split by blocks of 16 rows.  With R the first row of i's block and j in an EARLIER block,
+//     2^{G_i - G_j} = 2^{G_i - G_R} 2^{G_R - G_j}          (both exponents <= 0 per channel: G falls along the chunk)
+// so the blocks below the block diagonal are ONE tensor-core product of bounded bf16 operands,
+//     [q~ ; k~'] [128 x 128]  x  stack^T [128 x 96],   q~_i = q_i 2^{G_i - G_R},  k~'_i = k_i 2^{G_i - G_R},
+//     stack = [k_j 2^{G_16 - G_j}, j < 16 ; k_j 2^{G_32 - G_j}, j < 32 ; k_j 2^{G_48 - G_j}, j < 48]
+// (row block I of the result reads its own 16 I columns of the stack); only the four 16 x 16 blocks on the diagonal
+// are summed pair by pair on CUDA cores, every exponent formed from a non-positive difference.  Finite for any gate:
+// a factor that underflows belongs to a pair whose true weight underflows too.
 struct KdaIntraSmem {
-  static constexpr int kRow = 129;                                  // fp32 row stride of the q / k / G copies
-  static constexpr uint32_t kQ = 0;                                 // fp32 [64][129]; later the bf16 tiles below
-  static constexpr uint32_t kK = kQ + 64 * kRow * 4;
-  static constexpr uint32_t kG = kK + 64 * kRow * 4;
-  // after the pair phase (the copies above are dead; about 100 KB in all, so that two CTAs share an SM):
-  static constexpr uint32_t kA = 0;                                 // [64][64] bf16
-  static constexpr uint32_t kKB = 8192;                             // [64][128] beta kg
-  static constexpr uint32_t kVB = kKB + 16384;                      // [64][128] beta v
-  static constexpr uint32_t kSqk = kVB + 16384;                     // fp32 [64][65]
-  static constexpr uint32_t kSkk = kSqk + 64 * 65 * 4;
-  static constexpr uint32_t kL = kSkk + 64 * 65 * 4;                // fp32 [64][68]
-  static constexpr uint32_t kBeta = ((kG + 64 * kRow * 4 + 255) / 256) * 256;  // beta[64]
+  static constexpr int kGRow = 132;                                 // fp32 row stride of the G copy
+  static constexpr uint32_t kQK = 0;          // [128][128] bf16: rows 0..63 q -> q~, 64..127 k -> k~'; 2 blocks of 16 KiB
+  static constexpr uint32_t kStack = 32768;   // [96][128] bf16: 2 blocks of 12 KiB
+  static constexpr uint32_t kG = kStack + 24576;                    // fp32 [64][132]
+  static constexpr uint32_t kVB = kG + 64 * kGRow * 4;              // [64][128] beta v
+  static constexpr uint32_t kBeta = kVB + 16384;                    // beta[64]
   static constexpr uint32_t kBytes = kBeta + 256;
-  static_assert(kL + 64 * 68 * 4 <= kBeta, "the results of the pair phase fit the dead copies");
+  // after the block product (the operands above are dead):
+  static constexpr uint32_t kA = kQK;                               // [64][64] bf16
+  static constexpr uint32_t kKB = kQK + 8192;                       // [64][128] beta kg
+  static constexpr uint32_t kL = kStack;                            // fp32 [64][68]
+  static constexpr uint32_t kSqk = kG;                              // fp32 [64][65]
+  static constexpr uint32_t kSkk = kSqk + 64 * 65 * 4;
+  static_assert(kKB + 16384 <= kStack && 64 * 68 * 4 <= 24576 && 2 * 64 * 65 * 4 <= 64 * kGRow * 4, "overlays fit");
 };
 
-__global__ void __launch_bounds__(288, 2) kda_intra_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+// element (row, d) of a bf16 tile made of 64-column swizzled blocks `block_stride` bytes apart
+__device__ __forceinline__ float tile_elem(const uint8_t* tile, uint32_t block_stride, int row, int d) {
+  const uint8_t* at = tile + (d >> 6) * block_stride + sw128_offset(row, (d & 63) >> 3) + (d & 7) * 2;
+  return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(at));
+}
+
+struct KdaIntraMaps {
+  CUtensorMap q, k;  // rows [tokens, H * 128], box 64 x 64
+};
+
+constexpr int kIntraThreads = 320;  // 40 sub-blocks of the block diagonal x 8 channel slices
+
+__global__ void __launch_bounds__(kIntraThreads, 2) kda_intra_kernel(
+    const __grid_constant__ KdaIntraMaps maps, const __nv_bfloat16* __restrict__ v,
     const __nv_bfloat16* __restrict__ kg, const float* __restrict__ g2, const float* __restrict__ beta,
     __nv_bfloat16* __restrict__ a_out, __nv_bfloat16* __restrict__ aqk_out, __nv_bfloat16* __restrict__ w_out,
     __nv_bfloat16* __restrict__ u_out, const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len,
     int num_heads, float scale, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, bar_load;
   __shared__ uint32_t tmem_slot;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, h = blockIdx.y;
   const int start = chunk_start[c], len = chunk_len[c];
   if (len <= 0) return;
-  constexpr int kRow = KdaIntraSmem::kRow;
-  float* sq = reinterpret_cast<float*>(sm + KdaIntraSmem::kQ);
-  float* sk = reinterpret_cast<float*>(sm + KdaIntraSmem::kK);
+  constexpr int kGRow = KdaIntraSmem::kGRow;
+  uint8_t* qk_tile = sm + KdaIntraSmem::kQK;      // rows 0..63 q, rows 64..127 k
+  uint8_t* stack = sm + KdaIntraSmem::kStack;
   float* sg = reinterpret_cast<float*>(sm + KdaIntraSmem::kG);
   float* s_qk = reinterpret_cast<float*>(sm + KdaIntraSmem::kSqk);
   float* s_kk = reinterpret_cast<float*>(sm + KdaIntraSmem::kSkk);
@@ -94,109 +119,204 @@ __global__ void __launch_bounds__(288, 2) kda_intra_kernel(
   float* s_beta = reinterpret_cast<float*>(sm + KdaIntraSmem::kBeta);
   const int64_t stride = int64_t(num_heads) * kDim;
   const int64_t tile = int64_t(c) * num_heads + h;
+  const uint32_t sbase = smem_u32(sm);
 
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar_load, 1);
     fence_mbar_init();
+    // q and k rows by TMA into the stacked operand: block b of q at b * 16 KiB, of k 8 KiB behind it
+    mbar_arrive_expect(&bar_load, 2 * 16384);
+    tma_load_box(sbase + KdaIntraSmem::kQK, &maps.q, h * kDim, start, &bar_load);
+    tma_load_box(sbase + KdaIntraSmem::kQK + 16384, &maps.q, h * kDim + 64, start, &bar_load);
+    tma_load_box(sbase + KdaIntraSmem::kQK + 8192, &maps.k, h * kDim, start, &bar_load);
+    tma_load_box(sbase + KdaIntraSmem::kQK + 24576, &maps.k, h * kDim + 64, start, &bar_load);
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 256);
-  for (int i = tid; i < 64 * 16; i += 288) {  // 8 channels of one row per step, 16-byte loads
-    const int r = i >> 4, d = (i & 15) * 8;
-    const bool live = r < len;
-    const int64_t at = int64_t(start + (live ? r : len - 1)) * stride + h * kDim + d;
-    float qv[8], kv[8];
-    unpack8(live ? ldg16(q + at) : make_uint4(0u, 0u, 0u, 0u), qv);
-    unpack8(live ? ldg16(k + at) : make_uint4(0u, 0u, 0u, 0u), kv);
-    // rows past the chunk's length keep the last gate: every pair exponent stays <= 0
-    const float4 g_lo = __ldg(reinterpret_cast<const float4*>(g2 + at));
-    const float4 g_hi = __ldg(reinterpret_cast<const float4*>(g2 + at + 4));
-    const float gv[8] = {g_lo.x, g_lo.y, g_lo.z, g_lo.w, g_hi.x, g_hi.y, g_hi.z, g_hi.w};
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      sq[r * kRow + d + j] = qv[j];
-      sk[r * kRow + d + j] = kv[j];
-      sg[r * kRow + d + j] = gv[j];
-    }
+  for (int i = tid; i < 64 * 32; i += kIntraThreads) {  // the gates: rows past the chunk's length keep the last gate
+    const int r = i >> 5, d = (i & 31) * 4;              // (every pair exponent stays <= 0)
+    const int64_t at = int64_t(start + (r < len ? r : len - 1)) * stride + h * kDim + d;
+    *reinterpret_cast<float4*>(sg + r * kGRow + d) = __ldg(reinterpret_cast<const float4*>(g2 + at));
   }
   if (tid < 64) s_beta[tid] = tid < len ? beta[int64_t(start + tid) * num_heads + h] : 0.f;
+  __syncthreads();  // the barrier's initialisation is visible to every waiter
+  bool ok = __all_sync(0xffffffffu, mbar_wait(&bar_load, 0));
+  if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows of q and k
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = tid; i < (64 - len) * 32; i += kIntraThreads) {
+      const int r = len + (i >> 5), part = i & 31;  // 8 chunks of q and of k in each of the two blocks
+      const int blk = part >> 4, which = (part >> 3) & 1, cc = part & 7;
+      *reinterpret_cast<uint4*>(qk_tile + blk * 16384 + which * 8192 + r * 128 + cc * 16) = zero;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
 
-  // pair phase: a thread owns a 4 x 4 block (bi, bj), bj <= bi, of the lower triangle and one half of the channels:
-  // threads 0..239 the 120 blocks below the diagonal, threads 256..287 (one warp) the 16 diagonal blocks.
-  // Below the diagonal every pair of a block is valid and 2^{G_i - G_j} factors as 2^{G_i - G_{j0+3}} 2^{G_{j0+3} - G_j}
-  // with both exponents <= 0: 7 exponentials per channel instead of 16.
+  // ---- the four 16 x 16 diagonal blocks, pair by pair: thread (4 x 4 sub-block, eighth of the channels) ----------
+  // sub-blocks (bi, bj), bj <= bi, of a 16-block: 10 of them, 40 in all, times 8 channel slices = every thread.  A
+  // thread takes four runs of 4 channels (8-byte loads of the swizzled rows).  Off the sub-diagonal every pair is
+  // valid and 2^{G_i - G_j} factors as 2^{G_i - G_{j0+3}} 2^{G_{j0+3} - G_j} with both exponents <= 0.
   float aqk[4][4], akk[4][4];
-  int i0 = 0, j0 = 0;
 #pragma unroll
   for (int a = 0; a < 4; ++a)
 #pragma unroll
     for (int b = 0; b < 4; ++b) aqk[a][b] = akk[a][b] = 0.f;
-  if (tid < 240) {
-    const int t = tid >> 1, half = tid & 1;
-    int bi = int((sqrtf(8.f * t + 1.f) + 1.f) * 0.5f);
-    while (bi * (bi + 1) / 2 <= t) ++bi;
-    while (bi * (bi - 1) / 2 > t) --bi;
-    const int bj = t - bi * (bi - 1) / 2;
-    i0 = 4 * bi, j0 = 4 * bj;
-    for (int d = half * 64; d < half * 64 + 64; ++d) {
-      float qe[4], ke[4], kj[4], gj[4];
-#pragma unroll
-      for (int a = 0; a < 4; ++a) {
-        kj[a] = sk[(j0 + a) * kRow + d];
-        gj[a] = sg[(j0 + a) * kRow + d];
-      }
-#pragma unroll
-      for (int a = 0; a < 4; ++a) {
-        const float ea = fast_exp2(sg[(i0 + a) * kRow + d] - gj[3]);
-        qe[a] = sq[(i0 + a) * kRow + d] * ea;
-        ke[a] = sk[(i0 + a) * kRow + d] * ea;
-      }
-#pragma unroll
-      for (int b = 0; b < 3; ++b) kj[b] *= fast_exp2(gj[3] - gj[b]);
-#pragma unroll
-      for (int a = 0; a < 4; ++a)
+  int i0 = 0, j0 = 0;
+  {
+    const int s = tid >> 3, slice = tid & 7;
+    const int big = s / 10, t = s % 10;
+    const int bi = t == 0 ? 0 : (t < 3 ? 1 : (t < 6 ? 2 : 3));
+    const int bj = t - bi * (bi + 1) / 2;
+    i0 = 16 * big + 4 * bi, j0 = 16 * big + 4 * bj;
+    // 4 channels d .. d + 3 of tile row `row`: half of a 16-byte chunk
+    auto four = [&](int row, int d, float* out) {
+      const uint2 w = *reinterpret_cast<const uint2*>(qk_tile + (d >> 6) * 16384 + sw128_offset(row, (d & 63) >> 3) +
+                                                      (d & 4) * 2);
+      const float2 lo = unpack_bf16(w.x), hi = unpack_bf16(w.y);
+      out[0] = lo.x, out[1] = lo.y, out[2] = hi.x, out[3] = hi.y;
+    };
+    auto gates = [&](int row, int d, float* out) {
+      const float4 x = *reinterpret_cast<const float4*>(sg + row * kGRow + d);
+      out[0] = x.x, out[1] = x.y, out[2] = x.z, out[3] = x.w;
+    };
+#pragma unroll 1
+    for (int n = 0; n < 4; ++n) {
+      const int d = (n * 8 + slice) * 4;
+      if (bi != bj) {
+        float kj[4][4], g3[4];
+        gates(j0 + 3, d, g3);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          aqk[a][b] = fmaf(qe[a], kj[b], aqk[a][b]);
-          akk[a][b] = fmaf(ke[a], kj[b], akk[a][b]);
-        }
-    }
-  } else if (tid >= 256) {
-    const int bi = (tid - 256) >> 1, half = tid & 1;
-    i0 = j0 = 4 * bi;
-    for (int d = half * 64; d < half * 64 + 64; ++d) {
-      float qi[4], ki[4], gi[4];
+          float gj[4];
+          four(64 + j0 + b, d, kj[b]);
+          if (b < 3) {
+            gates(j0 + b, d, gj);
 #pragma unroll
-      for (int a = 0; a < 4; ++a) {
-        qi[a] = sq[(i0 + a) * kRow + d];
-        ki[a] = sk[(i0 + a) * kRow + d];
-        gi[a] = sg[(i0 + a) * kRow + d];
+            for (int e = 0; e < 4; ++e) kj[b][e] *= fast_exp2(g3[e] - gj[e]);
+          }
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          float qa[4], ka[4], ga[4];
+          four(i0 + a, d, qa);
+          four(64 + i0 + a, d, ka);
+          gates(i0 + a, d, ga);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float ea = fast_exp2(ga[e] - g3[e]);
+            qa[e] *= ea, ka[e] *= ea;
+          }
+#pragma unroll
+          for (int b = 0; b < 4; ++b)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              aqk[a][b] = fmaf(qa[e], kj[b][e], aqk[a][b]);
+              akk[a][b] = fmaf(ka[e], kj[b][e], akk[a][b]);
+            }
+        }
+      } else {
+        float qi[4][4], ki[4][4], gi[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          four(i0 + a, d, qi[a]);
+          four(64 + i0 + a, d, ki[a]);
+          gates(i0 + a, d, gi[a]);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int b = 0; b <= a; ++b)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {  // the exponent of a valid pair is <= 0
+              const float w = fast_exp2(gi[a][e] - gi[b][e]) * ki[b][e];
+              aqk[a][b] = fmaf(qi[a][e], w, aqk[a][b]);
+              akk[a][b] = fmaf(ki[a][e], w, akk[a][b]);
+            }
       }
-#pragma unroll
-      for (int a = 0; a < 4; ++a)
-#pragma unroll
-        for (int b = 0; b <= a; ++b) {  // the exponent of a valid pair is <= 0
-          const float e = fast_exp2(gi[a] - gi[b]) * ki[b];
-          aqk[a][b] = fmaf(qi[a], e, aqk[a][b]);
-          akk[a][b] = fmaf(ki[a], e, akk[a][b]);
-        }
     }
   }
-  // the two channel halves of a block sit in neighbouring lanes: half 0 + half 1, then one of them writes -- after a
-  // block barrier, because the results take the place of the q / k / G copies
+  // the eight channel slices of a sub-block sit in neighbouring lanes: a fixed-order butterfly sum
 #pragma unroll
   for (int a = 0; a < 4; ++a)
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-      const float oq = __shfl_xor_sync(0xffffffffu, aqk[a][b], 1), ok_ = __shfl_xor_sync(0xffffffffu, akk[a][b], 1);
-      aqk[a][b] = (tid & 1) ? oq + aqk[a][b] : aqk[a][b] + oq;
-      akk[a][b] = (tid & 1) ? ok_ + akk[a][b] : akk[a][b] + ok_;
+      float x = aqk[a][b], y = akk[a][b];
+#pragma unroll
+      for (int m = 1; m <= 4; m <<= 1) {
+        x += __shfl_xor_sync(0xffffffffu, x, m);
+        y += __shfl_xor_sync(0xffffffffu, y, m);
+      }
+      aqk[a][b] = x, akk[a][b] = y;
     }
+
+  // ---- the stack: row r holds k_j 2^{G_R - G_j} for (R, j) = (16, r), (32, r - 16), (48, r - 48) ------------------
+  for (int i = tid; i < 96 * 16; i += kIntraThreads) {
+    const int r = i >> 4, cc = i & 15;
+    const int ref = r < 16 ? 16 : (r < 48 ? 32 : 48);
+    const int j = r < 16 ? r : (r < 48 ? r - 16 : r - 48);
+    float x[8];
+    unpack8(*reinterpret_cast<const uint4*>(qk_tile + (cc >> 3) * 16384 + sw128_offset(64 + j, cc & 7)), x);
+    const float* gr = sg + ref * kGRow + cc * 8;
+    const float* gj = sg + j * kGRow + cc * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] *= fast_exp2(gr[e] - gj[e]);
+    *reinterpret_cast<uint4*>(stack + (cc >> 3) * 12288 + sw128_offset(r, cc & 7)) = pack8(x);
+  }
+  __syncthreads();  // the stack and the diagonal sums have read the raw rows: they become q~ and k~' in place
+  for (int i = tid; i < 64 * 16; i += kIntraThreads) {
+    const int r = i >> 4, cc = i & 15;
+    const float* gi = sg + r * kGRow + cc * 8;
+    const float* gr = sg + (r & ~15) * kGRow + cc * 8;
+    float f[8], x[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = fast_exp2(gi[e] - gr[e]);
+    uint8_t* qa = qk_tile + (cc >> 3) * 16384 + sw128_offset(r, cc & 7);
+    uint8_t* ka = qk_tile + (cc >> 3) * 16384 + sw128_offset(64 + r, cc & 7);
+    unpack8(*reinterpret_cast<const uint4*>(qa), x);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] *= f[e];
+    *reinterpret_cast<uint4*>(qa) = pack8(x);
+    unpack8(*reinterpret_cast<const uint4*>(ka), x);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] *= f[e];
+    *reinterpret_cast<uint4*>(ka) = pack8(x);
+  }
+  fence_async_smem();
+  tc_fence_before();
   __syncthreads();
-  if ((tid < 240 || tid >= 256) && (tid & 1) == 0) {
+  tc_fence_after();
+
+  // ---- the blocks below the block diagonal: [q~ ; k~'] stack^T, M = 128, N = 96, K = 128 --------------------------
+  if (tid == 0) {
+    const Operand op_a{sbase + KdaIntraSmem::kQK, 16384}, op_b{sbase + KdaIntraSmem::kStack, 12288};
+    umma_gemm<128, 96>(tmem, op_a, false, op_b, false, 128, false);
+    umma_commit(&bar);
+  }
+  ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0)) && ok;
+  tc_fence_after();
+  // every thread is past the operands: S_qk and S_kk take the gates' space, rows i of warps 0..1 / 2..3
+  if (warp < 4) {
+    const int i = (warp & 1) * 32 + lane;
+    float* dst = (warp < 2 ? s_qk : s_kk) + i * 65;
+    const int blk = i >> 4;
+    // row block 1 reads columns 0..15 of the product, block 2 columns 16..47, block 3 columns 48..95 (j = 0 .. 16 blk - 1)
+#pragma unroll
+    for (int p = 0; p < 3; ++p) {
+      float s[32];
+      tmem_ld32(tmem_addr(tmem, warp, p * 32), s);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const int col = p * 32 + e;
+        const int owner = col < 16 ? 1 : (col < 48 ? 2 : 3);
+        const int j = col < 16 ? col : (col < 48 ? col - 16 : col - 48);
+        if (blk == owner) dst[j] = s[e];
+      }
+    }
+  }
+  if ((tid & 7) == 0) {  // the diagonal blocks' sums (entries above the diagonal are zero)
 #pragma unroll
     for (int a = 0; a < 4; ++a)
 #pragma unroll
@@ -205,29 +325,26 @@ __global__ void __launch_bounds__(288, 2) kda_intra_kernel(
         s_kk[(i0 + a) * 65 + j0 + b] = akk[a][b];
       }
   }
+  tc_fence_before();
   __syncthreads();
 
-  // Aqk rows -> global; L rows -> shared
-  if (tid < 64) {
-    const int i = tid;
+  // Aqk rows -> global; L rows -> shared (a thread per run of 8 columns)
+  for (int t = tid; t < 64 * 8; t += kIntraThreads) {
+    const int i = t >> 3, jj = t & 7;
     const float bi = s_beta[i];
-    __nv_bfloat16* dst = aqk_out + tile * 4096 + i * 64;
-#pragma unroll 2
-    for (int jj = 0; jj < 8; ++jj) {
-      float x[8];
+    float x[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const int j = jj * 8 + e;
-        x[e] = j <= i ? scale * s_qk[i * 65 + j] : 0.f;
-        s_l[i * 68 + j] = j < i ? bi * s_kk[i * 65 + j] : 0.f;
-      }
-      reinterpret_cast<uint4*>(dst)[jj] = pack8(x);
+    for (int e = 0; e < 8; ++e) {
+      const int j = jj * 8 + e;
+      x[e] = j <= i ? scale * s_qk[i * 65 + j] : 0.f;
+      s_l[i * 68 + j] = j < i ? bi * s_kk[i * 65 + j] : 0.f;
     }
+    reinterpret_cast<uint4*>(aqk_out + tile * 4096 + i * 64)[jj] = pack8(x);
   }
   __syncthreads();
 
-  // kb = bf16(beta kg), vb = bf16(beta v)
-  for (int i = tid; i < 64 * 16; i += 288) {
+  // kb = bf16(beta kg), vb = bf16(beta v): by the warps that do not solve, while the first two do
+  for (int i = tid - 64; i >= 0 && i < 64 * 16; i += kIntraThreads - 64) {
     const int r = i >> 4, cc = i & 15;
     const float b = s_beta[r];
     float x[8];
@@ -267,10 +384,10 @@ __global__ void __launch_bounds__(288, 2) kda_intra_kernel(
       *reinterpret_cast<__nv_bfloat16*>(at + sw128_offset(i, tid >> 3) + (tid & 7) * 2) = __float2bfloat16_rn(x[i]);
   }
   fence_async_smem();
+  tc_fence_before();
   __syncthreads();
   tc_fence_after();
 
-  const uint32_t sbase = smem_u32(sm);
   if (tid == 0) {
     const Operand a{sbase + KdaIntraSmem::kA, 8192};
     const Operand kb{sbase + KdaIntraSmem::kKB, 8192};
@@ -280,9 +397,8 @@ __global__ void __launch_bounds__(288, 2) kda_intra_kernel(
     umma_commit(&bar);
   }
   if (tid < 128) store_tile<64, 64, 128>(sm + KdaIntraSmem::kA, 8192, a_out + tile * 4096, 64, 64, tid);
-  bool ok = true;
   if (warp < 4) {
-    ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0));
+    ok = __all_sync(0xffffffffu, mbar_wait(&bar, 1)) && ok;
     tc_fence_after();
     if (ok) {
       const int i = warp * 16 + (lane & 15);
@@ -570,224 +686,422 @@ __global__ void __launch_bounds__(256) kda_tail_mma_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// tail, pairwise part: one block per (chunk, head); thread (d, role) owns key channel d in one of two passes
+// tail, decayed part: one block per (chunk, head); thread (d, role, half) owns key channel d
 // ---------------------------------------------------------------------------------------------------------------
 // With E_ij = 2^{G_i - G_j} per channel (j <= i), M1 = scale tril(do v_new^T) and M2 = bf16(-tril(A^T dA A^T, -1)):
 //   row pass     RQ_i = sum_{j<=i} M1_ij k_j E_ij,  RK_i = sum_{j<i} M2_ij k_j E_ij     -> dq, the row part of dk, dg
 //   column pass  CC_j = sum_{i>=j} (M1_ij q_i + beta_i M2_ij k_i) E_ij                  -> the column part of dk, dg
-// No pair costs an exponential: E runs along a row or a column as a product of the per-token factors
-// R_i = 2^{G_i - G_{i-1}} <= 1 (E_{i,j-1} = E_ij R_j, E_{i+1,j} = E_ij R_{i+1}); all sums live in registers.  512
-// threads: thread (d, role, half) owns channel d in the row pass (role 0) or the column pass (role 1) for the even
-// (half 0) or odd (half 1) blocks of four rows / columns, so sixteen warps hide each other's latencies.
+// Both are split by blocks of 16 rows, like the forward's pairwise matrices.  With R the first row of i's block and
+// j in an earlier block, E_ij = 2^{G_i - G_R} 2^{G_R - G_j} (both exponents <= 0), so everything below the block
+// diagonal is tensor-core work on bounded bf16 operands (q~, k~', the stack: see kda_intra_kernel), computed
+// TRANSPOSED so that a thread finds its channel's sums in its own tensor-memory lane:
+//   DR^T [128 d x 128] = stack^T AR^T     AR row i (M1) / 64 + i (M2): the row's entries against its own block's
+//                                         part of the stack, zero elsewhere -> RQ_i = 2^{G_i - G_R} DR^T[d][i], RK alike
+//   PI^T [128 d x 64 j] = q~_I^T M1[I, :] + k~'_I^T (beta M2)[I, :]   (I = 1, 2, 3; entries of earlier blocks only)
+//                                         -> CC_j = sum_{I > block(j)} 2^{G_{16 I} - G_j} PI^T[d][j]
+// The four 16 x 16 blocks on the diagonal are summed on CUDA cores, without an exponential per pair: E runs along a
+// row or a column as a product of the per-token factors R_i = 2^{G_i - G_{i-1}} <= 1; these sums run while the
+// tensor core works.  512 threads: thread (d, role, half) owns channel d in the row pass (role 0) or the column pass
+// (role 1) for the even (half 0) or odd (half 1) groups of four rows / columns.
 struct KdaPairSmem {
-  static constexpr uint32_t kQ = 0;                  // fp32 [64][128] q
-  static constexpr uint32_t kK = 32768;              // fp32 [64][128] k
-  static constexpr uint32_t kR = 2 * 32768;          // fp32 [64][128] R
-  static constexpr uint32_t kCC = 3 * 32768;         // fp32 [64][128] column-pass sums
-  static constexpr uint32_t kM1 = 4 * 32768;         // fp32 [64][64] M1
-  static constexpr uint32_t kM2 = kM1 + 16384;       // fp32 [64][64] M2
-  static constexpr uint32_t kM1T = kM2 + 16384;      // fp32 [64][68] M1^T
-  static constexpr uint32_t kM2T = kM1T + 17408;     // fp32 [64][68] (beta_i M2_ij)^T
-  static constexpr uint32_t kBeta = kM2T + 17408;    // beta[64], db[64][4]
+  static constexpr uint32_t kG = 0;                    // fp32 [64][128] G (log2); after the passes: per-row dg
+  static constexpr uint32_t kR = 32768;                // fp32 [64][128] R; after the passes: the chunk-end terms
+  static constexpr uint32_t kRaw = 2 * 32768;          // bf16 [64][128] q, then k (raw rows, swizzled)
+  static constexpr uint32_t kCvt = 3 * 32768;          // bf16 [64][128] q~, then k~'
+  static constexpr uint32_t kStack = 4 * 32768;        // bf16 [96][128], 2 blocks of 12 KiB
+  static constexpr uint32_t kAR = kStack + 24576;      // bf16 [128][96] K-major, 2 blocks of 16 KiB; later CC fp32 [64][128]
+  static constexpr uint32_t kX1 = kAR + 32768;         // bf16 [64][64] M1, entries of earlier blocks
+  static constexpr uint32_t kX2 = kX1 + 8192;          // bf16 [64][64] beta M2, entries of earlier blocks
+  static constexpr uint32_t kMd = kX2 + 8192;          // fp32 [2][4][16][20]: the diagonal blocks of M1, M2
+  static constexpr uint32_t kBeta = kMd + 2 * 4 * 16 * 20 * 4;   // beta[64], db[64][4]
   static constexpr uint32_t kBytes = kBeta + 256 + 1024;
 };
 
+struct KdaPairMaps {
+  CUtensorMap q, k;  // rows [tokens, H * 128], box 64 x 64
+};
+
 __global__ void __launch_bounds__(512) kda_tail_pair_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const float* __restrict__ g2,
+    const __grid_constant__ KdaPairMaps maps, const float* __restrict__ g2,
     const float* __restrict__ beta, const float* __restrict__ m1, const float* __restrict__ m2,
     const float* __restrict__ dqg, const float* __restrict__ dkr, const float* __restrict__ dkg,
     const float* __restrict__ hdh, const float* __restrict__ dbeta_part, float* __restrict__ dq, float* __restrict__ dk,
     float* __restrict__ dg, float* __restrict__ dbeta, const int32_t* __restrict__ chunk_start,
-    const int32_t* __restrict__ chunk_len, int num_heads) {
+    const int32_t* __restrict__ chunk_len, int num_heads, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 127) & ~uintptr_t(127));
-  const int tid = threadIdx.x, d = tid & 127, role = (tid >> 7) & 1, half = tid >> 8, warp = (tid >> 5) & 3;
-  const int lane = tid & 31;
+  __shared__ uint64_t bar, bar_load;
+  __shared__ uint32_t tmem_slot;
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, d = tid & 127, role = (tid >> 7) & 1, half = tid >> 8, warp4 = (tid >> 5) & 3;
+  const int warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, h = blockIdx.y;
   const int start = chunk_start[c], len = chunk_len[c];
   if (len <= 0) return;
-  float* sQ = reinterpret_cast<float*>(sm + KdaPairSmem::kQ);
-  float* sK = reinterpret_cast<float*>(sm + KdaPairSmem::kK);
+  float* sG = reinterpret_cast<float*>(sm + KdaPairSmem::kG);
   float* sR = reinterpret_cast<float*>(sm + KdaPairSmem::kR);
-  float* sCC = reinterpret_cast<float*>(sm + KdaPairSmem::kCC);
-  float* sM1 = reinterpret_cast<float*>(sm + KdaPairSmem::kM1);
-  float* sM2 = reinterpret_cast<float*>(sm + KdaPairSmem::kM2);
-  float* sM1T = reinterpret_cast<float*>(sm + KdaPairSmem::kM1T);
-  float* sM2T = reinterpret_cast<float*>(sm + KdaPairSmem::kM2T);
+  uint8_t* q_raw = sm + KdaPairSmem::kRaw;
+  uint8_t* k_raw = q_raw + 16384;
+  uint8_t* q_cvt = sm + KdaPairSmem::kCvt;
+  uint8_t* k_cvt = q_cvt + 16384;
+  uint8_t* stack = sm + KdaPairSmem::kStack;
+  uint8_t* ar = sm + KdaPairSmem::kAR;
+  float* sCC = reinterpret_cast<float*>(sm + KdaPairSmem::kAR);
+  uint8_t* x1 = sm + KdaPairSmem::kX1;
+  uint8_t* x2 = sm + KdaPairSmem::kX2;
+  float* sM1d = reinterpret_cast<float*>(sm + KdaPairSmem::kMd);   // [4][16][20]
+  float* sM2d = sM1d + 4 * 16 * 20;
   float* s_beta = reinterpret_cast<float*>(sm + KdaPairSmem::kBeta);
   float* s_db = s_beta + 64;
   const int64_t stride = int64_t(num_heads) * kDim;
   const int64_t tile = int64_t(c) * num_heads + h;
   const int64_t col = int64_t(start) * stride + h * kDim + d;
+  const uint32_t sbase = smem_u32(sm);
+  // element [i][d] of a swizzled bf16 tile for this thread's channel: the channel's part of the address is fixed
+  const uint32_t d_base = uint32_t(d >> 6) * 8192u + uint32_t(d & 7) * 2u, d_chunk = uint32_t(d & 63) >> 3;
+  auto rq_at = [&](const uint8_t* t, int i) {
+    return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(
+        t + d_base + uint32_t(i) * 128u + ((d_chunk ^ (uint32_t(i) & 7u)) << 4)));
+  };
 
-  if (tid < 64) s_beta[tid] = tid < len ? beta[int64_t(start + tid) * num_heads + h] : 0.f;
-#pragma unroll 8
-  for (int i = tid >> 7; i < 64; i += 4) {  // rows past the chunk's length: q = k = 0, R = 1
-    const bool live = i < len;
-    const int64_t at = col + int64_t(live ? i : 0) * stride;
-    sQ[i * 128 + d] = live ? __bfloat162float(q[at]) : 0.f;
-    sK[i * 128 + d] = live ? __bfloat162float(k[at]) : 0.f;
-    sR[i * 128 + d] = (live && i > 0) ? fast_exp2(g2[at] - g2[at - stride]) : 1.f;
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_init(&bar_load, 1);
+    fence_mbar_init();
+    mbar_arrive_expect(&bar_load, 2 * 16384);
+    tma_load_tile128(sbase + KdaPairSmem::kRaw, 8192, &maps.q, h * kDim, start, &bar_load);
+    tma_load_tile128(sbase + KdaPairSmem::kRaw + 16384, 8192, &maps.k, h * kDim, start, &bar_load);
   }
-  __syncthreads();  // beta is in place for the transposed copy of M2
-#pragma unroll 8
-  for (int i = tid; i < 4096; i += 512) {  // M and its transpose (rows of 68 floats: 16-byte aligned, few conflicts)
-    const float a = m1[tile * 4096 + i], b = m2[tile * 4096 + i];
-    const int ii = i >> 6, jj = i & 63;
-    sM1[i] = a;
-    sM2[i] = b;
-    sM1T[jj * 68 + ii] = a;
-    sM2T[jj * 68 + ii] = s_beta[ii] * b;
+  if (warp == 0) tmem_alloc(&tmem_slot, 512);
+  if (tid < 64) s_beta[tid] = tid < len ? beta[int64_t(start + tid) * num_heads + h] : 0.f;
+#pragma unroll
+  for (int n = 0; n < 16; ++n) {  // rows past the chunk's length keep the last gate (R = 1 there)
+    const int i = (tid >> 7) + 4 * n;
+    sG[i * 128 + d] = g2[col + int64_t(i < len ? i : len - 1) * stride];
+  }
+  __syncthreads();  // beta, the gates and the barriers' initialisation are in place
+#pragma unroll
+  for (int n = 0; n < 16; ++n) {
+    const int i = (tid >> 7) + 4 * n;
+    sR[i * 128 + d] = (i < len && i > 0) ? fast_exp2(sG[i * 128 + d] - sG[(i - 1) * 128 + d]) : 1.f;
+  }
+  // the operands of the products from M1 and M2: AR (rows against their own block's part of the stack), X1 / X2 (the
+  // entries of earlier blocks), and the fp32 diagonal blocks
+  for (int t = tid; t < 128 * 12; t += 512) {
+    const int n = t / 12, cc = t % 12;            // row of AR, 16-byte chunk of its 96 columns
+    const int i = n & 63, colb = cc * 8;
+    const int owner = colb < 16 ? 1 : (colb < 48 ? 2 : 3);
+    const int j = colb < 16 ? colb : (colb < 48 ? colb - 16 : colb - 48);
+    float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if ((i >> 4) == owner) {
+      const float* src = (n < 64 ? m1 : m2) + tile * 4096 + i * 64 + j;
+      const float4 lo = __ldg(reinterpret_cast<const float4*>(src)), hi = __ldg(reinterpret_cast<const float4*>(src) + 1);
+      x[0] = lo.x, x[1] = lo.y, x[2] = lo.z, x[3] = lo.w, x[4] = hi.x, x[5] = hi.y, x[6] = hi.z, x[7] = hi.w;
+    }
+    *reinterpret_cast<uint4*>(ar + (cc >> 3) * 16384 + sw128_offset(n, cc & 7)) = pack8(x);
+  }
+  for (int t = tid; t < 64 * 8; t += 512) {
+    const int i = t >> 3, cc = t & 7;
+    const float* s1 = m1 + tile * 4096 + i * 64 + cc * 8;
+    const float* s2 = m2 + tile * 4096 + i * 64 + cc * 8;
+    const float4 a0 = __ldg(reinterpret_cast<const float4*>(s1)), a1 = __ldg(reinterpret_cast<const float4*>(s1) + 1);
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(s2)), b1 = __ldg(reinterpret_cast<const float4*>(s2) + 1);
+    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    const bool earlier = (cc >> 1) < (i >> 4);     // the 8 columns lie in a block before the row's
+    float xa[8], xb[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) xa[e] = earlier ? av[e] : 0.f, xb[e] = earlier ? bv[e] : 0.f;
+    *reinterpret_cast<uint4*>(x1 + sw128_offset(i, cc)) = pack8(xa);
+    *reinterpret_cast<uint4*>(x2 + sw128_offset(i, cc)) = pack8(xb);
+    if ((cc >> 1) == (i >> 4)) {                   // ... or in the row's own block: the fp32 diagonal blocks
+      const int at = ((i >> 4) * 16 + (i & 15)) * 20 + (cc & 1) * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sM1d[at + e] = av[e], sM2d[at + e] = bv[e];
+    }
+  }
+  bool ok = __all_sync(0xffffffffu, mbar_wait(&bar_load, 0));
+  if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows
+    clear_tile_rows<512>(q_raw, len, tid);
+    clear_tile_rows<512>(k_raw, len, tid);
   }
   __syncthreads();
+  // the stack (row r holds k_j 2^{G_R - G_j} for (R, j) = (16, r), (32, r - 16), (48, r - 48)) and q~, k~'
+  for (int t = tid; t < 96 * 16; t += 512) {
+    const int r = t >> 4, cc = t & 15;
+    const int ref = r < 16 ? 16 : (r < 48 ? 32 : 48);
+    const int j = r < 16 ? r : (r < 48 ? r - 16 : r - 48);
+    float x[8];
+    unpack8(tile_chunk(k_raw, 8192, j, cc), x);
+    const float* gr = sG + ref * 128 + cc * 8;
+    const float* gj = sG + j * 128 + cc * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] *= fast_exp2(gr[e] - gj[e]);
+    *reinterpret_cast<uint4*>(stack + (cc >> 3) * 12288 + sw128_offset(r, cc & 7)) = pack8(x);
+  }
+  for (int t = tid; t < 64 * 16; t += 512) {
+    const int r = t >> 4, cc = t & 15;
+    const float* gi = sG + r * 128 + cc * 8;
+    const float* gr = sG + (r & ~15) * 128 + cc * 8;
+    float f[8], x[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = fast_exp2(gi[e] - gr[e]);
+    unpack8(tile_chunk(q_raw, 8192, r, cc), x);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] *= f[e];
+    set_tile_chunk(q_cvt, 8192, r, cc, pack8(x));
+    unpack8(tile_chunk(k_raw, 8192, r, cc), x);
+    const float br = s_beta[r];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] *= f[e] * br;
+    set_tile_chunk(k_cvt, 8192, r, cc, pack8(x));
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  constexpr uint32_t kColDR = 0, kColP = 128;  // tensor-memory columns: DR^T, then P1^T, P2^T, P3^T (64 each)
+  if (tid == 0) {
+    const Operand op_stack{sbase + KdaPairSmem::kStack, 12288}, op_ar{sbase + KdaPairSmem::kAR, 16384};
+    const Operand op_q{sbase + KdaPairSmem::kCvt, 8192}, op_k{sbase + KdaPairSmem::kCvt + 16384, 8192};
+    const Operand op_x1{sbase + KdaPairSmem::kX1, 8192}, op_x2{sbase + KdaPairSmem::kX2, 8192};
+    umma_gemm<128, 128>(tmem + kColDR, op_stack, true, op_ar, false, 96, false);
+#pragma unroll
+    for (int blk = 1; blk < 4; ++blk) {
+      umma_gemm<128, 64>(tmem + kColP + 64 * (blk - 1), operand_at(op_q, 16 * blk), true, operand_at(op_x1, 16 * blk),
+                         true, 16, false);
+      umma_gemm<128, 64>(tmem + kColP + 64 * (blk - 1), operand_at(op_k, 16 * blk), true, operand_at(op_x2, 16 * blk),
+                         true, 16, true);
+    }
+    umma_commit(&bar);
+  }
+  bool products_seen = false;
+  auto wait_products = [&]() {  // a whole warp at a time (a warp shares role and half, and so its trip counts)
+    if (!products_seen) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0)) && ok;
+      tc_fence_after();
+      products_seen = true;
+    }
+  };
+  const uint32_t my_lane = tmem + (uint32_t(warp4 * 32) << 16);  // this thread's channel is its tensor-memory lane
 
+  // What a thread carries out of its pass, per row / column of its eight groups of four: the row pass dk's row part
+  // and the gate gradient's row part, the column pass CC and the gate gradient's column part.  The gate gradient is
+  // a sum of terms that cancel along the chunk (sum_i q_i RQ_i = sum_j k_j CK_j term by term), so both passes form
+  // their tensor-core parts from the SAME rounded factors (q~, beta k~', the stack, bf16 M): the terms still cancel
+  // to fp32 accuracy, which exact factors on one side and rounded ones on the other would not.
+  float keep_a[32], keep_b[32];
+#pragma unroll
+  for (int n = 0; n < 32; ++n) keep_a[n] = keep_b[n] = 0.f;
   float chunk_end = 0.f;
   if (role == 0) {
-    // ---- row pass: four rows at a time.  For j below the block, E_{i0+r, j} = E_{i0, j} E_{i0+r, i0}: the four rows
-    // share k_j E_{i0, j} and take their own factor (<= 1) once at the end; the 4 x 4 diagonal block is done apart.
-    const float gl = g2[col + int64_t(len - 1) * stride];
-    for (int i0 = 4 * half; i0 < len; i0 += 8) {
-      float rq[4] = {0.f, 0.f, 0.f, 0.f}, rk[4] = {0.f, 0.f, 0.f, 0.f};
-      float gi4[4], xq4[4], xr4[4], xg4[4];  // the rows' global operands, in flight while the sums run
+    // ---- row pass: four rows at a time.  For j below the group (inside the 16-block), E_{i0+r, j} = E_{i0, j}
+    // E_{i0+r, i0}: the four rows share k_j E_{i0, j} and take their own factor (<= 1) once at the end; the 4 x 4
+    // diagonal block is done apart; the earlier blocks come from the tensor core.
+    const float gl = sG[(len - 1) * 128 + d];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int64_t at = col + int64_t(i0 + r < len ? i0 + r : len - 1) * stride;
-        gi4[r] = g2[at], xq4[r] = dqg[at], xr4[r] = dkr[at], xg4[r] = dkg[at];
-      }
-      float e = sR[i0 * 128 + d];  // E_{i0, i0 - 1}
-      for (int j0 = i0 - 4; j0 >= 0; j0 -= 4) {
-        float av[4][4], bv[4][4];
+    for (int n = 0; n < 8; ++n) {
+      const int i0 = 4 * half + 8 * n;
+      if (i0 < len) {  // uniform over the block
+        const int big = i0 >> 4, bs = i0 & ~15;
+        const float* m1d = sM1d + big * 16 * 20;
+        const float* m2d = sM2d + big * 16 * 20;
+        float rq[4] = {0.f, 0.f, 0.f, 0.f}, rk[4] = {0.f, 0.f, 0.f, 0.f};
+        float xq4[4], xr4[4], xg4[4];  // the rows' global operands, in flight while the sums run
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-          const float4 a = *reinterpret_cast<const float4*>(sM1 + (i0 + r) * 64 + j0);
-          const float4 b = *reinterpret_cast<const float4*>(sM2 + (i0 + r) * 64 + j0);
-          av[r][0] = a.x, av[r][1] = a.y, av[r][2] = a.z, av[r][3] = a.w;
-          bv[r][0] = b.x, bv[r][1] = b.y, bv[r][2] = b.z, bv[r][3] = b.w;
+          const int64_t at = col + int64_t(i0 + r < len ? i0 + r : len - 1) * stride;
+          xq4[r] = dqg[at], xr4[r] = dkr[at], xg4[r] = dkg[at];
         }
-#pragma unroll
-        for (int t = 3; t >= 0; --t) {
-          const float kj = sK[(j0 + t) * 128 + d] * e;
+        float e = sR[i0 * 128 + d];  // E_{i0, i0 - 1}
+        for (int j0 = i0 - 4; j0 >= bs; j0 -= 4) {
+          float av[4][4], bv[4][4];
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
-            rq[r] = fmaf(av[r][t], kj, rq[r]);
-            rk[r] = fmaf(bv[r][t], kj, rk[r]);
+            const float4 a = *reinterpret_cast<const float4*>(m1d + (i0 + r - bs) * 20 + j0 - bs);
+            const float4 b = *reinterpret_cast<const float4*>(m2d + (i0 + r - bs) * 20 + j0 - bs);
+            av[r][0] = a.x, av[r][1] = a.y, av[r][2] = a.z, av[r][3] = a.w;
+            bv[r][0] = b.x, bv[r][1] = b.y, bv[r][2] = b.z, bv[r][3] = b.w;
           }
-          e *= sR[(j0 + t) * 128 + d];
+#pragma unroll
+          for (int t = 3; t >= 0; --t) {
+            const float kj = rq_at(k_raw, j0 + t) * e;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              rq[r] = fmaf(av[r][t], kj, rq[r]);
+              rk[r] = fmaf(bv[r][t], kj, rk[r]);
+            }
+            e *= sR[(j0 + t) * 128 + d];
+          }
         }
-      }
-      float r4[4], k4[4];
+        float r4[4], k4[4];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) r4[r] = sR[(i0 + r) * 128 + d], k4[r] = sK[(i0 + r) * 128 + d];
-      {
-        float f = 1.f;
+        for (int r = 0; r < 4; ++r) r4[r] = sR[(i0 + r) * 128 + d], k4[r] = rq_at(k_raw, i0 + r);
+        {
+          float f = 1.f;
 #pragma unroll
-        for (int r = 1; r < 4; ++r) {
-          f *= r4[r];  // E_{i0 + r, i0}
-          rq[r] *= f;
-          rk[r] *= f;
-        }
-      }
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {  // the diagonal block: pairs (i0 + r, i0 + t), t <= r
-        const float4 a = *reinterpret_cast<const float4*>(sM1 + (i0 + r) * 64 + i0);
-        const float4 b = *reinterpret_cast<const float4*>(sM2 + (i0 + r) * 64 + i0);  // zero on the diagonal
-        const float at4[4] = {a.x, a.y, a.z, a.w}, bt4[4] = {b.x, b.y, b.z, b.w};
-        float ee = 1.f;
-#pragma unroll
-        for (int t = r; t >= 0; --t) {
-          const float kj = k4[t] * ee;
-          rq[r] = fmaf(at4[t], kj, rq[r]);
-          rk[r] = fmaf(bt4[t], kj, rk[r]);
-          ee *= r4[t];
-        }
-      }
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int i = i0 + r;
-        float db = 0.f;
-        if (i < len) {
-          const float qi = sQ[i * 128 + d], ki = k4[r], bi = s_beta[i];
-          const int64_t at = col + i * stride;
-          const float gi = gi4[r];
-          const float eg = fast_exp2(gi), er = fast_exp2(gl - gi);
-          const float qgr = round_bf16(qi * eg), kgr = round_bf16(ki * eg), krr = round_bf16(ki * er);
-          const float xq = xq4[r], xr = xr4[r], xg = xg4[r];
-          dq[at] = fmaf(xq, eg, rq[r]);
-          dk[at] = fmaf(bi, rk[r], fmaf(xr, er, xg * eg));                             // + the column part below
-          dg[at] = qi * rq[r] + ki * bi * rk[r] + xq * qgr + xg * kgr - xr * krr;      // likewise
-          chunk_end = fmaf(xr, krr, chunk_end);
-          db = ki * rk[r];  // dbeta_i += sum_d k_id RK_id
+          for (int r = 1; r < 4; ++r) {
+            f *= r4[r];  // E_{i0 + r, i0}
+            rq[r] *= f;
+            rk[r] *= f;
+          }
         }
 #pragma unroll
-        for (int m = 16; m >= 1; m >>= 1) db += __shfl_xor_sync(0xffffffffu, db, m);
-        if (lane == 0 && i < len) s_db[i * 4 + warp] = db;
+        for (int r = 0; r < 4; ++r) {  // the diagonal 4 x 4 block: pairs (i0 + r, i0 + t), t <= r (M2 is zero on the diagonal)
+          const float4 a = *reinterpret_cast<const float4*>(m1d + (i0 + r - bs) * 20 + i0 - bs);
+          const float4 b = *reinterpret_cast<const float4*>(m2d + (i0 + r - bs) * 20 + i0 - bs);
+          const float at4[4] = {a.x, a.y, a.z, a.w}, bt4[4] = {b.x, b.y, b.z, b.w};
+          float ee = 1.f;
+#pragma unroll
+          for (int t = r; t >= 0; --t) {
+            const float kj = k4[t] * ee;
+            rq[r] = fmaf(at4[t], kj, rq[r]);
+            rk[r] = fmaf(bt4[t], kj, rk[r]);
+            ee *= r4[t];
+          }
+        }
+        // the earlier blocks: this channel's lane of DR^T, columns i0 .. i0 + 3 (M1) and 64 + i0 .. (M2)
+        wait_products();
+        float offq[4], offk[4];
+        tmem_ld4(my_lane + kColDR + i0, offq);
+        tmem_ld4(my_lane + kColDR + 64 + i0, offk);
+        tmem_ld_wait();
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int i = i0 + r;
+          float db = 0.f;
+          if (i < len) {
+            const float gi = sG[i * 128 + d];
+            const float down = fast_exp2(gi - sG[bs * 128 + d]);  // 2^{G_i - G_R}
+            const float rqt = fmaf(down, offq[r], rq[r]), rkt = fmaf(down, offk[r], rk[r]);
+            const float qi = rq_at(q_raw, i), ki = k4[r], bi = s_beta[i];
+            const int64_t at = col + i * stride;
+            const float eg = fast_exp2(gi), er = fast_exp2(gl - gi);
+            const float qgr = round_bf16(qi * eg), kgr = round_bf16(ki * eg), krr = round_bf16(ki * er);
+            const float xq = xq4[r], xr = xr4[r], xg = xg4[r];
+            dq[at] = fmaf(xq, eg, rqt);
+            keep_a[4 * n + r] = fmaf(bi, rkt, fmaf(xr, er, xg * eg));                // dk without its column part
+            // the gate gradient's row part: the tensor-core sums against the rounded factors they were formed from
+            keep_b[4 * n + r] = fmaf(rq_at(q_cvt, i), offq[r], fmaf(rq_at(k_cvt, i), offk[r], qi * rq[r] + ki * bi * rk[r])) +
+                                xq * qgr + xg * kgr - xr * krr;
+            chunk_end = fmaf(xr, krr, chunk_end);
+            db = ki * rkt;  // dbeta_i += sum_d k_id RK_id
+          }
+#pragma unroll
+          for (int m = 16; m >= 1; m >>= 1) db += __shfl_xor_sync(0xffffffffu, db, m);
+          if (lane == 0 && i < len) s_db[i * 4 + warp4] = db;
+        }
       }
     }
     if (half == 0) chunk_end = fmaf(fast_exp2(gl), hdh[tile * kDim + d], chunk_end);
   } else {
-    // ---- column pass: four columns at a time.  For i below the block, E_{i, j0+c} = E_{i, j0+3} E_{j0+3, j0+c}.
-    for (int j0 = 4 * half; j0 < len; j0 += 8) {
-      float cc[4] = {0.f, 0.f, 0.f, 0.f};
-      float e = 1.f;
-      for (int i0 = j0 + 4; i0 < len; i0 += 4) {  // rows at or past the chunk's length hold q = k = 0 and R = 1
-        float av[4][4], bv[4][4];
+    // ---- column pass: four columns at a time.  For i below the group (inside the 16-block), E_{i, j0+c} =
+    // E_{i, j0+3} E_{j0+3, j0+c}; the later blocks come from the tensor core.
+    wait_products();
 #pragma unroll
-        for (int cidx = 0; cidx < 4; ++cidx) {
-          const float4 a = *reinterpret_cast<const float4*>(sM1T + (j0 + cidx) * 68 + i0);
-          const float4 b = *reinterpret_cast<const float4*>(sM2T + (j0 + cidx) * 68 + i0);
-          av[cidx][0] = a.x, av[cidx][1] = a.y, av[cidx][2] = a.z, av[cidx][3] = a.w;
-          bv[cidx][0] = b.x, bv[cidx][1] = b.y, bv[cidx][2] = b.z, bv[cidx][3] = b.w;
+    for (int n = 0; n < 8; ++n) {
+      const int j0 = 4 * half + 8 * n;
+      if (j0 < len) {
+        const int big = j0 >> 4, bs = j0 & ~15;
+        const int be = len < bs + 16 ? len : bs + 16;
+        const float* m1d = sM1d + big * 16 * 20;
+        const float* m2d = sM2d + big * 16 * 20;
+        float cc[4] = {0.f, 0.f, 0.f, 0.f};
+        float e = 1.f;
+        for (int i0 = j0 + 4; i0 < be; i0 += 4) {  // rows at or past the chunk's length hold q = k = 0 and R = 1
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            e *= sR[(i0 + t) * 128 + d];  // E_{i0 + t, j0 + 3}
+            const float tq = rq_at(q_raw, i0 + t) * e, tk = rq_at(k_raw, i0 + t) * e * s_beta[i0 + t];
+            const float4 a = *reinterpret_cast<const float4*>(m1d + (i0 + t - bs) * 20 + j0 - bs);
+            const float4 b = *reinterpret_cast<const float4*>(m2d + (i0 + t - bs) * 20 + j0 - bs);
+            cc[0] = fmaf(a.x, tq, fmaf(b.x, tk, cc[0]));
+            cc[1] = fmaf(a.y, tq, fmaf(b.y, tk, cc[1]));
+            cc[2] = fmaf(a.z, tq, fmaf(b.z, tk, cc[2]));
+            cc[3] = fmaf(a.w, tq, fmaf(b.w, tk, cc[3]));
+          }
+        }
+        float r4[4], k4[4], q4[4], b4[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          r4[r] = sR[(j0 + r) * 128 + d], k4[r] = rq_at(k_raw, j0 + r), q4[r] = rq_at(q_raw, j0 + r);
+          b4[r] = s_beta[j0 + r];
+        }
+        {
+          float f = 1.f;
+#pragma unroll
+          for (int cidx = 2; cidx >= 0; --cidx) {
+            f *= r4[cidx + 1];  // E_{j0 + 3, j0 + cidx}
+            cc[cidx] *= f;
+          }
         }
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          e *= sR[(i0 + t) * 128 + d];  // E_{i0 + t, j0 + 3}
-          const float tq = sQ[(i0 + t) * 128 + d] * e, tk = sK[(i0 + t) * 128 + d] * e;
+        for (int cidx = 0; cidx < 4; ++cidx) {  // the diagonal 4 x 4 block: pairs (j0 + r, j0 + cidx), r >= cidx
+          float ee = 1.f;
 #pragma unroll
-          for (int cidx = 0; cidx < 4; ++cidx) cc[cidx] = fmaf(av[cidx][t], tq, fmaf(bv[cidx][t], tk, cc[cidx]));
+          for (int r = cidx; r < 4; ++r) {
+            if (r > cidx) ee *= r4[r];
+            cc[cidx] = fmaf(fmaf(m1d[(j0 + r - bs) * 20 + j0 + cidx - bs], q4[r],
+                                 m2d[(j0 + r - bs) * 20 + j0 + cidx - bs] * b4[r] * k4[r]), ee, cc[cidx]);
+          }
         }
-      }
-      float r4[4], k4[4], q4[4];
+        float kcc[4];
 #pragma unroll
-      for (int r = 0; r < 4; ++r)
-        r4[r] = sR[(j0 + r) * 128 + d], k4[r] = sK[(j0 + r) * 128 + d], q4[r] = sQ[(j0 + r) * 128 + d];
-      {
-        float f = 1.f;
+        for (int cidx = 0; cidx < 4; ++cidx) kcc[cidx] = k4[cidx] * cc[cidx];
+        // the later blocks: sum over I > block(j) of 2^{G_{16 I} - G_j} PI^T[d][j]; for the gate gradient the same
+        // sums against the stack's own (rounded) k_j 2^{G_{16 I} - G_j}
+        for (int blk = big + 1; blk < 4; ++blk) {
+          float p[4];
+          tmem_ld4(my_lane + kColP + 64 * (blk - 1) + j0, p);
+          tmem_ld_wait();
+          const float gref = sG[(16 * blk) * 128 + d];
+          const int base_row = blk == 1 ? 0 : (blk == 2 ? 16 : 48);
 #pragma unroll
-        for (int cidx = 2; cidx >= 0; --cidx) {
-          f *= r4[cidx + 1];  // E_{j0 + 3, j0 + cidx}
-          cc[cidx] *= f;
+          for (int cidx = 0; cidx < 4; ++cidx) {
+            cc[cidx] = fmaf(fast_exp2(gref - sG[(j0 + cidx) * 128 + d]), p[cidx], cc[cidx]);
+            const float kst = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(
+                stack + (d >> 6) * 12288 + sw128_offset(base_row + j0 + cidx, (d & 63) >> 3) + (d & 7) * 2));
+            kcc[cidx] = fmaf(kst, p[cidx], kcc[cidx]);
+          }
         }
-      }
 #pragma unroll
-      for (int cidx = 0; cidx < 4; ++cidx) {  // the diagonal block: pairs (j0 + r, j0 + cidx), r >= cidx
-        const float4 a = *reinterpret_cast<const float4*>(sM1T + (j0 + cidx) * 68 + j0);
-        const float4 b = *reinterpret_cast<const float4*>(sM2T + (j0 + cidx) * 68 + j0);
-        const float at4[4] = {a.x, a.y, a.z, a.w}, bt4[4] = {b.x, b.y, b.z, b.w};
-        float ee = 1.f;
-#pragma unroll
-        for (int r = cidx; r < 4; ++r) {
-          if (r > cidx) ee *= r4[r];
-          cc[cidx] = fmaf(fmaf(at4[r], q4[r], bt4[r] * k4[r]), ee, cc[cidx]);
-        }
-        sCC[(j0 + cidx) * 128 + d] = cc[cidx];
+        for (int cidx = 0; cidx < 4; ++cidx) keep_a[4 * n + cidx] = cc[cidx], keep_b[4 * n + cidx] = kcc[cidx];
       }
     }
   }
-  float* s_end = sR;  // after the passes: the chunk-end term per channel (two halves) in R's space ...
-  float* s_dg = sQ;   // ... and the per-row gate gradients in q's space
+  wait_products();
+  __syncthreads();  // both passes are done with the gates and the factors: their space takes the column pass's sums
+  float* s_cc = sG;    // CC [64][128]
+  float* s_kcc = sR;   // the gate gradient's column part [64][128]
+  float* s_dg = sCC;   // the per-row gate gradients (AR's space: the products are long done)
+  float* s_end = reinterpret_cast<float*>(sm + KdaPairSmem::kX1);  // the chunk-end term per channel, two halves
+  if (role == 1) {
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int j = 4 * half + 8 * n + r;
+        if (j < len) s_cc[j * 128 + d] = keep_a[4 * n + r], s_kcc[j * 128 + d] = keep_b[4 * n + r];
+      }
+    }
+  } else {
+    s_end[half * 128 + d] = chunk_end;
+  }
   __syncthreads();
-  if (role == 0) s_end[half * 128 + d] = chunk_end;
-  __syncthreads();
-  // every thread: the column parts join the row parts (which the row pass left in dk and dg) -- elementwise, so the
-  // global reads overlap; the block barriers above order the row pass's global writes before these reads
-#pragma unroll 8
-  for (int i = tid >> 7; i < len; i += 4) {
-    const int64_t at = col + i * stride;
-    const float cc = sCC[i * 128 + d];
-    dk[at] += cc;
-    float dgi = dg[at] - sK[i * 128 + d] * cc;
-    if (i == len - 1) dgi += s_end[d] + s_end[128 + d];
-    s_dg[i * 128 + d] = dgi;
+  if (role == 0) {  // the row pass's threads own the same (row, channel) pairs: dk and the gate gradient in one go
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int i = 4 * half + 8 * n + r;
+        if (i < len) {
+          dk[col + i * stride] = keep_a[4 * n + r] + s_cc[i * 128 + d];
+          float dgi = keep_b[4 * n + r] - s_kcc[i * 128 + d];
+          if (i == len - 1) dgi += s_end[d] + s_end[128 + d];
+          s_dg[i * 128 + d] = dgi;
+        }
+      }
+    }
   }
   __syncthreads();
   if (tid < 128) {  // the in-chunk suffix sum, one channel per thread
@@ -800,6 +1114,10 @@ __global__ void __launch_bounds__(512) kda_tail_pair_kernel(
     const int64_t at = int64_t(start + d) * num_heads + h;
     dbeta[at] = dbeta_part[at] + ((s_db[d * 4] + s_db[d * 4 + 1]) + (s_db[d * 4 + 2] + s_db[d * 4 + 3]));
   }
+  if (!ok && tid == 0) atomicExch(status, kDevWaitTimeout | (8 << 8));
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 // One warp per row of 128: out = bf16(x) or, with the norm's saved r, bf16(r (x - y (x . y))), y = raw r.
@@ -866,8 +1184,11 @@ int mek_kda_intra(const MekGdnDims* d, const void* q, const void* k, const void*
   if (int rc = check_kda(d, "kda_intra")) return rc;
   const size_t smem = KdaIntraSmem::kBytes + 1024;
   if (int rc = want_smem(kda_intra_kernel, smem, "kda_intra")) return rc;
-  kda_intra_kernel<<<dim3(d->num_chunks, d->num_v_heads), 288, smem, static_cast<cudaStream_t>(stream)>>>(
-      In(q), In(k), In(v), In(kg), g2, beta, Out(a_out), Out(aqk_out), Out(w_out), Out(u_out), d->chunk_start,
+  KdaIntraMaps maps;
+  if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_v_heads, "kda_intra")) return rc;
+  if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_v_heads, "kda_intra")) return rc;
+  kda_intra_kernel<<<dim3(d->num_chunks, d->num_v_heads), kIntraThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      maps, In(v), In(kg), g2, beta, Out(a_out), Out(aqk_out), Out(w_out), Out(u_out), d->chunk_start,
       d->chunk_len, d->num_v_heads, d->scale, status);
   return launched("kda_intra");
 }
@@ -879,7 +1200,10 @@ int mek_kda_bwd_tail(const MekGdnDims* d, const void* q, const void* k, const vo
                      int32_t* status, void* stream) {
   using namespace mek;
   if (int rc = check_kda(d, "kda_bwd_tail")) return rc;
-  const size_t smem_a = KdaTailSmem::kBytes + 1024, smem_b = KdaPairSmem::kBytes + 128;
+  const size_t smem_a = KdaTailSmem::kBytes + 1024, smem_b = KdaPairSmem::kBytes + 1024;
+  KdaPairMaps maps;
+  if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_v_heads, "kda_bwd_tail")) return rc;
+  if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_v_heads, "kda_bwd_tail")) return rc;
   if (int rc = want_smem(kda_tail_mma_kernel, smem_a, "kda_bwd_tail")) return rc;
   if (int rc = want_smem(kda_tail_pair_kernel, smem_b, "kda_bwd_tail")) return rc;
   const dim3 grid(d->num_chunks, d->num_v_heads);
@@ -888,8 +1212,8 @@ int mek_kda_bwd_tail(const MekGdnDims* d, const void* q, const void* k, const vo
                                                 In(dv_new), In(d_o), m1, m2, dqg, dkr, dkg, hdh, Out(dv), dbeta_part,
                                                 d->chunk_start, d->chunk_len, d->num_v_heads, d->scale, status);
   if (int rc = launched("kda_bwd_tail (tensor-core part)")) return rc;
-  kda_tail_pair_kernel<<<grid, 512, smem_b, s>>>(In(q), In(k), g2, beta, m1, m2, dqg, dkr, dkg, hdh, dbeta_part, dq32,
-                                                 dk32, dg, dbeta, d->chunk_start, d->chunk_len, d->num_v_heads);
+  kda_tail_pair_kernel<<<grid, 512, smem_b, s>>>(maps, g2, beta, m1, m2, dqg, dkr, dkg, hdh, dbeta_part, dq32, dk32, dg,
+                                                 dbeta, d->chunk_start, d->chunk_len, d->num_v_heads, status);
   return launched("kda_bwd_tail (pairwise part)");
 }
 
