@@ -83,7 +83,8 @@ __device__ __forceinline__ int f32_block_index(int row, int k) { return row * 32
 
 // Three CTAs per SM (shared memory) hide each other's global-load and solve latencies; tensor memory: 128 columns.
 struct WyMaps {
-  CUtensorMap q, k, v;  // rows, box 64 x 64
+  CUtensorMap q, k, v;      // rows, box 64 x 64
+  CUtensorMap w_out, u_out;  // rows, box 64 x 64 (stores)
 };
 
 __global__ void __launch_bounds__(128) gdn_wy_kernel(
@@ -141,49 +142,37 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
                            128, false, false);  // alternating: one product's instructions wait for one another
     umma_commit(&bar);
   }
-  // meanwhile: kb = bf16(beta 2^G k), vb = bf16(beta v) (in place)
-  for (int i = tid; i < 64 * 16; i += 128) {
-    const int r = i >> 4, cc = i & 15;
-    const float b = s_beta[r], s = b * fast_exp2(s_g2[r]);
-    float x[8];
-    unpack8(tile_chunk(sm + WySmem::kK, 8192, r, cc), x);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] *= s;
-    set_tile_chunk(sm + WySmem::kKB, 8192, r, cc, pack8(x));
-    unpack8(tile_chunk(sm + WySmem::kV, 8192, r, cc), x);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] *= b;
-    set_tile_chunk(sm + WySmem::kV, 8192, r, cc, pack8(x));
-  }
   ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0)) && ok;
   tc_fence_after();
   __syncthreads();  // every thread sees the products done: the q tile's space now takes L
 
   if (ok) {
-    // lanes 0..15: Aqk row i -> global; lanes 16..31: L row i -> shared
+    // lanes 0..15: Aqk row i -> global; lanes 16..31: L row i -> shared.  Both are the product's entry times the
+    // decay 2^{G_i - G_col} and a row factor (scale / beta_i), Aqk with its diagonal and L without: one instruction
+    // stream for both lane halves up to the stores.
     const int i = warp * 16 + (lane & 15);
     const bool upper = lane >= 16;
-    const float gi = s_g2[i], bi = s_beta[i];
+    const float gi = s_g2[i], factor = upper ? s_beta[i] : scale;
+    const int last = upper ? i - 1 : i;  // the last column that is kept
     __nv_bfloat16* dst = aqk_out + (int64_t(c) * num_v_heads + hv) * 4096 + i * 64;
 #pragma unroll
     for (int p = 0; p < 2; ++p) {
       float s[32];
       tmem_ld32(tmem_addr(tmem, warp, p * 32), s);
       tmem_ld_wait();
-      if (!upper) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = p * 32 + j;
-          s[j] = col <= i ? scale * s[j] * fast_exp2(gi - s_g2[col]) : 0.f;
-        }
+      for (int j = 0; j < 32; ++j) {
+        const int col = p * 32 + j;
+        s[j] = col <= last ? factor * s[j] * fast_exp2(gi - s_g2[col]) : 0.f;
+      }
+      if (!upper) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst + p * 32)[j] = pack8(s + 8 * j);
       } else {
+        // four consecutive columns are contiguous in the operand layout: 16-byte stores
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = p * 32 + j;
-          s_l[wy_l_index(i, col)] = col < i ? bi * s[j] * fast_exp2(gi - s_g2[col]) : 0.f;
-        }
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(s_l + wy_l_index(i, p * 32 + j)) = make_float4(s[j], s[j + 1], s[j + 2], s[j + 3]);
       }
     }
   }
@@ -198,6 +187,10 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   float* s_a2 = s_b1 + 1024;
   float* s_b2 = s_a2 + 2048;
   uint8_t* a_tile = sm + WySmem::kA;
+  // Warps 0..1 solve in registers while warps 2..3 build the last products' operands, kb = bf16(beta 2^G k) and
+  // vb = bf16(beta v) (in place), from the k tile, whose space the solve's results take afterwards: the two halves
+  // meet on a named barrier before anything is written there.
+  auto halves_meet = [] { asm volatile("bar.sync 1, 128;" ::: "memory"); };
   if (tid < 64) {
     const int b = tid >> 5, c = tid & 31, base = 32 * b;
     float x[32];
@@ -214,6 +207,7 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
       }
       x[i] = (acc0 + acc1) + (acc2 + acc3);
     }
+    halves_meet();  // the k tile has been read: its space takes B1 and A2
     const int col = base + c;
 #pragma unroll
     for (int i = 0; i < 32; ++i)
@@ -227,11 +221,27 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
 #pragma unroll
       for (int i = 0; i < 32; ++i) s_a2[f32_block_index(32 + i, c)] = x[i];
     }
-  } else {  // rows 0..31 of A2 and the upper right block of A are zero
+  } else {
     const int t = tid - 64;
-    for (int i = t; i < 256; i += 64) reinterpret_cast<float4*>(s_a2)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = t; i < 64 * 16; i += 64) {
+      const int r = i >> 4, cc = i & 15;
+      const float b = s_beta[r], sc = b * fast_exp2(s_g2[r]);
+      float x[8];
+      unpack8(tile_chunk(sm + WySmem::kK, 8192, r, cc), x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] *= sc;
+      set_tile_chunk(sm + WySmem::kKB, 8192, r, cc, pack8(x));
+      unpack8(tile_chunk(sm + WySmem::kV, 8192, r, cc), x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] *= b;
+      set_tile_chunk(sm + WySmem::kV, 8192, r, cc, pack8(x));
+    }
+    // the upper right block of A is zero (its tile is this phase's own)
     for (int i = t; i < 32 * 4; i += 64)
       set_tile_chunk(a_tile, 8192, i >> 2, 4 + (i & 3), make_uint4(0u, 0u, 0u, 0u));
+    halves_meet();
+    // rows 0..31 of A2 are zero
+    for (int i = t; i < 256; i += 64) reinterpret_cast<float4*>(s_a2)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   fence_async_smem();
   tc_fence_before();
@@ -302,19 +312,37 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   tc_fence_after();
 
   ok = __all_sync(0xffffffffu, ok);
+  // w and u leave through shared memory (the dead q / k tiles' space) and one TMA store each: a thread's row piece
+  // written straight to global memory would touch a different 128-byte line in every lane.  A ragged chunk's rows are
+  // stored by hand (a 64-row box would run into the next sequence).
+  const bool by_box = len == kChunk;
   if (ok) {
     const int i = warp * 16 + (lane & 15);
     const bool live = i < len;
     __nv_bfloat16* dst = (lane < 16 ? w_out : u_out) + int64_t(start + i) * v_stride + hv * kDim;
+    uint8_t* stage = sm + (lane < 16 ? WySmem::kQ : WySmem::kK);
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
       float s[32];
       tmem_ld32(tmem_addr(tmem, warp, p * 32), s);
       tmem_ld_wait();
-      if (live) {
+      if (by_box) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) set_tile_chunk(stage, 8192, i, p * 4 + j, pack8(s + 8 * j));
+      } else if (live) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst + p * 32)[j] = pack8(s + 8 * j);
       }
+    }
+  }
+  if (by_box) {
+    fence_async_smem();
+    __syncthreads();
+    if (tid == 0 && ok) {
+      tma_store_tile128(&maps.w_out, hv * kDim, start, sbase + WySmem::kQ, 8192);
+      tma_store_tile128(&maps.u_out, hv * kDim, start, sbase + WySmem::kK, 8192);
+      tma_store_commit();
+      tma_store_wait_read();  // the tiles must outlive the copies' reads; this thread keeps the CTA alive until then
     }
   }
   if (!ok && tid == 0) atomicExch(status, kDevWaitTimeout | (1 << 8));
@@ -849,6 +877,8 @@ int mek_gdn_wy_fwd(const MekGdnDims* d, const void* q, const void* k, const void
   if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_qk_heads, "wy_fwd", d->qk_pitch)) return rc;
   if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_qk_heads, "wy_fwd", d->qk_pitch)) return rc;
   if (int rc = make_rows_map(&maps.v, v, d->total_tokens, d->num_v_heads, "wy_fwd", d->v_pitch)) return rc;
+  if (int rc = make_rows_map(&maps.w_out, w_out, d->total_tokens, d->num_v_heads, "wy_fwd")) return rc;
+  if (int rc = make_rows_map(&maps.u_out, u_out, d->total_tokens, d->num_v_heads, "wy_fwd")) return rc;
   gdn_wy_kernel<<<dim3(d->num_chunks, d->num_v_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
       maps, beta, g_cs, static_cast<__nv_bfloat16*>(a_out), static_cast<__nv_bfloat16*>(aqk_out),
       static_cast<__nv_bfloat16*>(w_out), static_cast<__nv_bfloat16*>(u_out), d->chunk_start, d->chunk_len,
