@@ -24,7 +24,7 @@ namespace mek {
 struct TailSmem {
   static constexpr uint32_t kQK = 0;                   // 2 x {[64][128] q, [64][128] k}: one buffer per (chunk, key head)
   static constexpr uint32_t kQKStride = 32768;
-  static constexpr uint32_t kH = 2 * kQKStride;        // [128][128] h_tape; after phase A: dw at +0
+  static constexpr uint32_t kH = 2 * kQKStride;        // [128][128] h_tape; after phase A: dw at +0, dv at +16384
   static constexpr uint32_t kDH = kH + 32768;          // [128][128] dh_tape
   static constexpr uint32_t kDO = kDH + 32768;         // [64][128] do; after phase A: u
   static constexpr uint32_t kVN = kDO + 16384;         // [64][128] v_new; after phase A: w
@@ -34,12 +34,13 @@ struct TailSmem {
   static constexpr uint32_t kAqk = kA + 8192;          // [64][64] Aqk
   static constexpr uint32_t kB8 = kAqk + 8192;         // [64][64] dS, then bf16(beta dL D)
   static constexpr uint32_t kScal = kB8 + 8192;        // floats: beta[2][64], g2[2][64], cs[2][4][64], red[8][64],
-                                                       //         red2[8][64], warp[16 + 1]
-  static constexpr uint32_t kBytes = kScal + (2 * 64 * 2 + 2 * 4 * 64 + 16 * 64 + 32) * 4;
+                                                       //         red2[8][64], warp[16 + 1], rs[2][4][64]
+  static constexpr uint32_t kBytes = kScal + (2 * 64 * 2 + 2 * 4 * 64 + 16 * 64 + 32 + 2 * 4 * 64) * 4;
 };
 
 // Threads: kTailGroups warpgroups.  Warps w, w + 4, ... share the accumulator rows 16 (w % 4) .. + 15; a thread owns
-// kTailW columns of its row in every accumulator.
+// kTailW columns of its row in every 128-wide accumulator.  The 64-wide ones (dAqk, Y, k k^T: lanes 0..15 of a
+// quadrant) are read in the 16-lane fragment shape instead, so that all 32 threads of a warp share their elements.
 constexpr int kTailThreads = 512;
 constexpr int kTailGroups = kTailThreads / 128;  // warpgroups
 constexpr int kTailW = 64 / kTailGroups;         // columns of a thread's piece
@@ -88,6 +89,7 @@ struct TailMaps {
   CUtensorMap v, d_o, v_new, dv_new, w, u;  // rows [tokens, HV * 128], box 64 x 64
   CUtensorMap h, dh;                     // tiles [num_tiles * 128, 128], box 64 x 128
   CUtensorMap a, aqk;                    // tiles [num_tiles * 64, 64], box 64 x 64
+  CUtensorMap dv_out;                    // rows [tokens, HV * 128] of the gradient, box 64 x 64, written
 };
 
 __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
@@ -120,6 +122,9 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
   const int cq = lh * kTailGroups + ch;    // which piece of a 128-wide accumulator
   const int lcol = lh * 64 + ch * kTailW;  // its first logical column
   const int lchunk = lcol >> 3;        // ... as a 16-byte chunk index of a tile row
+  // A 64-wide accumulator (lanes 0..15 of each quadrant) is read by the whole warp: the warp (quad, ch) takes its 16
+  // rows x 16 columns, a thread the rows fr and fr + 8 at the columns fc + 8 i + {0, 1}.
+  const int fr = quad * 16 + (lane >> 2), fq = lane & 3, fc = ch * 16 + fq * 2;
 
   float* s_beta = reinterpret_cast<float*>(sm + TailSmem::kScal);  // [2][64]
   float* s_g2 = s_beta + 128;                                      // [2][64]
@@ -127,6 +132,7 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
   float* s_red = s_cs + 512;                                       // [kTailPieces][64]
   float* s_red2 = s_red + 512;                                     // [kTailPieces][64]
   float* s_warp = s_red2 + 512;                                    // [warps + 1]
+  float* s_rs = s_warp + 32;                                       // [2][4][64] partial row sums per column piece
   Abort abort{&abort_flag};
 
   if (tid == 0) {
@@ -258,30 +264,33 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
     umma_gemm_pair<64, 64>(tmem + col, a, a_mn, b, b_mn, kdim, accumulate, neg_a, tmem + col + kUpperLanes, a, a_mn,
                            b_hi, b_mn, kdim, accumulate, neg_a);
   };
-  // column sums of a [64 x 64] matrix held one 32-column row piece per owner thread: a butterfly over the 16 rows of
-  // the warp that halves the columns a lane carries at every step (30 shuffles instead of 128), then one partial per
-  // quadrant (summed after the next block barrier).  The order of the additions is fixed.
-  auto publish_column_sums = [&](float* piece, float* where) {
-    float x[kTailW];
-#pragma unroll
-    for (int j = 0; j < kTailW; ++j) x[j] = owner ? piece[j] : 0.f;
-    const int l16 = lane & 15;
-#pragma unroll
-    for (int width = kTailW / 2, m = 8; m >= 1; width >>= 1, m >>= 1) {
-      const bool up = (l16 & m) != 0;  // this lane keeps the upper half of the columns it still carries
-#pragma unroll
-      for (int j = 0; j < width; ++j) {
-        const float mine = up ? x[j + width] : x[j], send = up ? x[j] : x[j + width];
-        x[j] = mine + __shfl_xor_sync(0xffffffffu, send, m);
-      }
-    }
-    // lane l16 now holds, over the warp's 16 rows, the sums of the kTailW / 16 columns its butterfly path spells:
-    // bit 3 of l16 chose the half, bit 2 the quarter, ... -- the columns l16 (kTailW / 16) ...
-    if (lane < 16) {
-#pragma unroll
-      for (int j = 0; j < kTailW / 16; ++j) where[quad * 64 + ch * kTailW + l16 * (kTailW / 16) + j] = x[j];
+  // Row and column sums of a [64 x 64] matrix held as fragments.  rows[0], rows[1]: this thread's part of the rows
+  // fr, fr + 8 -> the piece's row sums (four lanes share a row); cols[4]: its part of four columns, both rows added
+  // -> the quadrant's column sums (eight lanes share a column).  Fixed order.
+  auto publish_fragment_rows = [&](float lo, float hi, float* where) {
+    lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+    hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+    lo += __shfl_xor_sync(0xffffffffu, lo, 2);
+    hi += __shfl_xor_sync(0xffffffffu, hi, 2);
+    if (fq == 0) {
+      where[ch * 64 + fr] = lo;
+      where[ch * 64 + fr + 8] = hi;
     }
   };
+  auto publish_fragment_columns = [&](float* cols, float* where) {
+#pragma unroll
+    for (int m = 4; m <= 16; m <<= 1)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) cols[j] += __shfl_xor_sync(0xffffffffu, cols[j], m);
+    if (lane < 4) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        where[quad * 64 + fc + 8 * i] = cols[2 * i];
+        where[quad * 64 + fc + 8 * i + 1] = cols[2 * i + 1];
+      }
+    }
+  };
+  auto four = [](const float* p, int row) { return (p[row] + p[64 + row]) + (p[128 + row] + p[192 + row]); };
 
   // scaled terms of this thread's (row, column piece) that cannot accumulate in tensor memory, summed over the
   // group: dq gets qscale (do h^T); dk gets rowscale (v_new dh^T) and beta 2^G dkb
@@ -364,27 +373,34 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
       mma_wait2();
       __syncthreads();  // every thread is past its reads of h / dh: epilogue A overwrites operand buffers
       {
-        // dAqk piece (lanes 0..15): dS, P = dAqk . Aqk
-        float s[kTailW];
-        tail_tmem_ld(tmem_addr(tmem, warp, kColTa + ch * kTailW), s);
+        // dAqk: dS = bf16(scale dAqk D) to its tile, P = dAqk . Aqk to the gate gradient (row sums - column sums)
+        float s[8];
+        tmem_ld_frag16(tmem_addr(tmem, warp, kColTa + ch * 16), s);
+        const float g_lo = g2[fr], g_hi = g2[fr + 8];
         tmem_ld_wait();
-        float rowsum = 0.f;
+        float rows[2] = {0.f, 0.f}, cols[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int jj = 0; jj < kTailJ; ++jj) {
-          float aq[8], ds[8];
-          unpack8(tile_chunk(sm + TailSmem::kAqk, 8192, row, ch * kTailJ + jj), aq);
+        for (int i = 0; i < 2; ++i) {
+          const int col = fc + 8 * i;
+          const float2 gc = *reinterpret_cast<const float2*>(g2 + col);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int col = ch * kTailW + jj * 8 + e;
-            const float d = col <= row ? s[jj * 8 + e] : 0.f;
-            ds[e] = col <= row ? scale * d * fast_exp2(gi_row - g2[col]) : 0.f;
-            s[jj * 8 + e] = d * aq[e];
-            rowsum += s[jj * 8 + e];
+          for (int h = 0; h < 2; ++h) {
+            const int r = fr + 8 * h;
+            const float g_r = h ? g_hi : g_lo;
+            const uint32_t at = sw128_offset(r, ch * 2 + i) + fq * 4;
+            const float2 aq = unpack_bf16(*reinterpret_cast<const uint32_t*>(sm + TailSmem::kAqk + at));
+            const float d0 = col <= r ? s[4 * i + 2 * h] : 0.f, d1 = col + 1 <= r ? s[4 * i + 2 * h + 1] : 0.f;
+            const float ds0 = col <= r ? scale * d0 * fast_exp2(g_r - gc.x) : 0.f;
+            const float ds1 = col + 1 <= r ? scale * d1 * fast_exp2(g_r - gc.y) : 0.f;
+            *reinterpret_cast<uint32_t*>(sm + TailSmem::kB8 + at) = pack_bf16(ds0, ds1);
+            const float p0 = d0 * aq.x, p1 = d1 * aq.y;
+            rows[h] += p0 + p1;
+            cols[2 * i] += p0;
+            cols[2 * i + 1] += p1;
           }
-          if (owner) set_tile_chunk(sm + TailSmem::kB8, 8192, row, ch * kTailJ + jj, pack8(ds));
         }
-        if (owner) dG += rowsum;
-        publish_column_sums(s, s_cs);
+        publish_fragment_rows(rows[0], rows[1], s_rs);
+        publish_fragment_columns(cols, s_cs);
       }
       {
         // dkh and dq2 pieces: the scaled terms go to the register accumulators, their row dots to the gate gradient
@@ -417,7 +433,6 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
         tail_tmem_ld(tmem_addr(tmem, warp, kColT3 + ch * kTailW), y);
         tmem_ld_wait();
         float dot_v = 0.f;
-        __nv_bfloat16* dv_row = dv + int64_t(start + row) * dv_pitch + hv * kDim + lcol;
         uint4 vraw[kTailJ];
 #pragma unroll
         for (int jj = 0; jj < kTailJ; ++jj) vraw[jj] = tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj);
@@ -431,7 +446,7 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
             dot_v = fmaf(y[jj * 8 + e], vv[e], dot_v);
             out[e] = y[jj * 8 + e] * beta_row;
           }
-          if (live) reinterpret_cast<uint4*>(dv_row)[jj] = pack8(out);
+          set_tile_chunk(sm + TailSmem::kH + 16384, 8192, row, lchunk + jj, pack8(out));
           set_tile_chunk(sm + TailSmem::kH, 8192, row, lchunk + jj, pack8(wv + jj * 8));
         }
         dB += dot_v;
@@ -440,8 +455,16 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
         for (int jj = 0; jj < kTailJ; ++jj) set_tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj, pack8(y + jj * 8));
       }
       stage_sync();
+      // dv leaves from its tile (the upper half of the h region) by one bulk store; a ragged chunk's rows by hand.
       // do and v_new are done with: this value head's u and w take their buffers; then the next item's Aqk
+      if (len < kChunk)
+        store_tile<64, 128, kTailThreads>(sm + TailSmem::kH + 16384, 8192, dv + int64_t(start) * dv_pitch + hv * kDim,
+                                          dv_pitch, len, tid);
       if (loader) {
+        if (len == kChunk) {
+          tma_store_tile128(&maps.dv_out, hv * kDim, start, sbase + TailSmem::kH + 16384, 8192);
+          tma_store_commit();
+        }
         load_uw(it);
         if (has_next) load_aqk(nx);
       }
@@ -457,7 +480,7 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
         gemm128(kColT0, op_a, true, op_dw, true, 64, false);
         umma_commit(&bar2);
       }
-      if (owner && ch == 0) dG -= s_cs[row] + s_cs[64 + row] + s_cs[128 + row] + s_cs[192 + row];
+      if (owner && ch == 0) dG += four(s_rs, row) - four(s_cs, row);
       mma_wait2();
       {
         float dkb[kTailW];
@@ -486,7 +509,10 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
         clear_tile_rows<kTailThreads>(sm + TailSmem::kVN, len, tid);
       }
       stage_sync();
-      if (has_next && loader) load_states(nx);  // h / dh (and the dw tile) and A are done with
+      if (has_next && loader) {  // h / dh (and the dw tile) and A are done with, once the dv tile has been read
+        tma_store_wait_read();
+        load_states(nx);
+      }
 
       // ---- phase C: Y = bf16(dkb) w^T + bf16(dvb) u^T ; KK = k k^T ---------------------------------------------------
       if (issuer) {
@@ -501,49 +527,49 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
       }
       mma_wait2();
       {
-        float s[kTailW], kk[kTailW];
-        {
-          float s2[kTailW];
-          tail_tmem_ld(tmem_addr(tmem, warp, kColTa + ch * kTailW), s);
-          tail_tmem_ld(tmem_addr(tmem, warp, kColT1 + ch * kTailW), s2);
-          tail_tmem_ld(tmem_addr(tmem, warp, kColTb + ch * kTailW), kk);
-          tmem_ld_wait();
+        // dL = bf16(-tril(Y, -1)); bf16(beta dL D) to its tile; dL D . KK to the beta gradient (row sums) and
+        // beta dL D . KK to the gate gradient (row sums - column sums)
+        float s[8], s2[8], kk[8];
+        tmem_ld_frag16(tmem_addr(tmem, warp, kColTa + ch * 16), s);
+        tmem_ld_frag16(tmem_addr(tmem, warp, kColT1 + ch * 16), s2);
+        tmem_ld_frag16(tmem_addr(tmem, warp, kColTb + ch * 16), kk);
+        const float g_lo = g2[fr], g_hi = g2[fr + 8], b_lo = beta_s[fr], b_hi = beta_s[fr + 8];
+        tmem_ld_wait();
+        float rows[2] = {0.f, 0.f}, dots[2] = {0.f, 0.f}, cols[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int j = 0; j < kTailW; ++j) s[j] += s2[j];
-        }
-        float rowsum = 0.f, dot = 0.f;
+        for (int i = 0; i < 2; ++i) {
+          const int col = fc + 8 * i;
+          const float2 gc = *reinterpret_cast<const float2*>(g2 + col);
 #pragma unroll
-        for (int jj = 0; jj < kTailJ; ++jj) {
-          float out[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int col = ch * kTailW + jj * 8 + e;
-            const float dl = col < row ? round_bf16(-s[jj * 8 + e]) : 0.f;
-            const float dld = col < row ? dl * fast_exp2(gi_row - g2[col]) : 0.f;
-            const float kij = col < row ? kk[jj * 8 + e] : 0.f;
-            dot = fmaf(dld, kij, dot);
-            out[e] = beta_row * dld;
-            s[jj * 8 + e] = out[e] * kij;  // dL . L
-            rowsum += s[jj * 8 + e];
+          for (int h = 0; h < 2; ++h) {
+            const int r = fr + 8 * h, e = 4 * i + 2 * h;
+            const float g_r = h ? g_hi : g_lo, b_r = h ? b_hi : b_lo;
+            const bool in0 = col < r, in1 = col + 1 < r;
+            const float dld0 = in0 ? round_bf16(-(s[e] + s2[e])) * fast_exp2(g_r - gc.x) : 0.f;
+            const float dld1 = in1 ? round_bf16(-(s[e + 1] + s2[e + 1])) * fast_exp2(g_r - gc.y) : 0.f;
+            const float k0 = in0 ? kk[e] : 0.f, k1 = in1 ? kk[e + 1] : 0.f;
+            dots[h] = fmaf(dld1, k1, fmaf(dld0, k0, dots[h]));
+            const float out0 = b_r * dld0, out1 = b_r * dld1;
+            *reinterpret_cast<uint32_t*>(sm + TailSmem::kB8 + sw128_offset(r, ch * 2 + i) + fq * 4) =
+                pack_bf16(out0, out1);
+            const float p0 = out0 * k0, p1 = out1 * k1;  // dL . L
+            rows[h] += p0 + p1;
+            cols[2 * i] += p0;
+            cols[2 * i + 1] += p1;
           }
-          if (owner) set_tile_chunk(sm + TailSmem::kB8, 8192, row, ch * kTailJ + jj, pack8(out));
         }
-        if (owner) {
-          dB += dot;
-          dG += rowsum;
-        }
-        publish_column_sums(s, s_cs + 256);
+        publish_fragment_rows(rows[0], rows[1], s_rs);  // phase B has read dAqk's
+        publish_fragment_rows(dots[0], dots[1], s_rs + 256);
+        publish_fragment_columns(cols, s_cs + 256);
       }
       stage_sync();
       if (has_next && loader) load_row_tiles(nx);  // w, u, bf16(dkb), bf16(dvb) are done with
 
       // ---- phase D: dk += bf16(beta dL D) k + bf16(beta dL D)^T k ------------------------------------------------
-      if (issuer) {
-        gemm128(kColDK, op_b8, false, op_k, true, 64, true);
-        gemm128(kColDK, op_b8, true, op_k, true, 64, true);
-        if (last_of_pair) umma_commit(&bar);  // otherwise the next item's first commit covers these too
+      if (owner && ch == 0) {
+        dG += four(s_rs, row) - four(s_cs + 256, row);
+        dB += four(s_rs + 256, row);
       }
-      if (owner && ch == 0) dG -= s_cs[256 + row] + s_cs[320 + row] + s_cs[384 + row] + s_cs[448 + row];
       // gate and beta gradients of this value head: combine the column quarters, add the chunk-end term, suffix sum
       float part = fmaf(fast_exp2(g_last), hdh, gdot);
 #pragma unroll
@@ -551,13 +577,23 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
       if (lane == 0) s_warp[warp] = part;
       s_red[cq * 64 + row] = dG;
       s_red2[cq * 64 + row] = dB;
-      __syncthreads();
-      // warps 0 and 1: the in-chunk suffix sum of the gate gradient as two warp scans joined by the upper total
-      float suffix = 0.f;
-      if (tid < 64) {
-        if (tid < len) {
-          suffix = tail_row_sum(s_red, tid);
-          if (tid == len - 1) {
+      // Everybody's partial sums are out: the warps 2 and 3 wait for them and finish the sums; nobody else waits (the
+      // thread that issues phase D least of all: its instructions take it several hundred cycles).
+      const bool reducer = warp == 2 || warp == 3;
+      if (reducer) asm volatile("bar.sync 1, %0;" ::"n"(kTailThreads) : "memory");
+      else asm volatile("bar.arrive 1, %0;" ::"n"(kTailThreads) : "memory");
+      if (issuer) {
+        gemm128(kColDK, op_b8, false, op_k, true, 64, true);
+        gemm128(kColDK, op_b8, true, op_k, true, 64, true);
+        if (last_of_pair) umma_commit(&bar);  // otherwise the next item's first commit covers these too
+      }
+      if (reducer) {
+        // the in-chunk suffix sum of the gate gradient as two warp scans joined by the upper total
+        const int r = tid - 64;
+        float suffix = 0.f;
+        if (r < len) {
+          suffix = tail_row_sum(s_red, r);
+          if (r == len - 1) {
             float gamma_dot = 0.f;
 #pragma unroll
             for (int wv = 0; wv < kTailThreads / 32; ++wv) gamma_dot += s_warp[wv];
@@ -569,13 +605,13 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
           const float other = __shfl_down_sync(0xffffffffu, suffix, m);
           if (lane + m < 32) suffix += other;
         }
-        if (tid == 32) s_warp[kTailThreads / 32] = suffix;  // the total of rows 32..63
-      }
-      __syncthreads();
-      if (tid < len) {
-        if (tid < 32) suffix += s_warp[kTailThreads / 32];
-        dg[int64_t(start + tid) * num_v_heads + hv] = suffix;
-        dbeta[int64_t(start + tid) * num_v_heads + hv] = tail_row_sum(s_red2, tid);
+        if (r == 32) s_warp[kTailThreads / 32] = suffix;  // the total of rows 32..63
+        asm volatile("bar.sync 2, 64;" ::: "memory");
+        if (r < len) {
+          if (r < 32) suffix += s_warp[kTailThreads / 32];
+          dg[int64_t(start + r) * num_v_heads + hv] = suffix;
+          dbeta[int64_t(start + r) * num_v_heads + hv] = tail_row_sum(s_red2, r);
+        }
       }
 
       if (last_of_pair) {
@@ -635,6 +671,7 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
     }
   }
   cp_async_wait_pending<0>();
+  if (loader) tma_store_wait_all();
   if (abort.raised()) {  // copies of the next item may still be in flight: give them time to land before the CTA ends
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 100000ull) {
@@ -687,6 +724,7 @@ extern "C" int mek_gdn_bwd_tail(const MekGdnDims* d, const void* q, const void* 
       {&maps.w, w, tokens, v_cols, 64, 0},                      {&maps.u, u, tokens, v_cols, 64, 0},
       {&maps.h, h_tape, tiles * 128, 128, 128, 0},              {&maps.dh, dh_tape, tiles * 128, 128, 128, 0},
       {&maps.a, a, tiles * 64, 64, 64, 0},                      {&maps.aqk, aqk, tiles * 64, 64, 64, 0},
+      {&maps.dv_out, dv, tokens, v_cols, 64, uint64_t(d->dv_pitch)},
   };
   for (const auto& m : wanted)
     if (int rc = make_tile_map(m.map, m.base, m.rows, m.cols, m.box_rows, "bwd_tail", m.pitch)) return rc;

@@ -130,6 +130,17 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float* v) {
                : "memory");
 }
 
+// 16 lanes x 16 columns shared by the whole warp (shape 16x256b, twice): thread t receives the rows t / 4 and
+// t / 4 + 8 of the lanes the address names, at the columns 8 i + 2 (t % 4) + {0, 1}, i = 0, 1:
+//   v[4 i + 0], v[4 i + 1]  row t / 4;   v[4 i + 2], v[4 i + 3]  row t / 4 + 8.
+__device__ __forceinline__ void tmem_ld_frag16(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
