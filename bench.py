@@ -216,10 +216,10 @@ KERNEL_BYTES.update({
 # was timed; a head configuration that was never captured reports null.
 NCU_TRAFFIC_BYTES_PER_TOKEN = {
     (16, 32): {  # an 8,192-token cut of cfg1
-        "gdn_wy_fwd": (136.9e6 + 149.2e6) / 8192,
-        "gdn_fwd_ho": (237.5e6 + 225.8e6) / 8192,
-        "gdn_bwd_dh": (237.4e6 + 154.6e6) / 8192,
-        "gdn_bwd_tail": (807.5e6 + 122.8e6) / 8192,
+        "gdn_wy_fwd": (137.0e6 + 151.6e6) / 8192,
+        "gdn_fwd_ho": (236.2e6 + 225.8e6) / 8192,
+        "gdn_bwd_dh": (236.0e6 + 154.8e6) / 8192,
+        "gdn_bwd_tail": (807.8e6 + 123.9e6) / 8192,
     },
 }
 KERNEL_FLOPS = {  # per (chunk, value head): dense contractions as 2 m n k
