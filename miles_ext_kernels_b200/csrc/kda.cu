@@ -13,7 +13,8 @@
 //                   the gate at the block's first row, on it pair by pair (every exponent is formed from a
 //                   non-positive difference: finite for any gate); then A = (I + L)^-1, w = A (beta kg),
 //                   u = A (beta v)                                                          [tcgen05 + CUDA cores]
-//   kda_tail_mma    the state-side gradient contractions of one (chunk, head)               [tcgen05]
+//   kda_tail_mma    the state-side gradient contractions, persistent over the (chunk, head) items, computed
+//                   transposed (channel = accumulator row) so that its fp32 results leave in whole lines      [tcgen05]
 //   kda_tail_pair   the decayed gradient contractions (the same split: tensor core below the block diagonal,
 //                   running products on it), dq, dk and the per-channel gate gradient with its in-chunk suffix
 //                   sum                                                                     [tcgen05 + CUDA cores]
@@ -425,91 +426,123 @@ __global__ void __launch_bounds__(kIntraThreads, 2) kda_intra_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// tail, tensor-core part: one CTA per (chunk, head)
+// tail, tensor-core part: persistent, one CTA per SM walks the (chunk, head) items
 // ---------------------------------------------------------------------------------------------------------------
+// Everything the decayed part reads per key channel (dqg, dkr, dkg, hdh) is computed TRANSPOSED, channel = accumulator
+// row = tensor-memory lane = thread, so that a warp writes 32 consecutive channels of one token: whole 128-byte
+// lines.  The factors beta and scale are applied to the fp32 results instead of to bf16 operands:
+//   phase 1  dqg^T = h do^T        dkr^T = dh v_new^T      dw^T = -h dv_new^T      (128 x 64, K = 128)
+//            dAqk  = do v_new^T    (64 x 64)               dvb^T = dv_new^T A      (128 x 64, K = 64)
+//   phase 2  dkgb^T = dw^T A       (128 x 64, K = 64)      dAu = dw kg^T + dv_new v^T   (64 x 64; dA = dAu diag(beta))
+//   phase 3  Xu = A^T dAu          -> dbeta = diag(Xu) (= sum_d dkgb kg + sum_v dvb v), X = bf16(Xu diag(beta))
+//   phase 4  Y = X A^T             -> M2 = bf16(-tril(Y, -1))
+// The next item's tiles arrive by TMA while the current one computes: the state tiles, do and v_new are free as soon
+// as phase 1's products are done, dv_new and A are double-buffered, kg and v follow when phase 2's products are done.
 struct KdaTailSmem {
-  static constexpr uint32_t kH = 0;                    // [128][128] h; later DW at +0, KB at +16384
-  static constexpr uint32_t kDH = 32768;               // [128][128] dh; later VB at +0
+  static constexpr uint32_t kH = 0;                    // [128][128] h
+  static constexpr uint32_t kDH = 32768;               // [128][128] dh
   static constexpr uint32_t kDO = 65536;               // [64][128] do
-  static constexpr uint32_t kDOS = kDO + 16384;        // [64][128] bf16(scale do)
-  static constexpr uint32_t kVN = kDOS + 16384;        // [64][128] v_new
-  static constexpr uint32_t kDVN = kVN + 16384;        // [64][128] dv_new
-  static constexpr uint32_t kKG = kDVN + 16384;        // [64][128] kg
+  static constexpr uint32_t kVN = kDO + 16384;         // [64][128] v_new
+  static constexpr uint32_t kDVN = kVN + 16384;        // 2 x [64][128] dv_new
+  static constexpr uint32_t kKG = kDVN + 2 * 16384;    // [64][128] kg
   static constexpr uint32_t kV = kKG + 16384;          // [64][128] v
-  static constexpr uint32_t kA = kV + 16384;           // [64][64] A
-  static constexpr uint32_t kDA = kA + 8192;           // [64][64] dA
-  static constexpr uint32_t kX = kDA + 8192;           // [64][64] X = A^T dA
-  static constexpr uint32_t kScal = kX + 8192;         // beta[64], red[2][64]
-  static constexpr uint32_t kBytes = kScal + 1024;
+  static constexpr uint32_t kA = kV + 16384;           // 2 x [64][64] A
+  static constexpr uint32_t kDW = kA + 2 * 8192;       // [128 channels][64 tokens] dw^T
+  static constexpr uint32_t kDA = kDW + 16384;         // [64][64] dAu
+  static constexpr uint32_t kX = kDA + 8192;           // [64][64] X
+  static constexpr uint32_t kScal = kX + 8192;         // beta[2][64]
+  static constexpr uint32_t kBytes = kScal + 512;
 };
 
-__global__ void __launch_bounds__(256) kda_tail_mma_kernel(
-    const __nv_bfloat16* __restrict__ v, const __nv_bfloat16* __restrict__ kg, const float* __restrict__ beta,
-    const __nv_bfloat16* __restrict__ a_in, const __nv_bfloat16* __restrict__ h_tape,
-    const __nv_bfloat16* __restrict__ dh_tape, const __nv_bfloat16* __restrict__ v_new,
-    const __nv_bfloat16* __restrict__ dv_new, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ m1,
+struct KdaTailMaps {
+  CUtensorMap d_o, v_new, dv_new, kg, v;  // rows [tokens, H * 128], box 64 x 64
+  CUtensorMap h, dh;                      // tiles [num_tiles * 128, 128], box 64 x 128
+  CUtensorMap a;                          // tiles [num_tiles * 64, 64], box 64 x 64
+};
+
+constexpr int kKdaTailThreads = 256;
+
+__global__ void __launch_bounds__(kKdaTailThreads) kda_tail_mma_kernel(
+    const __grid_constant__ KdaTailMaps maps, const float* __restrict__ beta, float* __restrict__ m1,
     float* __restrict__ m2, float* __restrict__ dqg, float* __restrict__ dkr, float* __restrict__ dkg,
     float* __restrict__ hdh, __nv_bfloat16* __restrict__ dv, float* __restrict__ dbeta_part,
-    const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len, int num_heads, float scale,
-    int32_t* __restrict__ status) {
+    const int32_t* __restrict__ chunk_start, const int32_t* __restrict__ chunk_len, int num_chunks, int num_heads,
+    float scale, int32_t* __restrict__ status) {
   extern __shared__ uint8_t raw[];
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar;        // tensor-core commits
+  __shared__ uint64_t bar_one;    // h, dh, do, v_new, dv_new, A of an item
+  __shared__ uint64_t bar_two;    // kg, v of an item
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = blockIdx.x, h = blockIdx.y;
-  const int start = chunk_start[c], len = chunk_len[c];
-  if (len <= 0) return;
-  const int quad = warp & 3, ch = warp >> 2;
-  const int row = quad * 16 + (lane & 15);
-  const bool owner = lane < 16;
-  const bool live = owner && row < len;
-  float* s_beta = reinterpret_cast<float*>(sm + KdaTailSmem::kScal);
-  float* s_red = s_beta + 64;
+  const bool issuer = tid == 0, loader = tid == 32;
+  const int quad = warp & 3, wg = warp >> 2;
+  // 128-row accumulators: this thread's row (a key or value channel) and its 32 of the 64 columns (tokens)
+  const int chan = quad * 32 + lane, tok0 = wg * 32;
+  // 64-row accumulators (lanes 0..15 of a quadrant), read in the 16-lane fragment shape: the rows fr, fr + 8 at
+  // the columns fc + 8 n + {0, 1}, n = 0..3
+  const int fr = quad * 16 + (lane >> 2), fq = lane & 3, fc = wg * 32 + fq * 2;
+  float* s_beta = reinterpret_cast<float*>(sm + KdaTailSmem::kScal);  // [2][64]
   Abort abort{&abort_flag};
   const int64_t stride = int64_t(num_heads) * kDim;
-  const int64_t tile = int64_t(c) * num_heads + h;
-  const int64_t rows = int64_t(start) * stride + h * kDim;
+  const int num_items = num_chunks * num_heads;
+  const uint32_t sbase = smem_u32(sm);
 
   if (tid == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar_one, 1);
+    mbar_init(&bar_two, 1);
     fence_mbar_init();
     abort_flag = 0;
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 512);
-  load_tile<128, 128, 256>(sm + KdaTailSmem::kH, 16384, h_tape + tile * 16384, 128, 128, tid);
-  load_tile<128, 128, 256>(sm + KdaTailSmem::kDH, 16384, dh_tape + tile * 16384, 128, 128, tid);
-  load_tile<64, 128, 256>(sm + KdaTailSmem::kDO, 8192, d_o + rows, stride, len, tid);
-  load_tile<64, 128, 256>(sm + KdaTailSmem::kVN, 8192, v_new + rows, stride, len, tid);
-  load_tile<64, 128, 256>(sm + KdaTailSmem::kDVN, 8192, dv_new + rows, stride, len, tid);
-  load_tile<64, 128, 256>(sm + KdaTailSmem::kKG, 8192, kg + rows, stride, len, tid);
-  load_tile<64, 128, 256>(sm + KdaTailSmem::kV, 8192, v + rows, stride, len, tid);
-  load_tile<64, 64, 256>(sm + KdaTailSmem::kA, 8192, a_in + tile * 4096, 64, 64, tid);
-  if (tid < 64) s_beta[tid] = tid < len ? beta[int64_t(start + tid) * num_heads + h] : 0.f;
-  __syncthreads();
-  for (int i = tid; i < 64 * 16; i += 256) {  // bf16(scale do)
-    const int r = i >> 4, cc = i & 15;
-    float x[8];
-    unpack8(tile_chunk(sm + KdaTailSmem::kDO, 8192, r, cc), x);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] *= scale;
-    set_tile_chunk(sm + KdaTailSmem::kDOS, 8192, r, cc, pack8(x));
-  }
-  fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t sbase = smem_u32(sm);
+
+  // an item is live when it exists and its chunk is not a pad chunk of a device-built table (pads come last)
+  auto item_live = [&](int it) { return it < num_items && chunk_len[it / num_heads] > 0; };
+  auto load_one = [&](int it, int buf) {  // loader thread
+    const int c = it / num_heads, hd = it % num_heads, start = chunk_start[c];
+    mbar_arrive_expect(&bar_one, 2 * 32768 + 3 * 16384 + 8192);
+    tma_load_tile128(sbase + KdaTailSmem::kH, 16384, &maps.h, 0, it * 128, &bar_one);
+    tma_load_tile128(sbase + KdaTailSmem::kDH, 16384, &maps.dh, 0, it * 128, &bar_one);
+    tma_load_tile128(sbase + KdaTailSmem::kDO, 8192, &maps.d_o, hd * kDim, start, &bar_one);
+    tma_load_tile128(sbase + KdaTailSmem::kVN, 8192, &maps.v_new, hd * kDim, start, &bar_one);
+    tma_load_tile128(sbase + KdaTailSmem::kDVN + buf * 16384, 8192, &maps.dv_new, hd * kDim, start, &bar_one);
+    tma_load_box(sbase + KdaTailSmem::kA + buf * 8192, &maps.a, 0, it * 64, &bar_one);
+  };
+  auto load_two = [&](int it) {
+    const int c = it / num_heads, hd = it % num_heads, start = chunk_start[c];
+    mbar_arrive_expect(&bar_two, 2 * 16384);
+    tma_load_tile128(sbase + KdaTailSmem::kKG, 8192, &maps.kg, hd * kDim, start, &bar_two);
+    tma_load_tile128(sbase + KdaTailSmem::kV, 8192, &maps.v, hd * kDim, start, &bar_two);
+  };
+  auto load_beta = [&](int it, int buf) {  // every thread calls; the first 64 copy
+    if (tid < 64) {
+      const int c = it / num_heads, hd = it % num_heads, len = chunk_len[c];
+      s_beta[buf * 64 + tid] = tid < len ? beta[int64_t(chunk_start[c] + tid) * num_heads + hd] : 0.f;
+    }
+  };
+
+  int item = blockIdx.x;
+  bool live = item_live(item);
+  if (live) {
+    if (loader) {
+      load_one(item, 0);
+      load_two(item);
+    }
+    load_beta(item, 0);
+  }
   const Operand op_h{sbase + KdaTailSmem::kH, 16384}, op_dh{sbase + KdaTailSmem::kDH, 16384};
-  const Operand op_dw{sbase + KdaTailSmem::kH, 8192}, op_kb{sbase + KdaTailSmem::kH + 16384, 8192};
-  const Operand op_vb{sbase + KdaTailSmem::kDH, 8192};
-  const Operand op_do{sbase + KdaTailSmem::kDO, 8192}, op_dos{sbase + KdaTailSmem::kDOS, 8192};
-  const Operand op_vn{sbase + KdaTailSmem::kVN, 8192}, op_dvn{sbase + KdaTailSmem::kDVN, 8192};
-  const Operand op_a{sbase + KdaTailSmem::kA, 8192}, op_da{sbase + KdaTailSmem::kDA, 8192};
+  const Operand op_do{sbase + KdaTailSmem::kDO, 8192}, op_vn{sbase + KdaTailSmem::kVN, 8192};
+  const Operand op_kg{sbase + KdaTailSmem::kKG, 8192}, op_v{sbase + KdaTailSmem::kV, 8192};
+  const Operand op_dw{sbase + KdaTailSmem::kDW, 16384}, op_da{sbase + KdaTailSmem::kDA, 8192};
   const Operand op_x{sbase + KdaTailSmem::kX, 8192};
-  constexpr uint32_t cAqk = 0, cDkr = 64, cDqg = 192, cDw = 320;
+  // tensor-memory columns
+  constexpr uint32_t cDqg = 0, cDkr = 64, cDw = 128, cDvb = 192, cAqk = 256, cDkg = 320, cDa = 384, cX = 448, cDa2 = 256, cY = 256;
 
   uint32_t phase = 0;
   auto mma_wait = [&]() {
@@ -524,159 +557,203 @@ __global__ void __launch_bounds__(256) kda_tail_mma_kernel(
     tc_fence_after();
   };
 
-  // ---- phase 1: dAqk = do v_new^T ; dkr = v_new dh^T ; dqg = (scale do) h^T ; dw = -dv_new h^T --------------------
-  if (tid == 0) {
-    // in alternating pairs: the instructions of one product wait for one another
-    umma_gemm_pair<64, 64, 128>(tmem + cAqk, op_do, false, op_vn, false, 128, false, false, tmem + cDkr, op_vn, false,
-                                op_dh, false, 128, false, false);
-    umma_gemm_pair<64, 128>(tmem + cDqg, op_dos, false, op_h, false, 128, false, false, tmem + cDw, op_dvn, false, op_h,
-                            false, 128, false, /*neg=*/true);
-    umma_commit(&bar);
-  }
-  if (tid < 128) {  // sum_v dh[k, v] h[k, v] per key channel
-    float acc = 0.f;
+  int parity = 0;
+  for (; live; item += gridDim.x, parity ^= 1) {
+    const int c = item / num_heads, hd = item % num_heads;
+    const int start = chunk_start[c], len = chunk_len[c];
+    const int next = item + gridDim.x;
+    const bool has_next = item_live(next);
+    const int64_t rows = int64_t(start) * stride + hd * kDim;
+    const int64_t tile = item;
+    const float* beta_s = s_beta + parity * 64;
+    uint8_t* dvn_tile = sm + KdaTailSmem::kDVN + parity * 16384;
+    const Operand op_dvn{sbase + KdaTailSmem::kDVN + parity * 16384, 8192};
+    const Operand op_a{sbase + KdaTailSmem::kA + parity * 8192, 8192};
+
+    if (!mbar_wait(&bar_one, parity)) abort.raise();
+    if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows
+      clear_tile_rows<kKdaTailThreads>(sm + KdaTailSmem::kDO, len, tid);
+      clear_tile_rows<kKdaTailThreads>(sm + KdaTailSmem::kVN, len, tid);
+      clear_tile_rows<kKdaTailThreads>(dvn_tile, len, tid);
+    }
+    stage_sync();
+    if (abort.raised()) break;
+    if (has_next) load_beta(next, parity ^ 1);
+
+    // ---- phase 1 -------------------------------------------------------------------------------------------------
+    if (issuer) {
+      umma_gemm_pair<128, 64>(tmem + cDqg, op_h, false, op_do, false, 128, false, false, tmem + cDkr, op_dh, false,
+                              op_vn, false, 128, false, false);
+      umma_gemm_pair<128, 64, 64>(tmem + cDw, op_h, false, op_dvn, false, 128, false, /*neg=*/true, tmem + cDvb, op_dvn,
+                                  true, op_a, true, 64, false, false);
+      umma_gemm<64, 64>(tmem + cAqk, op_do, false, op_vn, false, 128, false);
+      umma_commit(&bar);
+    }
+    if (tid < 128) {  // sum_v dh[k, v] h[k, v] per key channel
+      float acc = 0.f;
 #pragma unroll 4
-    for (int cc = 0; cc < 16; ++cc) {
-      float a[8], b[8];
-      unpack8(tile_chunk(sm + KdaTailSmem::kH, 16384, tid, cc), a);
-      unpack8(tile_chunk(sm + KdaTailSmem::kDH, 16384, tid, cc), b);
+      for (int cc = 0; cc < 16; ++cc) {
+        float a[8], b[8];
+        unpack8(tile_chunk(sm + KdaTailSmem::kH, 16384, tid, cc), a);
+        unpack8(tile_chunk(sm + KdaTailSmem::kDH, 16384, tid, cc), b);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc = fmaf(a[j], b[j], acc);
-    }
-    hdh[tile * kDim + tid] = acc;
-  }
-  mma_wait();
-  __syncthreads();  // every thread is past its reads of h / dh: their space takes dw, kb and vb
-  const float beta_row = s_beta[row];
-  {
-    float s[32];
-    tmem_ld32(tmem_addr(tmem, warp, cAqk + ch * 32), s);
-    tmem_ld_wait();
-    if (owner) {
-      float* dst = m1 + tile * 4096 + row * 64 + ch * 32;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) dst[j] = (ch * 32 + j <= row) ? scale * s[j] : 0.f;
-    }
-    float* dkr_row = dkr + rows + int64_t(row) * stride + ch * 64;
-    float* dqg_row = dqg + rows + int64_t(row) * stride + ch * 64;
-#pragma unroll
-    for (int p = 0; p < 2; ++p) {
-      float a[32], b[32], w[32];
-      tmem_ld32(tmem_addr(tmem, warp, cDkr + ch * 64 + p * 32), a);
-      tmem_ld32(tmem_addr(tmem, warp, cDqg + ch * 64 + p * 32), b);
-      tmem_ld32(tmem_addr(tmem, warp, cDw + ch * 64 + p * 32), w);
-      tmem_ld_wait();
-      if (live) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          reinterpret_cast<float4*>(dkr_row + p * 32)[j] = make_float4(a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3]);
-          reinterpret_cast<float4*>(dqg_row + p * 32)[j] = make_float4(b[4 * j], b[4 * j + 1], b[4 * j + 2], b[4 * j + 3]);
-        }
+        for (int j = 0; j < 8; ++j) acc = fmaf(a[j], b[j], acc);
       }
-      if (owner) {
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-          set_tile_chunk(sm + KdaTailSmem::kH, 8192, row, ch * 8 + p * 4 + jj, pack8(w + jj * 8));
-      }
+      hdh[tile * kDim + tid] = acc;
     }
-  }
-  for (int i = tid; i < 64 * 16; i += 256) {  // kb = bf16(beta kg), vb = bf16(beta v)
-    const int r = i >> 4, cc = i & 15;
-    const float b = s_beta[r];
-    float x[8];
-    unpack8(tile_chunk(sm + KdaTailSmem::kKG, 8192, r, cc), x);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] *= b;
-    set_tile_chunk(sm + KdaTailSmem::kH + 16384, 8192, r, cc, pack8(x));
-    unpack8(tile_chunk(sm + KdaTailSmem::kV, 8192, r, cc), x);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] *= b;
-    set_tile_chunk(sm + KdaTailSmem::kDH, 8192, r, cc, pack8(x));
-  }
-  stage_sync();
-
-  // ---- phase 2: dkgb = A^T dw ; dvb = A^T dv_new ; dA = dw kb^T + dv_new vb^T -------------------------------------
-  if (tid == 0) {
-    umma_gemm_pair<64, 128>(tmem + 0, op_a, true, op_dw, true, 64, false, false, tmem + 128, op_a, true, op_dvn, true, 64,
-                            false, false);
-    umma_gemm<64, 64>(tmem + 256, op_dw, false, op_kb, false, 128, false);
-    umma_gemm<64, 64>(tmem + 256, op_dvn, false, op_vb, false, 128, true);
-    umma_commit(&bar);
-  }
-  mma_wait();
-  {
-    float dot = 0.f;
-    float* dkg_row = dkg + rows + int64_t(row) * stride + ch * 64;
-    __nv_bfloat16* dv_row = dv + rows + int64_t(row) * stride + ch * 64;
-#pragma unroll
-    for (int p = 0; p < 2; ++p) {
+    mma_wait();
+    __syncthreads();  // the products and every thread's reads of h / dh are done: the next item's tiles may land
+    if (has_next && loader) load_one(next, parity ^ 1);
+    {
+      // dqg, dkr: 32 tokens of this thread's channel; a warp writes 32 consecutive channels of a token
       float a[32], b[32];
-      tmem_ld32(tmem_addr(tmem, warp, 0 + ch * 64 + p * 32), a);
-      tmem_ld32(tmem_addr(tmem, warp, 128 + ch * 64 + p * 32), b);
+      tmem_ld32(tmem_addr(tmem, warp, cDqg + tok0), a);
+      tmem_ld32(tmem_addr(tmem, warp, cDkr + tok0), b);
+      tmem_ld_wait();
+      float* dqg_col = dqg + rows + chan;
+      float* dkr_col = dkr + rows + chan;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (tok0 + j < len) {
+          dqg_col[int64_t(tok0 + j) * stride] = scale * a[j];
+          dkr_col[int64_t(tok0 + j) * stride] = b[j];
+        }
+      }
+      // dw^T -> its tile (row = channel); dvb^T -> dv = bf16(beta dvb)
+      tmem_ld32(tmem_addr(tmem, warp, cDw + tok0), a);
+      tmem_ld32(tmem_addr(tmem, warp, cDvb + tok0), b);
       tmem_ld_wait();
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        float kgv[8], vv[8], out[8], dk8[8];
-        unpack8(tile_chunk(sm + KdaTailSmem::kKG, 8192, row, ch * 8 + p * 4 + jj), kgv);
-        unpack8(tile_chunk(sm + KdaTailSmem::kV, 8192, row, ch * 8 + p * 4 + jj), vv);
+      for (int jj = 0; jj < 4; ++jj)
+        *reinterpret_cast<uint4*>(sm + KdaTailSmem::kDW + sw128_offset(chan, wg * 4 + jj)) = pack8(a + jj * 8);
+      __nv_bfloat16* dv_col = dv + rows + chan;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float x = a[jj * 8 + e], y = b[jj * 8 + e];
-          dot = fmaf(x, kgv[e], dot);
-          dot = fmaf(y, vv[e], dot);
-          dk8[e] = beta_row * x;
-          out[e] = beta_row * y;
-        }
-        if (live) {
-          reinterpret_cast<float4*>(dkg_row + p * 32)[2 * jj] = make_float4(dk8[0], dk8[1], dk8[2], dk8[3]);
-          reinterpret_cast<float4*>(dkg_row + p * 32)[2 * jj + 1] = make_float4(dk8[4], dk8[5], dk8[6], dk8[7]);
-          reinterpret_cast<uint4*>(dv_row + p * 32)[jj] = pack8(out);
+      for (int j = 0; j < 32; ++j)
+        if (tok0 + j < len) dv_col[int64_t(tok0 + j) * stride] = __float2bfloat16_rn(beta_s[tok0 + j] * b[j]);
+      // M1 = scale tril(dAqk)
+      float s[16];
+      tmem_ld_frag16(tmem_addr(tmem, warp, cAqk + wg * 32), s);
+      tmem_ld_frag16(tmem_addr(tmem, warp, cAqk + wg * 32 + 16), s + 8);
+      tmem_ld_wait();
+      float* m1_tile = m1 + tile * 4096;
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int col = fc + 8 * n;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int r = fr + 8 * hh;
+          const float x0 = col <= r ? scale * s[4 * n + 2 * hh] : 0.f, x1 = col + 1 <= r ? scale * s[4 * n + 2 * hh + 1] : 0.f;
+          *reinterpret_cast<float2*>(m1_tile + r * 64 + col) = make_float2(x0, x1);
         }
       }
     }
-    if (owner) s_red[ch * 64 + row] = dot;
-    float s[32];
-    tmem_ld32(tmem_addr(tmem, warp, 256 + ch * 32), s);
-    tmem_ld_wait();
-    if (owner) {
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) set_tile_chunk(sm + KdaTailSmem::kDA, 8192, row, ch * 4 + jj, pack8(s + jj * 8));
+    if (!mbar_wait(&bar_two, parity)) abort.raise();
+    if (len < kChunk) {
+      clear_tile_rows<kKdaTailThreads>(sm + KdaTailSmem::kKG, len, tid);
+      clear_tile_rows<kKdaTailThreads>(sm + KdaTailSmem::kV, len, tid);
     }
-  }
-  stage_sync();
-  if (tid < len) dbeta_part[int64_t(start + tid) * num_heads + h] = s_red[tid] + s_red[64 + tid];
+    stage_sync();
 
-  // ---- phase 3: X = A^T dA ------------------------------------------------------------------------------------------
-  if (tid == 0) {
-    umma_gemm<64, 64>(tmem + 320, op_a, true, op_da, true, 64, false);
-    umma_commit(&bar);
-  }
-  mma_wait();
-  {
-    float s[32];
-    tmem_ld32(tmem_addr(tmem, warp, 320 + ch * 32), s);
-    tmem_ld_wait();
-    if (owner) {
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) set_tile_chunk(sm + KdaTailSmem::kX, 8192, row, ch * 4 + jj, pack8(s + jj * 8));
+    // ---- phase 2 -------------------------------------------------------------------------------------------------
+    if (issuer) {
+      // dAu as two chains into two accumulators (the epilogue adds them): one chain's instructions wait for one another
+      umma_gemm_pair<64, 64>(tmem + cDa, op_dw, true, op_kg, false, 128, false, false, tmem + cDa2, op_dvn, false, op_v,
+                             false, 128, false, false);
+      umma_gemm<128, 64>(tmem + cDkg, op_dw, false, op_a, true, 64, false);
+      umma_commit(&bar);
     }
-  }
-  stage_sync();
-
-  // ---- phase 4: Y = X A^T ; dL = bf16(-tril(Y, -1)) -----------------------------------------------------------------
-  if (tid == 0) {
-    umma_gemm<64, 64>(tmem + 384, op_x, false, op_a, false, 64, false);
-    umma_commit(&bar);
-  }
-  mma_wait();
-  {
-    float s[32];
-    tmem_ld32(tmem_addr(tmem, warp, 384 + ch * 32), s);
-    tmem_ld_wait();
-    if (owner) {
-      float* dst = m2 + tile * 4096 + row * 64 + ch * 32;
+    mma_wait();
+    {
+      float a[32];
+      tmem_ld32(tmem_addr(tmem, warp, cDkg + tok0), a);
+      float s[16], s2[16];
+      tmem_ld_frag16(tmem_addr(tmem, warp, cDa + wg * 32), s);
+      tmem_ld_frag16(tmem_addr(tmem, warp, cDa + wg * 32 + 16), s + 8);
+      tmem_ld_frag16(tmem_addr(tmem, warp, cDa2 + wg * 32), s2);
+      tmem_ld_frag16(tmem_addr(tmem, warp, cDa2 + wg * 32 + 16), s2 + 8);
+      tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) dst[j] = (ch * 32 + j < row) ? round_bf16(-s[j]) : 0.f;
+      for (int j = 0; j < 16; ++j) s[j] += s2[j];
+      float* dkg_col = dkg + rows + chan;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (tok0 + j < len) dkg_col[int64_t(tok0 + j) * stride] = beta_s[tok0 + j] * a[j];
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int col = fc + 8 * n;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int r = fr + 8 * hh;
+          *reinterpret_cast<uint32_t*>(sm + KdaTailSmem::kDA + sw128_offset(r, col >> 3) + (col & 7) * 2) =
+              pack_bf16(s[4 * n + 2 * hh], s[4 * n + 2 * hh + 1]);
+        }
+      }
+    }
+    stage_sync();
+    if (has_next && loader) load_two(next);  // kg and v are done with
+
+    // ---- phase 3: Xu = A^T dAu -------------------------------------------------------------------------------------
+    if (issuer) {
+      umma_gemm<64, 64>(tmem + cX, op_a, true, op_da, true, 64, false);
+      umma_commit(&bar);
+    }
+    mma_wait();
+    {
+      float s[16];
+      tmem_ld_frag16(tmem_addr(tmem, warp, cX + wg * 32), s);
+      tmem_ld_frag16(tmem_addr(tmem, warp, cX + wg * 32 + 16), s + 8);
+      tmem_ld_wait();
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int col = fc + 8 * n;
+        const float b0 = beta_s[col], b1 = beta_s[col + 1];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int r = fr + 8 * hh;
+          const float x0 = s[4 * n + 2 * hh], x1 = s[4 * n + 2 * hh + 1];
+          if (col == r && r < len) dbeta_part[int64_t(start + r) * num_heads + hd] = x0;
+          if (col + 1 == r && r < len) dbeta_part[int64_t(start + r) * num_heads + hd] = x1;
+          *reinterpret_cast<uint32_t*>(sm + KdaTailSmem::kX + sw128_offset(r, col >> 3) + (col & 7) * 2) =
+              pack_bf16(b0 * x0, b1 * x1);
+        }
+      }
+    }
+    stage_sync();
+
+    // ---- phase 4: Y = X A^T ; M2 = bf16(-tril(Y, -1)) --------------------------------------------------------------
+    if (issuer) {
+      umma_gemm<64, 64>(tmem + cY, op_x, false, op_a, false, 64, false);
+      umma_commit(&bar);
+    }
+    mma_wait();
+    {
+      float s[16];
+      tmem_ld_frag16(tmem_addr(tmem, warp, cY + wg * 32), s);
+      tmem_ld_frag16(tmem_addr(tmem, warp, cY + wg * 32 + 16), s + 8);
+      tmem_ld_wait();
+      float* m2_tile = m2 + tile * 4096;
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int col = fc + 8 * n;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int r = fr + 8 * hh;
+          const float x0 = col < r ? round_bf16(-s[4 * n + 2 * hh]) : 0.f;
+          const float x1 = col + 1 < r ? round_bf16(-s[4 * n + 2 * hh + 1]) : 0.f;
+          *reinterpret_cast<float2*>(m2_tile + r * 64 + col) = make_float2(x0, x1);
+        }
+      }
+    }
+    live = has_next;
+    // the next item's phase 1 overwrites the accumulators this epilogue has just read, and its beta row replaces the
+    // one two items back: every thread must be past both
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  }
+  if (abort.raised()) {  // copies of the next item may still be in flight: give them time to land before the CTA ends
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 100000ull) {
     }
   }
   if (abort.raised() && tid == 0) atomicExch(status, kDevWaitTimeout | (7 << 8));
@@ -1204,13 +1281,32 @@ int mek_kda_bwd_tail(const MekGdnDims* d, const void* q, const void* k, const vo
   KdaPairMaps maps;
   if (int rc = make_rows_map(&maps.q, q, d->total_tokens, d->num_v_heads, "kda_bwd_tail")) return rc;
   if (int rc = make_rows_map(&maps.k, k, d->total_tokens, d->num_v_heads, "kda_bwd_tail")) return rc;
+  KdaTailMaps tail_maps;
+  const int64_t tiles = int64_t(d->num_chunks) * d->num_v_heads;
+  if (tiles * 128 > int64_t(INT32_MAX)) return fail(MEK_ERR_UNSUPPORTED, "kda_bwd_tail: %lld state tiles", (long long)tiles);
+  struct {
+    CUtensorMap* map;
+    const void* base;
+  } const row_maps[] = {{&tail_maps.d_o, d_o}, {&tail_maps.v_new, v_new}, {&tail_maps.dv_new, dv_new},
+                        {&tail_maps.kg, kg},   {&tail_maps.v, v}};
+  for (const auto& m : row_maps)
+    if (int rc = make_rows_map(m.map, m.base, d->total_tokens, d->num_v_heads, "kda_bwd_tail")) return rc;
+  if (int rc = make_tiles_map(&tail_maps.h, h_tape, tiles, 128, 128, "kda_bwd_tail")) return rc;
+  if (int rc = make_tiles_map(&tail_maps.dh, dh_tape, tiles, 128, 128, "kda_bwd_tail")) return rc;
+  if (int rc = make_tiles_map(&tail_maps.a, a, tiles, 64, 64, "kda_bwd_tail")) return rc;
   if (int rc = want_smem(kda_tail_mma_kernel, smem_a, "kda_bwd_tail")) return rc;
   if (int rc = want_smem(kda_tail_pair_kernel, smem_b, "kda_bwd_tail")) return rc;
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
+    cudaGetLastError();
+    return fail(MEK_ERR_CUDA, "kda_bwd_tail: cannot query the SM count");
+  }
   const dim3 grid(d->num_chunks, d->num_v_heads);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  kda_tail_mma_kernel<<<grid, 256, smem_a, s>>>(In(v), In(kg), beta, In(a), In(h_tape), In(dh_tape), In(v_new),
-                                                In(dv_new), In(d_o), m1, m2, dqg, dkr, dkg, hdh, Out(dv), dbeta_part,
-                                                d->chunk_start, d->chunk_len, d->num_v_heads, d->scale, status);
+  kda_tail_mma_kernel<<<tiles < sms ? int(tiles) : sms, kKdaTailThreads, smem_a, s>>>(
+      tail_maps, beta, m1, m2, dqg, dkr, dkg, hdh, Out(dv), dbeta_part, d->chunk_start, d->chunk_len, d->num_chunks,
+      d->num_v_heads, d->scale, status);
   if (int rc = launched("kda_bwd_tail (tensor-core part)")) return rc;
   kda_tail_pair_kernel<<<grid, 512, smem_b, s>>>(maps, g2, beta, m1, m2, dqg, dkr, dkg, hdh, dbeta_part, dq32, dk32, dg,
                                                  dbeta, d->chunk_start, d->chunk_len, d->num_v_heads, status);
