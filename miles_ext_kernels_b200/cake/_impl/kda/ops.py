@@ -210,13 +210,15 @@ def _forward(q, k, v, g, beta32, cu_seqlens, scale, use_qk_l2norm, *, cu_seqlens
         native.launch("gdn_l2norm", k_raw, k, rstd_k, S * H, H, 0, device=device)
     g2 = torch.empty((S, H, HEAD_DIM), dtype=F32, device=device)
     qg, kg, kr = (torch.empty_like(q) for _ in range(3))
-    gl2 = torch.zeros((NC, H, HEAD_DIM), dtype=F32, device=device)
+    # pad chunks of the device route are never written: their tiles must not hold NaN bit patterns
+    alloc = torch.empty if meta.exact else torch.zeros
+    gl2 = alloc((NC, H, HEAD_DIM), dtype=F32, device=device)
     native.launch("kda_prep", dims, q, k, g, g2, qg, kg, kr, gl2, device=device)
-    a = torch.zeros((NC, H, 64, 64), dtype=BF16, device=device)
-    aqk = torch.zeros((NC, H, 64, 64), dtype=BF16, device=device)
+    a = alloc((NC, H, 64, 64), dtype=BF16, device=device)
+    aqk = alloc((NC, H, 64, 64), dtype=BF16, device=device)
     w, u = torch.empty_like(v), torch.empty_like(v)
     native.launch("kda_intra", dims, q, k, v, kg, g2, beta32, a, aqk, w, u, status, device=device)
-    h = torch.zeros((NC, H, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
+    h = alloc((NC, H, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
     v_new = torch.empty_like(v)
     if state_provider is not None:
         h0 = state_provider(dims, meta, kr, w, u, gl2, status)
@@ -236,7 +238,10 @@ def _backward(s: Saved, v, beta32, do, *, dht=None, want_dh0=False, adjoint_prov
     NC = meta.num_chunks
     dims = dims_of(meta, H, H, s.scale)
     take = lambda role, shape, dtype: workspace.take(OP, role, shape, dtype, device)  # noqa: E731
-    dh = torch.zeros((NC, H, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)  # pad chunks are never written
+    if meta.exact:
+        dh = take("dh_tape", (NC, H, HEAD_DIM, HEAD_DIM), BF16)
+    else:  # pad chunks are never written
+        dh = torch.zeros((NC, H, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
     dv_new = take("dv_new", (S, H, HEAD_DIM), BF16)
     if adjoint_provider is not None:
         dht = adjoint_provider(dims, meta, s, do)
