@@ -763,7 +763,7 @@ __global__ void __launch_bounds__(kKdaTailThreads) kda_tail_mma_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// tail, decayed part: one block per (chunk, head); thread (d, role, half) owns key channel d
+// tail, decayed part: one block per (chunk, head); thread (d, quarter) owns key channel d
 // ---------------------------------------------------------------------------------------------------------------
 // With E_ij = 2^{G_i - G_j} per channel (j <= i), M1 = scale tril(do v_new^T) and M2 = bf16(-tril(A^T dA A^T, -1)):
 //   row pass     RQ_i = sum_{j<=i} M1_ij k_j E_ij,  RK_i = sum_{j<i} M2_ij k_j E_ij     -> dq, the row part of dk, dg
@@ -778,8 +778,8 @@ __global__ void __launch_bounds__(kKdaTailThreads) kda_tail_mma_kernel(
 //                                         -> CC_j = sum_{I > block(j)} 2^{G_{16 I} - G_j} PI^T[d][j]
 // The four 16 x 16 blocks on the diagonal are summed on CUDA cores, without an exponential per pair: E runs along a
 // row or a column as a product of the per-token factors R_i = 2^{G_i - G_{i-1}} <= 1; these sums run while the
-// tensor core works.  512 threads: thread (d, role, half) owns channel d in the row pass (role 0) or the column pass
-// (role 1) for the even (half 0) or odd (half 1) groups of four rows / columns.
+// tensor core works.  512 threads: thread (d, quarter) owns channel d for the groups of four rows AND of four columns
+// 4 quarter + 16 n: the row part and the column part of a (token, channel) pair meet in one thread.
 struct KdaPairSmem {
   static constexpr uint32_t kG = 0;                    // fp32 [64][128] G (log2); after the passes: per-row dg
   static constexpr uint32_t kR = 32768;                // fp32 [64][128] R; after the passes: the chunk-end terms
@@ -809,7 +809,7 @@ __global__ void __launch_bounds__(512) kda_tail_pair_kernel(
   __shared__ uint64_t bar, bar_load;
   __shared__ uint32_t tmem_slot;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
-  const int tid = threadIdx.x, d = tid & 127, role = (tid >> 7) & 1, half = tid >> 8, warp4 = (tid >> 5) & 3;
+  const int tid = threadIdx.x, d = tid & 127, quarter = tid >> 7, warp4 = (tid >> 5) & 3;
   const int warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, h = blockIdx.y;
   const int start = chunk_start[c], len = chunk_len[c];
@@ -822,7 +822,6 @@ __global__ void __launch_bounds__(512) kda_tail_pair_kernel(
   uint8_t* k_cvt = q_cvt + 16384;
   uint8_t* stack = sm + KdaPairSmem::kStack;
   uint8_t* ar = sm + KdaPairSmem::kAR;
-  float* sCC = reinterpret_cast<float*>(sm + KdaPairSmem::kAR);
   uint8_t* x1 = sm + KdaPairSmem::kX1;
   uint8_t* x2 = sm + KdaPairSmem::kX2;
   float* sM1d = reinterpret_cast<float*>(sm + KdaPairSmem::kMd);   // [4][16][20]
@@ -953,7 +952,7 @@ __global__ void __launch_bounds__(512) kda_tail_pair_kernel(
     umma_commit(&bar);
   }
   bool products_seen = false;
-  auto wait_products = [&]() {  // a whole warp at a time (a warp shares role and half, and so its trip counts)
+  auto wait_products = [&]() {  // a whole warp at a time (a warp shares its quarter, and so its trip counts)
     if (!products_seen) {
       ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0)) && ok;
       tc_fence_after();
@@ -967,19 +966,21 @@ __global__ void __launch_bounds__(512) kda_tail_pair_kernel(
   // a sum of terms that cancel along the chunk (sum_i q_i RQ_i = sum_j k_j CK_j term by term), so both passes form
   // their tensor-core parts from the SAME rounded factors (q~, beta k~', the stack, bf16 M): the terms still cancel
   // to fp32 accuracy, which exact factors on one side and rounded ones on the other would not.
-  float keep_a[32], keep_b[32];
+  // Every thread runs both passes for the groups of four rows / columns 4 quarter + 16 n, n = 0..3: it ends up
+  // holding the row part and the column part of the same 16 (token, channel) pairs.
+  float keep_a[16], keep_b[16], keep_c[16], keep_k[16], keep_db[16];
 #pragma unroll
-  for (int n = 0; n < 32; ++n) keep_a[n] = keep_b[n] = 0.f;
+  for (int n = 0; n < 16; ++n) keep_a[n] = keep_b[n] = keep_c[n] = keep_k[n] = keep_db[n] = 0.f;
   float chunk_end = 0.f;
-  if (role == 0) {
+  {
     // ---- row pass: four rows at a time.  For j below the group (inside the 16-block), E_{i0+r, j} = E_{i0, j}
     // E_{i0+r, i0}: the four rows share k_j E_{i0, j} and take their own factor (<= 1) once at the end; the 4 x 4
     // diagonal block is done apart; the earlier blocks come from the tensor core.
     const float gl = sG[(len - 1) * 128 + d];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const int i0 = 4 * half + 8 * n;
-      if (i0 < len) {  // uniform over the block
+    for (int n = 0; n < 4; ++n) {
+      const int i0 = 4 * quarter + 16 * n;
+      if (i0 < len) {  // uniform over the warp
         const int big = i0 >> 4, bs = i0 & ~15;
         const float* m1d = sM1d + big * 16 * 20;
         const float* m2d = sM2d + big * 16 * 20;
@@ -1046,7 +1047,6 @@ __global__ void __launch_bounds__(512) kda_tail_pair_kernel(
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           const int i = i0 + r;
-          float db = 0.f;
           if (i < len) {
             const float gi = sG[i * 128 + d];
             const float down = fast_exp2(gi - sG[bs * 128 + d]);  // 2^{G_i - G_R}
@@ -1062,22 +1062,20 @@ __global__ void __launch_bounds__(512) kda_tail_pair_kernel(
             keep_b[4 * n + r] = fmaf(rq_at(q_cvt, i), offq[r], fmaf(rq_at(k_cvt, i), offk[r], qi * rq[r] + ki * bi * rk[r])) +
                                 xq * qgr + xg * kgr - xr * krr;
             chunk_end = fmaf(xr, krr, chunk_end);
-            db = ki * rkt;  // dbeta_i += sum_d k_id RK_id
+            keep_db[4 * n + r] = ki * rkt;  // dbeta_i += sum_d k_id RK_id
           }
-#pragma unroll
-          for (int m = 16; m >= 1; m >>= 1) db += __shfl_xor_sync(0xffffffffu, db, m);
-          if (lane == 0 && i < len) s_db[i * 4 + warp4] = db;
         }
       }
     }
-    if (half == 0) chunk_end = fmaf(fast_exp2(gl), hdh[tile * kDim + d], chunk_end);
-  } else {
+    if (quarter == 0) chunk_end = fmaf(fast_exp2(gl), hdh[tile * kDim + d], chunk_end);
+  }
+  {
     // ---- column pass: four columns at a time.  For i below the group (inside the 16-block), E_{i, j0+c} =
     // E_{i, j0+3} E_{j0+3, j0+c}; the later blocks come from the tensor core.
     wait_products();
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const int j0 = 4 * half + 8 * n;
+    for (int n = 0; n < 4; ++n) {
+      const int j0 = 4 * quarter + 16 * n;
       if (j0 < len) {
         const int big = j0 >> 4, bs = j0 & ~15;
         const int be = len < bs + 16 ? len : bs + 16;
@@ -1142,54 +1140,69 @@ __global__ void __launch_bounds__(512) kda_tail_pair_kernel(
           }
         }
 #pragma unroll
-        for (int cidx = 0; cidx < 4; ++cidx) keep_a[4 * n + cidx] = cc[cidx], keep_b[4 * n + cidx] = kcc[cidx];
+        for (int cidx = 0; cidx < 4; ++cidx) keep_c[4 * n + cidx] = cc[cidx], keep_k[4 * n + cidx] = kcc[cidx];
       }
     }
   }
   wait_products();
-  __syncthreads();  // both passes are done with the gates and the factors: their space takes the column pass's sums
-  float* s_cc = sG;    // CC [64][128]
-  float* s_kcc = sR;   // the gate gradient's column part [64][128]
-  float* s_dg = sCC;   // the per-row gate gradients (AR's space: the products are long done)
-  float* s_end = reinterpret_cast<float*>(sm + KdaPairSmem::kX1);  // the chunk-end term per channel, two halves
-  if (role == 1) {
+  // dbeta's row part: sum over the channels of k_id RK_id.  The 16 rows' partials of the warp's 32 channels are summed
+  // by a butterfly that halves the rows a lane carries at every step (16 shuffles instead of 80); then one partial
+  // per warp of the quarter.
+  {
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+    for (int width = 8, m = 16; width >= 1; width >>= 1, m >>= 1) {
+      const bool up = (lane & m) != 0;  // this lane keeps the upper half of the rows it still carries
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int j = 4 * half + 8 * n + r;
-        if (j < len) s_cc[j * 128 + d] = keep_a[4 * n + r], s_kcc[j * 128 + d] = keep_b[4 * n + r];
+      for (int j = 0; j < width; ++j) {
+        const float mine = up ? keep_db[j + width] : keep_db[j], send = up ? keep_db[j] : keep_db[j + width];
+        keep_db[j] = mine + __shfl_xor_sync(0xffffffffu, send, m);
       }
     }
-  } else {
-    s_end[half * 128 + d] = chunk_end;
+    keep_db[0] += __shfl_xor_sync(0xffffffffu, keep_db[0], 1);
+    // lane bits 4..1 spell which of the 16 rows the lane holds: bit 4 the upper eight, bit 3 the upper four, ...
+    const int which = (lane >> 1) & 15, i = 4 * quarter + 16 * (which >> 2) + (which & 3);
+    if ((lane & 1) == 0 && i < len) s_db[i * 4 + warp4] = keep_db[0];
   }
+  __syncthreads();  // both passes are done with the gates and the factors: their space takes the sums below
+  float* s_end = sG;               // the chunk-end term per channel, one partial per quarter  [4][128]
+  float* s_tot = sG + 4 * 128;     // the gate gradient summed over each group of four rows     [16][128]
+  s_end[quarter * 128 + d] = chunk_end;
   __syncthreads();
-  if (role == 0) {  // the row pass's threads own the same (row, channel) pairs: dk and the gate gradient in one go
+  // dk and the gate gradient of this thread's 16 (token, channel) pairs; the in-chunk suffix sum of the gate gradient
+  // by groups: every thread sums its groups, publishes the totals and adds the totals of the later groups
+  float dgv[16];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+  for (int n = 0; n < 4; ++n) {
+    float total = 0.f;
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int i = 4 * half + 8 * n + r;
-        if (i < len) {
-          dk[col + i * stride] = keep_a[4 * n + r] + s_cc[i * 128 + d];
-          float dgi = keep_b[4 * n + r] - s_kcc[i * 128 + d];
-          if (i == len - 1) dgi += s_end[d] + s_end[128 + d];
-          s_dg[i * 128 + d] = dgi;
-        }
+    for (int r = 3; r >= 0; --r) {
+      const int i = 4 * quarter + 16 * n + r;
+      float dgi = 0.f;
+      if (i < len) {
+        dk[col + i * stride] = keep_a[4 * n + r] + keep_c[4 * n + r];
+        dgi = keep_b[4 * n + r] - keep_k[4 * n + r];
+        if (i == len - 1) dgi += (s_end[d] + s_end[128 + d]) + (s_end[256 + d] + s_end[384 + d]);
       }
+      total += dgi;
+      dgv[4 * n + r] = total;  // the suffix sum inside the group
     }
+    s_tot[(quarter + 4 * n) * 128 + d] = total;
   }
   __syncthreads();
-  if (tid < 128) {  // the in-chunk suffix sum, one channel per thread
-    float running = 0.f;
-    for (int i = len - 1; i >= 0; --i) {
-      running += s_dg[i * 128 + d];
-      dg[col + i * stride] = running;
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+    const int group = quarter + 4 * n;
+    float later = 0.f;
+    for (int g = 15; g > group; --g) later += s_tot[g * 128 + d];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = 4 * quarter + 16 * n + r;
+      if (i < len) dg[col + i * stride] = dgv[4 * n + r] + later;
     }
-  } else if (tid < 256 && d < len) {
-    const int64_t at = int64_t(start + d) * num_heads + h;
-    dbeta[at] = dbeta_part[at] + ((s_db[d * 4] + s_db[d * 4 + 1]) + (s_db[d * 4 + 2] + s_db[d * 4 + 3]));
+  }
+  if (tid < len) {
+    const int64_t at = int64_t(start + tid) * num_heads + h;
+    dbeta[at] = dbeta_part[at] + ((s_db[tid * 4] + s_db[tid * 4 + 1]) + (s_db[tid * 4 + 2] + s_db[tid * 4 + 3]));
   }
   if (!ok && tid == 0) atomicExch(status, kDevWaitTimeout | (8 << 8));
   tc_fence_before();
