@@ -38,20 +38,43 @@ __global__ void __launch_bounds__(128) kda_prep_kernel(
   if (len <= 0) return;
   const int64_t stride = int64_t(num_heads) * kDim;
   const int64_t base = int64_t(start) * stride + h * kDim + d;
+  // tokens in batches of eight: a batch's loads are all issued before the running sum needs the first of them
   float acc = 0.f;
-  for (int i = 0; i < len; ++i) {
-    const int64_t at = base + i * stride;
-    acc += g[at];
-    const float gi = acc * kLog2e, e = fast_exp2(gi);
-    g2[at] = gi;
-    qg[at] = __float2bfloat16_rn(__bfloat162float(q[at]) * e);
-    kg[at] = __float2bfloat16_rn(__bfloat162float(k[at]) * e);
+  for (int i0 = 0; i0 < len; i0 += 8) {
+    float gv[8], qv[8], kv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool in = i0 + j < len;
+      const int64_t at = base + (in ? i0 + j : i0) * stride;
+      gv[j] = in ? g[at] : 0.f;
+      qv[j] = __bfloat162float(q[at]);
+      kv[j] = __bfloat162float(k[at]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (i0 + j < len) {
+        const int64_t at = base + (i0 + j) * stride;
+        acc += gv[j];
+        const float gi = acc * kLog2e, e = fast_exp2(gi);
+        g2[at] = gi;
+        qg[at] = __float2bfloat16_rn(qv[j] * e);
+        kg[at] = __float2bfloat16_rn(kv[j] * e);
+      }
+    }
   }
   const float gl = acc * kLog2e;
   gl2[(int64_t(c) * num_heads + h) * kDim + d] = gl;
-  for (int i = 0; i < len; ++i) {
-    const int64_t at = base + i * stride;
-    kr[at] = __float2bfloat16_rn(__bfloat162float(k[at]) * fast_exp2(gl - g2[at]));
+  for (int i0 = 0; i0 < len; i0 += 8) {
+    float gv[8], kv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int64_t at = base + (i0 + j < len ? i0 + j : i0) * stride;
+      gv[j] = g2[at];
+      kv[j] = __bfloat162float(k[at]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (i0 + j < len) kr[base + (i0 + j) * stride] = __float2bfloat16_rn(kv[j] * fast_exp2(gl - gv[j]));
   }
 }
 
@@ -849,51 +872,64 @@ __global__ void __launch_bounds__(512) kda_tail_pair_kernel(
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 512);
   if (tid < 64) s_beta[tid] = tid < len ? beta[int64_t(start + tid) * num_heads + h] : 0.f;
+  // Every global read of the prologue is issued before the first of them is used: the gates, and the entries of M1
+  // and M2 for the products' operands -- AR (rows against their own block's part of the stack), X1 / X2 (the entries
+  // of earlier blocks) -- and for the fp32 diagonal blocks.
+  float gate[16];
 #pragma unroll
   for (int n = 0; n < 16; ++n) {  // rows past the chunk's length keep the last gate (R = 1 there)
     const int i = (tid >> 7) + 4 * n;
-    sG[i * 128 + d] = g2[col + int64_t(i < len ? i : len - 1) * stride];
+    gate[n] = g2[col + int64_t(i < len ? i : len - 1) * stride];
+  }
+  float4 ar_lo[3], ar_hi[3];
+#pragma unroll
+  for (int it = 0; it < 3; ++it) {
+    const int t = tid + 512 * it;
+    const int n = t / 12, cc = t % 12;            // row of AR, 16-byte chunk of its 96 columns
+    const int i = n & 63, colb = cc * 8;
+    const int owner = colb < 16 ? 1 : (colb < 48 ? 2 : 3);
+    const int j = colb < 16 ? colb : (colb < 48 ? colb - 16 : colb - 48);
+    ar_lo[it] = ar_hi[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if ((i >> 4) == owner) {
+      const float* src = (n < 64 ? m1 : m2) + tile * 4096 + i * 64 + j;
+      ar_lo[it] = __ldg(reinterpret_cast<const float4*>(src));
+      ar_hi[it] = __ldg(reinterpret_cast<const float4*>(src) + 1);
+    }
+  }
+  const int xi = tid >> 3, xc = tid & 7;
+  const float* s1 = m1 + tile * 4096 + xi * 64 + xc * 8;
+  const float* s2 = m2 + tile * 4096 + xi * 64 + xc * 8;
+  const float4 a0 = __ldg(reinterpret_cast<const float4*>(s1)), a1 = __ldg(reinterpret_cast<const float4*>(s1) + 1);
+  const float4 b0 = __ldg(reinterpret_cast<const float4*>(s2)), b1 = __ldg(reinterpret_cast<const float4*>(s2) + 1);
+#pragma unroll
+  for (int n = 0; n < 16; ++n) sG[((tid >> 7) + 4 * n) * 128 + d] = gate[n];
+#pragma unroll
+  for (int it = 0; it < 3; ++it) {
+    const int t = tid + 512 * it;
+    const int n = t / 12, cc = t % 12;
+    const float x[8] = {ar_lo[it].x, ar_lo[it].y, ar_lo[it].z, ar_lo[it].w, ar_hi[it].x, ar_hi[it].y, ar_hi[it].z, ar_hi[it].w};
+    *reinterpret_cast<uint4*>(ar + (cc >> 3) * 16384 + sw128_offset(n, cc & 7)) = pack8(x);
+  }
+  {
+    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    const bool earlier = (xc >> 1) < (xi >> 4);     // the 8 columns lie in a block before the row's
+    float xa[8], xb[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) xa[e] = earlier ? av[e] : 0.f, xb[e] = earlier ? bv[e] : 0.f;
+    *reinterpret_cast<uint4*>(x1 + sw128_offset(xi, xc)) = pack8(xa);
+    *reinterpret_cast<uint4*>(x2 + sw128_offset(xi, xc)) = pack8(xb);
+    if ((xc >> 1) == (xi >> 4)) {                   // ... or in the row's own block: the fp32 diagonal blocks
+      const int at = ((xi >> 4) * 16 + (xi & 15)) * 20 + (xc & 1) * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sM1d[at + e] = av[e], sM2d[at + e] = bv[e];
+    }
   }
   __syncthreads();  // beta, the gates and the barriers' initialisation are in place
 #pragma unroll
   for (int n = 0; n < 16; ++n) {
     const int i = (tid >> 7) + 4 * n;
     sR[i * 128 + d] = (i < len && i > 0) ? fast_exp2(sG[i * 128 + d] - sG[(i - 1) * 128 + d]) : 1.f;
-  }
-  // the operands of the products from M1 and M2: AR (rows against their own block's part of the stack), X1 / X2 (the
-  // entries of earlier blocks), and the fp32 diagonal blocks
-  for (int t = tid; t < 128 * 12; t += 512) {
-    const int n = t / 12, cc = t % 12;            // row of AR, 16-byte chunk of its 96 columns
-    const int i = n & 63, colb = cc * 8;
-    const int owner = colb < 16 ? 1 : (colb < 48 ? 2 : 3);
-    const int j = colb < 16 ? colb : (colb < 48 ? colb - 16 : colb - 48);
-    float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if ((i >> 4) == owner) {
-      const float* src = (n < 64 ? m1 : m2) + tile * 4096 + i * 64 + j;
-      const float4 lo = __ldg(reinterpret_cast<const float4*>(src)), hi = __ldg(reinterpret_cast<const float4*>(src) + 1);
-      x[0] = lo.x, x[1] = lo.y, x[2] = lo.z, x[3] = lo.w, x[4] = hi.x, x[5] = hi.y, x[6] = hi.z, x[7] = hi.w;
-    }
-    *reinterpret_cast<uint4*>(ar + (cc >> 3) * 16384 + sw128_offset(n, cc & 7)) = pack8(x);
-  }
-  for (int t = tid; t < 64 * 8; t += 512) {
-    const int i = t >> 3, cc = t & 7;
-    const float* s1 = m1 + tile * 4096 + i * 64 + cc * 8;
-    const float* s2 = m2 + tile * 4096 + i * 64 + cc * 8;
-    const float4 a0 = __ldg(reinterpret_cast<const float4*>(s1)), a1 = __ldg(reinterpret_cast<const float4*>(s1) + 1);
-    const float4 b0 = __ldg(reinterpret_cast<const float4*>(s2)), b1 = __ldg(reinterpret_cast<const float4*>(s2) + 1);
-    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-    const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-    const bool earlier = (cc >> 1) < (i >> 4);     // the 8 columns lie in a block before the row's
-    float xa[8], xb[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) xa[e] = earlier ? av[e] : 0.f, xb[e] = earlier ? bv[e] : 0.f;
-    *reinterpret_cast<uint4*>(x1 + sw128_offset(i, cc)) = pack8(xa);
-    *reinterpret_cast<uint4*>(x2 + sw128_offset(i, cc)) = pack8(xb);
-    if ((cc >> 1) == (i >> 4)) {                   // ... or in the row's own block: the fp32 diagonal blocks
-      const int at = ((i >> 4) * 16 + (i & 15)) * 20 + (cc & 1) * 8;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) sM1d[at + e] = av[e], sM2d[at + e] = bv[e];
-    }
   }
   bool ok = __all_sync(0xffffffffu, mbar_wait(&bar_load, 0));
   if (len < kChunk) {  // a ragged chunk's boxes reach into the next sequence: clear those rows
