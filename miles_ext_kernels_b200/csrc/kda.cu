@@ -189,10 +189,11 @@ __global__ void __launch_bounds__(kIntraThreads, 2) kda_intra_kernel(
     for (int b = 0; b < 4; ++b) aqk[a][b] = akk[a][b] = 0.f;
   int i0 = 0, j0 = 0;
   {
+    // warps 0..3 take the 16 sub-blocks on the diagonal, warps 4..9 the 24 below it: no warp runs both branches
     const int s = tid >> 3, slice = tid & 7;
-    const int big = s / 10, t = s % 10;
-    const int bi = t == 0 ? 0 : (t < 3 ? 1 : (t < 6 ? 2 : 3));
-    const int bj = t - bi * (bi + 1) / 2;
+    const int big = s < 16 ? s >> 2 : (s - 16) / 6, t = s < 16 ? 0 : (s - 16) % 6;
+    const int bi = s < 16 ? (s & 3) : (t < 1 ? 1 : (t < 3 ? 2 : 3));
+    const int bj = s < 16 ? bi : t - bi * (bi - 1) / 2;
     i0 = 16 * big + 4 * bi, j0 = 16 * big + 4 * bj;
     // 4 channels d .. d + 3 of tile row `row`: half of a 16-byte chunk
     auto four = [&](int row, int d, float* out) {
