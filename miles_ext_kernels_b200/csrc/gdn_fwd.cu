@@ -64,12 +64,11 @@ __global__ void gate_cumsum_kernel(const float* __restrict__ g, float* __restric
 // wy
 // ---------------------------------------------------------------------------------------------------------------
 struct WySmem {
-  static constexpr uint32_t kQ = 0;                // [64][128] q; after the first products: fp32 L [64][64], swizzled
-  static constexpr uint32_t kK = 16384;            // [64][128] k
-  static constexpr uint32_t kV = 32768;            // [64][128] v -> beta v
-  static constexpr uint32_t kKB = kV + 16384;      // [64][128] beta 2^G k
-  static constexpr uint32_t kA = kKB + 16384;      // [64][64] A (bf16)
-  static constexpr uint32_t kScal = kA + 8192;     // beta[64], g2[64]
+  static constexpr uint32_t kQ = 0;                // [64][128] q; after the first products: fp32 L [64][64], swizzled,
+                                                   // whose dead quarters take the TF32 operands; at the end A (bf16)
+  static constexpr uint32_t kK = 16384;            // [64][128] k -> beta 2^G k (in place)
+  static constexpr uint32_t kV = 32768;            // [64][128] v -> beta v (in place)
+  static constexpr uint32_t kScal = kV + 16384;    // beta[64], g2[64]
   static constexpr uint32_t kBytes = kScal + 512;
 };
 
@@ -81,7 +80,8 @@ __device__ __forceinline__ int wy_l_index(int i, int j) {
 // float index of element (row, k) of a one-block fp32 operand of 32 contraction columns
 __device__ __forceinline__ int f32_block_index(int row, int k) { return row * 32 + (((k >> 2) ^ (row & 7)) << 2) + (k & 3); }
 
-// Three CTAs per SM (shared memory) hide each other's global-load and solve latencies; tensor memory: 128 columns.
+// Four CTAs per SM (50 KB of shared memory each) hide each other's global-load and solve latencies; tensor memory:
+// 128 columns each.
 struct WyMaps {
   CUtensorMap q, k, v;      // rows, box 64 x 64
   CUtensorMap w_out, u_out;  // rows, box 64 x 64 (stores)
@@ -182,18 +182,22 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   // A = (I + L)^-1 by blocks of 32: with I + L = [[M11, 0], [L21, M22]],
   //     A = [[X11, 0], [X21, X22]],  X11 = M11^-1, X22 = M22^-1 (fp32 forward substitution, 64 threads, 496 FMAs each)
   //     X21 = -X22 (L21 X11)  (two tensor-core products with TF32 operands; A is rounded to bf16 afterwards)
-  // The dead k tile holds the products' operands: B1 = X11^T [32 x 32], A2 = [0; X22] [64 x 32], B2 = T^T [32 x 32].
-  float* s_b1 = reinterpret_cast<float*>(sm + WySmem::kK);
-  float* s_a2 = s_b1 + 1024;
-  float* s_b2 = s_a2 + 2048;
-  uint8_t* a_tile = sm + WySmem::kA;
-  // Warps 0..1 solve in registers while warps 2..3 build the last products' operands, kb = bf16(beta 2^G k) and
-  // vb = bf16(beta v) (in place), from the k tile, whose space the solve's results take afterwards: the two halves
-  // meet on a named barrier before anything is written there.
-  auto halves_meet = [] { asm volatile("bar.sync 1, 128;" ::: "memory"); };
+  // The products' operands take the quarters of L that are dead by then (L as two blocks of 32 columns, rows 0..31 /
+  // 32..63 of each a quarter of 4 KiB):
+  //     L11 -> B1 = X11^T [32 x 32]      L21 (stays: rows 32..63 of the first product's A operand, the block itself)
+  //     upper right (never used) -> X22  L22 -> B2 = T^T [32 x 32]
+  // A2 = [*; X22] [64 x 32] starts at L21, so that its rows 32..63 are the upper right quarter; its rows 0..31 (and the
+  // first product's: B1 by then) are whatever lies there -- a row of the result depends on its own operand row only,
+  // and the results' rows 0..31 are not read.
+  float* s_b1 = s_l;
+  float* s_a2 = s_l + 1024;
+  float* s_b2 = s_l + 3072;
+  // Warps 0..1 solve in registers while warps 2..3 turn k and v into the last products' operands, kb = bf16(beta 2^G k)
+  // and vb = bf16(beta v), in place.  The solving threads keep their columns of X11 / X22 in registers until A can be
+  // written (its tile takes L's space once the products are done).
+  float x[32];
   if (tid < 64) {
     const int b = tid >> 5, c = tid & 31, base = 32 * b;
-    float x[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       float acc0 = (i == c) ? 1.f : 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
@@ -207,12 +211,7 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
       }
       x[i] = (acc0 + acc1) + (acc2 + acc3);
     }
-    halves_meet();  // the k tile has been read: its space takes B1 and A2
-    const int col = base + c;
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      *reinterpret_cast<__nv_bfloat16*>(a_tile + sw128_offset(base + i, col >> 3) + (col & 7) * 2) =
-          __float2bfloat16_rn(x[i]);
+    asm volatile("bar.sync 1, 64;" ::: "memory");  // every solving thread has read L11 / L22: their space is rewritten
     if (b == 0) {  // row c of B1 = column c of X11
 #pragma unroll
       for (int i = 0; i < 32; i += 4)
@@ -226,34 +225,30 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
     for (int i = t; i < 64 * 16; i += 64) {
       const int r = i >> 4, cc = i & 15;
       const float b = s_beta[r], sc = b * fast_exp2(s_g2[r]);
-      float x[8];
-      unpack8(tile_chunk(sm + WySmem::kK, 8192, r, cc), x);
+      float y[8];
+      unpack8(tile_chunk(sm + WySmem::kK, 8192, r, cc), y);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] *= sc;
-      set_tile_chunk(sm + WySmem::kKB, 8192, r, cc, pack8(x));
-      unpack8(tile_chunk(sm + WySmem::kV, 8192, r, cc), x);
+      for (int j = 0; j < 8; ++j) y[j] *= sc;
+      set_tile_chunk(sm + WySmem::kK, 8192, r, cc, pack8(y));
+      unpack8(tile_chunk(sm + WySmem::kV, 8192, r, cc), y);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] *= b;
-      set_tile_chunk(sm + WySmem::kV, 8192, r, cc, pack8(x));
+      for (int j = 0; j < 8; ++j) y[j] *= b;
+      set_tile_chunk(sm + WySmem::kV, 8192, r, cc, pack8(y));
     }
-    // the upper right block of A is zero (its tile is this phase's own)
-    for (int i = t; i < 32 * 4; i += 64)
-      set_tile_chunk(a_tile, 8192, i >> 2, 4 + (i & 3), make_uint4(0u, 0u, 0u, 0u));
-    halves_meet();
-    // rows 0..31 of A2 are zero
-    for (int i = t; i < 256; i += 64) reinterpret_cast<float4*>(s_a2)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
 
-  const uint32_t l_addr = sbase + WySmem::kQ, k_addr = sbase + WySmem::kK;
+  const uint32_t l_addr = sbase + WySmem::kQ;
+  const uint32_t b1_addr = l_addr, a2_addr = l_addr + 4096, b2_addr = l_addr + 12288;
+  uint8_t* a_tile = sm + WySmem::kQ;  // written when the second product is done
   constexpr uint32_t kColT = 64, kColX = 96;  // free until the w / u products
   if (tid == 0) {  // T' = L[:, 0:32] X11 (rows 32..63 are T = L21 X11)
     const uint32_t idesc = umma_idesc_tf32(64, 32);
     for (uint32_t k0 = 0; k0 < 32; k0 += 8)
-      umma_tf32(tmem + kColT, umma_desc_sw128(l_addr + k0 * 4, 16u, kSbo), umma_desc_sw128(k_addr + k0 * 4, 16u, kSbo),
+      umma_tf32(tmem + kColT, umma_desc_sw128(l_addr + k0 * 4, 16u, kSbo), umma_desc_sw128(b1_addr + k0 * 4, 16u, kSbo),
                 idesc, k0 > 0 ? 1u : 0u);
     umma_commit(&bar);
   }
@@ -276,20 +271,34 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
   if (tid == 0) {  // X' = -A2 T (rows 32..63 are X21)
     const uint32_t idesc = umma_idesc_tf32(64, 32, /*neg_a=*/true);
     for (uint32_t k0 = 0; k0 < 32; k0 += 8)
-      umma_tf32(tmem + kColX, umma_desc_sw128(k_addr + 4096 + k0 * 4, 16u, kSbo),
-                umma_desc_sw128(k_addr + 12288 + k0 * 4, 16u, kSbo), idesc, k0 > 0 ? 1u : 0u);
+      umma_tf32(tmem + kColX, umma_desc_sw128(a2_addr + k0 * 4, 16u, kSbo),
+                umma_desc_sw128(b2_addr + k0 * 4, 16u, kSbo), idesc, k0 > 0 ? 1u : 0u);
     umma_commit(&bar);
   }
   ok = mbar_wait(&bar, 0) && ok;
   tc_fence_after();
   {
+    // both products are done: A (bf16) takes the first half of L's space -- the diagonal blocks from the solving
+    // threads' registers, X21 from the product, zeros above
     float xv[32];
     tmem_ld32(tmem_addr(tmem, warp, kColX), xv);
     tmem_ld_wait();
-    if (warp >= 2 && lane < 16) {
-      const int i = 16 * warp + lane;
+    if (warp >= 2) {
+      if (lane < 16) {
+        const int i = 16 * warp + lane;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) set_tile_chunk(a_tile, 8192, i, j, pack8(xv + 8 * j));
+        for (int j = 0; j < 4; ++j) set_tile_chunk(a_tile, 8192, i, j, pack8(xv + 8 * j));
+      } else {  // the upper right block of A is zero: the 16 rows 16 (warp - 2) .. + 15
+        const int i = 16 * (warp - 2) + lane - 16;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) set_tile_chunk(a_tile, 8192, i, 4 + j, make_uint4(0u, 0u, 0u, 0u));
+      }
+    } else {
+      const int b = tid >> 5, base = 32 * b, col = base + (tid & 31);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        *reinterpret_cast<__nv_bfloat16*>(a_tile + sw128_offset(base + i, col >> 3) + (col & 7) * 2) =
+            __float2bfloat16_rn(x[i]);
     }
   }
   fence_async_smem();
@@ -299,17 +308,18 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
 
   // w = A kb -> lanes 0..15, u = A vb -> lanes 16..31 of columns 0..127
   if (tid == 0) {
-    const Operand a{sbase + WySmem::kA, 8192};
-    const Operand kb{sbase + WySmem::kKB, 8192};
+    const Operand a{sbase + WySmem::kQ, 8192};
+    const Operand kb{sbase + WySmem::kK, 8192};
     const Operand vb{sbase + WySmem::kV, 8192};
     umma_gemm_pair<64, 128>(tmem, a, false, kb, true, 64, false, false, tmem + kUpper, a, false, vb, true, 64, false,
                             false);
     umma_commit(&bar);
   }
   // A -> global while the MMAs run
-  store_tile<64, 64, 128>(sm + WySmem::kA, 8192, a_out + (int64_t(c) * num_v_heads + hv) * 4096, 64, 64, tid);
+  store_tile<64, 64, 128>(sm + WySmem::kQ, 8192, a_out + (int64_t(c) * num_v_heads + hv) * 4096, 64, 64, tid);
   ok = mbar_wait(&bar, 1) && ok;  // the fourth commit on this barrier
   tc_fence_after();
+  __syncthreads();  // every thread has stored its part of A: the tile's space is staged over below
 
   ok = __all_sync(0xffffffffu, ok);
   // w and u leave through shared memory (the dead q / k tiles' space) and one TMA store each: a thread's row piece
