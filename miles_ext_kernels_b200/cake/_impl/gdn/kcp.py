@@ -225,7 +225,7 @@ class _Exchange:
         self.context = context
 
     # the hooks the stages call: around the state scan ...
-    def forward_begin(self, dims, meta, k, w, u, g_cs, status):
+    def forward_begin(self, dims, meta, k, w, u, g_cs, status, scan_segments: int = 0):
         """-> ``(h0 or None, keep the final state?)``"""
         ctx = self.context
         with _Timed("forward"):  # includes the wait for the rank before
@@ -237,7 +237,7 @@ class _Exchange:
             self.outgoing_state(final_state)
 
     # ... and around the adjoint scan
-    def backward_begin(self, dims, meta, tape, do):
+    def backward_begin(self, dims, meta, tape, do, scan_segments: int = 0):
         """-> ``(dht or None, keep dh0?)``"""
         ctx = self.context
         with _Timed("backward"):  # includes the wait for the rank after
@@ -247,6 +247,10 @@ class _Exchange:
     def backward_end(self, dh0) -> None:
         if dh0 is not None:
             self.outgoing_adjoint(dh0)
+
+    def take_prepared(self):
+        """The hand-over leaves the scan as it is."""
+        return None
 
     def _peer(self, offset: int) -> int:
         import torch.distributed as dist
@@ -311,6 +315,14 @@ class _ParallelExchange:
 
     def __init__(self, context: KcpContext) -> None:
         self.context = context
+        self._prepared = None
+
+    def take_prepared(self):
+        """``(plan, seg_dims, summary)`` when the exchange has already summarised the segments this rank's scan is cut
+        into (every segment from zero and from the identity): the scan then needs no pre-scan of its own, only the
+        stitch from the state that entered.  ``None`` otherwise.  Handed over once."""
+        prepared, self._prepared = self._prepared, None
+        return prepared
 
     def _gather(self, local: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
@@ -333,11 +345,27 @@ class _ParallelExchange:
 
         return flat.index_select(0, scan._small_table(tuple(index), torch.int64, flat.device))
 
-    def _exchange(self, dims, meta, HV, device, publish, slots, chains, summarise, reverse):
+    def _exchange(self, dims, meta, HV, device, publish, slots, chains, summarise, reverse, scan_segments: int = 0):
         from . import scan
 
         local = torch.zeros((max(slots, 1), HV, 2, 128, 128), dtype=torch.float32, device=device)
         table = meta.host_seq_chunk_start
+        self._prepared = None
+        shared = None
+        if meta.num_seqs == 1 and not getattr(self, "_exact", False):
+            # One sequence on this rank (a slice of a long document): its summary is composed from the very segments
+            # the scan planner cuts the slice into, so one pre-scan serves the exchange and the scan.  Every rank does
+            # it before the gather, the last one too, whose summary nobody reads.
+            shared = scan.plan_for(meta, HV, device, scan_segments)
+        if shared is not None:
+            ones = scan._small_table((1,) * shared.segments, torch.int32, device)
+            seg_dims = scan.segment_dims(dims, shared)
+            summary = torch.empty((shared.segments, HV, 2, 128, 128), dtype=torch.float32, device=device)
+            summarise(seg_dims, dataclasses.replace(shared, flags_fwd=ones, flags_bwd=ones), summary)
+            if publish:
+                local[0] = scan.compose_summary(seg_dims, shared, summary, self._g_cs, reverse=reverse)
+            self._prepared = (shared, seg_dims, summary)
+            publish = ()
         for slot, f in enumerate(publish):
             plan = scan.fragment_plan(table[f], table[f + 1], HV, device)
             if getattr(self, "_exact", False):
@@ -357,7 +385,7 @@ class _ParallelExchange:
                 states[f] = scan.fold_ranks(dims, run, 0, len(chain) - 1, reverse=reverse)[0]
         return states
 
-    def forward_begin(self, dims, meta, k, w, u, g_cs, status):
+    def forward_begin(self, dims, meta, k, w, u, g_cs, status, scan_segments: int = 0):
         from . import native
 
         plan = self.context.plan
@@ -370,7 +398,7 @@ class _ParallelExchange:
 
         with _Timed("forward"):
             h0 = self._exchange(dims, meta, HV, device, plan.publish_forward, plan.slots_forward, plan.chain_forward,
-                                summarise, reverse=False)
+                                summarise, reverse=False, scan_segments=scan_segments)
         return h0, False
 
     def forward_end(self, final_state) -> None:
@@ -405,7 +433,7 @@ class _ParallelExchange:
         return self._exchange(dims, meta, H, device, plan.publish_backward, plan.slots_backward, plan.chain_backward,
                               summarise, reverse=True)
 
-    def backward_begin(self, dims, meta, tape, do):
+    def backward_begin(self, dims, meta, tape, do, scan_segments: int = 0):
         from . import native
 
         plan = self.context.plan
@@ -419,7 +447,7 @@ class _ParallelExchange:
 
         with _Timed("backward"):
             dht = self._exchange(dims, meta, HV, device, plan.publish_backward, plan.slots_backward,
-                                 plan.chain_backward, summarise, reverse=True)
+                                 plan.chain_backward, summarise, reverse=True, scan_segments=scan_segments)
         return dht, False
 
     def backward_end(self, dh0) -> None:

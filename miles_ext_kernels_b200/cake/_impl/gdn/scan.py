@@ -107,6 +107,11 @@ class ScanPlan:
     state_row: torch.Tensor  # int32 [segments]: the sequence of each segment
     first_index: torch.Tensor  # int64 [N]: each sequence's first segment
     last_index: torch.Tensor  # int64 [N]: each sequence's last segment
+    # the same flags with the first segment of a cut sequence taken from zero / the identity like the others (its
+    # summary is chained from the boundary state by the stitch): under the warm-up rule no segment is then walked in
+    # full before the real walk
+    flags_fwd_all: torch.Tensor | None = None
+    flags_bwd_all: torch.Tensor | None = None
     warm_chunks: int = WARM_CHUNKS
     warm_log2: float = WARM_NATS * math.log2(math.e)
     guards: tuple = ()  # UploadGuards of the cached tables
@@ -122,22 +127,26 @@ def device_plan(seg: Segmentation, device: torch.device) -> ScanPlan:
         for guard in found.guards:
             guard.wait()
         return found
-    first, last, rows, fwd, bwd = [], [], [], [], []
+    first, last, rows, fwd, bwd, fwd_all, bwd_all = [], [], [], [], [], [], []
     for n, (a, b) in enumerate(zip(seg.seq_seg_start, seg.seq_seg_start[1:])):
         first.append(a)
         last.append(b - 1)
+        cut = 1 if b - a > 1 else 0
         for s in range(a, b):
             rows.append(n)
             fwd.append((1 if s > a else 0) | (2 if s == b - 1 else 0))
             bwd.append((1 if s < b - 1 else 0) | (2 if s == a else 0))
-    flat, guard_a = upload(torch.tensor([*seg.seg_chunk_start, *seg.seq_seg_start, *fwd, *bwd, *rows],
+            fwd_all.append(cut | (2 if s == b - 1 else 0))
+            bwd_all.append(cut | (2 if s == a else 0))
+    flat, guard_a = upload(torch.tensor([*seg.seg_chunk_start, *seg.seq_seg_start, *fwd, *bwd, *rows, *fwd_all, *bwd_all],
                                         dtype=torch.int32), device)
     index, guard_b = upload(torch.tensor([*first, *last], dtype=torch.int64), device)
     ns, n = seg.segments, len(seg.seq_seg_start) - 1
-    at = [0, ns + 1, ns + n + 2, 2 * ns + n + 2, 3 * ns + n + 2, 4 * ns + n + 2]
+    at = [0, ns + 1, ns + n + 2, 2 * ns + n + 2, 3 * ns + n + 2, 4 * ns + n + 2, 5 * ns + n + 2, 6 * ns + n + 2]
     plan = ScanPlan(ns, n, flat[at[0]:at[1]], flat[at[1]:at[2]], flat[at[2]:at[3]], flat[at[3]:at[4]],
                     flat[at[4]:at[5]], index[:n], index[n:],
-                    guards=tuple(g for g in (guard_a, guard_b) if g is not None))
+                    guards=tuple(g for g in (guard_a, guard_b) if g is not None),
+                    flags_fwd_all=flat[at[5]:at[6]], flags_bwd_all=flat[at[6]:at[7]])
     if len(_PLANS) >= 64:
         _PLANS.clear()
     _PLANS[key] = plan

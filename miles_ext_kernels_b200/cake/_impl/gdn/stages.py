@@ -95,11 +95,23 @@ def _walk_forward(dims, k, w, u, g_cs, h0, h, v_new, final, status, output) -> N
 
 
 def _scan_forward(dims, meta: ChunkMeta, k, w, u, g_cs, h0, h, v_new, want_final: bool, status, scan_segments: int,
-                  output=None):
+                  output=None, prepared=None):
     """The state scan: one serial walk per (sequence, value head), or the planner's segmented form (pre-scan,
-    stitch, real walk over the segments).  Returns the final state or None."""
+    stitch, real walk over the segments).  ``prepared``: a context-parallel exchange's ``(plan, seg_dims, summary)``
+    with every segment of this rank's slice already summarised from zero and from the identity -- the pre-scan is
+    skipped and the stitch chains all of them from ``h0``.  Returns the final state or None."""
     device = k.device
     HV = w.shape[1]
+    if prepared is not None:
+        plan, seg_dims, summary = prepared
+        seg_state = workspace.take(OP, "scan_state", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
+        native.launch("gdn_scan_stitch", seg_dims, plan.num_seqs, plan.seq_seg_start, summary, h0, g_cs, seg_state, None,
+                      0, plan.warm_chunks, plan.warm_log2, 4, device=device)
+        seg_final = None
+        if want_final:
+            seg_final = workspace.take(OP, "scan_final", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
+        _walk_forward(seg_dims, k, w, u, g_cs, seg_state, h, v_new, seg_final, status, output)
+        return seg_final.index_select(0, plan.last_index) if want_final else None
     plan = scan.plan_for(meta, HV, device, scan_segments)
     if plan is None:
         final = torch.empty((meta.num_seqs, HV, HEAD_DIM, HEAD_DIM), dtype=F32, device=device) if want_final else None
@@ -108,10 +120,12 @@ def _scan_forward(dims, meta: ChunkMeta, k, w, u, g_cs, h0, h, v_new, want_final
     seg_dims = scan.segment_dims(dims, plan)
     summary = workspace.take(OP, "scan_summary", (plan.segments, HV, 2, HEAD_DIM, HEAD_DIM), F32, device)
     seg_state = workspace.take(OP, "scan_state", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
-    native.launch("gdn_fwd_h_prescan", seg_dims, k, w, u, g_cs, h0, plan.flags_fwd, plan.state_row, plan.warm_chunks,
-                  plan.warm_log2, summary, status, device=device)
+    # every segment of a cut sequence is summarised from zero / the identity, the first too, and the stitch chains
+    # them from h0: where the warm-up rule applies no segment is walked in full before the real walk
+    native.launch("gdn_fwd_h_prescan", seg_dims, k, w, u, g_cs, None, plan.flags_fwd_all, plan.state_row,
+                  plan.warm_chunks, plan.warm_log2, summary, status, device=device)
     native.launch("gdn_scan_stitch", seg_dims, plan.num_seqs, plan.seq_seg_start, summary, h0, g_cs, seg_state, None, 0,
-                  plan.warm_chunks, plan.warm_log2, 0, device=device)
+                  plan.warm_chunks, plan.warm_log2, 4, device=device)
     seg_final = None
     if want_final:
         seg_final = workspace.take(OP, "scan_final", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
@@ -119,10 +133,22 @@ def _scan_forward(dims, meta: ChunkMeta, k, w, u, g_cs, h0, h, v_new, want_final
     return seg_final.index_select(0, plan.last_index) if want_final else None
 
 
-def _scan_backward(dims, meta: ChunkMeta, tape, do, dht, dh_tape, dv_new, want_dh0: bool, scan_segments: int):
-    """The adjoint scan, serial or segmented like the forward's.  Returns dh0 or None."""
+def _scan_backward(dims, meta: ChunkMeta, tape, do, dht, dh_tape, dv_new, want_dh0: bool, scan_segments: int,
+                   prepared=None):
+    """The adjoint scan, serial or segmented like the forward's (``prepared``: as there).  Returns dh0 or None."""
     device = do.device
     HV = tape.v.shape[1]
+    if prepared is not None:
+        plan, seg_dims, summary = prepared
+        seg_state = workspace.take(OP, "scan_state", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
+        native.launch("gdn_scan_stitch", seg_dims, plan.num_seqs, plan.seq_seg_start, summary, dht, tape.g_cs, seg_state,
+                      None, 1, plan.warm_chunks, plan.warm_log2, 4, device=device)
+        seg_dh0 = None
+        if want_dh0:
+            seg_dh0 = workspace.take(OP, "scan_final", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
+        native.launch("gdn_bwd_dh", seg_dims, tape.qn, tape.kn, tape.w, do, tape.aqk, tape.g_cs, seg_state, dh_tape,
+                      dv_new, seg_dh0, tape.status, device=device)
+        return seg_dh0.index_select(0, plan.first_index) if want_dh0 else None
     plan = scan.plan_for(meta, HV, device, scan_segments)
     if plan is None:
         dh0 = torch.empty((meta.num_seqs, HV, HEAD_DIM, HEAD_DIM), dtype=F32, device=device) if want_dh0 else None
@@ -132,11 +158,11 @@ def _scan_backward(dims, meta: ChunkMeta, tape, do, dht, dh_tape, dv_new, want_d
     seg_dims = scan.segment_dims(dims, plan)
     summary = workspace.take(OP, "scan_summary", (plan.segments, HV, 2, HEAD_DIM, HEAD_DIM), F32, device)
     seg_state = workspace.take(OP, "scan_state", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
-    native.launch("gdn_bwd_dh_prescan", seg_dims, tape.qn, tape.kn, tape.w, do, tape.aqk, tape.g_cs, dht,
-                  plan.flags_bwd, plan.state_row, plan.warm_chunks, plan.warm_log2, summary, tape.status,
+    native.launch("gdn_bwd_dh_prescan", seg_dims, tape.qn, tape.kn, tape.w, do, tape.aqk, tape.g_cs, None,
+                  plan.flags_bwd_all, plan.state_row, plan.warm_chunks, plan.warm_log2, summary, tape.status,
                   device=device)
     native.launch("gdn_scan_stitch", seg_dims, plan.num_seqs, plan.seq_seg_start, summary, dht, tape.g_cs, seg_state,
-                  None, 1, plan.warm_chunks, plan.warm_log2, 0, device=device)
+                  None, 1, plan.warm_chunks, plan.warm_log2, 4, device=device)
     seg_dh0 = None
     if want_dh0:
         seg_dh0 = workspace.take(OP, "scan_final", (plan.segments, HV, HEAD_DIM, HEAD_DIM), F32, device)
@@ -178,12 +204,14 @@ def forward(q, k, v, g, beta32, meta: ChunkMeta, scale: float, h0, output_final_
 
     h = alloc((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
     v_new = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
+    prepared = None
     if exchange is not None:
-        h0, output_final_state = exchange.forward_begin(dims, meta, k, w, u, g_cs, status)
+        h0, output_final_state = exchange.forward_begin(dims, meta, k, w, u, g_cs, status, scan_segments)
+        prepared = exchange.take_prepared()
     # the output is written by the walk itself (h_tape and v_new are consumed from shared memory, not read back)
     o = torch.empty((T, HV, HEAD_DIM), dtype=BF16, device=device)
     final_state = _scan_forward(dims, meta, k, w, u, g_cs, h0, h, v_new, output_final_state, status, scan_segments,
-                                output=(q, aqk, o))
+                                output=(q, aqk, o), prepared=prepared)
     if exchange is not None:
         exchange.forward_end(final_state)
         final_state = None
@@ -252,9 +280,11 @@ def backward(tape: ForwardTape, meta: ChunkMeta, scale: float, do, dht, h0, want
         else:  # pad chunks are never written
             dh_tape = torch.zeros((NC, HV, HEAD_DIM, HEAD_DIM), dtype=BF16, device=device)
         dv_new = workspace.take(OP, "dv_new", (T, HV, HEAD_DIM), BF16, device)
+    prepared = None
     if exchange is not None:
-        dht, want_dh0 = exchange.backward_begin(dims, meta, tape, do)
-    dh0 = _scan_backward(dims, meta, tape, do, dht, dh_tape, dv_new, want_dh0, scan_segments)
+        dht, want_dh0 = exchange.backward_begin(dims, meta, tape, do, scan_segments)
+        prepared = exchange.take_prepared()
+    dh0 = _scan_backward(dims, meta, tape, do, dht, dh_tape, dv_new, want_dh0, scan_segments, prepared=prepared)
     if exchange is not None:
         exchange.backward_end(dh0)
         dh0 = None
