@@ -185,6 +185,12 @@ int mek_gdn_bwd_dh_prescan(const MekGdnDims* seg_dims, const void* q, const void
 int mek_gdn_scan_stitch(const MekGdnDims* seg_dims, int num_seqs, const int32_t* seq_seg_start, const float* summary,
                         const float* boundary, const float* g_cs, float* seg_state, float* final_out, int reverse,
                         int warm_chunks, float warm_log2, int mode, void* stream);
+/* The summary (B, M) of ONE run of segments (seq_seg_start [2]) composed from the segments' summaries, every segment
+ * taken from zero / the identity, in one launch: out fp32 [HV, 2, 128, 128] (B, then M, per head) -- what a rank
+ * publishes of its slice under context parallelism (reference: the fragment summaries of
+ * miles_ext_kernels/cake/_impl/gdn/kcp.py:71-226). */
+int mek_gdn_scan_compose(const MekGdnDims* seg_dims, const int32_t* seq_seg_start, const float* summary,
+                         const float* g_cs, float* out, int reverse, int warm_chunks, float warm_log2, void* stream);
 
 /* Gradient tail per (chunk, key head): dq, dk bf16 [T, H, 128] (fp32 sum over the key head's value heads, the L2
  * norm's pull-back when q_raw / k_raw / rstd_q / rstd_k are given, one rounding), dv bf16 [T, HV, 128], dbeta and

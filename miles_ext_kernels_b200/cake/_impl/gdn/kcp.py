@@ -348,7 +348,8 @@ class _ParallelExchange:
     def _exchange(self, dims, meta, HV, device, publish, slots, chains, summarise, reverse, scan_segments: int = 0):
         from . import scan
 
-        local = torch.zeros((max(slots, 1), HV, 2, 128, 128), dtype=torch.float32, device=device)
+        # slots nobody publishes are read by nobody: a chain names published (rank, slot) pairs only
+        local = torch.empty((max(slots, 1), HV, 2, 128, 128), dtype=torch.float32, device=device)
         table = meta.host_seq_chunk_start
         self._prepared = None
         shared = None
@@ -363,7 +364,7 @@ class _ParallelExchange:
             summary = torch.empty((shared.segments, HV, 2, 128, 128), dtype=torch.float32, device=device)
             summarise(seg_dims, dataclasses.replace(shared, flags_fwd=ones, flags_bwd=ones), summary)
             if publish:
-                local[0] = scan.compose_summary(seg_dims, shared, summary, self._g_cs, reverse=reverse)
+                scan.compose_summary(seg_dims, shared, summary, self._g_cs, reverse=reverse, out=local[0])
             self._prepared = (shared, seg_dims, summary)
             publish = ()
         for slot, f in enumerate(publish):
@@ -373,16 +374,17 @@ class _ParallelExchange:
             seg_dims = scan.segment_dims(dims, plan)
             summary = torch.empty((plan.segments, HV, 2, 128, 128), dtype=torch.float32, device=device)
             summarise(seg_dims, plan, summary)
-            local[slot] = scan.compose_summary(seg_dims, plan, summary, self._g_cs, reverse=reverse)
+            scan.compose_summary(seg_dims, plan, summary, self._g_cs, reverse=reverse, out=local[slot])
         gathered = self._gather(local)
         if not any(chains):
             return None
         flat = gathered.view(-1, HV, 2, 128, 128)
-        states = torch.zeros((meta.num_seqs, HV, 128, 128), dtype=torch.float32, device=device)
+        alloc = torch.empty if all(chains) else torch.zeros  # a sequence nothing enters starts from zero
+        states = alloc((meta.num_seqs, HV, 128, 128), dtype=torch.float32, device=device)
         for f, chain in enumerate(chains):
             if chain:
                 run = self._chain(flat, max(slots, 1), chain)
-                states[f] = scan.fold_ranks(dims, run, 0, len(chain) - 1, reverse=reverse)[0]
+                scan.fold_ranks(dims, run, 0, len(chain) - 1, reverse=reverse, out=states[f : f + 1])
         return states
 
     def forward_begin(self, dims, meta, k, w, u, g_cs, status, scan_segments: int = 0):

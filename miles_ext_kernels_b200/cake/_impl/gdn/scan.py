@@ -208,25 +208,29 @@ def fragment_plan(chunk_begin: int, chunk_end: int, num_v_heads: int, device: to
     return plan
 
 
-def compose_summary(seg_dims: native.Dims, plan: ScanPlan, summary: torch.Tensor, g_cs: torch.Tensor, reverse: bool):
-    """``[HV, 2, 128, 128]``: the (B, M) of the whole run of segments, from the segments' summaries."""
+def compose_summary(seg_dims: native.Dims, plan: ScanPlan, summary: torch.Tensor, g_cs: torch.Tensor, reverse: bool,
+                    out: torch.Tensor | None = None):
+    """``[HV, 2, 128, 128]``: the (B, M) of the whole run of segments, from the segments' summaries (B: from zero with
+    the offsets; M: from the identity without them), one launch, written into ``out`` when given."""
     device = summary.device
     HV = summary.shape[1]
-    out = torch.empty((2, HV, 128, 128), dtype=torch.float32, device=device)
-    for which, mode in ((0, 4), (1, 7)):  # B: from zero with the offsets; M: from the identity without them
-        native.launch("gdn_scan_stitch", seg_dims, 1, plan.seq_seg_start, summary, None, g_cs, None, out[which],
-                      int(reverse), plan.warm_chunks, plan.warm_log2, mode, device=device)
-    return out.transpose(0, 1).contiguous()
+    if out is None:
+        out = torch.empty((HV, 2, 128, 128), dtype=torch.float32, device=device)
+    native.launch("gdn_scan_compose", seg_dims, plan.seq_seg_start, summary, g_cs, out, int(reverse), plan.warm_chunks,
+                  plan.warm_log2, device=device)
+    return out
 
 
-def fold_ranks(dims: native.Dims, gathered: torch.Tensor, first: int, last: int, reverse: bool) -> torch.Tensor:
+def fold_ranks(dims: native.Dims, gathered: torch.Tensor, first: int, last: int, reverse: bool,
+               out: torch.Tensor | None = None) -> torch.Tensor:
     """The state that the ranks ``first .. last`` (inclusive) hand on, from their gathered summaries
     ``[W, HV, 2, 128, 128]``: ``S = B_first``, then ``S = M_r S + B_r`` along the chain (``reverse``: from ``last``
     down to ``first``).  ``[1, HV, 128, 128]``."""
     device = gathered.device
     HV = gathered.shape[1]
     span = _small_table((first, last + 1), torch.int32, device)
-    out = torch.empty((1, HV, 128, 128), dtype=torch.float32, device=device)
+    if out is None:
+        out = torch.empty((1, HV, 128, 128), dtype=torch.float32, device=device)
     native.launch("gdn_scan_stitch", dims, 1, span, gathered, None, None, None, out, int(reverse), 0, 0.0, 0,
                   device=device)
     return out

@@ -17,20 +17,29 @@ constexpr int kStitchCols = 32;  // columns of the state per CTA (grid.z = 128 /
 // mode bits: 1 = start from the identity instead of the boundary state; 2 = leave the offsets out (B := 0);
 // 4 = every segment started from zero, the first too.  Modes 4 and 5 | 2 compose the summary of a whole run of
 // segments (its B, then its M); mode 0 with rank summaries as the "segments" folds a chain of ranks.
+// `final_pitch`: floats between the final states of consecutive (sequence, value head) pairs (16384: packed).
+// `compose`: the grid's upper half of blockIdx.z runs mode 7 into final_out + 16384 while the lower half runs
+// `mode`: the (B, M) pair of a run of segments in one launch, interleaved per head.
 __global__ void __launch_bounds__(256) scan_stitch_kernel(
     const float* __restrict__ summary, const float* __restrict__ boundary, const float* __restrict__ g_cs,
     float* __restrict__ seg_state, float* __restrict__ final_out, const int32_t* __restrict__ chunk_start,
     const int32_t* __restrict__ chunk_len, const int32_t* __restrict__ seg_chunk_start,
     const int32_t* __restrict__ seq_seg_start, int num_v_heads, int reverse, int warm_chunks, float warm_log2,
-    int mode) {
+    int mode, int64_t final_pitch, int compose) {
   extern __shared__ float s_state[];  // [128][kStitchCols]: this CTA's columns of the state
   const int n = blockIdx.x, hv = blockIdx.y, tid = threadIdx.x;
+  constexpr int kSlices = 128 / kStitchCols;
+  const int slice = int(blockIdx.z) % kSlices;
+  if (compose != 0 && int(blockIdx.z) >= kSlices) {
+    mode = 7;
+    final_out += 16384;
+  }
   const int seg_begin = seq_seg_start[n], seg_end = seq_seg_start[n + 1];
   const ScanPlan plan = {nullptr, nullptr, nullptr, warm_chunks, warm_log2};
   // the columns of a state are independent of one another (S' = M S + B column by column): blockIdx.z picks
   // kStitchCols of the 128, so that a call with few chains still fills the SMs.  A thread owns half of its row's slice.
   constexpr int kHalf = kStitchCols / 2, kVec = kHalf / 4;
-  const int col0 = blockIdx.z * kStitchCols;
+  const int col0 = slice * kStitchCols;
   const int r = tid >> 1, c0 = (tid & 1) * kHalf;  // row; first column inside the slice
 
   // the state the walk starts from
@@ -98,7 +107,7 @@ __global__ void __launch_bounds__(256) scan_stitch_kernel(
           make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
     __syncthreads();
   }
-  if (final_out != nullptr) store_state(final_out + (int64_t(n) * num_v_heads + hv) * 16384);
+  if (final_out != nullptr) store_state(final_out + (int64_t(n) * num_v_heads + hv) * final_pitch);
 }
 
 }  // namespace mek
@@ -118,6 +127,23 @@ extern "C" int mek_gdn_scan_stitch(const MekGdnDims* seg_dims, int num_seqs, con
   scan_stitch_kernel<<<dim3(num_seqs, seg_dims->num_v_heads, 128 / kStitchCols), 256, smem,
                        static_cast<cudaStream_t>(stream)>>>(
       summary, boundary, g_cs, seg_state, final_out, seg_dims->chunk_start, seg_dims->chunk_len,
-      seg_dims->seq_chunk_start, seq_seg_start, seg_dims->num_v_heads, reverse, warm_chunks, warm_log2, mode);
+      seg_dims->seq_chunk_start, seq_seg_start, seg_dims->num_v_heads, reverse, warm_chunks, warm_log2, mode, 16384, 0);
   return launched("scan_stitch");
+}
+
+extern "C" int mek_gdn_scan_compose(const MekGdnDims* seg_dims, const int32_t* seq_seg_start, const float* summary,
+                                    const float* g_cs, float* out, int reverse, int warm_chunks, float warm_log2,
+                                    void* stream) {
+  using namespace mek;
+  if (seg_dims == nullptr || seg_dims->num_v_heads <= 0 || !seq_seg_start || !summary || !out || warm_chunks < 0)
+    return fail(MEK_ERR_INVALID, "scan_compose: a null pointer or bad extents");
+  if (warm_chunks > 0 && (!g_cs || !seg_dims->seq_chunk_start || !seg_dims->chunk_start || !seg_dims->chunk_len))
+    return fail(MEK_ERR_INVALID, "scan_compose: the warm-up rule needs the gates and the chunk tables");
+  const size_t smem = 128 * kStitchCols * sizeof(float);
+  if (int rc = want_smem(scan_stitch_kernel, smem, "scan_compose")) return rc;
+  scan_stitch_kernel<<<dim3(1, seg_dims->num_v_heads, 2 * (128 / kStitchCols)), 256, smem,
+                       static_cast<cudaStream_t>(stream)>>>(
+      summary, nullptr, g_cs, nullptr, out, seg_dims->chunk_start, seg_dims->chunk_len, seg_dims->seq_chunk_start,
+      seq_seg_start, seg_dims->num_v_heads, reverse, warm_chunks, warm_log2, 4, 2 * 16384, 1);
+  return launched("scan_compose");
 }
