@@ -164,6 +164,13 @@ def cpu_tokens_per_sec(workload_name: str, steps: int, warmup: int) -> dict:
     }
 
 
+def _workload_title(name: str) -> str:
+    from miles_ext_kernels_b200.workloads import CONFIGS
+
+    cfg = CONFIGS.get(name)
+    return name if cfg is None else f"{cfg.name}: {cfg.description}"
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -173,7 +180,9 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * cpu["seconds_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "sample": cpu["sample"], "cpu_processes": 1},
+        # the same workload string as the GPU arm's line; what was timed of it is the bounded sample named beside it
+        "config": {"workload": _workload_title(args.workload), "sample": cpu["sample"], "cpu_processes": 1,
+                   "cpu_sample_tokens": CPU_SAMPLE_TOKENS},
         "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
