@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
   extern __shared__ uint8_t raw[];
   __shared__ uint64_t bar;         // tensor-core commits
   __shared__ uint64_t bar2;        // ... of the second issuing thread
+  __shared__ uint64_t bar_first;   // the first product of phase A alone (dAqk): its epilogue starts under the others
   __shared__ uint64_t bar_item;    // the item's tiles: three instalments, one arrival each
   __shared__ uint64_t bar_uw;      // the item's u and w
   __shared__ uint64_t bar_qk[2];   // q and k of a pair, one barrier per buffer
@@ -138,6 +139,7 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
   if (tid == 0) {
     mbar_init(&bar, 1);
     mbar_init(&bar2, 1);
+    mbar_init(&bar_first, 1);
     mbar_init(&bar_item, 3);
     mbar_init(&bar_uw, 1);
     mbar_init(&bar_qk[0], 1);
@@ -347,6 +349,7 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
       // ---- phase A: everything that needs only loaded tiles -------------------------------------------------------
       if (issuer) {
         umma_gemm<64, 64>(tmem + kColTa, op_do, false, op_vn, false, 128, false);   // dAqk = do v_new^T
+        umma_commit(&bar_first);
         gemm128(kColT0, op_vn, false, op_dh, false, 128, false);                    // dkh  = v_new dh^T
         gemm128(kColT3, op_a, true, op_dvn, true, 64, false);                       // dvb  = A^T dv_new
         umma_commit(&bar);
@@ -370,8 +373,11 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
       const float rs_row = fast_exp2(g_last - gi_row);
       const float eg = fast_exp2(gi_row), qs_row = scale * eg, sk = beta_row * eg;
       float dG = 0.f, dB = 0.f, gdot = 0.f;
-      mma_wait2();
-      __syncthreads();  // every thread is past its reads of h / dh: epilogue A overwrites operand buffers
+      // dAqk is done before the other products: its epilogue (reads Aqk, writes the dS tile; neither is an operand of
+      // this phase) runs under them.  (Measured: starting the dkh / dq2 epilogue early the same way, or dkb's under
+      // the dq / dk products, gains nothing or loses.)
+      if (!mbar_wait(&bar_first, item_parity)) abort.raise();
+      tc_fence_after();
       {
         // dAqk: dS = bf16(scale dAqk D) to its tile, P = dAqk . Aqk to the gate gradient (row sums - column sums)
         float s[8];
@@ -402,6 +408,8 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
         publish_fragment_rows(rows[0], rows[1], s_rs);
         publish_fragment_columns(cols, s_cs);
       }
+      mma_wait2();
+      __syncthreads();  // every thread is past its reads of h / dh: epilogue A overwrites operand buffers
       {
         // dkh and dq2 pieces: the scaled terms go to the register accumulators, their row dots to the gate gradient
         float a[kTailW], b[kTailW];
