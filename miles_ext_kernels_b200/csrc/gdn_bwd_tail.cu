@@ -149,7 +149,6 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
   }
   if (warp == 0) tmem_alloc(&tmem_slot, 512);
   const uint32_t sbase = smem_u32(sm);
-  const int64_t qk_stride = int64_t(num_qk_heads) * kDim, v_stride = int64_t(num_v_heads) * kDim;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
