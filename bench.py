@@ -225,10 +225,10 @@ KERNEL_BYTES.update({
 # was timed; a head configuration that was never captured reports null.
 NCU_TRAFFIC_BYTES_PER_TOKEN = {
     (16, 32): {  # an 8,192-token cut of cfg1
-        "gdn_wy_fwd": (137.0e6 + 151.6e6) / 8192,
+        "gdn_wy_fwd": (137.0e6 + 150.7e6) / 8192,
         "gdn_fwd_ho": (236.2e6 + 225.8e6) / 8192,
         "gdn_bwd_dh": (236.0e6 + 154.8e6) / 8192,
-        "gdn_bwd_tail": (807.8e6 + 123.9e6) / 8192,
+        "gdn_bwd_tail": (807.5e6 + 122.1e6) / 8192,
     },
 }
 KERNEL_FLOPS = {  # per (chunk, value head): dense contractions as 2 m n k
