@@ -23,25 +23,37 @@ namespace mek {
 // ---------------------------------------------------------------------------------------------------------------
 // prep
 // ---------------------------------------------------------------------------------------------------------------
-// One warp per row of 128 bf16: y = bf16(x r), r = 1 / sqrt(sum x^2 + 1e-6), r saved.  Row (token, head) of x sits
-// at token * pitch + head * 128 (x may be a column slice of a packed row); y and rstd are dense.
+// Half a warp per row of 128 bf16 (16-byte loads), two rows per half warp with both loads issued up front:
+// y = bf16(x r), r = 1 / sqrt(sum x^2 + 1e-6), r saved.  Row (token, head) of x sits at token * pitch + head * 128
+// (x may be a column slice of a packed row); y and rstd are dense.
 __global__ void __launch_bounds__(256) l2norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
                                                      float* __restrict__ rstd, int64_t rows, int heads, int64_t pitch) {
-  const int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
-  const int64_t at = (row / heads) * pitch + (row % heads) * kDim;
-  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + at) + lane);
-  const float2 a = unpack_bf16(raw.x), b = unpack_bf16(raw.y);
-  float ss = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+  const int part = threadIdx.x & 15;  // 16-byte piece of the row
+  const int64_t row0 = int64_t(blockIdx.x) * 32 + (threadIdx.x >> 4);
+  uint4 raw[2];
 #pragma unroll
-  for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
-  const float r = 1.0f / sqrtf(ss + 1e-6f);
-  uint2 out;
-  out.x = pack_bf16(a.x * r, a.y * r);
-  out.y = pack_bf16(b.x * r, b.y * r);
-  reinterpret_cast<uint2*>(y + row * kDim)[lane] = out;
-  if (lane == 0) rstd[row] = r;
+  for (int n = 0; n < 2; ++n) {
+    const int64_t row = row0 + 16 * n;
+    raw[n] = make_uint4(0u, 0u, 0u, 0u);
+    if (row < rows) raw[n] = ldg16(x + (row / heads) * pitch + (row % heads) * kDim + part * 8);
+  }
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    const int64_t row = row0 + 16 * n;
+    float v[8];
+    unpack8(raw[n], v);
+    // the same order of additions as a lane of the earlier one-warp-per-row form took: pairs, then a butterfly
+    float ss = (v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]) + (v[4] * v[4] + v[5] * v[5] + v[6] * v[6] + v[7] * v[7]);
+#pragma unroll
+    for (int m = 8; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+    const float r = 1.0f / sqrtf(ss + 1e-6f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= r;
+    if (row < rows) {
+      *reinterpret_cast<uint4*>(y + row * kDim + part * 8) = pack8(v);
+      if (part == 0) rstd[row] = r;
+    }
+  }
 }
 
 // One block per chunk, one thread per value head: g_cs[t, hv] = log2(e) * sum_{s <= t, same chunk} g[s, hv].
@@ -52,10 +64,17 @@ __global__ void gate_cumsum_kernel(const float* __restrict__ g, float* __restric
   const int start = chunk_start[c], len = chunk_len[c];
   for (int hv = threadIdx.x; hv < num_v_heads; hv += blockDim.x) {
     float acc = 0.f;
-    for (int i = 0; i < len; ++i) {
-      const int64_t at = int64_t(start + i) * num_v_heads + hv;
-      acc += g[at];
-      g_cs[at] = acc * kLog2e;
+    for (int i0 = 0; i0 < len; i0 += 8) {  // a batch's loads are issued before the running sum needs the first
+      float gv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) gv[j] = i0 + j < len ? g[int64_t(start + i0 + j) * num_v_heads + hv] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (i0 + j < len) {
+          acc += gv[j];
+          g_cs[int64_t(start + i0 + j) * num_v_heads + hv] = acc * kLog2e;
+        }
+      }
     }
   }
 }
@@ -860,9 +879,10 @@ int mek_gdn_l2norm(const void* x, void* y, float* rstd, int64_t rows, int heads,
   if (rows <= 0 || heads <= 0 || !x || !y || !rstd)
     return fail(MEK_ERR_INVALID, "l2norm: rows=%lld, heads=%d or a null pointer", (long long)rows, heads);
   const int64_t pitch = x_pitch != 0 ? x_pitch : int64_t(heads) * kDim;
-  if (pitch < int64_t(heads) * kDim || pitch % 4 != 0)
-    return fail(MEK_ERR_INVALID, "l2norm: x_pitch %lld does not hold %d heads of 128", (long long)x_pitch, heads);
-  l2norm_kernel<<<unsigned((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (pitch < int64_t(heads) * kDim || pitch % 8 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0)
+    return fail(MEK_ERR_INVALID, "l2norm: x_pitch %lld does not hold %d heads of 128 in 16-byte pieces", (long long)x_pitch,
+                heads);
+  l2norm_kernel<<<unsigned((rows + 31) / 32), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), rstd, rows, heads, pitch);
   return launched("l2norm");
 }
