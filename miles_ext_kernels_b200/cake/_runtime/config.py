@@ -102,8 +102,9 @@ def deterministic_mode(args: Any) -> bool:
 def _variant_help(spec: OpSpec) -> str:
     preferred = "fast" if "fast" in spec.cli_choices else "det"
     return (f"Variant of the cake {spec.name} kernels ({spec.summary}) under {spec.selector}: 'det' repeats bit "
-            f"for bit for identical inputs, 'fast' is faster. Default: '{preferred}', or 'det' under "
-            "--deterministic-mode, which rejects 'fast'.")
+            f"for bit for identical inputs; 'fast' may give that up for speed (in this build both run the same "
+            f"kernels, which reduce in a fixed order). Default: '{preferred}', or 'det' under --deterministic-mode, "
+            "which rejects 'fast'.")
 
 
 def add_arguments(parser: Any) -> None:
