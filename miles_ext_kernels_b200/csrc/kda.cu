@@ -26,55 +26,59 @@
 namespace mek {
 
 // ---------------------------------------------------------------------------------------------------------------
-// prep: one block per (chunk, head), one thread per key channel
+// prep: one block per (chunk, head), one thread per pair of key channels
 // ---------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) kda_prep_kernel(
+__global__ void __launch_bounds__(64) kda_prep_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const float* __restrict__ g,
     float* __restrict__ g2, __nv_bfloat16* __restrict__ qg, __nv_bfloat16* __restrict__ kg,
     __nv_bfloat16* __restrict__ kr, float* __restrict__ gl2, const int32_t* __restrict__ chunk_start,
     const int32_t* __restrict__ chunk_len, int num_heads) {
-  const int c = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  // a thread owns two neighbouring key channels: 4-byte bf16 pairs and 8-byte gate pairs (whole lines per warp)
+  const int c = blockIdx.x, h = blockIdx.y, d = 2 * threadIdx.x;
   const int start = chunk_start[c], len = chunk_len[c];
   if (len <= 0) return;
   const int64_t stride = int64_t(num_heads) * kDim;
   const int64_t base = int64_t(start) * stride + h * kDim + d;
+  auto pair_at = [](const __nv_bfloat16* p) { return unpack_bf16(*reinterpret_cast<const uint32_t*>(p)); };
+  auto put_pair = [](__nv_bfloat16* p, float x, float y) { *reinterpret_cast<uint32_t*>(p) = pack_bf16(x, y); };
   // tokens in batches of eight: a batch's loads are all issued before the running sum needs the first of them
-  float acc = 0.f;
+  float acc0 = 0.f, acc1 = 0.f;
   for (int i0 = 0; i0 < len; i0 += 8) {
-    float gv[8], qv[8], kv[8];
+    float2 gv[8], qv[8], kv[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const bool in = i0 + j < len;
       const int64_t at = base + (in ? i0 + j : i0) * stride;
-      gv[j] = in ? g[at] : 0.f;
-      qv[j] = __bfloat162float(q[at]);
-      kv[j] = __bfloat162float(k[at]);
+      gv[j] = in ? *reinterpret_cast<const float2*>(g + at) : make_float2(0.f, 0.f);
+      qv[j] = pair_at(q + at);
+      kv[j] = pair_at(k + at);
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       if (i0 + j < len) {
         const int64_t at = base + (i0 + j) * stride;
-        acc += gv[j];
-        const float gi = acc * kLog2e, e = fast_exp2(gi);
-        g2[at] = gi;
-        qg[at] = __float2bfloat16_rn(qv[j] * e);
-        kg[at] = __float2bfloat16_rn(kv[j] * e);
+        acc0 += gv[j].x, acc1 += gv[j].y;
+        const float g0 = acc0 * kLog2e, g1 = acc1 * kLog2e, e0 = fast_exp2(g0), e1 = fast_exp2(g1);
+        *reinterpret_cast<float2*>(g2 + at) = make_float2(g0, g1);
+        put_pair(qg + at, qv[j].x * e0, qv[j].y * e1);
+        put_pair(kg + at, kv[j].x * e0, kv[j].y * e1);
       }
     }
   }
-  const float gl = acc * kLog2e;
-  gl2[(int64_t(c) * num_heads + h) * kDim + d] = gl;
+  const float gl0 = acc0 * kLog2e, gl1 = acc1 * kLog2e;
+  *reinterpret_cast<float2*>(gl2 + (int64_t(c) * num_heads + h) * kDim + d) = make_float2(gl0, gl1);
   for (int i0 = 0; i0 < len; i0 += 8) {
-    float gv[8], kv[8];
+    float2 gv[8], kv[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int64_t at = base + (i0 + j < len ? i0 + j : i0) * stride;
-      gv[j] = g2[at];
-      kv[j] = __bfloat162float(k[at]);
+      gv[j] = *reinterpret_cast<const float2*>(g2 + at);
+      kv[j] = pair_at(k + at);
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j)
-      if (i0 + j < len) kr[base + (i0 + j) * stride] = __float2bfloat16_rn(kv[j] * fast_exp2(gl - gv[j]));
+      if (i0 + j < len)
+        put_pair(kr + base + (i0 + j) * stride, kv[j].x * fast_exp2(gl0 - gv[j].x), kv[j].y * fast_exp2(gl1 - gv[j].y));
   }
 }
 
@@ -1299,7 +1303,7 @@ int mek_kda_prep(const MekGdnDims* d, const void* q, const void* k, const float*
                  void* kr, float* gl2, void* stream) {
   using namespace mek;
   if (int rc = check_kda(d, "kda_prep")) return rc;
-  kda_prep_kernel<<<dim3(d->num_chunks, d->num_v_heads), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  kda_prep_kernel<<<dim3(d->num_chunks, d->num_v_heads), 64, 0, static_cast<cudaStream_t>(stream)>>>(
       In(q), In(k), g, g2, Out(qg), Out(kg), Out(kr), gl2, d->chunk_start, d->chunk_len, d->num_v_heads);
   return launched("kda_prep");
 }
