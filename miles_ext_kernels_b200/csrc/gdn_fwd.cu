@@ -91,14 +91,6 @@ struct WySmem {
   static constexpr uint32_t kBytes = kScal + 512;
 };
 
-// fp32 L[i][j] as a K-major tf32 operand: two blocks of 32 columns (8 KiB each), 128 bytes per row, the 16-byte
-// chunks of a row XOR-swizzled by the row (the layout of every operand tile, with 4-byte elements)
-__device__ __forceinline__ int wy_l_index(int i, int j) {
-  return (j >> 5) * 2048 + i * 32 + ((((j & 31) >> 2) ^ (i & 7)) << 2) + (j & 3);
-}
-// float index of element (row, k) of a one-block fp32 operand of 32 contraction columns
-__device__ __forceinline__ int f32_block_index(int row, int k) { return row * 32 + (((k >> 2) ^ (row & 7)) << 2) + (k & 3); }
-
 // Four CTAs per SM (50 KB of shared memory each) hide each other's global-load and solve latencies; tensor memory:
 // 128 columns each.
 struct WyMaps {

@@ -105,10 +105,10 @@ struct KdaIntraSmem {
   // after the block product (the operands above are dead):
   static constexpr uint32_t kA = kQK;                               // [64][64] bf16
   static constexpr uint32_t kKB = kQK + 8192;                       // [64][128] beta kg
-  static constexpr uint32_t kL = kStack;                            // fp32 [64][68]
+  static constexpr uint32_t kL = kStack;                            // fp32 [64][64], the TF32 operand layout (16 KiB)
   static constexpr uint32_t kSqk = kG;                              // fp32 [64][65]
   static constexpr uint32_t kSkk = kSqk + 64 * 65 * 4;
-  static_assert(kKB + 16384 <= kStack && 64 * 68 * 4 <= 24576 && 2 * 64 * 65 * 4 <= 64 * kGRow * 4, "overlays fit");
+  static_assert(kKB + 16384 <= kStack && 64 * 64 * 4 <= 24576 && 2 * 64 * 65 * 4 <= 64 * kGRow * 4, "overlays fit");
 };
 
 // element (row, d) of a bf16 tile made of 64-column swizzled blocks `block_stride` bytes apart
@@ -361,13 +361,16 @@ __global__ void __launch_bounds__(kIntraThreads, 2) kda_intra_kernel(
   for (int t = tid; t < 64 * 8; t += kIntraThreads) {
     const int i = t >> 3, jj = t & 7;
     const float bi = s_beta[i];
-    float x[8];
+    float x[8], l8[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const int j = jj * 8 + e;
       x[e] = j <= i ? scale * s_qk[i * 65 + j] : 0.f;
-      s_l[i * 68 + j] = j < i ? bi * s_kk[i * 65 + j] : 0.f;
+      l8[e] = j < i ? bi * s_kk[i * 65 + j] : 0.f;
     }
+    // four consecutive columns are contiguous in the operand layout
+    *reinterpret_cast<float4*>(s_l + wy_l_index(i, jj * 8)) = make_float4(l8[0], l8[1], l8[2], l8[3]);
+    *reinterpret_cast<float4*>(s_l + wy_l_index(i, jj * 8 + 4)) = make_float4(l8[4], l8[5], l8[6], l8[7]);
     reinterpret_cast<uint4*>(aqk_out + tile * 4096 + i * 64)[jj] = pack8(x);
   }
   __syncthreads();
@@ -391,15 +394,25 @@ __global__ void __launch_bounds__(kIntraThreads, 2) kda_intra_kernel(
     for (int j = 0; j < 8; ++j) x[j] *= b;
     set_tile_chunk(sm + KdaIntraSmem::kVB, 8192, r, cc, pack8(x));
   }
-  // A = (I + L)^-1 : thread c solves (I + L) x = e_c by forward substitution (columns are independent)
+  // A = (I + L)^-1 by blocks of 32, as in gdn_wy_kernel: with I + L = [[M11, 0], [L21, M22]],
+  //     A = [[X11, 0], [X21, X22]],  X11 = M11^-1, X22 = M22^-1 (fp32 forward substitution, 64 threads, 496 FMAs each)
+  //     X21 = -X22 (L21 X11)  (two tensor-core products with TF32 operands; A is rounded to bf16 afterwards)
+  // The products' operands take the quarters of L that are dead by then: L11 -> B1 = X11^T, the never-used upper
+  // right -> X22 (rows 32..63 of A2, whose rows 0..31 are whatever lies in L21: a result row depends on its own
+  // operand row only, and rows 0..31 of the results are not read), L22 -> B2 = T^T.
+  float* s_b1 = s_l;
+  float* s_a2 = s_l + 1024;
+  float* s_b2 = s_l + 3072;
+  uint8_t* a_tile = sm + KdaIntraSmem::kA;
   if (tid < 64) {
-    float x[64];
+    const int b = tid >> 5, c = tid & 31, base = 32 * b;
+    float x[32];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      float acc0 = (i == tid) ? 1.f : 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    for (int i = 0; i < 32; ++i) {
+      float acc0 = (i == c) ? 1.f : 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
       for (int j = 0; j < i; j += 4) {
-        const float4 l = *reinterpret_cast<const float4*>(s_l + i * 68 + j);
+        const float4 l = *reinterpret_cast<const float4*>(s_l + wy_l_index(base + i, base + j));
         acc0 = fmaf(-l.x, x[j], acc0);
         if (j + 1 < i) acc1 = fmaf(-l.y, x[j + 1], acc1);
         if (j + 2 < i) acc2 = fmaf(-l.z, x[j + 2], acc2);
@@ -407,15 +420,81 @@ __global__ void __launch_bounds__(kIntraThreads, 2) kda_intra_kernel(
       }
       x[i] = (acc0 + acc1) + (acc2 + acc3);
     }
-    uint8_t* at = sm + KdaIntraSmem::kA;
+    asm volatile("bar.sync 1, 64;" ::: "memory");  // every solving thread has read L11 / L22: their space is rewritten
+    const int col = base + c;
 #pragma unroll
-    for (int i = 0; i < 64; ++i)
-      *reinterpret_cast<__nv_bfloat16*>(at + sw128_offset(i, tid >> 3) + (tid & 7) * 2) = __float2bfloat16_rn(x[i]);
+    for (int i = 0; i < 32; ++i)
+      *reinterpret_cast<__nv_bfloat16*>(a_tile + sw128_offset(base + i, col >> 3) + (col & 7) * 2) =
+          __float2bfloat16_rn(x[i]);
+    if (b == 0) {  // row c of B1 = column c of X11
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        *reinterpret_cast<float4*>(s_b1 + f32_block_index(c, i)) = make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]);
+    } else {  // column c of X22 in the rows 32..63 of A2
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s_a2[f32_block_index(32 + i, c)] = x[i];
+    }
+  } else {
+    // the upper right block of A is zero
+    for (int i = tid - 64; i < 32 * 4; i += kIntraThreads - 64)
+      set_tile_chunk(a_tile, 8192, i >> 2, 4 + (i & 3), make_uint4(0u, 0u, 0u, 0u));
   }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+
+  {
+    const uint32_t l_addr = sbase + KdaIntraSmem::kL;
+    const uint32_t b1_addr = l_addr, a2_addr = l_addr + 4096, b2_addr = l_addr + 12288;
+    constexpr uint32_t kColT = 128, kColX = 160;  // free until the w / u products
+    if (tid == 0) {  // T' = L[:, 0:32] X11 (rows 32..63 are T = L21 X11)
+      const uint32_t idesc = umma_idesc_tf32(64, 32);
+      for (uint32_t k0 = 0; k0 < 32; k0 += 8)
+        umma_tf32(tmem + kColT, umma_desc_sw128(l_addr + k0 * 4, 16u, kSbo), umma_desc_sw128(b1_addr + k0 * 4, 16u, kSbo),
+                  idesc, k0 > 0 ? 1u : 0u);
+      umma_commit(&bar);
+    }
+    if (warp < 4) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar, 1)) && ok;
+      tc_fence_after();
+      float tt[32];
+      tmem_ld32(tmem_addr(tmem, warp, kColT), tt);
+      tmem_ld_wait();
+      if (warp >= 2 && lane < 16) {  // row i = 16 warp + lane of T' -> column i - 32 of B2 = T^T
+        const int kk = 16 * warp + lane - 32;
+#pragma unroll
+        for (int n = 0; n < 32; ++n) s_b2[f32_block_index(n, kk)] = tt[n];
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (tid == 0) {  // X' = -A2 T (rows 32..63 are X21)
+      const uint32_t idesc = umma_idesc_tf32(64, 32, /*neg_a=*/true);
+      for (uint32_t k0 = 0; k0 < 32; k0 += 8)
+        umma_tf32(tmem + kColX, umma_desc_sw128(a2_addr + k0 * 4, 16u, kSbo), umma_desc_sw128(b2_addr + k0 * 4, 16u, kSbo),
+                  idesc, k0 > 0 ? 1u : 0u);
+      umma_commit(&bar);
+    }
+    if (warp < 4) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar, 0)) && ok;
+      tc_fence_after();
+      float xv[32];
+      tmem_ld32(tmem_addr(tmem, warp, kColX), xv);
+      tmem_ld_wait();
+      if (warp >= 2 && lane < 16) {
+        const int i = 16 * warp + lane;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) set_tile_chunk(a_tile, 8192, i, j, pack8(xv + 8 * j));
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  }
 
   if (tid == 0) {
     const Operand a{sbase + KdaIntraSmem::kA, 8192};

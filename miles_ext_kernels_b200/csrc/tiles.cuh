@@ -87,6 +87,14 @@ __device__ __forceinline__ void unpack8(uint4 w, float* v) {
 // bf16 rounding of a value kept in fp32 (the kernels' one rounding primitive, cvt.rn.bf16.f32).
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+// fp32 L[i][j] as a K-major tf32 operand: two blocks of 32 columns (8 KiB each), 128 bytes per row, the 16-byte
+// chunks of a row XOR-swizzled by the row (the layout of every operand tile, with 4-byte elements)
+__device__ __forceinline__ int wy_l_index(int i, int j) {
+  return (j >> 5) * 2048 + i * 32 + ((((j & 31) >> 2) ^ (i & 7)) << 2) + (j & 3);
+}
+// float index of element (row, k) of a one-block fp32 operand of 32 contraction columns
+__device__ __forceinline__ int f32_block_index(int row, int k) { return row * 32 + (((k >> 2) ^ (row & 7)) << 2) + (k & 3); }
+
 // A block-wide abort flag for bounded waits: a thread whose wait ran out raises it, every thread reads it right
 // after the next __syncthreads and leaves its loop in step with the others.
 struct Abort {
