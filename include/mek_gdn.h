@@ -193,8 +193,10 @@ int mek_gdn_scan_compose(const MekGdnDims* seg_dims, const int32_t* seq_seg_star
                          const float* g_cs, float* out, int reverse, int warm_chunks, float warm_log2, void* stream);
 
 /* Gradient tail per (chunk, key head): dq, dk bf16 [T, H, 128] (fp32 sum over the key head's value heads, the L2
- * norm's pull-back when q_raw / k_raw / rstd_q / rstd_k are given, one rounding), dv bf16 [T, HV, 128], dbeta and
- * dg fp32 [T, HV] (dg includes the in-chunk suffix sum).  q, k are the normalised rows the forward used.
+ * norm's pull-back r (D - y (D . y)) when rstd_q / rstd_k are given, one rounding), dv bf16 [T, HV, 128], dbeta and
+ * dg fp32 [T, HV] (dg includes the in-chunk suffix sum).  q, k are the normalised rows the forward used; the
+ * pull-back takes y from them (the bf16 unit rows the products read), so q_raw / k_raw -- which must accompany the
+ * rstd pointers, as in the reference's signature -- are not read.
  * Replaces the `dqkwg`, `wy_bwd` and `finalize` launches (reference: ops.py:1642-1727). */
 int mek_gdn_bwd_tail(const MekGdnDims* dims, const void* q, const void* k, const void* v, const float* beta,
                      const float* g_cs, const void* a, const void* aqk, const void* w, const void* u,

@@ -626,25 +626,21 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
         mma_wait();
         // this thread's columns of its row: in the raw operands and in the outputs (token pitches may differ:
         // either may be a column slice of a packed row)
-        const int64_t raw_at = int64_t(start + row) * raw_pitch + hq * kDim + lcol;
         const int64_t out_at = int64_t(start + row) * dqk_pitch + hq * kDim + lcol;
-        // acc: this thread's columns of the fp32 group sum.  With the op's L2 norm: dx = r (D - y (D . y)),
-        // y = x r from the raw row and the saved r; the dot product spans the row's column pieces.
-        auto finish = [&](float* acc, const __nv_bfloat16* raw_rows, const float* rstd, __nv_bfloat16* out) {
+        // acc: this thread's columns of the fp32 group sum.  With the op's L2 norm: dx = r (D - y (D . y)) with the
+        // saved r and y = the unit row as the forward used it (the bf16 tile this pair's products read: no second
+        // read of the raw rows, whose row-per-thread pieces would touch a line per lane); the dot product spans the
+        // row's column pieces.
+        auto finish = [&](float* acc, const uint8_t* unit_rows, const float* rstd, __nv_bfloat16* out) {
           if (rstd != nullptr) {
             const float r = live ? rstd[int64_t(start + row) * num_qk_heads + hq] : 0.f;
             float y[kTailW];
             float dot = 0.f;
 #pragma unroll
             for (int jj = 0; jj < kTailJ; ++jj) {
-              uint4 x = make_uint4(0u, 0u, 0u, 0u);
-              if (live) x = ldg16(raw_rows + raw_at + jj * 8);
-              unpack8(x, y + jj * 8);
+              unpack8(tile_chunk(unit_rows, 8192, row, lchunk + jj), y + jj * 8);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                y[jj * 8 + e] *= r;
-                dot = fmaf(acc[jj * 8 + e], y[jj * 8 + e], dot);
-              }
+              for (int e = 0; e < 8; ++e) dot = fmaf(acc[jj * 8 + e], y[jj * 8 + e], dot);
             }
             __syncthreads();  // the previous reduction has read s_red
             s_red[cq * 64 + row] = dot;
@@ -665,7 +661,7 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
 #pragma unroll
           for (int j = 0; j < kTailW; ++j) dq_reg[j] += b[j];
         }
-        finish(dq_reg, q_raw, rstd_q, dq);
+        finish(dq_reg, q_tile, rstd_q, dq);
         {
           float b[kTailW];
           tail_tmem_ld(tmem_addr(tmem, warp, kColDK + ch * kTailW), b);
@@ -673,7 +669,7 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
 #pragma unroll
           for (int j = 0; j < kTailW; ++j) dk_reg[j] += b[j];
         }
-        finish(dk_reg, k_raw, rstd_k, dk);
+        finish(dk_reg, k_tile, rstd_k, dk);
       }
     }
   }
