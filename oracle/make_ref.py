@@ -1,6 +1,6 @@
 """Recipe for ``oracle/_ref/``: the reference's own CPU implementation of the GDN path, as it lies in a checkout.
 
-    python oracle/make_ref.py [<reference root>]        (default: the MILES_EXT_KERNELS_REFERENCE variable, else /root/reference)
+    python oracle/make_ref.py [<reference root>]        (default: the MILES_EXT_KERNELS_REFERENCE variable, else DEFAULT_ROOT)
 
 The reference is Python: its torch emulation of the nine GDN programs (``cake_fake_backend.py`` of the deterministic
 context-parallel package) runs on the host through the public entry point ``chunk_gated_delta_rule(...,
@@ -13,6 +13,8 @@ there.  Test infrastructure: only tests, the smoke check and the CPU legs of ``b
 """
 
 from __future__ import annotations
+
+DEFAULT_ROOT = "/root/reference"  # where the build machine mounts the checkout
 
 import os
 import shutil
@@ -55,7 +57,7 @@ print("\n".join(sorted(f for f in opened if "__pycache__" not in f)))
 
 
 def main(argv: list[str]) -> int:
-    root = Path(argv[1] if len(argv) > 1 else os.environ.get("MILES_EXT_KERNELS_REFERENCE", "/root/reference")).resolve()
+    root = Path(argv[1] if len(argv) > 1 else os.environ.get("MILES_EXT_KERNELS_REFERENCE", DEFAULT_ROOT)).resolve()
     if not (root / "miles_ext_kernels" / "cake").is_dir():
         print(f"make_ref: no reference checkout at {root}; oracle/_ref is left as it is", file=sys.stderr)
         return 1
