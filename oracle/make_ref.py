@@ -14,8 +14,6 @@ there.  Test infrastructure: only tests, the smoke check and the CPU legs of ``b
 
 from __future__ import annotations
 
-DEFAULT_ROOT = "/root/reference"  # where the build machine mounts the checkout
-
 import os
 import shutil
 import subprocess
@@ -27,6 +25,8 @@ TARGET = HERE / "_ref"
 
 _TRACE = r"""
 import sys, torch
+
+DEFAULT_ROOT = "/root/reference"  # where the build machine mounts the checkout
 root = sys.argv[1]
 opened = set()
 def audit(event, args):  # data files (registries, manifests) the modules read at import or call time
