@@ -20,13 +20,12 @@ import subprocess
 import sys
 from pathlib import Path
 
+DEFAULT_ROOT = "/root/reference"  # where the build machine mounts the checkout
 HERE = Path(__file__).resolve().parent
 TARGET = HERE / "_ref"
 
 _TRACE = r"""
 import sys, torch
-
-DEFAULT_ROOT = "/root/reference"  # where the build machine mounts the checkout
 root = sys.argv[1]
 opened = set()
 def audit(event, args):  # data files (registries, manifests) the modules read at import or call time
