@@ -98,3 +98,32 @@ def test_the_planner_engages_on_few_long_chains_and_the_recomputed_backward_foll
         assert torch.equal(saved[name], recomputed[name]), name
         m = O.metrics(saved[name].float(), serial[name].float())
         assert m["finite"] and m["rel_rms"] <= 2e-3, (name, m)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("reverse", [False, True])
+def test_a_run_of_segments_composed_in_one_launch_equals_the_two_stitches(reverse):
+    """``mek_gdn_scan_compose`` writes the (B, M) of a run of segments per head, interleaved, in one launch: the same
+    bits as the stitch kernel run once from zero with the offsets (B) and once from the identity without them (M)."""
+    from miles_ext_kernels_b200.cake._impl.gdn import meta as meta_module
+    from miles_ext_kernels_b200.cake._impl.gdn import native, scan
+    from miles_ext_kernels_b200.cake._impl.gdn.stages import dims_of
+
+    dev = torch.device("cuda")
+    heads, tokens = 3, 64 * 40
+    meta = meta_module.chunk_meta(torch.tensor((0, tokens)), (0, tokens), 1, tokens, dev)
+    plan = scan.fragment_plan(0, meta.num_chunks, heads, dev)
+    assert plan.segments > 1
+    dims = dims_of(meta, heads, heads, 1.0)
+    seg_dims = scan.segment_dims(dims, plan)
+    torch.manual_seed(5)
+    summary = (0.3 * torch.randn(plan.segments, heads, 2, 128, 128, device=dev)).contiguous()
+    g_cs = -torch.rand(tokens, heads, device=dev)  # mild gates: the warm-up rule does not apply, M matters
+    one = scan.compose_summary(seg_dims, plan, summary, g_cs, reverse=reverse)
+    two = torch.empty((2, heads, 128, 128), dtype=torch.float32, device=dev)
+    for which, mode in ((0, 4), (1, 7)):
+        native.launch("gdn_scan_stitch", seg_dims, 1, plan.seq_seg_start, summary, None, g_cs, None, two[which],
+                      int(reverse), plan.warm_chunks, plan.warm_log2, mode, device=dev)
+    torch.cuda.synchronize()
+    assert torch.equal(one[:, 0], two[0]) and torch.equal(one[:, 1], two[1])
+    assert float(one[:, 1].abs().max()) > 0  # the transfer part is not trivially zero here
