@@ -16,10 +16,12 @@
 namespace mek {
 
 // One CTA per (sequence, value head), warp-specialised like the forward scan: two epilogue warpgroups (thread
-// (k, half) holds row k of one half of the V columns of the fp32 adjoint state), one MMA-issuing warp and one copy
-// warp; the roles meet on mbarriers only.  Per chunk, last to first:
+// (k, half) holds row k of one half of the V columns of the fp32 adjoint state), two MMA-issuing threads and one
+// copy warp; the roles meet on mbarriers only.  The step's first two products are independent chains of
+// tcgen05.mma per 64-lane half of the accumulators, so each issuing thread takes one half and the wait for them
+// is about half as long; the third product is issued by the first thread alone.  Per chunk, last to first:
 //   A  epilogue   dh_tape = bf16(dh) -> shared                                            -> "state tile ready"
-//      issuer     D1 = k dh_tape, D1b = Aqk^T do
+//      issuers    D1 = k dh_tape, D1b = Aqk^T do
 //      copy warp  dh_tape tile -> the tape (TMA store); the tiles of the chunk walked next (TMA loads)
 //   B  epilogue   dv_new = bf16(bf16(D1b) + rowscale D1) -> shared; do -> bf16(qscale do) in place  -> "dv tile ready"
 //      issuer     D2 = q^T do_g - w^T dv_new
@@ -46,9 +48,10 @@ struct BwdDhMaps {
 };
 
 constexpr int kAdjEpilogueThreads = 256;             // warps 0..7
-constexpr int kAdjIssuer = kAdjEpilogueThreads;      // warp 8, lane 0: every tcgen05.mma of the walk
-constexpr int kAdjMover = kAdjEpilogueThreads + 32;  // warp 9, lane 0: every TMA load and store
-constexpr int kAdjThreads = kAdjEpilogueThreads + 64;
+constexpr int kAdjIssuer = kAdjEpilogueThreads;       // warp 8, lane 0: the products of the lower lane halves, and D2
+constexpr int kAdjMover = kAdjEpilogueThreads + 32;   // warp 9, lane 0: every TMA load and store
+constexpr int kAdjIssuer2 = kAdjEpilogueThreads + 64;  // warp 10, lane 0: the first products' upper lane halves
+constexpr int kAdjThreads = kAdjEpilogueThreads + 96;
 
 __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
     const __grid_constant__ BwdDhMaps maps, const float* __restrict__ g_cs,
@@ -101,7 +104,7 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
     mbar_init(&bar_load[1], 1);
     mbar_init(&bar_h, kAdjEpilogueThreads);
     mbar_init(&bar_vs, kAdjEpilogueThreads);
-    mbar_init(&bar_d1, 1);
+    mbar_init(&bar_d1, 2);  // one commit from each issuing thread
     mbar_init(&bar_d2, 1);
     mbar_init(&bar_free_h, 1);
     mbar_init(&bar_free_dv, 1);
@@ -129,12 +132,12 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
       const Operand op_aqk{sst + BwdDhSmem::kAqk, 8192};
       if (!abort.wait(&bar_h, par)) break;
       tc_fence_after();
-      // both [64 x 128] products as two N = 64 halves with alternating instructions: V columns 0..63 -> lanes
-      // 0..15, 64..127 -> lanes 16..31
-      umma_gemm_pair<64, 64>(tmem + kD1, op_k, false, op_dh, true, 128, false, false, tmem + kD1 + kUpper, op_k, false,
-                             operand_at(op_dh, 0, 1), true, 128, false, false);          // k dh_tape
-      umma_gemm_pair<64, 64>(tmem + kD1b, op_aqk, true, op_do, true, 64, false, false, tmem + kD1b + kUpper, op_aqk,
-                             true, operand_at(op_do, 0, 1), true, 64, false, false);       // Aqk^T do
+      // Both [64 x 128] products as two N = 64 halves: V columns 0..63 -> lanes 0..15 (this thread), 64..127 ->
+      // lanes 16..31 (the second issuing thread).  A thread alternates between its halves of the two products, so
+      // that neither chain of dependent instructions waits for the other: 12 instructions per thread instead of 24
+      // from one.
+      umma_gemm_pair<64, 64>(tmem + kD1, op_k, false, op_dh, true, 128, false, false, tmem + kD1b, op_aqk, true, op_do,
+                             true, 64, false, false);   // k dh_tape | Aqk^T do, lower halves
       umma_commit(&bar_d1);
       if (!abort.wait(&bar_vs, par)) break;
       tc_fence_after();
@@ -143,6 +146,18 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
       umma_gemm<128, 128>(tmem + kD2, op_q, true, op_do, true, 64, false);                  // q^T do_g
       umma_gemm<128, 128>(tmem + kD2, op_w, true, op_dv, true, 64, true, /*neg_a=*/true);   // - w^T dv_new
       umma_commit(&bar_d2);
+    }
+  } else if (tid == kAdjIssuer2) {
+    for (int c = c_end - 1; c >= c_begin; --c) {
+      const uint32_t par = uint32_t(c_end - 1 - c) & 1u;
+      const uint32_t sst = sbase + par * BwdDhSmem::kStage;
+      const Operand op_k{sst + BwdDhSmem::kK, 8192}, op_do{sst + BwdDhSmem::kDO, 8192};
+      const Operand op_aqk{sst + BwdDhSmem::kAqk, 8192};
+      if (!abort.wait(&bar_h, par)) break;
+      tc_fence_after();
+      umma_gemm_pair<64, 64>(tmem + kD1 + kUpper, op_k, false, operand_at(op_dh, 0, 1), true, 128, false, false,
+                             tmem + kD1b + kUpper, op_aqk, true, operand_at(op_do, 0, 1), true, 64, false, false);
+      umma_commit(&bar_d1);  // these products end before the step's second group is issued: its commit frees the stage
     }
   } else if (tid == kAdjMover) {
     auto load = [&](int c, uint32_t stage) {
