@@ -17,13 +17,14 @@ namespace mek {
 
 // One CTA per (sequence, value head), warp-specialised like the forward scan: two epilogue warpgroups (thread
 // (k, half) holds row k of one half of the V columns of the fp32 adjoint state), two MMA-issuing threads and one
-// copy warp; the roles meet on mbarriers only.  The step's first two products are independent chains of
-// tcgen05.mma per 64-lane half of the accumulators, so each issuing thread takes one half and the wait for them
-// is about half as long; the third product is issued by the first thread alone.  Per chunk, last to first:
+// copy warp; the roles meet on mbarriers only.  The step's first two products are independent chains of N = 128
+// instructions into two accumulators, one chain per issuing thread, so the wait for them is as long as the longer
+// chain; the third product is issued by the first thread alone.  Per chunk, last to first:
 //   A  epilogue   dh_tape = bf16(dh) -> shared                                            -> "state tile ready"
 //      issuers    D1 = k dh_tape, D1b = Aqk^T do
+//      epilogue   meanwhile: do_g = bf16(qscale do) -> its own tile
 //      copy warp  dh_tape tile -> the tape (TMA store); the tiles of the chunk walked next (TMA loads)
-//   B  epilogue   dv_new = bf16(bf16(D1b) + rowscale D1) -> shared; do -> bf16(qscale do) in place  -> "dv tile ready"
+//   B  epilogue   dv_new = bf16(bf16(D1b) + rowscale D1) -> shared                          -> "dv tile ready"
 //      issuer     D2 = q^T do_g - w^T dv_new
 //      copy warp  dv_new tile -> the tape (TMA store; a ragged chunk's rows are stored by the epilogue threads)
 //   C  epilogue   dh = gamma dh + D2.
@@ -32,12 +33,13 @@ struct BwdDhSmem {
   static constexpr uint32_t kK = 0;                 // [64][128] k        K-major A of k dh
   static constexpr uint32_t kQ = 16384;             // [64][128] q        MN-major A of q^T do_g
   static constexpr uint32_t kW = 2 * 16384;         // [64][128] w        MN-major A of w^T dv_new (negated)
-  static constexpr uint32_t kDO = 3 * 16384;        // [64][128] do -> bf16(qscale do) in place
+  static constexpr uint32_t kDO = 3 * 16384;        // [64][128] do
   static constexpr uint32_t kAqk = 4 * 16384;       // [64][64]
   static constexpr uint32_t kDV = 2 * kStage;       // [64][128] dv_new
   static constexpr uint32_t kDH = kDV + 16384;      // [128][128] bf16(dh), 2 blocks of 16 KiB (one per V half)
   static constexpr uint32_t kG = kDH + 32768;       // gates[2][128]
-  static constexpr uint32_t kBytes = kG + 1024;
+  static constexpr uint32_t kDOG = kG + 1024;       // [64][128] bf16(qscale do)
+  static constexpr uint32_t kBytes = kDOG + 16384;
 };
 
 struct BwdDhMaps {
@@ -48,9 +50,9 @@ struct BwdDhMaps {
 };
 
 constexpr int kAdjEpilogueThreads = 256;             // warps 0..7
-constexpr int kAdjIssuer = kAdjEpilogueThreads;       // warp 8, lane 0: the products of the lower lane halves, and D2
+constexpr int kAdjIssuer = kAdjEpilogueThreads;       // warp 8, lane 0: D1 and D2
 constexpr int kAdjMover = kAdjEpilogueThreads + 32;   // warp 9, lane 0: every TMA load and store
-constexpr int kAdjIssuer2 = kAdjEpilogueThreads + 64;  // warp 10, lane 0: the first products' upper lane halves
+constexpr int kAdjIssuer2 = kAdjEpilogueThreads + 64;  // warp 10, lane 0: D1b
 constexpr int kAdjThreads = kAdjEpilogueThreads + 96;
 
 __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
@@ -118,10 +120,11 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
   __syncthreads();  // the barriers' initialisation and the tensor-memory base are visible to every role
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  constexpr uint32_t kD1 = 0, kD1b = 128, kD2 = 256;  // tensor-memory columns
-  constexpr uint32_t kUpper = 16u << 16;
+  // tensor-memory columns: D1 and D1b [64 x 128] in lanes 0..15 of each quadrant, D2 [128 x 128] in every lane
+  constexpr uint32_t kD1 = 0, kD1b = 128, kD2 = 256;
   const int c_begin = c_first, c_end = c_last;
   const Operand op_dv{sbase + BwdDhSmem::kDV, 8192}, op_dh{sbase + BwdDhSmem::kDH, 16384};
+  const Operand op_dog{sbase + BwdDhSmem::kDOG, 8192};
 
   if (tid == kAdjIssuer) {
     for (int c = c_end - 1; c >= c_begin; --c) {
@@ -132,18 +135,16 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
       const Operand op_aqk{sst + BwdDhSmem::kAqk, 8192};
       if (!abort.wait(&bar_h, par)) break;
       tc_fence_after();
-      // Both [64 x 128] products as two N = 64 halves: V columns 0..63 -> lanes 0..15 (this thread), 64..127 ->
-      // lanes 16..31 (the second issuing thread).  A thread alternates between its halves of the two products, so
-      // that neither chain of dependent instructions waits for the other: 12 instructions per thread instead of 24
-      // from one.
-      umma_gemm_pair<64, 64>(tmem + kD1, op_k, false, op_dh, true, 128, false, false, tmem + kD1b, op_aqk, true, op_do,
-                             true, 64, false, false);   // k dh_tape | Aqk^T do, lower halves
+      // The two [64 x 128] products of the step's first group go out as one chain of N = 128 instructions each, this
+      // thread's and the second issuing thread's: two chains side by side end sooner than one thread's alternation,
+      // and an N = 128 instruction reads a third less from shared memory than two of N = 64.
+      umma_gemm<64, 128>(tmem + kD1, op_k, false, op_dh, true, 128, false);   // k dh_tape
       umma_commit(&bar_d1);
       if (!abort.wait(&bar_vs, par)) break;
       tc_fence_after();
       // one accumulator for both (two accumulators with alternating instructions and a sum in the epilogue measured
       // slower: the second tensor-memory load costs more than the shorter chain saves)
-      umma_gemm<128, 128>(tmem + kD2, op_q, true, op_do, true, 64, false);                  // q^T do_g
+      umma_gemm<128, 128>(tmem + kD2, op_q, true, op_dog, true, 64, false);                 // q^T do_g
       umma_gemm<128, 128>(tmem + kD2, op_w, true, op_dv, true, 64, true, /*neg_a=*/true);   // - w^T dv_new
       umma_commit(&bar_d2);
     }
@@ -155,8 +156,7 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
       const Operand op_aqk{sst + BwdDhSmem::kAqk, 8192};
       if (!abort.wait(&bar_h, par)) break;
       tc_fence_after();
-      umma_gemm_pair<64, 64>(tmem + kD1 + kUpper, op_k, false, operand_at(op_dh, 0, 1), true, 128, false, false,
-                             tmem + kD1b + kUpper, op_aqk, true, operand_at(op_do, 0, 1), true, 64, false, false);
+      umma_gemm<64, 128>(tmem + kD1b, op_aqk, true, op_do, true, 64, false);   // Aqk^T do
       umma_commit(&bar_d1);  // these products end before the step's second group is issued: its commit frees the stage
     }
   } else if (tid == kAdjMover) {
@@ -237,8 +237,6 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
       int next_start = 0, next_len = 0;
       if (c > c_begin) next_start = chunk_start[c - 1], next_len = chunk_len[c - 1];
       uint8_t* st = sm + stage * BwdDhSmem::kStage;
-      // the previous step's tape store has read the state tile
-      if (tapes && step > 0 && !abort.wait(&bar_free_h, par ^ 1u)) { alive = false; break; }
       // A. dh_tape = bf16(dh): this thread's half row -> shared (block `half`)
 #pragma unroll
       for (int cc = 0; cc < 8; ++cc) set_tile_chunk(sm + BwdDhSmem::kDH, 16384, krow, half * 8 + cc, pack8(dh + 8 * cc));
@@ -255,26 +253,39 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
       tc_fence_before();
       mbar_arrive(&bar_h);
       if (c > c_begin) prefetch_gates(c - 1, stage ^ 1, next_start, next_len);
-      if (!abort.wait(&bar_d1, par)) { alive = false; break; }
       // every epilogue thread's writes of this step (cleared rows, gates) are visible past the barrier they all
-      // arrived on; the previous step's tape store has read the dv_new tile
+      // arrived on
       if (!abort.wait(&bar_h, par)) { alive = false; break; }
+      const float* g2 = s_g2 + stage * 128;
+      // While the first products run: do_g = bf16(qscale do) into its own tile (the products read do itself), and
+      // the gates' factors of this thread's rows.
+      for (int i = tid; i < 64 * 16; i += kAdjEpilogueThreads) {
+        const int r = i >> 4, cc = i & 15;
+        const float qs = kda ? scale : scale * fast_exp2(g2[r]);
+        float x[8];
+        unpack8(tile_chunk(st + BwdDhSmem::kDO, 8192, r, cc), x);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] *= qs;
+        set_tile_chunk(sm + BwdDhSmem::kDOG, 8192, r, cc, pack8(x));
+      }
+      const float g_last = kda ? g2[krow] : g2[len - 1];
+      const int i = quad * 16 + (lane & 15);
+      const int lcol = (lane >> 4) * 64 + half * 32;
+      const bool live = i < len;
+      const bool by_hand = tapes && len < kChunk;  // a ragged chunk: no 64-row box may be stored
+      const float rs = live ? (kda ? 1.f : fast_exp2(g_last - g2[i])) : 0.f;
+      const float gamma = fast_exp2(g_last);
+      // the previous step's tape store has read the dv_new tile
       if (tapes && step > 0 && !abort.wait(&bar_free_dv, par ^ 1u)) { alive = false; break; }
+      if (!abort.wait(&bar_d1, par)) { alive = false; break; }
       tc_fence_after();
 
-      // B. dv_new and do_g
-      const float* g2 = s_g2 + stage * 128;
-      const float g_last = kda ? g2[krow] : g2[len - 1];
+      // B. dv_new
       {
-        const int i = quad * 16 + (lane & 15);
-        const int lcol = (lane >> 4) * 64 + half * 32;
-        const bool live = i < len;
-        const bool by_hand = tapes && len < kChunk;  // a ragged chunk: no 64-row box may be stored
-        const float rs = live ? (kda ? 1.f : fast_exp2(g_last - g2[i])) : 0.f;
         __nv_bfloat16* drow = dv_new + int64_t(start + i) * v_stride + hv * kDim + lcol;
         float a[32], b[32];
-        tmem_ld32(tmem_addr(tmem, warp, kD1 + half * 32), a);
-        tmem_ld32(tmem_addr(tmem, warp, kD1b + half * 32), b);
+        tmem_ld32_halves(tmem_addr(tmem, warp, kD1 + half * 32), a);
+        tmem_ld32_halves(tmem_addr(tmem, warp, kD1b + half * 32), b);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) a[j] = live ? fmaf(rs, a[j], round_bf16(b[j])) : 0.f;
@@ -285,24 +296,15 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
           set_tile_chunk(sm + BwdDhSmem::kDV, 8192, i, (lcol >> 3) + jj, packed);
         }
       }
-      // do -> do_g = bf16(qscale do), in place (Aqk^T do has read do)
-      for (int i = tid; i < 64 * 16; i += kAdjEpilogueThreads) {
-        const int r = i >> 4, cc = i & 15;
-        const float qs = kda ? scale : scale * fast_exp2(g2[r]);
-        float x[8];
-        unpack8(tile_chunk(st + BwdDhSmem::kDO, 8192, r, cc), x);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] *= qs;
-        set_tile_chunk(st + BwdDhSmem::kDO, 8192, r, cc, pack8(x));
-      }
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(&bar_vs);
+      // this step's tape store has read the state tile (long ago: asked here, off the path to the next step's A)
+      if (tapes && !abort.wait(&bar_free_h, par)) { alive = false; break; }
       if (!abort.wait(&bar_d2, par)) { alive = false; break; }
       tc_fence_after();
 
       // C. dh = gamma dh + D2
-      const float gamma = fast_exp2(g_last);
 #pragma unroll
       for (int p = 0; p < 2; ++p) {
         float d[32];

@@ -383,7 +383,8 @@ __global__ void __launch_bounds__(128) gdn_wy_kernel(
 //      copy warp  h_tape tile -> the tape (TMA store); next chunk's w / k / u (/ q / Aqk) tiles (TMA loads)
 //   B  epilogue   v_new = u - D1 -> shared; vs = bf16(rowscale v_new) -> shared   -> "v tiles ready"
 //      issuer     D2 = k^T vs (M=128,N=128,K=64) [+ Aqk v_new for the fused output]
-//      copy warp  v_new tile -> the tape (TMA store; a ragged chunk's rows are stored by the epilogue threads)
+//      copy warp  v_new tile -> the tape, the previous chunk's output tile -> o (TMA stores; a ragged chunk's rows
+//                 are stored by the epilogue threads)
 //   C  epilogue   h = gamma h + D2.
 // The roles meet on mbarriers only (no block barrier inside the walk): the epilogue threads never wait for an
 // instruction to be issued or for a store to leave, only for the two products on the step's dependency chain.
@@ -394,7 +395,8 @@ struct FwdHSmem {
   static constexpr uint32_t kVS = kH + 32768;     // [64][128] bf16(rowscale v_new)
   static constexpr uint32_t kVN = kVS + 16384;    // [64][128] v_new (the tape's source; the fused output's operand)
   static constexpr uint32_t kG = kVN + 16384;     // gates[2][128]: GDN g2 per token [64]; KDA chunk-end gate per channel
-  static constexpr uint32_t kBytes = kG + 1024;
+  static constexpr uint32_t kO = kG + 1024;      // [64][128] the fused output of the previous chunk (its store's source)
+  static constexpr uint32_t kBytes = kO + 16384;
 };
 
 // With `o` != nullptr the walk also writes the op's output, chunk by chunk (the reference's fused `fwd_ho`):
@@ -410,6 +412,7 @@ struct FwdHMaps {
   CUtensorMap aqk;         // tiles [num_tiles * 64, 64], box 64 x 64 (the fused output only)
   CUtensorMap h_out;       // tiles [num_tiles * 128, 128], box 64 x 128: the state tape (stores)
   CUtensorMap v_new_out;   // rows, box 64 x 64: the corrected values' tape (stores)
+  CUtensorMap o_out;       // rows, box 64 x 64: the op's output (stores; the fused output only)
 };
 
 constexpr int kScanEpilogueThreads = 256;            // warps 0..7
@@ -428,7 +431,9 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
   // bar_vs: the v tiles are ready -- every epilogue thread arrives
   // bar_d1 / bar_d2 / bar_o: commits of the step's two products and of the fused output's products
   // bar_free_h / bar_free_vn: the copy warp's store of this step has read the state tile / the v_new tile
-  __shared__ uint64_t bar_load[2], bar_h, bar_vs, bar_d1, bar_d2, bar_o, bar_free_h, bar_free_vn;
+  // bar_out / bar_free_o: the previous chunk's output tile is complete -- every epilogue thread arrives / its store has
+  // read the tile
+  __shared__ uint64_t bar_load[2], bar_h, bar_vs, bar_d1, bar_d2, bar_o, bar_free_h, bar_free_vn, bar_out, bar_free_o;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -473,6 +478,8 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
     mbar_init(&bar_o, 1);
     mbar_init(&bar_free_h, 1);
     mbar_init(&bar_free_vn, 1);
+    mbar_init(&bar_out, kScanEpilogueThreads);
+    mbar_init(&bar_free_o, 1);
     fence_mbar_init();
     abort_flag = 0;
   }
@@ -486,8 +493,9 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
   const uint32_t tmem = tmem_slot;
   const Operand op_h{sbase + FwdHSmem::kH, 16384}, op_vs{sbase + FwdHSmem::kVS, 8192};
   const Operand op_vn{sbase + FwdHSmem::kVN, 8192};
-  // tensor-memory columns: D1 0..63 (lane split), D2 128..255, the fused output's two accumulators (q h_tape at +0,
-  // Aqk v_new at +64, both lane split) in one of two sets at 256 and 384
+  // tensor-memory columns: D1 0..127 (lanes 0..15 of each quadrant), D2 128..255, the fused output's two accumulators
+  // (q h_tape at +0, Aqk v_new at +64, both lane split: logical columns 64..127 in lanes 16..31) in one of two sets
+  // at 256 and 384
   constexpr uint32_t kColO = 256;
   constexpr uint32_t kUpper = 16u << 16;
 
@@ -499,10 +507,9 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
       const Operand op_w{sst + FwdHSmem::kW, 8192}, op_k{sst + FwdHSmem::kK, 8192};
       if (!abort.wait(&bar_h, par)) break;
       tc_fence_after();
-      // D1 = w h_tape as two N = 64 products with alternating instructions: V columns 0..63 -> lanes 0..15,
-      // 64..127 -> lanes 16..31 (columns 0..63 of tensor memory), so every lane of a warp owns a row piece
-      umma_gemm_pair<64, 64>(tmem, op_w, false, op_h, true, 128, false, false, tmem + kUpper, op_w, false,
-                             operand_at(op_h, 0, 1), true, 128, false, false);
+      // D1 = w h_tape as one chain of N = 128 instructions into the columns 0..127 of lanes 0..15 (a chain of eight
+      // dependent instructions is shorter than sixteen alternating between two lane halves)
+      umma_gemm<64, 128>(tmem, op_w, false, op_h, true, 128, false);
       umma_commit(&bar_d1);
       if (fused) {  // q h_tape behind it; the state update's commit covers it (commits are cumulative)
         const Operand op_q{sst + FwdHSmem::kQ, 8192};
@@ -559,6 +566,15 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
           tma_store_wait_read();
         }
         mbar_arrive(&bar_free_vn);
+        if (fused && c > c_begin) {  // the previous chunk's output: complete once its second part is written
+          if (!abort.wait(&bar_out, par ^ 1u)) break;
+          if (chunk_len[c - 1] == kChunk) {  // a ragged chunk's rows are stored by the epilogue threads
+            tma_store_tile128(&maps.o_out, hv * kDim, chunk_start[c - 1], sbase + FwdHSmem::kO, 8192);
+            tma_store_commit();
+            tma_store_wait_read();
+          }
+          mbar_arrive(&bar_free_o);
+        }
       }
     }
     tma_store_wait_all();
@@ -608,12 +624,17 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
     } cur = {0, 0, 0.f}, prev = {0, 0, 0.f};  // of the chunk the walk is at / of the one before it
     // in two parts (16 of this thread's 32 columns each), one per wait of the step: a part is about as long as the
     // wait it fills
+    // Inside the walk a full chunk's output goes to a shared tile that the copy warp stores as one box (a thread's
+    // own stores would touch a line per lane); a ragged chunk's rows, and the walk's last chunk, go out by hand.
     bool alive = true;
-    auto write_output = [&](int c_prev, int part, const Rows& rows) {
+    uint32_t tiles_out = 0;  // output tiles handed to the copy warp so far
+    auto write_output = [&](int c_prev, int part, const Rows& rows, bool in_walk) {
       if (part == 0) {
         if (!abort.wait(&bar_o, phase_o)) alive = false;
         phase_o ^= 1;
         tc_fence_after();
+        // the store of the tile before this one has read it
+        if (alive && in_walk && tiles_out > 0 && !abort.wait(&bar_free_o, (tiles_out - 1) & 1u)) alive = false;
       }
       if (!alive) return;
       const uint32_t set = kColO + uint32_t((c_prev - c_begin) & 1) * 128;
@@ -623,10 +644,18 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 16; ++j) a[j] = fmaf(rows.qs, a[j], b[j]);
-      if (out_row < rows.len) {
+      if (in_walk && rows.len == kChunk) {
+        set_tile_chunk(sm + FwdHSmem::kO, 8192, out_row, (out_col >> 3) + part * 2, pack8(a));
+        set_tile_chunk(sm + FwdHSmem::kO, 8192, out_row, (out_col >> 3) + part * 2 + 1, pack8(a + 8));
+      } else if (out_row < rows.len) {
         __nv_bfloat16* dst = o + int64_t(rows.start + out_row) * v_stride + hv * kDim + out_col + part * 16;
         reinterpret_cast<uint4*>(dst)[0] = pack8(a);
         reinterpret_cast<uint4*>(dst)[1] = pack8(a + 8);
+      }
+      if (in_walk && part == 1) {
+        fence_async_smem();
+        mbar_arrive(&bar_out);
+        ++tiles_out;
       }
     };
 
@@ -637,8 +666,6 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
       int next_start = 0, next_len = 0;
       if (c + 1 < c_end) next_start = chunk_start[c + 1], next_len = chunk_len[c + 1];
       uint8_t* st = sm + stage * FwdHSmem::kStage;
-      // the previous step's tape store has read the state tile
-      if (tapes && step > 0 && !abort.wait(&bar_free_h, par ^ 1u)) break;
       // A. h_tape = bf16(h): this thread's half row -> shared (block `half`)
 #pragma unroll
       for (int cc = 0; cc < 8; ++cc) set_tile_chunk(sm + FwdHSmem::kH, 16384, krow, half * 8 + cc, pack8(h + 8 * cc));
@@ -655,33 +682,38 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
       tc_fence_before();
       mbar_arrive(&bar_h);
       // while the first product runs: the previous chunk's output, the next chunk's gates
-      if (fused && step > 0) write_output(c - 1, 0, cur);  // `cur` still describes chunk c - 1 here
+      if (fused && step > 0) write_output(c - 1, 0, cur, true);  // `cur` still describes chunk c - 1 here
       if (c + 1 < c_end) prefetch_gates(c + 1, stage ^ 1, next_start, next_len);
-      if (!alive || !abort.wait(&bar_d1, par)) break;
       // every epilogue thread's writes of this step (cleared rows, gates) are visible past the barrier they all
       // arrived on
-      if (!abort.wait(&bar_h, par)) break;
-      tc_fence_after();
-
-      // B. v_new = u - D1; vs = bf16(rowscale v_new)  (the previous step's tape store has read the v_new tile)
-      if (tapes && step > 0 && !abort.wait(&bar_free_vn, par ^ 1u)) break;
+      if (!alive || !abort.wait(&bar_h, par)) break;
+      // what B needs besides the product, read while the product runs: this thread's piece of u and the gates' factors
       const float* g2 = s_g2 + stage * 128;
       const float g_last = kda ? g2[krow] : g2[len - 1];  // KDA: this thread's key channel
+      // row i = 16 quad + lane % 16; logical V columns (lane / 16) * 64 + half * 32 .. + 32
+      const int i = quad * 16 + (lane & 15);
+      const int lcol = (lane >> 4) * 64 + half * 32;
+      const bool live = i < len;
+      const bool by_hand = tapes && len < kChunk;  // a ragged chunk: no 64-row box may be stored
+      const float rs = live ? (kda ? 1.f : fast_exp2(g_last - g2[i])) : 0.f;
+      const float qs_next = kda ? scale : scale * fast_exp2(g2[i]);
+      const float gamma = fast_exp2(g_last);
+      uint4 uraw[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) uraw[jj] = tile_chunk(st + FwdHSmem::kU, 8192, i, (lcol >> 3) + jj);
+      // B. v_new = u - D1; vs = bf16(rowscale v_new)  (the previous step's tape store has read the v_new tile)
+      if (tapes && step > 0 && !abort.wait(&bar_free_vn, par ^ 1u)) break;
+      if (!abort.wait(&bar_d1, par)) break;
+      tc_fence_after();
       {
-        // row i = 16 quad + lane % 16; logical V columns (lane / 16) * 64 + half * 32 .. + 32
-        const int i = quad * 16 + (lane & 15);
-        const int lcol = (lane >> 4) * 64 + half * 32;
-        const bool live = i < len;
-        const bool by_hand = tapes && len < kChunk;  // a ragged chunk: no 64-row box may be stored
-        const float rs = live ? (kda ? 1.f : fast_exp2(g_last - g2[i])) : 0.f;
         __nv_bfloat16* vrow = v_new + int64_t(start + i) * v_stride + hv * kDim + lcol;
         float d[32];
-        tmem_ld32(tmem_addr(tmem, warp, half * 32), d);
+        tmem_ld32_halves(tmem_addr(tmem, warp, half * 32), d);
         tmem_ld_wait();
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
           float uv[8], vs[8];
-          unpack8(tile_chunk(st + FwdHSmem::kU, 8192, i, (lcol >> 3) + jj), uv);
+          unpack8(uraw[jj], uv);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             uv[e] = live ? uv[e] - d[jj * 8 + e] : 0.f;
@@ -694,18 +726,19 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
         }
         if (fused) {  // what the output's epilogue needs one step from now
           prev = cur;
-          cur = {start, len, kda ? scale : scale * fast_exp2(g2[i])};
+          cur = {start, len, qs_next};
         }
       }
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(&bar_vs);
-      if (fused && step > 0) write_output(c - 1, 1, prev);
+      if (fused && step > 0) write_output(c - 1, 1, prev, true);
+      // this step's tape store has read the state tile (long ago: asked here, off the path to the next step's A)
+      if (tapes && !abort.wait(&bar_free_h, par)) break;
       if (!abort.wait(&bar_d2, par)) break;
       tc_fence_after();
 
       // C. h = gamma h + D2
-      const float gamma = fast_exp2(g_last);
 #pragma unroll
       for (int p = 0; p < 2; ++p) {
         float d[32];
@@ -718,8 +751,8 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
       start = next_start, len = next_len;
     }
     if (fused && c_end > c_begin && alive && !abort.raised()) {
-      write_output(c_end - 1, 0, cur);
-      write_output(c_end - 1, 1, cur);
+      write_output(c_end - 1, 0, cur, false);
+      write_output(c_end - 1, 1, cur, false);
     }
     cp_async_wait_all();
 
@@ -929,9 +962,11 @@ int launch_fwd_h(const MekGdnDims* d, const void* k, const void* w, const void* 
     if (int rc = make_rows_map(&maps.q, fused.q, d->total_tokens, d->num_qk_heads, what, d->qk_pitch)) return rc;
     if (int rc = make_tiles_map(&maps.aqk, fused.aqk, int64_t(d->num_chunks) * d->num_v_heads, 64, 64, what))
       return rc;
+    if (int rc = make_rows_map(&maps.o_out, fused.o, d->total_tokens, d->num_v_heads, what)) return rc;
   } else {
     maps.q = maps.k;  // never read
     maps.aqk = maps.k;
+    maps.o_out = maps.k;
   }
   if (plan.seg_flags == nullptr) {  // an ordinary walk writes the two tapes
     if (!h_tape || !v_new) return fail(MEK_ERR_INVALID, "%s: h_tape or v_new is null", what);
