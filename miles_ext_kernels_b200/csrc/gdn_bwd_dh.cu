@@ -152,8 +152,7 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
     for (int c = c_end - 1; c >= c_begin; --c) {
       const uint32_t par = uint32_t(c_end - 1 - c) & 1u;
       const uint32_t sst = sbase + par * BwdDhSmem::kStage;
-      const Operand op_k{sst + BwdDhSmem::kK, 8192}, op_do{sst + BwdDhSmem::kDO, 8192};
-      const Operand op_aqk{sst + BwdDhSmem::kAqk, 8192};
+      const Operand op_do{sst + BwdDhSmem::kDO, 8192}, op_aqk{sst + BwdDhSmem::kAqk, 8192};
       if (!abort.wait(&bar_h, par)) break;
       tc_fence_after();
       umma_gemm<64, 128>(tmem + kD1b, op_aqk, true, op_do, true, 64, false);   // Aqk^T do
