@@ -64,8 +64,9 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
   extern __shared__ uint8_t raw[];
   // bar_h: the state tile and this chunk's operand tiles are ready; bar_vs: the dv_new tile and do_g are ready (every
   // epilogue thread arrives on each); bar_d1 / bar_d2: the commits of the step's two groups of products;
+  // bar_seen: the copy warp is past this step's wait for a free stage
   // bar_free_h / bar_free_dv: the copy warp's store of this step has read the state tile / the dv_new tile
-  __shared__ uint64_t bar_load[2], bar_h, bar_vs, bar_d1, bar_d2, bar_free_h, bar_free_dv;
+  __shared__ uint64_t bar_load[2], bar_h, bar_vs, bar_d1, bar_d2, bar_free_h, bar_free_dv, bar_seen;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
     mbar_init(&bar_d1, 2);  // one commit from each issuing thread
     mbar_init(&bar_d2, 1);
     mbar_init(&bar_free_h, 1);
+    mbar_init(&bar_seen, 1);
     mbar_init(&bar_free_dv, 1);
     fence_mbar_init();
     abort_flag = 0;
@@ -131,8 +133,7 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
       const uint32_t par = uint32_t(c_end - 1 - c) & 1u;
       const uint32_t sst = sbase + par * BwdDhSmem::kStage;
       const Operand op_k{sst + BwdDhSmem::kK, 8192}, op_q{sst + BwdDhSmem::kQ, 8192};
-      const Operand op_w{sst + BwdDhSmem::kW, 8192}, op_do{sst + BwdDhSmem::kDO, 8192};
-      const Operand op_aqk{sst + BwdDhSmem::kAqk, 8192};
+      const Operand op_w{sst + BwdDhSmem::kW, 8192};
       if (!abort.wait(&bar_h, par)) break;
       tc_fence_after();
       // The two [64 x 128] products of the step's first group go out as one chain of N = 128 instructions each, this
@@ -177,13 +178,20 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
         if (step > 0 && !abort.wait(&bar_d2, par ^ 1u)) break;
         load(c - 1, par ^ 1u);
       }
+      // "This thread is past its wait for a free stage": the epilogue threads wait for it before they release the
+      // step's second group of products, so the barrier waited on above cannot complete twice before this thread has
+      // looked at it (a wait by parity would then miss the phase for good); and this thread in turn waits for the
+      // epilogue's release (bar_vs) before its next step, so neither barrier runs ahead of its waiter.
+      mbar_arrive(&bar_seen);
       if (tapes) {
         if (!abort.wait(&bar_h, par)) break;
         tma_store_tile128(&maps.dh_out, 0, int((int64_t(c) * num_v_heads + hv) * 128), sbase + BwdDhSmem::kDH, 16384);
         tma_store_commit();
         tma_store_wait_read();
         mbar_arrive(&bar_free_h);
-        if (!abort.wait(&bar_vs, par)) break;
+      }
+      if (!abort.wait(&bar_vs, par)) break;
+      if (tapes) {
         if (chunk_len[c] == kChunk) {  // a ragged chunk's rows are stored by the epilogue threads
           tma_store_tile128(&maps.dv_out, hv * kDim, chunk_start[c], sbase + BwdDhSmem::kDV, 8192);
           tma_store_commit();
@@ -276,6 +284,9 @@ __global__ void __launch_bounds__(kAdjThreads) gdn_bwd_dh_kernel(
       const float gamma = fast_exp2(g_last);
       // the previous step's tape store has read the dv_new tile
       if (tapes && step > 0 && !abort.wait(&bar_free_dv, par ^ 1u)) { alive = false; break; }
+      // The copy warp is past its wait for a free stage.  Asked before the arrival that releases the step's second
+      // group of products: the barrier that the copy warp waits on therefore cannot complete twice behind its back.
+      if (!abort.wait(&bar_seen, par)) { alive = false; break; }
       if (!abort.wait(&bar_d1, par)) { alive = false; break; }
       tc_fence_after();
 

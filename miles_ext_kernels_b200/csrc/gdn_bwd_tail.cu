@@ -344,6 +344,20 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
       }
       // the other q / k buffer is free: the previous pair is done
       if (last_of_pair && has_next_pair && loader) load_qk(next_pair, qk_buf ^ 1);
+      // Into L2 ahead of their copies into shared memory, whose buffers are free only a phase before they are read:
+      // this item's u and w, the next item's states and row tiles.
+      if (loader) {
+        tma_prefetch_tile128(&maps.u, hv * kDim, start);
+        tma_prefetch_tile128(&maps.w, hv * kDim, start);
+        if (has_next) {
+          tma_prefetch_tile128(&maps.h, 0, int(nx.tile * 128));
+          tma_prefetch_tile128(&maps.dh, 0, int(nx.tile * 128));
+          tma_prefetch_tile128(&maps.d_o, nx.hv * kDim, nx.start);
+          tma_prefetch_tile128(&maps.v_new, nx.hv * kDim, nx.start);
+          tma_prefetch_tile128(&maps.dv_new, nx.hv * kDim, nx.start);
+          tma_prefetch_tile128(&maps.v, nx.hv * kDim, nx.start);
+        }
+      }
 
       // ---- phase A: everything that needs only loaded tiles -------------------------------------------------------
       if (issuer) {
@@ -410,6 +424,107 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
       mma_wait2();
       __syncthreads();  // every thread is past its reads of h / dh: epilogue A overwrites operand buffers
       {
+        // dw -> its tile (the h region), phase B's operand; the phase's other results wait for a product to run under
+        float wv[kTailW];
+        tail_tmem_ld(tmem_addr(tmem, warp, kColT1 + ch * kTailW), wv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < kTailJ; ++jj)
+          set_tile_chunk(sm + TailSmem::kH, 8192, row, lchunk + jj, pack8(wv + jj * 8));
+      }
+      stage_sync();
+      // do and v_new are done with: this value head's u and w take their buffers; then the next item's Aqk
+      if (loader) {
+        load_uw(it);
+        if (has_next) load_aqk(nx);
+      }
+      if (has_next) load_scalars(nx, item_parity ^ 1);
+
+      // ---- phase B: dq += dS k ; dk += dS^T q ; dkb = A^T dw ---------------------------------------------------------
+      if (issuer) {
+        gemm128(kColDQ, op_b8, false, op_k, true, 64, gi > 0);
+        gemm128(kColDK, op_b8, true, op_q, true, 64, gi > 0);
+        umma_commit(&bar);
+      }
+      if (issuer2) {
+        gemm128(kColT1, op_a, true, op_dw, true, 64, false);  // dkb takes dw's columns; dkh, dq2 and dvb stay
+        umma_commit(&bar2);
+      }
+      {
+        // under phase B's products: dvb -> dv, dbeta, and its tile (the v buffer, read first), phase C's operand
+        float y[kTailW];
+        tail_tmem_ld(tmem_addr(tmem, warp, kColT3 + ch * kTailW), y);
+        tmem_ld_wait();
+        float dot_v = 0.f;
+        uint4 vraw[kTailJ];
+#pragma unroll
+        for (int jj = 0; jj < kTailJ; ++jj) vraw[jj] = tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj);
+        __syncwarp();
+#pragma unroll
+        for (int jj = 0; jj < kTailJ; ++jj) {
+          float vv[8], out[8];
+          unpack8(vraw[jj], vv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            dot_v = fmaf(y[jj * 8 + e], vv[e], dot_v);
+            out[e] = y[jj * 8 + e] * beta_row;
+          }
+          set_tile_chunk(sm + TailSmem::kH + 16384, 8192, row, lchunk + jj, pack8(out));
+        }
+        dB += dot_v;
+        // every thread reads only its own (row, chunk) cells of the v tile and rewrites exactly those with dvb
+#pragma unroll
+        for (int jj = 0; jj < kTailJ; ++jj) set_tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj, pack8(y + jj * 8));
+      }
+      // dAqk's sums are read here, before the block barrier behind which phase C's epilogue rewrites them; they join
+      // the gate gradient in the order they always did, after dkh's and dq2's
+      const float aqk_sums = (owner && ch == 0) ? four(s_rs, row) - four(s_cs, row) : 0.f;
+      mma_wait2();
+      {
+        // dkb -> its tile, phase C's operand; its sums wait until phase C's products run
+        float dkb[kTailW];
+        tail_tmem_ld(tmem_addr(tmem, warp, kColT1 + ch * kTailW), dkb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < kTailJ; ++jj)
+          set_tile_chunk(sm + TailSmem::kDVN, 8192, row, lchunk + jj, pack8(dkb + jj * 8));  // dv_new is done with
+      }
+      if (!mbar_wait(&bar_uw, item_parity)) abort.raise();  // u and w have landed
+      if (len < kChunk) {
+        clear_tile_rows<kTailThreads>(sm + TailSmem::kDO, len, tid);
+        clear_tile_rows<kTailThreads>(sm + TailSmem::kVN, len, tid);
+      }
+      stage_sync();
+      // dv leaves from its tile (the upper half of the h region) by one bulk store; a ragged chunk's rows by hand
+      if (len < kChunk) {
+        store_tile<64, 128, kTailThreads>(sm + TailSmem::kH + 16384, 8192, dv + int64_t(start) * dv_pitch + hv * kDim,
+                                          dv_pitch, len, tid);
+        __syncthreads();  // the tile is read: the next item's states may land on it
+      }
+      if (loader) {
+        if (len == kChunk) {
+          tma_store_tile128(&maps.dv_out, hv * kDim, start, sbase + TailSmem::kH + 16384, 8192);
+          tma_store_commit();
+        }
+        if (has_next) {  // h / dh (and the dw tile) and A are done with, once the dv tile has been read
+          tma_store_wait_read();
+          load_states(nx);
+        }
+      }
+
+      // ---- phase C: Y = bf16(dkb) w^T + bf16(dvb) u^T ; KK = k k^T ---------------------------------------------------
+      if (issuer) {
+        // Y as two chains into two accumulators (T3 is free by now: dvb was read under phase B); the epilogue adds them
+        umma_gemm_pair<64, 64>(tmem + kColTa, op_dkb, false, op_w, false, 128, false, false, tmem + kColT3, op_dvb,
+                               false, op_u, false, 128, false, false);
+        umma_commit(&bar);
+      }
+      if (issuer2) {
+        if (gi == 0) umma_gemm<64, 64>(tmem + kColTb, op_k, false, op_k, false, 128, false);  // KK: once per pair
+        umma_commit(&bar2);
+      }
+      // Under phase C's products (which write other columns): what of phase A's and B's results no product reads.
+      {
         // dkh and dq2 pieces: the scaled terms go to the register accumulators, their row dots to the gate gradient
         float a[kTailW], b[kTailW];
         tail_tmem_ld(tmem_addr(tmem, warp, kColT0 + ch * kTailW), a);
@@ -433,65 +548,11 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
         dG += dot_q - dot_k;
         gdot += dot_k;
       }
+      if (owner && ch == 0) dG += aqk_sums;
       {
-        // dw -> its tile (the h region); dvb -> dv, dbeta, and its tile (the v buffer, read first)
-        float wv[kTailW], y[kTailW];
-        tail_tmem_ld(tmem_addr(tmem, warp, kColT1 + ch * kTailW), wv);
-        tail_tmem_ld(tmem_addr(tmem, warp, kColT3 + ch * kTailW), y);
-        tmem_ld_wait();
-        float dot_v = 0.f;
-        uint4 vraw[kTailJ];
-#pragma unroll
-        for (int jj = 0; jj < kTailJ; ++jj) vraw[jj] = tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj);
-        __syncwarp();
-#pragma unroll
-        for (int jj = 0; jj < kTailJ; ++jj) {
-          float vv[8], out[8];
-          unpack8(vraw[jj], vv);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            dot_v = fmaf(y[jj * 8 + e], vv[e], dot_v);
-            out[e] = y[jj * 8 + e] * beta_row;
-          }
-          set_tile_chunk(sm + TailSmem::kH + 16384, 8192, row, lchunk + jj, pack8(out));
-          set_tile_chunk(sm + TailSmem::kH, 8192, row, lchunk + jj, pack8(wv + jj * 8));
-        }
-        dB += dot_v;
-        // every thread reads only its own (row, chunk) cells of the v tile and rewrites exactly those with dvb
-#pragma unroll
-        for (int jj = 0; jj < kTailJ; ++jj) set_tile_chunk(sm + TailSmem::kV, 8192, row, lchunk + jj, pack8(y + jj * 8));
-      }
-      stage_sync();
-      // dv leaves from its tile (the upper half of the h region) by one bulk store; a ragged chunk's rows by hand.
-      // do and v_new are done with: this value head's u and w take their buffers; then the next item's Aqk
-      if (len < kChunk)
-        store_tile<64, 128, kTailThreads>(sm + TailSmem::kH + 16384, 8192, dv + int64_t(start) * dv_pitch + hv * kDim,
-                                          dv_pitch, len, tid);
-      if (loader) {
-        if (len == kChunk) {
-          tma_store_tile128(&maps.dv_out, hv * kDim, start, sbase + TailSmem::kH + 16384, 8192);
-          tma_store_commit();
-        }
-        load_uw(it);
-        if (has_next) load_aqk(nx);
-      }
-      if (has_next) load_scalars(nx, item_parity ^ 1);
-
-      // ---- phase B: dq += dS k ; dk += dS^T q ; dkb = A^T dw ---------------------------------------------------------
-      if (issuer) {
-        gemm128(kColDQ, op_b8, false, op_k, true, 64, gi > 0);
-        gemm128(kColDK, op_b8, true, op_q, true, 64, gi > 0);
-        umma_commit(&bar);
-      }
-      if (issuer2) {
-        gemm128(kColT0, op_a, true, op_dw, true, 64, false);
-        umma_commit(&bar2);
-      }
-      if (owner && ch == 0) dG += four(s_rs, row) - four(s_cs, row);
-      mma_wait2();
-      {
+        // dkb's part of dk and of the beta / gate gradients
         float dkb[kTailW];
-        tail_tmem_ld(tmem_addr(tmem, warp, kColT0 + ch * kTailW), dkb);
+        tail_tmem_ld(tmem_addr(tmem, warp, kColT1 + ch * kTailW), dkb);
         tmem_ld_wait();
         float dot_k = 0.f, dot_kb = 0.f;
 #pragma unroll
@@ -505,32 +566,9 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
             dot_kb = fmaf(x, round_bf16(kk[e] * sk), dot_kb);  // kb = bf16(beta 2^G k), the forward's operand
             dk_reg[jj * 8 + e] = fmaf(sk, x, dk_reg[jj * 8 + e]);
           }
-          set_tile_chunk(sm + TailSmem::kDVN, 8192, row, lchunk + jj, pack8(dkb + jj * 8));  // dv_new is done with
         }
         dB += eg * dot_k;
         dG += dot_kb;
-      }
-      if (!mbar_wait(&bar_uw, item_parity)) abort.raise();  // u and w have landed
-      if (len < kChunk) {
-        clear_tile_rows<kTailThreads>(sm + TailSmem::kDO, len, tid);
-        clear_tile_rows<kTailThreads>(sm + TailSmem::kVN, len, tid);
-      }
-      stage_sync();
-      if (has_next && loader) {  // h / dh (and the dw tile) and A are done with, once the dv tile has been read
-        tma_store_wait_read();
-        load_states(nx);
-      }
-
-      // ---- phase C: Y = bf16(dkb) w^T + bf16(dvb) u^T ; KK = k k^T ---------------------------------------------------
-      if (issuer) {
-        // Y as two chains into two accumulators (T1 is free by now); the epilogue adds them
-        umma_gemm_pair<64, 64>(tmem + kColTa, op_dkb, false, op_w, false, 128, false, false, tmem + kColT1, op_dvb,
-                               false, op_u, false, 128, false, false);
-        umma_commit(&bar);
-      }
-      if (issuer2) {
-        if (gi == 0) umma_gemm<64, 64>(tmem + kColTb, op_k, false, op_k, false, 128, false);  // KK: once per pair
-        umma_commit(&bar2);
       }
       mma_wait2();
       {
@@ -538,7 +576,7 @@ __global__ void __launch_bounds__(kTailThreads) gdn_bwd_tail_kernel(
         // beta dL D . KK to the gate gradient (row sums - column sums)
         float s[8], s2[8], kk[8];
         tmem_ld_frag16(tmem_addr(tmem, warp, kColTa + ch * 16), s);
-        tmem_ld_frag16(tmem_addr(tmem, warp, kColT1 + ch * 16), s2);
+        tmem_ld_frag16(tmem_addr(tmem, warp, kColT3 + ch * 16), s2);
         tmem_ld_frag16(tmem_addr(tmem, warp, kColTb + ch * 16), kk);
         const float g_lo = g2[fr], g_hi = g2[fr + 8], b_lo = beta_s[fr], b_hi = beta_s[fr + 8];
         tmem_ld_wait();

@@ -431,9 +431,10 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
   // bar_vs: the v tiles are ready -- every epilogue thread arrives
   // bar_d1 / bar_d2 / bar_o: commits of the step's two products and of the fused output's products
   // bar_free_h / bar_free_vn: the copy warp's store of this step has read the state tile / the v_new tile
+  // bar_seen: the copy warp is past this step's wait for a free stage
   // bar_out / bar_free_o: the previous chunk's output tile is complete -- every epilogue thread arrives / its store has
   // read the tile
-  __shared__ uint64_t bar_load[2], bar_h, bar_vs, bar_d1, bar_d2, bar_o, bar_free_h, bar_free_vn, bar_out, bar_free_o;
+  __shared__ uint64_t bar_load[2], bar_h, bar_vs, bar_d1, bar_d2, bar_o, bar_free_h, bar_free_vn, bar_out, bar_free_o, bar_seen;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -480,6 +481,7 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
     mbar_init(&bar_free_vn, 1);
     mbar_init(&bar_out, kScanEpilogueThreads);
     mbar_init(&bar_free_o, 1);
+    mbar_init(&bar_seen, 1);
     fence_mbar_init();
     abort_flag = 0;
   }
@@ -553,13 +555,20 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
         if (c > c_begin && !abort.wait(fused ? &bar_o : &bar_d2, par ^ 1u)) break;
         load(c + 1, par ^ 1u);
       }
+      // "This thread is past its wait for a free stage": the epilogue threads wait for it before they release the
+      // step's second group of products, so the barrier waited on above cannot complete twice before this thread has
+      // looked at it (a wait by parity would then miss the phase for good); and this thread in turn waits for the
+      // epilogue's release (bar_vs) before its next step, so neither barrier runs ahead of its waiter.
+      mbar_arrive(&bar_seen);
       if (tapes) {
         if (!abort.wait(&bar_h, par)) break;
         tma_store_tile128(&maps.h_out, 0, int((int64_t(c) * num_v_heads + hv) * 128), sbase + FwdHSmem::kH, 16384);
         tma_store_commit();
         tma_store_wait_read();
         mbar_arrive(&bar_free_h);
-        if (!abort.wait(&bar_vs, par)) break;
+      }
+      if (!abort.wait(&bar_vs, par)) break;
+      if (tapes) {
         if (chunk_len[c] == kChunk) {  // a ragged chunk's rows are stored by the epilogue threads
           tma_store_tile128(&maps.v_new_out, hv * kDim, chunk_start[c], sbase + FwdHSmem::kVN, 8192);
           tma_store_commit();
@@ -703,6 +712,9 @@ __global__ void __launch_bounds__(kScanThreads) gdn_fwd_h_kernel(
       for (int jj = 0; jj < 4; ++jj) uraw[jj] = tile_chunk(st + FwdHSmem::kU, 8192, i, (lcol >> 3) + jj);
       // B. v_new = u - D1; vs = bf16(rowscale v_new)  (the previous step's tape store has read the v_new tile)
       if (tapes && step > 0 && !abort.wait(&bar_free_vn, par ^ 1u)) break;
+      // The copy warp is past its wait for a free stage.  Asked before the arrival that releases the step's second
+      // group of products: the barrier that the copy warp waits on therefore cannot complete twice behind its back.
+      if (!abort.wait(&bar_seen, par)) break;
       if (!abort.wait(&bar_d1, par)) break;
       tc_fence_after();
       {

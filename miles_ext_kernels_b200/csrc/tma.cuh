@@ -104,6 +104,16 @@ __device__ __forceinline__ void tma_load_tile128(uint32_t dst, uint32_t block_st
   tma_load_box(dst + block_stride, map, x + 64, y, bar);
 }
 
+// The same tile, asked into L2 only: a later copy of it into shared memory finds it there.
+__device__ __forceinline__ void tma_prefetch_tile128(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y)
+               : "memory");
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(x + 64), "r"(y)
+               : "memory");
+}
+
 // One box (64 columns x the map's box rows) from shared memory at `src` (1024-byte aligned, the swizzled block
 // layout) to the tensor at (x, y); joins the issuing thread's current bulk group.  Generic-proxy writes to the block
 // must have been fenced (fence.proxy.async) by their writers before the issuing thread learns of them.
